@@ -1,0 +1,111 @@
+/* zkb200 - C ABI of the B200 proving hot path (BN254 sumcheck provers, multilinear folds,
+ * KZH2/KZH3 commit/open multi-scalar multiplications).
+ *
+ * The reference (crate zk_torch_2) has no FFI for this path; its seams are Rust traits.  Each
+ * entry point below names the reference function it stands in for (paths relative to the
+ * reference crate root).  A Rust shim implements the traits on top of these calls.
+ *
+ * Conventions
+ *  - Fr / Fq elements cross the boundary as 4 x uint64_t little-endian limbs in Montgomery form
+ *    (a * 2^256 mod p): byte-identical to arkworks' in-memory Fp256, so a Vec<Fr> can be passed
+ *    by pointer.
+ *  - G1 affine points are {x[4], y[4]} (64 bytes, Montgomery mod q); the point at infinity is
+ *    encoded as x = y = 0 (not on the curve, so unambiguous).
+ *  - G1 projective results are Jacobian {X[4], Y[4], Z[4]} (96 bytes), Z = 0 for infinity;
+ *    compare after normalising, as with arkworks' Projective.
+ *  - Every function returns ZK_OK (0) or a negative zk_status; zk_last_error() gives the
+ *    message of the calling thread's last failure.  A Rust shim turns a non-zero status into
+ *    the panic / Err(String) the trait in question documents.
+ *  - `mem` arguments say where a caller buffer lives: ZK_MEM_HOST or ZK_MEM_DEVICE (a CUDA
+ *    device pointer on the context's GPU).  Inputs are never modified.
+ *  - A zk_ctx may be shared by host threads; calls on one context are serialised.
+ */
+#ifndef ZKB200_H
+#define ZKB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct zk_ctx zk_ctx;
+typedef struct zk_transcript zk_transcript;
+
+typedef enum zk_status {
+  ZK_OK = 0,
+  ZK_ERR_ARG = -1,         /* shape / argument errors: the reference's assert! panics */
+  ZK_ERR_OOM = -2,         /* device allocation failed */
+  ZK_ERR_CUDA = -3,        /* a CUDA call or kernel failed */
+  ZK_ERR_TIMEOUT = -4,     /* a bounded device-side wait ran out */
+  ZK_ERR_FS_CALLBACK = -5, /* the caller's Fiat-Shamir callback returned non-zero */
+  ZK_ERR_COMM = -6         /* multi-GPU exchange failed */
+} zk_status;
+
+typedef enum zk_mem { ZK_MEM_HOST = 0, ZK_MEM_DEVICE = 1 } zk_mem;
+
+#define ZK_MAX_POLYS 4
+
+/* ---- context ------------------------------------------------------------------------- */
+/* One context per GPU (and per process rank).  No counterpart in the reference: it holds
+ * the stream and scratch that rayon's global pool and Vec allocations stand for there. */
+int zk_init(int device, zk_ctx** out);
+void zk_free(zk_ctx* ctx);
+const char* zk_last_error(void);
+/* Number of kernels this library has launched on the context since it was created. */
+uint64_t zk_launch_count(const zk_ctx* ctx);
+/* Device memory owned by the caller (thin cudaMalloc / cudaFree / cudaMemcpy wrappers for
+ * hosts that do not link the CUDA runtime themselves). */
+int zk_device_alloc(zk_ctx* ctx, size_t bytes, void** out);
+int zk_device_free(zk_ctx* ctx, void* ptr);
+int zk_device_copy(zk_ctx* ctx, void* dst, zk_mem dst_mem, const void* src, zk_mem src_mem, size_t bytes);
+int zk_device_sync(zk_ctx* ctx);
+
+/* ---- Fiat-Shamir transcript: src/util/transcript.rs:13-46 (merlin 3.0.0) -------------- */
+zk_transcript* zk_transcript_new(const uint8_t* label, size_t label_len);     /* Transcript::new */
+zk_transcript* zk_transcript_clone(const zk_transcript* t);                   /* #[derive(Clone)] */
+void zk_transcript_free(zk_transcript* t);
+void zk_transcript_append_message(zk_transcript* t, const uint8_t* label, size_t label_len, const uint8_t* msg,
+                                  size_t msg_len);                            /* :19-21 */
+void zk_transcript_append_u64(zk_transcript* t, const uint8_t* label, size_t label_len, uint64_t value); /* :23-25 */
+void zk_transcript_append_scalar(zk_transcript* t, const uint8_t* label, size_t label_len,
+                                 const uint64_t scalar[4]);                   /* :27-30, Montgomery in */
+void zk_transcript_challenge_bytes(zk_transcript* t, const uint8_t* label, size_t label_len, uint8_t* out,
+                                   size_t n);
+void zk_transcript_challenge_scalar(zk_transcript* t, const uint8_t* label, size_t label_len,
+                                    uint64_t out[4]);                         /* :38-42, Montgomery out */
+
+/* Per-round Fiat-Shamir callback, for callers that keep their own transcript (the Rust shim
+ * passes the real merlin crate through this).  msgs: n_msgs round-message scalars; the
+ * callback absorbs them and writes the round challenge.  Return 0 on success. */
+typedef int (*zk_fs_round_fn)(void* user, const uint64_t* msgs, uint32_t n_msgs, uint64_t challenge_out[4]);
+
+/* ---- sumcheck provers ----------------------------------------------------------------- */
+/* LinearSumcheckProver::prove, src/crypto/sumcheck/linear_prover.rs:43-76 (rounds :82-178,
+ * final :181-190).  The header (num_var, num_poly) is absorbed by the caller as ::new does
+ * (:29-41).  tables: num_poly pointers to 2^num_var elements each.  With fs == NULL the
+ * built-in transcript `tr` absorbs each message scalar under "round_message" and draws
+ * "challenge".  Outputs (host): round_msgs[num_var][num_poly+1], challenges[num_var],
+ * final_table0[num_poly] (= a_arrays[i][0] after the last round), final_eval. */
+int zk_sumcheck_linear_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, const uint64_t* const* tables,
+                             zk_mem tables_mem, zk_fs_round_fn fs, void* fs_user, zk_transcript* tr,
+                             uint64_t* round_msgs, uint64_t* challenges, uint64_t* final_table0,
+                             uint64_t* final_eval);
+
+/* ---- multilinear helpers --------------------------------------------------------------- */
+/* DenseMLPoly::fix_variables, src/util/poly.rs:842-887: binds the k lowest variables of a
+ * 2^n table to point[0..k); out receives 2^(n-k) elements. */
+int zk_fold_lsb(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, uint32_t k, const uint64_t* point,
+                uint64_t* out, zk_mem out_mem);
+
+/* ---- measurement ---------------------------------------------------------------------- */
+/* Throughput probe for the integer roofline (no counterpart in the reference).  kind 0: 32-bit
+ * multiply-add, 1: 32x32+64 wide multiply-add, 2 / 3: Montgomery product in Fr / Fq.  Runs the
+ * probe twice and reports the second run: elapsed milliseconds and operations executed. */
+int zk_microbench(zk_ctx* ctx, int kind, int blocks, int threads, int iters, float* ms_out, double* ops_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZKB200_H */

@@ -1,0 +1,37 @@
+// Host build of the device field / curve arithmetic, exported for the CPU unit tests.
+// The carry chains compile to their portable C form here, so the algorithms (not the PTX)
+// are what these symbols exercise.
+#include "../../zkes_b200/csrc/ff.cuh"
+#include <cstring>
+using namespace zk;
+
+template <class P> static void ld(Fp<P>& x, const uint32_t* p) { memcpy(x.v, p, 32); }
+
+#define DEF(name, P)                                                                         \
+  extern "C" void zkh_##name##_mul(const uint32_t* a, const uint32_t* b, uint32_t* r) {      \
+    Fp<P> x, y; ld(x, a); ld(y, b); Fp<P> z = mul(x, y); memcpy(r, z.v, 32); }               \
+  extern "C" void zkh_##name##_add(const uint32_t* a, const uint32_t* b, uint32_t* r) {      \
+    Fp<P> x, y; ld(x, a); ld(y, b); Fp<P> z = add(x, y); memcpy(r, z.v, 32); }               \
+  extern "C" void zkh_##name##_sub(const uint32_t* a, const uint32_t* b, uint32_t* r) {      \
+    Fp<P> x, y; ld(x, a); ld(y, b); Fp<P> z = sub(x, y); memcpy(r, z.v, 32); }               \
+  extern "C" void zkh_##name##_inv(const uint32_t* a, uint32_t* r) {                         \
+    Fp<P> x; ld(x, a); Fp<P> z = inverse(x); memcpy(r, z.v, 32); }                           \
+  extern "C" void zkh_##name##_to_mont(const uint32_t* a, uint32_t* r) {                     \
+    Fp<P> x; ld(x, a); Fp<P> z = to_mont(x); memcpy(r, z.v, 32); }                           \
+  extern "C" void zkh_##name##_from_mont(const uint32_t* a, uint32_t* r) {                   \
+    Fp<P> x; ld(x, a); Fp<P> z = from_mont(x); memcpy(r, z.v, 32); }                         \
+  /* sum of n products through the lazy accumulator, trimmed every kLazyProducts */         \
+  extern "C" void zkh_##name##_dot(const uint32_t* a, const uint32_t* b, int n, uint32_t* r) { \
+    Wide acc; memset(&acc, 0, sizeof acc); int pending = 0;                                  \
+    for (int i = 0; i < n; i++) {                                                            \
+      Wide w; mul_wide(w, a + 8 * i, b + 8 * i); wide_add(acc, w);                           \
+      if (++pending == kLazyProducts) { wide_trim<P>(acc); pending = 0; }                    \
+    }                                                                                        \
+    wide_trim<P>(acc); Fp<P> z = redc<P>(acc); memcpy(r, z.v, 32); }
+
+DEF(fr, FrParams)
+DEF(fq, FqParams)
+
+extern "C" void zkh_mul_wide(const uint32_t* a, const uint32_t* b, uint32_t* r) {
+  Wide w; mul_wide(w, a, b); memcpy(r, w.v, 64);
+}

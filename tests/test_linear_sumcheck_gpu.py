@@ -1,0 +1,164 @@
+"""GPU parity of LinearSumcheckProver and the LSB fold against the big-integer oracle.
+
+Mirrors tests/test_linear_sumcheck.rs and tests/test_fix_variables.rs of the reference: small
+hand-checkable tables first, then seeded random tables; every proof must be accepted by the
+restated SumcheckVerifier and match the oracle prover bit for bit."""
+import random
+
+import pytest
+
+import pyoracle as o
+from zkes_b200 import DenseMLPoly, LinearSumcheckProver, Transcript
+
+pytestmark = pytest.mark.gpu
+
+
+def run_both(ctx, tables, label=b"sumcheck"):
+    n = len(tables[0]).bit_length() - 1
+    ell = len(tables)
+    t = Transcript(label)
+    prover = LinearSumcheckProver(n, ell, t)
+    proof = prover.prove(ctx, [DenseMLPoly.from_evaluations(p) for p in tables], t)
+    ot = o.Transcript(label)
+    oprover = o.LinearSumcheckProver(n, ell, ot)
+    oproof = oprover.prove(tables, ot)
+    assert proof.round_messages == oproof.round_messages
+    assert prover.challenges == oprover.challenges
+    assert proof.final_eval == oproof.final_eval
+    assert [a[0] for a in prover.a_arrays] == [a[0] for a in oprover.a_arrays]
+    # transcripts end in the same state
+    assert t.challenge_scalar(b"after") == ot.challenge_scalar(b"after")
+    return prover, proof
+
+
+def verify(proof, n, ell, claimed, label=b"sumcheck"):
+    vt = o.Transcript(label)
+    v = o.SumcheckVerifier(n, ell, vt)
+    res, ch = v.verify(vt, proof.round_messages, claimed)
+    assert res is not None, "verifier rejected an honest proof"
+    assert res == proof.final_eval
+    return ch
+
+
+def test_constant_polynomials(ctx):  # test_linear_sumcheck.rs:19-62, claimed sum 4
+    _, proof = run_both(ctx, [[1, 1, 1, 1], [1, 1, 1, 1]])
+    assert len(proof.round_messages) == 2 and all(len(m) == 3 for m in proof.round_messages)
+    verify(proof, 2, 2, 4)
+
+
+def test_identity_polynomials(ctx):  # :65-110, claimed sum 1
+    _, proof = run_both(ctx, [[0, 1, 0, 1], [0, 0, 1, 1]])
+    verify(proof, 2, 2, 1)
+
+
+def test_single_variable(ctx):  # :113-134, one table, claimed sum 1
+    _, proof = run_both(ctx, [[0, 1]])
+    assert len(proof.round_messages) == 1 and len(proof.round_messages[0]) == 2
+    verify(proof, 1, 1, 1)
+
+
+def test_all_zero(ctx):  # :237-275, all-zero tables give all-zero messages
+    _, proof = run_both(ctx, [[0] * 8, [0] * 8])
+    assert all(v == 0 for m in proof.round_messages for v in m)
+    assert proof.final_eval == 0
+
+
+def test_deterministic(ctx):  # :428-473
+    rnd = random.Random(9)
+    tables = [[rnd.randrange(o.R_MOD) for _ in range(16)] for _ in range(2)]
+    _, p1 = run_both(ctx, tables)
+    _, p2 = run_both(ctx, tables)
+    assert p1.round_messages == p2.round_messages and p1.final_eval == p2.final_eval
+
+
+@pytest.mark.parametrize("ell", [1, 2, 3, 4])
+@pytest.mark.parametrize("n", [1, 2, 3, 5, 6, 7, 10])
+def test_random_tables(ctx, n, ell):
+    rnd = random.Random(1000 * ell + n)
+    edge = [0, 1, o.R_MOD - 1, o.R_MOD - 2]
+    tables = [[rnd.choice(edge) if rnd.random() < 0.1 else rnd.randrange(o.R_MOD) for _ in range(1 << n)]
+              for _ in range(ell)]
+    prover, proof = run_both(ctx, tables)
+    claimed = 0
+    for x in range(1 << n):
+        g = 1
+        for t in tables:
+            g = g * t[x] % o.R_MOD
+        claimed += g
+    ch = verify(proof, n, ell, claimed % o.R_MOD)
+    prod = 1
+    for t in tables:
+        prod = prod * o.evaluate_multilinear_extension(t, ch) % o.R_MOD
+    assert prod == proof.final_eval
+
+
+def test_bench_style_tables(ctx):  # benches/sumcheck_prover.rs:20-34: entry i*2^n + j + 1
+    n = 8
+    tables = [[i * (1 << n) + j + 1 for j in range(1 << n)] for i in range(2)]
+    run_both(ctx, tables, label=b"sumcheck_bench")
+
+
+def test_medium_size_many_blocks(ctx):
+    n = 14  # several tiles per warp and a multi-block grid reduction
+    rnd = random.Random(77)
+    tables = [[rnd.randrange(o.R_MOD) for _ in range(1 << n)] for _ in range(2)]
+    run_both(ctx, tables)
+
+
+def test_callback_transcript(ctx):
+    """The per-round callback form drives an external transcript (here the oracle's)."""
+    import ctypes
+    from zkes_b200.field import from_mont_array, to_mont_array
+
+    rnd = random.Random(5)
+    n = 6
+    tables = [[rnd.randrange(o.R_MOD) for _ in range(1 << n)] for _ in range(2)]
+    ext = o.Transcript(b"sumcheck")
+    ext.append_u64(b"num_var", n)
+    ext.append_u64(b"num_poly", 2)
+
+    def cb(user, msgs, n_msgs, out):
+        import numpy as np
+        vals = from_mont_array(np.ctypeslib.as_array(msgs, shape=(n_msgs, 4)))
+        for v in vals:
+            ext.append_scalar(b"round_message", v)
+        ch = to_mont_array([ext.challenge_scalar(b"challenge")])[0]
+        for k in range(4):
+            out[k] = int(ch[k])
+        return 0
+
+    dummy = Transcript(b"unused")
+    prover = LinearSumcheckProver(n, 2, dummy)
+    proof = prover.prove(ctx, [DenseMLPoly.from_evaluations(p) for p in tables], dummy, fs_callback=cb)
+    ot = o.Transcript(b"sumcheck")
+    op = o.LinearSumcheckProver(n, 2, ot)
+    oproof = op.prove(tables, ot)
+    assert proof.round_messages == oproof.round_messages and proof.final_eval == oproof.final_eval
+
+
+def test_shape_errors(ctx):  # linear_prover.rs:44-52 panics become ZK_ERR_ARG / assertions
+    t = Transcript(b"sumcheck")
+    prover = LinearSumcheckProver(3, 2, t)
+    with pytest.raises(AssertionError):
+        prover.prove(ctx, [DenseMLPoly.from_evaluations([1, 2, 3, 4])] * 2, t)
+    with pytest.raises(AssertionError):
+        prover.prove(ctx, [], t)
+
+
+# ---- fold: tests/test_fix_variables.rs dense cases
+def test_fix_variables_known_answers(ctx):
+    f = DenseMLPoly.from_evaluations([1, 2, 3, 4])
+    assert f.fix_variables(ctx, [0]).evaluations == [1, 3]  # :19-48
+    assert f.fix_variables(ctx, [1]).evaluations == [2, 4]
+    assert f.fix_variables(ctx, []).evaluations == [1, 2, 3, 4]
+    g = DenseMLPoly.from_evaluations(list(range(1, 9)))  # 3 variables, :89-122
+    assert g.fix_variables(ctx, [1, 0]).evaluations == [2, 6]
+    assert g.fix_variables(ctx, [0, 1, 1]).evaluations == [7]
+
+
+@pytest.mark.parametrize("n,k", [(1, 1), (5, 2), (6, 6), (9, 3), (13, 13), (15, 4)])
+def test_fix_variables_random(ctx, n, k):
+    rnd = random.Random(31 * n + k)
+    f = [rnd.randrange(o.R_MOD) for _ in range(1 << n)]
+    pt = [rnd.randrange(o.R_MOD) for _ in range(k)]
+    assert DenseMLPoly.from_evaluations(f).fix_variables(ctx, pt).evaluations == o.fix_variables(f, pt)

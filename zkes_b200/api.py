@@ -1,0 +1,169 @@
+"""Host-side mirror of the reference's interface for the proving hot path.
+
+Class and method names follow the Rust crate (src/crypto/sumcheck, src/util/poly.rs,
+src/util/transcript.rs) so tests read like the reference's own.  Every method forwards to the
+C ABI in libzkb200.so; nothing here computes field arithmetic on the proving path."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_void_p
+
+import numpy as np
+
+from . import _lib
+from ._lib import ZK_MEM_DEVICE, ZK_MEM_HOST, check, lib
+from .field import from_mont_array, to_mont_array
+
+
+def _ptr(a: np.ndarray) -> c_void_p:
+    return c_void_p(a.ctypes.data)
+
+
+class Context:
+    """One per GPU: stream and scratch (zk_init / zk_free)."""
+
+    def __init__(self, device: int = 0):
+        h = c_void_p()
+        check(lib.zk_init(device, ctypes.byref(h)), "zk_init")
+        self.handle = h
+        self.device = device
+
+    def close(self):
+        if self.handle:
+            lib.zk_free(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def launch_count(self) -> int:
+        return int(lib.zk_launch_count(self.handle))
+
+    def sync(self):
+        check(lib.zk_device_sync(self.handle), "zk_device_sync")
+
+
+class Transcript:
+    """src/util/transcript.rs:13-46."""
+
+    def __init__(self, label: bytes, _handle=None):
+        self.handle = _handle if _handle is not None else lib.zk_transcript_new(label, len(label))
+
+    def clone(self) -> "Transcript":
+        return Transcript(b"", _handle=lib.zk_transcript_clone(self.handle))
+
+    def __del__(self):
+        if getattr(self, "handle", None):
+            lib.zk_transcript_free(self.handle)
+            self.handle = None
+
+    def append_message(self, label: bytes, message: bytes):
+        lib.zk_transcript_append_message(self.handle, label, len(label), message, len(message))
+
+    def append_u64(self, label: bytes, value: int):
+        lib.zk_transcript_append_u64(self.handle, label, len(label), value)
+
+    def append_scalar(self, label: bytes, scalar: int):
+        a = to_mont_array([scalar])
+        lib.zk_transcript_append_scalar(self.handle, label, len(label), _ptr(a))
+
+    def append_scalars(self, label: bytes, scalars):
+        for s in scalars:
+            self.append_scalar(label, s)
+
+    def challenge_bytes(self, label: bytes, n: int) -> bytes:
+        buf = ctypes.create_string_buffer(n)
+        lib.zk_transcript_challenge_bytes(self.handle, label, len(label), buf, n)
+        return buf.raw
+
+    def challenge_scalar(self, label: bytes) -> int:
+        out = np.zeros((1, 4), dtype=np.uint64)
+        lib.zk_transcript_challenge_scalar(self.handle, label, len(label), _ptr(out))
+        return from_mont_array(out)[0]
+
+    def challenge_vector(self, label: bytes, n: int):
+        return [self.challenge_scalar(label) for _ in range(n)]
+
+
+class DenseMLPoly:
+    """src/util/poly.rs:764-960.  Evaluations are held as Montgomery limbs, on the host
+    (numpy (2^n, 4) uint64) or on the device (a raw device pointer plus length)."""
+
+    def __init__(self, n: int, evaluations=None, *, mont: np.ndarray = None, device_ptr: int = None):
+        self.n = n
+        self.device_ptr = device_ptr
+        if device_ptr is not None:
+            self.mont = None
+        elif mont is not None:
+            self.mont = np.ascontiguousarray(mont, dtype=np.uint64).reshape(-1, 4)
+        else:
+            self.mont = to_mont_array(evaluations)
+
+    @classmethod
+    def from_evaluations(cls, evaluations):
+        n = len(evaluations).bit_length() - 1
+        assert 1 << n == len(evaluations), "Vector length must be a power of 2"
+        return cls(n, evaluations)
+
+    def __len__(self):
+        return 1 << self.n if self.device_ptr is not None else self.mont.shape[0]
+
+    @property
+    def evaluations(self):
+        return from_mont_array(self.mont)
+
+    def fix_variables(self, ctx: Context, partial_point) -> "DenseMLPoly":
+        assert len(partial_point) <= self.n, "invalid size of partial point"
+        k = len(partial_point)
+        pt = to_mont_array(partial_point) if k else np.zeros((1, 4), dtype=np.uint64)
+        out = np.zeros((1 << (self.n - k), 4), dtype=np.uint64)
+        src = c_void_p(self.device_ptr) if self.device_ptr is not None else _ptr(self.mont)
+        mem = ZK_MEM_DEVICE if self.device_ptr is not None else ZK_MEM_HOST
+        check(lib.zk_fold_lsb(ctx.handle, self.n, src, mem, k, _ptr(pt), _ptr(out), ZK_MEM_HOST), "zk_fold_lsb")
+        return DenseMLPoly(self.n - k, mont=out)
+
+
+class SumcheckProof:
+    """src/crypto/sumcheck/prover.rs:9-14."""
+
+    def __init__(self, final_eval, round_messages):
+        self.final_eval = final_eval
+        self.round_messages = round_messages
+
+
+class LinearSumcheckProver:
+    """src/crypto/sumcheck/linear_prover.rs:13-191 on the GPU."""
+
+    def __init__(self, num_var: int, num_polys: int, transcript: Transcript):
+        transcript.append_u64(b"num_var", num_var)
+        transcript.append_u64(b"num_poly", num_polys)
+        self.num_var = num_var
+        self.num_poly = num_polys
+        self.challenges = []
+        self.a_arrays = []  # after prove: a_arrays[i][0], the fully bound value of table i
+
+    def prove(self, ctx: Context, instances, transcript: Transcript, fs_callback=None) -> SumcheckProof:
+        assert len(instances) > 0, "Polynomials cannot be empty"
+        assert len(instances) == self.num_poly, "Number of polynomials mismatch"
+        for i, p in enumerate(instances):
+            assert len(p) == 1 << self.num_var, f"Polynomial {i} has incorrect size"
+        L, n = self.num_poly, self.num_var
+        on_dev = instances[0].device_ptr is not None
+        ptrs = (c_void_p * L)(*[c_void_p(p.device_ptr) if on_dev else _ptr(p.mont) for p in instances])
+        msgs = np.zeros((max(n, 1), L + 1, 4), dtype=np.uint64)
+        chal = np.zeros((max(n, 1), 4), dtype=np.uint64)
+        fin_t = np.zeros((L, 4), dtype=np.uint64)
+        fin = np.zeros((1, 4), dtype=np.uint64)
+        cb = _lib.FS_ROUND_FN(fs_callback) if fs_callback is not None else None
+        check(lib.zk_sumcheck_linear_prove(ctx.handle, n, L, ptrs, ZK_MEM_DEVICE if on_dev else ZK_MEM_HOST,
+                                           ctypes.cast(cb, c_void_p) if cb else None, None,
+                                           None if cb else transcript.handle, _ptr(msgs), _ptr(chal), _ptr(fin_t),
+                                           _ptr(fin)), "zk_sumcheck_linear_prove")
+        self.challenges = from_mont_array(chal[:n])
+        self.a_arrays = [[v] for v in from_mont_array(fin_t)]
+        rm = [from_mont_array(msgs[r]) for r in range(n)]
+        return SumcheckProof(from_mont_array(fin)[0], rm)

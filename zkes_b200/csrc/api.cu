@@ -1,0 +1,226 @@
+// C ABI layer: context, transcript objects and the host-side round loops that drive the
+// kernels.  See include/zkb200.h for the contract of every entry point.
+#include "../../include/zkb200.h"
+#include "ctx.hpp"
+
+#include <cstdio>
+#include <string>
+
+using namespace zk;
+
+namespace zk {
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+}  // namespace zk
+
+struct zk_transcript {
+  MerlinTranscript m;
+  zk_transcript(const uint8_t* label, size_t n) : m(label, n) {}
+};
+
+extern "C" {
+
+const char* zk_last_error(void) { return g_last_error.c_str(); }
+
+int zk_init(int device, zk_ctx** out) {
+  if (!out) return fail(ZK_ERR_ARG, "zk_init: out is NULL");
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess) return fail(ZK_ERR_CUDA, "zk_init: no CUDA device: %s", cudaGetErrorString(e));
+  if (device < 0 || device >= count) return fail(ZK_ERR_ARG, "zk_init: device %d out of range (%d present)", device, count);
+  zk_ctx* c = new zk_ctx();
+  c->device = device;
+  int rc = c->setup();
+  if (rc != ZK_OK) {
+    delete c;
+    return rc;
+  }
+  *out = c;
+  return ZK_OK;
+}
+
+void zk_free(zk_ctx* ctx) {
+  if (!ctx) return;
+  ctx->teardown();
+  delete ctx;
+}
+
+uint64_t zk_launch_count(const zk_ctx* ctx) { return ctx ? ctx->launches.load() : 0; }
+
+int zk_device_alloc(zk_ctx* ctx, size_t bytes, void** out) {
+  if (!ctx || !out) return fail(ZK_ERR_ARG, "zk_device_alloc: NULL argument");
+  CtxLock lk(ctx);
+  cudaError_t e = cudaMalloc(out, bytes ? bytes : 1);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(ZK_ERR_OOM, "zk_device_alloc: %zu bytes: %s", bytes, cudaGetErrorString(e));
+  }
+  return ZK_OK;
+}
+
+int zk_device_free(zk_ctx* ctx, void* ptr) {
+  if (!ctx) return fail(ZK_ERR_ARG, "zk_device_free: NULL context");
+  CtxLock lk(ctx);
+  ZK_CUDA(cudaFree(ptr));
+  return ZK_OK;
+}
+
+int zk_device_copy(zk_ctx* ctx, void* dst, zk_mem dst_mem, const void* src, zk_mem src_mem, size_t bytes) {
+  if (!ctx || (bytes && (!dst || !src))) return fail(ZK_ERR_ARG, "zk_device_copy: NULL argument");
+  CtxLock lk(ctx);
+  ZK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, ctx->stream));
+  ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+  (void)dst_mem;
+  (void)src_mem;
+  return ZK_OK;
+}
+
+int zk_device_sync(zk_ctx* ctx) {
+  if (!ctx) return fail(ZK_ERR_ARG, "zk_device_sync: NULL context");
+  CtxLock lk(ctx);
+  ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+  return ZK_OK;
+}
+
+// ---------------------------------------------------------------------------- transcript
+zk_transcript* zk_transcript_new(const uint8_t* label, size_t label_len) { return new zk_transcript(label, label_len); }
+zk_transcript* zk_transcript_clone(const zk_transcript* t) { return t ? new zk_transcript(*t) : nullptr; }
+void zk_transcript_free(zk_transcript* t) { delete t; }
+
+void zk_transcript_append_message(zk_transcript* t, const uint8_t* label, size_t label_len, const uint8_t* msg,
+                                  size_t msg_len) {
+  t->m.append_message(label, label_len, msg, msg_len);
+}
+void zk_transcript_append_u64(zk_transcript* t, const uint8_t* label, size_t label_len, uint64_t value) {
+  t->m.append_u64(label, label_len, value);
+}
+void zk_transcript_append_scalar(zk_transcript* t, const uint8_t* label, size_t label_len, const uint64_t scalar[4]) {
+  transcript_append_scalar(t->m, label, label_len, fr_load(scalar));
+}
+void zk_transcript_challenge_bytes(zk_transcript* t, const uint8_t* label, size_t label_len, uint8_t* out, size_t n) {
+  t->m.challenge_bytes(label, label_len, out, n);
+}
+void zk_transcript_challenge_scalar(zk_transcript* t, const uint8_t* label, size_t label_len, uint64_t out[4]) {
+  fr_store(out, transcript_challenge_scalar(t->m, label, label_len));
+}
+
+// ---------------------------------------------------------------------------- linear sumcheck
+int zk_sumcheck_linear_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, const uint64_t* const* tables,
+                             zk_mem tables_mem, zk_fs_round_fn fs, void* fs_user, zk_transcript* tr,
+                             uint64_t* round_msgs, uint64_t* challenges, uint64_t* final_table0,
+                             uint64_t* final_eval) {
+  if (!ctx) return fail(ZK_ERR_ARG, "linear_prove: NULL context");
+  if (!tables || num_poly == 0) return fail(ZK_ERR_ARG, "Polynomials cannot be empty");
+  if (num_poly > kMaxPolys) return fail(ZK_ERR_ARG, "linear_prove: num_poly %u exceeds %d", num_poly, kMaxPolys);
+  if (num_var > 40) return fail(ZK_ERR_ARG, "linear_prove: num_var %u too large", num_var);
+  if (!fs && !tr) return fail(ZK_ERR_ARG, "linear_prove: neither a callback nor a transcript was given");
+  for (uint32_t i = 0; i < num_poly; i++)
+    if (!tables[i]) return fail(ZK_ERR_ARG, "Polynomial %u has incorrect size", i);
+  if (num_var && (!round_msgs || !challenges)) return fail(ZK_ERR_ARG, "linear_prove: NULL output");
+  if (!final_eval) return fail(ZK_ERR_ARG, "linear_prove: NULL output");
+
+  CtxLock lk(ctx);
+  const uint64_t size = 1ull << num_var;
+  const int L = (int)num_poly;
+
+  // device layout: [copies of host inputs] [ping: L * size/2] [pong: L * size/4]
+  const uint64_t in_elems = tables_mem == ZK_MEM_HOST ? size * L : 0;
+  const uint64_t ping_elems = (size / 2) * L, pong_elems = (size / 4) * L;
+  Fr* base = nullptr;
+  int rc = ctx->reserve_work((in_elems + ping_elems + pong_elems + 1) * sizeof(Fr), (void**)&base);
+  if (rc != ZK_OK) return rc;
+  const Fr* cur[kMaxPolys];
+  Fr *ping[kMaxPolys], *pong[kMaxPolys];
+  for (int i = 0; i < L; i++) {
+    if (tables_mem == ZK_MEM_HOST) {
+      Fr* d = base + (uint64_t)i * size;
+      ZK_CUDA(cudaMemcpyAsync(d, tables[i], size * sizeof(Fr), cudaMemcpyHostToDevice, ctx->stream));
+      cur[i] = d;
+    } else {
+      cur[i] = reinterpret_cast<const Fr*>(tables[i]);
+    }
+    ping[i] = base + in_elems + (uint64_t)i * (size / 2);
+    pong[i] = base + in_elems + ping_elems + (uint64_t)i * (size / 4);
+  }
+
+  Fr challenge = Fr::zero();
+  for (uint32_t round = 0; round < num_var; round++) {
+    const uint64_t pairs = size >> (round + 1);
+    if (round == 0) {
+      launch_round(L, false, cur, nullptr, challenge, pairs, ctx->rs, ctx->stream);
+    } else {
+      Fr** dst = (round & 1) ? ping : pong;
+      launch_round(L, true, cur, dst, challenge, pairs, ctx->rs, ctx->stream);
+      for (int i = 0; i < L; i++) cur[i] = dst[i];
+    }
+    ctx->launches++;
+    ZK_CUDA(cudaGetLastError());
+    ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->rs.msg, (L + 1) * sizeof(Fr), cudaMemcpyDeviceToHost, ctx->stream));
+    ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+    const Fr* msg = reinterpret_cast<const Fr*>(ctx->host_small);
+    uint64_t* out_msg = round_msgs + (uint64_t)round * (L + 1) * 4;
+    for (int c = 0; c <= L; c++) fr_store(out_msg + 4 * c, msg[c]);
+    if (fs) {
+      uint64_t ch[4];
+      if (fs(fs_user, out_msg, (uint32_t)(L + 1), ch) != 0) return fail(ZK_ERR_FS_CALLBACK, "Fiat-Shamir callback failed in round %u", round);
+      challenge = fr_load(ch);
+    } else {
+      for (int c = 0; c <= L; c++) transcript_append_scalar(tr->m, (const uint8_t*)"round_message", 13, msg[c]);
+      challenge = transcript_challenge_scalar(tr->m, (const uint8_t*)"challenge", 9);
+    }
+    fr_store(challenges + 4 * (uint64_t)round, challenge);
+  }
+  launch_final(L, num_var > 0, cur, challenge, ctx->final_out, ctx->stream);
+  ctx->launches++;
+  ZK_CUDA(cudaGetLastError());
+  ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->final_out, (L + 1) * sizeof(Fr), cudaMemcpyDeviceToHost, ctx->stream));
+  ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+  const Fr* fin = reinterpret_cast<const Fr*>(ctx->host_small);
+  if (final_table0)
+    for (int i = 0; i < L; i++) fr_store(final_table0 + 4 * i, fin[i]);
+  fr_store(final_eval, fin[L]);
+  return ZK_OK;
+}
+
+// ---------------------------------------------------------------------------- folds
+int zk_fold_lsb(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, uint32_t k, const uint64_t* point,
+                uint64_t* out, zk_mem out_mem) {
+  if (!ctx || !evals || !out || (k && !point)) return fail(ZK_ERR_ARG, "fold_lsb: NULL argument");
+  if (k > n) return fail(ZK_ERR_ARG, "invalid size of partial point");
+  if (n > 40) return fail(ZK_ERR_ARG, "fold_lsb: n %u too large", n);
+  CtxLock lk(ctx);
+  const uint64_t size = 1ull << n;
+  const uint64_t in_elems = evals_mem == ZK_MEM_HOST ? size : 0;
+  Fr* base = nullptr;
+  int rc = ctx->reserve_work((in_elems + size / 2 + size / 4 + 2) * sizeof(Fr), (void**)&base);
+  if (rc != ZK_OK) return rc;
+  const Fr* cur = reinterpret_cast<const Fr*>(evals);
+  if (evals_mem == ZK_MEM_HOST) {
+    ZK_CUDA(cudaMemcpyAsync(base, evals, size * sizeof(Fr), cudaMemcpyHostToDevice, ctx->stream));
+    cur = base;
+  }
+  Fr* bufs[2] = {base + in_elems, base + in_elems + size / 2 + 1};
+  for (uint32_t i = 0; i < k; i++) {
+    Fr* dst = bufs[i & 1];
+    launch_fold(cur, dst, fr_load(point + 4 * (uint64_t)i), size >> (i + 1), ctx->rs.max_blocks, ctx->stream);
+    ctx->launches++;
+    cur = dst;
+  }
+  ZK_CUDA(cudaGetLastError());
+  ZK_CUDA(cudaMemcpyAsync(out, cur, (size >> k) * sizeof(Fr), cudaMemcpyDefault, ctx->stream));
+  ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+  (void)out_mem;
+  return ZK_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,71 @@
+// The library context and small host helpers shared by the C ABI translation units.
+#pragma once
+#include <atomic>
+#include <cstdarg>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "internal.hpp"
+#include "merlin.hpp"
+
+namespace zk {
+
+int fail(int code, const char* fmt, ...);
+
+#define ZK_CUDA(call)                                                                        \
+  do {                                                                                       \
+    cudaError_t e_ = (call);                                                                 \
+    if (e_ != cudaSuccess) return ::zk::fail(-3 /*ZK_ERR_CUDA*/, "%s: %s", #call, cudaGetErrorString(e_)); \
+  } while (0)
+
+inline Fr fr_load(const uint64_t* p) {
+  Fr x;
+  memcpy(x.v, p, 32);
+  return x;
+}
+inline void fr_store(uint64_t* p, const Fr& x) { memcpy(p, x.v, 32); }
+
+// CryptoField::to_bytes_le + Transcript::append_scalar (util/poly.rs:79-83, transcript.rs:27-30):
+// the 32-byte canonical little-endian value is absorbed.
+inline void transcript_append_scalar(MerlinTranscript& t, const uint8_t* label, size_t n, const Fr& mont) {
+  const Fr c = from_mont(mont);
+  t.append_message(label, n, reinterpret_cast<const uint8_t*>(c.v), 32);
+}
+// Transcript::challenge_scalar (transcript.rs:38-42) with CryptoField::from_bytes_le
+// (util/poly.rs:72-78): 64 bytes are drawn, the first 32 are reduced mod r.
+inline Fr transcript_challenge_scalar(MerlinTranscript& t, const uint8_t* label, size_t n) {
+  uint8_t buf[64];
+  t.challenge_bytes(label, n, buf, 64);
+  Fr raw;
+  memcpy(raw.v, buf, 32);
+  return to_mont(raw);  // Montgomery product with R^2 also reduces mod r
+}
+
+}  // namespace zk
+
+struct zk_ctx {
+  int device = 0;
+  int sm_count = 0;
+  cudaStream_t stream = nullptr;
+  zk::RoundScratch rs{};
+  zk::Fr* final_out = nullptr;   // kMaxPolys + 1 elements
+  void* host_small = nullptr;    // pinned, 4 KiB: round messages and other tiny read-backs
+  void* work = nullptr;          // grow-only device scratch
+  size_t work_bytes = 0;
+  std::mutex mu;
+  std::atomic<uint64_t> launches{0};
+
+  int setup();
+  void teardown();
+  // Make the scratch at least `bytes` large and return it (contents undefined).
+  int reserve_work(size_t bytes, void** out);
+};
+
+namespace zk {
+// Serialises calls on a context and makes its device current for the calling thread.
+struct CtxLock {
+  std::unique_lock<std::mutex> lk;
+  explicit CtxLock(zk_ctx* c) : lk(c->mu) { cudaSetDevice(c->device); }
+};
+}  // namespace zk

@@ -1,0 +1,309 @@
+// Dense sumcheck round kernels over BN254 Fr.
+//
+// One launch per round.  k_round<L, FOLD> binds the previous round's challenge (FOLD) and
+// computes this round's message in the same pass, so every live table entry is read once
+// per round and the folded half is written once:
+//   fold     u[j]  = t[2j] + r (t[2j+1] - t[2j])                    linear_prover.rs:151-178
+//   message  s(c)  = sum_y prod_i (u_i[2y] + c (u_i[2y+1] - u_i[2y])),  c = 0..L   :82-140
+// Sums of products are kept as unreduced 512-bit integers per thread (one Montgomery
+// reduction per thread per evaluation point), then reduced over the warp by shuffles, over
+// the block through shared memory and over the grid by the last block to finish.
+#include "internal.hpp"
+#include "warp_tile.cuh"
+
+namespace zk {
+
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kWarps = kThreads / 32;
+
+__device__ __forceinline__ Fr fr_from_chunks(const uint4& lo, const uint4& hi) {
+  Fr x;
+  x.v[0] = lo.x; x.v[1] = lo.y; x.v[2] = lo.z; x.v[3] = lo.w;
+  x.v[4] = hi.x; x.v[5] = hi.y; x.v[6] = hi.z; x.v[7] = hi.w;
+  return x;
+}
+__device__ __forceinline__ void fr_to_chunks(const Fr& x, uint4& lo, uint4& hi) {
+  lo = make_uint4(x.v[0], x.v[1], x.v[2], x.v[3]);
+  hi = make_uint4(x.v[4], x.v[5], x.v[6], x.v[7]);
+}
+
+__device__ __forceinline__ Fr shfl_down_fr(const Fr& x, int delta) {
+  Fr r;
+#pragma unroll
+  for (int i = 0; i < 8; i++) r.v[i] = __shfl_down_sync(0xffffffffu, x.v[i], delta);
+  return r;
+}
+
+__device__ __forceinline__ Fr warp_sum(Fr s) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s = add(s, shfl_down_fr(s, off));
+  return s;  // lane 0 holds the total
+}
+
+__device__ __forceinline__ Fr ld_cg_fr(const Fr* p) {
+  const uint4 lo = __ldcg(reinterpret_cast<const uint4*>(p));
+  const uint4 hi = __ldcg(reinterpret_cast<const uint4*>(p) + 1);
+  return fr_from_chunks(lo, hi);
+}
+
+// Sum NV per-thread values over the grid; the last block to arrive writes out[0..NV).
+// partials holds gridDim.x * NV elements; *counter must be zero on entry and is reset.
+template <int NV>
+__device__ __forceinline__ void grid_sum(Fr (&s)[NV], Fr* partials, unsigned int* counter, Fr* out) {
+  __shared__ Fr sh[kWarps][NV];
+  __shared__ bool is_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int c = 0; c < NV; c++) {
+    Fr t = warp_sum(s[c]);
+    if (lane == 0) sh[warp][c] = t;
+  }
+  __syncthreads();
+  if (threadIdx.x < NV) {
+    Fr t = sh[0][threadIdx.x];
+    for (int w = 1; w < kWarps; w++) t = add(t, sh[w][threadIdx.x]);
+    partials[(size_t)blockIdx.x * NV + threadIdx.x] = t;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int ticket = atomicAdd(counter, 1u);
+    is_last = (ticket == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+#pragma unroll
+  for (int c = 0; c < NV; c++) {
+    Fr t = Fr::zero();
+    for (unsigned int b = threadIdx.x; b < gridDim.x; b += blockDim.x) t = add(t, ld_cg_fr(partials + (size_t)b * NV + c));
+    t = warp_sum(t);
+    if (lane == 0) sh[warp][c] = t;
+  }
+  __syncthreads();
+  if (threadIdx.x < NV) {
+    Fr t = sh[0][threadIdx.x];
+    for (int w = 1; w < kWarps; w++) t = add(t, sh[w][threadIdx.x]);
+    out[threadIdx.x] = t;
+  }
+  if (threadIdx.x == 0) *counter = 0;
+}
+
+template <int L>
+struct RoundParams {
+  const Fr* src[L];
+  Fr* dst[L];
+  Fr r;
+  uint64_t pairs;  // (even, odd) pairs of the table the message is computed over
+  Fr* partials;
+  unsigned int* counter;
+  Fr* msg;
+};
+
+template <int L, bool FOLD>
+__global__ void __launch_bounds__(kThreads, (L <= 2 ? 3 : 2)) k_round(const RoundParams<L> p) {
+  __shared__ uint4 stage[kWarps][WarpTile<8>::kChunks];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint4* sw = stage[warp];
+  const uint64_t tiles = (p.pairs + 31) >> 5;
+  const uint64_t warp_global = (uint64_t)blockIdx.x * kWarps + warp;
+  const uint64_t warp_stride = (uint64_t)gridDim.x * kWarps;
+
+  Wide acc[L + 1];
+#pragma unroll
+  for (int c = 0; c <= L; c++)
+#pragma unroll
+    for (int k = 0; k < 16; k++) acc[c].v[k] = 0;
+  int pending = 0;
+
+  for (uint64_t tile = warp_global; tile < tiles; tile += warp_stride) {
+    const uint64_t pair0 = tile << 5;
+    const uint32_t valid_pairs = (uint32_t)((p.pairs - pair0) < 32 ? (p.pairs - pair0) : 32);
+    Fr u0[L], d[L];
+    if (FOLD) {
+      uint4 raw[L][8];
+#pragma unroll
+      for (int i = 0; i < L; i++)
+        WarpTile<8>::issue(reinterpret_cast<const uint4*>(p.src[i]) + pair0 * 8, valid_pairs * 8, lane, raw[i]);
+#pragma unroll
+      for (int i = 0; i < L; i++) {
+        uint4 q[8];
+        WarpTile<8>::transpose_in(sw, lane, raw[i], q);
+        const Fr t0 = fr_from_chunks(q[0], q[1]), t1 = fr_from_chunks(q[2], q[3]);
+        const Fr t2 = fr_from_chunks(q[4], q[5]), t3 = fr_from_chunks(q[6], q[7]);
+        const Fr a = add(t0, mul(p.r, sub(t1, t0)));
+        const Fr b = add(t2, mul(p.r, sub(t3, t2)));
+        uint4 o[4];
+        fr_to_chunks(a, o[0], o[1]);
+        fr_to_chunks(b, o[2], o[3]);
+        WarpTile<4>::store(reinterpret_cast<uint4*>(p.dst[i]) + pair0 * 4, valid_pairs * 4, sw, lane, o);
+        u0[i] = a;
+        d[i] = sub(b, a);
+      }
+    } else {
+      uint4 raw[L][4];
+#pragma unroll
+      for (int i = 0; i < L; i++)
+        WarpTile<4>::issue(reinterpret_cast<const uint4*>(p.src[i]) + pair0 * 4, valid_pairs * 4, lane, raw[i]);
+#pragma unroll
+      for (int i = 0; i < L; i++) {
+        uint4 q[4];
+        WarpTile<4>::transpose_in(sw, lane, raw[i], q);
+        const Fr a = fr_from_chunks(q[0], q[1]), b = fr_from_chunks(q[2], q[3]);
+        u0[i] = a;
+        d[i] = sub(b, a);
+      }
+    }
+    // lanes past the end of the table hold zeros and add nothing
+#pragma unroll
+    for (int c = 0; c <= L; c++) {
+      Wide w;
+      if (L == 1) {
+        const Fr one = Fr::one();
+        mul_wide(w, u0[0].v, one.v);
+      } else {
+        Fr prod = u0[0];
+#pragma unroll
+        for (int i = 1; i < L - 1; i++) prod = mul(prod, u0[i]);
+        mul_wide(w, prod.v, u0[L - 1].v);
+      }
+      wide_add(acc[c], w);
+      if (c < L) {
+#pragma unroll
+        for (int i = 0; i < L; i++) u0[i] = add(u0[i], d[i]);
+      }
+    }
+    if (++pending == kLazyProducts) {
+#pragma unroll
+      for (int c = 0; c <= L; c++) wide_trim<FrParams>(acc[c]);
+      pending = 0;
+    }
+  }
+  Fr s[L + 1];
+#pragma unroll
+  for (int c = 0; c <= L; c++) {
+    wide_trim<FrParams>(acc[c]);
+    s[c] = redc<FrParams>(acc[c]);
+  }
+  grid_sum<L + 1>(s, p.partials, p.counter, p.msg);
+}
+
+// Last step of the protocol: bind the final challenge on the two remaining entries of each
+// table and multiply the results (linear_prover.rs:181-190).  With bind == 0 the tables
+// already hold one entry each (num_var == 0).
+struct FinalParams {
+  const Fr* src[kMaxPolys];
+  int num_poly;
+  int bind;
+  Fr r;
+  Fr* out;  // out[0..num_poly) = a_arrays[i][0], out[num_poly] = product
+};
+
+__global__ void k_final(const FinalParams p) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  Fr prod = Fr::one();
+  for (int i = 0; i < p.num_poly; i++) {
+    Fr a = p.src[i][0];
+    if (p.bind) a = add(a, mul(p.r, sub(p.src[i][1], a)));
+    p.out[i] = a;
+    prod = mul(prod, a);
+  }
+  p.out[p.num_poly] = prod;
+}
+
+// Plain fold of the lowest variable (no message): util/poly.rs:852-884.
+struct FoldParams {
+  const Fr* src;
+  Fr* dst;
+  Fr r;
+  uint64_t out_len;
+};
+
+__global__ void __launch_bounds__(kThreads) k_fold(const FoldParams p) {
+  __shared__ uint4 stage[kWarps][WarpTile<4>::kChunks];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint4* sw = stage[warp];
+  const uint64_t tiles = (p.out_len + 31) >> 5;
+  for (uint64_t tile = (uint64_t)blockIdx.x * kWarps + warp; tile < tiles; tile += (uint64_t)gridDim.x * kWarps) {
+    const uint64_t e0 = tile << 5;
+    const uint32_t valid = (uint32_t)((p.out_len - e0) < 32 ? (p.out_len - e0) : 32);
+    uint4 raw[4], q[4];
+    WarpTile<4>::issue(reinterpret_cast<const uint4*>(p.src) + e0 * 4, valid * 4, lane, raw);
+    WarpTile<4>::transpose_in(sw, lane, raw, q);
+    const Fr a = fr_from_chunks(q[0], q[1]), b = fr_from_chunks(q[2], q[3]);
+    const Fr u = add(a, mul(p.r, sub(b, a)));
+    uint4 o[2];
+    fr_to_chunks(u, o[0], o[1]);
+    WarpTile<2>::store(reinterpret_cast<uint4*>(p.dst) + e0 * 2, valid * 2, sw, lane, o);
+  }
+}
+
+int grid_for(uint64_t tiles, int max_blocks) {
+  uint64_t blocks = (tiles + kWarps - 1) / kWarps;
+  if (blocks < 1) blocks = 1;
+  if (blocks > (uint64_t)max_blocks) blocks = max_blocks;
+  return (int)blocks;
+}
+
+template <int L>
+void launch_round_t(bool fold, const Fr* const* src, Fr* const* dst, const Fr& r, uint64_t pairs,
+                    const RoundScratch& sc, cudaStream_t stream) {
+  RoundParams<L> p;
+  for (int i = 0; i < L; i++) {
+    p.src[i] = src[i];
+    p.dst[i] = fold ? dst[i] : nullptr;
+  }
+  p.r = r;
+  p.pairs = pairs;
+  p.partials = sc.partials;
+  p.counter = sc.counter;
+  p.msg = sc.msg;
+  static int occ[2] = {0, 0};  // resident blocks per SM, per variant
+  if (!occ[fold]) {
+    int o = 0;
+    if (fold)
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o, k_round<L, true>, kThreads, 0);
+    else
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o, k_round<L, false>, kThreads, 0);
+    occ[fold] = o > 0 ? o : 1;
+  }
+  int cap = sc.sm_count * occ[fold];
+  if (cap > sc.max_blocks) cap = sc.max_blocks;
+  const int grid = grid_for((pairs + 31) / 32, cap);
+  if (fold)
+    k_round<L, true><<<grid, kThreads, 0, stream>>>(p);
+  else
+    k_round<L, false><<<grid, kThreads, 0, stream>>>(p);
+}
+
+}  // namespace
+
+void launch_round(int num_poly, bool fold, const Fr* const* src, Fr* const* dst, const Fr& r, uint64_t pairs,
+                  const RoundScratch& sc, cudaStream_t stream) {
+  switch (num_poly) {
+    case 1: launch_round_t<1>(fold, src, dst, r, pairs, sc, stream); break;
+    case 2: launch_round_t<2>(fold, src, dst, r, pairs, sc, stream); break;
+    case 3: launch_round_t<3>(fold, src, dst, r, pairs, sc, stream); break;
+    case 4: launch_round_t<4>(fold, src, dst, r, pairs, sc, stream); break;
+    default: break;  // callers check 1 <= num_poly <= kMaxPolys
+  }
+}
+
+void launch_final(int num_poly, bool bind, const Fr* const* src, const Fr& r, Fr* out, cudaStream_t stream) {
+  FinalParams p;
+  for (int i = 0; i < kMaxPolys; i++) p.src[i] = i < num_poly ? src[i] : nullptr;
+  p.num_poly = num_poly;
+  p.bind = bind ? 1 : 0;
+  p.r = r;
+  p.out = out;
+  k_final<<<1, 32, 0, stream>>>(p);
+}
+
+void launch_fold(const Fr* src, Fr* dst, const Fr& r, uint64_t out_len, int max_blocks, cudaStream_t stream) {
+  FoldParams p{src, dst, r, out_len};
+  k_fold<<<grid_for((out_len + 31) / 32, max_blocks), kThreads, 0, stream>>>(p);
+}
+
+}  // namespace zk
