@@ -93,6 +93,17 @@ int zk_sumcheck_linear_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, c
                              uint64_t* round_msgs, uint64_t* challenges, uint64_t* final_table0,
                              uint64_t* final_eval);
 
+/* Product sumcheck sum_x a(x) b(x) with `a` given by nnz non-zero entries (idx strictly
+ * increasing, < 2^num_var; vals their values) and `b` a dense table of 2^num_var elements.
+ * The reference has no prover of this shape in src/ (tests/test_sd_sumcheck.rs:46-58 imports
+ * a missing module); the result is defined as LinearSumcheckProver::prove
+ * (linear_prover.rs:43-76) on [a.to_dense(), b]: same messages (3 per round), challenges,
+ * final_table0 = {a(r), b(r)} and final_eval.  All three inputs live in `mem`.  num_var <= 32. */
+int zk_sumcheck_sparse_dense_prove(zk_ctx* ctx, uint32_t num_var, uint64_t nnz, const uint64_t* idx,
+                                   const uint64_t* vals, const uint64_t* dense, zk_mem mem, zk_fs_round_fn fs,
+                                   void* fs_user, zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges,
+                                   uint64_t* final_table0, uint64_t* final_eval);
+
 /* ---- multilinear helpers --------------------------------------------------------------- */
 /* DenseMLPoly::fix_variables, src/util/poly.rs:842-887: binds the k lowest variables of a
  * 2^n table to point[0..k); out receives 2^(n-k) elements. */

@@ -5,7 +5,8 @@ of the reference's Rust interface for that path; all arithmetic runs in libzkb20
 Names are resolved lazily so that `python -m zkes_b200.build` can run before the library exists."""
 import importlib
 
-_API = ("Context", "DenseMLPoly", "LinearSumcheckProver", "SumcheckProof", "Transcript")
+_API = ("Context", "DenseMLPoly", "LinearSumcheckProver", "SumcheckProof", "Transcript",
+        "SparseDenseSumcheckProver")
 
 
 def __getattr__(name):

@@ -37,6 +37,9 @@ SIGNATURES = {
     "zk_transcript_challenge_scalar": (None, [c_void_p, c_char_p, c_size_t, c_void_p]),
     "zk_sumcheck_linear_prove": (c_int, [c_void_p, c_uint32, c_uint32, POINTER(c_void_p), c_int, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "zk_sumcheck_sparse_dense_prove": (c_int, [c_void_p, c_uint32, c_uint64, c_void_p, c_void_p, c_void_p, c_int,
+                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                               c_void_p]),
     "zk_microbench": (c_int, [c_void_p, c_int, c_int, c_int, c_int, POINTER(ctypes.c_float),
                               POINTER(ctypes.c_double)]),
     "zk_fold_lsb": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_int]),

@@ -167,3 +167,40 @@ class LinearSumcheckProver:
         self.a_arrays = [[v] for v in from_mont_array(fin_t)]
         rm = [from_mont_array(msgs[r]) for r in range(n)]
         return SumcheckProof(from_mont_array(fin)[0], rm)
+
+
+class SparseDenseSumcheckProver:
+    """Product sumcheck of a sparse table (sorted non-zero entries) with a dense one.  Defined as
+    LinearSumcheckProver (two tables) on [a.to_dense(), b]; header as linear_prover.rs:29-32."""
+
+    def __init__(self, num_var: int, transcript: Transcript):
+        transcript.append_u64(b"num_var", num_var)
+        transcript.append_u64(b"num_poly", 2)
+        self.num_var = num_var
+        self.challenges = []
+        self.a_arrays = []
+
+    def prove(self, ctx: Context, indices, values, dense: DenseMLPoly, transcript: Transcript, *,
+              device_ptrs=None) -> SumcheckProof:
+        """indices: strictly increasing ints; values: canonical ints.  With device_ptrs =
+        (idx_ptr, val_ptr, nnz) all three inputs are device buffers."""
+        n = self.num_var
+        assert len(dense) == 1 << n, "Polynomials have incorrect size"
+        msgs = np.zeros((max(n, 1), 3, 4), dtype=np.uint64)
+        chal = np.zeros((max(n, 1), 4), dtype=np.uint64)
+        fin_t = np.zeros((2, 4), dtype=np.uint64)
+        fin = np.zeros((1, 4), dtype=np.uint64)
+        if device_ptrs is not None:
+            ip, vp, nnz = device_ptrs
+            args = (c_void_p(ip), c_void_p(vp), c_void_p(dense.device_ptr), ZK_MEM_DEVICE)
+        else:
+            nnz = len(indices)
+            ia = np.ascontiguousarray(np.array(list(indices), dtype=np.uint64))
+            va = to_mont_array(values) if nnz else np.zeros((1, 4), dtype=np.uint64)
+            args = (_ptr(ia) if nnz else None, _ptr(va), _ptr(dense.mont), ZK_MEM_HOST)
+        check(lib.zk_sumcheck_sparse_dense_prove(ctx.handle, n, nnz, args[0], args[1], args[2], args[3], None, None,
+                                                 transcript.handle, _ptr(msgs), _ptr(chal), _ptr(fin_t), _ptr(fin)),
+              "zk_sumcheck_sparse_dense_prove")
+        self.challenges = from_mont_array(chal[:n])
+        self.a_arrays = [[v] for v in from_mont_array(fin_t)]
+        return SumcheckProof(from_mont_array(fin)[0], [from_mont_array(msgs[r]) for r in range(n)])

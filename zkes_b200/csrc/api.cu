@@ -22,10 +22,30 @@ int fail(int code, const char* fmt, ...) {
 }
 }  // namespace zk
 
-struct zk_transcript {
-  MerlinTranscript m;
-  zk_transcript(const uint8_t* label, size_t n) : m(label, n) {}
-};
+namespace zk {
+// Reads the round message the last kernel left in rs.msg, records it, runs the Fiat-Shamir
+// step (callback or built-in transcript) and records the challenge.
+int fs_round(zk_ctx* ctx, int n_msgs, uint32_t round, zk_fs_round_fn fs, void* fs_user, zk_transcript* tr,
+             uint64_t* round_msgs, uint64_t* challenges, Fr* challenge) {
+  ZK_CUDA(cudaGetLastError());
+  ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->rs.msg, n_msgs * sizeof(Fr), cudaMemcpyDeviceToHost, ctx->stream));
+  ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+  const Fr* msg = reinterpret_cast<const Fr*>(ctx->host_small);
+  uint64_t* out_msg = round_msgs + (uint64_t)round * n_msgs * 4;
+  for (int c = 0; c < n_msgs; c++) fr_store(out_msg + 4 * c, msg[c]);
+  if (fs) {
+    uint64_t ch[4];
+    if (fs(fs_user, out_msg, (uint32_t)n_msgs, ch) != 0)
+      return fail(ZK_ERR_FS_CALLBACK, "Fiat-Shamir callback failed in round %u", round);
+    *challenge = fr_load(ch);
+  } else {
+    for (int c = 0; c < n_msgs; c++) transcript_append_scalar(tr->m, (const uint8_t*)"round_message", 13, msg[c]);
+    *challenge = transcript_challenge_scalar(tr->m, (const uint8_t*)"challenge", 9);
+  }
+  fr_store(challenges + 4 * (uint64_t)round, *challenge);
+  return ZK_OK;
+}
+}  // namespace zk
 
 extern "C" {
 
@@ -165,20 +185,8 @@ int zk_sumcheck_linear_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, c
     }
     ctx->launches++;
     ZK_CUDA(cudaGetLastError());
-    ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->rs.msg, (L + 1) * sizeof(Fr), cudaMemcpyDeviceToHost, ctx->stream));
-    ZK_CUDA(cudaStreamSynchronize(ctx->stream));
-    const Fr* msg = reinterpret_cast<const Fr*>(ctx->host_small);
-    uint64_t* out_msg = round_msgs + (uint64_t)round * (L + 1) * 4;
-    for (int c = 0; c <= L; c++) fr_store(out_msg + 4 * c, msg[c]);
-    if (fs) {
-      uint64_t ch[4];
-      if (fs(fs_user, out_msg, (uint32_t)(L + 1), ch) != 0) return fail(ZK_ERR_FS_CALLBACK, "Fiat-Shamir callback failed in round %u", round);
-      challenge = fr_load(ch);
-    } else {
-      for (int c = 0; c <= L; c++) transcript_append_scalar(tr->m, (const uint8_t*)"round_message", 13, msg[c]);
-      challenge = transcript_challenge_scalar(tr->m, (const uint8_t*)"challenge", 9);
-    }
-    fr_store(challenges + 4 * (uint64_t)round, challenge);
+    rc = fs_round(ctx, L + 1, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
+    if (rc != ZK_OK) return rc;
   }
   launch_final(L, num_var > 0, cur, challenge, ctx->final_out, ctx->stream);
   ctx->launches++;

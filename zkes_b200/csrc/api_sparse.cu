@@ -1,0 +1,145 @@
+// C ABI: sparse x dense product sumcheck (host round loop over the kernels of sparse.cu).
+#include "../../include/zkb200.h"
+#include "ctx.hpp"
+
+using namespace zk;
+
+namespace {
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Bump allocator over the context's scratch.
+struct Arena {
+  char* base;
+  size_t off = 0;
+  template <class T>
+  T* take(size_t n) {
+    T* p = reinterpret_cast<T*>(base + off);
+    off = align_up(off + n * sizeof(T), 256);
+    return p;
+  }
+};
+}  // namespace
+
+extern "C" int zk_sumcheck_sparse_dense_prove(zk_ctx* ctx, uint32_t num_var, uint64_t nnz, const uint64_t* idx,
+                                              const uint64_t* vals, const uint64_t* dense, zk_mem mem,
+                                              zk_fs_round_fn fs, void* fs_user, zk_transcript* tr,
+                                              uint64_t* round_msgs, uint64_t* challenges, uint64_t* final_table0,
+                                              uint64_t* final_eval) {
+  if (!ctx) return fail(ZK_ERR_ARG, "sparse_dense_prove: NULL context");
+  if (num_var > 32) return fail(ZK_ERR_ARG, "sparse_dense_prove: num_var %u exceeds 32", num_var);
+  const uint64_t size = 1ull << num_var;
+  if (nnz > size) return fail(ZK_ERR_ARG, "sparse_dense_prove: %llu entries in a domain of %llu", (unsigned long long)nnz, (unsigned long long)size);
+  if (!dense || (nnz && (!idx || !vals))) return fail(ZK_ERR_ARG, "sparse_dense_prove: NULL input");
+  if (!fs && !tr) return fail(ZK_ERR_ARG, "sparse_dense_prove: neither a callback nor a transcript was given");
+  if (!final_eval || (num_var && (!round_msgs || !challenges))) return fail(ZK_ERR_ARG, "sparse_dense_prove: NULL output");
+
+  CtxLock lk(ctx);
+  cudaStream_t s = ctx->stream;
+  const uint32_t K = (uint32_t)nnz;
+  // The dense phase starts at the first round whose table size is <= 2 * (entry bound).
+  uint64_t dense_cap = 2;
+  while (dense_cap < 2 * (uint64_t)K && dense_cap < size) dense_cap <<= 1;
+
+  size_t need = 4096;
+  const bool host_in = mem == ZK_MEM_HOST;
+  if (host_in) need += align_up(size * sizeof(Fr), 256) + align_up(K * 8ull, 256);
+  need += align_up((size / 2 + 1) * sizeof(Fr), 256) + align_up((size / 4 + 1) * sizeof(Fr), 256);
+  need += 2 * (align_up((K + 1) * 4ull, 256) + align_up((K + 1) * sizeof(Fr), 256));
+  need += align_up((K / 256 + 2) * 4ull, 256) + 1024;
+  need += 3 * align_up((dense_cap + 1) * sizeof(Fr), 256) + 2 * align_up((dense_cap / 4 + 1) * sizeof(Fr), 256);
+  Arena ar;
+  int rc = ctx->reserve_work(need, (void**)&ar.base);
+  if (rc != ZK_OK) return rc;
+
+  const Fr* b_cur = reinterpret_cast<const Fr*>(dense);
+  const uint64_t* idx64 = idx;
+  const Fr* val_in = reinterpret_cast<const Fr*>(vals);
+  if (host_in) {
+    Fr* d = ar.take<Fr>(size);
+    ZK_CUDA(cudaMemcpyAsync(d, dense, size * sizeof(Fr), cudaMemcpyHostToDevice, s));
+    b_cur = d;
+    uint64_t* di = ar.take<uint64_t>(K + 1);
+    if (K) ZK_CUDA(cudaMemcpyAsync(di, idx, K * 8ull, cudaMemcpyHostToDevice, s));
+    idx64 = di;
+  }
+  Fr* b_buf[2] = {ar.take<Fr>(size / 2 + 1), ar.take<Fr>(size / 4 + 1)};
+  uint32_t* e_idx[2] = {ar.take<uint32_t>(K + 1), ar.take<uint32_t>(K + 1)};
+  Fr* e_val[2] = {ar.take<Fr>(K + 1), ar.take<Fr>(K + 1)};
+  uint32_t* block_counts = ar.take<uint32_t>(K / 256 + 2);
+  uint32_t* counts = ar.take<uint32_t>(64);  // [0], [1]: entry counts (ping-pong); [2]: bad-input flag
+  Fr* a_dense = ar.take<Fr>(dense_cap + 1);
+  Fr* d_ping[2] = {ar.take<Fr>(dense_cap / 2 + 1), ar.take<Fr>(dense_cap / 2 + 1)};
+  Fr* d_pong[2] = {ar.take<Fr>(dense_cap / 4 + 1), ar.take<Fr>(dense_cap / 4 + 1)};
+
+  // entries: narrow the indices, copy the values, check order
+  ZK_CUDA(cudaMemsetAsync(counts, 0, 64 * 4, s));
+  ZK_CUDA(cudaMemcpyAsync(counts, &K, 4, cudaMemcpyHostToDevice, s));
+  if (K) {
+    launch_narrow_idx(idx64, K, e_idx[0], counts + 2, ctx->sm_count, s);
+    launch_check_sorted(e_idx[0], K, size, counts + 2, ctx->sm_count, s);
+    ctx->launches += 2;
+    ZK_CUDA(cudaMemcpyAsync(e_val[0], val_in, K * sizeof(Fr), cudaMemcpyDefault, s));
+    uint32_t bad = 0;
+    ZK_CUDA(cudaMemcpyAsync(ctx->host_small, counts + 2, 4, cudaMemcpyDeviceToHost, s));
+    ZK_CUDA(cudaStreamSynchronize(s));
+    memcpy(&bad, ctx->host_small, 4);
+    if (bad) return fail(ZK_ERR_ARG, "sparse_dense_prove: indices must be strictly increasing and below 2^num_var");
+  }
+
+  enum { kSparse, kDenseFirst, kDense } mode = kSparse;
+  int e = 0;            // which entry buffers are current
+  int d_toggle = 0;     // dense phase: next fold goes to ping (0) or pong (1)
+  uint32_t k_upper = K;  // bound on the live entry count
+  const Fr* d_cur[2] = {nullptr, nullptr};
+  Fr challenge = Fr::zero();
+  uint64_t S = size;
+  for (uint32_t round = 0; round < num_var; round++, S >>= 1) {
+    if (mode == kSparse && K && S <= dense_cap) {
+      ZK_CUDA(cudaMemsetAsync(a_dense, 0, S * sizeof(Fr), s));
+      launch_scatter(e_idx[e], e_val[e], counts + e, k_upper, a_dense, ctx->sm_count, s);
+      ctx->launches++;
+      d_cur[0] = a_dense;
+      d_cur[1] = b_cur;
+      mode = kDenseFirst;
+    }
+    if (mode == kSparse) {
+      launch_sparse_msg(e_idx[e], e_val[e], counts + e, k_upper, b_cur, ctx->rs, s);
+    } else if (mode == kDenseFirst) {
+      launch_round(2, false, d_cur, nullptr, challenge, S / 2, ctx->rs, s);
+      mode = kDense;
+    } else {
+      Fr** dst = d_toggle ? d_pong : d_ping;
+      d_toggle ^= 1;
+      launch_round(2, true, d_cur, dst, challenge, S / 2, ctx->rs, s);
+      d_cur[0] = dst[0];
+      d_cur[1] = dst[1];
+    }
+    ctx->launches++;
+    rc = fs_round(ctx, 3, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
+    if (rc != ZK_OK) return rc;
+    if (mode == kSparse) {
+      Fr* nb = b_buf[round & 1];
+      launch_fold(b_cur, nb, challenge, S / 2, ctx->rs.max_blocks, s);
+      b_cur = nb;
+      ctx->launches += 1 + launch_sparse_fold(e_idx[e], e_val[e], counts + e, k_upper, challenge, block_counts,
+                                              e_idx[e ^ 1], e_val[e ^ 1], counts + (e ^ 1), s);
+      e ^= 1;
+      if ((uint64_t)k_upper > S / 2) k_upper = (uint32_t)(S / 2);
+    }
+  }
+  if (mode == kSparse)
+    launch_sd_final(e_idx[e], e_val[e], counts + e, b_cur, ctx->final_out, s);
+  else
+    launch_final(2, true, d_cur, challenge, ctx->final_out, s);
+  ctx->launches++;
+  ZK_CUDA(cudaGetLastError());
+  ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->final_out, 3 * sizeof(Fr), cudaMemcpyDeviceToHost, s));
+  ZK_CUDA(cudaStreamSynchronize(s));
+  const Fr* fin = reinterpret_cast<const Fr*>(ctx->host_small);
+  if (final_table0) {
+    fr_store(final_table0, fin[0]);
+    fr_store(final_table0 + 4, fin[1]);
+  }
+  fr_store(final_eval, fin[2]);
+  return ZK_OK;
+}

@@ -62,7 +62,16 @@ struct zk_ctx {
   int reserve_work(size_t bytes, void** out);
 };
 
+struct zk_transcript {
+  zk::MerlinTranscript m;
+  zk_transcript(const uint8_t* label, size_t n) : m(label, n) {}
+};
+
 namespace zk {
+typedef int (*fs_round_fn_t)(void* user, const uint64_t* msgs, uint32_t n_msgs, uint64_t challenge_out[4]);
+int fs_round(zk_ctx* ctx, int n_msgs, uint32_t round, fs_round_fn_t fs, void* fs_user, zk_transcript* tr,
+             uint64_t* round_msgs, uint64_t* challenges, Fr* challenge);
+
 // Serialises calls on a context and makes its device current for the calling thread.
 struct CtxLock {
   std::unique_lock<std::mutex> lk;

@@ -23,4 +23,17 @@ void launch_round(int num_poly, bool fold, const Fr* const* src, Fr* const* dst,
 void launch_final(int num_poly, bool bind, const Fr* const* src, const Fr& r, Fr* out, cudaStream_t stream);
 void launch_fold(const Fr* src, Fr* dst, const Fr& r, uint64_t out_len, int max_blocks, cudaStream_t stream);
 
+
+// sparse.cu
+void launch_sparse_msg(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
+                       const RoundScratch& sc, cudaStream_t s);
+int launch_sparse_fold(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr& r,
+                       uint32_t* block_counts, uint32_t* idx_out, Fr* val_out, uint32_t* count_out, cudaStream_t s);
+void launch_scatter(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, Fr* dense,
+                    int sm_count, cudaStream_t s);
+void launch_check_sorted(const uint32_t* idx, uint32_t n, uint64_t limit, uint32_t* bad, int sm_count, cudaStream_t s);
+void launch_narrow_idx(const uint64_t* in, uint32_t n, uint32_t* out, uint32_t* bad, int sm_count, cudaStream_t s);
+void launch_sd_final(const uint32_t* idx, const Fr* val, const uint32_t* count, const Fr* dense, Fr* out,
+                     cudaStream_t s);
+
 }  // namespace zk

@@ -1,0 +1,237 @@
+// Sparse x dense product sumcheck: sum_x a(x) b(x) with a given by K sorted non-zero entries.
+//
+// While the live domain is much larger than K the prover keeps `a` as (index, value) entries:
+// the round message only needs b at the entries' pair positions, the dense table b is folded
+// by the plain fold kernel, and the entries are folded by a merge of adjacent indices followed
+// by a stream compaction.  Once the domain has shrunk to about the entry count the entries are
+// scattered into a dense table and the dense round kernel takes over.  The outputs equal those
+// of the dense prover on [a.to_dense(), b] (linear_prover.rs:43-191): zero entries of `a`
+// contribute nothing to any message.
+#include "internal.hpp"
+#include "reduce.cuh"
+
+namespace zk {
+namespace {
+
+constexpr int kSpThreads = 256;
+
+__device__ __forceinline__ Fr ld_fr(const Fr* p) {
+  const uint4 lo = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint4 hi = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+  return fr_from_chunks(lo, hi);
+}
+__device__ __forceinline__ void st_fr(Fr* p, const Fr& x) {
+  uint4 lo, hi;
+  fr_to_chunks(x, lo, hi);
+  reinterpret_cast<uint4*>(p)[0] = lo;
+  reinterpret_cast<uint4*>(p)[1] = hi;
+}
+
+// An entry leads its pair unless it is the odd partner of the entry just before it.
+__device__ __forceinline__ bool is_leader(const uint32_t* idx, uint32_t i, uint32_t pos) {
+  return (pos & 1u) == 0 || i == 0 || idx[i - 1] != pos - 1;
+}
+
+__global__ void __launch_bounds__(kSpThreads) k_sparse_msg(const uint32_t* __restrict__ idx, const Fr* __restrict__ val,
+                                                           const uint32_t* __restrict__ count,
+                                                           const Fr* __restrict__ dense, Fr* partials,
+                                                           unsigned int* counter, Fr* msg) {
+  const uint32_t n = *count;
+  Wide acc[3];
+#pragma unroll
+  for (int c = 0; c < 3; c++)
+#pragma unroll
+    for (int k = 0; k < 16; k++) acc[c].v[k] = 0;
+  int pending = 0;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const uint32_t pos = idx[i];
+    if (!is_leader(idx, i, pos)) continue;
+    Fr v0 = Fr::zero(), v1 = Fr::zero();
+    if ((pos & 1u) == 0) {
+      v0 = ld_fr(val + i);
+      if (i + 1 < n && idx[i + 1] == pos + 1) v1 = ld_fr(val + i + 1);
+    } else {
+      v1 = ld_fr(val + i);
+    }
+    const Fr b0 = ld_fr(dense + (pos & ~1u)), b1 = ld_fr(dense + (pos | 1u));
+    Wide w;
+    mul_wide(w, v0.v, b0.v);
+    wide_add(acc[0], w);
+    mul_wide(w, v1.v, b1.v);
+    wide_add(acc[1], w);
+    const Fr v2 = add(v1, sub(v1, v0)), b2 = add(b1, sub(b1, b0));
+    mul_wide(w, v2.v, b2.v);
+    wide_add(acc[2], w);
+    if (++pending == kLazyProducts) {
+#pragma unroll
+      for (int c = 0; c < 3; c++) wide_trim<FrParams>(acc[c]);
+      pending = 0;
+    }
+  }
+  Fr s[3];
+#pragma unroll
+  for (int c = 0; c < 3; c++) {
+    wide_trim<FrParams>(acc[c]);
+    s[c] = redc<FrParams>(acc[c]);
+  }
+  grid_sum<3, kSpThreads / 32>(s, partials, counter, msg);
+}
+
+// Pass 1 of the entry fold: leaders per block.
+__global__ void __launch_bounds__(kSpThreads) k_sparse_count(const uint32_t* __restrict__ idx,
+                                                             const uint32_t* __restrict__ count,
+                                                             uint32_t* block_counts) {
+  const uint32_t n = *count;
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool lead = i < n && is_leader(idx, i, idx[i]);
+  const int c = __syncthreads_count(lead);
+  if (threadIdx.x == 0) block_counts[blockIdx.x] = (uint32_t)c;
+}
+
+// Pass 2: exclusive scan of the block counts by one block; total goes to count_out.
+__global__ void __launch_bounds__(1024) k_scan_blocks(uint32_t* block_counts, uint32_t n_blocks, uint32_t* count_out) {
+  __shared__ uint32_t warp_tot[32];
+  __shared__ uint32_t carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (uint32_t base = 0; base < n_blocks; base += 1024) {
+    const uint32_t i = base + threadIdx.x;
+    const uint32_t v = i < n_blocks ? block_counts[i] : 0;
+    uint32_t x = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t y = __shfl_up_sync(0xffffffffu, x, off);
+      if (lane >= off) x += y;
+    }
+    if (lane == 31) warp_tot[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      uint32_t t = warp_tot[lane];
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t y = __shfl_up_sync(0xffffffffu, t, off);
+        if (lane >= off) t += y;
+      }
+      warp_tot[lane] = t;  // inclusive over warps
+    }
+    __syncthreads();
+    const uint32_t before = carry + (warp ? warp_tot[warp - 1] : 0) + x - v;
+    if (i < n_blocks) block_counts[i] = before;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry = before + v;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *count_out = carry;
+}
+
+// Pass 3: fold each pair and write it at its compacted slot.
+__global__ void __launch_bounds__(kSpThreads) k_sparse_fold(const uint32_t* __restrict__ idx, const Fr* __restrict__ val,
+                                                            const uint32_t* __restrict__ count,
+                                                            const uint32_t* __restrict__ block_offsets, Fr r,
+                                                            uint32_t* idx_out, Fr* val_out) {
+  __shared__ uint32_t warp_cnt[kSpThreads / 32];
+  const uint32_t n = *count;
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t pos = 0;
+  bool lead = false;
+  if (i < n) {
+    pos = idx[i];
+    lead = is_leader(idx, i, pos);
+  }
+  const unsigned int ballot = __ballot_sync(0xffffffffu, lead);
+  if (lane == 0) warp_cnt[warp] = __popc(ballot);
+  __syncthreads();
+  if (!lead) return;
+  uint32_t slot = block_offsets[blockIdx.x] + __popc(ballot & ((1u << lane) - 1u));
+  for (int w = 0; w < warp; w++) slot += warp_cnt[w];
+  Fr v0 = Fr::zero(), v1 = Fr::zero();
+  if ((pos & 1u) == 0) {
+    v0 = ld_fr(val + i);
+    if (i + 1 < n && idx[i + 1] == pos + 1) v1 = ld_fr(val + i + 1);
+  } else {
+    v1 = ld_fr(val + i);
+  }
+  idx_out[slot] = pos >> 1;
+  st_fr(val_out + slot, add(v0, mul(r, sub(v1, v0))));
+}
+
+__global__ void k_scatter(const uint32_t* __restrict__ idx, const Fr* __restrict__ val,
+                          const uint32_t* __restrict__ count, Fr* dense) {
+  const uint32_t n = *count;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    st_fr(dense + idx[i], ld_fr(val + i));
+}
+
+// 1 when idx[0..n) is strictly increasing and below `limit`, else 0.
+__global__ void k_check_sorted(const uint32_t* __restrict__ idx, uint32_t n, uint64_t limit, uint32_t* bad) {
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    if ((uint64_t)idx[i] >= limit || (i > 0 && idx[i - 1] >= idx[i])) *bad = 1;
+  }
+}
+
+// Narrow caller indices (u64) to the 32-bit form the kernels use; flags values >= 2^32.
+__global__ void k_narrow_idx(const uint64_t* __restrict__ in, uint32_t n, uint32_t* out, uint32_t* bad) {
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const uint64_t v = in[i];
+    if (v >> 32) *bad = 1;
+    out[i] = (uint32_t)v;
+  }
+}
+
+// Final values when the prover ended in entry form: a = entry 0 if its index is 0, else 0.
+__global__ void k_sd_final(const uint32_t* idx, const Fr* val, const uint32_t* count, const Fr* dense, Fr* out) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  Fr a = Fr::zero();
+  if (*count > 0 && idx[0] == 0) a = val[0];
+  const Fr b = dense[0];
+  out[0] = a;
+  out[1] = b;
+  out[2] = mul(a, b);
+}
+
+inline int blocks_for(uint64_t n, int threads, int cap) {
+  uint64_t b = (n + threads - 1) / threads;
+  if (b < 1) b = 1;
+  if (b > (uint64_t)cap) b = cap;
+  return (int)b;
+}
+
+}  // namespace
+
+void launch_sparse_msg(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
+                       const RoundScratch& sc, cudaStream_t s) {
+  const int cap = sc.sm_count * 2 < sc.max_blocks ? sc.sm_count * 2 : sc.max_blocks;
+  k_sparse_msg<<<blocks_for(upper, kSpThreads, cap), kSpThreads, 0, s>>>(idx, val, count, dense, sc.partials, sc.counter,
+                                                                         sc.msg);
+}
+
+int launch_sparse_fold(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr& r,
+                       uint32_t* block_counts, uint32_t* idx_out, Fr* val_out, uint32_t* count_out, cudaStream_t s) {
+  const uint32_t blocks = upper ? (upper + kSpThreads - 1) / kSpThreads : 1;
+  k_sparse_count<<<blocks, kSpThreads, 0, s>>>(idx, count, block_counts);
+  k_scan_blocks<<<1, 1024, 0, s>>>(block_counts, blocks, count_out);
+  k_sparse_fold<<<blocks, kSpThreads, 0, s>>>(idx, val, count, block_counts, r, idx_out, val_out);
+  return 3;
+}
+
+void launch_scatter(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, Fr* dense,
+                    int sm_count, cudaStream_t s) {
+  k_scatter<<<blocks_for(upper, 256, sm_count * 8), 256, 0, s>>>(idx, val, count, dense);
+}
+
+void launch_check_sorted(const uint32_t* idx, uint32_t n, uint64_t limit, uint32_t* bad, int sm_count, cudaStream_t s) {
+  k_check_sorted<<<blocks_for(n, 256, sm_count * 8), 256, 0, s>>>(idx, n, limit, bad);
+}
+
+void launch_narrow_idx(const uint64_t* in, uint32_t n, uint32_t* out, uint32_t* bad, int sm_count, cudaStream_t s) {
+  k_narrow_idx<<<blocks_for(n, 256, sm_count * 8), 256, 0, s>>>(in, n, out, bad);
+}
+
+void launch_sd_final(const uint32_t* idx, const Fr* val, const uint32_t* count, const Fr* dense, Fr* out,
+                     cudaStream_t s) {
+  k_sd_final<<<1, 32, 0, s>>>(idx, val, count, dense, out);
+}
+
+}  // namespace zk
