@@ -55,6 +55,23 @@ void zk_free(zk_ctx* ctx);
 const char* zk_last_error(void);
 /* Number of kernels this library has launched on the context since it was created. */
 uint64_t zk_launch_count(const zk_ctx* ctx);
+/* The CUDA stream (cudaStream_t) every kernel of this context is launched on, so a host can
+ * bracket calls with its own events. */
+void* zk_stream(zk_ctx* ctx);
+/* Per-kernel-kind device timing (CUDA events on the context's stream around each launch).
+ * Enabling clears the totals.  zk_profile_get synchronises the stream and returns, for one
+ * kind, the launches, their summed duration and their summed algorithmic bytes. */
+typedef enum zk_prof_kind {
+  ZK_PROF_ROUND = 0,       /* dense round kernel (fold + message) */
+  ZK_PROF_FOLD = 1,        /* plain LSB fold */
+  ZK_PROF_SPARSE_MSG = 2,  /* round message over sparse entries */
+  ZK_PROF_SPARSE_FOLD = 3, /* entry fold + compaction (3 launches per round) */
+  ZK_PROF_FROM_RIGHT = 4,  /* fix_variables_from_right / eq tables */
+  ZK_PROF_MSM = 5,         /* multi-scalar multiplication pipeline */
+  ZK_PROF_OTHER = 6
+} zk_prof_kind;
+int zk_profile_enable(zk_ctx* ctx, int on);
+int zk_profile_get(zk_ctx* ctx, int kind, uint64_t* launches, double* ms, double* bytes);
 /* Device memory owned by the caller (thin cudaMalloc / cudaFree / cudaMemcpy wrappers for
  * hosts that do not link the CUDA runtime themselves). */
 int zk_device_alloc(zk_ctx* ctx, size_t bytes, void** out);
@@ -109,6 +126,17 @@ int zk_sumcheck_sparse_dense_prove(zk_ctx* ctx, uint32_t num_var, uint64_t nnz, 
  * 2^n table to point[0..k); out receives 2^(n-k) elements. */
 int zk_fold_lsb(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, uint32_t k, const uint64_t* point,
                 uint64_t* out, zk_mem out_mem);
+
+/* ---- seeded synthetic inputs (no counterpart in the reference; its bins draw from StdRng) --- */
+/* Element i of stream (seed, stream) = ChaCha20 block `start + i` (key = seed | stream as two
+ * little-endian u64 then zeros, zero nonce) read as a 512-bit little-endian integer mod r.
+ * Writes `count` elements (Montgomery form) to the device buffer out_dev. */
+int zk_gen_uniform_fr(zk_ctx* ctx, uint64_t seed, uint64_t stream, uint64_t start, uint64_t count, uint64_t* out_dev);
+/* Same stream; element i = (first keystream word of block start+i, low `bits` bits) - 2^(bits-1),
+ * a signed `bits`-bit integer lifted into Fr (negatives as r - |v|), as quantised weights and
+ * activations are (src/bin/gpt2.rs:44-49). */
+int zk_gen_small_fr(zk_ctx* ctx, uint64_t seed, uint64_t stream, uint64_t start, uint64_t count, int bits,
+                    uint64_t* out_dev);
 
 /* ---- measurement ---------------------------------------------------------------------- */
 /* Throughput probe for the integer roofline (no counterpart in the reference).  kind 0: 32-bit

@@ -616,6 +616,16 @@ def gen_uniform_fr(seed: int, stream: int, start: int, count: int):
     return [int.from_bytes(_chacha_block(key, start + i), "little") % R_MOD for i in range(count)]
 
 
+def gen_small_fr(seed: int, stream: int, start: int, count: int, bits: int):
+    """Element i = (first keystream word of block i, low `bits` bits) - 2^(bits-1), lifted into Fr."""
+    key = chacha_key(seed, stream)
+    out = []
+    for i in range(count):
+        w = struct.unpack("<I", _chacha_block(key, start + i)[:4])[0] & ((1 << bits) - 1)
+        out.append((w - (1 << (bits - 1))) % R_MOD)
+    return out
+
+
 def gen_bytes(seed: int, stream: int, start_block: int, nblocks: int) -> bytes:
     key = chacha_key(seed, stream)
     return b"".join(_chacha_block(key, start_block + i) for i in range(nblocks))

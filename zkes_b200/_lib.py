@@ -23,6 +23,10 @@ SIGNATURES = {
     "zk_free": (None, [c_void_p]),
     "zk_last_error": (c_char_p, []),
     "zk_launch_count": (c_uint64, [c_void_p]),
+    "zk_stream": (c_void_p, [c_void_p]),
+    "zk_profile_enable": (c_int, [c_void_p, c_int]),
+    "zk_profile_get": (c_int, [c_void_p, c_int, POINTER(c_uint64), POINTER(ctypes.c_double),
+                               POINTER(ctypes.c_double)]),
     "zk_device_alloc": (c_int, [c_void_p, c_size_t, POINTER(c_void_p)]),
     "zk_device_free": (c_int, [c_void_p, c_void_p]),
     "zk_device_copy": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_size_t]),
@@ -40,6 +44,8 @@ SIGNATURES = {
     "zk_sumcheck_sparse_dense_prove": (c_int, [c_void_p, c_uint32, c_uint64, c_void_p, c_void_p, c_void_p, c_int,
                                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                c_void_p]),
+    "zk_gen_uniform_fr": (c_int, [c_void_p, c_uint64, c_uint64, c_uint64, c_uint64, c_void_p]),
+    "zk_gen_small_fr": (c_int, [c_void_p, c_uint64, c_uint64, c_uint64, c_uint64, c_int, c_void_p]),
     "zk_microbench": (c_int, [c_void_p, c_int, c_int, c_int, c_int, POINTER(ctypes.c_float),
                               POINTER(ctypes.c_double)]),
     "zk_fold_lsb": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_int]),

@@ -77,6 +77,37 @@ void zk_free(zk_ctx* ctx) {
 
 uint64_t zk_launch_count(const zk_ctx* ctx) { return ctx ? ctx->launches.load() : 0; }
 
+void* zk_stream(zk_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+int zk_profile_enable(zk_ctx* ctx, int on) {
+  if (!ctx) return fail(ZK_ERR_ARG, "zk_profile_enable: NULL context");
+  CtxLock lk(ctx);
+  ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+  int rc = ctx->prof_collect();
+  if (rc) return rc;
+  ctx->prof_on = on != 0;
+  if (on) {
+    for (int k = 0; k < zk_ctx::kProfKinds; k++) {
+      ctx->prof_launches[k] = 0;
+      ctx->prof_bytes[k] = 0;
+      ctx->prof_ms[k] = 0;
+    }
+  }
+  return ZK_OK;
+}
+
+int zk_profile_get(zk_ctx* ctx, int kind, uint64_t* launches, double* ms, double* bytes) {
+  if (!ctx || kind < 0 || kind >= zk_ctx::kProfKinds) return fail(ZK_ERR_ARG, "zk_profile_get: bad argument");
+  CtxLock lk(ctx);
+  ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+  int rc = ctx->prof_collect();
+  if (rc) return rc;
+  if (launches) *launches = ctx->prof_launches[kind];
+  if (ms) *ms = ctx->prof_ms[kind];
+  if (bytes) *bytes = ctx->prof_bytes[kind];
+  return ZK_OK;
+}
+
 int zk_device_alloc(zk_ctx* ctx, size_t bytes, void** out) {
   if (!ctx || !out) return fail(ZK_ERR_ARG, "zk_device_alloc: NULL argument");
   CtxLock lk(ctx);
@@ -177,12 +208,15 @@ int zk_sumcheck_linear_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, c
   for (uint32_t round = 0; round < num_var; round++) {
     const uint64_t pairs = size >> (round + 1);
     if (round == 0) {
+      ctx->prof_begin(ZK_PROF_ROUND, 64.0 * L * pairs);
       launch_round(L, false, cur, nullptr, challenge, pairs, ctx->rs, ctx->stream);
     } else {
       Fr** dst = (round & 1) ? ping : pong;
+      ctx->prof_begin(ZK_PROF_ROUND, 192.0 * L * pairs);
       launch_round(L, true, cur, dst, challenge, pairs, ctx->rs, ctx->stream);
       for (int i = 0; i < L; i++) cur[i] = dst[i];
     }
+    ctx->prof_end();
     ctx->launches++;
     ZK_CUDA(cudaGetLastError());
     rc = fs_round(ctx, L + 1, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
@@ -220,7 +254,9 @@ int zk_fold_lsb(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem
   Fr* bufs[2] = {base + in_elems, base + in_elems + size / 2 + 1};
   for (uint32_t i = 0; i < k; i++) {
     Fr* dst = bufs[i & 1];
+    ctx->prof_begin(ZK_PROF_FOLD, 96.0 * (double)(size >> (i + 1)));
     launch_fold(cur, dst, fr_load(point + 4 * (uint64_t)i), size >> (i + 1), ctx->rs.max_blocks, ctx->stream);
+    ctx->prof_end();
     ctx->launches++;
     cur = dst;
   }

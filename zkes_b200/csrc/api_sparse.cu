@@ -103,26 +103,35 @@ extern "C" int zk_sumcheck_sparse_dense_prove(zk_ctx* ctx, uint32_t num_var, uin
       mode = kDenseFirst;
     }
     if (mode == kSparse) {
+      // per live entry: index + value read, one 64-byte pair of b gathered
+      ctx->prof_begin(ZK_PROF_SPARSE_MSG, 104.0 * k_upper);
       launch_sparse_msg(e_idx[e], e_val[e], counts + e, k_upper, b_cur, ctx->rs, s);
     } else if (mode == kDenseFirst) {
+      ctx->prof_begin(ZK_PROF_ROUND, 64.0 * 2 * (double)(S / 2));
       launch_round(2, false, d_cur, nullptr, challenge, S / 2, ctx->rs, s);
       mode = kDense;
     } else {
       Fr** dst = d_toggle ? d_pong : d_ping;
       d_toggle ^= 1;
+      ctx->prof_begin(ZK_PROF_ROUND, 192.0 * 2 * (double)(S / 2));
       launch_round(2, true, d_cur, dst, challenge, S / 2, ctx->rs, s);
       d_cur[0] = dst[0];
       d_cur[1] = dst[1];
     }
+    ctx->prof_end();
     ctx->launches++;
     rc = fs_round(ctx, 3, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
     if (rc != ZK_OK) return rc;
     if (mode == kSparse) {
       Fr* nb = b_buf[round & 1];
+      ctx->prof_begin(ZK_PROF_FOLD, 96.0 * (double)(S / 2));
       launch_fold(b_cur, nb, challenge, S / 2, ctx->rs.max_blocks, s);
+      ctx->prof_end();
       b_cur = nb;
+      ctx->prof_begin(ZK_PROF_SPARSE_FOLD, 80.0 * k_upper, 3);
       ctx->launches += 1 + launch_sparse_fold(e_idx[e], e_val[e], counts + e, k_upper, challenge, block_counts,
                                               e_idx[e ^ 1], e_val[e ^ 1], counts + (e ^ 1), s);
+      ctx->prof_end();
       e ^= 1;
       if ((uint64_t)k_upper > S / 2) k_upper = (uint32_t)(S / 2);
     }

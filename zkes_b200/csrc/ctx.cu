@@ -27,6 +27,10 @@ void zk_ctx::teardown() {
   cudaFree(final_out);
   cudaFree(work);
   if (host_small) cudaFreeHost(host_small);
+  for (auto& sp : prof_spans) {
+    cudaEventDestroy(sp.e0);
+    cudaEventDestroy(sp.e1);
+  }
   if (stream) cudaStreamDestroy(stream);
 }
 
@@ -45,5 +49,37 @@ int zk_ctx::reserve_work(size_t bytes, void** out) {
     work_bytes = want;
   }
   *out = work;
+  return 0;
+}
+
+void zk_ctx::prof_begin(int kind, double bytes, int n_launches) {
+  if (!prof_on) return;
+  if (prof_used == prof_spans.size()) {
+    ProfSpan sp;
+    cudaEventCreate(&sp.e0);
+    cudaEventCreate(&sp.e1);
+    prof_spans.push_back(sp);
+  }
+  ProfSpan& sp = prof_spans[prof_used];
+  sp.kind = kind;
+  prof_launches[kind] += n_launches;
+  prof_bytes[kind] += bytes;
+  cudaEventRecord(sp.e0, stream);
+}
+
+void zk_ctx::prof_end() {
+  if (!prof_on) return;
+  cudaEventRecord(prof_spans[prof_used].e1, stream);
+  prof_used++;
+}
+
+int zk_ctx::prof_collect() {
+  for (size_t i = 0; i < prof_used; i++) {
+    float ms = 0;
+    ZK_CUDA(cudaEventSynchronize(prof_spans[i].e1));
+    ZK_CUDA(cudaEventElapsedTime(&ms, prof_spans[i].e0, prof_spans[i].e1));
+    prof_ms[prof_spans[i].kind] += ms;
+  }
+  prof_used = 0;
   return 0;
 }

@@ -5,6 +5,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "internal.hpp"
 #include "merlin.hpp"
@@ -55,6 +56,19 @@ struct zk_ctx {
   size_t work_bytes = 0;
   std::mutex mu;
   std::atomic<uint64_t> launches{0};
+
+  // Optional per-kernel-kind timing with CUDA events on the context's stream.
+  static constexpr int kProfKinds = 8;
+  bool prof_on = false;
+  struct ProfSpan { cudaEvent_t e0, e1; int kind; };
+  std::vector<ProfSpan> prof_spans;
+  size_t prof_used = 0;
+  uint64_t prof_launches[kProfKinds] = {0};
+  double prof_bytes[kProfKinds] = {0};
+  double prof_ms[kProfKinds] = {0};
+  void prof_begin(int kind, double bytes, int n_launches = 1);
+  void prof_end();
+  int prof_collect();  // after a stream sync: fold finished spans into prof_ms
 
   int setup();
   void teardown();
