@@ -127,6 +127,23 @@ int zk_sumcheck_sparse_dense_prove(zk_ctx* ctx, uint32_t num_var, uint64_t nnz, 
 int zk_fold_lsb(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, uint32_t k, const uint64_t* point,
                 uint64_t* out, zk_mem out_mem);
 
+/* Fold for callers that cannot allocate device memory (this entry point has no counterpart in
+ * the reference).  Same result as zk_fold_lsb for tables of at most 2^ZK_FOLD_STATIC_MAX_VARS
+ * elements; larger n is rejected with ZK_ERR_ARG.  evals_dev and out_dev are device buffers
+ * owned by the caller (2^n and 2^(n-k) elements, not overlapping), point is a host array of k
+ * elements, stream is the cudaStream_t (or NULL) the work is queued on; the call returns
+ * without waiting for it.  It uses the calling thread's current device, takes no zk_ctx, and
+ * calls no cudaMalloc / cudaFree or any other allocating routine: the intermediate tables
+ * live in a 1.5 MiB array that is part of the library image on every GPU that loads it.
+ * The first call on a device looks up that array's device address; make that first call
+ * outside any stream capture.  All calls on a device share the array (it keeps the previous
+ * call's intermediates; nothing in it has to start at zero, every element read was written
+ * earlier in the same call), so two calls whose work overlaps on the GPU race: keep them on
+ * one stream or order them yourself. */
+#define ZK_FOLD_STATIC_MAX_VARS 16
+int zk_fold_lsb_static(uint32_t n, const uint64_t* evals_dev, uint32_t k, const uint64_t* point, uint64_t* out_dev,
+                       void* stream);
+
 /* ---- seeded synthetic inputs (no counterpart in the reference; its bins draw from StdRng) --- */
 /* Element i of stream (seed, stream) = ChaCha20 block `start + i` (key = seed | stream as two
  * little-endian u64 then zeros, zero nonce) read as a 512-bit little-endian integer mod r.

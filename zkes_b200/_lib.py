@@ -44,6 +44,7 @@ SIGNATURES = {
     "zk_sumcheck_sparse_dense_prove": (c_int, [c_void_p, c_uint32, c_uint64, c_void_p, c_void_p, c_void_p, c_int,
                                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                c_void_p]),
+    "zk_fold_lsb_static": (c_int, [c_uint32, c_void_p, c_uint32, c_void_p, c_void_p, c_void_p]),
     "zk_gen_uniform_fr": (c_int, [c_void_p, c_uint64, c_uint64, c_uint64, c_uint64, c_void_p]),
     "zk_gen_small_fr": (c_int, [c_void_p, c_uint64, c_uint64, c_uint64, c_uint64, c_int, c_void_p]),
     "zk_microbench": (c_int, [c_void_p, c_int, c_int, c_int, c_int, POINTER(ctypes.c_float),
