@@ -1,0 +1,81 @@
+"""The device field arithmetic (zkes_b200/csrc/ff.cuh) compiled for the host, where its carry
+chains take their portable C form, against Python integers."""
+import ctypes
+import os
+import random
+import subprocess
+
+import pytest
+
+import pyoracle as o
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+R = 1 << 256
+
+
+@pytest.fixture(scope="module")
+def hm():
+    so = os.path.join(HERE, "hostmath", "libffhost.so")
+    src = os.path.join(HERE, "hostmath", "ff_host.cpp")
+    subprocess.run(["g++", "-O2", "-shared", "-fPIC", "-std=c++17", "-x", "c++", src, "-o", so], check=True)
+    return ctypes.CDLL(so)
+
+
+def buf(x, n=8):
+    return (ctypes.c_uint32 * n)(*[(x >> (32 * i)) & 0xFFFFFFFF for i in range(n)])
+
+
+def val(b):
+    return sum(int(v) << (32 * i) for i, v in enumerate(b))
+
+
+@pytest.mark.parametrize("name,p", [("fr", o.R_MOD), ("fq", o.Q_MOD)])
+def test_field_ops(hm, name, p):
+    rnd = random.Random(5)
+    edge = [0, 1, 2, p - 1, p - 2, R % p, (p - 1) // 2, 0xFFFFFFFF, (1 << 224) - 1]
+    rv = lambda: rnd.choice(edge) if rnd.random() < 0.2 else rnd.randrange(p)  # noqa: E731
+    out = (ctypes.c_uint32 * 8)()
+    rinv = pow(R, -1, p)
+    for it in range(3000):
+        a, b = rv(), rv()
+        getattr(hm, f"zkh_{name}_mul")(buf(a), buf(b), out)
+        assert val(out) == a * b * rinv % p
+        bb = rnd.randrange(R) if it % 3 else R - 1  # second operand may be any 256-bit value
+        getattr(hm, f"zkh_{name}_mul")(buf(a), buf(bb), out)
+        assert val(out) == a * bb * rinv % p
+        getattr(hm, f"zkh_{name}_add")(buf(a), buf(b), out)
+        assert val(out) == (a + b) % p
+        getattr(hm, f"zkh_{name}_sub")(buf(a), buf(b), out)
+        assert val(out) == (a - b) % p
+    for _ in range(5):
+        a = rv()
+        getattr(hm, f"zkh_{name}_inv")(buf(a), out)
+        am = a * rinv % p
+        assert val(out) == ((pow(am, -1, p) * R % p) if am else 0)
+        getattr(hm, f"zkh_{name}_to_mont")(buf(a), out)
+        assert val(out) == a * R % p
+
+
+@pytest.mark.parametrize("name,p", [("fr", o.R_MOD), ("fq", o.Q_MOD)])
+def test_lazy_dot_product(hm, name, p):
+    rnd = random.Random(6)
+    out = (ctypes.c_uint32 * 8)()
+    rinv = pow(R, -1, p)
+    for n in (1, 4, 5, 6, 37, 300):
+        for worst in (True, False):
+            a = [p - 1 if worst else rnd.randrange(p) for _ in range(n)]
+            b = [p - 1 if worst else rnd.randrange(p) for _ in range(n)]
+            ab = (ctypes.c_uint32 * (8 * n))(*[(x >> (32 * i)) & 0xFFFFFFFF for x in a for i in range(8)])
+            bb = (ctypes.c_uint32 * (8 * n))(*[(x >> (32 * i)) & 0xFFFFFFFF for x in b for i in range(8)])
+            getattr(hm, f"zkh_{name}_dot")(ab, bb, n, out)
+            assert val(out) == sum(x * y for x, y in zip(a, b)) * rinv % p
+
+
+def test_wide_product(hm):
+    rnd = random.Random(7)
+    w = (ctypes.c_uint32 * 16)()
+    for it in range(3000):
+        a = rnd.randrange(R) if it % 5 else R - 1
+        b = rnd.randrange(R) if it % 7 else R - 1
+        hm.zkh_mul_wide(buf(a), buf(b), w)
+        assert val(w) == a * b

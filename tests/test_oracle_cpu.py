@@ -1,0 +1,138 @@
+"""CPU checks of the oracle itself: known answers the reference's tests make derivable by hand,
+Keccak against hashlib, the committed golden vectors, and agreement of the two restatements."""
+import hashlib
+import json
+import os
+import random
+
+import coracle as c
+import pyoracle as o
+
+GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "sumcheck.json")))
+
+
+def ints(xs):
+    return [int(x, 16) for x in xs]
+
+
+def test_keccak_against_hashlib():
+    for msg in (b"", b"abc", b"q" * 135, b"q" * 136, b"z" * 777):
+        assert o.sponge(msg, 136, 0x06, 32) == hashlib.sha3_256(msg).digest()
+        assert o.sponge(msg, 168, 0x1F, 300) == hashlib.shake_128(msg).digest(300)
+
+
+def test_merlin_known_answer():
+    t = o.Transcript(b"test protocol")
+    t.append_message(b"some label", b"some data")
+    got = t.challenge_bytes(b"challenge", 32).hex()
+    assert got == GOLD["merlin"]["simple"]
+    # the merlin crate's published vector for this exchange, as recalled; one hex digit of the
+    # recollection differs, the other 63 agree
+    recalled = "d5a21972d0d5fe320c0d263fac7fffb8145aa640af6e9bfa177c03c7efcf0615"
+    assert sum(a == b for a, b in zip(got, recalled)) >= 63
+
+
+def test_fix_variables_hand_cases():  # tests/test_fix_variables.rs:19-140
+    assert o.fix_variables([1, 2, 3, 4], [0]) == [1, 3]
+    assert o.fix_variables([1, 2, 3, 4], [1]) == [2, 4]
+    assert c.fix_variables([1, 2, 3, 4], [0]) == [1, 3]
+    r = 5  # f(x0, x1) = 1 + x0 + 2 x1 on [1,2,3,4]: binding x0 = 5 gives [6, 8]
+    assert o.fix_variables([1, 2, 3, 4], [r]) == [6, 8]
+    g = list(range(1, 9))
+    assert o.fix_variables(g, [1, 0]) == [2, 6]
+    assert c.fix_variables(g, [0, 1, 1]) == [7]
+    # fix_variables_from_right against the closed form (:278-307): binding x1 of [1,2,3,4]
+    assert o.fix_variables_from_right([1, 2, 3, 4], [0]) == [1, 2]
+    assert o.fix_variables_from_right([1, 2, 3, 4], [1]) == [3, 4]
+    assert c.fix_from_right([1, 2, 3, 4], [7]) == [(1 + 7 * 2) % o.R_MOD, (2 + 7 * 2) % o.R_MOD]
+
+
+def test_lagrange_basis_hand_cases():  # tests/test_lagrange_basis.rs:16-127
+    assert o.evaluate_lagrange_basis([]) == [1]
+    r0, r1 = 3, 10
+    m = o.R_MOD
+    assert o.evaluate_lagrange_basis([r0]) == [(1 - r0) % m, r0]
+    assert o.evaluate_lagrange_basis([r0, r1]) == [(1 - r0) * (1 - r1) % m, r0 * (1 - r1) % m, (1 - r0) * r1 % m, r0 * r1 % m]
+    rnd = random.Random(1)
+    pt = [rnd.randrange(m) for _ in range(5)]
+    assert sum(o.evaluate_lagrange_basis(pt)) % m == 1  # partition of unity
+    assert o.evaluate_lagrange_basis([1, 0, 1]) == [1 if i == 5 else 0 for i in range(8)]  # vertices
+    assert c.eq_table(pt) == o.evaluate_lagrange_basis(pt)
+
+
+def test_claimed_sums_verify():  # tests/test_linear_sumcheck.rs: sums 4, 1, 1
+    for tables, claimed in (([[1, 1, 1, 1], [1, 1, 1, 1]], 4), ([[0, 1, 0, 1], [0, 0, 1, 1]], 1), ([[0, 1]], 1)):
+        n = len(tables[0]).bit_length() - 1
+        t = o.Transcript(b"sumcheck")
+        p = o.LinearSumcheckProver(n, len(tables), t)
+        pr = p.prove(tables, t)
+        vt = o.Transcript(b"sumcheck")
+        res, ch = o.SumcheckVerifier(n, len(tables), vt).verify(vt, pr.round_messages, claimed)
+        assert res == pr.final_eval and ch == p.challenges
+        vt = o.Transcript(b"sumcheck")
+        bad, _ = o.SumcheckVerifier(n, len(tables), vt).verify(vt, pr.round_messages, claimed + 1)
+        assert bad is None
+
+
+def test_golden_linear_both_oracles():
+    for case in GOLD["linear"]:
+        tables = [ints(t) for t in case["tables"]]
+        label = case["label"].encode()
+        n = len(tables[0]).bit_length() - 1
+        t = o.Transcript(label)
+        p = o.LinearSumcheckProver(n, len(tables), t)
+        pr = p.prove(tables, t)
+        want = [ints(m) for m in case["round_messages"]]
+        assert pr.round_messages == want and pr.final_eval == int(case["final_eval"], 16)
+        cp = c.linear_prove(label, tables)
+        assert cp.round_messages == want and cp.challenges == ints(case["challenges"])
+        assert cp.final_eval == int(case["final_eval"], 16) and cp.tail == int(case["tail"], 16)
+
+
+def test_golden_sparse_dense_and_bool():
+    import numpy as np
+    for case in GOLD["sparse_dense"]:
+        cp = c.sparse_dense_prove_mont(b"sd_sumcheck", case["n"], np.array(case["idx"], dtype=np.uint64),
+                                       c.mont(ints(case["vals"])), c.mont(ints(case["dense"])))
+        assert cp.round_messages == [ints(m) for m in case["round_messages"]]
+        assert cp.final_eval == int(case["final_eval"], 16) and cp.tail == int(case["tail"], 16)
+    for case in GOLD["sparse_bool"]:
+        cp = c.sparse_bool_prove(b"range", case["n"], ints(case["weights"]), case["positions"], ints(case["eq_point"]))
+        assert cp.round_messages == [ints(m) for m in case["round_messages"]]
+        assert cp.final_eval == int(case["final_eval"], 16) and cp.tail == int(case["tail"], 16)
+        vt = o.Transcript(b"range")  # the range-proof claim is 0 (dag/mod.rs:1343-1351)
+        res, _ = o.SumcheckVerifier(case["n"], 3, vt).verify(vt, [ints(m) for m in case["round_messages"]], 0)
+        assert res == int(case["final_eval"], 16)
+
+
+def test_golden_poly_helpers():
+    g = GOLD["poly"]
+    f, pt = ints(g["f"]), ints(g["point"])
+    assert c.eq_table(pt[:4]) == ints(g["eq"]) == o.evaluate_lagrange_basis(pt[:4])
+    assert c.fix_variables(f, pt[:3]) == ints(g["fix_lsb_3"])
+    assert c.fix_from_right(f, pt[:2]) == ints(g["fix_right_2"])
+    assert c.mle_eval(f, pt) == int(g["mle"], 16)
+    assert o.gen_uniform_fr(7, 3, 5, 4) == ints(g["uniform_seed7"])
+    assert o.gen_small_fr(7, 3, 5, 8, 8) == ints(g["small_seed7_bits8"])
+
+
+def test_chacha_against_cryptography():
+    """The input generator's keystream is RFC 8439 ChaCha20 (checked against `cryptography`)."""
+    import struct
+    from cryptography.hazmat.primitives.ciphers import Cipher, algorithms
+    key = struct.pack("<QQ16x", 9, 4)
+    for counter in (0, 1, 77):
+        nonce = struct.pack("<I12x", counter)  # library layout: 32-bit counter then 96-bit nonce
+        ks = Cipher(algorithms.ChaCha20(key, nonce), mode=None).encryptor().update(b"\x00" * 64)
+        assert ks == o.gen_bytes(9, 4, counter, 1)
+
+
+def test_multithreaded_oracle_matches_single():
+    rnd = random.Random(8)
+    tables = [[rnd.randrange(o.R_MOD) for _ in range(1 << 13)] for _ in range(2)]
+    c.set_threads(1)
+    a = c.linear_prove(b"x", tables)
+    c.set_threads(4)
+    b = c.linear_prove(b"x", tables)
+    c.set_threads(1)
+    assert a.round_messages == b.round_messages and a.final_eval == b.final_eval
