@@ -157,7 +157,9 @@ int zk_gen_small_fr(zk_ctx* ctx, uint64_t seed, uint64_t stream, uint64_t start,
 
 /* ---- measurement ---------------------------------------------------------------------- */
 /* Throughput probe for the integer roofline (no counterpart in the reference).  kind 0: 32-bit
- * multiply-add, 1: 32x32+64 wide multiply-add, 2 / 3: Montgomery product in Fr / Fq.  Runs the
+ * multiply-add, 1: 32x32+64 wide multiply-add, 2 / 3: Montgomery product in Fr / Fq, 4 / 5: wide
+ * multiply-adds inside carry chains (without / with carry-out), 6: separate lo and hi multiply-adds,
+ * 7: 32-bit adds in carry chains, 8: fp64 fused multiply-add, 9: product with a launch-constant multiplier in Fr.  Runs the
  * probe twice and reports the second run: elapsed milliseconds and operations executed. */
 int zk_microbench(zk_ctx* ctx, int kind, int blocks, int threads, int iters, float* ms_out, double* ops_out);
 

@@ -20,6 +20,9 @@ template <class P> static void ld(Fp<P>& x, const uint32_t* p) { memcpy(x.v, p, 
     Fp<P> x; ld(x, a); Fp<P> z = to_mont(x); memcpy(r, z.v, 32); }                           \
   extern "C" void zkh_##name##_from_mont(const uint32_t* a, uint32_t* r) {                   \
     Fp<P> x; ld(x, a); Fp<P> z = from_mont(x); memcpy(r, z.v, 32); }                         \
+  extern "C" void zkh_##name##_mul_fixed(const uint32_t* x, const uint32_t* d, uint32_t* r) {  \
+    Fp<P> a, b; ld(a, x); ld(b, d); FixedMul<P> t = make_fixed_mul(a);                        \
+    Fp<P> z = mul_fixed(t, b); memcpy(r, z.v, 32); }                                         \
   /* sum of n products through the lazy accumulator, trimmed every kLazyProducts */         \
   extern "C" void zkh_##name##_dot(const uint32_t* a, const uint32_t* b, int n, uint32_t* r) { \
     Wide acc; memset(&acc, 0, sizeof acc); int pending = 0;                                  \

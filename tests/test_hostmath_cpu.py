@@ -43,6 +43,8 @@ def test_field_ops(hm, name, p):
         bb = rnd.randrange(R) if it % 3 else R - 1  # second operand may be any 256-bit value
         getattr(hm, f"zkh_{name}_mul")(buf(a), buf(bb), out)
         assert val(out) == a * bb * rinv % p
+        getattr(hm, f"zkh_{name}_mul_fixed")(buf(a), buf(b), out)
+        assert val(out) == a * b * rinv % p
         getattr(hm, f"zkh_{name}_add")(buf(a), buf(b), out)
         assert val(out) == (a + b) % p
         getattr(hm, f"zkh_{name}_sub")(buf(a), buf(b), out)

@@ -101,6 +101,31 @@ ZK_HD void add_limb8(uint32_t* acc, uint32_t t) {
 #endif
 }
 
+// acc[0..8] += t (single limb) rippling through nine limbs; the caller has proved no carry out.
+ZK_HD void add_limb9(uint32_t* acc, uint32_t t) {
+#ifdef __CUDA_ARCH__
+  asm("add.cc.u32  %0, %0, %9;\n\t"
+      "addc.cc.u32 %1, %1, 0;\n\t"
+      "addc.cc.u32 %2, %2, 0;\n\t"
+      "addc.cc.u32 %3, %3, 0;\n\t"
+      "addc.cc.u32 %4, %4, 0;\n\t"
+      "addc.cc.u32 %5, %5, 0;\n\t"
+      "addc.cc.u32 %6, %6, 0;\n\t"
+      "addc.cc.u32 %7, %7, 0;\n\t"
+      "addc.u32    %8, %8, 0;"
+      : "+r"(acc[0]), "+r"(acc[1]), "+r"(acc[2]), "+r"(acc[3]), "+r"(acc[4]), "+r"(acc[5]), "+r"(acc[6]),
+        "+r"(acc[7]), "+r"(acc[8])
+      : "r"(t));
+#else
+  uint64_t c = t;
+  for (int k = 0; k < 9; k++) {
+    c += acc[k];
+    acc[k] = (uint32_t)c;
+    c >>= 32;
+  }
+#endif
+}
+
 // r = a + b over 8 limbs, returns the carry out.
 ZK_HD uint32_t add8(uint32_t* r, const uint32_t* a, const uint32_t* b) {
 #ifdef __CUDA_ARCH__
@@ -343,6 +368,74 @@ ZK_HD Fp<P> mul(const Fp<P>& a, const Fp<P>& b) {
     }
   }
   // value = E + 2^32 * O  (< 2p < 2^256)
+  Fp<P> r;
+  uint32_t S[8];
+  S[0] = 0;
+#pragma unroll
+  for (int k = 1; k < 8; k++) S[k] = O[k - 1];
+  (void)add8(r.v, E, S);
+  final_sub<P>(r.v, 0);
+  return r;
+}
+
+// Multiplication by a value that is fixed for a whole launch (a round challenge).
+//
+// For a fixed x the table holds c[j] = x * 2^(32 j + 64) mod p as plain integers.  Then for any
+// d in Montgomery form, sum_j d_j c[j] = 2^64 * (x d) (mod p) needs 8 rows of 8 multiply-adds
+// and no 512-bit intermediate; two Montgomery rounds remove the factor 2^64 and bring the
+// 291-bit sum below 2^227 + p, so one conditional subtraction completes it: 82 multiply-adds
+// against 136 for a general product.  The result is x*d in Montgomery form (d's own factor R).
+template <class P>
+struct FixedMul {
+  uint32_t c[8][8];
+};
+
+// Build the table from x in Montgomery form (host or device).
+template <class P>
+ZK_HD FixedMul<P> make_fixed_mul(const Fp<P>& x_mont) {
+  FixedMul<P> t;
+  Fp<P> two64 = Fp<P>::zero();
+  two64.v[2] = 1;
+  Fp<P> two32 = Fp<P>::zero();
+  two32.v[1] = 1;
+  const Fp<P> step = to_mont(two32);  // 2^32 * R
+  Fp<P> cur = mul(x_mont, two64);     // x * 2^64 as a plain integer mod p
+  for (int j = 0; j < 8; j++) {
+    for (int k = 0; k < 8; k++) t.c[j][k] = cur.v[k];
+    cur = mul(cur, step);             // times 2^32
+  }
+  return t;
+}
+
+template <class P>
+ZK_HD Fp<P> mul_fixed(const FixedMul<P>& t, const Fp<P>& d) {
+  uint32_t E[9], O[9];
+#pragma unroll
+  for (int i = 0; i < 9; i++) E[i] = O[i] = 0;
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    E[8] += madwide4_c(E, t.c[j][0], t.c[j][2], t.c[j][4], t.c[j][6], d.v[j]);
+    O[8] += madwide4_c(O, t.c[j][1], t.c[j][3], t.c[j][5], t.c[j][7], d.v[j]);
+  }
+#pragma unroll
+  for (int round = 0; round < 2; round++) {
+    const uint32_t m = E[0] * P::inv;
+    E[8] += madwide4_c(E, P::mod(0), P::mod(2), P::mod(4), P::mod(6), m);
+    O[8] += madwide4_c(O, P::mod(1), P::mod(3), P::mod(5), P::mod(7), m);
+    // divide by 2^32: new even = O + E[1] (nine limbs), new odd = E >> 64
+    add_limb9(O, E[1]);
+    uint32_t T[9];
+#pragma unroll
+    for (int k = 0; k < 7; k++) T[k] = E[k + 2];
+    T[7] = 0;
+    T[8] = 0;
+#pragma unroll
+    for (int k = 0; k < 9; k++) {
+      E[k] = O[k];
+      O[k] = T[k];
+    }
+  }
+  // value = E + 2^32 * O < 2^227 + p
   Fp<P> r;
   uint32_t S[8];
   S[0] = 0;

@@ -128,7 +128,8 @@ __global__ void __launch_bounds__(1024) k_scan_blocks(uint32_t* block_counts, ui
 // Pass 3: fold each pair and write it at its compacted slot.
 __global__ void __launch_bounds__(kSpThreads) k_sparse_fold(const uint32_t* __restrict__ idx, const Fr* __restrict__ val,
                                                             const uint32_t* __restrict__ count,
-                                                            const uint32_t* __restrict__ block_offsets, Fr r,
+                                                            const uint32_t* __restrict__ block_offsets,
+                                                            const FixedMul<FrParams> r,
                                                             uint32_t* idx_out, Fr* val_out) {
   __shared__ uint32_t warp_cnt[kSpThreads / 32];
   const uint32_t n = *count;
@@ -154,7 +155,7 @@ __global__ void __launch_bounds__(kSpThreads) k_sparse_fold(const uint32_t* __re
     v1 = ld_fr(val + i);
   }
   idx_out[slot] = pos >> 1;
-  st_fr(val_out + slot, add(v0, mul(r, sub(v1, v0))));
+  st_fr(val_out + slot, add(v0, mul_fixed(r, sub(v1, v0))));
 }
 
 __global__ void k_scatter(const uint32_t* __restrict__ idx, const Fr* __restrict__ val,
@@ -212,7 +213,7 @@ int launch_sparse_fold(const uint32_t* idx, const Fr* val, const uint32_t* count
   const uint32_t blocks = upper ? (upper + kSpThreads - 1) / kSpThreads : 1;
   k_sparse_count<<<blocks, kSpThreads, 0, s>>>(idx, count, block_counts);
   k_scan_blocks<<<1, 1024, 0, s>>>(block_counts, blocks, count_out);
-  k_sparse_fold<<<blocks, kSpThreads, 0, s>>>(idx, val, count, block_counts, r, idx_out, val_out);
+  k_sparse_fold<<<blocks, kSpThreads, 0, s>>>(idx, val, count, block_counts, make_fixed_mul(r), idx_out, val_out);
   return 3;
 }
 

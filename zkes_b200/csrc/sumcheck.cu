@@ -23,7 +23,7 @@ template <int L>
 struct RoundParams {
   const Fr* src[L];
   Fr* dst[L];
-  Fr r;
+  FixedMul<FrParams> r;  // multiplier table of the challenge being bound
   uint64_t pairs;  // (even, odd) pairs of the table the message is computed over
   Fr* partials;
   unsigned int* counter;
@@ -31,7 +31,7 @@ struct RoundParams {
 };
 
 template <int L, bool FOLD>
-__global__ void __launch_bounds__(kThreads, (L <= 2 ? 3 : 2)) k_round(const RoundParams<L> p) {
+__global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_round(const RoundParams<L> p) {
   __shared__ uint4 stage[kWarps][WarpTile<8>::kChunks];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   uint4* sw = stage[warp];
@@ -61,8 +61,8 @@ __global__ void __launch_bounds__(kThreads, (L <= 2 ? 3 : 2)) k_round(const Roun
         WarpTile<8>::transpose_in(sw, lane, raw[i], q);
         const Fr t0 = fr_from_chunks(q[0], q[1]), t1 = fr_from_chunks(q[2], q[3]);
         const Fr t2 = fr_from_chunks(q[4], q[5]), t3 = fr_from_chunks(q[6], q[7]);
-        const Fr a = add(t0, mul(p.r, sub(t1, t0)));
-        const Fr b = add(t2, mul(p.r, sub(t3, t2)));
+        const Fr a = add(t0, mul_fixed(p.r, sub(t1, t0)));
+        const Fr b = add(t2, mul_fixed(p.r, sub(t3, t2)));
         uint4 o[4];
         fr_to_chunks(a, o[0], o[1]);
         fr_to_chunks(b, o[2], o[3]);
@@ -145,7 +145,7 @@ __global__ void k_final(const FinalParams p) {
 struct FoldParams {
   const Fr* src;
   Fr* dst;
-  Fr r;
+  FixedMul<FrParams> r;
   uint64_t out_len;
 };
 
@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(kThreads) k_fold(const FoldParams p) {
     WarpTile<4>::issue(reinterpret_cast<const uint4*>(p.src) + e0 * 4, valid * 4, lane, raw);
     WarpTile<4>::transpose_in(sw, lane, raw, q);
     const Fr a = fr_from_chunks(q[0], q[1]), b = fr_from_chunks(q[2], q[3]);
-    const Fr u = add(a, mul(p.r, sub(b, a)));
+    const Fr u = add(a, mul_fixed(p.r, sub(b, a)));
     uint4 o[2];
     fr_to_chunks(u, o[0], o[1]);
     WarpTile<2>::store(reinterpret_cast<uint4*>(p.dst) + e0 * 2, valid * 2, sw, lane, o);
@@ -183,7 +183,7 @@ void launch_round_t(bool fold, const Fr* const* src, Fr* const* dst, const Fr& r
     p.src[i] = src[i];
     p.dst[i] = fold ? dst[i] : nullptr;
   }
-  p.r = r;
+  p.r = make_fixed_mul(r);
   p.pairs = pairs;
   p.partials = sc.partials;
   p.counter = sc.counter;
@@ -230,7 +230,7 @@ void launch_final(int num_poly, bool bind, const Fr* const* src, const Fr& r, Fr
 }
 
 void launch_fold(const Fr* src, Fr* dst, const Fr& r, uint64_t out_len, int max_blocks, cudaStream_t stream) {
-  FoldParams p{src, dst, r, out_len};
+  FoldParams p{src, dst, make_fixed_mul(r), out_len};
   k_fold<<<grid_for((out_len + 31) / 32, max_blocks), kThreads, 0, stream>>>(p);
 }
 
