@@ -127,6 +127,28 @@ int zk_sumcheck_sparse_dense_prove(zk_ctx* ctx, uint32_t num_var, uint64_t nnz, 
 int zk_fold_lsb(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, uint32_t k, const uint64_t* point,
                 uint64_t* out, zk_mem out_mem);
 
+/* ---- G1 multi-scalar multiplication ------------------------------------------------------ */
+/* P::G1::msm(bases, scalars) of ark-ec's VariableBaseMSM as called at
+ * src/crypto/polycommit/kzh2.rs:640 and kzh3.rs:666,772 (and the icicle-feature seam
+ * PairingG1::msm, src/crypto/polycommit/mod.rs:72-92): out = sum_i scalars[i] * bases[i].
+ * bases: n affine points (64 bytes each); scalars: n Fr elements; out_jac: one Jacobian point
+ * (12 x u64).  n = 0 gives the identity (mod.rs:127-130). */
+int zk_msm_g1(zk_ctx* ctx, const uint64_t* bases, zk_mem bases_mem, const uint64_t* scalars, zk_mem scalars_mem,
+              uint64_t n, uint64_t* out_jac, zk_mem out_mem);
+/* The d_x / d_y loops (kzh2.rs:653-660, kzh3.rs:680-687,743-750): n_rows independent MSMs over
+ * the same n_bases bases; scalars is row-major n_rows x n_bases; out_jac receives n_rows points. */
+int zk_msm_g1_batched(zk_ctx* ctx, const uint64_t* bases, zk_mem bases_mem, uint64_t n_bases, const uint64_t* scalars,
+                      zk_mem scalars_mem, uint64_t n_rows, uint64_t* out_jac, zk_mem out_mem);
+/* sparse_msm (src/crypto/polycommit/mod.rs:10-31): out = sum_i scalars[i] * all_bases[indices[i]].
+ * indices (k x u64) live where the scalars live; an index >= n_bases is ZK_ERR_ARG. */
+int zk_msm_g1_gather(zk_ctx* ctx, const uint64_t* all_bases, zk_mem bases_mem, uint64_t n_bases, const uint64_t* indices,
+                     const uint64_t* scalars, zk_mem scalars_mem, uint64_t k, uint64_t* out_jac, zk_mem out_mem);
+/* CurveGroup::into_affine / normalize_batch for n Jacobian points -> n affine points. */
+int zk_g1_normalize(zk_ctx* ctx, const uint64_t* jac, zk_mem jac_mem, uint64_t n, uint64_t* affine_out, zk_mem out_mem);
+/* Shape the last MSM on this context chose (window width, windows, largest scalar magnitude in
+ * bits, digit entries, buckets): used to report algorithmic work. */
+int zk_msm_last_stats(zk_ctx* ctx, int* window_bits, int* windows, int* max_bits, uint64_t* entries, uint64_t* buckets);
+
 /* Fold for callers that cannot allocate device memory (this entry point has no counterpart in
  * the reference).  Same result as zk_fold_lsb for tables of at most 2^ZK_FOLD_STATIC_MAX_VARS
  * elements; larger n is rejected with ZK_ERR_ARG.  evals_dev and out_dev are device buffers

@@ -38,3 +38,21 @@ DEF(fq, FqParams)
 extern "C" void zkh_mul_wide(const uint32_t* a, const uint32_t* b, uint32_t* r) {
   Wide w; mul_wide(w, a, b); memcpy(r, w.v, 64);
 }
+
+// ---- G1 group law (ec.cuh) on Montgomery-form coordinates
+#include "../../zkes_b200/csrc/ec.cuh"
+static Affine ld_aff(const uint32_t* p) { Affine a; memcpy(a.x.v, p, 32); memcpy(a.y.v, p + 8, 32); return a; }
+static void st_aff(uint32_t* p, const Affine& a) { memcpy(p, a.x.v, 32); memcpy(p + 8, a.y.v, 32); }
+// out = normalised ((((k1 * a) + b) + (k2 * c as xyzz)) doubled `dbls` times)
+extern "C" void zkh_g1_combo(const uint32_t* a, uint32_t k1, const uint32_t* b, const uint32_t* c, uint32_t k2,
+                             int dbls, uint32_t* out) {
+  Xyzz acc = mul_small(Xyzz::from_affine(ld_aff(a)), k1);
+  acc = add_mixed(acc, ld_aff(b));
+  acc = add(acc, mul_small(Xyzz::from_affine(ld_aff(c)), k2));
+  for (int i = 0; i < dbls; i++) acc = dbl(acc);
+  st_aff(out, to_affine(acc));
+}
+extern "C" void zkh_g1_jacobian(const uint32_t* a, uint32_t k, uint32_t* out) {
+  Jacobian j = to_jacobian(mul_small(Xyzz::from_affine(ld_aff(a)), k));
+  memcpy(out, j.x.v, 32); memcpy(out + 8, j.y.v, 32); memcpy(out + 16, j.z.v, 32);
+}

@@ -81,3 +81,48 @@ def test_wide_product(hm):
         b = rnd.randrange(R) if it % 7 else R - 1
         hm.zkh_mul_wide(buf(a), buf(b), w)
         assert val(w) == a * b
+
+
+def aff_buf(pt):
+    q = o.Q_MOD
+    if pt is None:
+        return (ctypes.c_uint32 * 16)()
+    x, y = pt[0] * R % q, pt[1] * R % q
+    return (ctypes.c_uint32 * 16)(*[(v >> (32 * i)) & 0xFFFFFFFF for v in (x, y) for i in range(8)])
+
+
+def aff_val(b):
+    q = o.Q_MOD
+    rinv = pow(R, -1, q)
+    x = sum(int(v) << (32 * i) for i, v in enumerate(b[:8])) * rinv % q
+    y = sum(int(v) << (32 * i) for i, v in enumerate(b[8:16])) * rinv % q
+    return None if x == 0 and y == 0 else (x, y)
+
+
+def test_g1_group_law(hm):
+    rnd = random.Random(11)
+    g = o.G1_GEN
+    out = (ctypes.c_uint32 * 16)()
+    pts = [o.g1_mul(g, rnd.randrange(1, o.R_MOD)) for _ in range(4)]
+    cases = []
+    for _ in range(30):
+        cases.append((rnd.choice(pts), rnd.randrange(0, 50), rnd.choice(pts + [None]), rnd.choice(pts + [None]),
+                      rnd.randrange(0, 50), rnd.randrange(0, 3)))
+    p = pts[0]
+    # exceptional cases: P + P, P + (-P), infinity operands, doubling of the result
+    cases += [(p, 1, p, p, 0, 0), (p, 1, o.g1_neg(p), p, 0, 1), (p, 0, None, p, 0, 0), (p, 2, o.g1_neg(p), o.g1_neg(p), 1, 0),
+              (p, 3, p, p, 4, 2), (p, 1, None, p, 1, 0), (p, 5, o.g1_neg(p), o.g1_mul(p, 4), 1, 0)]
+    for a, k1, b, c, k2, dbls in cases:
+        hm.zkh_g1_combo(aff_buf(a), k1, aff_buf(b), aff_buf(c), k2, dbls, out)
+        want = o.g1_add(o.g1_add(o.g1_mul(a, k1), b), o.g1_mul(c, k2) if c else None)
+        for _ in range(dbls):
+            want = o.g1_add(want, want)
+        assert aff_val(out) == want
+        assert o.g1_is_on_curve(aff_val(out))
+    jac = (ctypes.c_uint32 * 24)()
+    hm.zkh_g1_jacobian(aff_buf(p), 7, jac)
+    q = o.Q_MOD
+    rinv = pow(R, -1, q)
+    X, Y, Z = [sum(int(v) << (32 * i) for i, v in enumerate(jac[8 * k:8 * k + 8])) * rinv % q for k in range(3)]
+    zi = pow(Z, -1, q)
+    assert (X * zi * zi % q, Y * zi * zi * zi % q) == o.g1_mul(p, 7)

@@ -26,12 +26,37 @@ void zk_ctx::teardown() {
   cudaFree(rs.msg);
   cudaFree(final_out);
   cudaFree(work);
+  cudaFree(aux);
   if (host_small) cudaFreeHost(host_small);
   for (auto& sp : prof_spans) {
     cudaEventDestroy(sp.e0);
     cudaEventDestroy(sp.e1);
   }
   if (stream) cudaStreamDestroy(stream);
+}
+
+static int grow(cudaStream_t stream, void** buf, size_t* have, size_t bytes) {
+  if (bytes > *have) {
+    ZK_CUDA(cudaStreamSynchronize(stream));
+    if (*buf) cudaFree(*buf);
+    *buf = nullptr;
+    *have = 0;
+    const size_t want = (bytes + (1u << 20) - 1) & ~((size_t)(1u << 20) - 1);
+    cudaError_t e = cudaMalloc(buf, want);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(-2 /*ZK_ERR_OOM*/, "device scratch of %zu bytes: %s", want, cudaGetErrorString(e));
+    }
+    *have = want;
+  }
+  return 0;
+}
+
+int zk_ctx::reserve_aux(size_t bytes, void** out) {
+  int rc = grow(stream, &aux, &aux_bytes, bytes);
+  if (rc) return rc;
+  *out = aux;
+  return 0;
 }
 
 int zk_ctx::reserve_work(size_t bytes, void** out) {

@@ -45,6 +45,11 @@ inline Fr transcript_challenge_scalar(MerlinTranscript& t, const uint8_t* label,
 
 }  // namespace zk
 
+struct MsmStatsPod {
+  int window_bits = 0, windows = 0, max_bits = 0;
+  uint32_t entries = 0, buckets = 0;
+};
+
 struct zk_ctx {
   int device = 0;
   int sm_count = 0;
@@ -52,8 +57,11 @@ struct zk_ctx {
   zk::RoundScratch rs{};
   zk::Fr* final_out = nullptr;   // kMaxPolys + 1 elements
   void* host_small = nullptr;    // pinned, 4 KiB: round messages and other tiny read-backs
-  void* work = nullptr;          // grow-only device scratch
+  void* work = nullptr;          // grow-only device scratch (copies of caller data, round buffers)
   size_t work_bytes = 0;
+  void* aux = nullptr;           // second grow-only scratch (MSM sort and bucket storage)
+  size_t aux_bytes = 0;
+  MsmStatsPod last_msm;          // shape of the most recent MSM (window width, windows, entries)
   std::mutex mu;
   std::atomic<uint64_t> launches{0};
 
@@ -74,6 +82,7 @@ struct zk_ctx {
   void teardown();
   // Make the scratch at least `bytes` large and return it (contents undefined).
   int reserve_work(size_t bytes, void** out);
+  int reserve_aux(size_t bytes, void** out);
 };
 
 struct zk_transcript {

@@ -32,6 +32,7 @@ int launch_sparse_fold(const uint32_t* idx, const Fr* val, const uint32_t* count
 void launch_scatter(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, Fr* dense,
                     int sm_count, cudaStream_t s);
 void launch_check_sorted(const uint32_t* idx, uint32_t n, uint64_t limit, uint32_t* bad, int sm_count, cudaStream_t s);
+void launch_check_bound(const uint32_t* idx, uint32_t n, uint64_t limit, uint32_t* bad, int sm_count, cudaStream_t s);
 void launch_narrow_idx(const uint64_t* in, uint32_t n, uint32_t* out, uint32_t* bad, int sm_count, cudaStream_t s);
 void launch_sd_final(const uint32_t* idx, const Fr* val, const uint32_t* count, const Fr* dense, Fr* out,
                      cudaStream_t s);

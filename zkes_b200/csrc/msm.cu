@@ -1,0 +1,377 @@
+// Pippenger multi-scalar multiplication over BN254 G1, for one row or for many rows that share
+// the bases (the d_x / d_y loops of kzh2.rs:653-660, kzh3.rs:680-687,743-750).
+//
+//   1. k_msm_bits     largest magnitude of the sign-folded scalars -> window width W, windows K
+//   2. k_msm_digits   signed W-bit digits; MODE 0 counts (row, window, bucket) keys, MODE 1
+//                     scatters point indices (sign in bit 31) to their bucket's slots
+//   3. k_msm_accumulate  equal chunks of the sorted entry list are summed by one thread each with
+//                     mixed additions; a bucket inside one chunk is written directly, pieces of
+//                     buckets that cross chunk borders go to per-chunk head / tail slots
+//   4. k_msm_fixup    buckets that span chunks: tail of the first chunk + heads of the others
+//   5. k_msm_bucket_reduce  sum_j (j+1) B_j per (row, window) by running sums per thread,
+//                     a small scalar multiple for the thread's offset, then a block tree
+//   6. k_msm_combine  Horner over the windows (W doublings each), Jacobian out
+// Small scalars (quantised int8 / int16 weights and activations, negatives stored as r - |v|)
+// fold to a few bits, so they use one narrow window: no doublings, few buckets.
+#include "msm.hpp"
+#include "reduce.cuh"
+
+namespace zk {
+namespace {
+
+__device__ __forceinline__ Fr ld_scalar(const Fr* p) {
+  const uint4 lo = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint4 hi = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+  return fr_from_chunks(lo, hi);
+}
+
+// Canonical value of a Montgomery-form scalar, folded to min(s, r - s); returns the sign.
+__device__ __forceinline__ bool fold_scalar(const Fr& mont, uint32_t (&mag)[8]) {
+  const Fr c = from_mont(mont);
+  uint32_t m[8], d[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) m[i] = FrParams::mod(i);
+  (void)sub8(d, m, c.v);  // r - s
+  // s > r - s  <=>  borrow when computing (r - s) - s
+  uint32_t t[8];
+  const bool negv = sub8(t, d, c.v) != 0 && !c.is_zero();
+#pragma unroll
+  for (int i = 0; i < 8; i++) mag[i] = negv ? d[i] : c.v[i];
+  return negv;
+}
+
+__device__ __forceinline__ int bit_length(const uint32_t (&mag)[8]) {
+  int bits = 0;
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+    if (mag[i]) bits = 32 * i + (32 - __clz(mag[i]));
+  return bits;
+}
+
+__global__ void k_msm_bits(const Fr* __restrict__ scalars, uint64_t total, unsigned int* max_bits) {
+  int best = 0;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+    uint32_t mag[8];
+    (void)fold_scalar(ld_scalar(scalars + i), mag);
+    const int b = bit_length(mag);
+    best = b > best ? b : best;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const int o = __shfl_down_sync(0xffffffffu, best, off);
+    best = o > best ? o : best;
+  }
+  if ((threadIdx.x & 31) == 0 && best) atomicMax(max_bits, (unsigned int)best);
+}
+
+// W-bit field of mag starting at bit `pos` (pos + W may run past 256: zeros).
+__device__ __forceinline__ uint32_t bit_field(const uint32_t (&mag)[8], int pos, int w) {
+  const int limb = pos >> 5, sh = pos & 31;
+  uint64_t v = 0;
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    if (i == limb) v |= (uint64_t)mag[i];
+    if (i == limb + 1) v |= (uint64_t)mag[i] << 32;
+  }
+  return (uint32_t)(v >> sh) & ((1u << w) - 1u);
+}
+
+template <int MODE>  // 0: count keys, 1: scatter entries
+__global__ void k_msm_digits(const Fr* __restrict__ scalars, uint64_t n, uint32_t rows, int w, int k_windows,
+                             uint32_t* counts_or_cursor, uint32_t* entries) {
+  const uint64_t total = n * rows;
+  const uint32_t half = 1u << (w - 1);
+  for (uint64_t g = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (uint64_t)gridDim.x * blockDim.x) {
+    uint32_t mag[8];
+    const bool negv = fold_scalar(ld_scalar(scalars + g), mag);
+    const uint32_t row = (uint32_t)(g / n);
+    const uint32_t col = (uint32_t)(g - (uint64_t)row * n);
+    uint32_t carry = 0;
+    for (int k = 0; k < k_windows; k++) {
+      uint32_t raw = bit_field(mag, k * w, w) + carry;
+      bool dneg = false;
+      if (raw > half) {
+        raw = (1u << w) - raw;
+        dneg = true;
+        carry = 1;
+      } else {
+        carry = 0;
+      }
+      if (raw == 0) continue;
+      const uint32_t key = (row * (uint32_t)k_windows + (uint32_t)k) * half + (raw - 1);
+      if (MODE == 0) {
+        atomicAdd(counts_or_cursor + key, 1u);
+      } else {
+        const uint32_t slot = atomicAdd(counts_or_cursor + key, 1u);
+        entries[slot] = col | ((negv != dneg) ? 0x80000000u : 0u);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ Affine ld_affine(const Affine* p) {
+  const uint4* q = reinterpret_cast<const uint4*>(p);
+  const uint4 a = __ldg(q), b = __ldg(q + 1), c = __ldg(q + 2), d = __ldg(q + 3);
+  Affine r;
+  r.x.v[0] = a.x; r.x.v[1] = a.y; r.x.v[2] = a.z; r.x.v[3] = a.w;
+  r.x.v[4] = b.x; r.x.v[5] = b.y; r.x.v[6] = b.z; r.x.v[7] = b.w;
+  r.y.v[0] = c.x; r.y.v[1] = c.y; r.y.v[2] = c.z; r.y.v[3] = c.w;
+  r.y.v[4] = d.x; r.y.v[5] = d.y; r.y.v[6] = d.z; r.y.v[7] = d.w;
+  return r;
+}
+
+__device__ __forceinline__ void st_xyzz(Xyzz* p, const Xyzz& v) {
+  uint4* q = reinterpret_cast<uint4*>(p);
+  const Fq* f[4] = {&v.x, &v.y, &v.zz, &v.zzz};
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    q[2 * i] = make_uint4(f[i]->v[0], f[i]->v[1], f[i]->v[2], f[i]->v[3]);
+    q[2 * i + 1] = make_uint4(f[i]->v[4], f[i]->v[5], f[i]->v[6], f[i]->v[7]);
+  }
+}
+__device__ __forceinline__ Xyzz ld_xyzz(const Xyzz* p) {
+  const uint4* q = reinterpret_cast<const uint4*>(p);
+  Xyzz v;
+  Fq* f[4] = {&v.x, &v.y, &v.zz, &v.zzz};
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const uint4 a = q[2 * i], b = q[2 * i + 1];
+    f[i]->v[0] = a.x; f[i]->v[1] = a.y; f[i]->v[2] = a.z; f[i]->v[3] = a.w;
+    f[i]->v[4] = b.x; f[i]->v[5] = b.y; f[i]->v[6] = b.z; f[i]->v[7] = b.w;
+  }
+  return v;
+}
+
+// First bucket whose range ends after entry e: smallest b with offsets[b + 1] > e.
+__device__ __forceinline__ uint32_t bucket_of(const uint32_t* __restrict__ offsets, uint32_t n_buckets, uint32_t e) {
+  uint32_t lo = 0, hi = n_buckets - 1;
+  while (lo < hi) {
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    if (offsets[mid + 1] > e) hi = mid; else lo = mid + 1;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(128) k_msm_accumulate(const Affine* __restrict__ bases, const uint32_t* __restrict__ gather,
+                                                        const uint32_t* __restrict__ entries,
+                                                        const uint32_t* __restrict__ offsets, uint32_t n_buckets,
+                                                        uint32_t n_entries, uint32_t seg, uint32_t n_chunks,
+                                                        Xyzz* bucket_sums, Xyzz* heads, Xyzz* tails) {
+  const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= n_chunks) return;
+  const uint32_t begin = c * seg;
+  const uint32_t end = (begin + seg < n_entries) ? begin + seg : n_entries;
+  uint32_t b = bucket_of(offsets, n_buckets, begin);
+  uint32_t b_end = offsets[b + 1];
+  bool began_before = offsets[b] < begin;  // the current bucket started in an earlier chunk
+  Xyzz acc = Xyzz::inf();
+  for (uint32_t e = begin; e < end; e++) {
+    if (e == b_end) {  // bucket b is complete
+      if (began_before) st_xyzz(heads + c, acc); else st_xyzz(bucket_sums + b, acc);
+      acc = Xyzz::inf();
+      began_before = false;
+      do { b++; b_end = offsets[b + 1]; } while (b_end <= e);
+    }
+    const uint32_t ent = entries[e];
+    const uint32_t col = ent & 0x7fffffffu;
+    Affine pt = ld_affine(bases + (gather ? gather[col] : col));
+    if (ent & 0x80000000u) pt = neg(pt);
+    acc = add_mixed(acc, pt);
+  }
+  // the bucket in progress at the end of the chunk
+  const bool continues = b_end > end;
+  if (began_before)
+    st_xyzz(heads + c, acc);            // spans the whole chunk, or ends exactly at its end
+  else if (continues)
+    st_xyzz(tails + c, acc);
+  else
+    st_xyzz(bucket_sums + b, acc);
+}
+
+// One warp per bucket that crosses chunk borders.
+__global__ void __launch_bounds__(128) k_msm_fixup(const uint32_t* __restrict__ offsets, uint32_t n_buckets, uint32_t seg,
+                                                   Xyzz* bucket_sums, const Xyzz* heads, const Xyzz* tails) {
+  __shared__ Xyzz sh[4][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t b = blockIdx.x * 4 + warp;
+  if (b >= n_buckets) return;
+  const uint32_t s = offsets[b], e = offsets[b + 1];
+  if (e <= s) return;
+  const uint32_t c0 = s / seg, c1 = (e - 1) / seg;
+  if (c0 == c1) return;
+  // pieces: tail of chunk c0, heads of chunks c0+1 .. c1
+  Xyzz acc = Xyzz::inf();
+  for (uint32_t c = c0 + lane; c <= c1; c += 32) acc = add(acc, ld_xyzz(c == c0 ? tails + c : heads + c));
+  sh[warp][lane] = acc;
+  __syncwarp();
+  for (int off = 16; off > 0; off >>= 1) {
+    if (lane < off) {
+      acc = add(acc, sh[warp][lane + off]);
+      sh[warp][lane] = acc;
+    }
+    __syncwarp();
+  }
+  if (lane == 0) st_xyzz(bucket_sums + b, acc);
+}
+
+// One block per (row, window): sum_j (j + 1) * B_j over `half` buckets.
+__global__ void __launch_bounds__(256) k_msm_bucket_reduce(const Xyzz* __restrict__ bucket_sums, uint32_t half,
+                                                           Xyzz* window_sums) {
+  extern __shared__ unsigned char sh_raw[];
+  Xyzz* sh = reinterpret_cast<Xyzz*>(sh_raw);
+  const Xyzz* B = bucket_sums + (size_t)blockIdx.x * half;
+  const uint32_t per = (half + blockDim.x - 1) / blockDim.x;
+  const uint32_t lo = threadIdx.x * per;
+  const uint32_t hi = (lo + per < half) ? lo + per : half;
+  Xyzz running = Xyzz::inf(), acc = Xyzz::inf();
+  if (lo < half) {
+    for (uint32_t j = hi; j-- > lo;) {
+      running = add(running, ld_xyzz(B + j));
+      acc = add(acc, running);
+    }
+    if (lo) acc = add(acc, mul_small(running, lo));
+  }
+  sh[threadIdx.x] = acc;
+  __syncthreads();
+  for (uint32_t off = blockDim.x >> 1; off > 0; off >>= 1) {
+    if (threadIdx.x < off) {
+      acc = add(acc, sh[threadIdx.x + off]);
+      sh[threadIdx.x] = acc;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) st_xyzz(window_sums + blockIdx.x, acc);
+}
+
+__global__ void k_msm_combine(const Xyzz* __restrict__ window_sums, uint32_t rows, int w, int k_windows, Jacobian* out) {
+  const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  Xyzz acc = Xyzz::inf();
+  for (int k = k_windows - 1; k >= 0; k--) {
+    for (int i = 0; i < w; i++) acc = dbl(acc);
+    acc = add(acc, ld_xyzz(window_sums + (size_t)row * k_windows + k));
+  }
+  out[row] = to_jacobian(acc);
+}
+
+__global__ void k_set_infinity(Jacobian* out, uint32_t rows) {
+  const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row < rows) out[row] = to_jacobian(Xyzz::inf());
+}
+
+}  // namespace
+
+// Window width for n points per row whose scalars have at most max_bits magnitude bits.
+static int pick_window(uint64_t n, int max_bits) {
+  int lg = 0;
+  while ((1ull << (lg + 1)) <= n) lg++;
+  int w = lg - 2;
+  if (w > 16) w = 16;
+  if (w < 3) w = 3;
+  if (w > max_bits + 1) w = max_bits + 1;
+  if (w < 2) w = 2;
+  return w;
+}
+
+size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+int msm_run(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const Fr* scalars, uint64_t n, uint32_t rows,
+            Jacobian* out_dev, MsmStats* stats) {
+  cudaStream_t s = ctx->stream;
+  const uint64_t total = n * rows;
+  const int sm = ctx->sm_count;
+  if (rows == 0) return 0;
+  if (n == 0) {
+    k_set_infinity<<<(rows + 127) / 128, 128, 0, s>>>(out_dev, rows);
+    ctx->launches++;
+    return 0;
+  }
+  if (n >= (1ull << 31)) return fail(-1, "msm: at most 2^31 - 1 points per row");
+  // ---- pass 1: scalar magnitude
+  unsigned int* d_bits = ctx->rs.counter + 8;  // spare words of the context's counter block
+  ZK_CUDA(cudaMemsetAsync(d_bits, 0, 4, s));
+  k_msm_bits<<<sm * 8, 256, 0, s>>>(scalars, total, d_bits);
+  ctx->launches++;
+  ZK_CUDA(cudaMemcpyAsync(ctx->host_small, d_bits, 4, cudaMemcpyDeviceToHost, s));
+  ZK_CUDA(cudaStreamSynchronize(s));
+  unsigned int max_bits = 0;
+  memcpy(&max_bits, ctx->host_small, 4);
+  if (max_bits == 0) {
+    k_set_infinity<<<(rows + 127) / 128, 128, 0, s>>>(out_dev, rows);
+    ctx->launches++;
+    return 0;
+  }
+  const int w = pick_window(n, (int)max_bits);
+  const int k_windows = ((int)max_bits + 1 + w - 1) / w;
+  const uint32_t half = 1u << (w - 1);
+  const uint64_t n_buckets64 = (uint64_t)rows * k_windows * half;
+  if (n_buckets64 >= (1ull << 31)) return fail(-1, "msm: %llu buckets exceed the 32-bit key space; split the rows", (unsigned long long)n_buckets64);
+  const uint32_t n_buckets = (uint32_t)n_buckets64;
+
+  // ---- scratch layout (second scratch region of the context; the first holds caller data)
+  const uint64_t max_entries = total * (uint64_t)k_windows;
+  if (max_entries >= (1ull << 32)) return fail(-1, "msm: %llu digit entries exceed 2^32; split the call", (unsigned long long)max_entries);
+  size_t need = align256((n_buckets + 2) * 4ull) * 2 + align256(scan_scratch_elems(n_buckets + 1) * 4) +
+                align256((size_t)n_buckets * sizeof(Xyzz)) + align256((size_t)rows * k_windows * sizeof(Xyzz)) + 4096;
+  char* base = nullptr;
+  // entries and chunk slots are sized after the count pass; reserve the worst case now
+  uint64_t chunk_guess = max_entries / 32 + 1;
+  if (chunk_guess > (1u << 20)) chunk_guess = 1u << 20;
+  need += align256(max_entries * 4) + 2 * align256((chunk_guess + 1) * sizeof(Xyzz));
+  int rc = ctx->reserve_aux(need, (void**)&base);
+  if (rc) return rc;
+  size_t off = 0;
+  auto take = [&](size_t bytes) { char* p = base + off; off += align256(bytes); return p; };
+  uint32_t* offsets = (uint32_t*)take((n_buckets + 2) * 4ull);
+  uint32_t* cursor = (uint32_t*)take((n_buckets + 2) * 4ull);
+  uint32_t* scan_tmp = (uint32_t*)take(scan_scratch_elems(n_buckets + 1) * 4);
+  Xyzz* bucket_sums = (Xyzz*)take((size_t)n_buckets * sizeof(Xyzz));
+  Xyzz* window_sums = (Xyzz*)take((size_t)rows * k_windows * sizeof(Xyzz));
+  uint32_t* entries = (uint32_t*)take(max_entries * 4);
+  Xyzz* heads = (Xyzz*)take((chunk_guess + 1) * sizeof(Xyzz));
+  Xyzz* tails = (Xyzz*)take((chunk_guess + 1) * sizeof(Xyzz));
+
+  // ---- pass 2: count, scan, scatter
+  ZK_CUDA(cudaMemsetAsync(offsets, 0, (n_buckets + 2) * 4ull, s));
+  k_msm_digits<0><<<sm * 8, 256, 0, s>>>(scalars, n, rows, w, k_windows, offsets, nullptr);
+  ctx->launches++;
+  ctx->launches += exclusive_scan_u32(offsets, n_buckets, scan_tmp, true, s);
+  ZK_CUDA(cudaMemcpyAsync(cursor, offsets, (n_buckets + 1) * 4ull, cudaMemcpyDeviceToDevice, s));
+  k_msm_digits<1><<<sm * 8, 256, 0, s>>>(scalars, n, rows, w, k_windows, cursor, entries);
+  ctx->launches++;
+  ZK_CUDA(cudaMemcpyAsync(ctx->host_small, offsets + n_buckets, 4, cudaMemcpyDeviceToHost, s));
+  ZK_CUDA(cudaStreamSynchronize(s));
+  uint32_t n_entries = 0;
+  memcpy(&n_entries, ctx->host_small, 4);
+
+  // ---- accumulate
+  ZK_CUDA(cudaMemsetAsync(bucket_sums, 0, (size_t)n_buckets * sizeof(Xyzz), s));
+  if (n_entries) {
+    uint32_t n_chunks = n_entries / 32 + 1;
+    if (n_chunks > chunk_guess) n_chunks = (uint32_t)chunk_guess;
+    const uint32_t seg = (n_entries + n_chunks - 1) / n_chunks;
+    n_chunks = (n_entries + seg - 1) / seg;
+    k_msm_accumulate<<<(n_chunks + 127) / 128, 128, 0, s>>>(bases, gather, entries, offsets, n_buckets, n_entries, seg,
+                                                           n_chunks, bucket_sums, heads, tails);
+    k_msm_fixup<<<(n_buckets + 3) / 4, 128, 0, s>>>(offsets, n_buckets, seg, bucket_sums, heads, tails);
+    ctx->launches += 2;
+  }
+  // ---- reduce buckets, combine windows
+  uint32_t threads = half / 8;
+  if (threads < 32) threads = 32;
+  if (threads > 256) threads = 256;
+  k_msm_bucket_reduce<<<rows * k_windows, threads, threads * sizeof(Xyzz), s>>>(bucket_sums, half, window_sums);
+  k_msm_combine<<<(rows + 63) / 64, 64, 0, s>>>(window_sums, rows, w, k_windows, out_dev);
+  ctx->launches += 2;
+  ZK_CUDA(cudaGetLastError());
+  if (stats) {
+    stats->window_bits = w;
+    stats->windows = k_windows;
+    stats->entries = n_entries;
+    stats->buckets = n_buckets;
+    stats->max_bits = (int)max_bits;
+  }
+  return 0;
+}
+
+}  // namespace zk

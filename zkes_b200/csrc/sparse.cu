@@ -172,6 +172,12 @@ __global__ void k_check_sorted(const uint32_t* __restrict__ idx, uint32_t n, uin
   }
 }
 
+// Flags any idx[i] >= limit.
+__global__ void k_check_bound(const uint32_t* __restrict__ idx, uint32_t n, uint64_t limit, uint32_t* bad) {
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    if ((uint64_t)idx[i] >= limit) *bad = 1;
+}
+
 // Narrow caller indices (u64) to the 32-bit form the kernels use; flags values >= 2^32.
 __global__ void k_narrow_idx(const uint64_t* __restrict__ in, uint32_t n, uint32_t* out, uint32_t* bad) {
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
@@ -224,6 +230,10 @@ void launch_scatter(const uint32_t* idx, const Fr* val, const uint32_t* count, u
 
 void launch_check_sorted(const uint32_t* idx, uint32_t n, uint64_t limit, uint32_t* bad, int sm_count, cudaStream_t s) {
   k_check_sorted<<<blocks_for(n, 256, sm_count * 8), 256, 0, s>>>(idx, n, limit, bad);
+}
+
+void launch_check_bound(const uint32_t* idx, uint32_t n, uint64_t limit, uint32_t* bad, int sm_count, cudaStream_t s) {
+  k_check_bound<<<blocks_for(n, 256, sm_count * 8), 256, 0, s>>>(idx, n, limit, bad);
 }
 
 void launch_narrow_idx(const uint64_t* in, uint32_t n, uint32_t* out, uint32_t* bad, int sm_count, cudaStream_t s) {
