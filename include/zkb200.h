@@ -127,6 +127,15 @@ int zk_sumcheck_sparse_dense_prove(zk_ctx* ctx, uint32_t num_var, uint64_t nnz, 
 int zk_fold_lsb(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, uint32_t k, const uint64_t* point,
                 uint64_t* out, zk_mem out_mem);
 
+/* fix_variables_from_right, src/util/poly.rs:705-758: binds the k highest variables of a 2^n
+ * table to point[0..k) (point[0] is variable n-k); out receives 2^(n-k) elements:
+ * out[lo] = sum_hi eq(point)[hi] * evals[hi * 2^(n-k) + lo]. */
+int zk_fix_from_right(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, uint32_t k, const uint64_t* point,
+                      uint64_t* out, zk_mem out_mem);
+/* evaluate_lagrange_basis / precompute_eq, src/util/poly.rs:573-618, 657-699: out[x] = eq(x, point)
+ * for x < 2^k, variable 0 in index bit 0; k = 0 gives {1}.  point is a host array. */
+int zk_eq_table(zk_ctx* ctx, uint32_t k, const uint64_t* point, uint64_t* out, zk_mem out_mem);
+
 /* ---- G1 multi-scalar multiplication ------------------------------------------------------ */
 /* P::G1::msm(bases, scalars) of ark-ec's VariableBaseMSM as called at
  * src/crypto/polycommit/kzh2.rs:640 and kzh3.rs:666,772 (and the icicle-feature seam
@@ -148,6 +157,38 @@ int zk_g1_normalize(zk_ctx* ctx, const uint64_t* jac, zk_mem jac_mem, uint64_t n
 /* Shape the last MSM on this context chose (window width, windows, largest scalar magnitude in
  * bits, digit entries, buckets): used to report algorithmic work. */
 int zk_msm_last_stats(zk_ctx* ctx, int* window_bits, int* windows, int* max_bits, uint64_t* entries, uint64_t* buckets);
+
+/* ---- KZH2 / KZH3 polynomial commitments, G1 side ------------------------------------------ */
+/* Device-resident structured reference string.  dims = 2: KZH2SRS {h_xy, h_y} (kzh2.rs:27-35),
+ * split (x_log, y_log) = (n/2, n - n/2) (kzh2.rs:423-429); dims = 3: KZH3SRS {h_xyz, h_yz, h_z}
+ * (kzh3.rs:33-45), split as kzh3.rs:429-437.  G2 vectors and pairings stay with the caller. */
+typedef struct zk_kzh_srs zk_kzh_srs;
+/* setup_kzh2_srs (kzh2.rs:502-555) / setup_kzh3_srs (kzh3.rs:463-563), G1 half, from trapdoors
+ * the caller sampled in the reference's order: g (affine), tau_x[2^x_log], tau_y[2^y_log], then
+ * alpha (KZH2; tau_z NULL) or tau_z[2^z_log] (KZH3; alpha NULL).  All host arrays. */
+int zk_kzh_srs_setup(zk_ctx* ctx, int dims, uint32_t n, const uint64_t* g_affine, const uint64_t* tau_x,
+                     const uint64_t* tau_y, const uint64_t* tau_z, const uint64_t* alpha, zk_kzh_srs** out);
+/* An SRS the caller already holds (load_kzh3_srs, src/crypto/srs_storage.rs): h_full 2^n points,
+ * h_mid 2^(n - x_log), h_low 2^z_log (KZH3 only). */
+int zk_kzh_srs_upload(zk_ctx* ctx, int dims, uint32_t n, const uint64_t* h_full, const uint64_t* h_mid,
+                      const uint64_t* h_low, zk_mem mem, zk_kzh_srs** out);
+void zk_kzh_srs_free(zk_ctx* ctx, zk_kzh_srs* srs);
+int zk_kzh_srs_shape(const zk_kzh_srs* srs, uint32_t* x_log, uint32_t* y_log, uint32_t* z_log);
+/* Copy `count` points of vector `which` (0 full, 1 mid, 2 low) from `offset` to a host array. */
+int zk_kzh_srs_read(zk_ctx* ctx, const zk_kzh_srs* srs, int which, uint64_t offset, uint64_t count, uint64_t* out);
+/* kzh2_commit (kzh2.rs:619-673) / kzh3_commit (kzh3.rs:645-700): evals has 2^poly_n elements,
+ * zero-extended to the SRS size.  c_affine_out: 8 x u64; d_x_jac_out: 2^x_log Jacobian points (host). */
+int zk_kzh_commit(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uint64_t* evals, zk_mem evals_mem,
+                  uint64_t* c_affine_out, uint64_t* d_x_jac_out);
+/* kzh2_open (kzh2.rs:676-710): f_star_out receives 2^y_log elements (host); the opening's d_x is
+ * the commitment's own.  point is padded with leading zeros as split_input does (:479-498). */
+int zk_kzh2_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uint64_t* evals, zk_mem evals_mem,
+                 const uint64_t* point, uint32_t point_len, uint64_t* f_star_out);
+/* kzh3_open (kzh3.rs:702-787): d_x_jac is the commitment's aux (host, 2^x_log points); outputs
+ * (host) d_y_jac_out 2^y_log points, c_y_affine_out 8 x u64, f_star_out 2^z_log elements. */
+int zk_kzh3_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uint64_t* evals, zk_mem evals_mem,
+                 const uint64_t* point, uint32_t point_len, const uint64_t* d_x_jac, uint64_t* d_y_jac_out,
+                 uint64_t* c_y_affine_out, uint64_t* f_star_out);
 
 /* Fold for callers that cannot allocate device memory (this entry point has no counterpart in
  * the reference).  Same result as zk_fold_lsb for tables of at most 2^ZK_FOLD_STATIC_MAX_VARS

@@ -1,0 +1,104 @@
+"""KZH2 / KZH3 setup, commit and open on the GPU against the oracle (which restates kzh2.rs and
+kzh3.rs), plus the identities the reference's verifiers check (kzh2.rs:763-789, kzh3.rs:836-886)
+and the trapdoor identity C = (sum_i f_i t_i) g.  Mirrors tests/test_kzh2.rs:42-175 (n in 2, 4, 6)
+and tests/test_kzh3.rs:31-85 (n in 3, 4)."""
+import random
+
+import pytest
+
+import pyoracle as o
+from zkes_b200 import DenseMLPoly, kzh
+
+pytestmark = pytest.mark.gpu
+M = o.R_MOD
+
+
+def trapdoors(seed, n_x, n_y, n_z=0):
+    d = o.gen_uniform_fr(seed, 0, 0, 1 + n_x + n_y + max(n_z, 1))
+    return d[0], d[1:1 + n_x], d[1 + n_x:1 + n_x + n_y], d[1 + n_x + n_y:]
+
+
+@pytest.mark.parametrize("n,kind", [(2, "full"), (3, "int8"), (4, "full"), (5, "mixed"), (6, "int8")])
+def test_kzh2_commit_open(ctx, n, kind):
+    rnd = random.Random(n)
+    xl, yl = o.kzh2_degrees(n)
+    gk, tx, ty, rest = trapdoors(2, 1 << xl, 1 << yl)
+    alpha = rest[0]
+    osrs = o.KZH2SRS(n, gk, tx, ty, alpha)
+    srs = kzh.KZHSRS.setup(ctx, 2, n, osrs.g, tx, ty, alpha=alpha)
+    assert (srs.x_log, srs.y_log) == (xl, yl)
+    assert srs.read(0, 0, 1 << n) == osrs.h_xy and srs.read(1, 0, 1 << yl) == osrs.h_y
+    mk = {"full": lambda i: rnd.randrange(M), "int8": lambda i: o.fr_from_int(rnd.randrange(-128, 128)),
+          "mixed": lambda i: o.fr_from_int(rnd.randrange(-2 ** 15, 2 ** 15)) if i % 2 else rnd.randrange(M)}[kind]
+    f = [mk(i) for i in range(1 << n)]
+    poly = DenseMLPoly.from_evaluations(f)
+    com = kzh.commit(ctx, srs, poly)
+    oc, odx = o.kzh2_commit(osrs, f)
+    assert com.c == oc and com.d_x == odx
+    assert com.c == o.g1_mul(osrs.g, sum(a * b for a, b in zip(f, osrs.t_xy)) % M)  # trapdoor identity
+    pt = [rnd.randrange(M) for _ in range(n)]
+    d_x, f_star = kzh.kzh2_open(ctx, srs, pt, com, poly)
+    _, ofs = o.kzh2_open(osrs, pt, odx, f)
+    assert f_star == ofs and d_x == odx
+    r_y, r_x = o.split_input([yl, xl], pt)
+    assert o.g1_msm(d_x, o.evaluate_lagrange_basis(r_x)) == o.g1_msm(osrs.h_y, f_star)  # kzh2.rs:763-789
+    assert o.evaluate_multilinear_extension(f_star, r_y) == o.evaluate_multilinear_extension(f, pt)  # test_kzh2.rs:149-175
+
+
+def test_kzh2_small_poly_and_short_point(ctx):
+    """A polynomial with fewer variables than the SRS is zero-extended; a short point is left-padded."""
+    rnd = random.Random(9)
+    n = 6
+    gk, tx, ty, rest = trapdoors(3, 8, 8)
+    osrs = o.KZH2SRS(n, gk, tx, ty, rest[0])
+    srs = kzh.KZHSRS.upload(ctx, 2, n, osrs.h_xy, osrs.h_y)
+    f = [rnd.randrange(M) for _ in range(16)]
+    poly = DenseMLPoly.from_evaluations(f)
+    com = kzh.commit(ctx, srs, poly)
+    oc, odx = o.kzh2_commit(osrs, f)
+    assert com.c == oc and com.d_x == odx
+    pt = [rnd.randrange(M) for _ in range(4)]
+    _, f_star = kzh.kzh2_open(ctx, srs, pt, com, poly)
+    assert f_star == o.kzh2_open(osrs, pt, odx, f)[1]
+
+
+@pytest.mark.parametrize("n,kind", [(3, "full"), (4, "int8"), (5, "full"), (7, "mixed")])
+def test_kzh3_commit_open(ctx, n, kind):
+    rnd = random.Random(30 + n)
+    xl, yl, zl = o.kzh3_degrees(n)
+    gk, tx, ty, tz = trapdoors(3, 1 << xl, 1 << yl, 1 << zl)
+    tz = tz[:1 << zl]
+    osrs = o.KZH3SRS(n, gk, tx, ty, tz)
+    srs = kzh.KZHSRS.setup(ctx, 3, n, osrs.g, tx, ty, tau_z=tz)
+    assert (srs.x_log, srs.y_log, srs.z_log) == (xl, yl, zl)
+    assert srs.read(0, 0, 1 << n) == osrs.h_xyz and srs.read(1, 0, 1 << (yl + zl)) == osrs.h_yz
+    assert srs.read(2, 0, 1 << zl) == osrs.h_z
+    mk = {"full": lambda i: rnd.randrange(M), "int8": lambda i: o.fr_from_int(rnd.randrange(-128, 128)),
+          "mixed": lambda i: o.fr_from_int(rnd.randrange(-2 ** 15, 2 ** 15)) if (i >> 2) % 2 else rnd.randrange(M)}[kind]
+    f = [mk(i) for i in range(1 << n)]
+    poly = DenseMLPoly.from_evaluations(f)
+    com = kzh.commit(ctx, srs, poly)
+    oc, odx = o.kzh3_commit(osrs, f)
+    assert com.c == oc and com.d_x == odx
+    assert com.c == o.g1_mul(osrs.g, sum(a * b for a, b in zip(f, osrs.t_xyz)) % M)
+    pt = [rnd.randrange(M) for _ in range(n)]
+    d_x, d_y, c_y, f_star = kzh.kzh3_open(ctx, srs, pt, com, poly)
+    _, ody, ocy, ofs = o.kzh3_open(osrs, pt, odx, f)
+    assert d_y == ody and c_y == ocy and f_star == ofs
+    r_z, r_y, r_x = o.split_input([zl, yl, xl], pt)
+    assert c_y == o.g1_msm(d_x, o.evaluate_lagrange_basis(r_x))  # kzh3.rs:836-852
+    assert o.g1_msm(osrs.h_z, f_star) == o.g1_msm(d_y, o.evaluate_lagrange_basis(r_y))
+    assert o.evaluate_multilinear_extension(f_star, r_z) == o.evaluate_multilinear_extension(f, pt)
+
+
+def test_kzh_argument_errors(ctx):
+    from zkes_b200._lib import ZkError
+    gk, tx, ty, rest = trapdoors(2, 2, 2)
+    osrs = o.KZH2SRS(2, gk, tx, ty, rest[0])
+    srs = kzh.KZHSRS.upload(ctx, 2, 2, osrs.h_xy, osrs.h_y)
+    big = DenseMLPoly.from_evaluations([1] * 8)
+    with pytest.raises(ZkError):
+        kzh.commit(ctx, srs, big)  # more variables than the SRS supports
+    with pytest.raises(ZkError):
+        kzh.kzh3_open(ctx, srs, [1, 2], kzh.commit(ctx, srs, DenseMLPoly.from_evaluations([1, 2, 3, 4])),
+                      DenseMLPoly.from_evaluations([1, 2, 3, 4]))

@@ -6,7 +6,7 @@ Names are resolved lazily so that `python -m zkes_b200.build` can run before the
 import importlib
 
 _API = ("Context", "DenseMLPoly", "LinearSumcheckProver", "SumcheckProof", "Transcript",
-        "SparseDenseSumcheckProver")
+        "SparseDenseSumcheckProver", "evaluate_lagrange_basis", "fix_variables_from_right")
 
 
 def __getattr__(name):

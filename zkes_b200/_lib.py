@@ -44,6 +44,8 @@ SIGNATURES = {
     "zk_sumcheck_sparse_dense_prove": (c_int, [c_void_p, c_uint32, c_uint64, c_void_p, c_void_p, c_void_p, c_int,
                                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                c_void_p]),
+    "zk_fix_from_right": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_int]),
+    "zk_eq_table": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_int]),
     "zk_msm_g1": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_uint64, c_void_p, c_int]),
     "zk_msm_g1_batched": (c_int, [c_void_p, c_void_p, c_int, c_uint64, c_void_p, c_int, c_uint64, c_void_p, c_int]),
     "zk_msm_g1_gather": (c_int, [c_void_p, c_void_p, c_int, c_uint64, c_void_p, c_void_p, c_int, c_uint64, c_void_p,
@@ -51,6 +53,16 @@ SIGNATURES = {
     "zk_g1_normalize": (c_int, [c_void_p, c_void_p, c_int, c_uint64, c_void_p, c_int]),
     "zk_msm_last_stats": (c_int, [c_void_p, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_uint64),
                                   POINTER(c_uint64)]),
+    "zk_kzh_srs_setup": (c_int, [c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 POINTER(c_void_p)]),
+    "zk_kzh_srs_upload": (c_int, [c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p)]),
+    "zk_kzh_srs_free": (None, [c_void_p, c_void_p]),
+    "zk_kzh_srs_shape": (c_int, [c_void_p, POINTER(c_uint32), POINTER(c_uint32), POINTER(c_uint32)]),
+    "zk_kzh_srs_read": (c_int, [c_void_p, c_void_p, c_int, c_uint64, c_uint64, c_void_p]),
+    "zk_kzh_commit": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p, c_int, c_void_p, c_void_p]),
+    "zk_kzh2_open": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p, c_int, c_void_p, c_uint32, c_void_p]),
+    "zk_kzh3_open": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p, c_int, c_void_p, c_uint32, c_void_p, c_void_p,
+                             c_void_p, c_void_p]),
     "zk_fold_lsb_static": (c_int, [c_uint32, c_void_p, c_uint32, c_void_p, c_void_p, c_void_p]),
     "zk_gen_uniform_fr": (c_int, [c_void_p, c_uint64, c_uint64, c_uint64, c_uint64, c_void_p]),
     "zk_gen_small_fr": (c_int, [c_void_p, c_uint64, c_uint64, c_uint64, c_uint64, c_int, c_void_p]),

@@ -127,6 +127,27 @@ class DenseMLPoly:
         return DenseMLPoly(self.n - k, mont=out)
 
 
+def evaluate_lagrange_basis(ctx: Context, r):
+    """src/util/poly.rs:573-618 (and precompute_eq, :657-699)."""
+    k = len(r)
+    pt = to_mont_array(r) if k else np.zeros((1, 4), dtype=np.uint64)
+    out = np.zeros((1 << k, 4), dtype=np.uint64)
+    check(lib.zk_eq_table(ctx.handle, k, _ptr(pt), _ptr(out), ZK_MEM_HOST), "zk_eq_table")
+    return from_mont_array(out)
+
+
+def fix_variables_from_right(ctx: Context, poly: "DenseMLPoly", fixed_vars) -> "DenseMLPoly":
+    """src/util/poly.rs:705-758."""
+    assert len(fixed_vars) <= poly.n, "invalid size of partial point"
+    k = len(fixed_vars)
+    pt = to_mont_array(fixed_vars) if k else np.zeros((1, 4), dtype=np.uint64)
+    out = np.zeros((1 << (poly.n - k), 4), dtype=np.uint64)
+    src = c_void_p(poly.device_ptr) if poly.device_ptr is not None else _ptr(poly.mont)
+    mem = ZK_MEM_DEVICE if poly.device_ptr is not None else ZK_MEM_HOST
+    check(lib.zk_fix_from_right(ctx.handle, poly.n, src, mem, k, _ptr(pt), _ptr(out), ZK_MEM_HOST), "zk_fix_from_right")
+    return DenseMLPoly(poly.n - k, mont=out)
+
+
 class SumcheckProof:
     """src/crypto/sumcheck/prover.rs:9-14."""
 

@@ -1,0 +1,332 @@
+// C ABI: KZH2 / KZH3 structured reference strings, commit and open (G1 side).
+#include "../../include/zkb200.h"
+#include "msm.hpp"
+
+#include <vector>
+
+using namespace zk;
+
+namespace zk {
+size_t fixed_base_table_bytes();
+int fixed_base_build_table(const Affine& g, void* table_mem, cudaStream_t s);
+int fixed_base_generate(const void* table_mem, int n_factors, const Fr* const* tables, const uint32_t* bits,
+                        const Fr* alpha, uint64_t count, Affine* out, int sm_count, cudaStream_t s);
+int normalize_device(zk_ctx* ctx, const Jacobian* in, uint64_t n, Affine* out);
+size_t from_right_scratch_elems(zk_ctx* ctx, uint32_t n, uint32_t k);
+int fix_from_right_device(zk_ctx* ctx, uint32_t n, const Fr* f_dev, uint32_t k, const uint64_t* point_host, Fr* scratch,
+                          Fr* out_dev);
+int eq_table_device(zk_ctx* ctx, const uint64_t* point_host, uint32_t k, Fr* point_dev, Fr* table);
+}  // namespace zk
+
+struct zk_kzh_srs {
+  int dims = 0;
+  uint32_t n = 0, x_log = 0, y_log = 0, z_log = 0;
+  Affine* h[3] = {nullptr, nullptr, nullptr};  // full (2^n), mid (2^(n - x_log)), low (2^z_log, KZH3 only)
+  uint64_t count[3] = {0, 0, 0};
+};
+
+namespace {
+
+inline size_t al(size_t x) { return (x + 255) & ~(size_t)255; }
+
+// get_degree_from_maximum_supported_degree: kzh2.rs:423-429, kzh3.rs:429-437
+void split_degrees(int dims, uint32_t n, uint32_t* x, uint32_t* y, uint32_t* z) {
+  if (dims == 2) {
+    *x = n / 2;
+    *y = n - n / 2;
+    *z = 0;
+  } else {
+    const uint32_t k = n / 3;
+    *x = k + (n % 3 >= 1);
+    *y = k + (n % 3 == 2);
+    *z = k;
+  }
+}
+
+int alloc_srs(zk_ctx* ctx, int dims, uint32_t n, zk_kzh_srs** out) {
+  if (!ctx || !out) return fail(ZK_ERR_ARG, "kzh_srs: NULL argument");
+  if (dims != 2 && dims != 3) return fail(ZK_ERR_ARG, "kzh_srs: dims must be 2 or 3");
+  if (n > 30) return fail(ZK_ERR_ARG, "kzh_srs: n %u too large", n);
+  cudaSetDevice(ctx->device);
+  zk_kzh_srs* s = new zk_kzh_srs();
+  s->dims = dims;
+  s->n = n;
+  split_degrees(dims, n, &s->x_log, &s->y_log, &s->z_log);
+  s->count[0] = 1ull << n;
+  s->count[1] = 1ull << (n - s->x_log);
+  s->count[2] = dims == 3 ? 1ull << s->z_log : 0;
+  for (int k = 0; k < 3; k++) {
+    if (!s->count[k]) continue;
+    cudaError_t e = cudaMalloc(&s->h[k], s->count[k] * sizeof(Affine));
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      for (int j = 0; j < 3; j++) cudaFree(s->h[j]);
+      delete s;
+      return fail(ZK_ERR_OOM, "kzh_srs: %llu points: %s", (unsigned long long)(1ull << n), cudaGetErrorString(e));
+    }
+  }
+  *out = s;
+  return ZK_OK;
+}
+
+// Device copy of the evaluations, zero-extended to 2^n (extend_number_of_variables, poly.rs:925-938).
+int stage_poly(zk_ctx* ctx, uint32_t n, uint32_t poly_n, const uint64_t* evals, zk_mem mem, Fr* staging, const Fr** f) {
+  const uint64_t size = 1ull << n, have = 1ull << poly_n;
+  if (mem == ZK_MEM_DEVICE && poly_n == n) {
+    *f = reinterpret_cast<const Fr*>(evals);
+    return ZK_OK;
+  }
+  ZK_CUDA(cudaMemcpyAsync(staging, evals, have * sizeof(Fr), cudaMemcpyDefault, ctx->stream));
+  if (have < size) ZK_CUDA(cudaMemsetAsync(staging + have, 0, (size - have) * sizeof(Fr), ctx->stream));
+  *f = staging;
+  return ZK_OK;
+}
+
+// split_input (kzh2.rs:479-498, kzh3.rs:443-460): left-pad with zeros to n coordinates.
+void pad_point(const uint64_t* point, uint32_t point_len, uint32_t n, std::vector<uint64_t>& out) {
+  out.assign((size_t)n * 4, 0);
+  if (point_len >= n) {
+    if (n) memcpy(out.data(), point, (size_t)n * 32);  // longer inputs: the leading coordinates are used
+  } else if (point_len) {
+    memcpy(out.data() + (size_t)(n - point_len) * 4, point, (size_t)point_len * 32);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int zk_kzh_srs_setup(zk_ctx* ctx, int dims, uint32_t n, const uint64_t* g_affine, const uint64_t* tau_x,
+                     const uint64_t* tau_y, const uint64_t* tau_z, const uint64_t* alpha, zk_kzh_srs** out) {
+  if (!g_affine || !tau_x || !tau_y) return fail(ZK_ERR_ARG, "kzh_srs_setup: NULL argument");
+  if (dims == 2 && !alpha) return fail(ZK_ERR_ARG, "kzh_srs_setup: KZH2 needs alpha");
+  if (dims == 3 && !tau_z) return fail(ZK_ERR_ARG, "kzh_srs_setup: KZH3 needs tau_z");
+  zk_kzh_srs* s = nullptr;
+  int rc = alloc_srs(ctx, dims, n, &s);
+  if (rc) return rc;
+  CtxLock lk(ctx);
+  cudaStream_t st = ctx->stream;
+  const uint64_t nx = 1ull << s->x_log, ny = 1ull << s->y_log, nz = dims == 3 ? 1ull << s->z_log : 0;
+  char* base = nullptr;
+  rc = ctx->reserve_aux(fixed_base_table_bytes() + al((nx + ny + nz + 4) * sizeof(Fr)) + 1024, (void**)&base);
+  if (rc) { cudaFree(s->h[0]); cudaFree(s->h[1]); cudaFree(s->h[2]); delete s; return rc; }
+  void* table = base;
+  Fr* d_tx = reinterpret_cast<Fr*>(base + al(fixed_base_table_bytes()));
+  Fr* d_ty = d_tx + nx;
+  Fr* d_tz = d_ty + ny;
+  ZK_CUDA(cudaMemcpyAsync(d_tx, tau_x, nx * sizeof(Fr), cudaMemcpyHostToDevice, st));
+  ZK_CUDA(cudaMemcpyAsync(d_ty, tau_y, ny * sizeof(Fr), cudaMemcpyHostToDevice, st));
+  if (nz) ZK_CUDA(cudaMemcpyAsync(d_tz, tau_z, nz * sizeof(Fr), cudaMemcpyHostToDevice, st));
+  Affine g;
+  memcpy(&g, g_affine, sizeof(Affine));
+  ctx->launches += fixed_base_build_table(g, table, st);
+  if (dims == 2) {
+    // h_xy[i] = (tau_x[x] tau_y[y]) g with y in the low bits; h_y[j] = (alpha tau_y[j]) g   (kzh2.rs:521-541)
+    const Fr* t2[2] = {d_ty, d_tx};
+    const uint32_t b2[2] = {s->y_log, s->x_log};
+    ctx->launches += fixed_base_generate(table, 2, t2, b2, nullptr, s->count[0], s->h[0], ctx->sm_count, st);
+    Fr a = fr_load(alpha);
+    const Fr* t1[1] = {d_ty};
+    const uint32_t b1[1] = {s->y_log};
+    ctx->launches += fixed_base_generate(table, 1, t1, b1, &a, s->count[1], s->h[1], ctx->sm_count, st);
+  } else {
+    // h_xyz (z low, y middle, x high), h_yz, h_z   (kzh3.rs:480-531)
+    const Fr* t3[3] = {d_tz, d_ty, d_tx};
+    const uint32_t b3[3] = {s->z_log, s->y_log, s->x_log};
+    ctx->launches += fixed_base_generate(table, 3, t3, b3, nullptr, s->count[0], s->h[0], ctx->sm_count, st);
+    ctx->launches += fixed_base_generate(table, 2, t3, b3, nullptr, s->count[1], s->h[1], ctx->sm_count, st);
+    ctx->launches += fixed_base_generate(table, 1, t3, b3, nullptr, s->count[2], s->h[2], ctx->sm_count, st);
+  }
+  ZK_CUDA(cudaGetLastError());
+  ZK_CUDA(cudaStreamSynchronize(st));
+  *out = s;
+  return ZK_OK;
+}
+
+int zk_kzh_srs_upload(zk_ctx* ctx, int dims, uint32_t n, const uint64_t* h_full, const uint64_t* h_mid,
+                      const uint64_t* h_low, zk_mem mem, zk_kzh_srs** out) {
+  if (!h_full || !h_mid || (dims == 3 && !h_low)) return fail(ZK_ERR_ARG, "kzh_srs_upload: NULL argument");
+  zk_kzh_srs* s = nullptr;
+  int rc = alloc_srs(ctx, dims, n, &s);
+  if (rc) return rc;
+  CtxLock lk(ctx);
+  const uint64_t* src[3] = {h_full, h_mid, h_low};
+  for (int k = 0; k < 3; k++)
+    if (s->count[k]) ZK_CUDA(cudaMemcpyAsync(s->h[k], src[k], s->count[k] * sizeof(Affine), cudaMemcpyDefault, ctx->stream));
+  ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+  (void)mem;
+  *out = s;
+  return ZK_OK;
+}
+
+void zk_kzh_srs_free(zk_ctx* ctx, zk_kzh_srs* srs) {
+  if (!srs) return;
+  if (ctx) {
+    CtxLock lk(ctx);
+    cudaStreamSynchronize(ctx->stream);
+    for (int k = 0; k < 3; k++) cudaFree(srs->h[k]);
+  }
+  delete srs;
+}
+
+int zk_kzh_srs_shape(const zk_kzh_srs* srs, uint32_t* x_log, uint32_t* y_log, uint32_t* z_log) {
+  if (!srs) return fail(ZK_ERR_ARG, "kzh_srs_shape: NULL srs");
+  if (x_log) *x_log = srs->x_log;
+  if (y_log) *y_log = srs->y_log;
+  if (z_log) *z_log = srs->z_log;
+  return ZK_OK;
+}
+
+int zk_kzh_srs_read(zk_ctx* ctx, const zk_kzh_srs* srs, int which, uint64_t offset, uint64_t count, uint64_t* out) {
+  if (!ctx || !srs || !out || which < 0 || which > 2) return fail(ZK_ERR_ARG, "kzh_srs_read: bad argument");
+  if (offset + count > srs->count[which]) return fail(ZK_ERR_ARG, "kzh_srs_read: range past the end");
+  CtxLock lk(ctx);
+  ZK_CUDA(cudaMemcpyAsync(out, srs->h[which] + offset, count * sizeof(Affine), cudaMemcpyDeviceToHost, ctx->stream));
+  ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+  return ZK_OK;
+}
+
+int zk_kzh_commit(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uint64_t* evals, zk_mem evals_mem,
+                  uint64_t* c_affine_out, uint64_t* d_x_jac_out) {
+  if (!ctx || !srs || !evals || !c_affine_out || !d_x_jac_out) return fail(ZK_ERR_ARG, "kzh_commit: NULL argument");
+  if (poly_n > srs->n) return fail(ZK_ERR_ARG, "Cannot extend to fewer variables");
+  CtxLock lk(ctx);
+  cudaStream_t st = ctx->stream;
+  const uint32_t n = srs->n;
+  const uint64_t size = 1ull << n, rows = 1ull << srs->x_log;
+  char* base = nullptr;
+  int rc = ctx->reserve_work(al(size * sizeof(Fr)) + al((rows + 1) * sizeof(Jacobian)) + al(sizeof(Affine)) + 1024, (void**)&base);
+  if (rc) return rc;
+  Fr* staging = reinterpret_cast<Fr*>(base);
+  Jacobian* d_jac = reinterpret_cast<Jacobian*>(base + al(size * sizeof(Fr)));
+  Affine* d_c = reinterpret_cast<Affine*>(base + al(size * sizeof(Fr)) + al((rows + 1) * sizeof(Jacobian)));
+  const Fr* f = nullptr;
+  rc = stage_poly(ctx, n, poly_n, evals, evals_mem, staging, &f);
+  if (rc) return rc;
+  // C = sum_i f[i] h_full[i]   (kzh2.rs:636-647, kzh3.rs:662-673)
+  ctx->prof_begin(ZK_PROF_MSM, 0.0, 8);
+  rc = msm_run(ctx, srs->h[0], nullptr, f, size, 1, d_jac + rows, &ctx->last_msm);
+  ctx->prof_end();
+  if (rc) return rc;
+  rc = normalize_device(ctx, d_jac + rows, 1, d_c);
+  if (rc) return rc;
+  // d_x[i] = sum_j f[i * 2^(n - x_log) + j] h_mid[j]   (kzh2.rs:653-660, kzh3.rs:680-687)
+  ctx->prof_begin(ZK_PROF_MSM, 0.0, 8);
+  rc = msm_run(ctx, srs->h[1], nullptr, f, srs->count[1], (uint32_t)rows, d_jac, nullptr);
+  ctx->prof_end();
+  if (rc) return rc;
+  ZK_CUDA(cudaMemcpyAsync(c_affine_out, d_c, sizeof(Affine), cudaMemcpyDeviceToHost, st));
+  ZK_CUDA(cudaMemcpyAsync(d_x_jac_out, d_jac, rows * sizeof(Jacobian), cudaMemcpyDeviceToHost, st));
+  ZK_CUDA(cudaStreamSynchronize(st));
+  return ZK_OK;
+}
+
+int zk_kzh2_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uint64_t* evals, zk_mem evals_mem,
+                 const uint64_t* point, uint32_t point_len, uint64_t* f_star_out) {
+  if (!ctx || !srs || !evals || !f_star_out || (point_len && !point)) return fail(ZK_ERR_ARG, "kzh2_open: NULL argument");
+  if (srs->dims != 2) return fail(ZK_ERR_ARG, "kzh2_open: the SRS is not a KZH2 SRS");
+  if (poly_n > srs->n) return fail(ZK_ERR_ARG, "Cannot extend to fewer variables");
+  CtxLock lk(ctx);
+  cudaStream_t st = ctx->stream;
+  const uint32_t n = srs->n;
+  const uint64_t size = 1ull << n, ny = 1ull << srs->y_log;
+  std::vector<uint64_t> pt;
+  pad_point(point, point_len, n, pt);
+  char* base = nullptr;
+  int rc = ctx->reserve_work(al(size * sizeof(Fr)) + al(ny * sizeof(Fr)) +
+                             al(from_right_scratch_elems(ctx, n, srs->x_log) * sizeof(Fr)) + 1024, (void**)&base);
+  if (rc) return rc;
+  Fr* staging = reinterpret_cast<Fr*>(base);
+  Fr* d_out = reinterpret_cast<Fr*>(base + al(size * sizeof(Fr)));
+  Fr* scratch = reinterpret_cast<Fr*>(base + al(size * sizeof(Fr)) + al(ny * sizeof(Fr)));
+  const Fr* f = nullptr;
+  rc = stage_poly(ctx, n, poly_n, evals, evals_mem, staging, &f);
+  if (rc) return rc;
+  // f_star = fix_variables_from_right(poly, r_x), r_x = the x_log highest coordinates (kzh2.rs:700-704)
+  if (srs->x_log == 0) {
+    ZK_CUDA(cudaMemcpyAsync(d_out, f, ny * sizeof(Fr), cudaMemcpyDeviceToDevice, st));
+  } else {
+    rc = fix_from_right_device(ctx, n, f, srs->x_log, pt.data() + (size_t)srs->y_log * 4, scratch, d_out);
+    if (rc) return rc;
+  }
+  ZK_CUDA(cudaMemcpyAsync(f_star_out, d_out, ny * sizeof(Fr), cudaMemcpyDeviceToHost, st));
+  ZK_CUDA(cudaStreamSynchronize(st));
+  return ZK_OK;
+}
+
+int zk_kzh3_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uint64_t* evals, zk_mem evals_mem,
+                 const uint64_t* point, uint32_t point_len, const uint64_t* d_x_jac, uint64_t* d_y_jac_out,
+                 uint64_t* c_y_affine_out, uint64_t* f_star_out) {
+  if (!ctx || !srs || !evals || !d_x_jac || !d_y_jac_out || !c_y_affine_out || !f_star_out || (point_len && !point))
+    return fail(ZK_ERR_ARG, "kzh3_open: NULL argument");
+  if (srs->dims != 3) return fail(ZK_ERR_ARG, "kzh3_open: the SRS is not a KZH3 SRS");
+  if (poly_n > srs->n) return fail(ZK_ERR_ARG, "Cannot extend to fewer variables");
+  CtxLock lk(ctx);
+  cudaStream_t st = ctx->stream;
+  const uint32_t n = srs->n, xl = srs->x_log, yl = srs->y_log, zl = srs->z_log;
+  const uint64_t size = 1ull << n, nx = 1ull << xl, ny = 1ull << yl, nz = 1ull << zl, nyz = ny * nz;
+  std::vector<uint64_t> pt;
+  pad_point(point, point_len, n, pt);
+  const uint64_t* r_y = pt.data() + (size_t)zl * 4;
+  const uint64_t* r_x = pt.data() + (size_t)(zl + yl) * 4;
+  size_t fr_scr = from_right_scratch_elems(ctx, n, xl);
+  const size_t fr_scr2 = from_right_scratch_elems(ctx, yl + zl, yl);
+  if (fr_scr2 > fr_scr) fr_scr = fr_scr2;
+  char* base = nullptr;
+  size_t need = al(size * sizeof(Fr)) + al(nyz * sizeof(Fr)) + al(nz * sizeof(Fr)) + al((nx + 8) * sizeof(Fr)) * 2 +
+                al(fr_scr * sizeof(Fr)) + al((nx + ny + 2) * sizeof(Jacobian)) + al((nx + 1) * sizeof(Affine)) + 2048;
+  int rc = ctx->reserve_work(need, (void**)&base);
+  if (rc) return rc;
+  size_t off = 0;
+  auto take = [&](size_t bytes) { char* p = base + off; off += al(bytes); return p; };
+  Fr* staging = (Fr*)take(size * sizeof(Fr));
+  Fr* f_prime = (Fr*)take(nyz * sizeof(Fr));
+  Fr* f_star = (Fr*)take(nz * sizeof(Fr));
+  Fr* eq_x = (Fr*)take((nx + 8) * sizeof(Fr));
+  Fr* pt_dev = (Fr*)take((nx + 8) * sizeof(Fr));
+  Fr* scratch = (Fr*)take(fr_scr * sizeof(Fr));
+  Jacobian* d_dx = (Jacobian*)take(nx * sizeof(Jacobian));
+  Jacobian* d_dy = (Jacobian*)take((ny + 2) * sizeof(Jacobian));
+  Affine* d_aff = (Affine*)take((nx + 1) * sizeof(Affine));
+  const Fr* f = nullptr;
+  rc = stage_poly(ctx, n, poly_n, evals, evals_mem, staging, &f);
+  if (rc) return rc;
+  // f_prime = fix_variables_from_right(poly, r_x)   (kzh3.rs:736)
+  if (xl == 0) {
+    ZK_CUDA(cudaMemcpyAsync(f_prime, f, nyz * sizeof(Fr), cudaMemcpyDeviceToDevice, st));
+  } else {
+    rc = fix_from_right_device(ctx, n, f, xl, r_x, scratch, f_prime);
+    if (rc) return rc;
+  }
+  // d_y[i] = MSM(h_z, f_prime[i * 2^z_log ..])   (kzh3.rs:743-750)
+  ctx->prof_begin(ZK_PROF_MSM, 0.0, 8);
+  rc = msm_run(ctx, srs->h[2], nullptr, f_prime, nz, (uint32_t)ny, d_dy, nullptr);
+  ctx->prof_end();
+  if (rc) return rc;
+  // f_star = fix_variables_from_right(poly, r_y || r_x) = fix_variables_from_right(f_prime, r_y)   (kzh3.rs:762-764)
+  if (yl == 0) {
+    ZK_CUDA(cudaMemcpyAsync(f_star, f_prime, nz * sizeof(Fr), cudaMemcpyDeviceToDevice, st));
+  } else {
+    rc = fix_from_right_device(ctx, yl + zl, f_prime, yl, r_y, scratch, f_star);
+    if (rc) return rc;
+  }
+  // c_y = MSM(affine(d_x), eq(r_x))   (kzh3.rs:739, 767-779)
+  ZK_CUDA(cudaMemcpyAsync(d_dx, d_x_jac, nx * sizeof(Jacobian), cudaMemcpyHostToDevice, st));
+  rc = normalize_device(ctx, d_dx, nx, d_aff);
+  if (rc) return rc;
+  rc = eq_table_device(ctx, r_x, xl, pt_dev, eq_x);
+  if (rc) return rc;
+  ctx->prof_begin(ZK_PROF_MSM, 0.0, 8);
+  rc = msm_run(ctx, d_aff, nullptr, eq_x, nx, 1, d_dy + ny, &ctx->last_msm);
+  ctx->prof_end();
+  if (rc) return rc;
+  rc = normalize_device(ctx, d_dy + ny, 1, d_aff + nx);
+  if (rc) return rc;
+  ZK_CUDA(cudaMemcpyAsync(d_y_jac_out, d_dy, ny * sizeof(Jacobian), cudaMemcpyDeviceToHost, st));
+  ZK_CUDA(cudaMemcpyAsync(c_y_affine_out, d_aff + nx, sizeof(Affine), cudaMemcpyDeviceToHost, st));
+  ZK_CUDA(cudaMemcpyAsync(f_star_out, f_star, nz * sizeof(Fr), cudaMemcpyDeviceToHost, st));
+  ZK_CUDA(cudaStreamSynchronize(st));
+  return ZK_OK;
+}
+
+}  // extern "C"

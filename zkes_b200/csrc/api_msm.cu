@@ -22,6 +22,23 @@ __global__ void k_normalize(const Jacobian* __restrict__ in, uint64_t n, Affine*
   }
 }
 
+}  // namespace
+
+namespace zk {
+// out[i] = affine form of in[i]; device pointers.
+int normalize_device(zk_ctx* ctx, const Jacobian* in, uint64_t n, Affine* out) {
+  if (n == 0) return 0;
+  uint64_t blocks = (n + 127) / 128;
+  if (blocks > (uint64_t)ctx->sm_count * 16) blocks = ctx->sm_count * 16;
+  k_normalize<<<(unsigned)blocks, 128, 0, ctx->stream>>>(in, n, out);
+  ctx->launches++;
+  ZK_CUDA(cudaGetLastError());
+  return 0;
+}
+}  // namespace zk
+
+namespace {
+
 // Shared driver: stage host inputs in the work scratch, run, copy the Jacobian rows out.
 int msm_entry(zk_ctx* ctx, const uint64_t* bases, zk_mem bases_mem, uint64_t n_bases, const uint64_t* indices,
               const uint64_t* scalars, zk_mem scalars_mem, uint64_t n, uint64_t rows, uint64_t* out_jac, zk_mem out_mem,

@@ -24,6 +24,12 @@ void launch_final(int num_poly, bool bind, const Fr* const* src, const Fr& r, Fr
 void launch_fold(const Fr* src, Fr* dst, const Fr& r, uint64_t out_len, int max_blocks, cudaStream_t stream);
 
 
+// poly.cu
+int launch_eq_table(const Fr* point_dev, const Fr* point_host, uint32_t k, Fr* out, int sm_count, cudaStream_t s);
+uint32_t from_right_splits(uint64_t lo_n, uint64_t hi_n, int sm_count);
+int launch_from_right(const Fr* f, const Fr* eq, uint64_t lo_n, uint64_t hi_n, Fr* partial, Fr* out, int sm_count,
+                      cudaStream_t s);
+
 // sparse.cu
 void launch_sparse_msg(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
                        const RoundScratch& sc, cudaStream_t s);

@@ -1,0 +1,110 @@
+"""Host-side mirror of the KZH2 / KZH3 commitment interface (src/crypto/polycommit/kzh2.rs,
+kzh3.rs), G1 side: setup from trapdoors, commit, open.  Pairing checks stay with the caller."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_uint32, c_void_p
+
+import numpy as np
+
+from . import curve
+from ._lib import ZK_MEM_DEVICE, ZK_MEM_HOST, check, lib
+from .field import from_mont_array, to_mont_array
+
+
+def _p(a):
+    return c_void_p(a.ctypes.data)
+
+
+class KZHSRS:
+    """KZH2SRS (kzh2.rs:27-35) / KZH3SRS (kzh3.rs:33-45), resident on the device."""
+
+    def __init__(self, ctx, dims: int, n: int, handle):
+        self.ctx, self.dims, self.n, self.handle = ctx, dims, n, handle
+        x, y, z = c_uint32(), c_uint32(), c_uint32()
+        check(lib.zk_kzh_srs_shape(handle, ctypes.byref(x), ctypes.byref(y), ctypes.byref(z)), "zk_kzh_srs_shape")
+        self.x_log, self.y_log, self.z_log = x.value, y.value, z.value
+
+    @classmethod
+    def setup(cls, ctx, dims: int, n: int, g, tau_x, tau_y, tau_z=None, alpha=None):
+        """setup_kzh2_srs (kzh2.rs:502-555) / setup_kzh3_srs (kzh3.rs:463-563) from sampled trapdoors."""
+        h = c_void_p()
+        ga = curve.affine_to_array([g])
+        tx, ty = to_mont_array(tau_x), to_mont_array(tau_y)
+        tz = to_mont_array(tau_z) if tau_z is not None else None
+        al = to_mont_array([alpha]) if alpha is not None else None
+        check(lib.zk_kzh_srs_setup(ctx.handle, dims, n, _p(ga), _p(tx), _p(ty), _p(tz) if tz is not None else None,
+                                   _p(al) if al is not None else None, ctypes.byref(h)), "zk_kzh_srs_setup")
+        return cls(ctx, dims, n, h)
+
+    @classmethod
+    def upload(cls, ctx, dims: int, n: int, h_full, h_mid, h_low=None):
+        h = c_void_p()
+        a, b = curve.affine_to_array(h_full), curve.affine_to_array(h_mid)
+        c = curve.affine_to_array(h_low) if h_low is not None else None
+        check(lib.zk_kzh_srs_upload(ctx.handle, dims, n, _p(a), _p(b), _p(c) if c is not None else None, ZK_MEM_HOST,
+                                    ctypes.byref(h)), "zk_kzh_srs_upload")
+        return cls(ctx, dims, n, h)
+
+    def read(self, which: int, offset: int, count: int):
+        out = np.zeros((max(count, 1), 8), dtype=np.uint64)
+        check(lib.zk_kzh_srs_read(self.ctx.handle, self.handle, which, offset, count, _p(out)), "zk_kzh_srs_read")
+        return curve.affine_from_array(out[:count])
+
+    def close(self):
+        if self.handle:
+            lib.zk_kzh_srs_free(self.ctx.handle, self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class KZHCommitment:
+    """KZH2Commitment / KZH3Commitment: affine c and aux.d_x (projective), kzh2.rs:103-107."""
+
+    def __init__(self, srs, c, d_x_jac):
+        self.srs, self.c, self.d_x_jac = srs, c, d_x_jac
+
+    @property
+    def d_x(self):
+        return curve.jacobian_to_affine_py(self.d_x_jac)
+
+
+def _evals_arg(poly):
+    if poly.device_ptr is not None:
+        return c_void_p(poly.device_ptr), ZK_MEM_DEVICE
+    return _p(poly.mont), ZK_MEM_HOST
+
+
+def commit(ctx, srs: KZHSRS, poly) -> KZHCommitment:
+    """kzh2_commit (kzh2.rs:619-673) / kzh3_commit (kzh3.rs:645-700)."""
+    c = np.zeros((1, 8), dtype=np.uint64)
+    dx = np.zeros((1 << srs.x_log, 12), dtype=np.uint64)
+    ptr, mem = _evals_arg(poly)
+    check(lib.zk_kzh_commit(ctx.handle, srs.handle, poly.n, ptr, mem, _p(c), _p(dx)), "zk_kzh_commit")
+    return KZHCommitment(srs, curve.affine_from_array(c)[0], dx)
+
+
+def kzh2_open(ctx, srs: KZHSRS, point, com: KZHCommitment, poly):
+    """kzh2_open (kzh2.rs:676-710) -> (d_x, f_star)."""
+    pt = to_mont_array(point) if len(point) else np.zeros((1, 4), dtype=np.uint64)
+    out = np.zeros((1 << srs.y_log, 4), dtype=np.uint64)
+    ptr, mem = _evals_arg(poly)
+    check(lib.zk_kzh2_open(ctx.handle, srs.handle, poly.n, ptr, mem, _p(pt), len(point), _p(out)), "zk_kzh2_open")
+    return com.d_x, from_mont_array(out)
+
+
+def kzh3_open(ctx, srs: KZHSRS, point, com: KZHCommitment, poly):
+    """kzh3_open (kzh3.rs:702-787) -> (d_x, d_y, c_y, f_star)."""
+    pt = to_mont_array(point) if len(point) else np.zeros((1, 4), dtype=np.uint64)
+    dy = np.zeros((1 << srs.y_log, 12), dtype=np.uint64)
+    cy = np.zeros((1, 8), dtype=np.uint64)
+    fs = np.zeros((1 << srs.z_log, 4), dtype=np.uint64)
+    ptr, mem = _evals_arg(poly)
+    check(lib.zk_kzh3_open(ctx.handle, srs.handle, poly.n, ptr, mem, _p(pt), len(point), _p(com.d_x_jac), _p(dy), _p(cy),
+                           _p(fs)), "zk_kzh3_open")
+    return com.d_x, curve.jacobian_to_affine_py(dy), curve.affine_from_array(cy)[0], from_mont_array(fs)
