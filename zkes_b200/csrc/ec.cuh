@@ -154,7 +154,9 @@ ZK_HD Affine to_affine(const Xyzz& p) {
 // k * p for a small unsigned k (double and add, MSB first).
 ZK_HD Xyzz mul_small(const Xyzz& p, uint32_t k) {
   Xyzz acc = Xyzz::inf();
-  for (int bit = 31; bit >= 0; bit--) {
+  int top = 31;
+  while (top >= 0 && !((k >> top) & 1u)) top--;  // skip the leading zero bits
+  for (int bit = top; bit >= 0; bit--) {
     acc = dbl(acc);
     if ((k >> bit) & 1u) acc = add(acc, p);
   }

@@ -109,6 +109,66 @@ __global__ void k_msm_digits(const Fr* __restrict__ scalars, uint64_t n, uint32_
   }
 }
 
+// Same two passes for a small key space (at most kSmallKeys buckets in total): keys are counted in
+// shared memory first, so the global counters see one atomic per (block, bucket) instead of
+// one per digit.  In scatter mode the block reserves a contiguous range per bucket.
+constexpr uint32_t kSmallKeys = 4096;
+
+template <int MODE>
+__global__ void __launch_bounds__(256) k_msm_digits_small(const Fr* __restrict__ scalars, uint64_t n, uint32_t rows, int w,
+                                                          int k_windows, uint32_t n_keys, uint64_t per_block,
+                                                          uint32_t* counts_or_cursor, uint32_t* entries) {
+  __shared__ uint32_t hist[kSmallKeys];
+  __shared__ uint32_t basepos[kSmallKeys];
+  const uint64_t total = n * rows;
+  const uint32_t half = 1u << (w - 1);
+  const uint64_t begin = (uint64_t)blockIdx.x * per_block;
+  const uint64_t end = begin + per_block < total ? begin + per_block : total;
+  for (uint32_t k = threadIdx.x; k < n_keys; k += blockDim.x) hist[k] = 0;
+  __syncthreads();
+  for (int pass = 0; pass < (MODE == 0 ? 1 : 2); pass++) {
+    for (uint64_t g = begin + threadIdx.x; g < end; g += blockDim.x) {
+      uint32_t mag[8];
+      const bool negv = fold_scalar(ld_scalar(scalars + g), mag);
+      const uint32_t row = (uint32_t)(g / n);
+      const uint32_t col = (uint32_t)(g - (uint64_t)row * n);
+      uint32_t carry = 0;
+      for (int k = 0; k < k_windows; k++) {
+        uint32_t raw = bit_field(mag, k * w, w) + carry;
+        bool dneg = false;
+        if (raw > half) {
+          raw = (1u << w) - raw;
+          dneg = true;
+          carry = 1;
+        } else {
+          carry = 0;
+        }
+        if (raw == 0) continue;
+        const uint32_t key = (row * (uint32_t)k_windows + (uint32_t)k) * half + (raw - 1);
+        if (pass == 0) {
+          atomicAdd(hist + key, 1u);
+        } else {
+          const uint32_t slot = basepos[key] + atomicAdd(hist + key, 1u);
+          entries[slot] = col | ((negv != dneg) ? 0x80000000u : 0u);
+        }
+      }
+    }
+    __syncthreads();
+    if (pass == 0) {
+      for (uint32_t k = threadIdx.x; k < n_keys; k += blockDim.x) {
+        const uint32_t c = hist[k];
+        if (MODE == 0) {
+          if (c) atomicAdd(counts_or_cursor + k, c);
+        } else {
+          basepos[k] = c ? atomicAdd(counts_or_cursor + k, c) : 0;
+          hist[k] = 0;
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
 __device__ __forceinline__ Affine ld_affine(const Affine* p) {
   const uint4* q = reinterpret_cast<const uint4*>(p);
   const uint4 a = __ldg(q), b = __ldg(q + 1), c = __ldg(q + 2), d = __ldg(q + 3);
@@ -212,6 +272,29 @@ __global__ void __launch_bounds__(128) k_msm_fixup(const uint32_t* __restrict__ 
     __syncwarp();
   }
   if (lane == 0) st_xyzz(bucket_sums + b, acc);
+}
+
+// Few, long buckets (one narrow window over millions of points): one block per bucket.
+__global__ void __launch_bounds__(128) k_msm_fixup_block(const uint32_t* __restrict__ offsets, uint32_t seg,
+                                                         Xyzz* bucket_sums, const Xyzz* heads, const Xyzz* tails) {
+  __shared__ Xyzz sh[128];
+  const uint32_t b = blockIdx.x;
+  const uint32_t s = offsets[b], e = offsets[b + 1];
+  if (e <= s) return;
+  const uint32_t c0 = s / seg, c1 = (e - 1) / seg;
+  if (c0 == c1) return;
+  Xyzz acc = Xyzz::inf();
+  for (uint32_t c = c0 + threadIdx.x; c <= c1; c += blockDim.x) acc = add(acc, ld_xyzz(c == c0 ? tails + c : heads + c));
+  sh[threadIdx.x] = acc;
+  __syncthreads();
+  for (uint32_t off = blockDim.x >> 1; off > 0; off >>= 1) {
+    if (threadIdx.x < off) {
+      acc = add(acc, sh[threadIdx.x + off]);
+      sh[threadIdx.x] = acc;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) st_xyzz(bucket_sums + b, acc);
 }
 
 // One block per (row, window): sum_j (j + 1) * B_j over `half` buckets.
@@ -333,11 +416,21 @@ int msm_run(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const Fr* 
 
   // ---- pass 2: count, scan, scatter
   ZK_CUDA(cudaMemsetAsync(offsets, 0, (n_buckets + 2) * 4ull, s));
-  k_msm_digits<0><<<sm * 8, 256, 0, s>>>(scalars, n, rows, w, k_windows, offsets, nullptr);
+  const bool small_keys = n_buckets <= kSmallKeys;
+  uint32_t dig_blocks = (uint32_t)((total + 4095) / 4096);
+  if (dig_blocks > (uint32_t)sm * 8) dig_blocks = sm * 8;
+  const uint64_t per_block = (total + dig_blocks - 1) / dig_blocks;
+  if (small_keys)
+    k_msm_digits_small<0><<<dig_blocks, 256, 0, s>>>(scalars, n, rows, w, k_windows, n_buckets, per_block, offsets, nullptr);
+  else
+    k_msm_digits<0><<<sm * 8, 256, 0, s>>>(scalars, n, rows, w, k_windows, offsets, nullptr);
   ctx->launches++;
   ctx->launches += exclusive_scan_u32(offsets, n_buckets, scan_tmp, true, s);
   ZK_CUDA(cudaMemcpyAsync(cursor, offsets, (n_buckets + 1) * 4ull, cudaMemcpyDeviceToDevice, s));
-  k_msm_digits<1><<<sm * 8, 256, 0, s>>>(scalars, n, rows, w, k_windows, cursor, entries);
+  if (small_keys)
+    k_msm_digits_small<1><<<dig_blocks, 256, 0, s>>>(scalars, n, rows, w, k_windows, n_buckets, per_block, cursor, entries);
+  else
+    k_msm_digits<1><<<sm * 8, 256, 0, s>>>(scalars, n, rows, w, k_windows, cursor, entries);
   ctx->launches++;
   ZK_CUDA(cudaMemcpyAsync(ctx->host_small, offsets + n_buckets, 4, cudaMemcpyDeviceToHost, s));
   ZK_CUDA(cudaStreamSynchronize(s));
@@ -353,11 +446,14 @@ int msm_run(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const Fr* 
     n_chunks = (n_entries + seg - 1) / seg;
     k_msm_accumulate<<<(n_chunks + 127) / 128, 128, 0, s>>>(bases, gather, entries, offsets, n_buckets, n_entries, seg,
                                                            n_chunks, bucket_sums, heads, tails);
-    k_msm_fixup<<<(n_buckets + 3) / 4, 128, 0, s>>>(offsets, n_buckets, seg, bucket_sums, heads, tails);
+    if (n_buckets <= 8192)
+      k_msm_fixup_block<<<n_buckets, 128, 0, s>>>(offsets, seg, bucket_sums, heads, tails);
+    else
+      k_msm_fixup<<<(n_buckets + 3) / 4, 128, 0, s>>>(offsets, n_buckets, seg, bucket_sums, heads, tails);
     ctx->launches += 2;
   }
   // ---- reduce buckets, combine windows
-  uint32_t threads = half / 8;
+  uint32_t threads = half / 4;
   if (threads < 32) threads = 32;
   if (threads > 256) threads = 256;
   k_msm_bucket_reduce<<<rows * k_windows, threads, threads * sizeof(Xyzz), s>>>(bucket_sums, half, window_sums);
