@@ -32,6 +32,7 @@ extern "C" {
 
 typedef struct zk_ctx zk_ctx;
 typedef struct zk_transcript zk_transcript;
+typedef struct zk_comm zk_comm;
 
 typedef enum zk_status {
   ZK_OK = 0,
@@ -120,6 +121,30 @@ int zk_sumcheck_sparse_dense_prove(zk_ctx* ctx, uint32_t num_var, uint64_t nnz, 
                                    const uint64_t* vals, const uint64_t* dense, zk_mem mem, zk_fs_round_fn fs,
                                    void* fs_user, zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges,
                                    uint64_t* final_table0, uint64_t* final_eval);
+
+/* ---- multi-GPU (one process per GPU; no counterpart in the reference, which is single-process) --- */
+/* A communicator over `world` ranks (a power of two, at most 64), bound to NCCL at run time.
+ * Rank 0 calls zk_comm_unique_id and the host distributes the 128 bytes to the other ranks. */
+int zk_comm_unique_id(uint8_t out[128]);
+int zk_comm_init(zk_ctx* ctx, int rank, int world, const uint8_t unique_id[128], zk_comm** out);
+void zk_comm_free(zk_ctx* ctx, zk_comm* comm);
+/* Sharded provers: the hypercube is cut on its top log2(world) variables, rank p holding entries
+ * [p 2^num_var / world, (p+1) 2^num_var / world) of every table (for the sparse table: the
+ * entries of that range, with indices relative to its start).  Each local round ends with an
+ * all-gather of the ranks' partial round messages, summed on every rank; all ranks run
+ * identical transcripts (pass equal-state transcripts or equivalent callbacks) and return
+ * identical outputs, sized as for the unsharded call with the total num_var.  Once the local
+ * variables are bound, the per-rank values are gathered and every rank finishes the last
+ * log2(world) rounds on them. */
+int zk_sumcheck_linear_prove_sharded(zk_ctx* ctx, zk_comm* comm, uint32_t num_var, uint32_t num_poly,
+                                     const uint64_t* const* local_tables, zk_mem tables_mem, zk_fs_round_fn fs,
+                                     void* fs_user, zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges,
+                                     uint64_t* final_table0, uint64_t* final_eval);
+int zk_sumcheck_sparse_dense_prove_sharded(zk_ctx* ctx, zk_comm* comm, uint32_t num_var, uint64_t local_nnz,
+                                           const uint64_t* local_idx, const uint64_t* local_vals,
+                                           const uint64_t* local_dense, zk_mem mem, zk_fs_round_fn fs, void* fs_user,
+                                           zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges,
+                                           uint64_t* final_table0, uint64_t* final_eval);
 
 /* ---- multilinear helpers --------------------------------------------------------------- */
 /* DenseMLPoly::fix_variables, src/util/poly.rs:842-887: binds the k lowest variables of a

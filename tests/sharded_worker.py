@@ -1,0 +1,142 @@
+"""Worker for the multi-rank tests (launched by torch.distributed.run, one process per rank).
+
+  mode "gloo": CPU emulation of the sharded protocol with the oracle's arithmetic and the
+               product's sharding helpers, exchanged over gloo; checks equality with the
+               single-process oracle proof.
+  mode "nccl": the CUDA library's sharded provers on one GPU per rank against the oracle."""
+import os
+import random
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "oracle"))
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+import pyoracle as o  # noqa: E402
+from zkes_b200 import dist as zd  # noqa: E402
+
+
+def problem(n, nnz, seed):
+    rnd = random.Random(seed)
+    idx = sorted(rnd.sample(range(1 << n), nnz))
+    vals = [o.fr_from_int(rnd.randrange(-128, 128)) for _ in idx]
+    dense = [rnd.randrange(o.R_MOD) for _ in range(1 << n)]
+    f = [rnd.randrange(o.R_MOD) for _ in range(1 << n)]
+    return idx, vals, dense, f
+
+
+def emulate_sharded_linear(tables, rank, world, label):
+    """The sharded protocol with big-integer arithmetic: local partial messages, all-gather, sum,
+    replicated transcript, local folds, then the gathered tail."""
+    n = len(tables[0]).bit_length() - 1
+    L = len(tables)
+    local = [zd.shard_dense(t, rank, world) for t in tables]
+    tr = o.Transcript(label)
+    tr.append_u64(b"num_var", n)
+    tr.append_u64(b"num_poly", L)
+    helper = o.LinearSumcheckProver.__new__(o.LinearSumcheckProver)
+    helper.num_poly = L
+    msgs, chals = [], []
+    n_local = n - zd.log2_exact(world)
+    for _ in range(n_local):
+        helper.a_arrays = local
+        part = helper._round_message()
+        gathered = [None] * world
+        dist.all_gather_object(gathered, part)
+        msg = [sum(g[c] for g in gathered) % o.R_MOD for c in range(L + 1)]
+        for m in msg:
+            tr.append_scalar(b"round_message", m)
+        ch = tr.challenge_scalar(b"challenge")
+        msgs.append(msg)
+        chals.append(ch)
+        local = [o.fix_variables(t, [ch]) for t in local]
+    finals = [None] * world
+    dist.all_gather_object(finals, [t[0] for t in local])
+    tail = zd.tail_tables(finals)
+    for _ in range(n - n_local):
+        helper.a_arrays = tail
+        msg = helper._round_message()
+        for m in msg:
+            tr.append_scalar(b"round_message", m)
+        ch = tr.challenge_scalar(b"challenge")
+        msgs.append(msg)
+        chals.append(ch)
+        tail = [o.fix_variables(t, [ch]) for t in tail]
+    final = 1
+    for t in tail:
+        final = final * t[0] % o.R_MOD
+    return msgs, chals, [t[0] for t in tail], final
+
+
+def main():
+    mode = sys.argv[1]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    if mode == "gloo":
+        dist.init_process_group("gloo")
+        for n, nnz, seed in [(5, 7, 1), (7, 30, 2)]:
+            idx, vals, dense, f = problem(n, nnz, seed)
+            a = [0] * (1 << n)
+            for i, v in zip(idx, vals):
+                a[i] = v
+            # the sparse helper and the dense one describe the same shard
+            li, lv = zd.shard_sparse(idx, vals, rank, world, n)
+            la = zd.shard_dense(a, rank, world)
+            assert [la[i] for i in li] == lv and sum(1 for v in la if v) == sum(1 for v in lv if v)
+            got = emulate_sharded_linear([a, dense], rank, world, b"sharded")
+            t = o.Transcript(b"sharded")
+            p = o.LinearSumcheckProver(n, 2, t)
+            pr = p.prove([a, dense], t)
+            assert got[0] == pr.round_messages and got[1] == p.challenges and got[3] == pr.final_eval
+            got3 = emulate_sharded_linear([a, dense, f], rank, world, b"sharded")
+            t = o.Transcript(b"sharded")
+            p = o.LinearSumcheckProver(n, 3, t)
+            pr = p.prove([a, dense, f], t)
+            assert got3[0] == pr.round_messages and got3[3] == pr.final_eval
+    else:
+        local_rank = int(os.environ.get("LOCAL_RANK", rank))
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        from zkes_b200 import Context, DenseMLPoly, Transcript
+        ctx = Context(local_rank)
+        comm = zd.Comm(ctx)
+        for n, nnz, seed in [(3, 2, 1), (6, 9, 2), (11, 100, 3), (13, 3000, 4)]:
+            if n < zd.log2_exact(world):
+                continue
+            idx, vals, dense, f = problem(n, nnz, seed)
+            a = [0] * (1 << n)
+            for i, v in zip(idx, vals):
+                a[i] = v
+            for tables in ([a, dense], [dense, f, a], [f]):
+                t = Transcript(b"sharded")
+                t.append_u64(b"num_var", n)
+                t.append_u64(b"num_poly", len(tables))
+                local = [DenseMLPoly.from_evaluations(zd.shard_dense(tb, rank, world)) for tb in tables]
+                msgs, chals, fin_t, fin = zd.sharded_linear_prove(ctx, comm, n, local, t)
+                ot = o.Transcript(b"sharded")
+                op = o.LinearSumcheckProver(n, len(tables), ot)
+                opr = op.prove(tables, ot)
+                assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
+                assert fin_t == [x[0] for x in op.a_arrays]
+                assert t.challenge_scalar(b"after") == ot.challenge_scalar(b"after")
+            t = Transcript(b"sharded")
+            t.append_u64(b"num_var", n)
+            t.append_u64(b"num_poly", 2)
+            li, lv = zd.shard_sparse(idx, vals, rank, world, n)
+            ld = DenseMLPoly.from_evaluations(zd.shard_dense(dense, rank, world))
+            msgs, chals, fin_t, fin = zd.sharded_sparse_dense_prove(ctx, comm, n, li, lv, ld, t)
+            ot = o.Transcript(b"sharded")
+            op, opr = o.sparse_dense_prove(n, idx, vals, dense, ot)
+            assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
+        comm.close()
+        ctx.close()
+    dist.barrier()
+    if rank == 0:
+        print("sharded worker ok:", mode, "world", world)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

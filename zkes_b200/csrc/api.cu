@@ -25,9 +25,13 @@ int fail(int code, const char* fmt, ...) {
 namespace zk {
 // Reads the round message the last kernel left in rs.msg, records it, runs the Fiat-Shamir
 // step (callback or built-in transcript) and records the challenge.
-int fs_round(zk_ctx* ctx, int n_msgs, uint32_t round, zk_fs_round_fn fs, void* fs_user, zk_transcript* tr,
+int fs_round(zk_ctx* ctx, zk_comm* comm, int n_msgs, uint32_t round, zk_fs_round_fn fs, void* fs_user, zk_transcript* tr,
              uint64_t* round_msgs, uint64_t* challenges, Fr* challenge) {
   ZK_CUDA(cudaGetLastError());
+  if (comm) {  // every rank holds a partial message: sum them so all ranks absorb the same scalars
+    int rc = comm_sum_fr(ctx, comm, ctx->rs.msg, n_msgs);
+    if (rc) return rc;
+  }
   ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->rs.msg, n_msgs * sizeof(Fr), cudaMemcpyDeviceToHost, ctx->stream));
   ZK_CUDA(cudaStreamSynchronize(ctx->stream));
   const Fr* msg = reinterpret_cast<const Fr*>(ctx->host_small);
@@ -166,10 +170,74 @@ void zk_transcript_challenge_scalar(zk_transcript* t, const uint8_t* label, size
 }
 
 // ---------------------------------------------------------------------------- linear sumcheck
-int zk_sumcheck_linear_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, const uint64_t* const* tables,
-                             zk_mem tables_mem, zk_fs_round_fn fs, void* fs_user, zk_transcript* tr,
-                             uint64_t* round_msgs, uint64_t* challenges, uint64_t* final_table0,
-                             uint64_t* final_eval) {
+}  // extern "C"
+
+namespace zk {
+
+// `rounds` rounds of the dense prover over device tables cur[i] of 2^rounds elements each; the
+// folded tables alternate between ping and pong.  On return cur[] points at the two-entry
+// tables the last challenge has not been bound on yet (or the inputs when rounds == 0).
+int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr** cur, Fr** ping, Fr** pong,
+                  uint32_t round_offset, zk_fs_round_fn fs, void* fs_user, zk_transcript* tr, uint64_t* round_msgs,
+                  uint64_t* challenges, Fr* challenge) {
+  const uint64_t size = 1ull << rounds;
+  for (uint32_t round = 0; round < rounds; round++) {
+    const uint64_t pairs = size >> (round + 1);
+    if (round == 0) {
+      ctx->prof_begin(ZK_PROF_ROUND, 64.0 * L * pairs);
+      launch_round(L, false, cur, nullptr, *challenge, pairs, ctx->rs, ctx->stream);
+    } else {
+      Fr** dst = (round & 1) ? ping : pong;
+      ctx->prof_begin(ZK_PROF_ROUND, 192.0 * L * pairs);
+      launch_round(L, true, cur, dst, *challenge, pairs, ctx->rs, ctx->stream);
+      for (int i = 0; i < L; i++) cur[i] = dst[i];
+    }
+    ctx->prof_end();
+    ctx->launches++;
+    int rc = fs_round(ctx, comm, L + 1, round_offset + round, fs, fs_user, tr, round_msgs, challenges, challenge);
+    if (rc != ZK_OK) return rc;
+  }
+  return ZK_OK;
+}
+
+// After the local rounds of a sharded prove: ctx->final_out[0..L) holds this rank's fully bound
+// value of each table.  Gathers them into L tables of `world` entries, runs the remaining
+// log2(world) rounds identically on every rank and leaves the final values in ctx->final_out.
+int sharded_tail(zk_ctx* ctx, zk_comm* comm, int L, uint32_t n_local, zk_fs_round_fn fs, void* fs_user,
+                 zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges, Fr* challenge) {
+  const int world = comm_world(comm);
+  uint32_t logw = 0;
+  while ((1 << logw) < world) logw++;
+  Fr* buf = ctx->tail_buf;  // [gathered: world * L][tables: L * world][ping: L * world / 2][pong: L * world / 4]
+  Fr* gathered = buf;
+  Fr* tables = buf + (size_t)world * kMaxPolys;
+  int rc = comm_gather_fr(ctx, comm, ctx->final_out, L, gathered);
+  if (rc) return rc;
+  // transpose rank-major values into per-table arrays (tiny: through the host)
+  Fr host[64 * kMaxPolys], arranged[64 * kMaxPolys];
+  ZK_CUDA(cudaMemcpyAsync(host, gathered, (size_t)world * L * sizeof(Fr), cudaMemcpyDeviceToHost, ctx->stream));
+  ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+  for (int r = 0; r < world; r++)
+    for (int i = 0; i < L; i++) arranged[i * world + r] = host[r * L + i];
+  ZK_CUDA(cudaMemcpyAsync(tables, arranged, (size_t)world * L * sizeof(Fr), cudaMemcpyHostToDevice, ctx->stream));
+  const Fr* cur[kMaxPolys];
+  Fr *ping[kMaxPolys], *pong[kMaxPolys];
+  Fr* pp = tables + (size_t)world * kMaxPolys;
+  for (int i = 0; i < L; i++) {
+    cur[i] = tables + (size_t)i * world;
+    ping[i] = pp + (size_t)i * world;
+    pong[i] = pp + (size_t)(kMaxPolys + i) * world;
+  }
+  rc = linear_rounds(ctx, nullptr, L, logw, cur, ping, pong, n_local, fs, fs_user, tr, round_msgs, challenges, challenge);
+  if (rc) return rc;
+  launch_final(L, logw > 0, cur, *challenge, ctx->final_out, ctx->stream);
+  ctx->launches++;
+  return ZK_OK;
+}
+
+int linear_prove_impl(zk_ctx* ctx, zk_comm* comm, uint32_t num_var, uint32_t num_poly, const uint64_t* const* tables,
+                      zk_mem tables_mem, zk_fs_round_fn fs, void* fs_user, zk_transcript* tr, uint64_t* round_msgs,
+                      uint64_t* challenges, uint64_t* final_table0, uint64_t* final_eval) {
   if (!ctx) return fail(ZK_ERR_ARG, "linear_prove: NULL context");
   if (!tables || num_poly == 0) return fail(ZK_ERR_ARG, "Polynomials cannot be empty");
   if (num_poly > kMaxPolys) return fail(ZK_ERR_ARG, "linear_prove: num_poly %u exceeds %d", num_poly, kMaxPolys);
@@ -179,9 +247,15 @@ int zk_sumcheck_linear_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, c
     if (!tables[i]) return fail(ZK_ERR_ARG, "Polynomial %u has incorrect size", i);
   if (num_var && (!round_msgs || !challenges)) return fail(ZK_ERR_ARG, "linear_prove: NULL output");
   if (!final_eval) return fail(ZK_ERR_ARG, "linear_prove: NULL output");
+  const int world = comm_world(comm);
+  uint32_t logw = 0;
+  while ((1 << logw) < world) logw++;
+  if (num_var < logw) return fail(ZK_ERR_ARG, "linear_prove: %u variables cannot be sharded over %d ranks", num_var, world);
+  if (world > 64) return fail(ZK_ERR_ARG, "linear_prove: at most 64 ranks");
 
   CtxLock lk(ctx);
-  const uint64_t size = 1ull << num_var;
+  const uint32_t n_local = num_var - logw;
+  const uint64_t size = 1ull << n_local;
   const int L = (int)num_poly;
 
   // device layout: [copies of host inputs] [ping: L * size/2] [pong: L * size/4]
@@ -205,25 +279,15 @@ int zk_sumcheck_linear_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, c
   }
 
   Fr challenge = Fr::zero();
-  for (uint32_t round = 0; round < num_var; round++) {
-    const uint64_t pairs = size >> (round + 1);
-    if (round == 0) {
-      ctx->prof_begin(ZK_PROF_ROUND, 64.0 * L * pairs);
-      launch_round(L, false, cur, nullptr, challenge, pairs, ctx->rs, ctx->stream);
-    } else {
-      Fr** dst = (round & 1) ? ping : pong;
-      ctx->prof_begin(ZK_PROF_ROUND, 192.0 * L * pairs);
-      launch_round(L, true, cur, dst, challenge, pairs, ctx->rs, ctx->stream);
-      for (int i = 0; i < L; i++) cur[i] = dst[i];
-    }
-    ctx->prof_end();
-    ctx->launches++;
-    ZK_CUDA(cudaGetLastError());
-    rc = fs_round(ctx, L + 1, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
-    if (rc != ZK_OK) return rc;
-  }
-  launch_final(L, num_var > 0, cur, challenge, ctx->final_out, ctx->stream);
+  rc = linear_rounds(ctx, world > 1 ? comm : nullptr, L, n_local, cur, ping, pong, 0, fs, fs_user, tr, round_msgs,
+                     challenges, &challenge);
+  if (rc) return rc;
+  launch_final(L, n_local > 0, cur, challenge, ctx->final_out, ctx->stream);
   ctx->launches++;
+  if (world > 1) {
+    rc = sharded_tail(ctx, comm, L, n_local, fs, fs_user, tr, round_msgs, challenges, &challenge);
+    if (rc) return rc;
+  }
   ZK_CUDA(cudaGetLastError());
   ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->final_out, (L + 1) * sizeof(Fr), cudaMemcpyDeviceToHost, ctx->stream));
   ZK_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -232,6 +296,27 @@ int zk_sumcheck_linear_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, c
     for (int i = 0; i < L; i++) fr_store(final_table0 + 4 * i, fin[i]);
   fr_store(final_eval, fin[L]);
   return ZK_OK;
+}
+
+}  // namespace zk
+
+extern "C" {
+
+int zk_sumcheck_linear_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, const uint64_t* const* tables,
+                             zk_mem tables_mem, zk_fs_round_fn fs, void* fs_user, zk_transcript* tr,
+                             uint64_t* round_msgs, uint64_t* challenges, uint64_t* final_table0,
+                             uint64_t* final_eval) {
+  return linear_prove_impl(ctx, nullptr, num_var, num_poly, tables, tables_mem, fs, fs_user, tr, round_msgs, challenges,
+                           final_table0, final_eval);
+}
+
+int zk_sumcheck_linear_prove_sharded(zk_ctx* ctx, zk_comm* comm, uint32_t num_var, uint32_t num_poly,
+                                     const uint64_t* const* local_tables, zk_mem tables_mem, zk_fs_round_fn fs,
+                                     void* fs_user, zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges,
+                                     uint64_t* final_table0, uint64_t* final_eval) {
+  if (!comm) return fail(ZK_ERR_ARG, "linear_prove_sharded: NULL communicator");
+  return linear_prove_impl(ctx, comm, num_var, num_poly, local_tables, tables_mem, fs, fs_user, tr, round_msgs, challenges,
+                           final_table0, final_eval);
 }
 
 // ---------------------------------------------------------------------------- folds

@@ -20,18 +20,24 @@ struct Arena {
 };
 }  // namespace
 
-extern "C" int zk_sumcheck_sparse_dense_prove(zk_ctx* ctx, uint32_t num_var, uint64_t nnz, const uint64_t* idx,
-                                              const uint64_t* vals, const uint64_t* dense, zk_mem mem,
-                                              zk_fs_round_fn fs, void* fs_user, zk_transcript* tr,
-                                              uint64_t* round_msgs, uint64_t* challenges, uint64_t* final_table0,
-                                              uint64_t* final_eval) {
+static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uint64_t nnz, const uint64_t* idx,
+                             const uint64_t* vals, const uint64_t* dense, zk_mem mem, zk_fs_round_fn fs, void* fs_user,
+                             zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges, uint64_t* final_table0,
+                             uint64_t* final_eval) {
   if (!ctx) return fail(ZK_ERR_ARG, "sparse_dense_prove: NULL context");
+  const int world = comm_world(comm);
+  uint32_t logw = 0;
+  while ((1 << logw) < world) logw++;
+  if (total_var < logw) return fail(ZK_ERR_ARG, "sparse_dense_prove: %u variables cannot be sharded over %d ranks", total_var, world);
+  if (world > 64) return fail(ZK_ERR_ARG, "sparse_dense_prove: at most 64 ranks");
+  const uint32_t num_var = total_var - logw;  // variables of this rank's chunk
+  if (world == 1) comm = nullptr;
   if (num_var > 32) return fail(ZK_ERR_ARG, "sparse_dense_prove: num_var %u exceeds 32", num_var);
   const uint64_t size = 1ull << num_var;
   if (nnz > size) return fail(ZK_ERR_ARG, "sparse_dense_prove: %llu entries in a domain of %llu", (unsigned long long)nnz, (unsigned long long)size);
   if (!dense || (nnz && (!idx || !vals))) return fail(ZK_ERR_ARG, "sparse_dense_prove: NULL input");
   if (!fs && !tr) return fail(ZK_ERR_ARG, "sparse_dense_prove: neither a callback nor a transcript was given");
-  if (!final_eval || (num_var && (!round_msgs || !challenges))) return fail(ZK_ERR_ARG, "sparse_dense_prove: NULL output");
+  if (!final_eval || (total_var && (!round_msgs || !challenges))) return fail(ZK_ERR_ARG, "sparse_dense_prove: NULL output");
 
   CtxLock lk(ctx);
   cudaStream_t s = ctx->stream;
@@ -120,7 +126,7 @@ extern "C" int zk_sumcheck_sparse_dense_prove(zk_ctx* ctx, uint32_t num_var, uin
     }
     ctx->prof_end();
     ctx->launches++;
-    rc = fs_round(ctx, 3, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
+    rc = fs_round(ctx, comm, 3, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
     if (rc != ZK_OK) return rc;
     if (mode == kSparse) {
       Fr* nb = b_buf[round & 1];
@@ -141,6 +147,10 @@ extern "C" int zk_sumcheck_sparse_dense_prove(zk_ctx* ctx, uint32_t num_var, uin
   else
     launch_final(2, true, d_cur, challenge, ctx->final_out, s);
   ctx->launches++;
+  if (comm) {  // the remaining log2(world) variables: every rank finishes on the gathered values
+    rc = sharded_tail(ctx, comm, 2, num_var, fs, fs_user, tr, round_msgs, challenges, &challenge);
+    if (rc) return rc;
+  }
   ZK_CUDA(cudaGetLastError());
   ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->final_out, 3 * sizeof(Fr), cudaMemcpyDeviceToHost, s));
   ZK_CUDA(cudaStreamSynchronize(s));
@@ -151,4 +161,24 @@ extern "C" int zk_sumcheck_sparse_dense_prove(zk_ctx* ctx, uint32_t num_var, uin
   }
   fr_store(final_eval, fin[2]);
   return ZK_OK;
+}
+
+extern "C" int zk_sumcheck_sparse_dense_prove(zk_ctx* ctx, uint32_t num_var, uint64_t nnz, const uint64_t* idx,
+                                              const uint64_t* vals, const uint64_t* dense, zk_mem mem,
+                                              zk_fs_round_fn fs, void* fs_user, zk_transcript* tr,
+                                              uint64_t* round_msgs, uint64_t* challenges, uint64_t* final_table0,
+                                              uint64_t* final_eval) {
+  return sparse_dense_impl(ctx, nullptr, num_var, nnz, idx, vals, dense, mem, fs, fs_user, tr, round_msgs, challenges,
+                           final_table0, final_eval);
+}
+
+extern "C" int zk_sumcheck_sparse_dense_prove_sharded(zk_ctx* ctx, zk_comm* comm, uint32_t num_var, uint64_t local_nnz,
+                                                      const uint64_t* local_idx, const uint64_t* local_vals,
+                                                      const uint64_t* local_dense, zk_mem mem, zk_fs_round_fn fs,
+                                                      void* fs_user, zk_transcript* tr, uint64_t* round_msgs,
+                                                      uint64_t* challenges, uint64_t* final_table0,
+                                                      uint64_t* final_eval) {
+  if (!comm) return fail(ZK_ERR_ARG, "sparse_dense_prove_sharded: NULL communicator");
+  return sparse_dense_impl(ctx, comm, num_var, local_nnz, local_idx, local_vals, local_dense, mem, fs, fs_user, tr,
+                           round_msgs, challenges, final_table0, final_eval);
 }

@@ -1,0 +1,158 @@
+// Multi-GPU exchange: one process per GPU, NCCL all-gather of the per-round partial sums.
+//
+// NCCL is bound at run time (dlopen of libnccl.so.2: the copy the host process already loaded,
+// e.g. PyTorch's, or the system one) so the library has no link-time dependency on it.  The
+// host distributes the unique id (torch.distributed broadcast, MPI, a file ...).
+#include "../../include/zkb200.h"
+#include "ctx.hpp"
+#include "reduce.cuh"
+
+#include <dlfcn.h>
+
+using namespace zk;
+
+namespace {
+
+typedef struct ncclComm* ncclComm_t;
+struct NcclId { char internal[128]; };
+typedef int (*fn_get_id)(NcclId*);
+typedef int (*fn_init_rank)(ncclComm_t*, int, NcclId, int);
+typedef int (*fn_all_gather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t);
+typedef int (*fn_destroy)(ncclComm_t);
+typedef const char* (*fn_errstr)(int);
+
+struct NcclApi {
+  void* handle = nullptr;
+  fn_get_id get_id = nullptr;
+  fn_init_rank init_rank = nullptr;
+  fn_all_gather all_gather = nullptr;
+  fn_destroy destroy = nullptr;
+  fn_errstr errstr = nullptr;
+};
+NcclApi g_nccl;
+std::mutex g_nccl_mu;
+
+int load_nccl() {
+  std::lock_guard<std::mutex> lk(g_nccl_mu);
+  if (g_nccl.handle) return ZK_OK;
+  void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) return fail(ZK_ERR_COMM, "NCCL not found: %s", dlerror());
+  NcclApi a;
+  a.handle = h;
+  a.get_id = (fn_get_id)dlsym(h, "ncclGetUniqueId");
+  a.init_rank = (fn_init_rank)dlsym(h, "ncclCommInitRank");
+  a.all_gather = (fn_all_gather)dlsym(h, "ncclAllGather");
+  a.destroy = (fn_destroy)dlsym(h, "ncclCommDestroy");
+  a.errstr = (fn_errstr)dlsym(h, "ncclGetErrorString");
+  if (!a.get_id || !a.init_rank || !a.all_gather || !a.destroy) return fail(ZK_ERR_COMM, "NCCL symbols missing");
+  g_nccl = a;
+  return ZK_OK;
+}
+
+// out[c] = sum over ranks of gathered[rank * n_vals + c]
+__global__ void k_sum_ranks(const Fr* __restrict__ gathered, int world, int n_vals, Fr* out) {
+  const int c = threadIdx.x;
+  if (c >= n_vals) return;
+  Fr s = gathered[c];
+  for (int r = 1; r < world; r++) s = add(s, gathered[r * n_vals + c]);
+  out[c] = s;
+}
+
+}  // namespace
+
+struct zk_comm {
+  ncclComm_t comm = nullptr;
+  int rank = 0, world = 1;
+  Fr* gather_buf = nullptr;  // world * 16 elements
+};
+
+namespace zk {
+int comm_world(const zk_comm* c) { return c ? c->world : 1; }
+int comm_rank(const zk_comm* c) { return c ? c->rank : 0; }
+
+// vals (device, n_vals <= 16 elements) <- element-wise sum over all ranks; stream-ordered.
+int comm_sum_fr(zk_ctx* ctx, zk_comm* c, Fr* vals, int n_vals) {
+  if (!c || c->world == 1) return ZK_OK;
+  int rc = g_nccl.all_gather(vals, c->gather_buf, (size_t)n_vals * sizeof(Fr), 1 /*ncclUint8*/, c->comm, ctx->stream);
+  if (rc != 0) return fail(ZK_ERR_COMM, "ncclAllGather: %s", g_nccl.errstr ? g_nccl.errstr(rc) : "error");
+  k_sum_ranks<<<1, 32, 0, ctx->stream>>>(c->gather_buf, c->world, n_vals, vals);
+  ctx->launches++;
+  return ZK_OK;
+}
+
+// out (device, world * n_vals elements, rank-major) <- every rank's vals; stream-ordered.
+int comm_gather_fr(zk_ctx* ctx, zk_comm* c, const Fr* vals, int n_vals, Fr* out) {
+  if (!c || c->world == 1) {
+    ZK_CUDA(cudaMemcpyAsync(out, vals, (size_t)n_vals * sizeof(Fr), cudaMemcpyDeviceToDevice, ctx->stream));
+    return ZK_OK;
+  }
+  int rc = g_nccl.all_gather(vals, out, (size_t)n_vals * sizeof(Fr), 1, c->comm, ctx->stream);
+  if (rc != 0) return fail(ZK_ERR_COMM, "ncclAllGather: %s", g_nccl.errstr ? g_nccl.errstr(rc) : "error");
+  return ZK_OK;
+}
+
+// Raw bytes (device buffers), for the MSM partial points.
+int comm_gather_bytes(zk_ctx* ctx, zk_comm* c, const void* send, size_t bytes, void* recv) {
+  if (!c || c->world == 1) {
+    ZK_CUDA(cudaMemcpyAsync(recv, send, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    return ZK_OK;
+  }
+  int rc = g_nccl.all_gather(send, recv, bytes, 1, c->comm, ctx->stream);
+  if (rc != 0) return fail(ZK_ERR_COMM, "ncclAllGather: %s", g_nccl.errstr ? g_nccl.errstr(rc) : "error");
+  return ZK_OK;
+}
+}  // namespace zk
+
+extern "C" {
+
+int zk_comm_unique_id(uint8_t out[128]) {
+  if (!out) return fail(ZK_ERR_ARG, "comm_unique_id: NULL argument");
+  int rc = load_nccl();
+  if (rc) return rc;
+  NcclId id;
+  rc = g_nccl.get_id(&id);
+  if (rc != 0) return fail(ZK_ERR_COMM, "ncclGetUniqueId failed (%d)", rc);
+  memcpy(out, id.internal, 128);
+  return ZK_OK;
+}
+
+int zk_comm_init(zk_ctx* ctx, int rank, int world, const uint8_t unique_id[128], zk_comm** out) {
+  if (!ctx || !out || !unique_id) return fail(ZK_ERR_ARG, "comm_init: NULL argument");
+  if (world < 1 || rank < 0 || rank >= world) return fail(ZK_ERR_ARG, "comm_init: rank %d of %d", rank, world);
+  if (world & (world - 1)) return fail(ZK_ERR_ARG, "comm_init: the number of ranks must be a power of two");
+  int rc = load_nccl();
+  if (rc) return rc;
+  CtxLock lk(ctx);
+  zk_comm* c = new zk_comm();
+  c->rank = rank;
+  c->world = world;
+  NcclId id;
+  memcpy(id.internal, unique_id, 128);
+  rc = g_nccl.init_rank(&c->comm, world, id, rank);
+  if (rc != 0) {
+    delete c;
+    return fail(ZK_ERR_COMM, "ncclCommInitRank: %s", g_nccl.errstr ? g_nccl.errstr(rc) : "error");
+  }
+  cudaError_t e = cudaMalloc(&c->gather_buf, (size_t)world * 16 * sizeof(Fr));
+  if (e != cudaSuccess) {
+    g_nccl.destroy(c->comm);
+    delete c;
+    return fail(ZK_ERR_OOM, "comm_init: %s", cudaGetErrorString(e));
+  }
+  *out = c;
+  return ZK_OK;
+}
+
+void zk_comm_free(zk_ctx* ctx, zk_comm* c) {
+  if (!c) return;
+  if (ctx) {
+    CtxLock lk(ctx);
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(c->gather_buf);
+    if (c->comm && g_nccl.destroy) g_nccl.destroy(c->comm);
+  }
+  delete c;
+}
+
+}  // extern "C"

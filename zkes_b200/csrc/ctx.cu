@@ -13,6 +13,7 @@ int zk_ctx::setup() {
   ZK_CUDA(cudaMemsetAsync(rs.counter, 0, 256, stream));
   ZK_CUDA(cudaMalloc(&rs.msg, sizeof(Fr) * 16));
   ZK_CUDA(cudaMalloc(&final_out, sizeof(Fr) * 16));
+  ZK_CUDA(cudaMalloc(&tail_buf, sizeof(Fr) * 64 * kMaxPolys * 4));
   ZK_CUDA(cudaHostAlloc(&host_small, 4096, cudaHostAllocDefault));
   ZK_CUDA(cudaStreamSynchronize(stream));
   return 0;
@@ -25,6 +26,7 @@ void zk_ctx::teardown() {
   cudaFree(rs.counter);
   cudaFree(rs.msg);
   cudaFree(final_out);
+  cudaFree(tail_buf);
   cudaFree(work);
   cudaFree(aux);
   if (host_small) cudaFreeHost(host_small);

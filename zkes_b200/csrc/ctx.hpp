@@ -50,12 +50,15 @@ struct MsmStatsPod {
   uint32_t entries = 0, buckets = 0;
 };
 
+struct zk_comm;
+
 struct zk_ctx {
   int device = 0;
   int sm_count = 0;
   cudaStream_t stream = nullptr;
   zk::RoundScratch rs{};
   zk::Fr* final_out = nullptr;   // kMaxPolys + 1 elements
+  zk::Fr* tail_buf = nullptr;    // sharded proves: gathered values and the last log2(world) rounds' tables
   void* host_small = nullptr;    // pinned, 4 KiB: round messages and other tiny read-backs
   void* work = nullptr;          // grow-only device scratch (copies of caller data, round buffers)
   size_t work_bytes = 0;
@@ -92,8 +95,19 @@ struct zk_transcript {
 
 namespace zk {
 typedef int (*fs_round_fn_t)(void* user, const uint64_t* msgs, uint32_t n_msgs, uint64_t challenge_out[4]);
-int fs_round(zk_ctx* ctx, int n_msgs, uint32_t round, fs_round_fn_t fs, void* fs_user, zk_transcript* tr,
+int fs_round(zk_ctx* ctx, zk_comm* comm, int n_msgs, uint32_t round, fs_round_fn_t fs, void* fs_user, zk_transcript* tr,
              uint64_t* round_msgs, uint64_t* challenges, Fr* challenge);
+int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr** cur, Fr** ping, Fr** pong,
+                  uint32_t round_offset, fs_round_fn_t fs, void* fs_user, zk_transcript* tr, uint64_t* round_msgs,
+                  uint64_t* challenges, Fr* challenge);
+int sharded_tail(zk_ctx* ctx, zk_comm* comm, int L, uint32_t n_local, fs_round_fn_t fs, void* fs_user,
+                 zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges, Fr* challenge);
+// comm.cu
+int comm_world(const zk_comm* c);
+int comm_rank(const zk_comm* c);
+int comm_sum_fr(zk_ctx* ctx, zk_comm* c, Fr* vals, int n_vals);
+int comm_gather_fr(zk_ctx* ctx, zk_comm* c, const Fr* vals, int n_vals, Fr* out);
+int comm_gather_bytes(zk_ctx* ctx, zk_comm* c, const void* send, size_t bytes, void* recv);
 
 // Serialises calls on a context and makes its device current for the calling thread.
 struct CtxLock {

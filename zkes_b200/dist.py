@@ -1,0 +1,119 @@
+"""Multi-GPU host logic: one process per GPU (torch.distributed for the plumbing), the hypercube
+cut on its top log2(world) variables.  The reference is single-process; these helpers have no
+counterpart there."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_void_p
+
+import numpy as np
+
+from ._lib import ZK_MEM_DEVICE, ZK_MEM_HOST, check, lib
+from .field import from_mont_array, to_mont_array
+
+
+def log2_exact(world: int) -> int:
+    lg = world.bit_length() - 1
+    if world < 1 or (1 << lg) != world:
+        raise ValueError(f"the number of ranks must be a power of two, got {world}")
+    return lg
+
+
+def shard_range(rank: int, world: int, num_var: int):
+    """Index range [begin, end) of the 2^num_var table that `rank` owns (contiguous chunks: the top
+    log2(world) variables select the rank, and they are the last ones the protocol binds)."""
+    lg = log2_exact(world)
+    if num_var < lg:
+        raise ValueError(f"{num_var} variables cannot be sharded over {world} ranks")
+    chunk = 1 << (num_var - lg)
+    return rank * chunk, (rank + 1) * chunk
+
+
+def shard_dense(table, rank: int, world: int):
+    n = len(table).bit_length() - 1
+    b, e = shard_range(rank, world, n)
+    return table[b:e]
+
+
+def shard_sparse(indices, values, rank: int, world: int, num_var: int):
+    """Entries of a sorted sparse table that fall in the rank's range, indices made local."""
+    b, e = shard_range(rank, world, num_var)
+    idx, val = [], []
+    for i, v in zip(indices, values):
+        if b <= i < e:
+            idx.append(i - b)
+            val.append(v)
+    return idx, val
+
+
+def tail_tables(per_rank_values):
+    """per_rank_values[r][i] = rank r's fully bound value of table i  ->  table i over the top variables."""
+    world = len(per_rank_values)
+    log2_exact(world)
+    n_tables = len(per_rank_values[0])
+    return [[per_rank_values[r][i] for r in range(world)] for i in range(n_tables)]
+
+
+class Comm:
+    """zk_comm over the ranks of an initialised torch.distributed process group."""
+
+    def __init__(self, ctx, rank: int = None, world: int = None):
+        import torch
+        import torch.distributed as dist
+
+        self.ctx = ctx
+        self.rank = dist.get_rank() if rank is None else rank
+        self.world = dist.get_world_size() if world is None else world
+        log2_exact(self.world)
+        uid = (ctypes.c_uint8 * 128)()
+        if self.rank == 0:
+            check(lib.zk_comm_unique_id(uid), "zk_comm_unique_id")
+        dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
+        t = torch.tensor(list(uid), dtype=torch.uint8, device=dev)
+        dist.broadcast(t, src=0)
+        uid = (ctypes.c_uint8 * 128)(*t.cpu().tolist())
+        h = c_void_p()
+        check(lib.zk_comm_init(ctx.handle, self.rank, self.world, uid, ctypes.byref(h)), "zk_comm_init")
+        self.handle = h
+
+    def close(self):
+        if self.handle:
+            lib.zk_comm_free(self.ctx.handle, self.handle)
+            self.handle = None
+
+
+def _p(a):
+    return c_void_p(a.ctypes.data)
+
+
+def sharded_linear_prove(ctx, comm: Comm, num_var: int, local_tables, transcript):
+    """Every rank passes its chunk of each table (DenseMLPoly) and an equal-state transcript whose
+    header (num_var, num_poly) is already absorbed.  Returns (round_messages, challenges,
+    final_table0, final_eval) as canonical ints, identical on all ranks."""
+    L = len(local_tables)
+    on_dev = local_tables[0].device_ptr is not None
+    ptrs = (c_void_p * L)(*[c_void_p(t.device_ptr) if on_dev else _p(t.mont) for t in local_tables])
+    msgs = np.zeros((max(num_var, 1), L + 1, 4), dtype=np.uint64)
+    chal = np.zeros((max(num_var, 1), 4), dtype=np.uint64)
+    fin_t = np.zeros((L, 4), dtype=np.uint64)
+    fin = np.zeros((1, 4), dtype=np.uint64)
+    check(lib.zk_sumcheck_linear_prove_sharded(ctx.handle, comm.handle, num_var, L, ptrs, ZK_MEM_DEVICE if on_dev else ZK_MEM_HOST,
+                                               None, None, transcript.handle, _p(msgs), _p(chal), _p(fin_t), _p(fin)),
+          "zk_sumcheck_linear_prove_sharded")
+    return ([from_mont_array(msgs[r]) for r in range(num_var)], from_mont_array(chal[:num_var]), from_mont_array(fin_t),
+            from_mont_array(fin)[0])
+
+
+def sharded_sparse_dense_prove(ctx, comm: Comm, num_var: int, local_idx, local_vals, local_dense, transcript):
+    nnz = len(local_idx)
+    ia = np.ascontiguousarray(np.array(list(local_idx) or [0], dtype=np.uint64))
+    va = to_mont_array(local_vals) if nnz else np.zeros((1, 4), dtype=np.uint64)
+    msgs = np.zeros((max(num_var, 1), 3, 4), dtype=np.uint64)
+    chal = np.zeros((max(num_var, 1), 4), dtype=np.uint64)
+    fin_t = np.zeros((2, 4), dtype=np.uint64)
+    fin = np.zeros((1, 4), dtype=np.uint64)
+    check(lib.zk_sumcheck_sparse_dense_prove_sharded(ctx.handle, comm.handle, num_var, nnz, _p(ia), _p(va), _p(local_dense.mont),
+                                                     ZK_MEM_HOST, None, None, transcript.handle, _p(msgs), _p(chal),
+                                                     _p(fin_t), _p(fin)), "zk_sumcheck_sparse_dense_prove_sharded")
+    return ([from_mont_array(msgs[r]) for r in range(num_var)], from_mont_array(chal[:num_var]), from_mont_array(fin_t),
+            from_mont_array(fin)[0])
