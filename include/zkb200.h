@@ -122,6 +122,26 @@ int zk_sumcheck_sparse_dense_prove(zk_ctx* ctx, uint32_t num_var, uint64_t nnz, 
                                    void* fs_user, zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges,
                                    uint64_t* final_table0, uint64_t* final_eval);
 
+/* SparseBoolSumcheckProver::prove, src/crypto/sumcheck/linear_prover.rs:486-656 (header
+ * num_var, num_poly = 3 absorbed by the caller as ::new does, :468-478): proves
+ * sum_x eq(eq_point, x) sum_j weights[j] s_j(x) (s_j(x) - 1) with s_j the 0/1 selection table whose
+ * ones are term j's positions.  positions: the terms' position lists concatenated (any order
+ * inside a term, distinct; n_positions[j] entries for term j).  Host inputs.  Outputs:
+ * round_msgs[num_var][4], challenges[num_var], final_eval. */
+int zk_sumcheck_sparse_bool_prove(zk_ctx* ctx, uint32_t num_var, uint32_t n_terms, const uint64_t* weights,
+                                  const uint64_t* positions, const uint64_t* n_positions, const uint64_t* eq_point,
+                                  zk_fs_round_fn fs, void* fs_user, zk_transcript* tr, uint64_t* round_msgs,
+                                  uint64_t* challenges, uint64_t* final_eval);
+/* GeneralLinearSumcheckProver::prove, linear_prover.rs:229-438: sum_x eq(x) sum_j scalars[j]
+ * prod_i p_ji(x).  num_poly counts eq as one factor (:233), so every term has num_poly - 1 tables;
+ * tables[j * (num_poly - 1) + i] = p_ji, eq = the eq table, all 2^num_var elements in `mem`.
+ * Outputs: round_msgs[num_var][num_poly + 1], challenges, final_tables[n_terms * (num_poly - 1)]
+ * (every table's fully bound value; may be NULL), final_eval. */
+int zk_sumcheck_general_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, uint32_t n_terms, const uint64_t* scalars,
+                              const uint64_t* const* tables, const uint64_t* eq, zk_mem mem, zk_fs_round_fn fs,
+                              void* fs_user, zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges,
+                              uint64_t* final_tables, uint64_t* final_eval);
+
 /* ---- multi-GPU (one process per GPU; no counterpart in the reference, which is single-process) --- */
 /* A communicator over `world` ranks (a power of two, at most 64), bound to NCCL at run time.
  * Rank 0 calls zk_comm_unique_id and the host distributes the 128 bytes to the other ranks. */

@@ -66,6 +66,10 @@ SIGNATURES = {
     "zk_fold_lsb_static": (c_int, [c_uint32, c_void_p, c_uint32, c_void_p, c_void_p, c_void_p]),
     "zk_gen_uniform_fr": (c_int, [c_void_p, c_uint64, c_uint64, c_uint64, c_uint64, c_void_p]),
     "zk_gen_small_fr": (c_int, [c_void_p, c_uint64, c_uint64, c_uint64, c_uint64, c_int, c_void_p]),
+    "zk_sumcheck_sparse_bool_prove": (c_int, [c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "zk_sumcheck_general_prove": (c_int, [c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, POINTER(c_void_p), c_void_p,
+                                          c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "zk_comm_unique_id": (c_int, [c_void_p]),
     "zk_comm_init": (c_int, [c_void_p, c_int, c_int, c_void_p, POINTER(c_void_p)]),
     "zk_comm_free": (None, [c_void_p, c_void_p]),

@@ -225,3 +225,64 @@ class SparseDenseSumcheckProver:
         self.challenges = from_mont_array(chal[:n])
         self.a_arrays = [[v] for v in from_mont_array(fin_t)]
         return SumcheckProof(from_mont_array(fin)[0], [from_mont_array(msgs[r]) for r in range(n)])
+
+
+class SparseBoolSumcheckProver:
+    """src/crypto/sumcheck/linear_prover.rs:455-656."""
+
+    def __init__(self, num_var: int, transcript: Transcript):
+        transcript.append_u64(b"num_var", num_var)
+        transcript.append_u64(b"num_poly", 3)
+        self.num_var = num_var
+        self.challenges = []
+
+    def prove(self, ctx: Context, weights, positions, eq_challenge, transcript: Transcript) -> SumcheckProof:
+        assert len(weights) == len(positions)
+        assert len(eq_challenge) == self.num_var
+        n = self.num_var
+        w = to_mont_array(weights) if len(weights) else np.zeros((1, 4), dtype=np.uint64)
+        flat = np.array([p for pos in positions for p in pos] or [0], dtype=np.uint64)
+        cnt = np.array([len(p) for p in positions] or [0], dtype=np.uint64)
+        pt = to_mont_array(eq_challenge) if n else np.zeros((1, 4), dtype=np.uint64)
+        msgs = np.zeros((max(n, 1), 4, 4), dtype=np.uint64)
+        chal = np.zeros((max(n, 1), 4), dtype=np.uint64)
+        fin = np.zeros((1, 4), dtype=np.uint64)
+        check(lib.zk_sumcheck_sparse_bool_prove(ctx.handle, n, len(weights), _ptr(w), _ptr(flat), _ptr(cnt), _ptr(pt), None,
+                                                None, transcript.handle, _ptr(msgs), _ptr(chal), _ptr(fin)),
+              "zk_sumcheck_sparse_bool_prove")
+        self.challenges = from_mont_array(chal[:n])
+        return SumcheckProof(from_mont_array(fin)[0], [from_mont_array(msgs[r]) for r in range(n)])
+
+
+class GeneralLinearSumcheckProver:
+    """src/crypto/sumcheck/linear_prover.rs:193-438; Instance = (scalars, tables per term, eq)."""
+
+    def __init__(self, num_var: int, num_polys: int, transcript: Transcript):
+        transcript.append_u64(b"num_var", num_var)
+        transcript.append_u64(b"num_poly", num_polys)
+        self.num_var, self.num_poly = num_var, num_polys
+        self.challenges = []
+        self.a_arrays = []
+
+    def prove(self, ctx: Context, instance, transcript: Transcript) -> SumcheckProof:
+        scalars, arrays, eq = instance
+        assert len(arrays) > 0 and len(scalars) > 0, "Polynomials cannot be empty"
+        assert len(arrays[0]) == self.num_poly - 1, "Number of polynomials mismatch"
+        assert len(scalars) == len(arrays), "Number of scalars mismatch"
+        n, nf, nt = self.num_var, self.num_poly - 1, len(arrays)
+        flat = [p for term in arrays for p in term]
+        for i, p in enumerate(flat):
+            assert len(p) == 1 << n, f"Polynomial {i} has incorrect size"
+        ptrs = (c_void_p * max(len(flat), 1))(*[_ptr(p.mont) for p in flat])
+        sc = to_mont_array(scalars)
+        msgs = np.zeros((max(n, 1), self.num_poly + 1, 4), dtype=np.uint64)
+        chal = np.zeros((max(n, 1), 4), dtype=np.uint64)
+        fin_t = np.zeros((max(nt * nf, 1), 4), dtype=np.uint64)
+        fin = np.zeros((1, 4), dtype=np.uint64)
+        check(lib.zk_sumcheck_general_prove(ctx.handle, n, self.num_poly, nt, _ptr(sc), ptrs, _ptr(eq.mont), ZK_MEM_HOST, None,
+                                            None, transcript.handle, _ptr(msgs), _ptr(chal), _ptr(fin_t), _ptr(fin)),
+              "zk_sumcheck_general_prove")
+        self.challenges = from_mont_array(chal[:n])
+        vals = from_mont_array(fin_t)
+        self.a_arrays = [[[vals[j * nf + i]] for i in range(nf)] for j in range(nt)]
+        return SumcheckProof(from_mont_array(fin)[0], [from_mont_array(msgs[r]) for r in range(n)])

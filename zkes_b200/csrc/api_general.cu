@@ -1,0 +1,181 @@
+// C ABI: SparseBoolSumcheckProver and GeneralLinearSumcheckProver (host round loops).
+#include "../../include/zkb200.h"
+#include "ctx.hpp"
+
+#include <algorithm>
+#include <vector>
+
+using namespace zk;
+
+namespace zk {
+int eq_table_device(zk_ctx* ctx, const uint64_t* point_host, uint32_t k, Fr* point_dev, Fr* table);
+}
+
+namespace {
+inline size_t al(size_t x) { return (x + 255) & ~(size_t)255; }
+}
+
+extern "C" {
+
+int zk_sumcheck_sparse_bool_prove(zk_ctx* ctx, uint32_t num_var, uint32_t n_terms, const uint64_t* weights,
+                                  const uint64_t* positions, const uint64_t* n_positions, const uint64_t* eq_point,
+                                  zk_fs_round_fn fs, void* fs_user, zk_transcript* tr, uint64_t* round_msgs,
+                                  uint64_t* challenges, uint64_t* final_eval) {
+  if (!ctx || !final_eval) return fail(ZK_ERR_ARG, "sparse_bool_prove: NULL argument");
+  if (n_terms && (!weights || !n_positions)) return fail(ZK_ERR_ARG, "sparse_bool_prove: NULL input");
+  if (num_var && (!eq_point || !round_msgs || !challenges)) return fail(ZK_ERR_ARG, "sparse_bool_prove: NULL argument");
+  if (!fs && !tr) return fail(ZK_ERR_ARG, "sparse_bool_prove: neither a callback nor a transcript was given");
+  uint32_t term_bits = 0;
+  while ((1ull << term_bits) < n_terms) term_bits++;
+  if (num_var + term_bits > 32) return fail(ZK_ERR_ARG, "sparse_bool_prove: num_var %u with %u terms exceeds the 32-bit key space", num_var, n_terms);
+  // entries: sort every term's positions (linear_prover.rs:497-506), key = term * 2^num_var + position
+  std::vector<uint32_t> keys;
+  uint64_t off = 0;
+  for (uint32_t j = 0; j < n_terms; j++) {
+    if (n_positions[j] && !positions) return fail(ZK_ERR_ARG, "sparse_bool_prove: NULL positions");
+    std::vector<uint64_t> pos(positions + off, positions + off + n_positions[j]);
+    off += n_positions[j];
+    std::sort(pos.begin(), pos.end());
+    for (size_t i = 0; i < pos.size(); i++) {
+      if (pos[i] >> num_var) return fail(ZK_ERR_ARG, "sparse_bool_prove: position out of range in term %u", j);
+      if (i && pos[i] == pos[i - 1]) return fail(ZK_ERR_ARG, "sparse_bool_prove: duplicate position in term %u", j);
+      keys.push_back((uint32_t)(((uint64_t)j << num_var) | pos[i]));
+    }
+  }
+  const uint32_t K = (uint32_t)keys.size();
+  if (keys.size() >> 31) return fail(ZK_ERR_ARG, "sparse_bool_prove: too many entries");
+
+  CtxLock lk(ctx);
+  cudaStream_t s = ctx->stream;
+  const uint64_t size = 1ull << num_var;
+  char* base = nullptr;
+  size_t need = al((size + size / 2 + 8) * sizeof(Fr)) + al((num_var + 8) * sizeof(Fr)) + 2 * (al((K + 1) * 4ull) + al((K + 1) * sizeof(Fr))) +
+                al((K / 256 + 2) * 4ull) + al((n_terms + 1) * sizeof(Fr)) + 4096;
+  int rc = ctx->reserve_work(need, (void**)&base);
+  if (rc) return rc;
+  size_t o = 0;
+  auto take = [&](size_t bytes) { char* p = base + o; o += al(bytes); return p; };
+  Fr* eq0 = (Fr*)take((size + 1) * sizeof(Fr));
+  Fr* eq1 = (Fr*)take((size / 2 + 1) * sizeof(Fr));
+  Fr* pt_dev = (Fr*)take((num_var + 8) * sizeof(Fr));
+  uint32_t* e_key[2] = {(uint32_t*)take((K + 1) * 4ull), (uint32_t*)take((K + 1) * 4ull)};
+  Fr* e_val[2] = {(Fr*)take((K + 1) * sizeof(Fr)), (Fr*)take((K + 1) * sizeof(Fr))};
+  uint32_t* block_counts = (uint32_t*)take((K / 256 + 2) * 4ull);
+  Fr* d_w = (Fr*)take((n_terms + 1) * sizeof(Fr));
+  uint32_t* counts = (uint32_t*)take(256);
+
+  if (K) ZK_CUDA(cudaMemcpyAsync(e_key[0], keys.data(), (size_t)K * 4, cudaMemcpyHostToDevice, s));
+  if (n_terms) ZK_CUDA(cudaMemcpyAsync(d_w, weights, (size_t)n_terms * sizeof(Fr), cudaMemcpyHostToDevice, s));
+  ZK_CUDA(cudaMemsetAsync(counts, 0, 256, s));
+  ZK_CUDA(cudaMemcpyAsync(counts, &K, 4, cudaMemcpyHostToDevice, s));
+  if (K) {
+    launch_fill_ones(e_val[0], K, ctx->sm_count, s);
+    ctx->launches++;
+  }
+  // dense eq(eq_challenge, .) over the full hypercube (:509)
+  rc = eq_table_device(ctx, eq_point, num_var, pt_dev, eq0);
+  if (rc) return rc;
+  ZK_CUDA(cudaStreamSynchronize(s));  // keys / weights host buffers may go out of scope after this
+
+  const Fr* eq_cur = eq0;
+  int e = 0;
+  uint32_t k_upper = K;
+  Fr challenge = Fr::zero();
+  for (uint32_t round = 0; round < num_var; round++) {
+    const uint32_t vars_left = num_var - round;
+    const uint64_t S = 1ull << vars_left;
+    launch_sbool_msg(e_key[e], e_val[e], counts + e, k_upper, eq_cur, d_w, vars_left, ctx->rs, s);
+    ctx->launches++;
+    rc = fs_round(ctx, nullptr, 4, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
+    if (rc) return rc;
+    Fr* eq_next = (round & 1) ? eq0 : eq1;  // eq0 holds 2^n, eq1 2^(n-1); later rounds fit either
+    launch_fold(eq_cur, eq_next, challenge, S / 2, ctx->rs.max_blocks, s);
+    eq_cur = eq_next;
+    ctx->launches += 1 + launch_sparse_fold(e_key[e], e_val[e], counts + e, k_upper, challenge, block_counts, e_key[e ^ 1],
+                                            e_val[e ^ 1], counts + (e ^ 1), s);
+    e ^= 1;
+  }
+  launch_sbool_final(e_key[e], e_val[e], counts + e, eq_cur, d_w, n_terms, ctx->final_out, s);
+  ctx->launches++;
+  ZK_CUDA(cudaGetLastError());
+  ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->final_out, sizeof(Fr), cudaMemcpyDeviceToHost, s));
+  ZK_CUDA(cudaStreamSynchronize(s));
+  fr_store(final_eval, *reinterpret_cast<const Fr*>(ctx->host_small));
+  return ZK_OK;
+}
+
+int zk_sumcheck_general_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, uint32_t n_terms, const uint64_t* scalars,
+                              const uint64_t* const* tables, const uint64_t* eq, zk_mem mem, zk_fs_round_fn fs,
+                              void* fs_user, zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges,
+                              uint64_t* final_tables, uint64_t* final_eval) {
+  if (!ctx || !final_eval) return fail(ZK_ERR_ARG, "general_prove: NULL argument");
+  if (n_terms == 0 || !scalars || !tables || !eq) return fail(ZK_ERR_ARG, "Polynomials cannot be empty");
+  if (num_poly < 1 || num_poly > kMaxPolys + 1) return fail(ZK_ERR_ARG, "general_prove: num_poly %u out of range", num_poly);
+  if (num_var > 34) return fail(ZK_ERR_ARG, "general_prove: num_var %u too large", num_var);
+  if (num_var && (!round_msgs || !challenges)) return fail(ZK_ERR_ARG, "general_prove: NULL output");
+  if (!fs && !tr) return fail(ZK_ERR_ARG, "general_prove: neither a callback nor a transcript was given");
+  const uint32_t nf = num_poly - 1;  // factors per term; eq is the remaining one (linear_prover.rs:233)
+  const uint32_t nt = n_terms * nf;
+  if (nt > 256) return fail(ZK_ERR_ARG, "general_prove: at most 256 tables");
+  for (uint32_t i = 0; i < nt; i++)
+    if (!tables[i]) return fail(ZK_ERR_ARG, "Polynomial %u has incorrect size", i);
+
+  CtxLock lk(ctx);
+  cudaStream_t s = ctx->stream;
+  const uint64_t size = 1ull << num_var;
+  const uint64_t all = (uint64_t)nt + 1;  // tables + eq
+  const uint64_t in_elems = mem == ZK_MEM_HOST ? size * all : 0;
+  char* base = nullptr;
+  size_t need = al(in_elems * sizeof(Fr)) + al(all * (size / 2 + 1) * sizeof(Fr)) + al(all * (size / 4 + 1) * sizeof(Fr)) +
+                al((n_terms + 1) * sizeof(Fr)) + al((nt + 1) * sizeof(Fr)) + 2 * al((nt + 1) * 8) + 4096;
+  int rc = ctx->reserve_work(need, (void**)&base);
+  if (rc) return rc;
+  size_t o = 0;
+  auto take = [&](size_t bytes) { char* p = base + o; o += al(bytes); return p; };
+  Fr* in_copy = (Fr*)take(in_elems * sizeof(Fr));
+  Fr* ping = (Fr*)take(all * (size / 2 + 1) * sizeof(Fr));
+  Fr* pong = (Fr*)take(all * (size / 4 + 1) * sizeof(Fr));
+  Fr* d_scalars = (Fr*)take((n_terms + 1) * sizeof(Fr));
+  Fr* d_vals = (Fr*)take((nt + 1) * sizeof(Fr));
+  const Fr** d_ptrs[2] = {(const Fr**)take((nt + 1) * 8), (const Fr**)take((nt + 1) * 8)};
+  std::vector<const Fr*> cur(all);
+  for (uint64_t i = 0; i < all; i++) {
+    const uint64_t* src = i < nt ? tables[i] : eq;
+    if (mem == ZK_MEM_HOST) {
+      ZK_CUDA(cudaMemcpyAsync(in_copy + i * size, src, size * sizeof(Fr), cudaMemcpyHostToDevice, s));
+      cur[i] = in_copy + i * size;
+    } else {
+      cur[i] = reinterpret_cast<const Fr*>(src);
+    }
+  }
+  ZK_CUDA(cudaMemcpyAsync(d_scalars, scalars, (size_t)n_terms * sizeof(Fr), cudaMemcpyHostToDevice, s));
+  Fr challenge = Fr::zero();
+  for (uint32_t round = 0; round < num_var; round++) {
+    const uint64_t S = size >> round;
+    const Fr** dp = d_ptrs[round & 1];
+    ZK_CUDA(cudaMemcpyAsync(dp, cur.data(), nt * 8, cudaMemcpyHostToDevice, s));
+    launch_general_msg(dp, d_scalars, cur[nt], n_terms, nf, S / 2, ctx->rs, s);
+    ctx->launches++;
+    rc = fs_round(ctx, nullptr, (int)num_poly + 1, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
+    if (rc) return rc;
+    Fr* dst = (round & 1) ? pong : ping;
+    const uint64_t stride = (round & 1) ? size / 4 + 1 : size / 2 + 1;
+    for (uint64_t i = 0; i < all; i++) {
+      launch_fold(cur[i], dst + i * stride, challenge, S / 2, ctx->rs.max_blocks, s);
+      cur[i] = dst + i * stride;
+      ctx->launches++;
+    }
+  }
+  const Fr** dp = d_ptrs[num_var & 1];
+  ZK_CUDA(cudaMemcpyAsync(dp, cur.data(), nt * 8, cudaMemcpyHostToDevice, s));
+  launch_general_final(dp, d_scalars, cur[nt], n_terms, nf, d_vals, ctx->final_out, s);
+  ctx->launches++;
+  ZK_CUDA(cudaGetLastError());
+  ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->final_out, sizeof(Fr), cudaMemcpyDeviceToHost, s));
+  if (final_tables) ZK_CUDA(cudaMemcpyAsync(final_tables, d_vals, (size_t)nt * sizeof(Fr), cudaMemcpyDeviceToHost, s));
+  ZK_CUDA(cudaStreamSynchronize(s));
+  fr_store(final_eval, *reinterpret_cast<const Fr*>(ctx->host_small));
+  return ZK_OK;
+}
+
+}  // extern "C"

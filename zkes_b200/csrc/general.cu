@@ -1,0 +1,180 @@
+// The two remaining provers of src/crypto/sumcheck/linear_prover.rs:
+//   SparseBoolSumcheckProver (:455-656)   sum_x eq(r,x) sum_j w_j s_j(x)(s_j(x) - 1), s_j sparse
+//   GeneralLinearSumcheckProver (:193-438) sum_x eq(x) sum_j a_j prod_i p_ji(x)
+// Both reuse the plain fold kernel for their dense tables; the sparse one reuses the entry fold
+// and compaction of sparse.cu with keys = term * 2^(remaining variables) + index, so entries of
+// different terms never pair up.
+#include "internal.hpp"
+#include "reduce.cuh"
+
+namespace zk {
+namespace {
+
+constexpr int kGThreads = 256;
+
+__device__ __forceinline__ Fr g_ld(const Fr* p) {
+  const uint4 lo = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint4 hi = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+  return fr_from_chunks(lo, hi);
+}
+
+// T(c), c = 0..3, over the live entries (compute_round_message, :529-591).
+__global__ void __launch_bounds__(kGThreads) k_sbool_msg(const uint32_t* __restrict__ keys, const Fr* __restrict__ val,
+                                                         const uint32_t* __restrict__ count, const Fr* __restrict__ eq,
+                                                         const Fr* __restrict__ weights, uint32_t vars_left,
+                                                         Fr* partials, unsigned int* counter, Fr* msg) {
+  const uint32_t n = *count;
+  const uint32_t mask = (vars_left >= 32) ? 0xffffffffu : ((1u << vars_left) - 1u);
+  const Fr one = Fr::one();
+  Fr s[4] = {Fr::zero(), Fr::zero(), Fr::zero(), Fr::zero()};
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const uint32_t key = keys[i];
+    const bool lead = (key & 1u) == 0 || i == 0 || keys[i - 1] != key - 1;
+    if (!lead) continue;
+    Fr v0 = Fr::zero(), v1 = Fr::zero();
+    if ((key & 1u) == 0) {
+      v0 = g_ld(val + i);
+      if (i + 1 < n && keys[i + 1] == key + 1) v1 = g_ld(val + i + 1);
+    } else {
+      v1 = g_ld(val + i);
+    }
+    const uint32_t pos = key & mask;
+    const Fr w = g_ld(weights + (vars_left >= 32 ? 0 : (key >> vars_left)));
+    const Fr e0 = g_ld(eq + (pos & ~1u)), e1 = g_ld(eq + (pos | 1u));
+    const Fr dv = sub(v1, v0), de = sub(e1, e0);
+    Fr aux = v0, e = e0;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      // w * aux * (aux - 1) * eq at evaluation point c
+      const Fr t = mul(mul(w, aux), mul(sub(aux, one), e));
+      s[c] = add(s[c], t);
+      aux = add(aux, dv);
+      e = add(e, de);
+    }
+  }
+  grid_sum<4, kGThreads / 32>(s, partials, counter, msg);
+}
+
+// final_evaluation (:644-655): eq[0] * sum_j w_j v_j (v_j - 1), v_j = the entry with key j.
+__global__ void k_sbool_final(const uint32_t* keys, const Fr* val, const uint32_t* count, const Fr* eq,
+                              const Fr* weights, uint32_t n_terms, Fr* out) {
+  if (threadIdx.x || blockIdx.x) return;
+  const uint32_t n = *count;
+  const Fr one = Fr::one();
+  Fr inner = Fr::zero();
+  for (uint32_t i = 0; i < n; i++) {
+    const uint32_t j = keys[i];
+    if (j >= n_terms) continue;
+    const Fr v = val[i];
+    inner = add(inner, mul(weights[j], mul(v, sub(v, one))));
+  }
+  out[0] = mul(eq[0], inner);
+}
+
+__global__ void k_fill_ones(Fr* out, uint32_t n) {
+  const Fr one = Fr::one();
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) out[i] = one;
+}
+
+struct GeneralParams {
+  const Fr* const* tables;  // device array: n_terms * n_factors pointers
+  const Fr* scalars;        // n_terms
+  const Fr* eq;
+  uint32_t n_terms, n_factors;
+  uint64_t pairs;
+  Fr* partials;
+  unsigned int* counter;
+  Fr* msg;
+};
+
+// s(c) = sum_y eq_c(y) sum_j a_j prod_i p_ji,c(y) for c = 0 .. n_factors + 1 (compute_g_value, :298-357).
+__global__ void __launch_bounds__(kGThreads) k_general_msg(const GeneralParams p) {
+  constexpr int kMaxEval = kMaxPolys + 2;
+  Fr s[kMaxEval];
+#pragma unroll
+  for (int c = 0; c < kMaxEval; c++) s[c] = Fr::zero();
+  const int n_eval = (int)p.n_factors + 2;
+  for (uint64_t y = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; y < p.pairs; y += (uint64_t)gridDim.x * blockDim.x) {
+    const Fr e0 = g_ld(p.eq + 2 * y), e1 = g_ld(p.eq + 2 * y + 1);
+    const Fr de = sub(e1, e0);
+    Fr inner[kMaxEval];
+#pragma unroll
+    for (int c = 0; c < kMaxEval; c++) inner[c] = Fr::zero();
+    for (uint32_t j = 0; j < p.n_terms; j++) {
+      Fr prod[kMaxEval];
+      const Fr a = g_ld(p.scalars + j);
+#pragma unroll
+      for (int c = 0; c < kMaxEval; c++) prod[c] = a;
+      for (uint32_t i = 0; i < p.n_factors; i++) {
+        const Fr* t = p.tables[j * p.n_factors + i];
+        const Fr v0 = g_ld(t + 2 * y), v1 = g_ld(t + 2 * y + 1);
+        const Fr dv = sub(v1, v0);
+        Fr v = v0;
+#pragma unroll
+        for (int c = 0; c < kMaxEval; c++) {
+          if (c < n_eval) prod[c] = mul(prod[c], v);
+          v = add(v, dv);
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < kMaxEval; c++) inner[c] = add(inner[c], prod[c]);
+    }
+    Fr e = e0;
+#pragma unroll
+    for (int c = 0; c < kMaxEval; c++) {
+      if (c < n_eval) s[c] = add(s[c], mul(inner[c], e));
+      e = add(e, de);
+    }
+  }
+  grid_sum<kMaxEval, kGThreads / 32>(s, p.partials, p.counter, p.msg);
+}
+
+// final_evaluation (:420-437): eq[0] * sum_j a_j prod_i p_ji[0]; also writes every table's value.
+__global__ void k_general_final(const Fr* const* tables, const Fr* scalars, const Fr* eq, uint32_t n_terms,
+                                uint32_t n_factors, Fr* table_vals, Fr* out) {
+  if (threadIdx.x || blockIdx.x) return;
+  Fr inner = Fr::zero();
+  for (uint32_t j = 0; j < n_terms; j++) {
+    Fr prod = scalars[j];
+    for (uint32_t i = 0; i < n_factors; i++) {
+      const Fr v = tables[j * n_factors + i][0];
+      if (table_vals) table_vals[j * n_factors + i] = v;
+      prod = mul(prod, v);
+    }
+    inner = add(inner, prod);
+  }
+  out[0] = mul(inner, eq[0]);
+}
+
+inline int g_blocks(uint64_t n, const RoundScratch& sc) {
+  uint64_t b = (n + kGThreads - 1) / kGThreads;
+  const uint64_t cap = (uint64_t)sc.sm_count * 2 < (uint64_t)sc.max_blocks ? sc.sm_count * 2 : sc.max_blocks;
+  if (b < 1) b = 1;
+  if (b > cap) b = cap;
+  return (int)b;
+}
+
+}  // namespace
+
+void launch_sbool_msg(const uint32_t* keys, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* eq,
+                      const Fr* weights, uint32_t vars_left, const RoundScratch& sc, cudaStream_t s) {
+  k_sbool_msg<<<g_blocks(upper, sc), kGThreads, 0, s>>>(keys, val, count, eq, weights, vars_left, sc.partials, sc.counter, sc.msg);
+}
+void launch_sbool_final(const uint32_t* keys, const Fr* val, const uint32_t* count, const Fr* eq, const Fr* weights,
+                        uint32_t n_terms, Fr* out, cudaStream_t s) {
+  k_sbool_final<<<1, 32, 0, s>>>(keys, val, count, eq, weights, n_terms, out);
+}
+void launch_fill_ones(Fr* out, uint32_t n, int sm_count, cudaStream_t s) {
+  k_fill_ones<<<sm_count * 2, 256, 0, s>>>(out, n);
+}
+void launch_general_msg(const Fr* const* tables_dev, const Fr* scalars, const Fr* eq, uint32_t n_terms, uint32_t n_factors,
+                        uint64_t pairs, const RoundScratch& sc, cudaStream_t s) {
+  GeneralParams p{tables_dev, scalars, eq, n_terms, n_factors, pairs, sc.partials, sc.counter, sc.msg};
+  k_general_msg<<<g_blocks(pairs, sc), kGThreads, 0, s>>>(p);
+}
+void launch_general_final(const Fr* const* tables_dev, const Fr* scalars, const Fr* eq, uint32_t n_terms,
+                          uint32_t n_factors, Fr* table_vals, Fr* out, cudaStream_t s) {
+  k_general_final<<<1, 32, 0, s>>>(tables_dev, scalars, eq, n_terms, n_factors, table_vals, out);
+}
+
+}  // namespace zk

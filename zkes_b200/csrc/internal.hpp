@@ -30,6 +30,17 @@ uint32_t from_right_splits(uint64_t lo_n, uint64_t hi_n, int sm_count);
 int launch_from_right(const Fr* f, const Fr* eq, uint64_t lo_n, uint64_t hi_n, Fr* partial, Fr* out, int sm_count,
                       cudaStream_t s);
 
+// general.cu
+void launch_sbool_msg(const uint32_t* keys, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* eq,
+                      const Fr* weights, uint32_t vars_left, const RoundScratch& sc, cudaStream_t s);
+void launch_sbool_final(const uint32_t* keys, const Fr* val, const uint32_t* count, const Fr* eq, const Fr* weights,
+                        uint32_t n_terms, Fr* out, cudaStream_t s);
+void launch_fill_ones(Fr* out, uint32_t n, int sm_count, cudaStream_t s);
+void launch_general_msg(const Fr* const* tables_dev, const Fr* scalars, const Fr* eq, uint32_t n_terms, uint32_t n_factors,
+                        uint64_t pairs, const RoundScratch& sc, cudaStream_t s);
+void launch_general_final(const Fr* const* tables_dev, const Fr* scalars, const Fr* eq, uint32_t n_terms,
+                          uint32_t n_factors, Fr* table_vals, Fr* out, cudaStream_t s);
+
 // sparse.cu
 void launch_sparse_msg(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
                        const RoundScratch& sc, cudaStream_t s);
