@@ -23,6 +23,15 @@ template <class P> static void ld(Fp<P>& x, const uint32_t* p) { memcpy(x.v, p, 
   extern "C" void zkh_##name##_mul_fixed(const uint32_t* x, const uint32_t* d, uint32_t* r) {  \
     Fp<P> a, b; ld(a, x); ld(b, d); FixedMul<P> t = make_fixed_mul(a);                        \
     Fp<P> z = mul_fixed(t, b); memcpy(r, z.v, 32); }                                         \
+  /* x0*(a1-a0) + x1*(a2-a0) + x2*((a3-a2)-(a1-a0)) through mul_fixed3 with lazy differences */ \
+  extern "C" void zkh_##name##_fold2(const uint32_t* x, const uint32_t* a, uint32_t* r) {      \
+    Fp<P> x0, x1, t[4]; ld(x0, x); ld(x1, x + 8); for (int i = 0; i < 4; i++) ld(t[i], a + 8 * i); \
+    FixedMul<P> f0 = make_fixed_mul(x0), f1 = make_fixed_mul(x1), f01 = make_fixed_mul(mul(x0, x1)); \
+    uint32_t d01[8], d02[8], d23[8], dd[8], m2[8], tmp[8];                                    \
+    sub_lazy<P>(d01, t[1], t[0]); sub_lazy<P>(d02, t[2], t[0]); sub_lazy<P>(d23, t[3], t[2]); \
+    for (int i = 0; i < 8; i++) m2[i] = P::mod(i);                                            \
+    add8(tmp, d23, m2); add8(tmp, tmp, m2); sub8(dd, tmp, d01);                               \
+    Fp<P> z = add(t[0], mul_fixed3(f0, d01, f1, d02, f01, dd)); memcpy(r, z.v, 32); }         \
   /* sum of n products through the lazy accumulator, trimmed every kLazyProducts */         \
   extern "C" void zkh_##name##_dot(const uint32_t* a, const uint32_t* b, int n, uint32_t* r) { \
     Wide acc; memset(&acc, 0, sizeof acc); int pending = 0;                                  \

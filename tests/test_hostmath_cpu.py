@@ -59,6 +59,23 @@ def test_field_ops(hm, name, p):
 
 
 @pytest.mark.parametrize("name,p", [("fr", o.R_MOD), ("fq", o.Q_MOD)])
+def test_double_fold_formula(hm, name, p):
+    """t0 + r0 d01 + r1 (t2 - t0) + r0 r1 (d23 - d01) equals two successive folds."""
+    rnd = random.Random(12)
+    out = (ctypes.c_uint32 * 8)()
+    edge = [0, 1, p - 1, p - 2]
+    for it in range(500):
+        r0, r1 = rnd.randrange(p), rnd.randrange(p)
+        t = [rnd.choice(edge) if rnd.random() < 0.3 else rnd.randrange(p) for _ in range(4)]
+        xs = (ctypes.c_uint32 * 16)(*[((v * R % p) >> (32 * i)) & 0xFFFFFFFF for v in (r0, r1) for i in range(8)])
+        ts = (ctypes.c_uint32 * 32)(*[((v * R % p) >> (32 * i)) & 0xFFFFFFFF for v in t for i in range(8)])
+        getattr(hm, f"zkh_{name}_fold2")(xs, ts, out)
+        a = (t[0] + r0 * (t[1] - t[0])) % p
+        b = (t[2] + r0 * (t[3] - t[2])) % p
+        assert val(out) == ((a + r1 * (b - a)) % p) * R % p
+
+
+@pytest.mark.parametrize("name,p", [("fr", o.R_MOD), ("fq", o.Q_MOD)])
 def test_lazy_dot_product(hm, name, p):
     rnd = random.Random(6)
     out = (ctypes.c_uint32 * 8)()

@@ -3,6 +3,7 @@
 #include "../../include/zkb200.h"
 #include "ctx.hpp"
 
+#include <chrono>
 #include <cstdio>
 #include <string>
 
@@ -29,12 +30,29 @@ int fs_round(zk_ctx* ctx, zk_comm* comm, int n_msgs, uint32_t round, zk_fs_round
              uint64_t* round_msgs, uint64_t* challenges, Fr* challenge) {
   ZK_CUDA(cudaGetLastError());
   if (comm) {  // every rank holds a partial message: sum them so all ranks absorb the same scalars
-    int rc = comm_sum_fr(ctx, comm, ctx->rs.msg, n_msgs);
+    int rc = comm_sum_fr(ctx, comm, ctx->rs.sink.msg, n_msgs);
     if (rc) return rc;
   }
-  ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->rs.msg, n_msgs * sizeof(Fr), cudaMemcpyDeviceToHost, ctx->stream));
-  ZK_CUDA(cudaStreamSynchronize(ctx->stream));
-  const Fr* msg = reinterpret_cast<const Fr*>(ctx->host_small);
+  // The kernel that completes the message publishes it to the host-mapped mailbox and then
+  // writes this launch's sequence number; poll for it instead of synchronising the stream.
+  {
+    volatile unsigned int* flag =
+        reinterpret_cast<volatile unsigned int*>(reinterpret_cast<char*>(ctx->mailbox) + 16 * sizeof(Fr));
+    const unsigned int want = ctx->rs.sink.seq;
+    const auto t0 = std::chrono::steady_clock::now();
+    uint64_t spins = 0;
+    while (*flag != want) {
+      if ((++spins & 0x3fff) == 0) {
+        cudaError_t e = cudaStreamQuery(ctx->stream);
+        if (e != cudaSuccess && e != cudaErrorNotReady) return fail(ZK_ERR_CUDA, "round kernel failed: %s", cudaGetErrorString(e));
+        const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+        if (e == cudaSuccess && *flag != want && waited > 1.0)
+          return fail(ZK_ERR_TIMEOUT, "round %u: the stream drained without publishing the message", round);
+        if (waited > 60.0) return fail(ZK_ERR_TIMEOUT, "round %u: no message after 60 s", round);
+      }
+    }
+  }
+  const Fr* msg = reinterpret_cast<const Fr*>(ctx->mailbox);
   uint64_t* out_msg = round_msgs + (uint64_t)round * n_msgs * 4;
   for (int c = 0; c < n_msgs; c++) fr_store(out_msg + 4 * c, msg[c]);
   if (fs) {
@@ -183,13 +201,14 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
   const uint64_t size = 1ull << rounds;
   for (uint32_t round = 0; round < rounds; round++) {
     const uint64_t pairs = size >> (round + 1);
+    const RoundScratch sc = ctx->next_msg_scratch(comm != nullptr);
     if (round == 0) {
       ctx->prof_begin(ZK_PROF_ROUND, 64.0 * L * pairs);
-      launch_round(L, false, cur, nullptr, *challenge, pairs, ctx->rs, ctx->stream);
+      launch_round(L, false, cur, nullptr, *challenge, pairs, sc, ctx->stream);
     } else {
       Fr** dst = (round & 1) ? ping : pong;
       ctx->prof_begin(ZK_PROF_ROUND, 192.0 * L * pairs);
-      launch_round(L, true, cur, dst, *challenge, pairs, ctx->rs, ctx->stream);
+      launch_round(L, true, cur, dst, *challenge, pairs, sc, ctx->stream);
       for (int i = 0; i < L; i++) cur[i] = dst[i];
     }
     ctx->prof_end();

@@ -84,7 +84,7 @@ int zk_sumcheck_sparse_bool_prove(zk_ctx* ctx, uint32_t num_var, uint32_t n_term
   for (uint32_t round = 0; round < num_var; round++) {
     const uint32_t vars_left = num_var - round;
     const uint64_t S = 1ull << vars_left;
-    launch_sbool_msg(e_key[e], e_val[e], counts + e, k_upper, eq_cur, d_w, vars_left, ctx->rs, s);
+    launch_sbool_msg(e_key[e], e_val[e], counts + e, k_upper, eq_cur, d_w, vars_left, ctx->next_msg_scratch(false), s);
     ctx->launches++;
     rc = fs_round(ctx, nullptr, 4, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
     if (rc) return rc;
@@ -154,7 +154,7 @@ int zk_sumcheck_general_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, 
     const uint64_t S = size >> round;
     const Fr** dp = d_ptrs[round & 1];
     ZK_CUDA(cudaMemcpyAsync(dp, cur.data(), nt * 8, cudaMemcpyHostToDevice, s));
-    launch_general_msg(dp, d_scalars, cur[nt], n_terms, nf, S / 2, ctx->rs, s);
+    launch_general_msg(dp, d_scalars, cur[nt], n_terms, nf, S / 2, ctx->next_msg_scratch(false), s);
     ctx->launches++;
     rc = fs_round(ctx, nullptr, (int)num_poly + 1, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
     if (rc) return rc;

@@ -76,11 +76,11 @@ int msm_entry(zk_ctx* ctx, const uint64_t* bases, zk_mem bases_mem, uint64_t n_b
     uint64_t* i64 = (uint64_t*)take(n * 8);
     d_gather = (uint32_t*)take(n * 4);
     ZK_CUDA(cudaMemcpyAsync(i64, indices, n * 8, cudaMemcpyDefault, s));
-    ZK_CUDA(cudaMemsetAsync(ctx->rs.counter + 16, 0, 4, s));
-    launch_narrow_idx(i64, (uint32_t)n, d_gather, ctx->rs.counter + 16, ctx->sm_count, s);
-    launch_check_bound(d_gather, (uint32_t)n, n_bases, ctx->rs.counter + 16, ctx->sm_count, s);
+    ZK_CUDA(cudaMemsetAsync(ctx->rs.sink.counter + 16, 0, 4, s));
+    launch_narrow_idx(i64, (uint32_t)n, d_gather, ctx->rs.sink.counter + 16, ctx->sm_count, s);
+    launch_check_bound(d_gather, (uint32_t)n, n_bases, ctx->rs.sink.counter + 16, ctx->sm_count, s);
     ctx->launches += 2;
-    ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->rs.counter + 16, 4, cudaMemcpyDeviceToHost, s));
+    ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->rs.sink.counter + 16, 4, cudaMemcpyDeviceToHost, s));
     ZK_CUDA(cudaStreamSynchronize(s));
     uint32_t bad = 0;
     memcpy(&bad, ctx->host_small, 4);

@@ -51,12 +51,20 @@ int load_nccl() {
 }
 
 // out[c] = sum over ranks of gathered[rank * n_vals + c]
-__global__ void k_sum_ranks(const Fr* __restrict__ gathered, int world, int n_vals, Fr* out) {
+// The sum is the complete round message: it is also published to the polling host.
+__global__ void k_sum_ranks(const Fr* __restrict__ gathered, int world, int n_vals, Fr* out, const MsgSink sink) {
   const int c = threadIdx.x;
-  if (c >= n_vals) return;
-  Fr s = gathered[c];
-  for (int r = 1; r < world; r++) s = add(s, gathered[r * n_vals + c]);
-  out[c] = s;
+  if (c < n_vals) {
+    Fr s = gathered[c];
+    for (int r = 1; r < world; r++) s = add(s, gathered[r * n_vals + c]);
+    out[c] = s;
+    if (sink.pub_flag) st_fr_sys(sink.pub_msg + c, s);
+  }
+  if (sink.pub_flag) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(sink.pub_flag) = sink.seq;
+  }
 }
 
 }  // namespace
@@ -76,7 +84,7 @@ int comm_sum_fr(zk_ctx* ctx, zk_comm* c, Fr* vals, int n_vals) {
   if (!c || c->world == 1) return ZK_OK;
   int rc = g_nccl.all_gather(vals, c->gather_buf, (size_t)n_vals * sizeof(Fr), 1 /*ncclUint8*/, c->comm, ctx->stream);
   if (rc != 0) return fail(ZK_ERR_COMM, "ncclAllGather: %s", g_nccl.errstr ? g_nccl.errstr(rc) : "error");
-  k_sum_ranks<<<1, 32, 0, ctx->stream>>>(c->gather_buf, c->world, n_vals, vals);
+  k_sum_ranks<<<1, 32, 0, ctx->stream>>>(c->gather_buf, c->world, n_vals, vals, ctx->rs.sink);
   ctx->launches++;
   return ZK_OK;
 }

@@ -8,10 +8,18 @@ int zk_ctx::setup() {
   ZK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
   rs.max_blocks = sm_count * 8;
   rs.sm_count = sm_count;
-  ZK_CUDA(cudaMalloc(&rs.partials, sizeof(Fr) * (size_t)rs.max_blocks * (kMaxPolys + 1)));
-  ZK_CUDA(cudaMalloc(&rs.counter, 256));
-  ZK_CUDA(cudaMemsetAsync(rs.counter, 0, 256, stream));
-  ZK_CUDA(cudaMalloc(&rs.msg, sizeof(Fr) * 16));
+  ZK_CUDA(cudaMalloc(&rs.sink.partials, sizeof(Fr) * (size_t)rs.max_blocks * (kMaxPolys + 1)));
+  ZK_CUDA(cudaMalloc(&rs.sink.counter, 256));
+  ZK_CUDA(cudaMemsetAsync(rs.sink.counter, 0, 256, stream));
+  ZK_CUDA(cudaMalloc(&rs.sink.msg, sizeof(Fr) * 16));
+  // host-mapped mailbox: 16 message elements, then the sequence word
+  ZK_CUDA(cudaHostAlloc(&mailbox, 1024, cudaHostAllocMapped));
+  memset(mailbox, 0, 1024);
+  void* dev_view = nullptr;
+  ZK_CUDA(cudaHostGetDevicePointer(&dev_view, mailbox, 0));
+  rs.sink.pub_msg = reinterpret_cast<Fr*>(dev_view);
+  rs.sink.pub_flag = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(dev_view) + 16 * sizeof(Fr));
+  rs.sink.seq = 0;
   ZK_CUDA(cudaMalloc(&final_out, sizeof(Fr) * 16));
   ZK_CUDA(cudaMalloc(&tail_buf, sizeof(Fr) * 64 * kMaxPolys * 4));
   ZK_CUDA(cudaHostAlloc(&host_small, 4096, cudaHostAllocDefault));
@@ -22,9 +30,10 @@ int zk_ctx::setup() {
 void zk_ctx::teardown() {
   cudaSetDevice(device);
   if (stream) cudaStreamSynchronize(stream);
-  cudaFree(rs.partials);
-  cudaFree(rs.counter);
-  cudaFree(rs.msg);
+  cudaFree(rs.sink.partials);
+  cudaFree(rs.sink.counter);
+  cudaFree(rs.sink.msg);
+  if (mailbox) cudaFreeHost(mailbox);
   cudaFree(final_out);
   cudaFree(tail_buf);
   cudaFree(work);

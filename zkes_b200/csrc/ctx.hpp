@@ -60,6 +60,7 @@ struct zk_ctx {
   zk::Fr* final_out = nullptr;   // kMaxPolys + 1 elements
   zk::Fr* tail_buf = nullptr;    // sharded proves: gathered values and the last log2(world) rounds' tables
   void* host_small = nullptr;    // pinned, 4 KiB: round messages and other tiny read-backs
+  void* mailbox = nullptr;       // pinned + mapped: message kernels publish here, the host polls
   void* work = nullptr;          // grow-only device scratch (copies of caller data, round buffers)
   size_t work_bytes = 0;
   void* aux = nullptr;           // second grow-only scratch (MSM sort and bucket storage)
@@ -84,6 +85,14 @@ struct zk_ctx {
   int setup();
   void teardown();
   // Make the scratch at least `bytes` large and return it (contents undefined).
+  // Scratch for the next message-producing launch: a fresh sequence number; with `partial`
+  // (multi-GPU: the launch yields only this rank's share) the kernel does not publish.
+  zk::RoundScratch next_msg_scratch(bool partial) {
+    rs.sink.seq++;
+    zk::RoundScratch sc = rs;
+    if (partial) sc.sink.pub_flag = nullptr;
+    return sc;
+  }
   int reserve_work(size_t bytes, void** out);
   int reserve_aux(size_t bytes, void** out);
 };

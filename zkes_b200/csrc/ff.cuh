@@ -446,6 +446,62 @@ ZK_HD Fp<P> mul_fixed(const FixedMul<P>& t, const Fp<P>& d) {
   return r;
 }
 
+// t0 * d0 + t1 * d1 + t2 * d2 for three launch-constant multipliers in one accumulation: the
+// three 291-bit row sums share the accumulators and one pair of Montgomery rounds, 210
+// multiply-adds in all.  The d's may be any 256-bit values (unreduced differences).
+template <class P>
+ZK_HD Fp<P> mul_fixed3(const FixedMul<P>& t0, const uint32_t* d0, const FixedMul<P>& t1, const uint32_t* d1,
+                       const FixedMul<P>& t2, const uint32_t* d2) {
+  uint32_t E[9], O[9];
+#pragma unroll
+  for (int i = 0; i < 9; i++) E[i] = O[i] = 0;
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    E[8] += madwide4_c(E, t0.c[j][0], t0.c[j][2], t0.c[j][4], t0.c[j][6], d0[j]);
+    O[8] += madwide4_c(O, t0.c[j][1], t0.c[j][3], t0.c[j][5], t0.c[j][7], d0[j]);
+    E[8] += madwide4_c(E, t1.c[j][0], t1.c[j][2], t1.c[j][4], t1.c[j][6], d1[j]);
+    O[8] += madwide4_c(O, t1.c[j][1], t1.c[j][3], t1.c[j][5], t1.c[j][7], d1[j]);
+    E[8] += madwide4_c(E, t2.c[j][0], t2.c[j][2], t2.c[j][4], t2.c[j][6], d2[j]);
+    O[8] += madwide4_c(O, t2.c[j][1], t2.c[j][3], t2.c[j][5], t2.c[j][7], d2[j]);
+  }
+#pragma unroll
+  for (int round = 0; round < 2; round++) {
+    const uint32_t m = E[0] * P::inv;
+    E[8] += madwide4_c(E, P::mod(0), P::mod(2), P::mod(4), P::mod(6), m);
+    O[8] += madwide4_c(O, P::mod(1), P::mod(3), P::mod(5), P::mod(7), m);
+    add_limb9(O, E[1]);
+    uint32_t T[9];
+#pragma unroll
+    for (int k = 0; k < 7; k++) T[k] = E[k + 2];
+    T[7] = 0;
+    T[8] = 0;
+#pragma unroll
+    for (int k = 0; k < 9; k++) {
+      E[k] = O[k];
+      O[k] = T[k];
+    }
+  }
+  // value = E + 2^32 * O < 3 * 2^225 + p < 2p
+  Fp<P> r;
+  uint32_t S[8];
+  S[0] = 0;
+#pragma unroll
+  for (int k = 1; k < 8; k++) S[k] = O[k - 1];
+  (void)add8(r.v, E, S);
+  final_sub<P>(r.v, 0);
+  return r;
+}
+
+// a + p - b without the conditional correction: any value congruent to a - b below 2p.
+template <class P>
+ZK_HD void sub_lazy(uint32_t* out, const Fp<P>& a, const Fp<P>& b) {
+  uint32_t m[8], t[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) m[i] = P::mod(i);
+  (void)add8(t, a.v, m);
+  (void)sub8(out, t, b.v);
+}
+
 template <class P>
 ZK_HD Fp<P> sqr(const Fp<P>& a) {
   return mul(a, a);

@@ -22,7 +22,7 @@ __device__ __forceinline__ Fr g_ld(const Fr* p) {
 __global__ void __launch_bounds__(kGThreads) k_sbool_msg(const uint32_t* __restrict__ keys, const Fr* __restrict__ val,
                                                          const uint32_t* __restrict__ count, const Fr* __restrict__ eq,
                                                          const Fr* __restrict__ weights, uint32_t vars_left,
-                                                         Fr* partials, unsigned int* counter, Fr* msg) {
+                                                         const MsgSink sink) {
   const uint32_t n = *count;
   const uint32_t mask = (vars_left >= 32) ? 0xffffffffu : ((1u << vars_left) - 1u);
   const Fr one = Fr::one();
@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(kGThreads) k_sbool_msg(const uint32_t* __restr
       e = add(e, de);
     }
   }
-  grid_sum<4, kGThreads / 32>(s, partials, counter, msg);
+  grid_sum<4, kGThreads / 32>(s, sink);
 }
 
 // final_evaluation (:644-655): eq[0] * sum_j w_j v_j (v_j - 1), v_j = the entry with key j.
@@ -82,9 +82,7 @@ struct GeneralParams {
   const Fr* eq;
   uint32_t n_terms, n_factors;
   uint64_t pairs;
-  Fr* partials;
-  unsigned int* counter;
-  Fr* msg;
+  MsgSink sink;
 };
 
 // s(c) = sum_y eq_c(y) sum_j a_j prod_i p_ji,c(y) for c = 0 .. n_factors + 1 (compute_g_value, :298-357).
@@ -126,7 +124,7 @@ __global__ void __launch_bounds__(kGThreads) k_general_msg(const GeneralParams p
       e = add(e, de);
     }
   }
-  grid_sum<kMaxEval, kGThreads / 32>(s, p.partials, p.counter, p.msg);
+  grid_sum<kMaxEval, kGThreads / 32>(s, p.sink);
 }
 
 // final_evaluation (:420-437): eq[0] * sum_j a_j prod_i p_ji[0]; also writes every table's value.
@@ -158,7 +156,7 @@ inline int g_blocks(uint64_t n, const RoundScratch& sc) {
 
 void launch_sbool_msg(const uint32_t* keys, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* eq,
                       const Fr* weights, uint32_t vars_left, const RoundScratch& sc, cudaStream_t s) {
-  k_sbool_msg<<<g_blocks(upper, sc), kGThreads, 0, s>>>(keys, val, count, eq, weights, vars_left, sc.partials, sc.counter, sc.msg);
+  k_sbool_msg<<<g_blocks(upper, sc), kGThreads, 0, s>>>(keys, val, count, eq, weights, vars_left, sc.sink);
 }
 void launch_sbool_final(const uint32_t* keys, const Fr* val, const uint32_t* count, const Fr* eq, const Fr* weights,
                         uint32_t n_terms, Fr* out, cudaStream_t s) {
@@ -169,7 +167,7 @@ void launch_fill_ones(Fr* out, uint32_t n, int sm_count, cudaStream_t s) {
 }
 void launch_general_msg(const Fr* const* tables_dev, const Fr* scalars, const Fr* eq, uint32_t n_terms, uint32_t n_factors,
                         uint64_t pairs, const RoundScratch& sc, cudaStream_t s) {
-  GeneralParams p{tables_dev, scalars, eq, n_terms, n_factors, pairs, sc.partials, sc.counter, sc.msg};
+  GeneralParams p{tables_dev, scalars, eq, n_terms, n_factors, pairs, sc.sink};
   k_general_msg<<<g_blocks(pairs, sc), kGThreads, 0, s>>>(p);
 }
 void launch_general_final(const Fr* const* tables_dev, const Fr* scalars, const Fr* eq, uint32_t n_terms,

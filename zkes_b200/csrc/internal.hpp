@@ -9,11 +9,21 @@ namespace zk {
 constexpr int kMaxPolys = 4;  // tables per product term the dense round kernel is built for
 
 // Device scratch every round launch needs (owned by the context).
-struct RoundScratch {
+// Where a message kernel leaves its result.  The last block to finish writes the summed message
+// to msg (device) and, when pub_flag is set, also to pub_msg in host-mapped memory followed by
+// the launch's sequence number in pub_flag, which the host polls instead of synchronising.
+struct MsgSink {
   Fr* partials;           // max_blocks * (kMaxPolys + 1) elements
   unsigned int* counter;  // zero between launches
-  Fr* msg;                // kMaxPolys + 1 elements: the round message
-  int max_blocks;         // capacity of partials, in blocks
+  Fr* msg;                // up to 16 elements: the round message
+  Fr* pub_msg;            // host-mapped copy of msg (device-visible address), or nullptr
+  unsigned int* pub_flag; // host-mapped sequence word, or nullptr
+  unsigned int seq;       // value to publish for this launch
+};
+
+struct RoundScratch {
+  MsgSink sink;
+  int max_blocks;         // capacity of sink.partials, in blocks
   int sm_count;
 };
 
@@ -22,6 +32,8 @@ void launch_round(int num_poly, bool fold, const Fr* const* src, Fr* const* dst,
                   const RoundScratch& sc, cudaStream_t stream);
 void launch_final(int num_poly, bool bind, const Fr* const* src, const Fr& r, Fr* out, cudaStream_t stream);
 void launch_fold(const Fr* src, Fr* dst, const Fr& r, uint64_t out_len, int max_blocks, cudaStream_t stream);
+void launch_fold2(const Fr* src, Fr* dst, const Fr& r0, const Fr& r1, uint64_t out_len, int max_blocks,
+                  cudaStream_t stream);
 
 
 // poly.cu
@@ -43,7 +55,7 @@ void launch_general_final(const Fr* const* tables_dev, const Fr* scalars, const 
 
 // sparse.cu
 void launch_sparse_msg(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
-                       const RoundScratch& sc, cudaStream_t s);
+                       const Fr* pending, const RoundScratch& sc, cudaStream_t s);
 int launch_sparse_fold(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr& r,
                        uint32_t* block_counts, uint32_t* idx_out, Fr* val_out, uint32_t* count_out, cudaStream_t s);
 void launch_scatter(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, Fr* dense,

@@ -371,7 +371,7 @@ int msm_run(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const Fr* 
   }
   if (n >= (1ull << 31)) return fail(-1, "msm: at most 2^31 - 1 points per row");
   // ---- pass 1: scalar magnitude
-  unsigned int* d_bits = ctx->rs.counter + 8;  // spare words of the context's counter block
+  unsigned int* d_bits = ctx->rs.sink.counter + 8;  // spare words of the context's counter block
   ZK_CUDA(cudaMemsetAsync(d_bits, 0, 4, s));
   k_msm_bits<<<sm * 8, 256, 0, s>>>(scalars, total, d_bits);
   ctx->launches++;

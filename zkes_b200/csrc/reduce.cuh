@@ -2,6 +2,7 @@
 // warp / block / grid reduction of field elements.
 #pragma once
 #include "ff.cuh"
+#include "internal.hpp"
 #include <cuda_runtime.h>
 
 namespace zk {
@@ -15,6 +16,12 @@ __device__ __forceinline__ Fr fr_from_chunks(const uint4& lo, const uint4& hi) {
 __device__ __forceinline__ void fr_to_chunks(const Fr& x, uint4& lo, uint4& hi) {
   lo = make_uint4(x.v[0], x.v[1], x.v[2], x.v[3]);
   hi = make_uint4(x.v[4], x.v[5], x.v[6], x.v[7]);
+}
+
+__device__ __forceinline__ void st_fr_sys(Fr* p, const Fr& x) {
+  volatile uint32_t* q = reinterpret_cast<volatile uint32_t*>(p);
+#pragma unroll
+  for (int i = 0; i < 8; i++) q[i] = x.v[i];
 }
 
 __device__ __forceinline__ Fr shfl_down_fr(const Fr& x, int delta) {
@@ -39,7 +46,10 @@ __device__ __forceinline__ Fr ld_cg_fr(const Fr* p) {
 // Sum NV per-thread values over the grid; the last block to arrive writes out[0..NV).
 // partials holds gridDim.x * NV elements; *counter must be zero on entry and is reset.
 template <int NV, int kWarps>
-__device__ __forceinline__ void grid_sum(Fr (&s)[NV], Fr* partials, unsigned int* counter, Fr* out) {
+__device__ __forceinline__ void grid_sum(Fr (&s)[NV], const MsgSink& sink) {
+  Fr* partials = sink.partials;
+  unsigned int* counter = sink.counter;
+  Fr* out = sink.msg;
   __shared__ Fr sh[kWarps][NV];
   __shared__ bool is_last;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -75,8 +85,14 @@ __device__ __forceinline__ void grid_sum(Fr (&s)[NV], Fr* partials, unsigned int
     Fr t = sh[0][threadIdx.x];
     for (int w = 1; w < kWarps; w++) t = add(t, sh[w][threadIdx.x]);
     out[threadIdx.x] = t;
+    if (sink.pub_flag) st_fr_sys(sink.pub_msg + threadIdx.x, t);
   }
   if (threadIdx.x == 0) *counter = 0;
+  if (sink.pub_flag) {  // publish to the polling host: data, system-wide fence, then the sequence word
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(sink.pub_flag) = sink.seq;
+  }
 }
 
 }  // namespace zk

@@ -32,10 +32,13 @@ __device__ __forceinline__ bool is_leader(const uint32_t* idx, uint32_t i, uint3
   return (pos & 1u) == 0 || i == 0 || idx[i - 1] != pos - 1;
 }
 
+// With DEFERRED the dense table has not been folded by the previous challenge yet: the two
+// values an entry pair needs are folded on the fly from four consecutive entries.
+template <bool DEFERRED>
 __global__ void __launch_bounds__(kSpThreads) k_sparse_msg(const uint32_t* __restrict__ idx, const Fr* __restrict__ val,
                                                            const uint32_t* __restrict__ count,
-                                                           const Fr* __restrict__ dense, Fr* partials,
-                                                           unsigned int* counter, Fr* msg) {
+                                                           const Fr* __restrict__ dense, const FixedMul<FrParams> pend,
+                                                           const MsgSink sink) {
   const uint32_t n = *count;
   Wide acc[3];
 #pragma unroll
@@ -53,7 +56,16 @@ __global__ void __launch_bounds__(kSpThreads) k_sparse_msg(const uint32_t* __res
     } else {
       v1 = ld_fr(val + i);
     }
-    const Fr b0 = ld_fr(dense + (pos & ~1u)), b1 = ld_fr(dense + (pos | 1u));
+    Fr b0, b1;
+    if (DEFERRED) {
+      const Fr* q = dense + 4 * (uint64_t)(pos >> 1);
+      const Fr t0 = ld_fr(q), t1 = ld_fr(q + 1), t2 = ld_fr(q + 2), t3 = ld_fr(q + 3);
+      b0 = add(t0, mul_fixed(pend, sub(t1, t0)));
+      b1 = add(t2, mul_fixed(pend, sub(t3, t2)));
+    } else {
+      b0 = ld_fr(dense + (pos & ~1u));
+      b1 = ld_fr(dense + (pos | 1u));
+    }
     Wide w;
     mul_wide(w, v0.v, b0.v);
     wide_add(acc[0], w);
@@ -74,7 +86,7 @@ __global__ void __launch_bounds__(kSpThreads) k_sparse_msg(const uint32_t* __res
     wide_trim<FrParams>(acc[c]);
     s[c] = redc<FrParams>(acc[c]);
   }
-  grid_sum<3, kSpThreads / 32>(s, partials, counter, msg);
+  grid_sum<3, kSpThreads / 32>(s, sink);
 }
 
 // Pass 1 of the entry fold: leaders per block.
@@ -207,11 +219,15 @@ inline int blocks_for(uint64_t n, int threads, int cap) {
 
 }  // namespace
 
+// pending: the challenge the dense table still has to be folded by, or nullptr.
 void launch_sparse_msg(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
-                       const RoundScratch& sc, cudaStream_t s) {
-  const int cap = sc.sm_count * 2 < sc.max_blocks ? sc.sm_count * 2 : sc.max_blocks;
-  k_sparse_msg<<<blocks_for(upper, kSpThreads, cap), kSpThreads, 0, s>>>(idx, val, count, dense, sc.partials, sc.counter,
-                                                                         sc.msg);
+                       const Fr* pending, const RoundScratch& sc, cudaStream_t s) {
+  const int cap = sc.sm_count * 4 < sc.max_blocks ? sc.sm_count * 4 : sc.max_blocks;
+  const int grid = blocks_for(upper, kSpThreads, cap);
+  if (pending)
+    k_sparse_msg<true><<<grid, kSpThreads, 0, s>>>(idx, val, count, dense, make_fixed_mul(*pending), sc.sink);
+  else
+    k_sparse_msg<false><<<grid, kSpThreads, 0, s>>>(idx, val, count, dense, FixedMul<FrParams>(), sc.sink);
 }
 
 int launch_sparse_fold(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr& r,

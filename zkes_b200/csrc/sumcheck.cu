@@ -25,9 +25,7 @@ struct RoundParams {
   Fr* dst[L];
   FixedMul<FrParams> r;  // multiplier table of the challenge being bound
   uint64_t pairs;  // (even, odd) pairs of the table the message is computed over
-  Fr* partials;
-  unsigned int* counter;
-  Fr* msg;
+  MsgSink sink;
 };
 
 template <int L, bool FOLD>
@@ -115,7 +113,7 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_round(const Roun
     wide_trim<FrParams>(acc[c]);
     s[c] = redc<FrParams>(acc[c]);
   }
-  grid_sum<L + 1, kWarps>(s, p.partials, p.counter, p.msg);
+  grid_sum<L + 1, kWarps>(s, p.sink);
 }
 
 // Last step of the protocol: bind the final challenge on the two remaining entries of each
@@ -168,6 +166,45 @@ __global__ void __launch_bounds__(kThreads) k_fold(const FoldParams p) {
   }
 }
 
+// Two folds in one pass (challenges r0 then r1): dst[y] from src[4y .. 4y+3].  Used when the
+// first of the two folds could be postponed, so the table is read once for both.
+struct Fold2Params {
+  const Fr* src;
+  Fr* dst;
+  FixedMul<FrParams> r0, r1, r01;  // r01 = r0 * r1
+  uint64_t out_len;
+};
+
+__global__ void __launch_bounds__(kThreads) k_fold2(const Fold2Params p) {
+  __shared__ uint4 stage[kWarps][WarpTile<8>::kChunks];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint4* sw = stage[warp];
+  const uint64_t tiles = (p.out_len + 31) >> 5;
+  for (uint64_t tile = (uint64_t)blockIdx.x * kWarps + warp; tile < tiles; tile += (uint64_t)gridDim.x * kWarps) {
+    const uint64_t e0 = tile << 5;
+    const uint32_t valid = (uint32_t)((p.out_len - e0) < 32 ? (p.out_len - e0) : 32);
+    uint4 raw[8], q[8];
+    WarpTile<8>::issue(reinterpret_cast<const uint4*>(p.src) + e0 * 8, valid * 8, lane, raw);
+    WarpTile<8>::transpose_in(sw, lane, raw, q);
+    const Fr t0 = fr_from_chunks(q[0], q[1]), t1 = fr_from_chunks(q[2], q[3]);
+    const Fr t2 = fr_from_chunks(q[4], q[5]), t3 = fr_from_chunks(q[6], q[7]);
+    // (t0 + r0 d01) + r1 ((t2 + r0 d23) - (t0 + r0 d01)) = t0 + r0 d01 + r1 (t2 - t0) + r0 r1 (d23 - d01)
+    uint32_t d01[8], d02[8], d23[8], dd[8], m2[8], tmp[8];
+    sub_lazy<FrParams>(d01, t1, t0);
+    sub_lazy<FrParams>(d02, t2, t0);
+    sub_lazy<FrParams>(d23, t3, t2);
+#pragma unroll
+    for (int i = 0; i < 8; i++) m2[i] = FrParams::mod(i);
+    (void)add8(tmp, d23, m2);  // d23 + 2p - d01 stays below 4p < 2^256
+    (void)add8(tmp, tmp, m2);
+    (void)sub8(dd, tmp, d01);
+    const Fr u = add(t0, mul_fixed3(p.r0, d01, p.r1, d02, p.r01, dd));
+    uint4 o[2];
+    fr_to_chunks(u, o[0], o[1]);
+    WarpTile<2>::store(reinterpret_cast<uint4*>(p.dst) + e0 * 2, valid * 2, sw, lane, o);
+  }
+}
+
 int grid_for(uint64_t tiles, int max_blocks) {
   uint64_t blocks = (tiles + kWarps - 1) / kWarps;
   if (blocks < 1) blocks = 1;
@@ -185,9 +222,7 @@ void launch_round_t(bool fold, const Fr* const* src, Fr* const* dst, const Fr& r
   }
   p.r = make_fixed_mul(r);
   p.pairs = pairs;
-  p.partials = sc.partials;
-  p.counter = sc.counter;
-  p.msg = sc.msg;
+  p.sink = sc.sink;
   static int occ[2] = {0, 0};  // resident blocks per SM, per variant
   if (!occ[fold]) {
     int o = 0;
@@ -232,6 +267,12 @@ void launch_final(int num_poly, bool bind, const Fr* const* src, const Fr& r, Fr
 void launch_fold(const Fr* src, Fr* dst, const Fr& r, uint64_t out_len, int max_blocks, cudaStream_t stream) {
   FoldParams p{src, dst, make_fixed_mul(r), out_len};
   k_fold<<<grid_for((out_len + 31) / 32, max_blocks), kThreads, 0, stream>>>(p);
+}
+
+void launch_fold2(const Fr* src, Fr* dst, const Fr& r0, const Fr& r1, uint64_t out_len, int max_blocks,
+                  cudaStream_t stream) {
+  Fold2Params p{src, dst, make_fixed_mul(r0), make_fixed_mul(r1), make_fixed_mul(mul(r0, r1)), out_len};
+  k_fold2<<<grid_for((out_len + 31) / 32, max_blocks), kThreads, 0, stream>>>(p);
 }
 
 }  // namespace zk
