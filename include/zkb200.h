@@ -166,6 +166,16 @@ int zk_sumcheck_sparse_dense_prove_sharded(zk_ctx* ctx, zk_comm* comm, uint32_t 
                                            zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges,
                                            uint64_t* final_table0, uint64_t* final_eval);
 
+/* MSM sharded by point range: every rank passes its own bases and scalars (n_local pairs), the
+ * partial G1 sums are all-gathered and added; all ranks receive the same Jacobian point. */
+int zk_msm_g1_sharded(zk_ctx* ctx, zk_comm* comm, const uint64_t* local_bases, zk_mem bases_mem,
+                      const uint64_t* local_scalars, zk_mem scalars_mem, uint64_t n_local, uint64_t* out_jac);
+/* fix_variables_from_right (src/util/poly.rs:705-758) over a table cut on its top log2(world)
+ * variables: local_evals = the rank's 2^n / world entries, point binds the k highest variables
+ * (k >= log2 world); every rank receives the whole 2^(n-k) result (host). */
+int zk_fix_from_right_sharded(zk_ctx* ctx, zk_comm* comm, uint32_t n, const uint64_t* local_evals, zk_mem evals_mem,
+                              uint32_t k, const uint64_t* point, uint64_t* out);
+
 /* ---- multilinear helpers --------------------------------------------------------------- */
 /* DenseMLPoly::fix_variables, src/util/poly.rs:842-887: binds the k lowest variables of a
  * 2^n table to point[0..k); out receives 2^(n-k) elements. */
@@ -213,6 +223,16 @@ typedef struct zk_kzh_srs zk_kzh_srs;
  * alpha (KZH2; tau_z NULL) or tau_z[2^z_log] (KZH3; alpha NULL).  All host arrays. */
 int zk_kzh_srs_setup(zk_ctx* ctx, int dims, uint32_t n, const uint64_t* g_affine, const uint64_t* tau_x,
                      const uint64_t* tau_y, const uint64_t* tau_z, const uint64_t* alpha, zk_kzh_srs** out);
+/* Sharded SRS: rank `rank` of `world` (a power of two, at most 2^x_log) generates and keeps only
+ * its slab of the full vector (whole x-rows); the mid and low vectors are replicated. */
+int zk_kzh_srs_setup_sharded(zk_ctx* ctx, int rank, int world, int dims, uint32_t n, const uint64_t* g_affine,
+                             const uint64_t* tau_x, const uint64_t* tau_y, const uint64_t* tau_z, const uint64_t* alpha,
+                             zk_kzh_srs** out);
+/* Commit with a sharded SRS: local_evals = this rank's 2^n / world evaluations (its x-rows).  The
+ * partial commitments are summed over ranks and the rows of d_x all-gathered; every rank receives
+ * c (8 x u64) and all 2^x_log Jacobian points of d_x. */
+int zk_kzh_commit_sharded(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs* srs, const uint64_t* local_evals,
+                          zk_mem evals_mem, uint64_t* c_affine_out, uint64_t* d_x_jac_out);
 /* An SRS the caller already holds (load_kzh3_srs, src/crypto/srs_storage.rs): h_full 2^n points,
  * h_mid 2^(n - x_log), h_low 2^z_log (KZH3 only). */
 int zk_kzh_srs_upload(zk_ctx* ctx, int dims, uint32_t n, const uint64_t* h_full, const uint64_t* h_mid,

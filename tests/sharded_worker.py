@@ -130,6 +130,41 @@ def main():
             ot = o.Transcript(b"sharded")
             op, opr = o.sparse_dense_prove(n, idx, vals, dense, ot)
             assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
+        # ---- MSM by point range, KZH commit by x-rows, fix_from_right over the top variables
+        from zkes_b200 import curve
+        rnd = random.Random(77)
+        pts = [o.g1_mul(o.G1_GEN, rnd.randrange(1, o.R_MOD)) for _ in range(16 * world)]
+        sc = [rnd.randrange(o.R_MOD) if i % 3 else o.fr_from_int(rnd.randrange(-128, 128)) for i in range(len(pts))]
+        b, e = rank * 16, (rank + 1) * 16
+        got = zd.sharded_msm(ctx, comm, curve.affine_to_array(pts[b:e]), sc[b:e])
+        assert got == o.g1_msm(pts, sc)
+        for dims, n in ((2, 6), (3, 7)):
+            if dims == 2:
+                xl, yl = o.kzh2_degrees(n)
+                d = o.gen_uniform_fr(5, 0, 0, 2 + (1 << xl) + (1 << yl))
+                tx, ty, alpha = d[1:1 + (1 << xl)], d[1 + (1 << xl):1 + (1 << xl) + (1 << yl)], d[-1]
+                osrs = o.KZH2SRS(n, d[0], tx, ty, alpha)
+                srs = zd.sharded_kzh_setup(ctx, comm, 2, n, osrs.g, tx, ty, alpha=alpha)
+                full = osrs.h_xy
+            else:
+                xl, yl, zl = o.kzh3_degrees(n)
+                d = o.gen_uniform_fr(6, 0, 0, 1 + (1 << xl) + (1 << yl) + (1 << zl))
+                tx = d[1:1 + (1 << xl)]
+                ty = d[1 + (1 << xl):1 + (1 << xl) + (1 << yl)]
+                tz = d[1 + (1 << xl) + (1 << yl):]
+                osrs = o.KZH3SRS(n, d[0], tx, ty, tz)
+                srs = zd.sharded_kzh_setup(ctx, comm, 3, n, osrs.g, tx, ty, tau_z=tz)
+                full = osrs.h_xyz
+            lo, hi = zd.shard_range(rank, world, n)
+            assert srs.read(0, 0, hi - lo) == full[lo:hi]
+            f = [rnd.randrange(o.R_MOD) if i % 2 else o.fr_from_int(rnd.randrange(-128, 128)) for i in range(1 << n)]
+            c, dx = zd.sharded_kzh_commit(ctx, comm, srs, f[lo:hi])
+            oc, odx = (o.kzh2_commit if dims == 2 else o.kzh3_commit)(osrs, f)
+            assert c == oc and dx == odx
+            pt = [rnd.randrange(o.R_MOD) for _ in range(xl)]
+            got = zd.sharded_fix_from_right(ctx, comm, n, f[lo:hi], pt)
+            assert got == o.fix_variables_from_right(f, pt)
+            srs.close()
         comm.close()
         ctx.close()
     dist.barrier()

@@ -78,6 +78,11 @@ SIGNATURES = {
     "zk_sumcheck_sparse_dense_prove_sharded": (c_int, [c_void_p, c_void_p, c_uint32, c_uint64, c_void_p, c_void_p,
                                                        c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                                        c_void_p, c_void_p, c_void_p]),
+    "zk_msm_g1_sharded": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_uint64, c_void_p]),
+    "zk_fix_from_right_sharded": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_void_p]),
+    "zk_kzh_srs_setup_sharded": (c_int, [c_void_p, c_int, c_int, c_int, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, POINTER(c_void_p)]),
+    "zk_kzh_commit_sharded": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "zk_microbench": (c_int, [c_void_p, c_int, c_int, c_int, c_int, POINTER(ctypes.c_float),
                               POINTER(ctypes.c_double)]),
     "zk_fold_lsb": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_int]),

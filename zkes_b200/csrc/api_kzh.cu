@@ -1,6 +1,7 @@
 // C ABI: KZH2 / KZH3 structured reference strings, commit and open (G1 side).
 #include "../../include/zkb200.h"
 #include "msm.hpp"
+#include "kzh.hpp"
 
 #include <vector>
 
@@ -10,20 +11,15 @@ namespace zk {
 size_t fixed_base_table_bytes();
 int fixed_base_build_table(const Affine& g, void* table_mem, cudaStream_t s);
 int fixed_base_generate(const void* table_mem, int n_factors, const Fr* const* tables, const uint32_t* bits,
-                        const Fr* alpha, uint64_t count, Affine* out, int sm_count, cudaStream_t s);
+                        const Fr* alpha, uint64_t start, uint64_t count, Affine* out, int sm_count, cudaStream_t s);
+int comm_sum_points(zk_ctx* ctx, zk_comm* c, Jacobian* point);
+int comm_sum_fr_vec(zk_ctx* ctx, zk_comm* c, Fr* vals, uint64_t n);
 int normalize_device(zk_ctx* ctx, const Jacobian* in, uint64_t n, Affine* out);
 size_t from_right_scratch_elems(zk_ctx* ctx, uint32_t n, uint32_t k);
 int fix_from_right_device(zk_ctx* ctx, uint32_t n, const Fr* f_dev, uint32_t k, const uint64_t* point_host, Fr* scratch,
                           Fr* out_dev);
 int eq_table_device(zk_ctx* ctx, const uint64_t* point_host, uint32_t k, Fr* point_dev, Fr* table);
 }  // namespace zk
-
-struct zk_kzh_srs {
-  int dims = 0;
-  uint32_t n = 0, x_log = 0, y_log = 0, z_log = 0;
-  Affine* h[3] = {nullptr, nullptr, nullptr};  // full (2^n), mid (2^(n - x_log)), low (2^z_log, KZH3 only)
-  uint64_t count[3] = {0, 0, 0};
-};
 
 namespace {
 
@@ -43,7 +39,7 @@ void split_degrees(int dims, uint32_t n, uint32_t* x, uint32_t* y, uint32_t* z) 
   }
 }
 
-int alloc_srs(zk_ctx* ctx, int dims, uint32_t n, zk_kzh_srs** out) {
+int alloc_srs(zk_ctx* ctx, int dims, uint32_t n, int rank, int world, zk_kzh_srs** out) {
   if (!ctx || !out) return fail(ZK_ERR_ARG, "kzh_srs: NULL argument");
   if (dims != 2 && dims != 3) return fail(ZK_ERR_ARG, "kzh_srs: dims must be 2 or 3");
   if (n > 30) return fail(ZK_ERR_ARG, "kzh_srs: n %u too large", n);
@@ -52,7 +48,14 @@ int alloc_srs(zk_ctx* ctx, int dims, uint32_t n, zk_kzh_srs** out) {
   s->dims = dims;
   s->n = n;
   split_degrees(dims, n, &s->x_log, &s->y_log, &s->z_log);
-  s->count[0] = 1ull << n;
+  if (world < 1 || (world & (world - 1)) || rank < 0 || rank >= world || (uint64_t)world > (1ull << s->x_log)) {
+    delete s;
+    return fail(ZK_ERR_ARG, "kzh_srs: %d ranks cannot share 2^%u rows", world, s->x_log);
+  }
+  s->rank = rank;
+  s->world = world;
+  s->count[0] = (1ull << n) / world;
+  s->slab_begin = s->count[0] * rank;
   s->count[1] = 1ull << (n - s->x_log);
   s->count[2] = dims == 3 ? 1ull << s->z_log : 0;
   for (int k = 0; k < 3; k++) {
@@ -96,13 +99,23 @@ void pad_point(const uint64_t* point, uint32_t point_len, uint32_t n, std::vecto
 
 extern "C" {
 
+int zk_kzh_srs_setup_sharded(zk_ctx* ctx, int rank, int world, int dims, uint32_t n, const uint64_t* g_affine,
+                             const uint64_t* tau_x, const uint64_t* tau_y, const uint64_t* tau_z, const uint64_t* alpha,
+                             zk_kzh_srs** out);
+
 int zk_kzh_srs_setup(zk_ctx* ctx, int dims, uint32_t n, const uint64_t* g_affine, const uint64_t* tau_x,
                      const uint64_t* tau_y, const uint64_t* tau_z, const uint64_t* alpha, zk_kzh_srs** out) {
+  return zk_kzh_srs_setup_sharded(ctx, 0, 1, dims, n, g_affine, tau_x, tau_y, tau_z, alpha, out);
+}
+
+int zk_kzh_srs_setup_sharded(zk_ctx* ctx, int rank, int world, int dims, uint32_t n, const uint64_t* g_affine,
+                             const uint64_t* tau_x, const uint64_t* tau_y, const uint64_t* tau_z, const uint64_t* alpha,
+                             zk_kzh_srs** out) {
   if (!g_affine || !tau_x || !tau_y) return fail(ZK_ERR_ARG, "kzh_srs_setup: NULL argument");
   if (dims == 2 && !alpha) return fail(ZK_ERR_ARG, "kzh_srs_setup: KZH2 needs alpha");
   if (dims == 3 && !tau_z) return fail(ZK_ERR_ARG, "kzh_srs_setup: KZH3 needs tau_z");
   zk_kzh_srs* s = nullptr;
-  int rc = alloc_srs(ctx, dims, n, &s);
+  int rc = alloc_srs(ctx, dims, n, rank, world, &s);
   if (rc) return rc;
   CtxLock lk(ctx);
   cudaStream_t st = ctx->stream;
@@ -124,18 +137,18 @@ int zk_kzh_srs_setup(zk_ctx* ctx, int dims, uint32_t n, const uint64_t* g_affine
     // h_xy[i] = (tau_x[x] tau_y[y]) g with y in the low bits; h_y[j] = (alpha tau_y[j]) g   (kzh2.rs:521-541)
     const Fr* t2[2] = {d_ty, d_tx};
     const uint32_t b2[2] = {s->y_log, s->x_log};
-    ctx->launches += fixed_base_generate(table, 2, t2, b2, nullptr, s->count[0], s->h[0], ctx->sm_count, st);
+    ctx->launches += fixed_base_generate(table, 2, t2, b2, nullptr, s->slab_begin, s->count[0], s->h[0], ctx->sm_count, st);
     Fr a = fr_load(alpha);
     const Fr* t1[1] = {d_ty};
     const uint32_t b1[1] = {s->y_log};
-    ctx->launches += fixed_base_generate(table, 1, t1, b1, &a, s->count[1], s->h[1], ctx->sm_count, st);
+    ctx->launches += fixed_base_generate(table, 1, t1, b1, &a, 0, s->count[1], s->h[1], ctx->sm_count, st);
   } else {
     // h_xyz (z low, y middle, x high), h_yz, h_z   (kzh3.rs:480-531)
     const Fr* t3[3] = {d_tz, d_ty, d_tx};
     const uint32_t b3[3] = {s->z_log, s->y_log, s->x_log};
-    ctx->launches += fixed_base_generate(table, 3, t3, b3, nullptr, s->count[0], s->h[0], ctx->sm_count, st);
-    ctx->launches += fixed_base_generate(table, 2, t3, b3, nullptr, s->count[1], s->h[1], ctx->sm_count, st);
-    ctx->launches += fixed_base_generate(table, 1, t3, b3, nullptr, s->count[2], s->h[2], ctx->sm_count, st);
+    ctx->launches += fixed_base_generate(table, 3, t3, b3, nullptr, s->slab_begin, s->count[0], s->h[0], ctx->sm_count, st);
+    ctx->launches += fixed_base_generate(table, 2, t3, b3, nullptr, 0, s->count[1], s->h[1], ctx->sm_count, st);
+    ctx->launches += fixed_base_generate(table, 1, t3, b3, nullptr, 0, s->count[2], s->h[2], ctx->sm_count, st);
   }
   ZK_CUDA(cudaGetLastError());
   ZK_CUDA(cudaStreamSynchronize(st));
@@ -147,7 +160,7 @@ int zk_kzh_srs_upload(zk_ctx* ctx, int dims, uint32_t n, const uint64_t* h_full,
                       const uint64_t* h_low, zk_mem mem, zk_kzh_srs** out) {
   if (!h_full || !h_mid || (dims == 3 && !h_low)) return fail(ZK_ERR_ARG, "kzh_srs_upload: NULL argument");
   zk_kzh_srs* s = nullptr;
-  int rc = alloc_srs(ctx, dims, n, &s);
+  int rc = alloc_srs(ctx, dims, n, 0, 1, &s);
   if (rc) return rc;
   CtxLock lk(ctx);
   const uint64_t* src[3] = {h_full, h_mid, h_low};

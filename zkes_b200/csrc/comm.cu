@@ -6,6 +6,7 @@
 #include "../../include/zkb200.h"
 #include "ctx.hpp"
 #include "reduce.cuh"
+#include "ec.cuh"
 
 #include <dlfcn.h>
 
@@ -67,6 +68,33 @@ __global__ void k_sum_ranks(const Fr* __restrict__ gathered, int world, int n_va
   }
 }
 
+// point <- sum of `world` Jacobian points (rank-major in gathered)
+__global__ void k_sum_points(const Jacobian* __restrict__ gathered, int world, int n_points, Jacobian* out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_points) return;
+  Xyzz acc = Xyzz::inf();
+  for (int r = 0; r < world; r++) {
+    const Jacobian j = gathered[(size_t)r * n_points + i];
+    if (j.z.is_zero()) continue;
+    Xyzz p;
+    p.x = j.x;
+    p.y = j.y;
+    p.zz = sqr(j.z);
+    p.zzz = mul(p.zz, j.z);
+    acc = add(acc, p);
+  }
+  out[i] = to_jacobian(acc);
+}
+
+// vals[i] <- sum over ranks of gathered[r * n + i]
+__global__ void k_sum_ranks_vec(const Fr* __restrict__ gathered, int world, uint64_t n, Fr* out) {
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    Fr s = gathered[i];
+    for (int r = 1; r < world; r++) s = add(s, gathered[(uint64_t)r * n + i]);
+    out[i] = s;
+  }
+}
+
 }  // namespace
 
 struct zk_comm {
@@ -97,6 +125,35 @@ int comm_gather_fr(zk_ctx* ctx, zk_comm* c, const Fr* vals, int n_vals, Fr* out)
   }
   int rc = g_nccl.all_gather(vals, out, (size_t)n_vals * sizeof(Fr), 1, c->comm, ctx->stream);
   if (rc != 0) return fail(ZK_ERR_COMM, "ncclAllGather: %s", g_nccl.errstr ? g_nccl.errstr(rc) : "error");
+  return ZK_OK;
+}
+
+// point[0 .. n_points) (device) <- element-wise group sum over all ranks; uses the aux scratch.
+int comm_sum_points_n(zk_ctx* ctx, zk_comm* c, Jacobian* points, int n_points) {
+  if (!c || c->world == 1) return ZK_OK;
+  void* buf = nullptr;
+  int rc = ctx->reserve_aux((size_t)c->world * n_points * sizeof(Jacobian) + 256, &buf);
+  if (rc) return rc;
+  rc = comm_gather_bytes(ctx, c, points, (size_t)n_points * sizeof(Jacobian), buf);
+  if (rc) return rc;
+  k_sum_points<<<(n_points + 63) / 64, 64, 0, ctx->stream>>>((const Jacobian*)buf, c->world, n_points, points);
+  ctx->launches++;
+  return ZK_OK;
+}
+int comm_sum_points(zk_ctx* ctx, zk_comm* c, Jacobian* point) { return comm_sum_points_n(ctx, c, point, 1); }
+
+// vals[0 .. n) (device) <- element-wise field sum over all ranks; uses the aux scratch.
+int comm_sum_fr_vec(zk_ctx* ctx, zk_comm* c, Fr* vals, uint64_t n) {
+  if (!c || c->world == 1 || n == 0) return ZK_OK;
+  void* buf = nullptr;
+  int rc = ctx->reserve_aux((size_t)c->world * n * sizeof(Fr) + 256, &buf);
+  if (rc) return rc;
+  rc = comm_gather_bytes(ctx, c, vals, n * sizeof(Fr), buf);
+  if (rc) return rc;
+  uint64_t blocks = (n + 255) / 256;
+  if (blocks > (uint64_t)ctx->sm_count * 8) blocks = ctx->sm_count * 8;
+  k_sum_ranks_vec<<<(unsigned)blocks, 256, 0, ctx->stream>>>((const Fr*)buf, c->world, n, vals);
+  ctx->launches++;
   return ZK_OK;
 }
 

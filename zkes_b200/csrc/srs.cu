@@ -36,11 +36,12 @@ struct FbFactors {
   Fr alpha;
 };
 
-__global__ void __launch_bounds__(128) k_fb_generate(const Affine* __restrict__ table, const FbFactors f, uint64_t count,
-                                                     Affine* out) {
+__global__ void __launch_bounds__(128) k_fb_generate(const Affine* __restrict__ table, const FbFactors f, uint64_t start,
+                                                     uint64_t count, Affine* out) {
   for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (uint64_t)gridDim.x * blockDim.x) {
+    const uint64_t g = start + i;  // index into the whole vector; out holds the slab [start, start + count)
     Fr s = f.has_alpha ? f.alpha : Fr::one();
-    for (int k = 0; k < f.count; k++) s = mul(s, f.table[k][(i >> f.shift[k]) & f.mask[k]]);
+    for (int k = 0; k < f.count; k++) s = mul(s, f.table[k][(g >> f.shift[k]) & f.mask[k]]);
     const Fr c = from_mont(s);
     uint32_t m[8], d[8], t[8], mag[8];
 #pragma unroll
@@ -84,10 +85,10 @@ int fixed_base_build_table(const Affine& g, void* table_mem, cudaStream_t s) {
   return 2;
 }
 
-// out[i] = (alpha * prod_k tables[k][(i >> shift_k) & (2^bits_k - 1)]) * g for i < count; shift_k is
+// out[i] = (alpha * prod_k tables[k][((start + i) >> shift_k) & (2^bits_k - 1)]) * g for i < count; shift_k is
 // the sum of the earlier factors' bits (factor 0 indexes the lowest bits).  Device pointers.
 int fixed_base_generate(const void* table_mem, int n_factors, const Fr* const* tables, const uint32_t* bits,
-                        const Fr* alpha, uint64_t count, Affine* out, int sm_count, cudaStream_t s) {
+                        const Fr* alpha, uint64_t start, uint64_t count, Affine* out, int sm_count, cudaStream_t s) {
   FbFactors f;
   uint32_t shift = 0;
   for (int k = 0; k < 3; k++) {
@@ -101,7 +102,7 @@ int fixed_base_generate(const void* table_mem, int n_factors, const Fr* const* t
   f.alpha = alpha ? *alpha : Fr::one();
   uint64_t blocks = (count + 127) / 128;
   if (blocks > (uint64_t)sm_count * 16) blocks = sm_count * 16;
-  k_fb_generate<<<(unsigned)blocks, 128, 0, s>>>(reinterpret_cast<const Affine*>(table_mem) + kFbWindows, f, count, out);
+  k_fb_generate<<<(unsigned)blocks, 128, 0, s>>>(reinterpret_cast<const Affine*>(table_mem) + kFbWindows, f, start, count, out);
   return 1;
 }
 

@@ -117,3 +117,48 @@ def sharded_sparse_dense_prove(ctx, comm: Comm, num_var: int, local_idx, local_v
                                                      _p(fin_t), _p(fin)), "zk_sumcheck_sparse_dense_prove_sharded")
     return ([from_mont_array(msgs[r]) for r in range(num_var)], from_mont_array(chal[:num_var]), from_mont_array(fin_t),
             from_mont_array(fin)[0])
+
+
+def sharded_msm(ctx, comm: Comm, local_bases_arr: np.ndarray, local_scalars):
+    """sum over all ranks of MSM(local bases, local scalars) -> affine tuple, the same on every rank."""
+    from . import curve
+    n = len(local_scalars)
+    sc = to_mont_array(local_scalars) if n else np.zeros((1, 4), dtype=np.uint64)
+    out = np.zeros((1, 12), dtype=np.uint64)
+    check(lib.zk_msm_g1_sharded(ctx.handle, comm.handle, _p(local_bases_arr), ZK_MEM_HOST, _p(sc), ZK_MEM_HOST, n, _p(out)),
+          "zk_msm_g1_sharded")
+    return curve.jacobian_to_affine_py(out)[0]
+
+
+def sharded_fix_from_right(ctx, comm: Comm, n: int, local_evals, point):
+    ev = to_mont_array(local_evals)
+    pt = to_mont_array(point) if len(point) else np.zeros((1, 4), dtype=np.uint64)
+    out = np.zeros((1 << (n - len(point)), 4), dtype=np.uint64)
+    check(lib.zk_fix_from_right_sharded(ctx.handle, comm.handle, n, _p(ev), ZK_MEM_HOST, len(point), _p(pt), _p(out)),
+          "zk_fix_from_right_sharded")
+    return from_mont_array(out)
+
+
+def sharded_kzh_setup(ctx, comm: Comm, dims: int, n: int, g, tau_x, tau_y, tau_z=None, alpha=None):
+    from . import curve
+    from .kzh import KZHSRS
+    h = c_void_p()
+    ga = curve.affine_to_array([g])
+    tx, ty = to_mont_array(tau_x), to_mont_array(tau_y)
+    tz = to_mont_array(tau_z) if tau_z is not None else None
+    al = to_mont_array([alpha]) if alpha is not None else None
+    check(lib.zk_kzh_srs_setup_sharded(ctx.handle, comm.rank, comm.world, dims, n, _p(ga), _p(tx), _p(ty),
+                                       _p(tz) if tz is not None else None, _p(al) if al is not None else None,
+                                       ctypes.byref(h)), "zk_kzh_srs_setup_sharded")
+    return KZHSRS(ctx, dims, n, h)
+
+
+def sharded_kzh_commit(ctx, comm: Comm, srs, local_evals):
+    """-> (c affine, d_x affine list), identical on every rank."""
+    from . import curve
+    ev = to_mont_array(local_evals)
+    c = np.zeros((1, 8), dtype=np.uint64)
+    dx = np.zeros((1 << srs.x_log, 12), dtype=np.uint64)
+    check(lib.zk_kzh_commit_sharded(ctx.handle, comm.handle, srs.handle, _p(ev), ZK_MEM_HOST, _p(c), _p(dx)),
+          "zk_kzh_commit_sharded")
+    return curve.affine_from_array(c)[0], curve.jacobian_to_affine_py(dx)
