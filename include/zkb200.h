@@ -56,6 +56,11 @@ void zk_free(zk_ctx* ctx);
 const char* zk_last_error(void);
 /* Number of kernels this library has launched on the context since it was created. */
 uint64_t zk_launch_count(const zk_ctx* ctx);
+/* Options.  ZK_OPT_DEVICE_TAIL (default 0): when 1, the dense provers hand the rounds below 1024
+ * table entries to one resident block that also runs the built-in transcript on the device
+ * (identical outputs; only taken without a Fiat-Shamir callback and outside sharded rounds). */
+typedef enum zk_option { ZK_OPT_DEVICE_TAIL = 1 } zk_option;
+int zk_set_option(zk_ctx* ctx, int option, int value);
 /* The CUDA stream (cudaStream_t) every kernel of this context is launched on, so a host can
  * bracket calls with its own events. */
 void* zk_stream(zk_ctx* ctx);

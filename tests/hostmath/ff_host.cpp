@@ -65,3 +65,21 @@ extern "C" void zkh_g1_jacobian(const uint32_t* a, uint32_t k, uint32_t* out) {
   Jacobian j = to_jacobian(mul_small(Xyzz::from_affine(ld_aff(a)), k));
   memcpy(out, j.x.v, 32); memcpy(out + 8, j.y.v, 32); memcpy(out + 16, j.z.v, 32);
 }
+
+// ---- device-form transcript (strobe_dev.cuh) driven from a raw 200-byte state
+#include "../../zkes_b200/csrc/strobe_dev.cuh"
+// state: 200 bytes + pos, pos_begin, cur_flags (3 x u32).  Appends n scalars (Montgomery) under
+// "round_message", draws one "challenge"; writes the challenge (Montgomery) and the new state.
+extern "C" void zkh_strobe_round(uint8_t* state200, uint32_t* pos3, const uint32_t* scalars, int n, uint32_t* challenge) {
+  StrobeState st;
+  memcpy(st.lanes, state200, 200);
+  st.pos = pos3[0]; st.pos_begin = pos3[1]; st.cur_flags = pos3[2];
+  for (int i = 0; i < n; i++) {
+    Fr x; memcpy(x.v, scalars + 8 * i, 32);
+    transcript_append_scalar_dev(st, "round_message", 13, x);
+  }
+  Fr c = transcript_challenge_scalar_dev(st, "challenge", 9);
+  memcpy(challenge, c.v, 32);
+  memcpy(state200, st.lanes, 200);
+  pos3[0] = st.pos; pos3[1] = st.pos_begin; pos3[2] = st.cur_flags;
+}

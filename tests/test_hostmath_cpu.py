@@ -143,3 +143,27 @@ def test_g1_group_law(hm):
     X, Y, Z = [sum(int(v) << (32 * i) for i, v in enumerate(jac[8 * k:8 * k + 8])) * rinv % q for k in range(3)]
     zi = pow(Z, -1, q)
     assert (X * zi * zi % q, Y * zi * zi * zi % q) == o.g1_mul(p, 7)
+
+
+def test_device_form_transcript_matches_oracle(hm):
+    """strobe_dev.cuh (the single-thread GPU transcript) against the oracle's Merlin, continuing
+    from an arbitrary mid-stream state over many rounds."""
+    rnd = random.Random(21)
+    t = o.Transcript(b"sumcheck")
+    t.append_u64(b"num_var", 20)
+    t.append_u64(b"num_poly", 2)
+    t.append_message(b"x", bytes(rnd.randrange(256) for _ in range(77)))
+    state = (ctypes.c_uint8 * 200)(*t.strobe.state)
+    pos3 = (ctypes.c_uint32 * 3)(t.strobe.pos, t.strobe.pos_begin, t.strobe.cur_flags)
+    ch = (ctypes.c_uint32 * 8)()
+    for rounds in range(40):
+        n = rnd.choice([2, 3, 4, 5])
+        scalars = [rnd.randrange(o.R_MOD) for _ in range(n)]
+        buf = (ctypes.c_uint32 * (8 * n))(*[((v * R % o.R_MOD) >> (32 * i)) & 0xFFFFFFFF for v in scalars for i in range(8)])
+        hm.zkh_strobe_round(state, pos3, buf, n, ch)
+        for s_ in scalars:
+            t.append_scalar(b"round_message", s_)
+        want = t.challenge_scalar(b"challenge")
+        assert val(ch) == want * R % o.R_MOD
+        assert bytes(state) == bytes(t.strobe.state)
+        assert (pos3[0], pos3[1]) == (t.strobe.pos, t.strobe.pos_begin)

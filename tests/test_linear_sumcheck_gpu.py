@@ -162,3 +162,18 @@ def test_fix_variables_random(ctx, n, k):
     f = [rnd.randrange(o.R_MOD) for _ in range(1 << n)]
     pt = [rnd.randrange(o.R_MOD) for _ in range(k)]
     assert DenseMLPoly.from_evaluations(f).fix_variables(ctx, pt).evaluations == o.fix_variables(f, pt)
+
+
+@pytest.mark.parametrize("ell", [1, 2, 3, 4])
+@pytest.mark.parametrize("n", [0, 1, 4, 9, 10, 11, 13])
+def test_device_tail_option(ctx, n, ell):
+    """With ZK_OPT_DEVICE_TAIL the last rounds (tables below 1024 entries) run in one resident block
+    with the transcript on the device; every output and the transcript state must be unchanged."""
+    from zkes_b200._lib import ZK_OPT_DEVICE_TAIL
+    rnd = random.Random(5000 + 10 * n + ell)
+    tables = [[rnd.randrange(o.R_MOD) for _ in range(1 << n)] for _ in range(ell)]
+    ctx.set_option(ZK_OPT_DEVICE_TAIL, 1)
+    try:
+        run_both(ctx, tables)
+    finally:
+        ctx.set_option(ZK_OPT_DEVICE_TAIL, 0)

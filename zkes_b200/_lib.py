@@ -10,6 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libzkb200.so")
 
 ZK_MEM_HOST, ZK_MEM_DEVICE = 0, 1
+ZK_OPT_DEVICE_TAIL = 1
 ZK_OK, ZK_ERR_ARG, ZK_ERR_OOM, ZK_ERR_CUDA, ZK_ERR_TIMEOUT, ZK_ERR_FS_CALLBACK, ZK_ERR_COMM = 0, -1, -2, -3, -4, -5, -6
 
 FS_ROUND_FN = ctypes.CFUNCTYPE(c_int, c_void_p, POINTER(c_uint64), c_uint32, POINTER(c_uint64))
@@ -23,6 +24,7 @@ SIGNATURES = {
     "zk_free": (None, [c_void_p]),
     "zk_last_error": (c_char_p, []),
     "zk_launch_count": (c_uint64, [c_void_p]),
+    "zk_set_option": (c_int, [c_void_p, c_int, c_int]),
     "zk_stream": (c_void_p, [c_void_p]),
     "zk_profile_enable": (c_int, [c_void_p, c_int]),
     "zk_profile_get": (c_int, [c_void_p, c_int, POINTER(c_uint64), POINTER(ctypes.c_double),

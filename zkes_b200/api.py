@@ -43,6 +43,9 @@ class Context:
     def launch_count(self) -> int:
         return int(lib.zk_launch_count(self.handle))
 
+    def set_option(self, option: int, value: int):
+        check(lib.zk_set_option(self.handle, option, value), "zk_set_option")
+
     def sync(self):
         check(lib.zk_device_sync(self.handle), "zk_device_sync")
 

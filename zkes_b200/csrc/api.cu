@@ -2,6 +2,7 @@
 // kernels.  See include/zkb200.h for the contract of every entry point.
 #include "../../include/zkb200.h"
 #include "ctx.hpp"
+#include "strobe_dev.cuh"
 
 #include <chrono>
 #include <cstdio>
@@ -99,6 +100,15 @@ void zk_free(zk_ctx* ctx) {
 
 uint64_t zk_launch_count(const zk_ctx* ctx) { return ctx ? ctx->launches.load() : 0; }
 
+int zk_set_option(zk_ctx* ctx, int option, int value) {
+  if (!ctx) return fail(ZK_ERR_ARG, "zk_set_option: NULL context");
+  CtxLock lk(ctx);
+  switch (option) {
+    case ZK_OPT_DEVICE_TAIL: ctx->device_tail = value != 0; return ZK_OK;
+    default: return fail(ZK_ERR_ARG, "zk_set_option: unknown option %d", option);
+  }
+}
+
 void* zk_stream(zk_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
 
 int zk_profile_enable(zk_ctx* ctx, int on) {
@@ -194,12 +204,52 @@ namespace zk {
 
 // `rounds` rounds of the dense prover over device tables cur[i] of 2^rounds elements each; the
 // folded tables alternate between ping and pong.  On return cur[] points at the two-entry
-// tables the last challenge has not been bound on yet (or the inputs when rounds == 0).
+// tables the last challenge has not been bound on yet (or the inputs when rounds == 0), unless
+// *finals_done is set: then the single-block tail kernel ran the last rounds with the built-in
+// transcript on the device and ctx->final_out already holds the final values.
 int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr** cur, Fr** ping, Fr** pong,
                   uint32_t round_offset, zk_fs_round_fn fs, void* fs_user, zk_transcript* tr, uint64_t* round_msgs,
-                  uint64_t* challenges, Fr* challenge) {
+                  uint64_t* challenges, Fr* challenge, bool* finals_done) {
   const uint64_t size = 1ull << rounds;
+  *finals_done = false;
+  uint64_t cur_size = size;  // entries of the tables cur[] points at
+  const bool tail_ok = ctx->device_tail && !fs && tr && !comm;
   for (uint32_t round = 0; round < rounds; round++) {
+    if (tail_ok && cur_size <= kTailMax) {
+      // hand the remaining rounds to one resident block; round > 0 means `*challenge` is still to be bound
+      StrobeState st;
+      memcpy(st.lanes, tr->m.strobe().state(), 200);
+      st.pos = tr->m.strobe().pos();
+      st.pos_begin = tr->m.strobe().pos_begin();
+      st.cur_flags = tr->m.strobe().cur_flags();
+      st.pad = 0;
+      const uint32_t left = rounds - round;
+      Fr* d_msgs = reinterpret_cast<Fr*>(ctx->tail_out);
+      Fr* d_chal = d_msgs + (size_t)left * (L + 1);
+      StrobeState* d_st = reinterpret_cast<StrobeState*>(d_chal + left);
+      if (launch_tail(L, cur, (uint32_t)cur_size, round > 0, *challenge, st, d_msgs, d_chal, ctx->final_out, d_st, ctx->stream))
+        return fail(ZK_ERR_CUDA, "tail kernel launch failed");
+      ctx->launches++;
+      ZK_CUDA(cudaGetLastError());
+      const size_t bytes = ((size_t)left * (L + 2)) * sizeof(Fr) + sizeof(StrobeState);
+      ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->tail_out, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+      ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+      const Fr* h_msgs = reinterpret_cast<const Fr*>(ctx->host_small);
+      const Fr* h_chal = h_msgs + (size_t)left * (L + 1);
+      const StrobeState* h_st = reinterpret_cast<const StrobeState*>(h_chal + left);
+      for (uint32_t k = 0; k < left; k++) {
+        for (int c = 0; c <= L; c++)
+          fr_store(round_msgs + ((uint64_t)(round_offset + round + k) * (L + 1) + c) * 4, h_msgs[(size_t)k * (L + 1) + c]);
+        fr_store(challenges + 4 * (uint64_t)(round_offset + round + k), h_chal[k]);
+      }
+      *challenge = h_chal[left - 1];
+      memcpy(tr->m.strobe().state(), h_st->lanes, 200);
+      tr->m.strobe().pos() = (uint8_t)h_st->pos;
+      tr->m.strobe().pos_begin() = (uint8_t)h_st->pos_begin;
+      tr->m.strobe().cur_flags() = (uint8_t)h_st->cur_flags;
+      *finals_done = true;
+      return ZK_OK;
+    }
     const uint64_t pairs = size >> (round + 1);
     const RoundScratch sc = ctx->next_msg_scratch(comm != nullptr);
     if (round == 0) {
@@ -210,6 +260,7 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
       ctx->prof_begin(ZK_PROF_ROUND, 192.0 * L * pairs);
       launch_round(L, true, cur, dst, *challenge, pairs, sc, ctx->stream);
       for (int i = 0; i < L; i++) cur[i] = dst[i];
+      cur_size >>= 1;
     }
     ctx->prof_end();
     ctx->launches++;
@@ -247,10 +298,13 @@ int sharded_tail(zk_ctx* ctx, zk_comm* comm, int L, uint32_t n_local, zk_fs_roun
     ping[i] = pp + (size_t)i * world;
     pong[i] = pp + (size_t)(kMaxPolys + i) * world;
   }
-  rc = linear_rounds(ctx, nullptr, L, logw, cur, ping, pong, n_local, fs, fs_user, tr, round_msgs, challenges, challenge);
+  bool done = false;
+  rc = linear_rounds(ctx, nullptr, L, logw, cur, ping, pong, n_local, fs, fs_user, tr, round_msgs, challenges, challenge, &done);
   if (rc) return rc;
-  launch_final(L, logw > 0, cur, *challenge, ctx->final_out, ctx->stream);
-  ctx->launches++;
+  if (!done) {
+    launch_final(L, logw > 0, cur, *challenge, ctx->final_out, ctx->stream);
+    ctx->launches++;
+  }
   return ZK_OK;
 }
 
@@ -298,11 +352,14 @@ int linear_prove_impl(zk_ctx* ctx, zk_comm* comm, uint32_t num_var, uint32_t num
   }
 
   Fr challenge = Fr::zero();
+  bool done = false;
   rc = linear_rounds(ctx, world > 1 ? comm : nullptr, L, n_local, cur, ping, pong, 0, fs, fs_user, tr, round_msgs,
-                     challenges, &challenge);
+                     challenges, &challenge, &done);
   if (rc) return rc;
-  launch_final(L, n_local > 0, cur, challenge, ctx->final_out, ctx->stream);
-  ctx->launches++;
+  if (!done) {
+    launch_final(L, n_local > 0, cur, challenge, ctx->final_out, ctx->stream);
+    ctx->launches++;
+  }
   if (world > 1) {
     rc = sharded_tail(ctx, comm, L, n_local, fs, fs_user, tr, round_msgs, challenges, &challenge);
     if (rc) return rc;

@@ -92,18 +92,17 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
     if (bad) return fail(ZK_ERR_ARG, "sparse_dense_prove: indices must be strictly increasing and below 2^num_var");
   }
 
-  enum { kSparse, kDenseFirst, kDense } mode = kSparse;
   bool pending = false;  // the dense table still has to be folded by pend_r (done together with the next fold)
   Fr pend_r = Fr::zero();
   auto other_buf = [&](const Fr* cur) { return cur == b_buf[0] ? b_buf[1] : b_buf[0]; };
-  int e = 0;            // which entry buffers are current
-  int d_toggle = 0;     // dense phase: next fold goes to ping (0) or pong (1)
+  int e = 0;             // which entry buffers are current
   uint32_t k_upper = K;  // bound on the live entry count
-  const Fr* d_cur[2] = {nullptr, nullptr};
   Fr challenge = Fr::zero();
   uint64_t S = size;
+  bool finished = false;  // the dense phase ran to the end (final values are in ctx->final_out)
   for (uint32_t round = 0; round < num_var; round++, S >>= 1) {
-    if (mode == kSparse && K && S <= dense_cap) {
+    if (K && S <= dense_cap) {
+      // hand over to the dense prover: scatter the entries into a table and run the remaining rounds
       if (pending) {  // not reached with the pairing rule below; kept so the hand-over never sees a stale table
         Fr* nb = other_buf(b_cur);
         launch_fold(b_cur, nb, pend_r, S, ctx->rs.max_blocks, s);
@@ -114,68 +113,60 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
       ZK_CUDA(cudaMemsetAsync(a_dense, 0, S * sizeof(Fr), s));
       launch_scatter(e_idx[e], e_val[e], counts + e, k_upper, a_dense, ctx->sm_count, s);
       ctx->launches++;
-      d_cur[0] = a_dense;
-      d_cur[1] = b_cur;
-      mode = kDenseFirst;
+      const Fr* d_cur[2] = {a_dense, b_cur};
+      bool done = false;
+      rc = linear_rounds(ctx, comm, 2, num_var - round, d_cur, d_ping, d_pong, round, fs, fs_user, tr, round_msgs,
+                         challenges, &challenge, &done);
+      if (rc) return rc;
+      if (!done) {
+        launch_final(2, true, d_cur, challenge, ctx->final_out, s);
+        ctx->launches++;
+      }
+      finished = true;
+      break;
     }
     const RoundScratch sc = ctx->next_msg_scratch(comm != nullptr);
-    if (mode == kSparse) {
-      // per live entry: index + value read, one 64-byte pair of b gathered
-      ctx->prof_begin(ZK_PROF_SPARSE_MSG, 104.0 * k_upper);
-      launch_sparse_msg(e_idx[e], e_val[e], counts + e, k_upper, b_cur, pending ? &pend_r : nullptr, sc, s);
-    } else if (mode == kDenseFirst) {
-      ctx->prof_begin(ZK_PROF_ROUND, 64.0 * 2 * (double)(S / 2));
-      launch_round(2, false, d_cur, nullptr, challenge, S / 2, sc, s);
-      mode = kDense;
-    } else {
-      Fr** dst = d_toggle ? d_pong : d_ping;
-      d_toggle ^= 1;
-      ctx->prof_begin(ZK_PROF_ROUND, 192.0 * 2 * (double)(S / 2));
-      launch_round(2, true, d_cur, dst, challenge, S / 2, sc, s);
-      d_cur[0] = dst[0];
-      d_cur[1] = dst[1];
-    }
+    // per live entry: index + value read, one 64-byte pair of b gathered
+    ctx->prof_begin(ZK_PROF_SPARSE_MSG, 104.0 * k_upper);
+    launch_sparse_msg(e_idx[e], e_val[e], counts + e, k_upper, b_cur, pending ? &pend_r : nullptr, sc, s);
     ctx->prof_end();
     ctx->launches++;
     rc = fs_round(ctx, comm, 3, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
     if (rc != ZK_OK) return rc;
-    if (mode == kSparse) {
-      // Fold of the dense table.  When the next round is still in entry form its message can fold
-      // the few values it needs on the fly, so this fold waits and is done together with the next
-      // one in a single pass over the table (k_fold2).
-      const bool next_sparse = round + 1 < num_var && (S / 2) > dense_cap;
-      if (pending) {
-        Fr* nb = other_buf(b_cur);
-        ctx->prof_begin(ZK_PROF_FOLD, 32.0 * (double)(2 * S + S / 2));
-        launch_fold2(b_cur, nb, pend_r, challenge, S / 2, ctx->rs.max_blocks, s);
-        ctx->prof_end();
-        ctx->launches++;
-        b_cur = nb;
-        pending = false;
-      } else if (next_sparse) {
-        pending = true;
-        pend_r = challenge;
-      } else {
-        Fr* nb = other_buf(b_cur);
-        ctx->prof_begin(ZK_PROF_FOLD, 96.0 * (double)(S / 2));
-        launch_fold(b_cur, nb, challenge, S / 2, ctx->rs.max_blocks, s);
-        ctx->prof_end();
-        ctx->launches++;
-        b_cur = nb;
-      }
-      ctx->prof_begin(ZK_PROF_SPARSE_FOLD, 80.0 * k_upper, 3);
-      ctx->launches += launch_sparse_fold(e_idx[e], e_val[e], counts + e, k_upper, challenge, block_counts,
-                                              e_idx[e ^ 1], e_val[e ^ 1], counts + (e ^ 1), s);
+    // Fold of the dense table.  When the next round is still in entry form its message can fold
+    // the few values it needs on the fly, so this fold waits and is done together with the next
+    // one in a single pass over the table (k_fold2).
+    const bool next_sparse = round + 1 < num_var && (!K || (S / 2) > dense_cap);
+    if (pending) {
+      Fr* nb = other_buf(b_cur);
+      ctx->prof_begin(ZK_PROF_FOLD, 32.0 * (double)(2 * S + S / 2));
+      launch_fold2(b_cur, nb, pend_r, challenge, S / 2, ctx->rs.max_blocks, s);
       ctx->prof_end();
-      e ^= 1;
-      if ((uint64_t)k_upper > S / 2) k_upper = (uint32_t)(S / 2);
+      ctx->launches++;
+      b_cur = nb;
+      pending = false;
+    } else if (next_sparse) {
+      pending = true;
+      pend_r = challenge;
+    } else {
+      Fr* nb = other_buf(b_cur);
+      ctx->prof_begin(ZK_PROF_FOLD, 96.0 * (double)(S / 2));
+      launch_fold(b_cur, nb, challenge, S / 2, ctx->rs.max_blocks, s);
+      ctx->prof_end();
+      ctx->launches++;
+      b_cur = nb;
     }
+    ctx->prof_begin(ZK_PROF_SPARSE_FOLD, 80.0 * k_upper, 3);
+    ctx->launches += launch_sparse_fold(e_idx[e], e_val[e], counts + e, k_upper, challenge, block_counts, e_idx[e ^ 1],
+                                        e_val[e ^ 1], counts + (e ^ 1), s);
+    ctx->prof_end();
+    e ^= 1;
+    if ((uint64_t)k_upper > S / 2) k_upper = (uint32_t)(S / 2);
   }
-  if (mode == kSparse)
+  if (!finished) {  // no entries, or no variables: the entry form ran to the end
     launch_sd_final(e_idx[e], e_val[e], counts + e, b_cur, ctx->final_out, s);
-  else
-    launch_final(2, true, d_cur, challenge, ctx->final_out, s);
-  ctx->launches++;
+    ctx->launches++;
+  }
   if (comm) {  // the remaining log2(world) variables: every rank finishes on the gathered values
     rc = sharded_tail(ctx, comm, 2, num_var, fs, fs_user, tr, round_msgs, challenges, &challenge);
     if (rc) return rc;

@@ -21,6 +21,7 @@ int zk_ctx::setup() {
   rs.sink.pub_flag = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(dev_view) + 16 * sizeof(Fr));
   rs.sink.seq = 0;
   ZK_CUDA(cudaMalloc(&final_out, sizeof(Fr) * 16));
+  ZK_CUDA(cudaMalloc(&tail_out, 8192));
   ZK_CUDA(cudaMalloc(&tail_buf, sizeof(Fr) * 64 * kMaxPolys * 4));
   ZK_CUDA(cudaHostAlloc(&host_small, 4096, cudaHostAllocDefault));
   ZK_CUDA(cudaStreamSynchronize(stream));
@@ -36,6 +37,7 @@ void zk_ctx::teardown() {
   if (mailbox) cudaFreeHost(mailbox);
   cudaFree(final_out);
   cudaFree(tail_buf);
+  cudaFree(tail_out);
   cudaFree(work);
   cudaFree(aux);
   if (host_small) cudaFreeHost(host_small);

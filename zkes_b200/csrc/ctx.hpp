@@ -58,6 +58,7 @@ struct zk_ctx {
   cudaStream_t stream = nullptr;
   zk::RoundScratch rs{};
   zk::Fr* final_out = nullptr;   // kMaxPolys + 1 elements
+  void* tail_out = nullptr;      // single-block tail kernel: messages, challenges, transcript state (8 KiB)
   zk::Fr* tail_buf = nullptr;    // sharded proves: gathered values and the last log2(world) rounds' tables
   void* host_small = nullptr;    // pinned, 4 KiB: round messages and other tiny read-backs
   void* mailbox = nullptr;       // pinned + mapped: message kernels publish here, the host polls
@@ -65,6 +66,7 @@ struct zk_ctx {
   size_t work_bytes = 0;
   void* aux = nullptr;           // second grow-only scratch (MSM sort and bucket storage)
   size_t aux_bytes = 0;
+  bool device_tail = false;      // run the last dense rounds in the single-block kernel (zk_set_option)
   MsmStatsPod last_msm;          // shape of the most recent MSM (window width, windows, entries)
   std::mutex mu;
   std::atomic<uint64_t> launches{0};
@@ -108,7 +110,7 @@ int fs_round(zk_ctx* ctx, zk_comm* comm, int n_msgs, uint32_t round, fs_round_fn
              uint64_t* round_msgs, uint64_t* challenges, Fr* challenge);
 int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr** cur, Fr** ping, Fr** pong,
                   uint32_t round_offset, fs_round_fn_t fs, void* fs_user, zk_transcript* tr, uint64_t* round_msgs,
-                  uint64_t* challenges, Fr* challenge);
+                  uint64_t* challenges, Fr* challenge, bool* finals_done);
 int sharded_tail(zk_ctx* ctx, zk_comm* comm, int L, uint32_t n_local, fs_round_fn_t fs, void* fs_user,
                  zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges, Fr* challenge);
 // comm.cu

@@ -53,6 +53,12 @@ void launch_general_msg(const Fr* const* tables_dev, const Fr* scalars, const Fr
 void launch_general_final(const Fr* const* tables_dev, const Fr* scalars, const Fr* eq, uint32_t n_terms,
                           uint32_t n_factors, Fr* table_vals, Fr* out, cudaStream_t s);
 
+// tail.cu
+struct StrobeState;
+constexpr uint32_t kTailMax = 1024;  // entries per table the single-block tail kernel takes over at
+int launch_tail(int num_poly, const Fr* const* src, uint32_t size, bool fold_first, const Fr& r, const StrobeState& st,
+                Fr* out_msgs, Fr* out_chal, Fr* out_final, StrobeState* out_st, cudaStream_t stream);
+
 // sparse.cu
 void launch_sparse_msg(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
                        const Fr* pending, const RoundScratch& sc, cudaStream_t s);

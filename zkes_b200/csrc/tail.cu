@@ -1,0 +1,159 @@
+// The last rounds of the dense prover in one launch: once the tables are small (at most
+// kTailMax entries each) a single block keeps them in shared memory and runs every remaining
+// round - message, Fiat-Shamir step, fold - plus the final product, so the per-round launch,
+// read-back and host transcript latency disappears.  Only for the built-in transcript: with a
+// caller-supplied callback the host has to see every message.
+// Rounds: linear_prover.rs:59-72; message :82-140; fold :151-178; final :181-190.
+#include "internal.hpp"
+#include "reduce.cuh"
+#include "strobe_dev.cuh"
+
+namespace zk {
+namespace {
+
+constexpr int kTailThreads = 256;
+
+template <int L>
+struct TailParams {
+  const Fr* src[L];
+  uint32_t size;    // entries per table on entry
+  int fold_first;   // bind `r` on the tables before the first message
+  Fr r;
+  StrobeState st;
+  Fr* out_msgs;     // rounds * (L + 1)
+  Fr* out_chal;     // rounds
+  Fr* out_final;    // L table values, then their product
+  StrobeState* out_st;
+};
+
+template <int L>
+__global__ void __launch_bounds__(kTailThreads) k_tail(const TailParams<L> p) {
+  extern __shared__ uint4 tail_smem[];
+  Fr* A = reinterpret_cast<Fr*>(tail_smem);         // L * size
+  Fr* B = A + (size_t)L * p.size;                   // L * size / 2
+  Fr* red = B + (size_t)L * (p.size / 2 + 1);       // (kTailThreads / 32) * (L + 1)
+  Fr* chal = red + (kTailThreads / 32) * (L + 1);   // 1
+  __shared__ StrobeState st;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  for (uint32_t i = tid; i < p.size; i += kTailThreads)
+#pragma unroll
+    for (int t = 0; t < L; t++) A[(size_t)t * p.size + i] = p.src[t][i];
+  if (tid == 0) {
+    st = p.st;
+    chal[0] = p.r;
+  }
+  __syncthreads();
+
+  Fr* cur = A;
+  Fr* nxt = B;
+  uint32_t cur_size = p.size, cur_stride = p.size, nxt_stride = p.size / 2 + 1;
+  bool fold_now = p.fold_first != 0;
+  uint32_t round = 0;
+  while (true) {
+    if (fold_now) {
+      const Fr r = chal[0];
+      const uint32_t half = cur_size >> 1;
+      for (uint32_t y = tid; y < half; y += kTailThreads)
+#pragma unroll
+        for (int t = 0; t < L; t++) {
+          const Fr a0 = cur[(size_t)t * cur_stride + 2 * y], a1 = cur[(size_t)t * cur_stride + 2 * y + 1];
+          nxt[(size_t)t * nxt_stride + y] = add(a0, mul(r, sub(a1, a0)));
+        }
+      __syncthreads();
+      Fr* tmp = cur; cur = nxt; nxt = tmp;
+      const uint32_t ts = cur_stride; cur_stride = nxt_stride; nxt_stride = ts;
+      cur_size = half;
+    }
+    if (cur_size <= 1) break;
+    // ---- message of this round
+    Fr s[L + 1];
+#pragma unroll
+    for (int c = 0; c <= L; c++) s[c] = Fr::zero();
+    const uint32_t pairs = cur_size >> 1;
+    for (uint32_t y = tid; y < pairs; y += kTailThreads) {
+      Fr v[L], d[L];
+#pragma unroll
+      for (int t = 0; t < L; t++) {
+        v[t] = cur[(size_t)t * cur_stride + 2 * y];
+        d[t] = sub(cur[(size_t)t * cur_stride + 2 * y + 1], v[t]);
+      }
+#pragma unroll
+      for (int c = 0; c <= L; c++) {
+        Fr prod = v[0];
+#pragma unroll
+        for (int t = 1; t < L; t++) prod = mul(prod, v[t]);
+        s[c] = add(s[c], prod);
+        if (c < L) {
+#pragma unroll
+          for (int t = 0; t < L; t++) v[t] = add(v[t], d[t]);
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c <= L; c++) {
+      const Fr t = warp_sum(s[c]);
+      if (lane == 0) red[warp * (L + 1) + c] = t;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      for (int c = 0; c <= L; c++) {
+        Fr t = red[c];
+        for (int w = 1; w < kTailThreads / 32; w++) t = add(t, red[w * (L + 1) + c]);
+        p.out_msgs[(size_t)round * (L + 1) + c] = t;
+        transcript_append_scalar_dev(st, "round_message", 13, t);
+      }
+      const Fr ch = transcript_challenge_scalar_dev(st, "challenge", 9);
+      p.out_chal[round] = ch;
+      chal[0] = ch;
+    }
+    __syncthreads();
+    fold_now = true;
+    round++;
+  }
+  if (tid == 0) {
+    Fr prod = Fr::one();
+    for (int t = 0; t < L; t++) {
+      const Fr a = cur[(size_t)t * cur_stride];
+      p.out_final[t] = a;
+      prod = mul(prod, a);
+    }
+    p.out_final[L] = prod;
+    *p.out_st = st;
+  }
+}
+
+template <int L>
+int launch_tail_t(const Fr* const* src, uint32_t size, bool fold_first, const Fr& r, const StrobeState& st, Fr* out_msgs,
+                  Fr* out_chal, Fr* out_final, StrobeState* out_st, cudaStream_t stream) {
+  TailParams<L> p;
+  for (int i = 0; i < L; i++) p.src[i] = src[i];
+  p.size = size;
+  p.fold_first = fold_first ? 1 : 0;
+  p.r = r;
+  p.st = st;
+  p.out_msgs = out_msgs;
+  p.out_chal = out_chal;
+  p.out_final = out_final;
+  p.out_st = out_st;
+  const size_t smem = ((size_t)L * size + (size_t)L * (size / 2 + 1) + (kTailThreads / 32) * (L + 1) + 2) * sizeof(Fr);
+  // the opt-in is per device, and a process may hold contexts on several: set it on every launch
+  if (cudaFuncSetAttribute(k_tail<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return -3;
+  k_tail<L><<<1, kTailThreads, smem, stream>>>(p);
+  return 0;
+}
+
+}  // namespace
+
+int launch_tail(int num_poly, const Fr* const* src, uint32_t size, bool fold_first, const Fr& r, const StrobeState& st,
+                Fr* out_msgs, Fr* out_chal, Fr* out_final, StrobeState* out_st, cudaStream_t stream) {
+  switch (num_poly) {
+    case 1: return launch_tail_t<1>(src, size, fold_first, r, st, out_msgs, out_chal, out_final, out_st, stream);
+    case 2: return launch_tail_t<2>(src, size, fold_first, r, st, out_msgs, out_chal, out_final, out_st, stream);
+    case 3: return launch_tail_t<3>(src, size, fold_first, r, st, out_msgs, out_chal, out_final, out_st, stream);
+    case 4: return launch_tail_t<4>(src, size, fold_first, r, st, out_msgs, out_chal, out_final, out_st, stream);
+    default: return -1;
+  }
+}
+
+}  // namespace zk
