@@ -45,6 +45,7 @@ def parse_args():
     ap.add_argument("--nnz-log", type=int, default=NNZ_LOG)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-msm", action="store_true", help="skip the KZH2 commit (MSM points/s) leg")
     return ap.parse_args()
 
 
@@ -321,6 +322,63 @@ def gpu_arm(args):
     return ctx, rank, world, ms_per_step, value, launches, prof, e2e, clocks
 
 
+def msm_leg(ctx):
+    """Second half of the metric: KZH2 commit of 2^24 int8 evaluations on a 2^12 x 2^12 split
+    (BASELINE.json config 3), points/s = 2 * 2^24 / t, with the integer-pipe fraction."""
+    import numpy as np
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from zkes_b200 import DenseMLPoly, curve, kzh
+    from zkes_b200._lib import check, lib
+    from zkes_b200.field import from_mont_array
+
+    n = 24
+
+    def uniform(stream, count):
+        t = torch.empty((count, 4), dtype=torch.int64, device="cuda")
+        torch.cuda.synchronize()
+        check(lib.zk_gen_uniform_fr(ctx.handle, 2, stream, 0, count, t.data_ptr()), "zk_gen_uniform_fr")
+        return from_mont_array(t.cpu().numpy().view(np.uint64))
+
+    tau_x, tau_y, alpha = uniform(1, 1 << 12), uniform(2, 1 << 12), uniform(3, 1)[0]
+    # g = 2 * (1, 2) on y^2 = x^3 + 3, in affine form
+    g = (1368015179489954701390400359078579693043519447331113978918064868415326638035,
+         9918110051302171585080402603319702774565515993150576347155970296011118125764)
+    t0 = time.perf_counter()
+    srs = kzh.KZHSRS.setup(ctx, 2, n, g, tau_x, tau_y, alpha=alpha)
+    setup_s = time.perf_counter() - t0
+    f = torch.empty((1 << n, 4), dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    check(lib.zk_gen_small_fr(ctx.handle, 2, 7, 0, 1 << n, 8, f.data_ptr()), "zk_gen_small_fr")
+    poly = DenseMLPoly(n, device_ptr=f.data_ptr())
+    stream = torch.cuda.ExternalStream(lib.zk_stream(ctx.handle))
+    kzh.commit(ctx, srs, poly)  # warm-up (allocates scratch)
+    kzh.commit(ctx, srs, poly)
+    steps = 5
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        kzh.commit(ctx, srs, poly)
+    e1.record(stream)
+    e1.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    stats = curve.last_stats(ctx)
+    ms_imad, ops = ctypes.c_float(), ctypes.c_double()
+    check(lib.zk_microbench(ctx.handle, 0, 148 * 8, 256, 4000, ctypes.byref(ms_imad), ctypes.byref(ops)), "zk_microbench")
+    imad_peak = ops.value / (ms_imad.value * 1e-3)
+    pairs = 2.0 * (1 << n)
+    mac32 = pairs * (255.0 / 256.0) * 1360.0  # one mixed addition (10 products of 136) per non-zero digit
+    srs.close()
+    return {"metric": "kzh2_commit_msm_points_per_s", "value": pairs / (ms * 1e-3), "unit": "points/s", "ms_per_commit": ms,
+            "config": "KZH2 commit, 2^24 int8 evaluations, 2^12 x 2^12 split, seed 2 (C over 2^24 points + 2^12 rows of 2^12)",
+            "srs_setup_s": setup_s, "window_bits_last_msm": stats["window_bits"],
+            "integer_roofline": {"bound": "imad", "achieved_mac32_per_s": mac32 / (ms * 1e-3), "peak_mac32_per_s": imad_peak,
+                                 "frac": mac32 / (ms * 1e-3) / imad_peak,
+                                 "note": "algorithmic 32x32+64 multiply-adds (1360 per mixed addition) over the measured "
+                                         "32-bit multiply-add rate of this GPU (zk_microbench kind 0)"}}
+
+
 def measured_peak_gbs():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -363,12 +421,15 @@ def main():
                "kind": "port",
                "sample": f"one prove on num_var={CPU_SAMPLE_VAR}, nnz=2^{CPU_SAMPLE_NNZ_LOG} (same density), mean of 2 "
                          f"runs, {sec:.2f} s each; CPU restatement of the reference prover, not arkworks"}
+    msm = None
+    if world == 1 and not args.no_msm:
+        msm = msm_leg(ctx)
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u256 (BN254 Fr, Montgomery, 8x32-bit limbs)", "data": "synthetic",
         "config": workload_config(args.num_var, args.nnz_log, world),
-        "gpu_launches": launches, "clocks": clocks, "e2e": e2e, "roofline": roofline, "cpu_baseline": cpu,
+        "gpu_launches": launches, "clocks": clocks, "e2e": e2e, "roofline": roofline, "cpu_baseline": cpu, "msm": msm,
     }
     print(json.dumps(out))
 
