@@ -192,6 +192,11 @@ int zk_fold_lsb(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem
  * out[lo] = sum_hi eq(point)[hi] * evals[hi * 2^(n-k) + lo]. */
 int zk_fix_from_right(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, uint32_t k, const uint64_t* point,
                       uint64_t* out, zk_mem out_mem);
+/* out[lo] = sum_hi weights[hi] * evals[hi * 2^(n-k) + lo]: the contraction inside
+ * fix_variables_from_right (poly.rs:719-741) with caller-given weights instead of an eq table
+ * (no separate counterpart in the reference; used for trapdoor checksums of commitments). */
+int zk_weighted_fold_from_right(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, uint32_t k,
+                                const uint64_t* weights, zk_mem weights_mem, uint64_t* out, zk_mem out_mem);
 /* evaluate_lagrange_basis / precompute_eq, src/util/poly.rs:573-618, 657-699: out[x] = eq(x, point)
  * for x < 2^k, variable 0 in index bit 0; k = 0 gives {1}.  point is a host array. */
 int zk_eq_table(zk_ctx* ctx, uint32_t k, const uint64_t* point, uint64_t* out, zk_mem out_mem);
@@ -286,6 +291,12 @@ int zk_gen_uniform_fr(zk_ctx* ctx, uint64_t seed, uint64_t stream, uint64_t star
  * a signed `bits`-bit integer lifted into Fr (negatives as r - |v|), as quantised weights and
  * activations are (src/bin/gpt2.rs:44-49). */
 int zk_gen_small_fr(zk_ctx* ctx, uint64_t seed, uint64_t stream, uint64_t start, uint64_t count, int bits,
+                    uint64_t* out_dev);
+
+/* Fixed-point activations: element i = round(N(0,1) * 2^scale_log2) (Box-Muller on two keystream
+ * words of block start+i, computed in double precision on the device), clamped to +-32767 and
+ * lifted into Fr.  Device-generated only: libm on a CPU need not round identically. */
+int zk_gen_gauss_fr(zk_ctx* ctx, uint64_t seed, uint64_t stream, uint64_t start, uint64_t count, int scale_log2,
                     uint64_t* out_dev);
 
 /* ---- measurement ---------------------------------------------------------------------- */

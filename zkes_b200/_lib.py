@@ -66,6 +66,9 @@ SIGNATURES = {
     "zk_kzh3_open": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p, c_int, c_void_p, c_uint32, c_void_p, c_void_p,
                              c_void_p, c_void_p]),
     "zk_fold_lsb_static": (c_int, [c_uint32, c_void_p, c_uint32, c_void_p, c_void_p, c_void_p]),
+    "zk_gen_gauss_fr": (c_int, [c_void_p, c_uint64, c_uint64, c_uint64, c_uint64, c_int, c_void_p]),
+    "zk_weighted_fold_from_right": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_int, c_void_p,
+                                            c_int]),
     "zk_gen_uniform_fr": (c_int, [c_void_p, c_uint64, c_uint64, c_uint64, c_uint64, c_void_p]),
     "zk_gen_small_fr": (c_int, [c_void_p, c_uint64, c_uint64, c_uint64, c_uint64, c_int, c_void_p]),
     "zk_sumcheck_sparse_bool_prove": (c_int, [c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p,

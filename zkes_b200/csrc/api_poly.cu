@@ -56,6 +56,38 @@ int zk_eq_table(zk_ctx* ctx, uint32_t k, const uint64_t* point, uint64_t* out, z
   return ZK_OK;
 }
 
+int zk_weighted_fold_from_right(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, uint32_t k,
+                                const uint64_t* weights, zk_mem weights_mem, uint64_t* out, zk_mem out_mem) {
+  if (!ctx || !evals || !out || !weights) return fail(ZK_ERR_ARG, "weighted_fold_from_right: NULL argument");
+  if (k > n || n > 34) return fail(ZK_ERR_ARG, "weighted_fold_from_right: bad dimensions");
+  CtxLock lk(ctx);
+  cudaStream_t s = ctx->stream;
+  const uint64_t size = 1ull << n, lo_n = 1ull << (n - k), hi_n = 1ull << k;
+  const size_t in_elems = evals_mem == ZK_MEM_HOST ? size : 0;
+  const size_t w_elems = weights_mem == ZK_MEM_HOST ? hi_n : 0;
+  const size_t out_elems = out_mem == ZK_MEM_HOST ? lo_n : 0;
+  const size_t part = (size_t)from_right_splits(lo_n, hi_n, ctx->sm_count) * lo_n;
+  Fr* base = nullptr;
+  int rc = ctx->reserve_work((in_elems + w_elems + out_elems + part + 16) * sizeof(Fr), (void**)&base);
+  if (rc) return rc;
+  const Fr* f = reinterpret_cast<const Fr*>(evals);
+  const Fr* w = reinterpret_cast<const Fr*>(weights);
+  if (evals_mem == ZK_MEM_HOST) {
+    ZK_CUDA(cudaMemcpyAsync(base, evals, size * sizeof(Fr), cudaMemcpyHostToDevice, s));
+    f = base;
+  }
+  if (weights_mem == ZK_MEM_HOST) {
+    ZK_CUDA(cudaMemcpyAsync(base + in_elems, weights, hi_n * sizeof(Fr), cudaMemcpyHostToDevice, s));
+    w = base + in_elems;
+  }
+  Fr* d_out = out_mem == ZK_MEM_HOST ? base + in_elems + w_elems : reinterpret_cast<Fr*>(out);
+  ctx->launches += launch_from_right(f, w, lo_n, hi_n, base + in_elems + w_elems + out_elems, d_out, ctx->sm_count, s);
+  ZK_CUDA(cudaGetLastError());
+  if (out_mem == ZK_MEM_HOST) ZK_CUDA(cudaMemcpyAsync(out, d_out, lo_n * sizeof(Fr), cudaMemcpyDeviceToHost, s));
+  ZK_CUDA(cudaStreamSynchronize(s));
+  return ZK_OK;
+}
+
 int zk_fix_from_right(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, uint32_t k, const uint64_t* point,
                       uint64_t* out, zk_mem out_mem) {
   if (!ctx || !evals || !out || (k && !point)) return fail(ZK_ERR_ARG, "fix_from_right: NULL argument");

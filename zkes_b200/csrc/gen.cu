@@ -71,7 +71,44 @@ __global__ void k_gen_small(uint64_t seed, uint64_t stream, uint64_t start, uint
   }
 }
 
+// round(N(0,1) * 2^scale_log2) from a Box-Muller transform of two keystream words, clamped to int16.
+__global__ void k_gen_gauss(uint64_t seed, uint64_t stream, uint64_t start, uint64_t count, int scale_log2, Fr* out) {
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (uint64_t)gridDim.x * blockDim.x) {
+    uint32_t ks[16];
+    chacha_block(seed, stream, (uint32_t)(start + i), ks);
+    const double u1 = ((double)ks[0] + 1.0) / 4294967297.0, u2 = (double)ks[1] / 4294967296.0;
+    double z = sqrt(-2.0 * log(u1)) * cospi(2.0 * u2) * (double)(1 << scale_log2);
+    z = rint(z);
+    if (z > 32767.0) z = 32767.0;
+    if (z < -32767.0) z = -32767.0;
+    const int32_t sv = (int32_t)z;
+    Fr c = Fr::zero();
+    c.v[0] = (uint32_t)(sv < 0 ? -sv : sv);
+    Fr v = to_mont(c);
+    if (sv < 0) v = neg(v);
+    uint4 a, b;
+    fr_to_chunks(v, a, b);
+    reinterpret_cast<uint4*>(out + i)[0] = a;
+    reinterpret_cast<uint4*>(out + i)[1] = b;
+  }
+}
+
 }  // namespace
+
+extern "C" int zk_gen_gauss_fr(zk_ctx* ctx, uint64_t seed, uint64_t stream, uint64_t start, uint64_t count, int scale_log2,
+                               uint64_t* out_dev) {
+  if (!ctx || !out_dev) return fail(ZK_ERR_ARG, "gen_gauss_fr: NULL argument");
+  if (scale_log2 < 0 || scale_log2 > 14) return fail(ZK_ERR_ARG, "gen_gauss_fr: scale_log2 must be in [0, 14]");
+  if (start + count > (1ull << 32)) return fail(ZK_ERR_ARG, "gen_gauss_fr: the block counter is 32 bits");
+  CtxLock lk(ctx);
+  if (count) {
+    k_gen_gauss<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(seed, stream, start, count, scale_log2, reinterpret_cast<Fr*>(out_dev));
+    ctx->launches++;
+  }
+  ZK_CUDA(cudaGetLastError());
+  ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+  return ZK_OK;
+}
 
 extern "C" int zk_gen_uniform_fr(zk_ctx* ctx, uint64_t seed, uint64_t stream, uint64_t start, uint64_t count,
                                  uint64_t* out_dev) {

@@ -337,6 +337,15 @@ __global__ void k_msm_combine(const Xyzz* __restrict__ window_sums, uint32_t row
   out[row] = to_jacobian(acc);
 }
 
+// 64-bit total of the per-bucket counts (the 32-bit prefix sums would wrap silently past 2^32).
+__global__ void k_total64(const uint32_t* __restrict__ counts, uint32_t n, unsigned long long* total) {
+  unsigned long long s = 0;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) s += counts[i];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
+  if ((threadIdx.x & 31) == 0 && s) atomicAdd(total, s);
+}
+
 __global__ void k_set_infinity(Jacobian* out, uint32_t rows) {
   const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row < rows) out[row] = to_jacobian(Xyzz::inf());
@@ -345,10 +354,12 @@ __global__ void k_set_infinity(Jacobian* out, uint32_t rows) {
 }  // namespace
 
 // Window width for n points per row whose scalars have at most max_bits magnitude bits.
-static int pick_window(uint64_t n, int max_bits) {
+static int pick_window(uint64_t n, uint32_t rows, int max_bits) {
   int lg = 0;
   while ((1ull << (lg + 1)) <= n) lg++;
-  int w = lg - 2;
+  // a row costs windows * (n + 2 * 2^(w-1)) additions; with many rows the buckets (128 bytes each, per
+  // row and window) also have to fit in memory, so rows use a narrower window
+  int w = rows > 1 ? lg - 4 : lg - 2;
   if (w > 16) w = 16;
   if (w < 3) w = 3;
   if (w > max_bits + 1) w = max_bits + 1;
@@ -384,7 +395,7 @@ int msm_run(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const Fr* 
     ctx->launches++;
     return 0;
   }
-  const int w = pick_window(n, (int)max_bits);
+  const int w = pick_window(n, rows, (int)max_bits);
   const int k_windows = ((int)max_bits + 1 + w - 1) / w;
   const uint32_t half = 1u << (w - 1);
   const uint64_t n_buckets64 = (uint64_t)rows * k_windows * half;
@@ -392,8 +403,10 @@ int msm_run(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const Fr* 
   const uint32_t n_buckets = (uint32_t)n_buckets64;
 
   // ---- scratch layout (second scratch region of the context; the first holds caller data)
-  const uint64_t max_entries = total * (uint64_t)k_windows;
-  if (max_entries >= (1ull << 32)) return fail(-1, "msm: %llu digit entries exceed 2^32; split the call", (unsigned long long)max_entries);
+  // worst case: every scalar has a non-zero digit in every window; small scalars have fewer, and the
+  // real total is checked after the count pass (entry slots are 32-bit)
+  uint64_t max_entries = total * (uint64_t)k_windows;
+  if (max_entries > 0xffffffffull) max_entries = 0xffffffffull;
   size_t need = align256((n_buckets + 2) * 4ull) * 2 + align256(scan_scratch_elems(n_buckets + 1) * 4) +
                 align256((size_t)n_buckets * sizeof(Xyzz)) + align256((size_t)rows * k_windows * sizeof(Xyzz)) + 4096;
   char* base = nullptr;
@@ -425,6 +438,15 @@ int msm_run(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const Fr* 
   else
     k_msm_digits<0><<<sm * 8, 256, 0, s>>>(scalars, n, rows, w, k_windows, offsets, nullptr);
   ctx->launches++;
+  unsigned long long* d_total = reinterpret_cast<unsigned long long*>(ctx->rs.sink.counter + 10);
+  ZK_CUDA(cudaMemsetAsync(d_total, 0, 8, s));
+  k_total64<<<sm * 4, 256, 0, s>>>(offsets, n_buckets, d_total);
+  ctx->launches++;
+  ZK_CUDA(cudaMemcpyAsync(ctx->host_small, d_total, 8, cudaMemcpyDeviceToHost, s));
+  ZK_CUDA(cudaStreamSynchronize(s));
+  unsigned long long total64 = 0;
+  memcpy(&total64, ctx->host_small, 8);
+  if (total64 > 0xffffffffull) return fail(-1, "msm: %llu digit entries exceed 2^32 - 1; split the call", total64);
   ctx->launches += exclusive_scan_u32(offsets, n_buckets, scan_tmp, true, s);
   ZK_CUDA(cudaMemcpyAsync(cursor, offsets, (n_buckets + 1) * 4ull, cudaMemcpyDeviceToDevice, s));
   if (small_keys)
