@@ -248,17 +248,39 @@ __global__ void __launch_bounds__(128) k_msm_accumulate(const Affine* __restrict
     st_xyzz(bucket_sums + b, acc);
 }
 
-// One warp per bucket that crosses chunk borders.
-__global__ void __launch_bounds__(128) k_msm_fixup(const uint32_t* __restrict__ offsets, uint32_t n_buckets, uint32_t seg,
-                                                   Xyzz* bucket_sums, const Xyzz* heads, const Xyzz* tails) {
-  __shared__ Xyzz sh[4][32];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint32_t b = blockIdx.x * 4 + warp;
+constexpr uint32_t kFewPieces = 8;
+
+// One thread per bucket: buckets cut into at most kFewPieces pieces are summed in place; longer
+// ones are left to the warp-per-bucket kernel below (found through the `many` list).
+__global__ void __launch_bounds__(256) k_msm_fixup_few(const uint32_t* __restrict__ offsets, uint32_t n_buckets, uint32_t seg,
+                                                       Xyzz* bucket_sums, const Xyzz* heads, const Xyzz* tails,
+                                                       uint32_t* many, uint32_t* n_many) {
+  const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= n_buckets) return;
   const uint32_t s = offsets[b], e = offsets[b + 1];
   if (e <= s) return;
   const uint32_t c0 = s / seg, c1 = (e - 1) / seg;
   if (c0 == c1) return;
+  if (c1 - c0 >= kFewPieces) {
+    many[atomicAdd(n_many, 1u)] = b;
+    return;
+  }
+  Xyzz acc = ld_xyzz(tails + c0);
+  for (uint32_t c = c0 + 1; c <= c1; c++) acc = add(acc, ld_xyzz(heads + c));
+  st_xyzz(bucket_sums + b, acc);
+}
+
+// One warp per listed bucket (those cut into many pieces).
+__global__ void __launch_bounds__(128) k_msm_fixup(const uint32_t* __restrict__ offsets, const uint32_t* __restrict__ many,
+                                                   const uint32_t* __restrict__ n_many, uint32_t seg,
+                                                   Xyzz* bucket_sums, const Xyzz* heads, const Xyzz* tails) {
+  __shared__ Xyzz sh[4][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t total = *n_many;
+  for (uint32_t item = blockIdx.x * 4 + warp; item < total; item += gridDim.x * 4) {
+  const uint32_t b = many[item];
+  const uint32_t s = offsets[b], e = offsets[b + 1];
+  const uint32_t c0 = s / seg, c1 = (e - 1) / seg;
   // pieces: tail of chunk c0, heads of chunks c0+1 .. c1
   Xyzz acc = Xyzz::inf();
   for (uint32_t c = c0 + lane; c <= c1; c += 32) acc = add(acc, ld_xyzz(c == c0 ? tails + c : heads + c));
@@ -272,6 +294,8 @@ __global__ void __launch_bounds__(128) k_msm_fixup(const uint32_t* __restrict__ 
     __syncwarp();
   }
   if (lane == 0) st_xyzz(bucket_sums + b, acc);
+  __syncwarp();
+  }
 }
 
 // Few, long buckets (one narrow window over millions of points): one block per bucket.
@@ -468,14 +492,24 @@ int msm_run(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const Fr* 
     n_chunks = (n_entries + seg - 1) / seg;
     k_msm_accumulate<<<(n_chunks + 127) / 128, 128, 0, s>>>(bases, gather, entries, offsets, n_buckets, n_entries, seg,
                                                            n_chunks, bucket_sums, heads, tails);
-    if (n_buckets <= 8192)
+    if (n_buckets <= 8192) {
       k_msm_fixup_block<<<n_buckets, 128, 0, s>>>(offsets, seg, bucket_sums, heads, tails);
-    else
-      k_msm_fixup<<<(n_buckets + 3) / 4, 128, 0, s>>>(offsets, n_buckets, seg, bucket_sums, heads, tails);
+    } else {
+      // cursor[] is free again after the scatter: reuse it as the list of long buckets
+      uint32_t* n_many = ctx->rs.sink.counter + 12;
+      ZK_CUDA(cudaMemsetAsync(n_many, 0, 4, s));
+      k_msm_fixup_few<<<(n_buckets + 255) / 256, 256, 0, s>>>(offsets, n_buckets, seg, bucket_sums, heads, tails, cursor, n_many);
+      k_msm_fixup<<<sm * 4, 128, 0, s>>>(offsets, cursor, n_many, seg, bucket_sums, heads, tails);
+      ctx->launches++;
+    }
     ctx->launches += 2;
   }
   // ---- reduce buckets, combine windows
-  uint32_t threads = half / 4;
+  // buckets per thread: the running sums cost 2 additions per bucket, the thread's offset multiple and
+  // the block tree are per-thread overhead, so threads take up to 32 buckets while enough threads remain
+  uint32_t per_thread = 4;
+  while (per_thread < 32 && (uint64_t)rows * k_windows * (half / (per_thread * 2)) >= 200000) per_thread *= 2;
+  uint32_t threads = half / per_thread;
   if (threads < 32) threads = 32;
   if (threads > 256) threads = 256;
   k_msm_bucket_reduce<<<rows * k_windows, threads, threads * sizeof(Xyzz), s>>>(bucket_sums, half, window_sums);
