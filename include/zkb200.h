@@ -265,6 +265,18 @@ int zk_kzh3_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uint
                  const uint64_t* point, uint32_t point_len, const uint64_t* d_x_jac, uint64_t* d_y_jac_out,
                  uint64_t* c_y_affine_out, uint64_t* f_star_out);
 
+/* sparse_kzh2_commit (src/crypto/polycommit/sparse_kzh2.rs:14-82) / sparse_kzh3_commit (sparse_kzh3.rs:32-110):
+ * the polynomial is given by nnz (index, value) pairs with distinct indices below 2^n (host arrays). */
+int zk_sparse_kzh_commit(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const uint64_t* indices, const uint64_t* vals,
+                         uint64_t* c_affine_out, uint64_t* d_x_jac_out);
+/* sparse_kzh2_open (sparse_kzh2.rs:84-127): f_star_out receives 2^y_log elements. */
+int zk_sparse_kzh2_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const uint64_t* indices, const uint64_t* vals,
+                        const uint64_t* point, uint32_t point_len, uint64_t* f_star_out);
+/* sparse_kzh3_open (sparse_kzh3.rs:112-232); a short point is padded with trailing zeros (:124-131). */
+int zk_sparse_kzh3_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const uint64_t* indices, const uint64_t* vals,
+                        const uint64_t* point, uint32_t point_len, const uint64_t* d_x_jac, uint64_t* d_y_jac_out,
+                        uint64_t* c_y_affine_out, uint64_t* f_star_out);
+
 /* Fold for callers that cannot allocate device memory (this entry point has no counterpart in
  * the reference).  Same result as zk_fold_lsb for tables of at most 2^ZK_FOLD_STATIC_MAX_VARS
  * elements; larger n is rejected with ZK_ERR_ARG.  evals_dev and out_dev are device buffers

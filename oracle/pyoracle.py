@@ -726,3 +726,57 @@ def kzh3_open(srs, point, d_x, evals):
     f_star = fix_variables_from_right(f, r_y + r_x)
     c_y = g1_msm(d_x, eq_x)
     return list(d_x), d_y, c_y, f_star
+
+
+# ----------------------------------------------------------------------------- sparse KZH
+def sparse_kzh2_commit(srs, evaluations: dict):
+    """src/crypto/polycommit/sparse_kzh2.rs:14-82: evaluations = {index: value}."""
+    idx, sc = list(evaluations.keys()), list(evaluations.values())
+    c = g1_msm([srs.h_xy[i] for i in idx], sc)
+    ym = (1 << srs.y_log) - 1
+    d_x = []
+    for x in range(1 << srs.x_log):
+        ent = [(i & ym, v) for i, v in evaluations.items() if (i >> srs.y_log) == x]
+        d_x.append(g1_msm([srs.h_y[y] for y, _ in ent], [v for _, v in ent]))
+    return c, d_x
+
+
+def sparse_kzh2_open(srs, point, d_x, evaluations: dict):
+    """sparse_kzh2.rs:84-127."""
+    r_y, r_x = split_input([srs.y_log, srs.x_log], point)
+    eq = evaluate_lagrange_basis(r_x)
+    f_star = [0] * (1 << srs.y_log)
+    for i, v in evaluations.items():
+        f_star[i & ((1 << srs.y_log) - 1)] = (f_star[i & ((1 << srs.y_log) - 1)] + eq[i >> srs.y_log] * v) % R_MOD
+    return list(d_x), f_star
+
+
+def sparse_kzh3_commit(srs, evaluations: dict):
+    """src/crypto/polycommit/sparse_kzh3.rs:32-110."""
+    idx, sc = list(evaluations.keys()), list(evaluations.values())
+    c = g1_msm([srs.h_xyz[i] for i in idx], sc)
+    low = srs.y_log + srs.z_log
+    d_x = []
+    for x in range(1 << srs.x_log):
+        ent = [(i & ((1 << low) - 1), v) for i, v in evaluations.items() if (i >> low) == x]
+        d_x.append(g1_msm([srs.h_yz[j] for j, _ in ent], [v for _, v in ent]))
+    return c, d_x
+
+
+def sparse_kzh3_open(srs, point, d_x, evaluations: dict):
+    """sparse_kzh3.rs:112-232: the point is padded with TRAILING zeros here (:124-131)."""
+    zl, yl, xl = srs.z_log, srs.y_log, srs.x_log
+    n = zl + yl + xl
+    pt = list(point)[:n] + [0] * max(0, n - len(point))
+    eq_x = evaluate_lagrange_basis(pt[zl + yl:])
+    eq_xy = evaluate_lagrange_basis(pt[zl:])
+    f_prime = [0] * (1 << (yl + zl))
+    f_star = [0] * (1 << zl)
+    for i, v in evaluations.items():
+        z, y, x = i & ((1 << zl) - 1), (i >> zl) & ((1 << yl) - 1), i >> (zl + yl)
+        f_prime[z + (y << zl)] = (f_prime[z + (y << zl)] + eq_x[x] * v) % R_MOD
+        f_star[z] = (f_star[z] + eq_xy[y + (x << yl)] * v) % R_MOD
+    dz = 1 << zl
+    d_y = [g1_msm(srs.h_z, f_prime[i * dz:(i + 1) * dz]) for i in range(1 << yl)]
+    c_y = g1_msm(d_x, eq_x)
+    return list(d_x), d_y, c_y, f_star

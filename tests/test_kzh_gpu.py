@@ -102,3 +102,35 @@ def test_kzh_argument_errors(ctx):
     with pytest.raises(ZkError):
         kzh.kzh3_open(ctx, srs, [1, 2], kzh.commit(ctx, srs, DenseMLPoly.from_evaluations([1, 2, 3, 4])),
                       DenseMLPoly.from_evaluations([1, 2, 3, 4]))
+
+
+@pytest.mark.parametrize("dims,n,nnz,ones", [(2, 4, 5, False), (2, 6, 20, True), (3, 5, 9, False), (3, 7, 40, True), (2, 6, 0, False)])
+def test_sparse_kzh_commit_open(ctx, dims, n, nnz, ones):
+    """sparse_kzh2 / sparse_kzh3 commit and open (sparse_kzh2.rs:14-127, sparse_kzh3.rs:32-232); `ones`
+    mirrors the selection polynomials of the range proofs (all-one values)."""
+    rnd = random.Random(1000 * dims + n)
+    if dims == 2:
+        xl, yl = o.kzh2_degrees(n)
+        gk, tx, ty, rest = trapdoors(7, 1 << xl, 1 << yl)
+        osrs = o.KZH2SRS(n, gk, tx, ty, rest[0])
+        srs = kzh.KZHSRS.upload(ctx, 2, n, osrs.h_xy, osrs.h_y)
+    else:
+        xl, yl, zl = o.kzh3_degrees(n)
+        gk, tx, ty, tz = trapdoors(8, 1 << xl, 1 << yl, 1 << zl)
+        osrs = o.KZH3SRS(n, gk, tx, ty, tz[:1 << zl])
+        srs = kzh.KZHSRS.upload(ctx, 3, n, osrs.h_xyz, osrs.h_yz, osrs.h_z)
+    ev = {i: (1 if ones else rnd.randrange(M)) for i in rnd.sample(range(1 << n), nnz)}
+    com = kzh.sparse_commit(ctx, srs, ev)
+    oc, odx = (o.sparse_kzh2_commit if dims == 2 else o.sparse_kzh3_commit)(osrs, ev)
+    assert com.c == oc and com.d_x == odx
+    dense = [ev.get(i, 0) for i in range(1 << n)]
+    assert (oc, odx) == (o.kzh2_commit if dims == 2 else o.kzh3_commit)(osrs, dense)  # same commitment as the dense form
+    for plen in (n, n - 2):
+        pt = [rnd.randrange(M) for _ in range(plen)]
+        if dims == 2:
+            _, fs = kzh.sparse_kzh2_open(ctx, srs, pt, com, ev)
+            assert fs == o.sparse_kzh2_open(osrs, pt, odx, ev)[1]
+        else:
+            _, dy, cy, fs = kzh.sparse_kzh3_open(ctx, srs, pt, com, ev)
+            _, ody, ocy, ofs = o.sparse_kzh3_open(osrs, pt, odx, ev)
+            assert (dy, cy, fs) == (ody, ocy, ofs)

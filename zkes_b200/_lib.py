@@ -65,6 +65,10 @@ SIGNATURES = {
     "zk_kzh2_open": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p, c_int, c_void_p, c_uint32, c_void_p]),
     "zk_kzh3_open": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p, c_int, c_void_p, c_uint32, c_void_p, c_void_p,
                              c_void_p, c_void_p]),
+    "zk_sparse_kzh_commit": (c_int, [c_void_p, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "zk_sparse_kzh2_open": (c_int, [c_void_p, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_uint32, c_void_p]),
+    "zk_sparse_kzh3_open": (c_int, [c_void_p, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_uint32, c_void_p,
+                                    c_void_p, c_void_p, c_void_p]),
     "zk_fold_lsb_static": (c_int, [c_uint32, c_void_p, c_uint32, c_void_p, c_void_p, c_void_p]),
     "zk_gen_gauss_fr": (c_int, [c_void_p, c_uint64, c_uint64, c_uint64, c_uint64, c_int, c_void_p]),
     "zk_weighted_fold_from_right": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_int, c_void_p,

@@ -77,15 +77,16 @@ __device__ __forceinline__ uint32_t bit_field(const uint32_t (&mag)[8], int pos,
 }
 
 template <int MODE>  // 0: count keys, 1: scatter entries
-__global__ void k_msm_digits(const Fr* __restrict__ scalars, uint64_t n, uint32_t rows, int w, int k_windows,
-                             uint32_t* counts_or_cursor, uint32_t* entries) {
-  const uint64_t total = n * rows;
+__global__ void k_msm_digits(const Fr* __restrict__ scalars, const uint32_t* __restrict__ row_ids, uint64_t n, uint32_t rows,
+                             int w, int k_windows, uint32_t* counts_or_cursor, uint32_t* entries) {
+  const uint64_t total = row_ids ? n : n * rows;
   const uint32_t half = 1u << (w - 1);
   for (uint64_t g = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (uint64_t)gridDim.x * blockDim.x) {
     uint32_t mag[8];
     const bool negv = fold_scalar(ld_scalar(scalars + g), mag);
-    const uint32_t row = (uint32_t)(g / n);
-    const uint32_t col = (uint32_t)(g - (uint64_t)row * n);
+    // dense rows: scalar g belongs to row g / n; listed rows: the caller names the row of every scalar
+    const uint32_t row = row_ids ? row_ids[g] : (uint32_t)(g / n);
+    const uint32_t col = row_ids ? (uint32_t)g : (uint32_t)(g - (uint64_t)row * n);
     uint32_t carry = 0;
     for (int k = 0; k < k_windows; k++) {
       uint32_t raw = bit_field(mag, k * w, w) + carry;
@@ -115,12 +116,12 @@ __global__ void k_msm_digits(const Fr* __restrict__ scalars, uint64_t n, uint32_
 constexpr uint32_t kSmallKeys = 4096;
 
 template <int MODE>
-__global__ void __launch_bounds__(256) k_msm_digits_small(const Fr* __restrict__ scalars, uint64_t n, uint32_t rows, int w,
-                                                          int k_windows, uint32_t n_keys, uint64_t per_block,
-                                                          uint32_t* counts_or_cursor, uint32_t* entries) {
+__global__ void __launch_bounds__(256) k_msm_digits_small(const Fr* __restrict__ scalars, const uint32_t* __restrict__ row_ids,
+                                                          uint64_t n, uint32_t rows, int w, int k_windows, uint32_t n_keys,
+                                                          uint64_t per_block, uint32_t* counts_or_cursor, uint32_t* entries) {
   __shared__ uint32_t hist[kSmallKeys];
   __shared__ uint32_t basepos[kSmallKeys];
-  const uint64_t total = n * rows;
+  const uint64_t total = row_ids ? n : n * rows;
   const uint32_t half = 1u << (w - 1);
   const uint64_t begin = (uint64_t)blockIdx.x * per_block;
   const uint64_t end = begin + per_block < total ? begin + per_block : total;
@@ -130,8 +131,8 @@ __global__ void __launch_bounds__(256) k_msm_digits_small(const Fr* __restrict__
     for (uint64_t g = begin + threadIdx.x; g < end; g += blockDim.x) {
       uint32_t mag[8];
       const bool negv = fold_scalar(ld_scalar(scalars + g), mag);
-      const uint32_t row = (uint32_t)(g / n);
-      const uint32_t col = (uint32_t)(g - (uint64_t)row * n);
+      const uint32_t row = row_ids ? row_ids[g] : (uint32_t)(g / n);
+      const uint32_t col = row_ids ? (uint32_t)g : (uint32_t)(g - (uint64_t)row * n);
       uint32_t carry = 0;
       for (int k = 0; k < k_windows; k++) {
         uint32_t raw = bit_field(mag, k * w, w) + carry;
@@ -395,8 +396,15 @@ size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 int msm_run(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const Fr* scalars, uint64_t n, uint32_t rows,
             Jacobian* out_dev, MsmStats* stats) {
+  return msm_run_rows(ctx, bases, gather, nullptr, scalars, n, rows, out_dev, stats);
+}
+
+// row_ids == nullptr: `rows` dense rows of n scalars each over the same n bases.  Otherwise: n scalars in
+// all, scalar i contributes scalars[i] * bases[gather ? gather[i] : i] to output row row_ids[i] < rows.
+int msm_run_rows(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const uint32_t* row_ids, const Fr* scalars,
+                 uint64_t n, uint32_t rows, Jacobian* out_dev, MsmStats* stats) {
   cudaStream_t s = ctx->stream;
-  const uint64_t total = n * rows;
+  const uint64_t total = row_ids ? n : n * rows;
   const int sm = ctx->sm_count;
   if (rows == 0) return 0;
   if (n == 0) {
@@ -419,7 +427,7 @@ int msm_run(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const Fr* 
     ctx->launches++;
     return 0;
   }
-  const int w = pick_window(n, rows, (int)max_bits);
+  const int w = pick_window(row_ids ? (n / rows ? n / rows : 1) : n, rows, (int)max_bits);
   const int k_windows = ((int)max_bits + 1 + w - 1) / w;
   const uint32_t half = 1u << (w - 1);
   const uint64_t n_buckets64 = (uint64_t)rows * k_windows * half;
@@ -458,9 +466,9 @@ int msm_run(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const Fr* 
   if (dig_blocks > (uint32_t)sm * 8) dig_blocks = sm * 8;
   const uint64_t per_block = (total + dig_blocks - 1) / dig_blocks;
   if (small_keys)
-    k_msm_digits_small<0><<<dig_blocks, 256, 0, s>>>(scalars, n, rows, w, k_windows, n_buckets, per_block, offsets, nullptr);
+    k_msm_digits_small<0><<<dig_blocks, 256, 0, s>>>(scalars, row_ids, n, rows, w, k_windows, n_buckets, per_block, offsets, nullptr);
   else
-    k_msm_digits<0><<<sm * 8, 256, 0, s>>>(scalars, n, rows, w, k_windows, offsets, nullptr);
+    k_msm_digits<0><<<sm * 8, 256, 0, s>>>(scalars, row_ids, n, rows, w, k_windows, offsets, nullptr);
   ctx->launches++;
   unsigned long long* d_total = reinterpret_cast<unsigned long long*>(ctx->rs.sink.counter + 10);
   ZK_CUDA(cudaMemsetAsync(d_total, 0, 8, s));
@@ -474,9 +482,9 @@ int msm_run(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const Fr* 
   ctx->launches += exclusive_scan_u32(offsets, n_buckets, scan_tmp, true, s);
   ZK_CUDA(cudaMemcpyAsync(cursor, offsets, (n_buckets + 1) * 4ull, cudaMemcpyDeviceToDevice, s));
   if (small_keys)
-    k_msm_digits_small<1><<<dig_blocks, 256, 0, s>>>(scalars, n, rows, w, k_windows, n_buckets, per_block, cursor, entries);
+    k_msm_digits_small<1><<<dig_blocks, 256, 0, s>>>(scalars, row_ids, n, rows, w, k_windows, n_buckets, per_block, cursor, entries);
   else
-    k_msm_digits<1><<<sm * 8, 256, 0, s>>>(scalars, n, rows, w, k_windows, cursor, entries);
+    k_msm_digits<1><<<sm * 8, 256, 0, s>>>(scalars, row_ids, n, rows, w, k_windows, cursor, entries);
   ctx->launches++;
   ZK_CUDA(cudaMemcpyAsync(ctx->host_small, offsets + n_buckets, 4, cudaMemcpyDeviceToHost, s));
   ZK_CUDA(cudaStreamSynchronize(s));

@@ -17,4 +17,7 @@ int exclusive_scan_u32(uint32_t* data, uint64_t n, uint32_t* scratch, bool write
 int msm_run(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const Fr* scalars, uint64_t n, uint32_t rows,
             Jacobian* out_dev, MsmStats* stats);
 
+int msm_run_rows(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const uint32_t* row_ids, const Fr* scalars,
+                 uint64_t n, uint32_t rows, Jacobian* out_dev, MsmStats* stats);
+
 }  // namespace zk

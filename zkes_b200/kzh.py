@@ -108,3 +108,37 @@ def kzh3_open(ctx, srs: KZHSRS, point, com: KZHCommitment, poly):
     check(lib.zk_kzh3_open(ctx.handle, srs.handle, poly.n, ptr, mem, _p(pt), len(point), _p(com.d_x_jac), _p(dy), _p(cy),
                            _p(fs)), "zk_kzh3_open")
     return com.d_x, curve.jacobian_to_affine_py(dy), curve.affine_from_array(cy)[0], from_mont_array(fs)
+
+
+def sparse_commit(ctx, srs: KZHSRS, evaluations: dict) -> KZHCommitment:
+    """sparse_kzh2_commit (sparse_kzh2.rs:14-82) / sparse_kzh3_commit (sparse_kzh3.rs:32-110);
+    evaluations: {index: value} as SparseMLPoly.evaluations."""
+    idx = np.array(list(evaluations.keys()) or [0], dtype=np.uint64)
+    vals = to_mont_array(list(evaluations.values())) if evaluations else np.zeros((1, 4), dtype=np.uint64)
+    c = np.zeros((1, 8), dtype=np.uint64)
+    dx = np.zeros((1 << srs.x_log, 12), dtype=np.uint64)
+    check(lib.zk_sparse_kzh_commit(ctx.handle, srs.handle, len(evaluations), _p(idx), _p(vals), _p(c), _p(dx)),
+          "zk_sparse_kzh_commit")
+    return KZHCommitment(srs, curve.affine_from_array(c)[0], dx)
+
+
+def sparse_kzh2_open(ctx, srs: KZHSRS, point, com: KZHCommitment, evaluations: dict):
+    idx = np.array(list(evaluations.keys()) or [0], dtype=np.uint64)
+    vals = to_mont_array(list(evaluations.values())) if evaluations else np.zeros((1, 4), dtype=np.uint64)
+    pt = to_mont_array(point) if len(point) else np.zeros((1, 4), dtype=np.uint64)
+    out = np.zeros((1 << srs.y_log, 4), dtype=np.uint64)
+    check(lib.zk_sparse_kzh2_open(ctx.handle, srs.handle, len(evaluations), _p(idx), _p(vals), _p(pt), len(point), _p(out)),
+          "zk_sparse_kzh2_open")
+    return com.d_x, from_mont_array(out)
+
+
+def sparse_kzh3_open(ctx, srs: KZHSRS, point, com: KZHCommitment, evaluations: dict):
+    idx = np.array(list(evaluations.keys()) or [0], dtype=np.uint64)
+    vals = to_mont_array(list(evaluations.values())) if evaluations else np.zeros((1, 4), dtype=np.uint64)
+    pt = to_mont_array(point) if len(point) else np.zeros((1, 4), dtype=np.uint64)
+    dy = np.zeros((1 << srs.y_log, 12), dtype=np.uint64)
+    cy = np.zeros((1, 8), dtype=np.uint64)
+    fs = np.zeros((1 << srs.z_log, 4), dtype=np.uint64)
+    check(lib.zk_sparse_kzh3_open(ctx.handle, srs.handle, len(evaluations), _p(idx), _p(vals), _p(pt), len(point),
+                                  _p(com.d_x_jac), _p(dy), _p(cy), _p(fs)), "zk_sparse_kzh3_open")
+    return com.d_x, curve.jacobian_to_affine_py(dy), curve.affine_from_array(cy)[0], from_mont_array(fs)
