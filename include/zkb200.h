@@ -56,9 +56,10 @@ void zk_free(zk_ctx* ctx);
 const char* zk_last_error(void);
 /* Number of kernels this library has launched on the context since it was created. */
 uint64_t zk_launch_count(const zk_ctx* ctx);
-/* Options.  ZK_OPT_DEVICE_TAIL (default 0): when 1, the dense provers hand the rounds below 1024
+/* Options.  ZK_OPT_DEVICE_TAIL (default 1): the dense provers hand the rounds at or below 1024
  * table entries to one resident block that also runs the built-in transcript on the device
- * (identical outputs; only taken without a Fiat-Shamir callback and outside sharded rounds). */
+ * (identical outputs; only taken without a Fiat-Shamir callback and outside sharded rounds).
+ * 0 keeps every round on the per-round kernels with the transcript on the host. */
 typedef enum zk_option { ZK_OPT_DEVICE_TAIL = 1 } zk_option;
 int zk_set_option(zk_ctx* ctx, int option, int value);
 /* The CUDA stream (cudaStream_t) every kernel of this context is launched on, so a host can
@@ -192,6 +193,9 @@ int zk_fold_lsb(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem
  * out[lo] = sum_hi eq(point)[hi] * evals[hi * 2^(n-k) + lo]. */
 int zk_fix_from_right(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, uint32_t k, const uint64_t* point,
                       uint64_t* out, zk_mem out_mem);
+/* evaluate_multilinear_extension / DenseMLPoly::evaluate_at_point, src/util/poly.rs:622-652, 788-791:
+ * out (4 x u64, host) = sum_i evals[i] * eq(i, point) for a table of 2^n elements and n coordinates. */
+int zk_mle_eval(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, const uint64_t* point, uint64_t* out);
 /* out[lo] = sum_hi weights[hi] * evals[hi * 2^(n-k) + lo]: the contraction inside
  * fix_variables_from_right (poly.rs:719-741) with caller-given weights instead of an eq table
  * (no separate counterpart in the reference; used for trapdoor checksums of commitments). */

@@ -167,13 +167,24 @@ def test_fix_variables_random(ctx, n, k):
 @pytest.mark.parametrize("ell", [1, 2, 3, 4])
 @pytest.mark.parametrize("n", [0, 1, 4, 9, 10, 11, 13])
 def test_device_tail_option(ctx, n, ell):
-    """With ZK_OPT_DEVICE_TAIL the last rounds (tables below 1024 entries) run in one resident block
-    with the transcript on the device; every output and the transcript state must be unchanged."""
+    """ZK_OPT_DEVICE_TAIL (on by default) runs the last rounds (tables of at most 1024 entries) in one
+    resident block with the transcript on the device; switched off, every round goes through the per-round
+    kernels with the transcript on the host.  Every output and the transcript state must be the same."""
     from zkes_b200._lib import ZK_OPT_DEVICE_TAIL
     rnd = random.Random(5000 + 10 * n + ell)
     tables = [[rnd.randrange(o.R_MOD) for _ in range(1 << n)] for _ in range(ell)]
-    ctx.set_option(ZK_OPT_DEVICE_TAIL, 1)
+    ctx.set_option(ZK_OPT_DEVICE_TAIL, 0)
     try:
         run_both(ctx, tables)
     finally:
-        ctx.set_option(ZK_OPT_DEVICE_TAIL, 0)
+        ctx.set_option(ZK_OPT_DEVICE_TAIL, 1)
+
+
+@pytest.mark.parametrize("ell", [1, 2, 3, 4])
+@pytest.mark.parametrize("label_len", list(range(1, 40, 3)) + [150, 165, 166, 167, 200])
+def test_device_transcript_block_boundaries(ctx, label_len, ell):
+    """The device transcript meets the sponge's 166-byte block boundary at a position set by what was absorbed
+    before the prover ran: sweep that position so framing bytes, labels and data each straddle a boundary."""
+    rnd = random.Random(7000 + 10 * label_len + ell)
+    tables = [[rnd.randrange(o.R_MOD) for _ in range(1 << 4)] for _ in range(ell)]
+    run_both(ctx, tables, label=bytes(rnd.randrange(256) for _ in range(label_len)))

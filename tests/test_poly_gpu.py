@@ -47,3 +47,14 @@ def test_from_right_random(ctx, n, k):
     if n <= 12:
         lowpt = [rnd.randrange(M) for _ in range(n - k)]
         assert o.evaluate_multilinear_extension(got, lowpt) == o.evaluate_multilinear_extension(f, lowpt + pt)
+
+
+@pytest.mark.parametrize("n", [0, 1, 3, 8, 11, 15])
+def test_evaluate_at_point(ctx, n):
+    """DenseMLPoly::evaluate_at_point (poly.rs:788-791); test_kzh2.rs:149-175 relies on it."""
+    rnd = random.Random(900 + n)
+    f = [rnd.randrange(M) for _ in range(1 << n)]
+    pt = [rnd.randrange(M) for _ in range(n)]
+    assert DenseMLPoly.from_evaluations(f).evaluate_at_point(ctx, pt) == o.evaluate_multilinear_extension(f, pt)
+    if n == 3:  # a vertex picks one table entry
+        assert DenseMLPoly.from_evaluations(f).evaluate_at_point(ctx, [1, 0, 1]) == f[5]

@@ -47,6 +47,7 @@ SIGNATURES = {
                                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                c_void_p]),
     "zk_fix_from_right": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_int]),
+    "zk_mle_eval": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_void_p, c_void_p]),
     "zk_eq_table": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_int]),
     "zk_msm_g1": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_uint64, c_void_p, c_int]),
     "zk_msm_g1_batched": (c_int, [c_void_p, c_void_p, c_int, c_uint64, c_void_p, c_int, c_uint64, c_void_p, c_int]),

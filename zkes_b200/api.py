@@ -119,6 +119,16 @@ class DenseMLPoly:
     def evaluations(self):
         return from_mont_array(self.mont)
 
+    def evaluate_at_point(self, ctx: Context, point) -> int:
+        """src/util/poly.rs:788-791 (evaluate_multilinear_extension, :622-652)."""
+        assert len(point) == self.n, "invalid size of point"
+        pt = to_mont_array(point) if self.n else np.zeros((1, 4), dtype=np.uint64)
+        out = np.zeros((1, 4), dtype=np.uint64)
+        src = c_void_p(self.device_ptr) if self.device_ptr is not None else _ptr(self.mont)
+        mem = ZK_MEM_DEVICE if self.device_ptr is not None else ZK_MEM_HOST
+        check(lib.zk_mle_eval(ctx.handle, self.n, src, mem, _ptr(pt), _ptr(out)), "zk_mle_eval")
+        return from_mont_array(out)[0]
+
     def fix_variables(self, ctx: Context, partial_point) -> "DenseMLPoly":
         assert len(partial_point) <= self.n, "invalid size of partial point"
         k = len(partial_point)

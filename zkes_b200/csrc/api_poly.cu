@@ -88,6 +88,35 @@ int zk_weighted_fold_from_right(zk_ctx* ctx, uint32_t n, const uint64_t* evals, 
   return ZK_OK;
 }
 
+int zk_mle_eval(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, const uint64_t* point, uint64_t* out) {
+  if (!ctx || !evals || !out || (n && !point)) return fail(ZK_ERR_ARG, "mle_eval: NULL argument");
+  if (n > 34) return fail(ZK_ERR_ARG, "mle_eval: n %u too large", n);
+  CtxLock lk(ctx);
+  cudaStream_t s = ctx->stream;
+  const uint64_t size = 1ull << n;
+  const size_t in_elems = evals_mem == ZK_MEM_HOST ? size : 0;
+  Fr* base = nullptr;
+  int rc = ctx->reserve_work((in_elems + size + n + 16) * sizeof(Fr), (void**)&base);
+  if (rc) return rc;
+  const Fr* f = reinterpret_cast<const Fr*>(evals);
+  if (evals_mem == ZK_MEM_HOST) {
+    ZK_CUDA(cudaMemcpyAsync(base, evals, size * sizeof(Fr), cudaMemcpyHostToDevice, s));
+    f = base;
+  }
+  Fr* eq = base + in_elems;
+  rc = eq_table_device(ctx, point, n, eq + size, eq);
+  if (rc) return rc;
+  RoundScratch sc = ctx->rs;
+  sc.sink.pub_flag = nullptr;  // read back with a copy: nothing polls this result
+  launch_dot(f, eq, size, sc, s);
+  ctx->launches++;
+  ZK_CUDA(cudaGetLastError());
+  ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->rs.sink.msg, sizeof(Fr), cudaMemcpyDeviceToHost, s));
+  ZK_CUDA(cudaStreamSynchronize(s));
+  memcpy(out, ctx->host_small, sizeof(Fr));
+  return ZK_OK;
+}
+
 int zk_fix_from_right(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, uint32_t k, const uint64_t* point,
                       uint64_t* out, zk_mem out_mem) {
   if (!ctx || !evals || !out || (k && !point)) return fail(ZK_ERR_ARG, "fix_from_right: NULL argument");

@@ -66,7 +66,7 @@ struct zk_ctx {
   size_t work_bytes = 0;
   void* aux = nullptr;           // second grow-only scratch (MSM sort and bucket storage)
   size_t aux_bytes = 0;
-  bool device_tail = false;      // run the last dense rounds in the single-block kernel (zk_set_option)
+  bool device_tail = true;       // run the last dense rounds in the single-block kernel (zk_set_option turns it off)
   MsmStatsPod last_msm;          // shape of the most recent MSM (window width, windows, entries)
   std::mutex mu;
   std::atomic<uint64_t> launches{0};

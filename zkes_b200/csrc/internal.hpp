@@ -38,6 +38,7 @@ void launch_fold2(const Fr* src, Fr* dst, const Fr& r0, const Fr& r1, uint64_t o
 
 // poly.cu
 int launch_eq_table(const Fr* point_dev, const Fr* point_host, uint32_t k, Fr* out, int sm_count, cudaStream_t s);
+void launch_dot(const Fr* a, const Fr* b, uint64_t n, const RoundScratch& sc, cudaStream_t s);
 uint32_t from_right_splits(uint64_t lo_n, uint64_t hi_n, int sm_count);
 int launch_from_right(const Fr* f, const Fr* eq, uint64_t lo_n, uint64_t hi_n, Fr* partial, Fr* out, int sm_count,
                       cudaStream_t s);

@@ -87,7 +87,37 @@ __global__ void __launch_bounds__(256) k_sum_splits(const Fr* __restrict__ parti
   st_fr_plain(out + lo, s);
 }
 
+// sum_i a[i] * b[i] with lazily reduced products (evaluate_multilinear_extension's final sum, poly.rs:635-647).
+__global__ void __launch_bounds__(256) k_dot(const Fr* __restrict__ a, const Fr* __restrict__ b, uint64_t n, const MsgSink sink) {
+  Wide acc;
+#pragma unroll
+  for (int k = 0; k < 16; k++) acc.v[k] = 0;
+  int pending = 0;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    const Fr x = ldg_fr(a + i), y = ldg_fr(b + i);
+    Wide w;
+    mul_wide(w, x.v, y.v);
+    wide_add(acc, w);
+    if (++pending == kLazyProducts) {
+      wide_trim<FrParams>(acc);
+      pending = 0;
+    }
+  }
+  wide_trim<FrParams>(acc);
+  Fr s[1] = {redc<FrParams>(acc)};
+  grid_sum<1, 8>(s, sink);
+}
+
 }  // namespace
+
+// sink.msg[0] = sum_i a[i] b[i]
+void launch_dot(const Fr* a, const Fr* b, uint64_t n, const RoundScratch& sc, cudaStream_t s) {
+  uint64_t blocks = (n + 255) / 256;
+  const uint64_t cap = (uint64_t)sc.sm_count * 4 < (uint64_t)sc.max_blocks ? sc.sm_count * 4 : sc.max_blocks;
+  if (blocks < 1) blocks = 1;
+  if (blocks > cap) blocks = cap;
+  k_dot<<<(unsigned)blocks, 256, 0, s>>>(a, b, n, sc.sink);
+}
 
 // out[0 .. 2^k) = eq(., point); point_dev holds the k coordinates on the device, point_host the
 // same values on the host (for the per-level multiplier tables).  Returns launches.

@@ -115,4 +115,152 @@ ZK_HD Fr transcript_challenge_scalar_dev(StrobeState& st, const char* label, uin
   return to_mont(raw);
 }
 
+#ifdef __CUDACC__
+// ---- warp-parallel form: state lane i lives in thread i of one warp (threads 25..31 idle along).
+// Every function below is collective over the full warp.
+
+static __constant__ uint64_t kKeccakRcDev[24] = {
+    0x0000000000000001ull, 0x0000000000008082ull, 0x800000000000808Aull, 0x8000000080008000ull,
+    0x000000000000808Bull, 0x0000000080000001ull, 0x8000000080008081ull, 0x8000000000008009ull,
+    0x000000000000008Aull, 0x0000000000000088ull, 0x0000000080008009ull, 0x000000008000000Aull,
+    0x000000008000808Bull, 0x800000000000008Bull, 0x8000000000008089ull, 0x8000000000008003ull,
+    0x8000000000008002ull, 0x8000000000000080ull, 0x000000000000800Aull, 0x800000008000000Aull,
+    0x8000000080008081ull, 0x8000000000008080ull, 0x0000000080000001ull, 0x8000000080008008ull};
+
+// One Keccak-f[1600] over a warp.  Per round every thread pulls the ten lanes of its two neighbour
+// columns (theta), rotates its own lane (rho), then pulls the three rotated lanes that pi moves into
+// its row positions x, x+1, x+2 (pi and chi together): two shuffle stages per round.
+static __device__ __noinline__ uint2 keccak_f1600_warp(uint2 a, int lane) {
+  const int l = lane < 25 ? lane : 0;  // idle threads mirror lane 0's indices; their values are never used
+  const int x = l % 5, y = l / 5;
+  // rho offsets, lane = x + 5 y, packed 6 bits each
+  const int my_rot = (int)((l < 10 ? (0x5371AC91B73E040ull >> (6 * l))                      // 0 1 62 28 27 36 44 6 55 20
+                                   : l < 20 ? (0x2153EDA6766B283ull >> (6 * (l - 10)))      // 3 10 43 25 39 41 45 15 21 8
+                                            : (0xEE3D092ull >> (6 * (l - 20)))) & 63);  // 18 2 61 56 14
+  const bool swap_halves = my_rot >= 32;
+  const int sh = my_rot & 31;
+  const int col_prev = (x + 4) % 5, col_next = (x + 1) % 5;
+  // pi: the lane that lands at (X, Y) comes from ((X + 3Y) mod 5, X)
+  const int x1 = (x + 1) % 5, x2 = (x + 2) % 5;
+  const int s0 = ((x + 3 * y) % 5) + 5 * x, s1 = ((x1 + 3 * y) % 5) + 5 * x1, s2 = ((x2 + 3 * y) % 5) + 5 * x2;
+  uint32_t lo = a.x, hi = a.y;
+#pragma unroll 2
+  for (int round = 0; round < 24; round++) {
+    uint32_t plo = 0, phi = 0, nlo = 0, nhi = 0;
+#pragma unroll
+    for (int k = 0; k < 5; k++) {
+      plo ^= __shfl_sync(0xffffffffu, lo, col_prev + 5 * k);
+      phi ^= __shfl_sync(0xffffffffu, hi, col_prev + 5 * k);
+      nlo ^= __shfl_sync(0xffffffffu, lo, col_next + 5 * k);
+      nhi ^= __shfl_sync(0xffffffffu, hi, col_next + 5 * k);
+    }
+    lo ^= plo ^ __funnelshift_l(nhi, nlo, 1);
+    hi ^= phi ^ __funnelshift_l(nlo, nhi, 1);
+    const uint32_t tl = swap_halves ? hi : lo, th = swap_halves ? lo : hi;
+    const uint32_t rlo = __funnelshift_l(th, tl, sh), rhi = __funnelshift_l(tl, th, sh);
+    const uint32_t b0l = __shfl_sync(0xffffffffu, rlo, s0), b0h = __shfl_sync(0xffffffffu, rhi, s0);
+    const uint32_t b1l = __shfl_sync(0xffffffffu, rlo, s1), b1h = __shfl_sync(0xffffffffu, rhi, s1);
+    const uint32_t b2l = __shfl_sync(0xffffffffu, rlo, s2), b2h = __shfl_sync(0xffffffffu, rhi, s2);
+    lo = b0l ^ (~b1l & b2l);
+    hi = b0h ^ (~b1h & b2h);
+    const uint64_t rc = kKeccakRcDev[round];  // uniform load; selected, not branched on, so the warp stays converged
+    lo ^= lane == 0 ? (uint32_t)rc : 0u;
+    hi ^= lane == 0 ? (uint32_t)(rc >> 32) : 0u;
+  }
+  return make_uint2(lo, hi);
+}
+
+struct WarpStrobe {
+  uint64_t a;                // this thread's state lane (threads 0..24)
+  uint32_t pos, pos_begin;   // identical in every thread
+
+  __device__ __forceinline__ void run_f(int lane) {
+    if ((int)(pos >> 3) == lane) a ^= (uint64_t)(pos_begin & 0xffu) << (8 * (pos & 7));
+    if ((int)((pos + 1) >> 3) == lane) a ^= (uint64_t)0x04 << (8 * ((pos + 1) & 7));
+    if (lane == 20) a ^= (uint64_t)0x80 << 56;  // byte kStrobeRate + 1 = 167
+    __syncwarp();  // shuffles between diverged threads are far slower than between converged ones
+    const uint2 t = keccak_f1600_warp(make_uint2((uint32_t)a, (uint32_t)(a >> 32)), lane);
+    a = ((uint64_t)t.y << 32) | t.x;
+    pos = 0;
+    pos_begin = 0;
+  }
+  // XOR m bytes of buf (shared memory, visible to the warp) into the state from byte `start`.
+  __device__ __forceinline__ void xor_segment(const uint8_t* buf, uint32_t start, uint32_t m, int lane) {
+#pragma unroll
+    for (int b = 0; b < 8; b++) {
+      const uint32_t p = 8u * lane + b;
+      if (lane < 25 && p >= start && p < start + m) a ^= (uint64_t)buf[p - start] << (8 * b);
+    }
+    __syncwarp();
+  }
+
+  // Bytes of one sumcheck round as the transcript sees them (transcript.rs:27-42 over Merlin's framing):
+  // per evaluation [begin, 0x12] "round_message" len32 [begin, 0x02] 32 data bytes, then
+  // [begin, 0x12] "challenge" len64 [begin, 0x07].  The `begin` bytes depend on the position and are
+  // filled in while absorbing; everything else but the data is constant.
+  template <int L>
+  static constexpr int round_stream_bytes() { return 53 * (L + 1) + 17; }
+
+  template <int L>
+  static __device__ void init_round_stream(uint8_t* stream) {  // one thread
+    const char* l1 = "round_message";
+    const char* l2 = "challenge";
+    for (int c = 0; c <= L; c++) {
+      uint8_t* s = stream + 53 * c;
+      s[0] = 0; s[1] = 16u | 2u;
+      for (int i = 0; i < 13; i++) s[2 + i] = (uint8_t)l1[i];
+      s[15] = 32; s[16] = 0; s[17] = 0; s[18] = 0;
+      s[19] = 0; s[20] = 2u;
+    }
+    uint8_t* s = stream + 53 * (L + 1);
+    s[0] = 0; s[1] = 16u | 2u;
+    for (int i = 0; i < 9; i++) s[2 + i] = (uint8_t)l2[i];
+    s[11] = 64; s[12] = 0; s[13] = 0; s[14] = 0;
+    s[15] = 0; s[16] = 1u | 2u | 4u;
+  }
+  static __device__ __forceinline__ uint8_t* round_stream_data(uint8_t* stream, int c) { return stream + 53 * c + 21; }
+
+  // Absorbs the round's stream (data bytes already written, warp synchronised), draws the 64
+  // challenge bytes and returns the first 32 as eight little-endian words in every thread.
+  template <int L>
+  __device__ __forceinline__ void fs_round(uint8_t* stream, int lane, uint32_t* raw) {
+    constexpr int kPieces = 2 * (L + 1) + 2;
+    uint32_t off = 0, seg_off = 0, seg_pos = pos;
+#pragma unroll
+    for (int j = 0; j < kPieces; j++) {
+      const uint32_t len = j == kPieces - 1 ? 0u : (j == kPieces - 2 ? 13u : ((j & 1) ? 32u : 17u));
+      if (lane == 0) stream[off] = (uint8_t)pos_begin;  // the operation's first framing byte
+      pos_begin = pos + 1;
+      uint32_t n = 2 + len;
+      while (pos + n >= kStrobeRate) {  // the block fills up inside this piece
+        const uint32_t take = kStrobeRate - pos;
+        __syncwarp();
+        xor_segment(stream + seg_off, seg_pos, off + take - seg_off, lane);
+        pos = kStrobeRate;
+        run_f(lane);
+        off += take;
+        n -= take;
+        seg_off = off;
+        seg_pos = 0;
+      }
+      pos += n;
+      off += n;
+    }
+    __syncwarp();
+    xor_segment(stream + seg_off, seg_pos, off - seg_off, lane);
+    if (pos != 0) run_f(lane);  // the PRF operation starts on a fresh block
+    // squeeze: the 64 bytes at position 0 are state lanes 0..7; they are zeroed behind the read
+    const uint32_t lo = (uint32_t)a, hi = (uint32_t)(a >> 32);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      raw[2 * i] = __shfl_sync(0xffffffffu, lo, i);
+      raw[2 * i + 1] = __shfl_sync(0xffffffffu, hi, i);
+    }
+    if (lane < 8) a = 0;
+    pos = 64;
+    __syncwarp();
+  }
+};
+#endif  // __CUDACC__
+
 }  // namespace zk

@@ -33,16 +33,18 @@ __global__ void __launch_bounds__(kTailThreads) k_tail(const TailParams<L> p) {
   Fr* B = A + (size_t)L * p.size;                   // L * size / 2
   Fr* red = B + (size_t)L * (p.size / 2 + 1);       // (kTailThreads / 32) * (L + 1)
   Fr* chal = red + (kTailThreads / 32) * (L + 1);   // 1
-  __shared__ StrobeState st;
+  __shared__ __align__(16) uint8_t stream[WarpStrobe::round_stream_bytes<L>() + 15];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  WarpStrobe ws;                  // live in warp 0 only
+  ws.a = (warp == 0 && lane < 25) ? p.st.lanes[lane] : 0;
+  ws.pos = p.st.pos;
+  ws.pos_begin = p.st.pos_begin;
+  if (tid == 0) WarpStrobe::init_round_stream<L>(stream);
 
   for (uint32_t i = tid; i < p.size; i += kTailThreads)
 #pragma unroll
     for (int t = 0; t < L; t++) A[(size_t)t * p.size + i] = p.src[t][i];
-  if (tid == 0) {
-    st = p.st;
-    chal[0] = p.r;
-  }
+  if (tid == 0) chal[0] = p.r;
   __syncthreads();
 
   Fr* cur = A;
@@ -96,16 +98,27 @@ __global__ void __launch_bounds__(kTailThreads) k_tail(const TailParams<L> p) {
       if (lane == 0) red[warp * (L + 1) + c] = t;
     }
     __syncthreads();
-    if (tid == 0) {
-      for (int c = 0; c <= L; c++) {
-        Fr t = red[c];
-        for (int w = 1; w < kTailThreads / 32; w++) t = add(t, red[w * (L + 1) + c]);
-        p.out_msgs[(size_t)round * (L + 1) + c] = t;
-        transcript_append_scalar_dev(st, "round_message", 13, t);
+    if (warp == 0) {
+      // Fiat-Shamir step by the whole first warp (transcript.rs:27-42 over STROBE / Keccak-f)
+      if (lane <= L) {  // one lane per evaluation: total, canonical form, bytes
+        Fr t = red[lane];
+        for (int w = 1; w < kTailThreads / 32; w++) t = add(t, red[w * (L + 1) + lane]);
+        p.out_msgs[(size_t)round * (L + 1) + lane] = t;
+        const Fr canon = from_mont(t);
+        uint8_t* dst = WarpStrobe::round_stream_data(stream, lane);
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+#pragma unroll
+          for (int k = 0; k < 4; k++) dst[4 * i + k] = (uint8_t)(canon.v[i] >> (8 * k));
       }
-      const Fr ch = transcript_challenge_scalar_dev(st, "challenge", 9);
-      p.out_chal[round] = ch;
-      chal[0] = ch;
+      __syncwarp();
+      Fr raw;
+      ws.fs_round<L>(stream, lane, raw.v);
+      if (lane == 0) {
+        const Fr ch = to_mont(raw);
+        p.out_chal[round] = ch;
+        chal[0] = ch;
+      }
     }
     __syncthreads();
     fold_now = true;
@@ -119,8 +132,12 @@ __global__ void __launch_bounds__(kTailThreads) k_tail(const TailParams<L> p) {
       prod = mul(prod, a);
     }
     p.out_final[L] = prod;
-    *p.out_st = st;
+    p.out_st->pos = ws.pos;
+    p.out_st->pos_begin = ws.pos_begin;
+    p.out_st->cur_flags = 1u | 2u | 4u;  // the last operation was the PRF of a challenge (or nothing ran)
+    p.out_st->pad = 0;
   }
+  if (warp == 0 && lane < 25) p.out_st->lanes[lane] = ws.a;
 }
 
 template <int L>
