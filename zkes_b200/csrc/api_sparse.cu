@@ -137,10 +137,20 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
     // the few values it needs on the fly, so this fold waits and is done together with the next
     // one in a single pass over the table (k_fold2).
     const bool next_sparse = round + 1 < num_var && (!K || (S / 2) > dense_cap);
+    // The table fold (bandwidth-bound, long) and the entry fold (three short launches) touch disjoint
+    // buffers: the table fold goes to the side stream and the two run side by side.  With the
+    // per-kernel profiler on they stay in line so that each span times one kernel alone.
+    const bool fold_now = pending || !next_sparse;
+    const bool beside = fold_now && !ctx->prof_on;
+    cudaStream_t fs_stream = beside ? ctx->side_stream : s;
+    if (beside) {
+      ZK_CUDA(cudaEventRecord(ctx->ev_fork, s));
+      ZK_CUDA(cudaStreamWaitEvent(fs_stream, ctx->ev_fork, 0));
+    }
     if (pending) {
       Fr* nb = other_buf(b_cur);
       ctx->prof_begin(ZK_PROF_FOLD, 32.0 * (double)(2 * S + S / 2));
-      launch_fold2(b_cur, nb, pend_r, challenge, S / 2, ctx->rs.max_blocks, s);
+      launch_fold2(b_cur, nb, pend_r, challenge, S / 2, ctx->rs.max_blocks, fs_stream);
       ctx->prof_end();
       ctx->launches++;
       b_cur = nb;
@@ -151,15 +161,17 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
     } else {
       Fr* nb = other_buf(b_cur);
       ctx->prof_begin(ZK_PROF_FOLD, 96.0 * (double)(S / 2));
-      launch_fold(b_cur, nb, challenge, S / 2, ctx->rs.max_blocks, s);
+      launch_fold(b_cur, nb, challenge, S / 2, ctx->rs.max_blocks, fs_stream);
       ctx->prof_end();
       ctx->launches++;
       b_cur = nb;
     }
+    if (beside) ZK_CUDA(cudaEventRecord(ctx->ev_join, fs_stream));
     ctx->prof_begin(ZK_PROF_SPARSE_FOLD, 80.0 * k_upper, 3);
     ctx->launches += launch_sparse_fold(e_idx[e], e_val[e], counts + e, k_upper, challenge, block_counts, e_idx[e ^ 1],
                                         e_val[e ^ 1], counts + (e ^ 1), s);
     ctx->prof_end();
+    if (beside) ZK_CUDA(cudaStreamWaitEvent(s, ctx->ev_join, 0));
     e ^= 1;
     if ((uint64_t)k_upper > S / 2) k_upper = (uint32_t)(S / 2);
   }

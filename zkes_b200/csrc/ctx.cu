@@ -6,6 +6,9 @@ int zk_ctx::setup() {
   ZK_CUDA(cudaSetDevice(device));
   ZK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
   ZK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  ZK_CUDA(cudaStreamCreateWithFlags(&side_stream, cudaStreamNonBlocking));
+  ZK_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
+  ZK_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
   rs.max_blocks = sm_count * 8;
   rs.sm_count = sm_count;
   ZK_CUDA(cudaMalloc(&rs.sink.partials, sizeof(Fr) * (size_t)rs.max_blocks * (kMaxPolys + 1)));
@@ -31,6 +34,7 @@ int zk_ctx::setup() {
 void zk_ctx::teardown() {
   cudaSetDevice(device);
   if (stream) cudaStreamSynchronize(stream);
+  if (side_stream) cudaStreamSynchronize(side_stream);
   cudaFree(rs.sink.partials);
   cudaFree(rs.sink.counter);
   cudaFree(rs.sink.msg);
@@ -45,6 +49,9 @@ void zk_ctx::teardown() {
     cudaEventDestroy(sp.e0);
     cudaEventDestroy(sp.e1);
   }
+  if (ev_fork) cudaEventDestroy(ev_fork);
+  if (ev_join) cudaEventDestroy(ev_join);
+  if (side_stream) cudaStreamDestroy(side_stream);
   if (stream) cudaStreamDestroy(stream);
 }
 

@@ -56,6 +56,8 @@ struct zk_ctx {
   int device = 0;
   int sm_count = 0;
   cudaStream_t stream = nullptr;
+  cudaStream_t side_stream = nullptr;  // a bandwidth-bound pass that may run beside latency-bound launches
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   zk::RoundScratch rs{};
   zk::Fr* final_out = nullptr;   // kMaxPolys + 1 elements
   void* tail_out = nullptr;      // single-block tail kernel: messages, challenges, transcript state (8 KiB)
