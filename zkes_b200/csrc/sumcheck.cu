@@ -176,16 +176,29 @@ struct Fold2Params {
 };
 
 __global__ void __launch_bounds__(kThreads) k_fold2(const Fold2Params p) {
-  __shared__ uint4 stage[kWarps][WarpTile<8>::kChunks];
+  // two input stages per warp: the next tile streams in (cp.async) while this one is folded
+  __shared__ uint4 stage[2][kWarps][WarpTile<8>::kChunks];
+  __shared__ uint4 out_stage[kWarps][WarpTile<2>::kChunks];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint4* sw = stage[warp];
   const uint64_t tiles = (p.out_len + 31) >> 5;
-  for (uint64_t tile = (uint64_t)blockIdx.x * kWarps + warp; tile < tiles; tile += (uint64_t)gridDim.x * kWarps) {
+  const uint64_t stride = (uint64_t)gridDim.x * kWarps;
+  const uint4* src = reinterpret_cast<const uint4*>(p.src);
+  auto valid_of = [&](uint64_t tile) { return (uint32_t)((p.out_len - (tile << 5)) < 32 ? (p.out_len - (tile << 5)) : 32); };
+  uint64_t tile = (uint64_t)blockIdx.x * kWarps + warp;
+  int buf = 0;
+  if (tile < tiles) WarpTile<8>::prefetch_async(stage[0][warp], src + (tile << 5) * 8, valid_of(tile) * 8, lane);
+  for (; tile < tiles; tile += stride, buf ^= 1) {
     const uint64_t e0 = tile << 5;
-    const uint32_t valid = (uint32_t)((p.out_len - e0) < 32 ? (p.out_len - e0) : 32);
-    uint4 raw[8], q[8];
-    WarpTile<8>::issue(reinterpret_cast<const uint4*>(p.src) + e0 * 8, valid * 8, lane, raw);
-    WarpTile<8>::transpose_in(sw, lane, raw, q);
+    const uint32_t valid = valid_of(tile);
+    const uint64_t next = tile + stride;
+    if (next < tiles) {
+      WarpTile<8>::prefetch_async(stage[buf ^ 1][warp], src + (next << 5) * 8, valid_of(next) * 8, lane);
+      WarpTile<8>::wait_async<1>();
+    } else {
+      WarpTile<8>::wait_async<0>();
+    }
+    uint4 q[8];
+    WarpTile<8>::read_rows(stage[buf][warp], lane, q);
     const Fr t0 = fr_from_chunks(q[0], q[1]), t1 = fr_from_chunks(q[2], q[3]);
     const Fr t2 = fr_from_chunks(q[4], q[5]), t3 = fr_from_chunks(q[6], q[7]);
     // (t0 + r0 d01) + r1 ((t2 + r0 d23) - (t0 + r0 d01)) = t0 + r0 d01 + r1 (t2 - t0) + r0 r1 (d23 - d01)
@@ -201,7 +214,7 @@ __global__ void __launch_bounds__(kThreads) k_fold2(const Fold2Params p) {
     const Fr u = add(t0, mul_fixed3(p.r0, d01, p.r1, d02, p.r01, dd));
     uint4 o[2];
     fr_to_chunks(u, o[0], o[1]);
-    WarpTile<2>::store(reinterpret_cast<uint4*>(p.dst) + e0 * 2, valid * 2, sw, lane, o);
+    WarpTile<2>::store(reinterpret_cast<uint4*>(p.dst) + e0 * 2, valid * 2, out_stage[warp], lane, o);
   }
 }
 

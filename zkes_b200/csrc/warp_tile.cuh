@@ -44,6 +44,36 @@ struct WarpTile {
     __syncwarp();
   }
 
+  // Asynchronous form of issue + the first half of transpose_in: the tile goes from global memory
+  // straight into its swizzled shared-memory slots (16-byte cp.async, no registers), as one commit
+  // group.  Chunks at or beyond `valid` are zero-filled.  Pair with wait_async + read_rows.
+  static __device__ __forceinline__ void prefetch_async(uint4* smem_warp, const uint4* __restrict__ g, uint32_t valid,
+                                                        int lane) {
+#pragma unroll
+    for (int j = 0; j < CH; j++) {
+      const uint32_t c = j * 32 + lane;
+      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_warp + phys(c / CH, c % CH));
+      const uint32_t bytes = c < valid ? 16u : 0u;  // 0: nothing is read, the slot is zero-filled
+      const uint4* src = c < valid ? g + c : g;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+
+  // Wait until at most `Pending` of this thread's commit groups are still in flight, then make the
+  // warp's copies visible to all its lanes.
+  template <int Pending>
+  static __device__ __forceinline__ void wait_async() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(Pending) : "memory");
+    __syncwarp();
+  }
+
+  static __device__ __forceinline__ void read_rows(const uint4* smem_warp, int lane, uint4 (&out)[CH]) {
+#pragma unroll
+    for (int k = 0; k < CH; k++) out[k] = smem_warp[phys(lane, k)];
+    __syncwarp();
+  }
+
   // Lane's own CH chunks -> shared -> coalesced global writes (chunks below `valid` only).
   static __device__ __forceinline__ void store(uint4* __restrict__ g, uint32_t valid, uint4* smem_warp, int lane,
                                                const uint4 (&in)[CH]) {
