@@ -40,6 +40,13 @@ def verify(proof, n, ell, claimed, label=b"sumcheck"):
     return ch
 
 
+def eval_prod(tables, i):
+    v = 1
+    for t in tables:
+        v = v * t[i] % o.R_MOD
+    return v
+
+
 def test_constant_polynomials(ctx):  # test_linear_sumcheck.rs:19-62, claimed sum 4
     _, proof = run_both(ctx, [[1, 1, 1, 1], [1, 1, 1, 1]])
     assert len(proof.round_messages) == 2 and all(len(m) == 3 for m in proof.round_messages)
@@ -173,11 +180,26 @@ def test_device_tail_option(ctx, n, ell):
     from zkes_b200._lib import ZK_OPT_DEVICE_TAIL
     rnd = random.Random(5000 + 10 * n + ell)
     tables = [[rnd.randrange(o.R_MOD) for _ in range(1 << n)] for _ in range(ell)]
+    run_both(ctx, tables)  # default: device-resident rounds (multi-block above 1024 entries, then one block)
     ctx.set_option(ZK_OPT_DEVICE_TAIL, 0)
     try:
         run_both(ctx, tables)
     finally:
         ctx.set_option(ZK_OPT_DEVICE_TAIL, 1)
+
+
+@pytest.mark.parametrize("n,ell", [(12, 1), (14, 3), (15, 2), (16, 2), (12, 4)])
+def test_resident_rounds(ctx, n, ell):
+    """Tables above 1024 entries: the cooperative multi-block kernel runs the first rounds with the transcript
+    on the device and hands the last 1024 entries to the single-block kernel without a host step between."""
+    rnd = random.Random(9100 + 10 * n + ell)
+    edge = [0, 1, o.R_MOD - 1]
+    tables = [[rnd.choice(edge) if rnd.random() < 0.05 else rnd.randrange(o.R_MOD) for _ in range(1 << n)]
+              for _ in range(ell)]
+    _, proof = run_both(ctx, tables, label=b"resident-%d" % n)
+    claimed = sum(eval_prod(tables, i) for i in range(1 << n)) % o.R_MOD if n <= 12 else None
+    if claimed is not None:
+        verify(proof, n, ell, claimed, label=b"resident-%d" % n)
 
 
 @pytest.mark.parametrize("ell", [1, 2, 3, 4])

@@ -214,9 +214,12 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
   *finals_done = false;
   uint64_t cur_size = size;  // entries of the tables cur[] points at
   const bool tail_ok = ctx->device_tail && !fs && tr && !comm;
+  uint32_t resident_rounds = 0;  // rounds the resident kernel has produced (their results are still on the device)
   for (uint32_t round = 0; round < rounds; round++) {
-    if (tail_ok && cur_size <= kTailMax) {
-      // hand the remaining rounds to one resident block; round > 0 means `*challenge` is still to be bound
+    if (tail_ok && (cur_size <= kTailMax || round == 0)) {
+      // Device-resident rounds.  Tables above kTailMax entries go through the cooperative multi-block
+      // kernel until kTailMax entries are left, then (or at once, for small tables) one block finishes
+      // in shared memory; messages, challenges and the transcript state come back in a single copy.
       StrobeState st;
       memcpy(st.lanes, tr->m.strobe().state(), 200);
       st.pos = tr->m.strobe().pos();
@@ -227,28 +230,57 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
       Fr* d_msgs = reinterpret_cast<Fr*>(ctx->tail_out);
       Fr* d_chal = d_msgs + (size_t)left * (L + 1);
       StrobeState* d_st = reinterpret_cast<StrobeState*>(d_chal + left);
-      if (launch_tail(L, cur, (uint32_t)cur_size, round > 0, *challenge, st, d_msgs, d_chal, ctx->final_out, d_st, ctx->stream))
-        return fail(ZK_ERR_CUDA, "tail kernel launch failed");
-      ctx->launches++;
-      ZK_CUDA(cudaGetLastError());
-      const size_t bytes = ((size_t)left * (L + 2)) * sizeof(Fr) + sizeof(StrobeState);
-      ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->tail_out, bytes, cudaMemcpyDeviceToHost, ctx->stream));
-      ZK_CUDA(cudaStreamSynchronize(ctx->stream));
-      const Fr* h_msgs = reinterpret_cast<const Fr*>(ctx->host_small);
-      const Fr* h_chal = h_msgs + (size_t)left * (L + 1);
-      const StrobeState* h_st = reinterpret_cast<const StrobeState*>(h_chal + left);
-      for (uint32_t k = 0; k < left; k++) {
-        for (int c = 0; c <= L; c++)
-          fr_store(round_msgs + ((uint64_t)(round_offset + round + k) * (L + 1) + c) * 4, h_msgs[(size_t)k * (L + 1) + c]);
-        fr_store(challenges + 4 * (uint64_t)(round_offset + round + k), h_chal[k]);
+      ResidentShared* sh = reinterpret_cast<ResidentShared*>(ctx->resident_sh);
+      bool resident = false;
+      if (cur_size > kTailMax) {
+        // rounds whose tables (before the fold) are above kTailMax entries: log2(size) - 10 folds + the first
+        uint32_t lg = 0;
+        while ((1ull << lg) < cur_size) lg++;
+        resident_rounds = lg - 9;
+        ctx->prof_begin(ZK_PROF_ROUND, 64.0 * L * (double)(cur_size / 2) + 192.0 * L * (double)(cur_size / 2));
+        const int lrc = launch_resident(L, cur, ping, pong, cur_size, resident_rounds, st, ctx->rs.sink.partials,
+                                        ctx->rs.max_blocks, ctx->sm_count, sh, d_msgs, d_chal, ctx->stream);
+        ctx->prof_end();
+        if (lrc != 0) {
+          resident_rounds = 0;  // no cooperative launch on this device: stay on the per-round kernels
+        } else {
+          ctx->launches++;
+          resident = true;
+          Fr** last = ((resident_rounds - 1) & 1) ? ping : pong;
+          for (int i = 0; i < L; i++) cur[i] = last[i];
+          cur_size >>= (resident_rounds - 1);
+        }
       }
-      *challenge = h_chal[left - 1];
-      memcpy(tr->m.strobe().state(), h_st->lanes, 200);
-      tr->m.strobe().pos() = (uint8_t)h_st->pos;
-      tr->m.strobe().pos_begin() = (uint8_t)h_st->pos_begin;
-      tr->m.strobe().cur_flags() = (uint8_t)h_st->cur_flags;
-      *finals_done = true;
-      return ZK_OK;
+      if (cur_size <= kTailMax) {
+        const bool fold_first = resident || round > 0;
+        if (launch_tail(L, cur, (uint32_t)cur_size, fold_first, *challenge, st, d_msgs + (size_t)resident_rounds * (L + 1),
+                        d_chal + resident_rounds, ctx->final_out, d_st, ctx->stream, resident ? &sh->challenge : nullptr,
+                        resident ? &sh->st : nullptr))
+          return fail(ZK_ERR_CUDA, "tail kernel launch failed");
+        ctx->launches++;
+        ZK_CUDA(cudaGetLastError());
+        const size_t bytes = ((size_t)left * (L + 2)) * sizeof(Fr) + sizeof(StrobeState);
+        unsigned int* h_flags = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(ctx->host_small) + 8192 - 16);
+        ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->tail_out, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        if (resident) ZK_CUDA(cudaMemcpyAsync(h_flags, sh, 16, cudaMemcpyDeviceToHost, ctx->stream));
+        ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (resident && h_flags[2] != 0) return fail(ZK_ERR_TIMEOUT, "resident round kernel: a wait for a challenge ran out");
+        const Fr* h_msgs = reinterpret_cast<const Fr*>(ctx->host_small);
+        const Fr* h_chal = h_msgs + (size_t)left * (L + 1);
+        const StrobeState* h_st = reinterpret_cast<const StrobeState*>(h_chal + left);
+        for (uint32_t k = 0; k < left; k++) {
+          for (int c = 0; c <= L; c++)
+            fr_store(round_msgs + ((uint64_t)(round_offset + round + k) * (L + 1) + c) * 4, h_msgs[(size_t)k * (L + 1) + c]);
+          fr_store(challenges + 4 * (uint64_t)(round_offset + round + k), h_chal[k]);
+        }
+        *challenge = h_chal[left - 1];
+        memcpy(tr->m.strobe().state(), h_st->lanes, 200);
+        tr->m.strobe().pos() = (uint8_t)h_st->pos;
+        tr->m.strobe().pos_begin() = (uint8_t)h_st->pos_begin;
+        tr->m.strobe().cur_flags() = (uint8_t)h_st->cur_flags;
+        *finals_done = true;
+        return ZK_OK;
+      }
     }
     const uint64_t pairs = size >> (round + 1);
     const RoundScratch sc = ctx->next_msg_scratch(comm != nullptr);

@@ -25,8 +25,10 @@ int zk_ctx::setup() {
   rs.sink.seq = 0;
   ZK_CUDA(cudaMalloc(&final_out, sizeof(Fr) * 16));
   ZK_CUDA(cudaMalloc(&tail_out, 8192));
+  ZK_CUDA(cudaMalloc(&resident_sh, 1024));
+  ZK_CUDA(cudaMemsetAsync(resident_sh, 0, 1024, stream));
   ZK_CUDA(cudaMalloc(&tail_buf, sizeof(Fr) * 64 * kMaxPolys * 4));
-  ZK_CUDA(cudaHostAlloc(&host_small, 4096, cudaHostAllocDefault));
+  ZK_CUDA(cudaHostAlloc(&host_small, 8192, cudaHostAllocDefault));
   ZK_CUDA(cudaStreamSynchronize(stream));
   return 0;
 }
@@ -42,6 +44,7 @@ void zk_ctx::teardown() {
   cudaFree(final_out);
   cudaFree(tail_buf);
   cudaFree(tail_out);
+  cudaFree(resident_sh);
   cudaFree(work);
   cudaFree(aux);
   if (host_small) cudaFreeHost(host_small);

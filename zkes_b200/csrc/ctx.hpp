@@ -60,9 +60,10 @@ struct zk_ctx {
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   zk::RoundScratch rs{};
   zk::Fr* final_out = nullptr;   // kMaxPolys + 1 elements
-  void* tail_out = nullptr;      // single-block tail kernel: messages, challenges, transcript state (8 KiB)
+  void* tail_out = nullptr;      // device-resident rounds: messages, challenges, transcript state (8 KiB)
+  void* resident_sh = nullptr;   // zk::ResidentShared: hand-over area of the resident multi-round kernel
   zk::Fr* tail_buf = nullptr;    // sharded proves: gathered values and the last log2(world) rounds' tables
-  void* host_small = nullptr;    // pinned, 4 KiB: round messages and other tiny read-backs
+  void* host_small = nullptr;    // pinned, 8 KiB: round messages and other tiny read-backs
   void* mailbox = nullptr;       // pinned + mapped: message kernels publish here, the host polls
   void* work = nullptr;          // grow-only device scratch (copies of caller data, round buffers)
   size_t work_bytes = 0;

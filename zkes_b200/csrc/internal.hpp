@@ -57,8 +57,17 @@ void launch_general_final(const Fr* const* tables_dev, const Fr* scalars, const 
 // tail.cu
 struct StrobeState;
 constexpr uint32_t kTailMax = 1024;  // entries per table the single-block tail kernel takes over at
+// r_dev / st_dev (device pointers, both or neither): take the challenge to bind first and the transcript
+// state from device memory (left there by the resident kernel) instead of from r / st.
 int launch_tail(int num_poly, const Fr* const* src, uint32_t size, bool fold_first, const Fr& r, const StrobeState& st,
-                Fr* out_msgs, Fr* out_chal, Fr* out_final, StrobeState* out_st, cudaStream_t stream);
+                Fr* out_msgs, Fr* out_chal, Fr* out_final, StrobeState* out_st, cudaStream_t stream,
+                const Fr* r_dev = nullptr, const StrobeState* st_dev = nullptr);
+
+// resident.cu
+struct ResidentShared;
+int launch_resident(int num_poly, const Fr* const* src, Fr* const* ping, Fr* const* pong, uint64_t size, uint32_t rounds,
+                    const StrobeState& st, Fr* partials, int max_blocks, int sm_count, ResidentShared* sh, Fr* out_msgs,
+                    Fr* out_chal, cudaStream_t stream);
 
 // sparse.cu
 void launch_sparse_msg(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,

@@ -12,6 +12,17 @@ struct StrobeState {
   uint32_t pos, pos_begin, cur_flags, pad;
 };
 
+// Hand-over area of the resident multi-round kernel (device global memory).
+struct ResidentShared {
+  unsigned int arrive;       // block tickets, counted up over all rounds
+  unsigned int seq;          // rounds whose challenge has been published
+  unsigned int error;        // non-zero: a bounded wait ran out
+  unsigned int pad;
+  FixedMul<FrParams> table;  // multiplier table of the latest challenge
+  Fr challenge;              // the latest challenge (Montgomery form)
+  StrobeState st;            // transcript state after the latest challenge
+};
+
 ZK_HD uint64_t rotl64_c(uint64_t x, int n) { return n ? (x << n) | (x >> (64 - n)) : x; }
 
 ZK_HD void keccak_f1600_dev(uint64_t* a) {

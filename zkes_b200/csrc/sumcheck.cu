@@ -10,14 +10,14 @@
 // the block through shared memory and over the grid by the last block to finish.
 #include "internal.hpp"
 #include "reduce.cuh"
-#include "warp_tile.cuh"
+#include "round_pass.cuh"
 
 namespace zk {
 
 namespace {
 
-constexpr int kThreads = 128;
-constexpr int kWarps = kThreads / 32;
+constexpr int kThreads = kRoundThreads;
+constexpr int kWarps = kRoundWarps;
 
 template <int L>
 struct RoundParams {
@@ -32,87 +32,9 @@ template <int L, bool FOLD>
 __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_round(const RoundParams<L> p) {
   __shared__ uint4 stage[kWarps][WarpTile<8>::kChunks];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint4* sw = stage[warp];
-  const uint64_t tiles = (p.pairs + 31) >> 5;
-  const uint64_t warp_global = (uint64_t)blockIdx.x * kWarps + warp;
-  const uint64_t warp_stride = (uint64_t)gridDim.x * kWarps;
-
-  Wide acc[L + 1];
-#pragma unroll
-  for (int c = 0; c <= L; c++)
-#pragma unroll
-    for (int k = 0; k < 16; k++) acc[c].v[k] = 0;
-  int pending = 0;
-
-  for (uint64_t tile = warp_global; tile < tiles; tile += warp_stride) {
-    const uint64_t pair0 = tile << 5;
-    const uint32_t valid_pairs = (uint32_t)((p.pairs - pair0) < 32 ? (p.pairs - pair0) : 32);
-    Fr u0[L], d[L];
-    if (FOLD) {
-      uint4 raw[L][8];
-#pragma unroll
-      for (int i = 0; i < L; i++)
-        WarpTile<8>::issue(reinterpret_cast<const uint4*>(p.src[i]) + pair0 * 8, valid_pairs * 8, lane, raw[i]);
-#pragma unroll
-      for (int i = 0; i < L; i++) {
-        uint4 q[8];
-        WarpTile<8>::transpose_in(sw, lane, raw[i], q);
-        const Fr t0 = fr_from_chunks(q[0], q[1]), t1 = fr_from_chunks(q[2], q[3]);
-        const Fr t2 = fr_from_chunks(q[4], q[5]), t3 = fr_from_chunks(q[6], q[7]);
-        const Fr a = add(t0, mul_fixed(p.r, sub(t1, t0)));
-        const Fr b = add(t2, mul_fixed(p.r, sub(t3, t2)));
-        uint4 o[4];
-        fr_to_chunks(a, o[0], o[1]);
-        fr_to_chunks(b, o[2], o[3]);
-        WarpTile<4>::store(reinterpret_cast<uint4*>(p.dst[i]) + pair0 * 4, valid_pairs * 4, sw, lane, o);
-        u0[i] = a;
-        d[i] = sub(b, a);
-      }
-    } else {
-      uint4 raw[L][4];
-#pragma unroll
-      for (int i = 0; i < L; i++)
-        WarpTile<4>::issue(reinterpret_cast<const uint4*>(p.src[i]) + pair0 * 4, valid_pairs * 4, lane, raw[i]);
-#pragma unroll
-      for (int i = 0; i < L; i++) {
-        uint4 q[4];
-        WarpTile<4>::transpose_in(sw, lane, raw[i], q);
-        const Fr a = fr_from_chunks(q[0], q[1]), b = fr_from_chunks(q[2], q[3]);
-        u0[i] = a;
-        d[i] = sub(b, a);
-      }
-    }
-    // lanes past the end of the table hold zeros and add nothing
-#pragma unroll
-    for (int c = 0; c <= L; c++) {
-      Wide w;
-      if (L == 1) {
-        const Fr one = Fr::one();
-        mul_wide(w, u0[0].v, one.v);
-      } else {
-        Fr prod = u0[0];
-#pragma unroll
-        for (int i = 1; i < L - 1; i++) prod = mul(prod, u0[i]);
-        mul_wide(w, prod.v, u0[L - 1].v);
-      }
-      wide_add(acc[c], w);
-      if (c < L) {
-#pragma unroll
-        for (int i = 0; i < L; i++) u0[i] = add(u0[i], d[i]);
-      }
-    }
-    if (++pending == kLazyProducts) {
-#pragma unroll
-      for (int c = 0; c <= L; c++) wide_trim<FrParams>(acc[c]);
-      pending = 0;
-    }
-  }
   Fr s[L + 1];
-#pragma unroll
-  for (int c = 0; c <= L; c++) {
-    wide_trim<FrParams>(acc[c]);
-    s[c] = redc<FrParams>(acc[c]);
-  }
+  round_pass<L, FOLD>(p.src, p.dst, p.r, p.pairs, (uint64_t)blockIdx.x * kWarps + warp, (uint64_t)gridDim.x * kWarps,
+                      stage[warp], lane, s);
   grid_sum<L + 1, kWarps>(s, p.sink);
 }
 

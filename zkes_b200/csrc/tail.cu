@@ -20,6 +20,8 @@ struct TailParams {
   int fold_first;   // bind `r` on the tables before the first message
   Fr r;
   StrobeState st;
+  const Fr* r_dev;            // when set: read r and the transcript state from device memory instead
+  const StrobeState* st_dev;
   Fr* out_msgs;     // rounds * (L + 1)
   Fr* out_chal;     // rounds
   Fr* out_final;    // L table values, then their product
@@ -36,15 +38,21 @@ __global__ void __launch_bounds__(kTailThreads) k_tail(const TailParams<L> p) {
   __shared__ __align__(16) uint8_t stream[WarpStrobe::round_stream_bytes<L>() + 15];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   WarpStrobe ws;                  // live in warp 0 only
-  ws.a = (warp == 0 && lane < 25) ? p.st.lanes[lane] : 0;
-  ws.pos = p.st.pos;
-  ws.pos_begin = p.st.pos_begin;
+  if (p.st_dev) {
+    ws.a = (warp == 0 && lane < 25) ? p.st_dev->lanes[lane] : 0;
+    ws.pos = p.st_dev->pos;
+    ws.pos_begin = p.st_dev->pos_begin;
+  } else {
+    ws.a = (warp == 0 && lane < 25) ? p.st.lanes[lane] : 0;
+    ws.pos = p.st.pos;
+    ws.pos_begin = p.st.pos_begin;
+  }
   if (tid == 0) WarpStrobe::init_round_stream<L>(stream);
 
   for (uint32_t i = tid; i < p.size; i += kTailThreads)
 #pragma unroll
     for (int t = 0; t < L; t++) A[(size_t)t * p.size + i] = p.src[t][i];
-  if (tid == 0) chal[0] = p.r;
+  if (tid == 0) chal[0] = p.r_dev ? *p.r_dev : p.r;
   __syncthreads();
 
   Fr* cur = A;
@@ -142,8 +150,11 @@ __global__ void __launch_bounds__(kTailThreads) k_tail(const TailParams<L> p) {
 
 template <int L>
 int launch_tail_t(const Fr* const* src, uint32_t size, bool fold_first, const Fr& r, const StrobeState& st, Fr* out_msgs,
-                  Fr* out_chal, Fr* out_final, StrobeState* out_st, cudaStream_t stream) {
+                  Fr* out_chal, Fr* out_final, StrobeState* out_st, cudaStream_t stream, const Fr* r_dev,
+                  const StrobeState* st_dev) {
   TailParams<L> p;
+  p.r_dev = r_dev;
+  p.st_dev = st_dev;
   for (int i = 0; i < L; i++) p.src[i] = src[i];
   p.size = size;
   p.fold_first = fold_first ? 1 : 0;
@@ -163,12 +174,13 @@ int launch_tail_t(const Fr* const* src, uint32_t size, bool fold_first, const Fr
 }  // namespace
 
 int launch_tail(int num_poly, const Fr* const* src, uint32_t size, bool fold_first, const Fr& r, const StrobeState& st,
-                Fr* out_msgs, Fr* out_chal, Fr* out_final, StrobeState* out_st, cudaStream_t stream) {
+                Fr* out_msgs, Fr* out_chal, Fr* out_final, StrobeState* out_st, cudaStream_t stream, const Fr* r_dev,
+                const StrobeState* st_dev) {
   switch (num_poly) {
-    case 1: return launch_tail_t<1>(src, size, fold_first, r, st, out_msgs, out_chal, out_final, out_st, stream);
-    case 2: return launch_tail_t<2>(src, size, fold_first, r, st, out_msgs, out_chal, out_final, out_st, stream);
-    case 3: return launch_tail_t<3>(src, size, fold_first, r, st, out_msgs, out_chal, out_final, out_st, stream);
-    case 4: return launch_tail_t<4>(src, size, fold_first, r, st, out_msgs, out_chal, out_final, out_st, stream);
+    case 1: return launch_tail_t<1>(src, size, fold_first, r, st, out_msgs, out_chal, out_final, out_st, stream, r_dev, st_dev);
+    case 2: return launch_tail_t<2>(src, size, fold_first, r, st, out_msgs, out_chal, out_final, out_st, stream, r_dev, st_dev);
+    case 3: return launch_tail_t<3>(src, size, fold_first, r, st, out_msgs, out_chal, out_final, out_st, stream, r_dev, st_dev);
+    case 4: return launch_tail_t<4>(src, size, fold_first, r, st, out_msgs, out_chal, out_final, out_st, stream, r_dev, st_dev);
     default: return -1;
   }
 }

@@ -20,13 +20,15 @@ struct WarpTile {
     return row * CH + (col ^ ((row / (8 / CH)) % CH));
   }
 
-  // Coalesced global reads into registers; chunks at or beyond `valid` read as zero.
+  // Coalesced global reads into registers; chunks at or beyond `valid` read as zero.  COHERENT
+  // reads through L2 only (ld.cg): for data that other blocks of the same launch have written.
+  template <bool COHERENT = false>
   static __device__ __forceinline__ void issue(const uint4* __restrict__ g, uint32_t valid, int lane,
                                                uint4 (&raw)[CH]) {
 #pragma unroll
     for (int j = 0; j < CH; j++) {
       const uint32_t c = j * 32 + lane;
-      raw[j] = (c < valid) ? __ldg(g + c) : make_uint4(0, 0, 0, 0);
+      raw[j] = (c < valid) ? (COHERENT ? __ldcg(g + c) : __ldg(g + c)) : make_uint4(0, 0, 0, 0);
     }
   }
 
