@@ -42,6 +42,7 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
   __shared__ Fr msg[L + 1];
   __shared__ __align__(16) uint8_t stream[WarpStrobe::round_stream_bytes<L>() + 15];
   __shared__ int flag, ok_flag;
+  __shared__ __align__(16) uint64_t keccak_scratch[64];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int NV = L + 1;
   if (threadIdx.x == 0) WarpStrobe::init_round_stream<L>(stream);
@@ -120,6 +121,7 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
       __syncthreads();
       if (warp == 0) {
         WarpStrobe ws;
+        ws.scratch = keccak_scratch;
         if (round == 0) {
           ws.a = lane < 25 ? p.st.lanes[lane] : 0;
           ws.pos = p.st.pos;

@@ -138,45 +138,52 @@ static __constant__ uint64_t kKeccakRcDev[24] = {
     0x8000000000008002ull, 0x8000000000000080ull, 0x000000000000800Aull, 0x800000008000000Aull,
     0x8000000080008081ull, 0x8000000000008080ull, 0x0000000080000001ull, 0x8000000080008008ull};
 
-// One Keccak-f[1600] over a warp.  Per round every thread pulls the ten lanes of its two neighbour
-// columns (theta), rotates its own lane (rho), then pulls the three rotated lanes that pi moves into
-// its row positions x, x+1, x+2 (pi and chi together): two shuffle stages per round.
-static __device__ __noinline__ uint2 keccak_f1600_warp(uint2 a, int lane) {
-  const int l = lane < 25 ? lane : 0;  // idle threads mirror lane 0's indices; their values are never used
+// One Keccak-f[1600] over a warp, exchanging lanes through shared memory: a 64-bit load moves a
+// whole lane where a shuffle moves half of one, and a 128-bit load two.  Per round: every thread
+// parks its lane column-major, reads its two neighbour columns (theta, 6 loads), rotates (rho),
+// parks the result at its pi position row-major and reads the three lanes of its row that chi
+// needs.  scratch: 2 x 32 eight-byte slots, 16-byte aligned, private to the warp.
+static __device__ __noinline__ uint2 keccak_f1600_warp(uint2 a, int lane, uint64_t* scratch) {
+  const int l = lane < 25 ? lane : 0;  // idle threads mirror lane 0's indices; they store nothing
   const int x = l % 5, y = l / 5;
   // rho offsets, lane = x + 5 y, packed 6 bits each
-  const int my_rot = (int)((l < 10 ? (0x5371AC91B73E040ull >> (6 * l))                      // 0 1 62 28 27 36 44 6 55 20
+  const int my_rot = (int)((l < 10 ? (0x5371AC91B73E040ull >> (6 * l))                     // 0 1 62 28 27 36 44 6 55 20
                                    : l < 20 ? (0x2153EDA6766B283ull >> (6 * (l - 10)))      // 3 10 43 25 39 41 45 15 21 8
-                                            : (0xEE3D092ull >> (6 * (l - 20)))) & 63);  // 18 2 61 56 14
+                                            : (0xEE3D092ull >> (6 * (l - 20)))) & 63);      // 18 2 61 56 14
   const bool swap_halves = my_rot >= 32;
   const int sh = my_rot & 31;
-  const int col_prev = (x + 4) % 5, col_next = (x + 1) % 5;
-  // pi: the lane that lands at (X, Y) comes from ((X + 3Y) mod 5, X)
+  // column-major tile A (column stride 6 slots) and row-major tile B (row stride 6 slots)
+  uint64_t* A = scratch;
+  uint64_t* B = scratch + 32;
+  uint64_t* a_slot = A + 6 * x + y;
+  const uint64_t* col_p = A + 6 * ((x + 4) % 5);
+  const uint64_t* col_n = A + 6 * ((x + 1) % 5);
+  // pi: lane (x, y) moves to (y, (2x + 3y) mod 5)
+  uint64_t* b_slot = B + 6 * ((2 * x + 3 * y) % 5) + y;
+  const uint64_t* row = B + 6 * y;
   const int x1 = (x + 1) % 5, x2 = (x + 2) % 5;
-  const int s0 = ((x + 3 * y) % 5) + 5 * x, s1 = ((x1 + 3 * y) % 5) + 5 * x1, s2 = ((x2 + 3 * y) % 5) + 5 * x2;
   uint32_t lo = a.x, hi = a.y;
-#pragma unroll 2
-  for (int round = 0; round < 24; round++) {
-    uint32_t plo = 0, phi = 0, nlo = 0, nhi = 0;
 #pragma unroll
-    for (int k = 0; k < 5; k++) {
-      plo ^= __shfl_sync(0xffffffffu, lo, col_prev + 5 * k);
-      phi ^= __shfl_sync(0xffffffffu, hi, col_prev + 5 * k);
-      nlo ^= __shfl_sync(0xffffffffu, lo, col_next + 5 * k);
-      nhi ^= __shfl_sync(0xffffffffu, hi, col_next + 5 * k);
-    }
+  for (int round = 0; round < 24; round++) {
+    const uint64_t rc = kKeccakRcDev[round];  // uniform load; selected, not branched on, so the warp stays converged
+    if (lane < 25) *reinterpret_cast<uint2*>(a_slot) = make_uint2(lo, hi);
+    __syncwarp();
+    const uint4 p01 = *reinterpret_cast<const uint4*>(col_p), p23 = *reinterpret_cast<const uint4*>(col_p + 2);
+    const uint2 p4 = *reinterpret_cast<const uint2*>(col_p + 4);
+    const uint4 n01 = *reinterpret_cast<const uint4*>(col_n), n23 = *reinterpret_cast<const uint4*>(col_n + 2);
+    const uint2 n4 = *reinterpret_cast<const uint2*>(col_n + 4);
+    const uint32_t plo = p01.x ^ p01.z ^ p23.x ^ p23.z ^ p4.x, phi = p01.y ^ p01.w ^ p23.y ^ p23.w ^ p4.y;
+    const uint32_t nlo = n01.x ^ n01.z ^ n23.x ^ n23.z ^ n4.x, nhi = n01.y ^ n01.w ^ n23.y ^ n23.w ^ n4.y;
     lo ^= plo ^ __funnelshift_l(nhi, nlo, 1);
     hi ^= phi ^ __funnelshift_l(nlo, nhi, 1);
     const uint32_t tl = swap_halves ? hi : lo, th = swap_halves ? lo : hi;
     const uint32_t rlo = __funnelshift_l(th, tl, sh), rhi = __funnelshift_l(tl, th, sh);
-    const uint32_t b0l = __shfl_sync(0xffffffffu, rlo, s0), b0h = __shfl_sync(0xffffffffu, rhi, s0);
-    const uint32_t b1l = __shfl_sync(0xffffffffu, rlo, s1), b1h = __shfl_sync(0xffffffffu, rhi, s1);
-    const uint32_t b2l = __shfl_sync(0xffffffffu, rlo, s2), b2h = __shfl_sync(0xffffffffu, rhi, s2);
-    lo = b0l ^ (~b1l & b2l);
-    hi = b0h ^ (~b1h & b2h);
-    const uint64_t rc = kKeccakRcDev[round];  // uniform load; selected, not branched on, so the warp stays converged
-    lo ^= lane == 0 ? (uint32_t)rc : 0u;
-    hi ^= lane == 0 ? (uint32_t)(rc >> 32) : 0u;
+    if (lane < 25) *reinterpret_cast<uint2*>(b_slot) = make_uint2(rlo, rhi);
+    __syncwarp();
+    const uint2 b0 = *reinterpret_cast<const uint2*>(row + x), b1 = *reinterpret_cast<const uint2*>(row + x1),
+                b2 = *reinterpret_cast<const uint2*>(row + x2);
+    lo = b0.x ^ (~b1.x & b2.x) ^ (lane == 0 ? (uint32_t)rc : 0u);
+    hi = b0.y ^ (~b1.y & b2.y) ^ (lane == 0 ? (uint32_t)(rc >> 32) : 0u);
   }
   return make_uint2(lo, hi);
 }
@@ -184,13 +191,14 @@ static __device__ __noinline__ uint2 keccak_f1600_warp(uint2 a, int lane) {
 struct WarpStrobe {
   uint64_t a;                // this thread's state lane (threads 0..24)
   uint32_t pos, pos_begin;   // identical in every thread
+  uint64_t* scratch;         // 64 eight-byte slots of shared memory (16-byte aligned) for the permutation
 
   __device__ __forceinline__ void run_f(int lane) {
     if ((int)(pos >> 3) == lane) a ^= (uint64_t)(pos_begin & 0xffu) << (8 * (pos & 7));
     if ((int)((pos + 1) >> 3) == lane) a ^= (uint64_t)0x04 << (8 * ((pos + 1) & 7));
     if (lane == 20) a ^= (uint64_t)0x80 << 56;  // byte kStrobeRate + 1 = 167
     __syncwarp();  // shuffles between diverged threads are far slower than between converged ones
-    const uint2 t = keccak_f1600_warp(make_uint2((uint32_t)a, (uint32_t)(a >> 32)), lane);
+    const uint2 t = keccak_f1600_warp(make_uint2((uint32_t)a, (uint32_t)(a >> 32)), lane, scratch);
     a = ((uint64_t)t.y << 32) | t.x;
     pos = 0;
     pos_begin = 0;

@@ -37,7 +37,9 @@ __global__ void __launch_bounds__(kTailThreads) k_tail(const TailParams<L> p) {
   Fr* chal = red + (kTailThreads / 32) * (L + 1);   // 1
   __shared__ __align__(16) uint8_t stream[WarpStrobe::round_stream_bytes<L>() + 15];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  __shared__ __align__(16) uint64_t keccak_scratch[64];
   WarpStrobe ws;                  // live in warp 0 only
+  ws.scratch = keccak_scratch;
   if (p.st_dev) {
     ws.a = (warp == 0 && lane < 25) ? p.st_dev->lanes[lane] : 0;
     ws.pos = p.st_dev->pos;
