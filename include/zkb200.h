@@ -196,6 +196,19 @@ int zk_fix_from_right(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem eva
 /* evaluate_multilinear_extension / DenseMLPoly::evaluate_at_point, src/util/poly.rs:622-652, 788-791:
  * out (4 x u64, host) = sum_i evals[i] * eq(i, point) for a table of 2^n elements and n coordinates. */
 int zk_mle_eval(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, const uint64_t* point, uint64_t* out);
+/* permute_evals_by_ranges, src/basicblock/einsum.rs:142-198: reorders the variables of a table of 2^n elements
+ * of elem_bytes (32: field elements; 16: the i128 witness integers).  ranges holds n_ranges (start, end) pairs
+ * of old variable indices; listed one after the other they are the new variable order, lowest first.  Ranges
+ * that are invalid, overlap or do not cover all n variables are ZK_ERR_ARG (the reference's asserts).  out
+ * must not alias evals. */
+int zk_permute_by_ranges(zk_ctx* ctx, uint32_t n, uint32_t elem_bytes, const void* evals, zk_mem evals_mem,
+                         uint32_t n_ranges, const uint64_t* ranges, void* out, zk_mem out_mem);
+/* fix_variables_zkgpt, src/util/poly.rs:1378-1473: t holds 2^num_vars signed 128-bit little-endian integers
+ * (Rust i128), laid out b + c * 2^k; binds the k low variables to point[0..k):
+ * out[c] = sum_b eq(point)[b] * t[c * 2^k + b], 2^(num_vars-k) field elements.  The reference's q_bits argument
+ * only sizes its table of small multiples and does not change the result; it has no counterpart here. */
+int zk_fix_variables_int(zk_ctx* ctx, uint32_t num_vars, const void* t, zk_mem t_mem, uint32_t k, const uint64_t* point,
+                         uint64_t* out, zk_mem out_mem);
 /* out[lo] = sum_hi weights[hi] * evals[hi * 2^(n-k) + lo]: the contraction inside
  * fix_variables_from_right (poly.rs:719-741) with caller-given weights instead of an eq table
  * (no separate counterpart in the reference; used for trapdoor checksums of commitments). */
@@ -268,6 +281,18 @@ int zk_kzh2_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uint
 int zk_kzh3_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uint64_t* evals, zk_mem evals_mem,
                  const uint64_t* point, uint32_t point_len, const uint64_t* d_x_jac, uint64_t* d_y_jac_out,
                  uint64_t* c_y_affine_out, uint64_t* f_star_out);
+
+/* The G1 and field checks of kzh2_verify (src/crypto/polycommit/kzh2.rs:763-789, steps 2 and 3) and kzh3_verify
+ * (kzh3.rs:836-886, checks 2, 4 and 5); the pairing checks (step 1; checks 1 and 3) stay with the caller.
+ *   KZH2: MSM(h_y, f_star) == sum_i eq(r_x)[i] d_x[i];  f_star(r_y) == output.
+ *   KZH3: c_y == sum_i eq(r_x)[i] d_x[i];  MSM(h_z, f_star) == sum_i eq(r_y)[i] d_y[i];  f_star(r_z) == output.
+ * point as for the opens (left-padded to n coordinates); output: 4 x u64; d_x_jac / d_y_jac: Jacobian points as the
+ * commit and open return them (d_y_jac and c_y_affine only for a KZH3 SRS, else NULL); f_star: 2^y_log (KZH2) or
+ * 2^z_log (KZH3) elements.  All host pointers.  *ok = 1 when every check holds; *failed_check (optional) = the
+ * reference's number of the first failing check, 0 when none. */
+int zk_kzh_verify_g1(zk_ctx* ctx, const zk_kzh_srs* srs, const uint64_t* point, uint32_t point_len, const uint64_t* output,
+                     const uint64_t* d_x_jac, const uint64_t* d_y_jac, const uint64_t* c_y_affine, const uint64_t* f_star,
+                     int* ok, int* failed_check);
 
 /* sparse_kzh2_commit (src/crypto/polycommit/sparse_kzh2.rs:14-82) / sparse_kzh3_commit (sparse_kzh3.rs:32-110):
  * the polynomial is given by nnz (index, value) pairs with distinct indices below 2^n (host arrays). */

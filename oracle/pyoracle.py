@@ -247,6 +247,73 @@ def fix_variables_from_right(evals, fixed):
     return out
 
 
+def permute_evals_by_ranges(evals, n, ranges):
+    """src/basicblock/einsum.rs:142-198: the ranges, one after the other, list the old variables in their new
+    order; bit old_var of the old index moves to its new position."""
+    assert len(evals) == 1 << n, "evals length must be 2^n"
+    assert len(ranges) > 0, "ranges must not be empty"
+    new_var_order, seen = [], [False] * n
+    for start, end in ranges:
+        assert start <= end <= n, "invalid range"
+        for v in range(start, end):
+            assert not seen[v], "variable appears in multiple ranges"
+            seen[v] = True
+            new_var_order.append(v)
+    assert len(new_var_order) == n, "ranges must cover all variables exactly once"
+    pos_new = [0] * n
+    for new_pos, old_var in enumerate(new_var_order):
+        pos_new[old_var] = new_pos
+    out = [evals[0]] * len(evals)
+    for idx_old in range(len(evals)):
+        idx_new = 0
+        for old_var in range(n):
+            if idx_old >> old_var & 1:
+                idx_new |= 1 << pos_new[old_var]
+        out[idx_new] = evals[idx_old]
+    return out
+
+
+def fix_variables_zkgpt(num_vars, t_idx, r, q_bits):
+    """src/util/poly.rs:1378-1473: t_idx holds integers laid out b + c * n (n = 2^len(r)); the challenges split
+    into y = r[:right_bits], x = r[right_bits:]; a table fm[br][t] = t * eqy[br] built by additions serves
+    |t| <= 2^q_bits, larger magnitudes go through quotient and remainder; per column the partial sums over
+    the right index are combined with eqx."""
+    n = 1 << len(r)
+    m = 1 << (num_vars - len(r))
+    logn = len(r)
+    left_bits = logn // 2
+    right_bits = logn - left_bits
+    eqy = precompute_eq(r[:right_bits])
+    eqx = precompute_eq(r[right_bits:])
+    max_t = 1 << q_bits
+    right_size = 1 << right_bits
+    fm = []
+    for br in range(right_size):
+        row = [0] * (max_t + 1)
+        for t in range(1, max_t + 1):
+            row[t] = (row[t - 1] + eqy[br]) % R_MOD
+        fm.append(row)
+    out = [0] * m
+    for c in range(m):
+        ac = [0] * (1 << left_bits)
+        for b in range(n):
+            br, bl = b & (right_size - 1), b >> right_bits
+            t = t_idx[c * n + b]
+            abs_t = abs(t)
+            if abs_t == 0:
+                continue
+            if abs_t <= max_t:
+                val = fm[br][abs_t]
+            else:
+                q, rem = divmod(abs_t, max_t)
+                val = fm[br][max_t] * q % R_MOD
+                if rem > 0:
+                    val = (val + fm[br][rem]) % R_MOD
+            ac[bl] = (ac[bl] + val) % R_MOD if t > 0 else (ac[bl] - val) % R_MOD
+        out[c] = sum(e * a for e, a in zip(eqx, ac)) % R_MOD
+    return out
+
+
 def evaluate_multilinear_extension(u, r):
     """src/util/poly.rs:622-652."""
     assert len(u) == 1 << len(r)

@@ -134,3 +134,56 @@ def test_sparse_kzh_commit_open(ctx, dims, n, nnz, ones):
             _, dy, cy, fs = kzh.sparse_kzh3_open(ctx, srs, pt, com, ev)
             _, ody, ocy, ofs = o.sparse_kzh3_open(osrs, pt, odx, ev)
             assert (dy, cy, fs) == (ody, ocy, ofs)
+
+
+@pytest.mark.parametrize("n", [2, 4, 5])
+def test_kzh2_verify_g1(ctx, n):
+    """The G1 / field steps of kzh2_verify (kzh2.rs:763-789) on the device: an honest opening passes,
+    and each tampered part fails at the step the reference would fail at (tests/test_kzh2.rs:42-175
+    checks only that honest openings verify)."""
+    rnd = random.Random(400 + n)
+    xl, yl = o.kzh2_degrees(n)
+    gk, tx, ty, rest = trapdoors(5, 1 << xl, 1 << yl)
+    osrs = o.KZH2SRS(n, gk, tx, ty, rest[0])
+    srs = kzh.KZHSRS.setup(ctx, 2, n, osrs.g, tx, ty, alpha=rest[0])
+    f = [rnd.randrange(M) for _ in range(1 << n)]
+    poly = DenseMLPoly.from_evaluations(f)
+    com = kzh.commit(ctx, srs, poly)
+    pt = [rnd.randrange(M) for _ in range(n)]
+    d_x, f_star = kzh.kzh2_open(ctx, srs, pt, com, poly)
+    value = o.evaluate_multilinear_extension(f, pt)
+    assert kzh.verify_g1(ctx, srs, pt, value, com.d_x_jac, f_star) == (True, 0)
+    assert kzh.verify_g1(ctx, srs, pt, value, d_x, f_star) == (True, 0)  # affine d_x as the proof carries it
+    assert kzh.verify_g1(ctx, srs, pt, (value + 1) % M, d_x, f_star) == (False, 3)
+    bad_f = list(f_star)
+    bad_f[0] = (bad_f[0] + 1) % M
+    assert kzh.verify_g1(ctx, srs, pt, value, d_x, bad_f) == (False, 2)
+    bad_dx = list(d_x)
+    bad_dx[-1] = o.g1_add(bad_dx[-1], osrs.g) if bad_dx[-1] is not None else osrs.g
+    assert kzh.verify_g1(ctx, srs, pt, value, bad_dx, f_star) == (False, 2)
+
+
+@pytest.mark.parametrize("n", [3, 4, 7])
+def test_kzh3_verify_g1(ctx, n):
+    """Checks 2, 4 and 5 of kzh3_verify (kzh3.rs:836-886)."""
+    rnd = random.Random(500 + n)
+    xl, yl, zl = o.kzh3_degrees(n)
+    gk, tx, ty, tz = trapdoors(6, 1 << xl, 1 << yl, 1 << zl)
+    tz = tz[:1 << zl]
+    osrs = o.KZH3SRS(n, gk, tx, ty, tz)
+    srs = kzh.KZHSRS.setup(ctx, 3, n, osrs.g, tx, ty, tau_z=tz)
+    f = [o.fr_from_int(rnd.randrange(-2 ** 15, 2 ** 15)) if i % 3 else rnd.randrange(M) for i in range(1 << n)]
+    poly = DenseMLPoly.from_evaluations(f)
+    com = kzh.commit(ctx, srs, poly)
+    pt = [rnd.randrange(M) for _ in range(n)]
+    d_x, d_y, c_y, f_star = kzh.kzh3_open(ctx, srs, pt, com, poly)
+    value = o.evaluate_multilinear_extension(f, pt)
+    assert kzh.verify_g1(ctx, srs, pt, value, d_x, f_star, d_y=d_y, c_y=c_y) == (True, 0)
+    assert kzh.verify_g1(ctx, srs, pt, (value + 5) % M, d_x, f_star, d_y=d_y, c_y=c_y) == (False, 5)
+    assert kzh.verify_g1(ctx, srs, pt, value, d_x, f_star, d_y=d_y, c_y=o.g1_add(c_y, osrs.g) if c_y else osrs.g) == (False, 2)
+    bad_dy = list(d_y)
+    bad_dy[0] = o.g1_add(bad_dy[0], osrs.g) if bad_dy[0] is not None else osrs.g
+    assert kzh.verify_g1(ctx, srs, pt, value, d_x, f_star, d_y=bad_dy, c_y=c_y) == (False, 4)
+    bad_f = list(f_star)
+    bad_f[-1] = (bad_f[-1] + 1) % M
+    assert kzh.verify_g1(ctx, srs, pt, value, d_x, bad_f, d_y=d_y, c_y=c_y) == (False, 4)

@@ -5,6 +5,8 @@ import json
 import os
 import random
 
+import pytest
+
 import coracle as c
 import pyoracle as o
 
@@ -136,3 +138,26 @@ def test_multithreaded_oracle_matches_single():
     b = c.linear_prove(b"x", tables)
     c.set_threads(1)
     assert a.round_messages == b.round_messages and a.final_eval == b.final_eval
+
+
+def test_permute_evals_by_ranges_hand_cases():
+    """src/basicblock/einsum.rs:142-198: identity, swapped halves, and the inverse of a permutation."""
+    evals = list(range(16))
+    assert o.permute_evals_by_ranges(evals, 4, [(0, 4)]) == evals
+    out = o.permute_evals_by_ranges(evals, 4, [(2, 4), (0, 2)])
+    assert out == [((i & 3) << 2) | (i >> 2) for i in range(16)]
+    assert o.permute_evals_by_ranges(out, 4, [(2, 4), (0, 2)]) == evals
+    with pytest.raises(AssertionError):
+        o.permute_evals_by_ranges(evals, 4, [(0, 3)])
+    with pytest.raises(AssertionError):
+        o.permute_evals_by_ranges(evals, 4, [(0, 3), (2, 4)])
+
+
+@pytest.mark.parametrize("num_vars,k,q_bits", [(4, 0, 3), (5, 2, 2), (7, 3, 4), (8, 5, 12), (9, 9, 3)])
+def test_fix_variables_zkgpt_is_the_lsb_fold_of_the_lifted_integers(num_vars, k, q_bits):
+    """The table-of-multiples algorithm of src/util/poly.rs:1378-1473 (both its lookup and its quotient branch)
+    computes sum_b eq(r)[b] t[c n + b], i.e. DenseMLPoly::fix_variables on the integers lifted to the field."""
+    rnd = random.Random(num_vars * 100 + k)
+    t = [rnd.randrange(-(1 << 9), 1 << 9) for _ in range(1 << num_vars)]
+    r = [rnd.randrange(o.R_MOD) for _ in range(k)]
+    assert o.fix_variables_zkgpt(num_vars, t, r, q_bits) == o.fix_variables([v % o.R_MOD for v in t], r)

@@ -6,7 +6,7 @@ Names are resolved lazily so that `python -m zkes_b200.build` can run before the
 import importlib
 
 _API = ("Context", "DenseMLPoly", "LinearSumcheckProver", "SumcheckProof", "Transcript",
-        "SparseDenseSumcheckProver", "evaluate_lagrange_basis", "fix_variables_from_right",
+        "SparseDenseSumcheckProver", "evaluate_lagrange_basis", "fix_variables_from_right", "permute_evals_by_ranges", "fix_variables_zkgpt",
         "SparseBoolSumcheckProver", "GeneralLinearSumcheckProver")
 
 

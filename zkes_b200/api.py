@@ -161,6 +161,49 @@ def fix_variables_from_right(ctx: Context, poly: "DenseMLPoly", fixed_vars) -> "
     return DenseMLPoly(poly.n - k, mont=out)
 
 
+def _i128_array(values):
+    """Python integers -> (len, 2) u64 array holding Rust i128 values (two's complement, little-endian)."""
+    out = np.empty((len(values), 2), dtype=np.uint64)
+    for i, v in enumerate(values):
+        assert -(1 << 127) <= v < (1 << 127), "value does not fit an i128"
+        u = v & ((1 << 128) - 1)
+        out[i, 0] = u & 0xFFFFFFFFFFFFFFFF
+        out[i, 1] = u >> 64
+    return out
+
+
+def permute_evals_by_ranges(ctx: Context, evals, n: int, ranges, integers: bool = False):
+    """src/basicblock/einsum.rs:142-198.  evals: field elements (canonical integers), or with integers=True
+    the i128 witness values; ranges: (start, end) pairs of old variables in their new order."""
+    assert len(evals) == 1 << n, "evals length must be 2^n"
+    assert len(ranges) > 0, "ranges must not be empty"
+    src = _i128_array(evals) if integers else to_mont_array(evals)
+    out = np.zeros_like(src)
+    rg = np.array([v for r in ranges for v in r], dtype=np.uint64)
+    check(lib.zk_permute_by_ranges(ctx.handle, n, 16 if integers else 32, _ptr(src), ZK_MEM_HOST, len(ranges), _ptr(rg),
+                                   _ptr(out), ZK_MEM_HOST), "zk_permute_by_ranges")
+    if integers:
+        res = []
+        for lo, hi in out.tolist():
+            u = (hi << 64) | lo
+            res.append(u - (1 << 128) if u >> 127 else u)
+        return res
+    return from_mont_array(out)
+
+
+def fix_variables_zkgpt(ctx: Context, num_vars: int, t_idx, r, q_bits: int = 0) -> "DenseMLPoly":
+    """src/util/poly.rs:1378-1473: binds the len(r) low variables of the integer table t_idx (layout b + c * n).
+    q_bits sizes the reference's lookup table and does not change the result; it is accepted and unused."""
+    k = len(r)
+    assert k <= num_vars and len(t_idx) == 1 << num_vars
+    src = _i128_array(t_idx)
+    pt = to_mont_array(r) if k else np.zeros((1, 4), dtype=np.uint64)
+    out = np.zeros((1 << (num_vars - k), 4), dtype=np.uint64)
+    check(lib.zk_fix_variables_int(ctx.handle, num_vars, _ptr(src), ZK_MEM_HOST, k, _ptr(pt), _ptr(out), ZK_MEM_HOST),
+          "zk_fix_variables_int")
+    return DenseMLPoly(num_vars - k, mont=out)
+
+
 class SumcheckProof:
     """src/crypto/sumcheck/prover.rs:9-14."""
 

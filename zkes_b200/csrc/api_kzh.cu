@@ -342,4 +342,93 @@ int zk_kzh3_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uint
   return ZK_OK;
 }
 
+// The G1 and field checks of kzh2_verify (kzh2.rs:763-789: steps 2 and 3) and kzh3_verify
+// (kzh3.rs:836-886: checks 2, 4 and 5); the pairing checks stay with the caller.
+int zk_kzh_verify_g1(zk_ctx* ctx, const zk_kzh_srs* srs, const uint64_t* point, uint32_t point_len, const uint64_t* output,
+                     const uint64_t* d_x_jac, const uint64_t* d_y_jac, const uint64_t* c_y_affine, const uint64_t* f_star,
+                     int* ok, int* failed_check) {
+  if (!ctx || !srs || !output || !d_x_jac || !f_star || !ok || (point_len && !point))
+    return fail(ZK_ERR_ARG, "kzh_verify_g1: NULL argument");
+  if (srs->dims == 3 && (!d_y_jac || !c_y_affine)) return fail(ZK_ERR_ARG, "kzh_verify_g1: a KZH3 opening carries d_y and c_y");
+  if (srs->world != 1) return fail(ZK_ERR_ARG, "kzh_verify_g1: needs a whole (unsharded) SRS");
+  CtxLock lk(ctx);
+  cudaStream_t st = ctx->stream;
+  const bool k3 = srs->dims == 3;
+  const uint32_t n = srs->n, xl = srs->x_log, yl = srs->y_log, zl = srs->z_log;
+  const uint32_t low_log = k3 ? zl : yl;                  // variables of f_star
+  const uint64_t nx = 1ull << xl, ny = 1ull << yl, n_low = 1ull << low_log;
+  std::vector<uint64_t> pt;
+  pad_point(point, point_len, n, pt);
+  const uint64_t* r_low = pt.data();                                  // r_y (KZH2) or r_z (KZH3)
+  const uint64_t* r_y3 = pt.data() + (size_t)zl * 4;                  // KZH3 only
+  const uint64_t* r_x = pt.data() + (size_t)(k3 ? zl + yl : yl) * 4;
+  const uint64_t n_big = nx > ny ? nx : ny;
+  char* base = nullptr;
+  size_t need = al((n_big + 1) * sizeof(Jacobian)) + al((n_big + 1) * sizeof(Affine)) + al((n_big + 40) * sizeof(Fr)) * 2 +
+                al(n_low * sizeof(Fr)) * 2 + al(8 * sizeof(Jacobian)) + al(8 * sizeof(Affine)) + 2048;
+  int rc = ctx->reserve_work(need, (void**)&base);
+  if (rc) return rc;
+  size_t off = 0;
+  auto take = [&](size_t bytes) { char* p = base + off; off += al(bytes); return p; };
+  Jacobian* d_jac = (Jacobian*)take((n_big + 1) * sizeof(Jacobian));
+  Affine* d_aff = (Affine*)take((n_big + 1) * sizeof(Affine));
+  Fr* eq = (Fr*)take((n_big + 40) * sizeof(Fr));
+  Fr* pt_dev = (Fr*)take((n_big + 40) * sizeof(Fr));
+  Fr* d_fstar = (Fr*)take(n_low * sizeof(Fr));
+  Fr* eq_low = (Fr*)take(n_low * sizeof(Fr));
+  Jacobian* res = (Jacobian*)take(8 * sizeof(Jacobian));
+  Affine* res_aff = (Affine*)take(8 * sizeof(Affine));
+
+  // res[0] = MSM(affine(d_x), eq(r_x))
+  ZK_CUDA(cudaMemcpyAsync(d_jac, d_x_jac, nx * sizeof(Jacobian), cudaMemcpyHostToDevice, st));
+  rc = normalize_device(ctx, d_jac, nx, d_aff);
+  if (rc) return rc;
+  rc = eq_table_device(ctx, r_x, xl, pt_dev, eq);
+  if (rc) return rc;
+  rc = msm_run(ctx, d_aff, nullptr, eq, nx, 1, res + 0, nullptr);
+  if (rc) return rc;
+  // res[1] = MSM(h_low, f_star)
+  ZK_CUDA(cudaMemcpyAsync(d_fstar, f_star, n_low * sizeof(Fr), cudaMemcpyHostToDevice, st));
+  rc = msm_run(ctx, srs->h[k3 ? 2 : 1], nullptr, d_fstar, n_low, 1, res + 1, nullptr);
+  if (rc) return rc;
+  if (k3) {  // res[2] = MSM(affine(d_y), eq(r_y))
+    ZK_CUDA(cudaMemcpyAsync(d_jac, d_y_jac, ny * sizeof(Jacobian), cudaMemcpyHostToDevice, st));
+    rc = normalize_device(ctx, d_jac, ny, d_aff);
+    if (rc) return rc;
+    rc = eq_table_device(ctx, r_y3, yl, pt_dev, eq);
+    if (rc) return rc;
+    rc = msm_run(ctx, d_aff, nullptr, eq, ny, 1, res + 2, nullptr);
+    if (rc) return rc;
+  }
+  rc = normalize_device(ctx, res, k3 ? 3 : 2, res_aff);
+  if (rc) return rc;
+  // f_star(r_low)
+  rc = eq_table_device(ctx, r_low, low_log, pt_dev, eq_low);
+  if (rc) return rc;
+  RoundScratch sc = ctx->rs;
+  sc.sink.pub_flag = nullptr;
+  launch_dot(d_fstar, eq_low, n_low, sc, st);
+  ctx->launches++;
+  ZK_CUDA(cudaGetLastError());
+  char* h = reinterpret_cast<char*>(ctx->host_small);
+  ZK_CUDA(cudaMemcpyAsync(h, res_aff, 3 * sizeof(Affine), cudaMemcpyDeviceToHost, st));
+  ZK_CUDA(cudaMemcpyAsync(h + 256, ctx->rs.sink.msg, sizeof(Fr), cudaMemcpyDeviceToHost, st));
+  ZK_CUDA(cudaStreamSynchronize(st));
+  const char* a0 = h;                    // sum eq(r_x)[i] d_x[i]
+  const char* a1 = h + sizeof(Affine);   // MSM(h_low, f_star)
+  const char* a2 = h + 2 * sizeof(Affine);
+  int bad = 0;
+  if (!k3) {
+    if (memcmp(a0, a1, sizeof(Affine)) != 0) bad = 2;
+    else if (memcmp(h + 256, output, sizeof(Fr)) != 0) bad = 3;
+  } else {
+    if (memcmp(a0, c_y_affine, sizeof(Affine)) != 0) bad = 2;
+    else if (memcmp(a1, a2, sizeof(Affine)) != 0) bad = 4;
+    else if (memcmp(h + 256, output, sizeof(Fr)) != 0) bad = 5;
+  }
+  *ok = bad == 0;
+  if (failed_check) *failed_check = bad;
+  return ZK_OK;
+}
+
 }  // extern "C"

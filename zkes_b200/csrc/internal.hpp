@@ -43,6 +43,13 @@ uint32_t from_right_splits(uint64_t lo_n, uint64_t hi_n, int sm_count);
 int launch_from_right(const Fr* f, const Fr* eq, uint64_t lo_n, uint64_t hi_n, Fr* partial, Fr* out, int sm_count,
                       cudaStream_t s);
 
+// intfold.cu
+int launch_permute_ranges(const void* in, void* out, uint32_t n, uint32_t elem_bytes, const uint32_t* ranges,
+                          uint32_t n_ranges, int sm_count, cudaStream_t s);
+uint32_t int_fold_splits(uint64_t n_rows, uint64_t m_cols, int sm_count);
+int launch_int_fold(const void* t, const Fr* eq, uint64_t n_rows, uint64_t m_cols, Fr* partial, Fr* out, int sm_count,
+                    cudaStream_t s);
+
 // general.cu
 void launch_sbool_msg(const uint32_t* keys, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* eq,
                       const Fr* weights, uint32_t vars_left, const RoundScratch& sc, cudaStream_t s);

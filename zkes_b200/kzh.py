@@ -110,6 +110,39 @@ def kzh3_open(ctx, srs: KZHSRS, point, com: KZHCommitment, poly):
     return com.d_x, curve.jacobian_to_affine_py(dy), curve.affine_from_array(cy)[0], from_mont_array(fs)
 
 
+def _jac_array(points_or_jac):
+    """(len, 12) Jacobian array from either such an array or a list of affine points (None = infinity)."""
+    if isinstance(points_or_jac, np.ndarray):
+        return points_or_jac
+    out = np.zeros((max(len(points_or_jac), 1), 12), dtype=np.uint64)
+    aff = curve.affine_to_array(points_or_jac)
+    one = to_mont_array([1], curve.Q_MOD)[0]
+    for i, p in enumerate(points_or_jac):
+        if p is None:      # infinity: z = 0 (x = y = 1 as to_jacobian writes it)
+            out[i, 0:4] = one
+            out[i, 4:8] = one
+            continue
+        out[i, :8] = aff[i]
+        out[i, 8:] = one
+    return out
+
+
+def verify_g1(ctx, srs: KZHSRS, point, output: int, d_x, f_star, d_y=None, c_y=None):
+    """The G1 / field part of kzh2_verify (kzh2.rs:763-789) and kzh3_verify (kzh3.rs:836-886): returns
+    (ok, number of the first failing check in the reference's numbering, 0 if none).  Pairing checks are the caller's."""
+    pt = to_mont_array(point) if len(point) else np.zeros((1, 4), dtype=np.uint64)
+    outp = to_mont_array([output])
+    dx = _jac_array(d_x)
+    dy = _jac_array(d_y) if d_y is not None else None
+    cy = curve.affine_to_array([c_y]) if srs.dims == 3 else None
+    fs = to_mont_array(f_star)
+    ok, failed = ctypes.c_int(0), ctypes.c_int(0)
+    check(lib.zk_kzh_verify_g1(ctx.handle, srs.handle, _p(pt), len(point), _p(outp), _p(dx), _p(dy) if dy is not None else None,
+                               _p(cy) if cy is not None else None, _p(fs), ctypes.byref(ok), ctypes.byref(failed)),
+          "zk_kzh_verify_g1")
+    return bool(ok.value), failed.value
+
+
 def sparse_commit(ctx, srs: KZHSRS, evaluations: dict) -> KZHCommitment:
     """sparse_kzh2_commit (sparse_kzh2.rs:14-82) / sparse_kzh3_commit (sparse_kzh3.rs:32-110);
     evaluations: {index: value} as SparseMLPoly.evaluations."""
