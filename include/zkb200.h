@@ -236,6 +236,15 @@ int zk_msm_g1_gather(zk_ctx* ctx, const uint64_t* all_bases, zk_mem bases_mem, u
                      const uint64_t* scalars, zk_mem scalars_mem, uint64_t k, uint64_t* out_jac, zk_mem out_mem);
 /* CurveGroup::into_affine / normalize_batch for n Jacobian points -> n affine points. */
 int zk_g1_normalize(zk_ctx* ctx, const uint64_t* jac, zk_mem jac_mem, uint64_t n, uint64_t* affine_out, zk_mem out_mem);
+/* ark-serialize's compressed form of G1 points (what `serialize_compressed` writes: the transcript bytes of a
+ * KZH3 commitment, src/crypto/polycommit/kzh3.rs:406-411 through util/serialization.rs:14-21, and the G1 vectors
+ * of the SRS files, src/crypto/srs_storage.rs:15-58).  32 bytes per point: x little-endian, bit 7 of the last
+ * byte set when y is the larger of {y, q - y}, bit 6 set (and everything else zero) for the point at infinity.
+ * Points cross as in the MSM entry points (64 bytes, Montgomery form, infinity = zeros).  Decompression rejects
+ * (ZK_ERR_ARG, with the index in zk_last_error) an x >= q, an x with no point above it, and inconsistent flags. */
+int zk_g1_compress(zk_ctx* ctx, const uint64_t* affine, zk_mem affine_mem, uint64_t n, uint8_t* out, zk_mem out_mem);
+int zk_g1_decompress(zk_ctx* ctx, const uint8_t* in, zk_mem in_mem, uint64_t n, uint64_t* affine_out, zk_mem out_mem);
+
 /* Shape the last MSM on this context chose (window width, windows, largest scalar magnitude in
  * bits, digit entries, buckets): used to report algorithmic work. */
 int zk_msm_last_stats(zk_ctx* ctx, int* window_bits, int* windows, int* max_bits, uint64_t* entries, uint64_t* buckets);

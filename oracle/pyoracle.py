@@ -651,6 +651,27 @@ def g1_serialize_compressed(p) -> bytes:
     return bytes(b)
 
 
+def g1_deserialize_compressed(b: bytes):
+    """Inverse of g1_serialize_compressed (ark-serialize `deserialize_compressed` for a curve of cofactor 1):
+    q = 3 mod 4, so the root of x^3 + 3 is its (q + 1) / 4-th power; the flag picks the root."""
+    assert len(b) == 32
+    neg, inf = bool(b[31] & 0x80), bool(b[31] & 0x40)
+    x = int.from_bytes(bytes(b[:31]) + bytes([b[31] & 0x3F]), "little")
+    if inf:
+        if neg or x:
+            raise ValueError("invalid flags")
+        return None
+    if x >= Q_MOD:
+        raise ValueError("x out of range")
+    rhs = (x * x * x + 3) % Q_MOD
+    y = pow(rhs, (Q_MOD + 1) // 4, Q_MOD)
+    if y * y % Q_MOD != rhs:
+        raise ValueError("not on the curve")
+    if (y > (Q_MOD - 1) // 2) != neg:
+        y = Q_MOD - y
+    return (x, y)
+
+
 # ----------------------------------------------------------------------------- seeded inputs
 def _chacha_block(key_words, counter):
     """RFC 8439 ChaCha20 block, zero nonce, 32-bit block counter."""

@@ -161,3 +161,16 @@ def test_fix_variables_zkgpt_is_the_lsb_fold_of_the_lifted_integers(num_vars, k,
     t = [rnd.randrange(-(1 << 9), 1 << 9) for _ in range(1 << num_vars)]
     r = [rnd.randrange(o.R_MOD) for _ in range(k)]
     assert o.fix_variables_zkgpt(num_vars, t, r, q_bits) == o.fix_variables([v % o.R_MOD for v in t], r)
+
+
+def test_g1_compressed_encoding_round_trip():
+    """The flag convention of the compressed form: generator (1, 2) has the smaller y, its negative the larger."""
+    g = (1, 2)
+    assert o.g1_serialize_compressed(g) == bytes([1]) + bytes(31)
+    assert o.g1_serialize_compressed((1, o.Q_MOD - 2)) == bytes([1]) + bytes(30) + bytes([0x80])
+    assert o.g1_serialize_compressed(None) == bytes(31) + bytes([0x40])
+    rnd = random.Random(3)
+    for _ in range(20):
+        p = o.g1_mul(g, rnd.randrange(1, o.R_MOD))
+        assert o.g1_deserialize_compressed(o.g1_serialize_compressed(p)) == p
+    assert o.g1_deserialize_compressed(o.g1_serialize_compressed(None)) is None

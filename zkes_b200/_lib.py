@@ -49,6 +49,8 @@ SIGNATURES = {
     "zk_fix_from_right": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_int]),
     "zk_kzh_verify_g1": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_void_p]),
+    "zk_g1_compress": (c_int, [c_void_p, c_void_p, c_int, c_uint64, c_void_p, c_int]),
+    "zk_g1_decompress": (c_int, [c_void_p, c_void_p, c_int, c_uint64, c_void_p, c_int]),
     "zk_mle_eval": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_void_p, c_void_p]),
     "zk_permute_by_ranges": (c_int, [c_void_p, c_uint32, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_int]),
     "zk_fix_variables_int": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_int]),

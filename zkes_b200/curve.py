@@ -88,6 +88,25 @@ def normalize(ctx, jac_arr: np.ndarray):
     return affine_from_array(out[:n])
 
 
+def serialize_compressed(ctx, points) -> bytes:
+    """ark-serialize compressed encoding of affine points ([(x, y) | None]), 32 bytes each."""
+    arr = affine_to_array(points)
+    out = np.zeros(max(len(points), 1) * 32, dtype=np.uint8)
+    check(lib.zk_g1_compress(ctx.handle, _p(arr) if len(points) else None, ZK_MEM_HOST, len(points), _p(out), ZK_MEM_HOST),
+          "zk_g1_compress")
+    return out[:32 * len(points)].tobytes()
+
+
+def deserialize_compressed(ctx, data: bytes):
+    """Inverse of serialize_compressed; raises ZkError for an invalid encoding."""
+    assert len(data) % 32 == 0
+    n = len(data) // 32
+    src = np.frombuffer(data, dtype=np.uint8).copy() if n else np.zeros(32, dtype=np.uint8)
+    out = np.zeros((max(n, 1), 8), dtype=np.uint64)
+    check(lib.zk_g1_decompress(ctx.handle, _p(src), ZK_MEM_HOST, n, _p(out), ZK_MEM_HOST), "zk_g1_decompress")
+    return affine_from_array(out[:n])
+
+
 def last_stats(ctx):
     w, k, mb = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
     e, b = ctypes.c_uint64(), ctypes.c_uint64()

@@ -73,6 +73,11 @@ class KZHCommitment:
     def d_x(self):
         return curve.jacobian_to_affine_py(self.d_x_jac)
 
+    def to_transcript_bytes(self, ctx) -> bytes:
+        """Commitment::to_transcript_bytes: the compressed c for KZH3 (kzh3.rs:406-411), nothing for KZH2
+        (the trait's default, polycommit/mod.rs:408-412)."""
+        return curve.serialize_compressed(ctx, [self.c]) if self.srs.dims == 3 else b""
+
 
 def _evals_arg(poly):
     if poly.device_ptr is not None:
