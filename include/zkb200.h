@@ -59,8 +59,11 @@ uint64_t zk_launch_count(const zk_ctx* ctx);
 /* Options.  ZK_OPT_DEVICE_TAIL (default 1): the dense provers hand the rounds at or below 1024
  * table entries to one resident block that also runs the built-in transcript on the device
  * (identical outputs; only taken without a Fiat-Shamir callback and outside sharded rounds).
- * 0 keeps every round on the per-round kernels with the transcript on the host. */
-typedef enum zk_option { ZK_OPT_DEVICE_TAIL = 1 } zk_option;
+ * 0 keeps every round on the per-round kernels with the transcript on the host.
+ * ZK_OPT_REPLICATE_LOG (default 18): a sharded dense round loop gathers the tables onto every rank once all
+ * ranks together hold at most 2^value entries per table and finishes there without further exchanges
+ * (identical outputs); 0 keeps every local round sharded. */
+typedef enum zk_option { ZK_OPT_DEVICE_TAIL = 1, ZK_OPT_REPLICATE_LOG = 2 } zk_option;
 int zk_set_option(zk_ctx* ctx, int option, int value);
 /* The CUDA stream (cudaStream_t) every kernel of this context is launched on, so a host can
  * bracket calls with its own events. */
@@ -269,6 +272,14 @@ int zk_kzh_srs_setup_sharded(zk_ctx* ctx, int rank, int world, int dims, uint32_
  * c (8 x u64) and all 2^x_log Jacobian points of d_x. */
 int zk_kzh_commit_sharded(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs* srs, const uint64_t* local_evals,
                           zk_mem evals_mem, uint64_t* c_affine_out, uint64_t* d_x_jac_out);
+
+/* kzh2_open (src/crypto/polycommit/kzh2.rs:676-710) / kzh3_open (kzh3.rs:702-787) over a table sharded by
+ * x-rows, the layout of zk_kzh_commit_sharded: local_evals holds this rank's 2^n / world evaluations and srs is
+ * the rank's sharded SRS.  d_x_jac (all 2^x_log rows, as zk_kzh_commit_sharded returns them), d_y_jac_out and
+ * c_y_affine_out are used for a KZH3 SRS only (NULL otherwise).  Every rank receives the whole opening. */
+int zk_kzh_open_sharded(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs* srs, const uint64_t* local_evals, zk_mem evals_mem,
+                        const uint64_t* point, uint32_t point_len, const uint64_t* d_x_jac, uint64_t* d_y_jac_out,
+                        uint64_t* c_y_affine_out, uint64_t* f_star_out);
 /* An SRS the caller already holds (load_kzh3_srs, src/crypto/srs_storage.rs): h_full 2^n points,
  * h_mid 2^(n - x_log), h_low 2^z_log (KZH3 only). */
 int zk_kzh_srs_upload(zk_ctx* ctx, int dims, uint32_t n, const uint64_t* h_full, const uint64_t* h_mid,

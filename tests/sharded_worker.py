@@ -28,9 +28,11 @@ def problem(n, nnz, seed):
     return idx, vals, dense, f
 
 
-def emulate_sharded_linear(tables, rank, world, label):
+def emulate_sharded_linear(tables, rank, world, label, replicate_entries=0):
     """The sharded protocol with big-integer arithmetic: local partial messages, all-gather, sum,
-    replicated transcript, local folds, then the gathered tail."""
+    replicated transcript, local folds, then the gathered tail.  With replicate_entries, once all ranks
+    together hold at most that many entries per table the chunks are gathered (rank order = table order)
+    and every rank runs the remaining rounds on the whole table."""
     n = len(tables[0]).bit_length() - 1
     L = len(tables)
     local = [zd.shard_dense(t, rank, world) for t in tables]
@@ -42,6 +44,25 @@ def emulate_sharded_linear(tables, rank, world, label):
     msgs, chals = [], []
     n_local = n - zd.log2_exact(world)
     for _ in range(n_local):
+        if replicate_entries and len(local[0]) * world <= replicate_entries:
+            whole = []
+            for t in local:
+                parts = [None] * world
+                dist.all_gather_object(parts, t)
+                whole.append([v for part in parts for v in part])
+            while len(whole[0]) > 1:
+                helper.a_arrays = whole
+                msg = helper._round_message()
+                for m in msg:
+                    tr.append_scalar(b"round_message", m)
+                ch = tr.challenge_scalar(b"challenge")
+                msgs.append(msg)
+                chals.append(ch)
+                whole = [o.fix_variables(t, [ch]) for t in whole]
+            final = 1
+            for t in whole:
+                final = final * t[0] % o.R_MOD
+            return msgs, chals, [t[0] for t in whole], final
         helper.a_arrays = local
         part = helper._round_message()
         gathered = [None] * world
@@ -95,6 +116,10 @@ def main():
             p = o.LinearSumcheckProver(n, 3, t)
             pr = p.prove([a, dense, f], t)
             assert got3[0] == pr.round_messages and got3[3] == pr.final_eval
+            for entries in (1 << n, 8):  # gathered at once; gathered after some sharded rounds
+                rep = emulate_sharded_linear([a, dense, f], rank, world, b"sharded", replicate_entries=entries)
+                assert rep[0] == pr.round_messages and rep[1] == p.challenges and rep[3] == pr.final_eval
+                assert rep[2] == [x[0] for x in p.a_arrays]
     else:
         local_rank = int(os.environ.get("LOCAL_RANK", rank))
         torch.cuda.set_device(local_rank)
@@ -102,34 +127,39 @@ def main():
         from zkes_b200 import Context, DenseMLPoly, Transcript
         ctx = Context(local_rank)
         comm = zd.Comm(ctx)
-        for n, nnz, seed in [(3, 2, 1), (6, 9, 2), (11, 100, 3), (13, 3000, 4)]:
-            if n < zd.log2_exact(world):
-                continue
-            idx, vals, dense, f = problem(n, nnz, seed)
-            a = [0] * (1 << n)
-            for i, v in zip(idx, vals):
-                a[i] = v
-            for tables in ([a, dense], [dense, f, a], [f]):
+        from zkes_b200._lib import ZK_OPT_REPLICATE_LOG
+        # 0: every local round sharded; 8: sharded rounds, then the tables are gathered with a challenge still
+        # to bind; 18 (the default): gathered at once at these sizes
+        for replicate_log in (0, 8, 18):
+            ctx.set_option(ZK_OPT_REPLICATE_LOG, replicate_log)
+            for n, nnz, seed in [(3, 2, 1), (6, 9, 2), (11, 100, 3), (13, 3000, 4)]:
+                if n < zd.log2_exact(world):
+                    continue
+                idx, vals, dense, f = problem(n, nnz, seed)
+                a = [0] * (1 << n)
+                for i, v in zip(idx, vals):
+                    a[i] = v
+                for tables in ([a, dense], [dense, f, a], [f]):
+                    t = Transcript(b"sharded")
+                    t.append_u64(b"num_var", n)
+                    t.append_u64(b"num_poly", len(tables))
+                    local = [DenseMLPoly.from_evaluations(zd.shard_dense(tb, rank, world)) for tb in tables]
+                    msgs, chals, fin_t, fin = zd.sharded_linear_prove(ctx, comm, n, local, t)
+                    ot = o.Transcript(b"sharded")
+                    op = o.LinearSumcheckProver(n, len(tables), ot)
+                    opr = op.prove(tables, ot)
+                    assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
+                    assert fin_t == [x[0] for x in op.a_arrays]
+                    assert t.challenge_scalar(b"after") == ot.challenge_scalar(b"after")
                 t = Transcript(b"sharded")
                 t.append_u64(b"num_var", n)
-                t.append_u64(b"num_poly", len(tables))
-                local = [DenseMLPoly.from_evaluations(zd.shard_dense(tb, rank, world)) for tb in tables]
-                msgs, chals, fin_t, fin = zd.sharded_linear_prove(ctx, comm, n, local, t)
+                t.append_u64(b"num_poly", 2)
+                li, lv = zd.shard_sparse(idx, vals, rank, world, n)
+                ld = DenseMLPoly.from_evaluations(zd.shard_dense(dense, rank, world))
+                msgs, chals, fin_t, fin = zd.sharded_sparse_dense_prove(ctx, comm, n, li, lv, ld, t)
                 ot = o.Transcript(b"sharded")
-                op = o.LinearSumcheckProver(n, len(tables), ot)
-                opr = op.prove(tables, ot)
+                op, opr = o.sparse_dense_prove(n, idx, vals, dense, ot)
                 assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
-                assert fin_t == [x[0] for x in op.a_arrays]
-                assert t.challenge_scalar(b"after") == ot.challenge_scalar(b"after")
-            t = Transcript(b"sharded")
-            t.append_u64(b"num_var", n)
-            t.append_u64(b"num_poly", 2)
-            li, lv = zd.shard_sparse(idx, vals, rank, world, n)
-            ld = DenseMLPoly.from_evaluations(zd.shard_dense(dense, rank, world))
-            msgs, chals, fin_t, fin = zd.sharded_sparse_dense_prove(ctx, comm, n, li, lv, ld, t)
-            ot = o.Transcript(b"sharded")
-            op, opr = o.sparse_dense_prove(n, idx, vals, dense, ot)
-            assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
         # ---- MSM by point range, KZH commit by x-rows, fix_from_right over the top variables
         from zkes_b200 import curve
         rnd = random.Random(77)
@@ -158,9 +188,16 @@ def main():
             lo, hi = zd.shard_range(rank, world, n)
             assert srs.read(0, 0, hi - lo) == full[lo:hi]
             f = [rnd.randrange(o.R_MOD) if i % 2 else o.fr_from_int(rnd.randrange(-128, 128)) for i in range(1 << n)]
-            c, dx = zd.sharded_kzh_commit(ctx, comm, srs, f[lo:hi])
+            c, dx, dx_jac = zd.sharded_kzh_commit(ctx, comm, srs, f[lo:hi], with_jacobian=True)
             oc, odx = (o.kzh2_commit if dims == 2 else o.kzh3_commit)(osrs, f)
             assert c == oc and dx == odx
+            full_pt = [rnd.randrange(o.R_MOD) for _ in range(n)]
+            if dims == 2:
+                assert zd.sharded_kzh_open(ctx, comm, srs, full_pt, f[lo:hi]) == o.kzh2_open(osrs, full_pt, odx, f)[1]
+            else:
+                dy, cy, fs = zd.sharded_kzh_open(ctx, comm, srs, full_pt, f[lo:hi], dx_jac)
+                _, ody, ocy, ofs = o.kzh3_open(osrs, full_pt, odx, f)
+                assert dy == ody and cy == ocy and fs == ofs
             pt = [rnd.randrange(o.R_MOD) for _ in range(xl)]
             got = zd.sharded_fix_from_right(ctx, comm, n, f[lo:hi], pt)
             assert got == o.fix_variables_from_right(f, pt)

@@ -18,6 +18,6 @@ def test_nccl_sharded_provers(world):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
            "127.0.0.1", "--master-port", str(29600 + world), os.path.join(ROOT, "tests", "sharded_worker.py"), "nccl"]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=420, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert "sharded worker ok" in r.stdout

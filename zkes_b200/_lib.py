@@ -11,6 +11,7 @@ LIB_PATH = os.path.join(HERE, "libzkb200.so")
 
 ZK_MEM_HOST, ZK_MEM_DEVICE = 0, 1
 ZK_OPT_DEVICE_TAIL = 1
+ZK_OPT_REPLICATE_LOG = 2
 ZK_OK, ZK_ERR_ARG, ZK_ERR_OOM, ZK_ERR_CUDA, ZK_ERR_TIMEOUT, ZK_ERR_FS_CALLBACK, ZK_ERR_COMM = 0, -1, -2, -3, -4, -5, -6
 
 FS_ROUND_FN = ctypes.CFUNCTYPE(c_int, c_void_p, POINTER(c_uint64), c_uint32, POINTER(c_uint64))
@@ -51,6 +52,8 @@ SIGNATURES = {
                                  c_void_p, c_void_p]),
     "zk_g1_compress": (c_int, [c_void_p, c_void_p, c_int, c_uint64, c_void_p, c_int]),
     "zk_g1_decompress": (c_int, [c_void_p, c_void_p, c_int, c_uint64, c_void_p, c_int]),
+    "zk_kzh_open_sharded": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_uint32, c_void_p, c_void_p,
+                                    c_void_p, c_void_p]),
     "zk_mle_eval": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_void_p, c_void_p]),
     "zk_permute_by_ranges": (c_int, [c_void_p, c_uint32, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_int]),
     "zk_fix_variables_int": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_int]),

@@ -105,6 +105,10 @@ int zk_set_option(zk_ctx* ctx, int option, int value) {
   CtxLock lk(ctx);
   switch (option) {
     case ZK_OPT_DEVICE_TAIL: ctx->device_tail = value != 0; return ZK_OK;
+    case ZK_OPT_REPLICATE_LOG:
+      if (value < 0 || value > 30) return fail(ZK_ERR_ARG, "zk_set_option: replicate threshold out of range");
+      ctx->replicate_entries = value == 0 ? 0 : 1ull << value;
+      return ZK_OK;
     default: return fail(ZK_ERR_ARG, "zk_set_option: unknown option %d", option);
   }
 }
@@ -212,6 +216,7 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
                   uint64_t* challenges, Fr* challenge, bool* finals_done) {
   const uint64_t size = 1ull << rounds;
   *finals_done = false;
+  if (comm) ctx->sharded_finished = false;
   uint64_t cur_size = size;  // entries of the tables cur[] points at
   const bool tail_ok = ctx->device_tail && !fs && tr && !comm;
   uint32_t resident_rounds = 0;  // rounds the resident kernel has produced (their results are still on the device)
@@ -278,6 +283,52 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
         tr->m.strobe().pos() = (uint8_t)h_st->pos;
         tr->m.strobe().pos_begin() = (uint8_t)h_st->pos_begin;
         tr->m.strobe().cur_flags() = (uint8_t)h_st->cur_flags;
+        *finals_done = true;
+        return ZK_OK;
+      }
+    }
+    if (comm) {
+      // Sharded prove, small tables: a round is then all exchange and no work.  Bind the pending
+      // challenge, gather every rank's chunk (the chunks are the table's top index bits, so rank order
+      // is table order) and let every rank run the rest of the protocol on the whole table, where the
+      // rounds stay on the device.  Every rank computes the same messages, so the transcripts agree.
+      const uint64_t after_fold = round == 0 ? cur_size : cur_size >> 1;
+      const int world = comm_world(comm);
+      if (after_fold * (uint64_t)world <= ctx->replicate_entries && after_fold >= 1) {
+        uint32_t logw = 0;
+        while ((1 << logw) < world) logw++;
+        const uint64_t full = after_fold * world;
+        Fr* rep = nullptr;
+        int rc = ctx->reserve_aux(((size_t)L * (full + full / 2 + full / 4) + 16) * sizeof(Fr), (void**)&rep);
+        if (rc) return rc;
+        const Fr* rcur[kMaxPolys];
+        Fr *rping[kMaxPolys], *rpong[kMaxPolys];
+        for (int i = 0; i < L; i++) {
+          const Fr* chunk = cur[i];
+          if (round > 0) {
+            Fr* dst = ((round & 1) ? ping : pong)[i];
+            launch_fold(cur[i], dst, *challenge, after_fold, ctx->rs.max_blocks, ctx->stream);
+            ctx->launches++;
+            chunk = dst;
+          }
+          Fr* whole = rep + (size_t)i * full;
+          rc = comm_gather_bytes(ctx, comm, chunk, after_fold * sizeof(Fr), whole);
+          if (rc) return rc;
+          rcur[i] = whole;
+          rping[i] = rep + (size_t)L * full + (size_t)i * (full / 2);
+          rpong[i] = rep + (size_t)L * (full + full / 2) + (size_t)i * (full / 4);
+        }
+        uint32_t lg = 0;
+        while ((1ull << lg) < full) lg++;
+        bool done = false;
+        rc = linear_rounds(ctx, nullptr, L, lg, rcur, rping, rpong, round_offset + round, fs, fs_user, tr, round_msgs, challenges,
+                           challenge, &done);
+        if (rc) return rc;
+        if (!done) {
+          launch_final(L, lg > 0, rcur, *challenge, ctx->final_out, ctx->stream);
+          ctx->launches++;
+        }
+        ctx->sharded_finished = true;
         *finals_done = true;
         return ZK_OK;
       }
@@ -392,7 +443,7 @@ int linear_prove_impl(zk_ctx* ctx, zk_comm* comm, uint32_t num_var, uint32_t num
     launch_final(L, n_local > 0, cur, challenge, ctx->final_out, ctx->stream);
     ctx->launches++;
   }
-  if (world > 1) {
+  if (world > 1 && !ctx->sharded_finished) {
     rc = sharded_tail(ctx, comm, L, n_local, fs, fs_user, tr, round_msgs, challenges, &challenge);
     if (rc) return rc;
   }

@@ -95,6 +95,62 @@ void pad_point(const uint64_t* point, uint32_t point_len, uint32_t n, std::vecto
   }
 }
 
+// Everything of kzh3_open after f_prime (kzh3.rs:739-779), shared by the whole-table and the
+// sharded entry points; scratch is kzh3_tail_bytes() of device memory.
+size_t kzh3_tail_bytes(zk_ctx* ctx, const zk_kzh_srs* srs) {
+  const uint64_t nx = 1ull << srs->x_log, ny = 1ull << srs->y_log, nz = 1ull << srs->z_log;
+  return al(nz * sizeof(Fr)) + al((nx + 8) * sizeof(Fr)) * 2 +
+         al(from_right_scratch_elems(ctx, srs->y_log + srs->z_log, srs->y_log) * sizeof(Fr)) + al((nx + 2) * sizeof(Jacobian)) +
+         al((ny + 2) * sizeof(Jacobian)) + al((nx + 1) * sizeof(Affine)) + 2048;
+}
+
+int kzh3_open_tail(zk_ctx* ctx, const zk_kzh_srs* srs, const Fr* f_prime, const std::vector<uint64_t>& pt,
+                   const uint64_t* d_x_jac, char* mem, uint64_t* d_y_jac_out, uint64_t* c_y_affine_out, uint64_t* f_star_out) {
+  cudaStream_t st = ctx->stream;
+  const uint32_t xl = srs->x_log, yl = srs->y_log, zl = srs->z_log;
+  const uint64_t nx = 1ull << xl, ny = 1ull << yl, nz = 1ull << zl;
+  const uint64_t* r_y = pt.data() + (size_t)zl * 4;
+  const uint64_t* r_x = pt.data() + (size_t)(zl + yl) * 4;
+  size_t off = 0;
+  auto take = [&](size_t bytes) { char* p = mem + off; off += al(bytes); return p; };
+  Fr* f_star = (Fr*)take(nz * sizeof(Fr));
+  Fr* eq_x = (Fr*)take((nx + 8) * sizeof(Fr));
+  Fr* pt_dev = (Fr*)take((nx + 8) * sizeof(Fr));
+  Fr* scratch = (Fr*)take(from_right_scratch_elems(ctx, yl + zl, yl) * sizeof(Fr));
+  Jacobian* d_dx = (Jacobian*)take((nx + 2) * sizeof(Jacobian));
+  Jacobian* d_dy = (Jacobian*)take((ny + 2) * sizeof(Jacobian));
+  Affine* d_aff = (Affine*)take((nx + 1) * sizeof(Affine));
+  // d_y[i] = MSM(h_z, f_prime[i * 2^z_log ..])   (kzh3.rs:743-750)
+  ctx->prof_begin(ZK_PROF_MSM, 0.0, 8);
+  int rc = msm_run(ctx, srs->h[2], nullptr, f_prime, nz, (uint32_t)ny, d_dy, nullptr);
+  ctx->prof_end();
+  if (rc) return rc;
+  // f_star = fix_variables_from_right(poly, r_y || r_x) = fix_variables_from_right(f_prime, r_y)   (kzh3.rs:762-764)
+  if (yl == 0) {
+    ZK_CUDA(cudaMemcpyAsync(f_star, f_prime, nz * sizeof(Fr), cudaMemcpyDeviceToDevice, st));
+  } else {
+    rc = fix_from_right_device(ctx, yl + zl, f_prime, yl, r_y, scratch, f_star);
+    if (rc) return rc;
+  }
+  // c_y = MSM(affine(d_x), eq(r_x))   (kzh3.rs:739, 767-779)
+  ZK_CUDA(cudaMemcpyAsync(d_dx, d_x_jac, nx * sizeof(Jacobian), cudaMemcpyHostToDevice, st));
+  rc = normalize_device(ctx, d_dx, nx, d_aff);
+  if (rc) return rc;
+  rc = eq_table_device(ctx, r_x, xl, pt_dev, eq_x);
+  if (rc) return rc;
+  ctx->prof_begin(ZK_PROF_MSM, 0.0, 8);
+  rc = msm_run(ctx, d_aff, nullptr, eq_x, nx, 1, d_dy + ny, &ctx->last_msm);
+  ctx->prof_end();
+  if (rc) return rc;
+  rc = normalize_device(ctx, d_dy + ny, 1, d_aff + nx);
+  if (rc) return rc;
+  ZK_CUDA(cudaMemcpyAsync(d_y_jac_out, d_dy, ny * sizeof(Jacobian), cudaMemcpyDeviceToHost, st));
+  ZK_CUDA(cudaMemcpyAsync(c_y_affine_out, d_aff + nx, sizeof(Affine), cudaMemcpyDeviceToHost, st));
+  ZK_CUDA(cudaMemcpyAsync(f_star_out, f_star, nz * sizeof(Fr), cudaMemcpyDeviceToHost, st));
+  ZK_CUDA(cudaStreamSynchronize(st));
+  return ZK_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -276,31 +332,20 @@ int zk_kzh3_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uint
   if (poly_n > srs->n) return fail(ZK_ERR_ARG, "Cannot extend to fewer variables");
   CtxLock lk(ctx);
   cudaStream_t st = ctx->stream;
-  const uint32_t n = srs->n, xl = srs->x_log, yl = srs->y_log, zl = srs->z_log;
-  const uint64_t size = 1ull << n, nx = 1ull << xl, ny = 1ull << yl, nz = 1ull << zl, nyz = ny * nz;
+  const uint32_t n = srs->n, xl = srs->x_log;
+  const uint64_t size = 1ull << n, nyz = 1ull << (srs->y_log + srs->z_log);
   std::vector<uint64_t> pt;
   pad_point(point, point_len, n, pt);
-  const uint64_t* r_y = pt.data() + (size_t)zl * 4;
-  const uint64_t* r_x = pt.data() + (size_t)(zl + yl) * 4;
-  size_t fr_scr = from_right_scratch_elems(ctx, n, xl);
-  const size_t fr_scr2 = from_right_scratch_elems(ctx, yl + zl, yl);
-  if (fr_scr2 > fr_scr) fr_scr = fr_scr2;
+  const uint64_t* r_x = pt.data() + (size_t)(srs->z_log + srs->y_log) * 4;
+  const size_t fr_scr = from_right_scratch_elems(ctx, n, xl);
   char* base = nullptr;
-  size_t need = al(size * sizeof(Fr)) + al(nyz * sizeof(Fr)) + al(nz * sizeof(Fr)) + al((nx + 8) * sizeof(Fr)) * 2 +
-                al(fr_scr * sizeof(Fr)) + al((nx + ny + 2) * sizeof(Jacobian)) + al((nx + 1) * sizeof(Affine)) + 2048;
-  int rc = ctx->reserve_work(need, (void**)&base);
+  int rc = ctx->reserve_work(al(size * sizeof(Fr)) + al(nyz * sizeof(Fr)) + al(fr_scr * sizeof(Fr)) + kzh3_tail_bytes(ctx, srs),
+                             (void**)&base);
   if (rc) return rc;
-  size_t off = 0;
-  auto take = [&](size_t bytes) { char* p = base + off; off += al(bytes); return p; };
-  Fr* staging = (Fr*)take(size * sizeof(Fr));
-  Fr* f_prime = (Fr*)take(nyz * sizeof(Fr));
-  Fr* f_star = (Fr*)take(nz * sizeof(Fr));
-  Fr* eq_x = (Fr*)take((nx + 8) * sizeof(Fr));
-  Fr* pt_dev = (Fr*)take((nx + 8) * sizeof(Fr));
-  Fr* scratch = (Fr*)take(fr_scr * sizeof(Fr));
-  Jacobian* d_dx = (Jacobian*)take(nx * sizeof(Jacobian));
-  Jacobian* d_dy = (Jacobian*)take((ny + 2) * sizeof(Jacobian));
-  Affine* d_aff = (Affine*)take((nx + 1) * sizeof(Affine));
+  Fr* staging = (Fr*)base;
+  Fr* f_prime = (Fr*)(base + al(size * sizeof(Fr)));
+  Fr* scratch = (Fr*)(base + al(size * sizeof(Fr)) + al(nyz * sizeof(Fr)));
+  char* tail_mem = base + al(size * sizeof(Fr)) + al(nyz * sizeof(Fr)) + al(fr_scr * sizeof(Fr));
   const Fr* f = nullptr;
   rc = stage_poly(ctx, n, poly_n, evals, evals_mem, staging, &f);
   if (rc) return rc;
@@ -311,35 +356,59 @@ int zk_kzh3_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uint
     rc = fix_from_right_device(ctx, n, f, xl, r_x, scratch, f_prime);
     if (rc) return rc;
   }
-  // d_y[i] = MSM(h_z, f_prime[i * 2^z_log ..])   (kzh3.rs:743-750)
-  ctx->prof_begin(ZK_PROF_MSM, 0.0, 8);
-  rc = msm_run(ctx, srs->h[2], nullptr, f_prime, nz, (uint32_t)ny, d_dy, nullptr);
-  ctx->prof_end();
+  return kzh3_open_tail(ctx, srs, f_prime, pt, d_x_jac, tail_mem, d_y_jac_out, c_y_affine_out, f_star_out);
+}
+
+// kzh2_open / kzh3_open over a table sharded by x-rows (the layout of zk_kzh_commit_sharded): every
+// rank contracts its slab with its slice of eq(r_x), the partial tables are summed over the ranks,
+// and the small remainder of the opening (d_y, f_star, c_y) is computed on every rank alike.
+int zk_kzh_open_sharded(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs* srs, const uint64_t* local_evals, zk_mem evals_mem,
+                        const uint64_t* point, uint32_t point_len, const uint64_t* d_x_jac, uint64_t* d_y_jac_out,
+                        uint64_t* c_y_affine_out, uint64_t* f_star_out) {
+  if (!ctx || !comm || !srs || !local_evals || !f_star_out || (point_len && !point))
+    return fail(ZK_ERR_ARG, "kzh_open_sharded: NULL argument");
+  const bool k3 = srs->dims == 3;
+  if (k3 && (!d_x_jac || !d_y_jac_out || !c_y_affine_out)) return fail(ZK_ERR_ARG, "kzh_open_sharded: a KZH3 opening needs d_x, d_y and c_y");
+  const int world = comm_world(comm), rank = comm_rank(comm);
+  if (world != srs->world || rank != srs->rank) return fail(ZK_ERR_ARG, "kzh_open_sharded: the SRS was set up for rank %d of %d", srs->rank, srs->world);
+  CtxLock lk(ctx);
+  cudaStream_t st = ctx->stream;
+  const uint32_t n = srs->n, xl = srs->x_log;
+  const uint64_t lo_n = 1ull << (n - xl), hi_n = 1ull << xl, hi_local = hi_n / world, slab = hi_local * lo_n;
+  std::vector<uint64_t> pt;
+  pad_point(point, point_len, n, pt);
+  const uint64_t* r_x = pt.data() + (size_t)(n - xl) * 4;
+  const uint32_t splits = from_right_splits(lo_n, hi_local, ctx->sm_count);
+  char* base = nullptr;
+  size_t need = al((xl + 8) * sizeof(Fr)) + al(hi_n * sizeof(Fr)) + al((size_t)splits * lo_n * sizeof(Fr)) + al(lo_n * sizeof(Fr)) +
+                (evals_mem == ZK_MEM_HOST ? al(slab * sizeof(Fr)) : 0) + (k3 ? kzh3_tail_bytes(ctx, srs) : 0) + 1024;
+  int rc = ctx->reserve_work(need, (void**)&base);
   if (rc) return rc;
-  // f_star = fix_variables_from_right(poly, r_y || r_x) = fix_variables_from_right(f_prime, r_y)   (kzh3.rs:762-764)
-  if (yl == 0) {
-    ZK_CUDA(cudaMemcpyAsync(f_star, f_prime, nz * sizeof(Fr), cudaMemcpyDeviceToDevice, st));
-  } else {
-    rc = fix_from_right_device(ctx, yl + zl, f_prime, yl, r_y, scratch, f_star);
-    if (rc) return rc;
+  size_t off = 0;
+  auto take = [&](size_t bytes) { char* p = base + off; off += al(bytes); return p; };
+  Fr* pt_dev = (Fr*)take((xl + 8) * sizeof(Fr));
+  Fr* eq = (Fr*)take(hi_n * sizeof(Fr));
+  Fr* partial = (Fr*)take((size_t)splits * lo_n * sizeof(Fr));
+  Fr* f_prime = (Fr*)take(lo_n * sizeof(Fr));
+  const Fr* f = reinterpret_cast<const Fr*>(local_evals);
+  if (evals_mem == ZK_MEM_HOST) {
+    Fr* p = (Fr*)take(slab * sizeof(Fr));
+    ZK_CUDA(cudaMemcpyAsync(p, local_evals, slab * sizeof(Fr), cudaMemcpyHostToDevice, st));
+    f = p;
   }
-  // c_y = MSM(affine(d_x), eq(r_x))   (kzh3.rs:739, 767-779)
-  ZK_CUDA(cudaMemcpyAsync(d_dx, d_x_jac, nx * sizeof(Jacobian), cudaMemcpyHostToDevice, st));
-  rc = normalize_device(ctx, d_dx, nx, d_aff);
+  char* tail_mem = k3 ? take(kzh3_tail_bytes(ctx, srs)) : nullptr;
+  rc = eq_table_device(ctx, r_x, xl, pt_dev, eq);
   if (rc) return rc;
-  rc = eq_table_device(ctx, r_x, xl, pt_dev, eq_x);
+  ctx->launches += launch_from_right(f, eq + hi_local * rank, lo_n, hi_local, partial, f_prime, ctx->sm_count, st);
+  rc = comm_sum_fr_vec(ctx, comm, f_prime, lo_n);
   if (rc) return rc;
-  ctx->prof_begin(ZK_PROF_MSM, 0.0, 8);
-  rc = msm_run(ctx, d_aff, nullptr, eq_x, nx, 1, d_dy + ny, &ctx->last_msm);
-  ctx->prof_end();
-  if (rc) return rc;
-  rc = normalize_device(ctx, d_dy + ny, 1, d_aff + nx);
-  if (rc) return rc;
-  ZK_CUDA(cudaMemcpyAsync(d_y_jac_out, d_dy, ny * sizeof(Jacobian), cudaMemcpyDeviceToHost, st));
-  ZK_CUDA(cudaMemcpyAsync(c_y_affine_out, d_aff + nx, sizeof(Affine), cudaMemcpyDeviceToHost, st));
-  ZK_CUDA(cudaMemcpyAsync(f_star_out, f_star, nz * sizeof(Fr), cudaMemcpyDeviceToHost, st));
-  ZK_CUDA(cudaStreamSynchronize(st));
-  return ZK_OK;
+  ZK_CUDA(cudaGetLastError());
+  if (!k3) {  // f_star = fix_variables_from_right(poly, r_x)   (kzh2.rs:700-704)
+    ZK_CUDA(cudaMemcpyAsync(f_star_out, f_prime, lo_n * sizeof(Fr), cudaMemcpyDeviceToHost, st));
+    ZK_CUDA(cudaStreamSynchronize(st));
+    return ZK_OK;
+  }
+  return kzh3_open_tail(ctx, srs, f_prime, pt, d_x_jac, tail_mem, d_y_jac_out, c_y_affine_out, f_star_out);
 }
 
 // The G1 and field checks of kzh2_verify (kzh2.rs:763-789: steps 2 and 3) and kzh3_verify

@@ -42,9 +42,23 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
   CtxLock lk(ctx);
   cudaStream_t s = ctx->stream;
   const uint32_t K = (uint32_t)nnz;
+  // Sharded: every rank must leave the entry form at the same round (the dense rounds exchange
+  // differently, and may gather the tables), so the rule below uses the largest entry count of any rank.
+  uint32_t K_rule = K;
+  if (comm) {
+    uint32_t* d_k = reinterpret_cast<uint32_t*>(ctx->tail_buf);
+    ZK_CUDA(cudaMemcpyAsync(d_k, &K, 4, cudaMemcpyHostToDevice, s));
+    int grc = comm_gather_bytes(ctx, comm, d_k, 4, d_k + 64);
+    if (grc) return grc;
+    ZK_CUDA(cudaMemcpyAsync(ctx->host_small, d_k + 64, 4 * (size_t)world, cudaMemcpyDeviceToHost, s));
+    ZK_CUDA(cudaStreamSynchronize(s));
+    const uint32_t* all = reinterpret_cast<const uint32_t*>(ctx->host_small);
+    for (int r = 0; r < world; r++)
+      if (all[r] > K_rule) K_rule = all[r];
+  }
   // The dense phase starts at the first round whose table size is <= 2 * (entry bound).
   uint64_t dense_cap = 2;
-  while (dense_cap < 2 * (uint64_t)K && dense_cap < size) dense_cap <<= 1;
+  while (dense_cap < 2 * (uint64_t)K_rule && dense_cap < size) dense_cap <<= 1;
 
   size_t need = 4096;
   const bool host_in = mem == ZK_MEM_HOST;
@@ -101,7 +115,7 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
   uint64_t S = size;
   bool finished = false;  // the dense phase ran to the end (final values are in ctx->final_out)
   for (uint32_t round = 0; round < num_var; round++, S >>= 1) {
-    if (K && S <= dense_cap) {
+    if (K_rule && S <= dense_cap) {
       // hand over to the dense prover: scatter the entries into a table and run the remaining rounds
       if (pending) {  // not reached with the pairing rule below; kept so the hand-over never sees a stale table
         Fr* nb = other_buf(b_cur);
@@ -136,7 +150,7 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
     // Fold of the dense table.  When the next round is still in entry form its message can fold
     // the few values it needs on the fly, so this fold waits and is done together with the next
     // one in a single pass over the table (k_fold2).
-    const bool next_sparse = round + 1 < num_var && (!K || (S / 2) > dense_cap);
+    const bool next_sparse = round + 1 < num_var && (!K_rule || (S / 2) > dense_cap);
     // The table fold (bandwidth-bound, long) and the entry fold (three short launches) touch disjoint
     // buffers: the table fold goes to the side stream and the two run side by side.  With the
     // per-kernel profiler on they stay in line so that each span times one kernel alone.
@@ -179,7 +193,7 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
     launch_sd_final(e_idx[e], e_val[e], counts + e, b_cur, ctx->final_out, s);
     ctx->launches++;
   }
-  if (comm) {  // the remaining log2(world) variables: every rank finishes on the gathered values
+  if (comm && !(finished && ctx->sharded_finished)) {  // the remaining log2(world) variables: every rank finishes on the gathered values
     rc = sharded_tail(ctx, comm, 2, num_var, fs, fs_user, tr, round_msgs, challenges, &challenge);
     if (rc) return rc;
   }

@@ -63,6 +63,7 @@ void launch_general_final(const Fr* const* tables_dev, const Fr* scalars, const 
 
 // tail.cu
 struct StrobeState;
+constexpr uint64_t kReplicateEntries = 1ull << 18;  // sharded proves: gather the tables once all ranks together hold this few entries
 constexpr uint32_t kTailMax = 1024;  // entries per table the single-block tail kernel takes over at
 // r_dev / st_dev (device pointers, both or neither): take the challenge to bind first and the transcript
 // state from device memory (left there by the resident kernel) instead of from r / st.

@@ -153,12 +153,32 @@ def sharded_kzh_setup(ctx, comm: Comm, dims: int, n: int, g, tau_x, tau_y, tau_z
     return KZHSRS(ctx, dims, n, h)
 
 
-def sharded_kzh_commit(ctx, comm: Comm, srs, local_evals):
-    """-> (c affine, d_x affine list), identical on every rank."""
+def sharded_kzh_commit(ctx, comm: Comm, srs, local_evals, with_jacobian: bool = False):
+    """-> (c affine, d_x affine list), identical on every rank; with_jacobian adds the raw d_x array
+    that sharded_kzh_open takes."""
     from . import curve
     ev = to_mont_array(local_evals)
     c = np.zeros((1, 8), dtype=np.uint64)
     dx = np.zeros((1 << srs.x_log, 12), dtype=np.uint64)
     check(lib.zk_kzh_commit_sharded(ctx.handle, comm.handle, srs.handle, _p(ev), ZK_MEM_HOST, _p(c), _p(dx)),
           "zk_kzh_commit_sharded")
-    return curve.affine_from_array(c)[0], curve.jacobian_to_affine_py(dx)
+    res = (curve.affine_from_array(c)[0], curve.jacobian_to_affine_py(dx))
+    return res + (dx,) if with_jacobian else res
+
+
+def sharded_kzh_open(ctx, comm: Comm, srs, point, local_evals, d_x_jac=None):
+    """kzh2_open / kzh3_open over x-row shards -> f_star (KZH2) or (d_y, c_y, f_star) (KZH3), on every rank."""
+    from . import curve
+    ev = to_mont_array(local_evals)
+    pt = to_mont_array(point) if len(point) else np.zeros((1, 4), dtype=np.uint64)
+    if srs.dims == 2:
+        fs = np.zeros((1 << srs.y_log, 4), dtype=np.uint64)
+        check(lib.zk_kzh_open_sharded(ctx.handle, comm.handle, srs.handle, _p(ev), ZK_MEM_HOST, _p(pt), len(point), None, None,
+                                      None, _p(fs)), "zk_kzh_open_sharded")
+        return from_mont_array(fs)
+    dy = np.zeros((1 << srs.y_log, 12), dtype=np.uint64)
+    cy = np.zeros((1, 8), dtype=np.uint64)
+    fs = np.zeros((1 << srs.z_log, 4), dtype=np.uint64)
+    check(lib.zk_kzh_open_sharded(ctx.handle, comm.handle, srs.handle, _p(ev), ZK_MEM_HOST, _p(pt), len(point), _p(d_x_jac),
+                                  _p(dy), _p(cy), _p(fs)), "zk_kzh_open_sharded")
+    return curve.jacobian_to_affine_py(dy), curve.affine_from_array(cy)[0], from_mont_array(fs)
