@@ -47,14 +47,22 @@ __global__ void __launch_bounds__(kSpThreads) k_sparse_msg(const uint32_t* __res
     for (int k = 0; k < 16; k++) acc[c].v[k] = 0;
   int pending = 0;
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    // everything that depends on i alone is loaded at once (the partner's value speculatively), so that
+    // only the gather of the dense pair waits for an earlier load
     const uint32_t pos = idx[i];
-    if (!is_leader(idx, i, pos)) continue;
+    const uint32_t prev = i ? idx[i - 1] : 0u;
+    const bool has_next = i + 1 < n;
+    const uint32_t next = has_next ? idx[i + 1] : 0u;
+    const Fr va = ld_fr(val + i);
+    const Fr vb = has_next ? ld_fr(val + i + 1) : Fr::zero();
+    const bool even = (pos & 1u) == 0;
+    if (!(even || i == 0 || prev != pos - 1)) continue;  // the odd partner of the entry before it
     Fr v0 = Fr::zero(), v1 = Fr::zero();
-    if ((pos & 1u) == 0) {
-      v0 = ld_fr(val + i);
-      if (i + 1 < n && idx[i + 1] == pos + 1) v1 = ld_fr(val + i + 1);
+    if (even) {
+      v0 = va;
+      if (has_next && next == pos + 1) v1 = vb;
     } else {
-      v1 = ld_fr(val + i);
+      v1 = va;
     }
     Fr b0, b1;
     if (DEFERRED) {
