@@ -47,6 +47,8 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--device-tail", type=int, default=None, help="override the library's ZK_OPT_DEVICE_TAIL default (0/1)")
     ap.add_argument("--no-msm", action="store_true", help="skip the KZH2 commit (MSM points/s) leg")
+    ap.add_argument("--msm-only", action="store_true", help="run the KZH2 commit leg alone and print its JSON (profiling captures)")
+    ap.add_argument("--msm-log", type=int, default=24, help="log2 of the committed table (smaller sizes are for profiling captures only)")
     return ap.parse_args()
 
 
@@ -325,7 +327,7 @@ def gpu_arm(args):
     return ctx, rank, world, ms_per_step, value, launches, prof, e2e, clocks
 
 
-def msm_leg(ctx):
+def msm_leg(ctx, n=24, steps=5):
     """Second half of the metric: KZH2 commit of 2^24 int8 evaluations on a 2^12 x 2^12 split
     (BASELINE.json config 3), points/s = 2 * 2^24 / t, with the integer-pipe fraction."""
     import numpy as np
@@ -336,7 +338,7 @@ def msm_leg(ctx):
     from zkes_b200._lib import check, lib
     from zkes_b200.field import from_mont_array
 
-    n = 24
+    x_log, y_log = n // 2, n - n // 2
 
     def uniform(stream, count):
         t = torch.empty((count, 4), dtype=torch.int64, device="cuda")
@@ -344,7 +346,7 @@ def msm_leg(ctx):
         check(lib.zk_gen_uniform_fr(ctx.handle, 2, stream, 0, count, t.data_ptr()), "zk_gen_uniform_fr")
         return from_mont_array(t.cpu().numpy().view(np.uint64))
 
-    tau_x, tau_y, alpha = uniform(1, 1 << 12), uniform(2, 1 << 12), uniform(3, 1)[0]
+    tau_x, tau_y, alpha = uniform(1, 1 << x_log), uniform(2, 1 << y_log), uniform(3, 1)[0]
     # g = 2 * (1, 2) on y^2 = x^3 + 3, in affine form
     g = (1368015179489954701390400359078579693043519447331113978918064868415326638035,
          9918110051302171585080402603319702774565515993150576347155970296011118125764)
@@ -358,7 +360,6 @@ def msm_leg(ctx):
     stream = torch.cuda.ExternalStream(lib.zk_stream(ctx.handle))
     kzh.commit(ctx, srs, poly)  # warm-up (allocates scratch)
     kzh.commit(ctx, srs, poly)
-    steps = 5
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(steps):
@@ -374,7 +375,7 @@ def msm_leg(ctx):
     mac32 = pairs * (255.0 / 256.0) * 1360.0  # one mixed addition (10 products of 136) per non-zero digit
     srs.close()
     return {"metric": "kzh2_commit_msm_points_per_s", "value": pairs / (ms * 1e-3), "unit": "points/s", "ms_per_commit": ms,
-            "config": "KZH2 commit, 2^24 int8 evaluations, 2^12 x 2^12 split, seed 2 (C over 2^24 points + 2^12 rows of 2^12)",
+            "config": f"KZH2 commit, 2^{n} int8 evaluations, 2^{x_log} x 2^{y_log} split, seed 2 (C over 2^{n} points + 2^{x_log} rows of 2^{y_log})",
             "srs_setup_s": setup_s, "window_bits_last_msm": stats["window_bits"],
             "integer_roofline": {"bound": "imad", "achieved_mac32_per_s": mac32 / (ms * 1e-3), "peak_mac32_per_s": imad_peak,
                                  "frac": mac32 / (ms * 1e-3) / imad_peak,
@@ -399,6 +400,12 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         reference_arm(args)
+        return
+    if args.msm_only:
+        from zkes_b200 import Context
+
+        ctx = Context(0)
+        print(json.dumps(msm_leg(ctx, args.msm_log, max(1, args.steps))))
         return
     ctx, rank, world, ms_per_step, value, launches, prof, e2e, clocks = gpu_arm(args)
     if rank != 0:

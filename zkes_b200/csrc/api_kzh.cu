@@ -273,15 +273,16 @@ int zk_kzh_commit(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uin
   rc = stage_poly(ctx, n, poly_n, evals, evals_mem, staging, &f);
   if (rc) return rc;
   // C = sum_i f[i] h_full[i]   (kzh2.rs:636-647, kzh3.rs:662-673)
+  MsmPrep prep;  // both MSMs run over the same scalars: one analysis pass serves the two
   ctx->prof_begin(ZK_PROF_MSM, 0.0, 8);
-  rc = msm_run(ctx, srs->h[0], nullptr, f, size, 1, d_jac + rows, &ctx->last_msm);
+  rc = msm_run(ctx, srs->h[0], nullptr, f, size, 1, d_jac + rows, &ctx->last_msm, &prep);
   ctx->prof_end();
   if (rc) return rc;
   rc = normalize_device(ctx, d_jac + rows, 1, d_c);
   if (rc) return rc;
   // d_x[i] = sum_j f[i * 2^(n - x_log) + j] h_mid[j]   (kzh2.rs:653-660, kzh3.rs:680-687)
   ctx->prof_begin(ZK_PROF_MSM, 0.0, 8);
-  rc = msm_run(ctx, srs->h[1], nullptr, f, srs->count[1], (uint32_t)rows, d_jac, nullptr);
+  rc = msm_run(ctx, srs->h[1], nullptr, f, srs->count[1], (uint32_t)rows, d_jac, nullptr, &prep);
   ctx->prof_end();
   if (rc) return rc;
   ZK_CUDA(cudaMemcpyAsync(c_affine_out, d_c, sizeof(Affine), cudaMemcpyDeviceToHost, st));

@@ -80,7 +80,8 @@ int zk_kzh_commit_sharded(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs* srs, con
     f = staging;
   }
   // partial C over this rank's slab of h_full, then the group sum over ranks
-  rc = msm_run(ctx, srs->h[0], nullptr, f, slab, 1, d_jac + rows, &ctx->last_msm);
+  MsmPrep prep;  // one analysis pass over the scalars serves both MSMs
+  rc = msm_run(ctx, srs->h[0], nullptr, f, slab, 1, d_jac + rows, &ctx->last_msm, &prep);
   if (rc) return rc;
   rc = comm_sum_points_n(ctx, comm, d_jac + rows, 1);
   if (rc) return rc;
@@ -88,7 +89,7 @@ int zk_kzh_commit_sharded(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs* srs, con
   if (rc) return rc;
   // this rank's rows of d_x, written at their place in the full vector, then all-gathered in place
   Jacobian* mine = d_jac + rows_local * srs->rank;
-  rc = msm_run(ctx, srs->h[1], nullptr, f, srs->count[1], (uint32_t)rows_local, mine, nullptr);
+  rc = msm_run(ctx, srs->h[1], nullptr, f, srs->count[1], (uint32_t)rows_local, mine, nullptr, &prep);
   if (rc) return rc;
   void* tmp = nullptr;
   rc = ctx->reserve_aux(rows * sizeof(Jacobian) + 256, &tmp);

@@ -47,6 +47,7 @@ void zk_ctx::teardown() {
   cudaFree(resident_sh);
   cudaFree(work);
   cudaFree(aux);
+  cudaFree(cmp);
   if (host_small) cudaFreeHost(host_small);
   for (auto& sp : prof_spans) {
     cudaEventDestroy(sp.e0);
@@ -79,6 +80,13 @@ int zk_ctx::reserve_aux(size_t bytes, void** out) {
   int rc = grow(stream, &aux, &aux_bytes, bytes);
   if (rc) return rc;
   *out = aux;
+  return 0;
+}
+
+int zk_ctx::reserve_cmp(size_t bytes, void** out) {
+  int rc = grow(stream, &cmp, &cmp_bytes, bytes);
+  if (rc) return rc;
+  *out = cmp;
   return 0;
 }
 

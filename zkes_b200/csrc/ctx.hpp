@@ -69,6 +69,8 @@ struct zk_ctx {
   size_t work_bytes = 0;
   void* aux = nullptr;           // second grow-only scratch (MSM sort and bucket storage)
   size_t aux_bytes = 0;
+  void* cmp = nullptr;           // third grow-only scratch (compact small scalars of the MSM)
+  size_t cmp_bytes = 0;
   uint64_t replicate_entries = zk::kReplicateEntries;  // sharded proves gather the tables at this many entries in all (0: never)
   bool sharded_finished = false; // set by the dense round loop of a sharded prove when it gathered the tables and ran to the end
   bool device_tail = true;       // run the last dense rounds in the single-block kernel (zk_set_option turns it off)
@@ -102,6 +104,7 @@ struct zk_ctx {
   }
   int reserve_work(size_t bytes, void** out);
   int reserve_aux(size_t bytes, void** out);
+  int reserve_cmp(size_t bytes, void** out);
 };
 
 struct zk_transcript {

@@ -81,6 +81,14 @@ ZK_HD Xyzz dbl(const Xyzz& p) {
   return r;
 }
 
+// The doubling that an addition falls into when both operands are the same point: rare, so on the
+// device it is a call rather than a second copy of the formulas inside every addition (the kernels'
+// code has to stay within the instruction cache).
+#ifdef __CUDACC__
+static __device__ __noinline__ void dbl_rare(Xyzz* r, const Xyzz* p) { *r = dbl(*p); }
+static __device__ __noinline__ void dbl_affine_rare(Xyzz* r, const Affine* a) { *r = dbl_affine(*a); }
+#endif
+
 // p + (affine q), madd-2008-s with the exceptional cases handled.
 ZK_HD Xyzz add_mixed(const Xyzz& p, const Affine& q) {
   if (q.is_inf()) return p;
@@ -88,8 +96,14 @@ ZK_HD Xyzz add_mixed(const Xyzz& p, const Affine& q) {
   const Fq u2 = mul(q.x, p.zz), s2 = mul(q.y, p.zzz);
   const Fq pp_ = sub(u2, p.x), r_ = sub(s2, p.y);
   if (pp_.is_zero()) {
-    if (r_.is_zero()) return dbl_affine(q);
-    return Xyzz::inf();
+    if (!r_.is_zero()) return Xyzz::inf();
+#ifdef __CUDA_ARCH__
+    Xyzz d;
+    dbl_affine_rare(&d, &q);
+    return d;
+#else
+    return dbl_affine(q);
+#endif
   }
   Xyzz r;
   const Fq pp = sqr(pp_), ppp = mul(pp_, pp), q_ = mul(p.x, pp);
@@ -108,8 +122,14 @@ ZK_HD Xyzz add(const Xyzz& p, const Xyzz& q) {
   const Fq s1 = mul(p.y, q.zzz), s2 = mul(q.y, p.zzz);
   const Fq pp_ = sub(u2, u1), r_ = sub(s2, s1);
   if (pp_.is_zero()) {
-    if (r_.is_zero()) return dbl(p);
-    return Xyzz::inf();
+    if (!r_.is_zero()) return Xyzz::inf();
+#ifdef __CUDA_ARCH__
+    Xyzz d;
+    dbl_rare(&d, &p);
+    return d;
+#else
+    return dbl(p);
+#endif
   }
   Xyzz r;
   const Fq pp = sqr(pp_), ppp = mul(pp_, pp), q_ = mul(u1, pp);
@@ -151,14 +171,25 @@ ZK_HD Affine to_affine(const Xyzz& p) {
   return a;
 }
 
+// One copy of the full addition / doubling per translation unit, for kernels that add in many
+// places (tree reductions, running sums): operands go through memory, which costs a few per cent
+// of an addition and keeps those kernels a fraction of their inlined size.
+#ifdef __CUDA_ARCH__
+static __device__ __noinline__ void add_to(Xyzz* acc, const Xyzz* q) { *acc = add(*acc, *q); }
+static __device__ __noinline__ void dbl_in_place(Xyzz* acc) { *acc = dbl(*acc); }
+#else
+inline void add_to(Xyzz* acc, const Xyzz* q) { *acc = add(*acc, *q); }
+inline void dbl_in_place(Xyzz* acc) { *acc = dbl(*acc); }
+#endif
+
 // k * p for a small unsigned k (double and add, MSB first).
 ZK_HD Xyzz mul_small(const Xyzz& p, uint32_t k) {
   Xyzz acc = Xyzz::inf();
   int top = 31;
   while (top >= 0 && !((k >> top) & 1u)) top--;  // skip the leading zero bits
   for (int bit = top; bit >= 0; bit--) {
-    acc = dbl(acc);
-    if ((k >> bit) & 1u) acc = add(acc, p);
+    dbl_in_place(&acc);
+    if ((k >> bit) & 1u) add_to(&acc, &p);
   }
   return acc;
 }
