@@ -46,18 +46,22 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--device-tail", type=int, default=None, help="override the library's ZK_OPT_DEVICE_TAIL default (0/1)")
+    ap.add_argument("--peer-exchange", type=int, default=None, help="override ZK_OPT_PEER_EXCHANGE (0: NCCL all-gather per round)")
+    ap.add_argument("--trace", action="store_true", help="print rank 0's per-round host times of one prove to stderr")
     ap.add_argument("--no-msm", action="store_true", help="skip the KZH2 commit (MSM points/s) leg")
     ap.add_argument("--msm-only", action="store_true", help="run the KZH2 commit leg alone and print its JSON (profiling captures)")
     ap.add_argument("--msm-log", type=int, default=24, help="log2 of the committed table (smaller sizes are for profiling captures only)")
     return ap.parse_args()
 
 
-def workload_config(num_var: int, nnz_log: int, gpus: int):
+def workload_config(num_var: int, nnz_log: int, gpus: int, exchange: str = "nccl"):
     lg = gpus.bit_length() - 1
     return {"workload": f"sparse-dense product sumcheck, BN254 Fr, num_var={num_var}, dense 2^{num_var} uniform, "
                         f"sparse 2^{nnz_log} int8 non-zeros, seed {SEED}" +
                         (f" per GPU (one instance of num_var={num_var + lg} sharded on its top {lg} variables)" if lg else ""),
-            "parallelism": (f"hypercube sharded over {gpus} GPUs, NCCL all-gather of the partial round messages"
+            "parallelism": (f"hypercube sharded over {gpus} GPUs, partial round messages exchanged per round "
+                            + ("by peer stores over NVLink inside one kernel" if exchange == "peer memory"
+                               else "by an NCCL all-gather")
                             if gpus > 1 else "1 GPU"),
             "l2": "inputs (2 GiB dense table) larger than the 126 MB L2"}
 
@@ -217,6 +221,10 @@ def gpu_arm(args):
     if world > 1:
         from zkes_b200.dist import Comm, log2_exact
         comm = Comm(ctx, rank, world)
+        if args.peer_exchange is not None:
+            from zkes_b200._lib import ZK_OPT_PEER_EXCHANGE
+            ctx.set_option(ZK_OPT_PEER_EXCHANGE, args.peer_exchange)
+        args.exchange = "peer memory" if comm.peer_exchange and args.peer_exchange != 0 else "nccl"
     total_var = n + (world.bit_length() - 1)  # weak scaling: every rank owns a 2^n chunk of a 2^total_var table
 
     # ---- inputs, resident in HBM (weak scaling: every rank owns a 2^n chunk of one sharded instance)
@@ -285,6 +293,20 @@ def gpu_arm(args):
 
     for _ in range(args.warmup):
         dev_step()
+    if args.trace:
+        buf = (ctypes.c_double * 4096)()
+        cnt = ctypes.c_uint32()
+        lib.zk_round_times(ctx.handle, buf, 4096, ctypes.byref(cnt))  # clears the warm-up's record
+        barrier()
+        t0 = time.perf_counter()
+        dev_step()
+        t1 = time.perf_counter()
+        lib.zk_round_times(ctx.handle, buf, 4096, ctypes.byref(cnt))
+        if rank == 0:
+            ts = [buf[i] for i in range(cnt.value)]
+            sys.stderr.write("trace: prove %.1f us; host-stepped rounds at (us): %s\n" % (
+                (t1 - t0) * 1e6, " ".join("%.0f" % t for t in ts)))
+            sys.stderr.write("trace: per-round gaps (us): %s\n" % " ".join("%.0f" % (b - a) for a, b in zip(ts, ts[1:])))
     l0 = ctx.launch_count
     total_ms = timed(dev_step, args.steps, 0)
     launches = ctx.launch_count - l0
@@ -440,7 +462,7 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u256 (BN254 Fr, Montgomery, 8x32-bit limbs)", "data": "synthetic",
-        "config": workload_config(args.num_var, args.nnz_log, world),
+        "config": workload_config(args.num_var, args.nnz_log, world, getattr(args, "exchange", "nccl")),
         "gpu_launches": launches, "clocks": clocks, "e2e": e2e, "roofline": roofline, "cpu_baseline": cpu, "msm": msm,
     }
     print(json.dumps(out))

@@ -62,9 +62,19 @@ uint64_t zk_launch_count(const zk_ctx* ctx);
  * 0 keeps every round on the per-round kernels with the transcript on the host.
  * ZK_OPT_REPLICATE_LOG (default 18): a sharded dense round loop gathers the tables onto every rank once all
  * ranks together hold at most 2^value entries per table and finishes there without further exchanges
- * (identical outputs); 0 keeps every local round sharded. */
-typedef enum zk_option { ZK_OPT_DEVICE_TAIL = 1, ZK_OPT_REPLICATE_LOG = 2 } zk_option;
+ * (identical outputs); 0 keeps every local round sharded.
+ * ZK_OPT_PEER_EXCHANGE (default 1): sharded proves exchange the per-round partial sums through peer memory
+ * (one kernel per round that stores into every rank's box over NVLink and waits, bounded, for the others'
+ * shares) when zk_comm_init could map the ranks' boxes; 0 uses the NCCL all-gather (identical outputs).  Set it
+ * to the same value on every rank. */
+typedef enum zk_option { ZK_OPT_DEVICE_TAIL = 1, ZK_OPT_REPLICATE_LOG = 2, ZK_OPT_PEER_EXCHANGE = 3 } zk_option;
 int zk_set_option(zk_ctx* ctx, int option, int value);
+/* Diagnostics: the host clock, in microseconds from the first entry, at which each round that the host steps
+ * (a caller's transcript, the entry-form rounds of the sparse provers, sharded rounds) had its challenge, for
+ * the proves since the last call (at most 4096 entries are kept).  Writes up to cap entries, sets *n to the
+ * number recorded and clears the record.  Rounds that run inside the resident kernels leave no entry.  No
+ * counterpart in the reference. */
+int zk_round_times(zk_ctx* ctx, double* out_us, uint32_t cap, uint32_t* n);
 /* The CUDA stream (cudaStream_t) every kernel of this context is launched on, so a host can
  * bracket calls with its own events. */
 void* zk_stream(zk_ctx* ctx);
@@ -157,6 +167,10 @@ int zk_sumcheck_general_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, 
 int zk_comm_unique_id(uint8_t out[128]);
 int zk_comm_init(zk_ctx* ctx, int rank, int world, const uint8_t unique_id[128], zk_comm** out);
 void zk_comm_free(zk_ctx* ctx, zk_comm* comm);
+/* 1 when every rank of the communicator mapped every other rank's exchange box (CUDA IPC over NVLink peer
+ * access) at zk_comm_init, so that ZK_OPT_PEER_EXCHANGE applies; 0 when the ranks stay on NCCL.  No counterpart
+ * in the reference (single process). */
+int zk_comm_peer_exchange(const zk_comm* comm);
 /* Sharded provers: the hypercube is cut on its top log2(world) variables, rank p holding entries
  * [p 2^num_var / world, (p+1) 2^num_var / world) of every table (for the sparse table: the
  * entries of that range, with indices relative to its start).  Each local round ends with an

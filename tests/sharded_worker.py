@@ -127,39 +127,44 @@ def main():
         from zkes_b200 import Context, DenseMLPoly, Transcript
         ctx = Context(local_rank)
         comm = zd.Comm(ctx)
-        from zkes_b200._lib import ZK_OPT_REPLICATE_LOG
-        # 0: every local round sharded; 8: sharded rounds, then the tables are gathered with a challenge still
-        # to bind; 18 (the default): gathered at once at these sizes
-        for replicate_log in (0, 8, 18):
-            ctx.set_option(ZK_OPT_REPLICATE_LOG, replicate_log)
-            for n, nnz, seed in [(3, 2, 1), (6, 9, 2), (11, 100, 3), (13, 3000, 4)]:
-                if n < zd.log2_exact(world):
-                    continue
-                idx, vals, dense, f = problem(n, nnz, seed)
-                a = [0] * (1 << n)
-                for i, v in zip(idx, vals):
-                    a[i] = v
-                for tables in ([a, dense], [dense, f, a], [f]):
-                    t = Transcript(b"sharded")
-                    t.append_u64(b"num_var", n)
-                    t.append_u64(b"num_poly", len(tables))
-                    local = [DenseMLPoly.from_evaluations(zd.shard_dense(tb, rank, world)) for tb in tables]
-                    msgs, chals, fin_t, fin = zd.sharded_linear_prove(ctx, comm, n, local, t)
-                    ot = o.Transcript(b"sharded")
-                    op = o.LinearSumcheckProver(n, len(tables), ot)
-                    opr = op.prove(tables, ot)
-                    assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
-                    assert fin_t == [x[0] for x in op.a_arrays]
-                    assert t.challenge_scalar(b"after") == ot.challenge_scalar(b"after")
-                t = Transcript(b"sharded")
-                t.append_u64(b"num_var", n)
-                t.append_u64(b"num_poly", 2)
-                li, lv = zd.shard_sparse(idx, vals, rank, world, n)
-                ld = DenseMLPoly.from_evaluations(zd.shard_dense(dense, rank, world))
-                msgs, chals, fin_t, fin = zd.sharded_sparse_dense_prove(ctx, comm, n, li, lv, ld, t)
-                ot = o.Transcript(b"sharded")
-                op, opr = o.sparse_dense_prove(n, idx, vals, dense, ot)
-                assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
+        from zkes_b200._lib import ZK_OPT_PEER_EXCHANGE, ZK_OPT_REPLICATE_LOG
+        if rank == 0:
+            print("peer exchange mapped:", comm.peer_exchange, flush=True)
+        # the round messages cross the ranks through peer memory (1, when the boxes could be mapped) or NCCL (0)
+        for peer in (1, 0):
+          ctx.set_option(ZK_OPT_PEER_EXCHANGE, peer)
+          # 0: every local round sharded; 8: sharded rounds, then the tables are gathered with a challenge still
+          # to bind; 18 (the default): gathered at once at these sizes
+          for replicate_log in (0, 8, 18):
+              ctx.set_option(ZK_OPT_REPLICATE_LOG, replicate_log)
+              for n, nnz, seed in [(3, 2, 1), (6, 9, 2), (11, 100, 3), (13, 3000, 4)]:
+                  if n < zd.log2_exact(world):
+                      continue
+                  idx, vals, dense, f = problem(n, nnz, seed)
+                  a = [0] * (1 << n)
+                  for i, v in zip(idx, vals):
+                      a[i] = v
+                  for tables in ([a, dense], [dense, f, a], [f]):
+                      t = Transcript(b"sharded")
+                      t.append_u64(b"num_var", n)
+                      t.append_u64(b"num_poly", len(tables))
+                      local = [DenseMLPoly.from_evaluations(zd.shard_dense(tb, rank, world)) for tb in tables]
+                      msgs, chals, fin_t, fin = zd.sharded_linear_prove(ctx, comm, n, local, t)
+                      ot = o.Transcript(b"sharded")
+                      op = o.LinearSumcheckProver(n, len(tables), ot)
+                      opr = op.prove(tables, ot)
+                      assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
+                      assert fin_t == [x[0] for x in op.a_arrays]
+                      assert t.challenge_scalar(b"after") == ot.challenge_scalar(b"after")
+                  t = Transcript(b"sharded")
+                  t.append_u64(b"num_var", n)
+                  t.append_u64(b"num_poly", 2)
+                  li, lv = zd.shard_sparse(idx, vals, rank, world, n)
+                  ld = DenseMLPoly.from_evaluations(zd.shard_dense(dense, rank, world))
+                  msgs, chals, fin_t, fin = zd.sharded_sparse_dense_prove(ctx, comm, n, li, lv, ld, t)
+                  ot = o.Transcript(b"sharded")
+                  op, opr = o.sparse_dense_prove(n, idx, vals, dense, ot)
+                  assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
         # ---- MSM by point range, KZH commit by x-rows, fix_from_right over the top variables
         from zkes_b200 import curve
         rnd = random.Random(77)

@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(HERE, "libzkb200.so")
 ZK_MEM_HOST, ZK_MEM_DEVICE = 0, 1
 ZK_OPT_DEVICE_TAIL = 1
 ZK_OPT_REPLICATE_LOG = 2
+ZK_OPT_PEER_EXCHANGE = 3
 ZK_OK, ZK_ERR_ARG, ZK_ERR_OOM, ZK_ERR_CUDA, ZK_ERR_TIMEOUT, ZK_ERR_FS_CALLBACK, ZK_ERR_COMM = 0, -1, -2, -3, -4, -5, -6
 
 FS_ROUND_FN = ctypes.CFUNCTYPE(c_int, c_void_p, POINTER(c_uint64), c_uint32, POINTER(c_uint64))
@@ -92,6 +93,8 @@ SIGNATURES = {
     "zk_comm_unique_id": (c_int, [c_void_p]),
     "zk_comm_init": (c_int, [c_void_p, c_int, c_int, c_void_p, POINTER(c_void_p)]),
     "zk_comm_free": (None, [c_void_p, c_void_p]),
+    "zk_comm_peer_exchange": (c_int, [c_void_p]),
+    "zk_round_times": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p]),
     "zk_sumcheck_linear_prove_sharded": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, POINTER(c_void_p), c_int,
                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "zk_sumcheck_sparse_dense_prove_sharded": (c_int, [c_void_p, c_void_p, c_uint32, c_uint64, c_void_p, c_void_p,

@@ -53,6 +53,8 @@ int fs_round(zk_ctx* ctx, zk_comm* comm, int n_msgs, uint32_t round, zk_fs_round
       }
     }
   }
+  if (comm && *reinterpret_cast<volatile unsigned int*>(reinterpret_cast<char*>(ctx->mailbox) + 16 * sizeof(Fr) + 4) != 0)
+    return fail(ZK_ERR_TIMEOUT, "round %u: the other ranks' partial sums did not arrive", round);  // the exchange kernel's wait ran out
   const Fr* msg = reinterpret_cast<const Fr*>(ctx->mailbox);
   uint64_t* out_msg = round_msgs + (uint64_t)round * n_msgs * 4;
   for (int c = 0; c < n_msgs; c++) fr_store(out_msg + 4 * c, msg[c]);
@@ -66,6 +68,11 @@ int fs_round(zk_ctx* ctx, zk_comm* comm, int n_msgs, uint32_t round, zk_fs_round
     *challenge = transcript_challenge_scalar(tr->m, (const uint8_t*)"challenge", 9);
   }
   fr_store(challenges + 4 * (uint64_t)round, *challenge);
+  if (ctx->round_times.size() < 4096) {
+    const auto now = std::chrono::steady_clock::now();
+    if (ctx->round_times.empty()) ctx->round_t0 = now;
+    ctx->round_times.push_back(std::chrono::duration<double, std::micro>(now - ctx->round_t0).count());
+  }
   return ZK_OK;
 }
 }  // namespace zk
@@ -105,12 +112,22 @@ int zk_set_option(zk_ctx* ctx, int option, int value) {
   CtxLock lk(ctx);
   switch (option) {
     case ZK_OPT_DEVICE_TAIL: ctx->device_tail = value != 0; return ZK_OK;
+    case ZK_OPT_PEER_EXCHANGE: ctx->peer_exchange = value != 0; return ZK_OK;
     case ZK_OPT_REPLICATE_LOG:
       if (value < 0 || value > 30) return fail(ZK_ERR_ARG, "zk_set_option: replicate threshold out of range");
       ctx->replicate_entries = value == 0 ? 0 : 1ull << value;
       return ZK_OK;
     default: return fail(ZK_ERR_ARG, "zk_set_option: unknown option %d", option);
   }
+}
+
+int zk_round_times(zk_ctx* ctx, double* out_us, uint32_t cap, uint32_t* n) {
+  if (!ctx || !n) return fail(ZK_ERR_ARG, "zk_round_times: NULL argument");
+  CtxLock lk(ctx);
+  *n = (uint32_t)ctx->round_times.size();
+  for (uint32_t i = 0; i < *n && i < cap && out_us; i++) out_us[i] = ctx->round_times[i];
+  ctx->round_times.clear();
+  return ZK_OK;
 }
 
 void* zk_stream(zk_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
@@ -220,17 +237,100 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
   uint64_t cur_size = size;  // entries of the tables cur[] points at
   const bool tail_ok = ctx->device_tail && !fs && tr && !comm;
   uint32_t resident_rounds = 0;  // rounds the resident kernel has produced (their results are still on the device)
+  // Reads back what the device-resident rounds left in ctx->tail_out: `left` messages and challenges
+  // (rounds round_offset + first ...), the transcript state and the resident kernel's error word.
+  auto collect_device_rounds = [&](uint32_t first, uint32_t left, bool resident) -> int {
+    ResidentShared* sh = reinterpret_cast<ResidentShared*>(ctx->resident_sh);
+    const size_t bytes = ((size_t)left * (L + 2)) * sizeof(Fr) + sizeof(StrobeState);
+    unsigned int* h_flags = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(ctx->host_small) + 8192 - 16);
+    ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->tail_out, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    if (resident) ZK_CUDA(cudaMemcpyAsync(h_flags, sh, 16, cudaMemcpyDeviceToHost, ctx->stream));
+    ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (resident && h_flags[2] == 2) return fail(ZK_ERR_TIMEOUT, "resident round kernel: another rank's partial sums did not arrive");
+    if (resident && h_flags[2] != 0) return fail(ZK_ERR_TIMEOUT, "resident round kernel: a wait for a challenge ran out");
+    const Fr* h_msgs = reinterpret_cast<const Fr*>(ctx->host_small);
+    const Fr* h_chal = h_msgs + (size_t)left * (L + 1);
+    const StrobeState* h_st = reinterpret_cast<const StrobeState*>(h_chal + left);
+    for (uint32_t k = 0; k < left; k++) {
+      for (int c = 0; c <= L; c++)
+        fr_store(round_msgs + ((uint64_t)(round_offset + first + k) * (L + 1) + c) * 4, h_msgs[(size_t)k * (L + 1) + c]);
+      fr_store(challenges + 4 * (uint64_t)(round_offset + first + k), h_chal[k]);
+    }
+    *challenge = h_chal[left - 1];
+    memcpy(tr->m.strobe().state(), h_st->lanes, 200);
+    tr->m.strobe().pos() = (uint8_t)h_st->pos;
+    tr->m.strobe().pos_begin() = (uint8_t)h_st->pos_begin;
+    tr->m.strobe().cur_flags() = (uint8_t)h_st->cur_flags;
+    return ZK_OK;
+  };
+  auto strobe_now = [&]() {
+    StrobeState st;
+    memcpy(st.lanes, tr->m.strobe().state(), 200);
+    st.pos = tr->m.strobe().pos();
+    st.pos_begin = tr->m.strobe().pos_begin();
+    st.cur_flags = tr->m.strobe().cur_flags();
+    st.pad = 0;
+    return st;
+  };
+  // Sharded prove with the built-in transcript and peer-mapped exchange boxes: all local rounds in one
+  // cooperative launch per rank.  The block that completes a round's local sums exchanges them with the
+  // other ranks' kernels through the boxes (stores over NVLink, bounded wait) and runs the transcript
+  // step, so no round returns to the host.  The launch stops when the ranks together hold kTailMax
+  // entries per table; the chunks are gathered (rank order is table order) and every rank finishes in
+  // the single-block kernel, which also covers the rounds of the ranks' own variables.
+  PeerExchange px;
+  if (comm && ctx->device_tail && !fs && tr && rounds >= 11 && comm_peer_args(ctx, comm, &px) &&
+      (uint32_t)px.world <= kTailMax / 2) {
+    uint32_t logw = 0;
+    while ((1 << logw) < px.world) logw++;
+    const uint32_t R = rounds - 9 + logw;       // leaves kTailMax / world entries per table, last challenge unbound
+    const uint32_t left = rounds + logw;         // messages until the end of the protocol
+    const size_t bytes = ((size_t)left * (L + 2)) * sizeof(Fr) + sizeof(StrobeState);
+    if (R <= rounds && bytes <= 8192 - 16) {
+      const StrobeState st = strobe_now();
+      Fr* d_msgs = reinterpret_cast<Fr*>(ctx->tail_out);
+      Fr* d_chal = d_msgs + (size_t)left * (L + 1);
+      StrobeState* d_st = reinterpret_cast<StrobeState*>(d_chal + left);
+      ResidentShared* sh = reinterpret_cast<ResidentShared*>(ctx->resident_sh);
+      Fr* rep = nullptr;
+      int rc = ctx->reserve_aux((size_t)L * kTailMax * sizeof(Fr) + 256, (void**)&rep);
+      if (rc) return rc;
+      ctx->prof_begin(ZK_PROF_ROUND, 64.0 * L * (double)(size / 2) + 192.0 * L * (double)(size / 2));
+      const int lrc = launch_resident(L, cur, ping, pong, size, R, st, ctx->rs.sink.partials, ctx->rs.max_blocks,
+                                      ctx->sm_count, sh, d_msgs, d_chal, ctx->stream, &px);
+      ctx->prof_end();
+      if (lrc == 0) {
+        ctx->launches++;
+        comm_peer_advance(comm, R);
+        Fr** last = ((R - 1) & 1) ? ping : pong;
+        const uint64_t m = size >> (R - 1);
+        const Fr* gathered[kMaxPolys];
+        for (int i = 0; i < L; i++) {
+          Fr* whole = rep + (size_t)i * kTailMax;
+          rc = comm_gather_bytes(ctx, comm, last[i], m * sizeof(Fr), whole);
+          if (rc) return rc;
+          gathered[i] = whole;
+        }
+        if (launch_tail(L, gathered, kTailMax, true, *challenge, st, d_msgs + (size_t)R * (L + 1), d_chal + R, ctx->final_out,
+                        d_st, ctx->stream, &sh->challenge, &sh->st))
+          return fail(ZK_ERR_CUDA, "tail kernel launch failed");
+        ctx->launches++;
+        ZK_CUDA(cudaGetLastError());
+        rc = collect_device_rounds(0, left, true);
+        if (rc) return rc;
+        ctx->sharded_finished = true;
+        *finals_done = true;
+        return ZK_OK;
+      }
+      // no cooperative launch on this device: the per-round path below (every rank of one machine takes the same turn)
+    }
+  }
   for (uint32_t round = 0; round < rounds; round++) {
     if (tail_ok && (cur_size <= kTailMax || round == 0)) {
       // Device-resident rounds.  Tables above kTailMax entries go through the cooperative multi-block
       // kernel until kTailMax entries are left, then (or at once, for small tables) one block finishes
       // in shared memory; messages, challenges and the transcript state come back in a single copy.
-      StrobeState st;
-      memcpy(st.lanes, tr->m.strobe().state(), 200);
-      st.pos = tr->m.strobe().pos();
-      st.pos_begin = tr->m.strobe().pos_begin();
-      st.cur_flags = tr->m.strobe().cur_flags();
-      st.pad = 0;
+      const StrobeState st = strobe_now();
       const uint32_t left = rounds - round;
       Fr* d_msgs = reinterpret_cast<Fr*>(ctx->tail_out);
       Fr* d_chal = d_msgs + (size_t)left * (L + 1);
@@ -264,25 +364,8 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
           return fail(ZK_ERR_CUDA, "tail kernel launch failed");
         ctx->launches++;
         ZK_CUDA(cudaGetLastError());
-        const size_t bytes = ((size_t)left * (L + 2)) * sizeof(Fr) + sizeof(StrobeState);
-        unsigned int* h_flags = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(ctx->host_small) + 8192 - 16);
-        ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->tail_out, bytes, cudaMemcpyDeviceToHost, ctx->stream));
-        if (resident) ZK_CUDA(cudaMemcpyAsync(h_flags, sh, 16, cudaMemcpyDeviceToHost, ctx->stream));
-        ZK_CUDA(cudaStreamSynchronize(ctx->stream));
-        if (resident && h_flags[2] != 0) return fail(ZK_ERR_TIMEOUT, "resident round kernel: a wait for a challenge ran out");
-        const Fr* h_msgs = reinterpret_cast<const Fr*>(ctx->host_small);
-        const Fr* h_chal = h_msgs + (size_t)left * (L + 1);
-        const StrobeState* h_st = reinterpret_cast<const StrobeState*>(h_chal + left);
-        for (uint32_t k = 0; k < left; k++) {
-          for (int c = 0; c <= L; c++)
-            fr_store(round_msgs + ((uint64_t)(round_offset + round + k) * (L + 1) + c) * 4, h_msgs[(size_t)k * (L + 1) + c]);
-          fr_store(challenges + 4 * (uint64_t)(round_offset + round + k), h_chal[k]);
-        }
-        *challenge = h_chal[left - 1];
-        memcpy(tr->m.strobe().state(), h_st->lanes, 200);
-        tr->m.strobe().pos() = (uint8_t)h_st->pos;
-        tr->m.strobe().pos_begin() = (uint8_t)h_st->pos_begin;
-        tr->m.strobe().cur_flags() = (uint8_t)h_st->cur_flags;
+        int rc = collect_device_rounds(round, left, resident);
+        if (rc) return rc;
         *finals_done = true;
         return ZK_OK;
       }

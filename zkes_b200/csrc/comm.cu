@@ -9,6 +9,7 @@
 #include "ec.cuh"
 
 #include <dlfcn.h>
+#include <vector>
 
 using namespace zk;
 
@@ -68,6 +69,64 @@ __global__ void k_sum_ranks(const Fr* __restrict__ gathered, int world, int n_va
   }
 }
 
+// ---- exchange of the round messages through peer memory
+//
+// Every rank owns one ExchangeBox in its own HBM and holds a peer mapping of every other rank's
+// box.  A round's exchange is one single-block kernel per rank: it stores this rank's partial sums
+// into slot [rank] of every rank's box (ordinary stores over NVLink), fences, stores the exchange's
+// sequence number into the matching flag of every box, then polls the flags of its *own* box until
+// all ranks' values of this exchange have landed, adds them in rank order (the same order on every
+// rank, so the sums are bit-identical) and publishes the complete message to the polling host.
+// Ranks only ever write remotely and read locally.  Two sets of slots alternate: a rank can be at
+// most one exchange ahead of the slowest, because finishing exchange k needs everybody's flag k.
+// The wait is bounded; when it runs out the kernel reports through the error word and returns.
+__global__ void __launch_bounds__(256) k_exchange_sum(const Fr* vals, int n_vals, int rank, int world, const PeerTable peers,
+                                                      unsigned int xseq, unsigned int spin_limit, Fr* out,
+                                                      const MsgSink sink, unsigned int* pub_error) {
+  __shared__ int ok;
+  const int par = xseq & 1u, t = threadIdx.x;
+  if (t == 0) ok = 1;
+  if (t < world * n_vals) {
+    const int r = t / n_vals, c = t - r * n_vals;
+    st_fr_sys(&peers.box[r]->slots[par][rank][c], vals[c]);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (t < world) *reinterpret_cast<volatile unsigned int*>(&peers.box[t]->flags[par][rank]) = xseq;
+  ExchangeBox* mine = peers.box[rank];
+  if (t < world) {
+    const volatile unsigned int* f = reinterpret_cast<const volatile unsigned int*>(&mine->flags[par][t]);
+    unsigned int polls = 0;
+    while (*f != xseq) {
+      if (++polls > spin_limit) {
+        ok = 0;
+        break;
+      }
+      __nanosleep(32);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (t < n_vals && ok) {
+    Fr sum = Fr::zero();
+    for (int r = 0; r < world; r++) {
+      const volatile uint32_t* q = reinterpret_cast<const volatile uint32_t*>(&mine->slots[par][r][t]);
+      Fr v;
+#pragma unroll
+      for (int i = 0; i < 8; i++) v.v[i] = q[i];
+      sum = add(sum, v);
+    }
+    out[t] = sum;
+    if (sink.pub_flag) st_fr_sys(sink.pub_msg + t, sum);
+  }
+  if (sink.pub_flag) {
+    if (t == 0) *reinterpret_cast<volatile unsigned int*>(pub_error) = ok ? 0u : 1u;
+    __threadfence_system();
+    __syncthreads();
+    if (t == 0) *reinterpret_cast<volatile unsigned int*>(sink.pub_flag) = sink.seq;
+  }
+}
+
 // point <- sum of `world` Jacobian points (rank-major in gathered)
 __global__ void k_sum_points(const Jacobian* __restrict__ gathered, int world, int n_points, Jacobian* out) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -101,15 +160,132 @@ struct zk_comm {
   ncclComm_t comm = nullptr;
   int rank = 0, world = 1;
   Fr* gather_buf = nullptr;  // world * 16 elements
+  // exchange through peer memory (all ranks agree on peer_ok)
+  bool peer_ok = false;
+  ExchangeBox* box = nullptr;  // this rank's box
+  PeerTable peers;             // every rank's box as this rank addresses it
+  unsigned int xseq = 0;       // exchanges so far: the same on every rank
 };
+
+// Maps every rank's exchange box into this process.  Leaves c->peer_ok false (and the NCCL path
+// in use) when any rank could not: the ranks agree on the outcome through one more all-gather.
+static void peer_setup(zk_ctx* ctx, zk_comm* c) {
+  for (int r = 0; r < kPeerRanks; r++) c->peers.box[r] = nullptr;
+  if (c->world > kPeerRanks) return;
+  cudaStream_t s = ctx->stream;
+  unsigned char mine_ok = 1;
+  cudaIpcMemHandle_t handle;
+  memset(&handle, 0, sizeof handle);
+  if (cudaMalloc(&c->box, sizeof(ExchangeBox)) != cudaSuccess) {
+    cudaGetLastError();
+    c->box = nullptr;
+    mine_ok = 0;
+  } else {
+    cudaMemsetAsync(c->box, 0, sizeof(ExchangeBox), s);
+    if (cudaIpcGetMemHandle(&handle, c->box) != cudaSuccess) {
+      cudaGetLastError();
+      mine_ok = 0;
+    }
+  }
+  // all-gather (handle, ok) through NCCL: 128 bytes per rank
+  constexpr size_t kRec = 128;
+  static_assert(sizeof(cudaIpcMemHandle_t) < kRec, "record too small");
+  unsigned char* d_rec = nullptr;
+  if (cudaMalloc(&d_rec, kRec * (c->world + 1)) != cudaSuccess) {
+    cudaGetLastError();
+    return;  // cannot even exchange the outcome; every rank that fails here stays on NCCL, the others time out loudly
+  }
+  std::vector<unsigned char> rec(kRec * (c->world + 1), 0);
+  memcpy(rec.data(), &handle, sizeof handle);
+  rec[kRec - 1] = mine_ok;
+  bool good = cudaMemcpyAsync(d_rec, rec.data(), kRec, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+              g_nccl.all_gather(d_rec, d_rec + kRec, kRec, 1, c->comm, s) == 0 &&
+              cudaMemcpyAsync(rec.data() + kRec, d_rec + kRec, kRec * c->world, cudaMemcpyDeviceToHost, s) == cudaSuccess &&
+              cudaStreamSynchronize(s) == cudaSuccess;
+  cudaFree(d_rec);
+  if (!good) {
+    cudaGetLastError();
+    return;
+  }
+  bool all_ok = true;
+  for (int r = 0; r < c->world; r++) all_ok = all_ok && rec[kRec * (r + 1) + kRec - 1] == 1;
+  unsigned char open_ok = all_ok ? 1 : 0;
+  if (all_ok) {
+    for (int r = 0; r < c->world; r++) {
+      if (r == c->rank) {
+        c->peers.box[r] = c->box;
+        continue;
+      }
+      cudaIpcMemHandle_t h;
+      memcpy(&h, rec.data() + kRec * (r + 1), sizeof h);
+      void* p = nullptr;
+      if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        cudaGetLastError();
+        open_ok = 0;
+        break;
+      }
+      c->peers.box[r] = reinterpret_cast<ExchangeBox*>(p);
+    }
+  }
+  // second agreement: every rank opened every box
+  unsigned char* d_ok = nullptr;
+  if (cudaMalloc(&d_ok, 256 * (c->world + 1)) != cudaSuccess) {
+    cudaGetLastError();
+    return;
+  }
+  std::vector<unsigned char> oks(256 * (c->world + 1), 0);
+  oks[0] = open_ok;
+  good = cudaMemcpyAsync(d_ok, oks.data(), 256, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+         g_nccl.all_gather(d_ok, d_ok + 256, 256, 1, c->comm, s) == 0 &&
+         cudaMemcpyAsync(oks.data() + 256, d_ok + 256, 256 * c->world, cudaMemcpyDeviceToHost, s) == cudaSuccess &&
+         cudaStreamSynchronize(s) == cudaSuccess;
+  cudaFree(d_ok);
+  if (!good) {
+    cudaGetLastError();
+    return;
+  }
+  bool every = true;
+  for (int r = 0; r < c->world; r++) every = every && oks[256 * (r + 1)] == 1;
+  c->peer_ok = every;
+}
+
+static void peer_teardown(zk_comm* c) {
+  for (int r = 0; r < c->world && r < kPeerRanks; r++)
+    if (r != c->rank && c->peers.box[r]) cudaIpcCloseMemHandle(c->peers.box[r]);
+  if (c->box) cudaFree(c->box);
+  cudaGetLastError();
+}
 
 namespace zk {
 int comm_world(const zk_comm* c) { return c ? c->world : 1; }
+
+// Arguments for kernels that exchange through the peer boxes themselves; false when the ranks have
+// no peer mapping (or the option is off) and the caller has to stay on the host-stepped exchange.
+bool comm_peer_args(const zk_ctx* ctx, const zk_comm* c, PeerExchange* out) {
+  if (!c || c->world == 1 || !c->peer_ok || !ctx->peer_exchange) return false;
+  out->peers = c->peers;
+  out->rank = c->rank;
+  out->world = c->world;
+  out->xseq_base = c->xseq;
+  out->spin_limit = 40u << 20;
+  return true;
+}
+// Accounts for `n` exchanges a kernel made on its own.
+void comm_peer_advance(zk_comm* c, unsigned int n) { c->xseq += n; }
 int comm_rank(const zk_comm* c) { return c ? c->rank : 0; }
 
 // vals (device, n_vals <= 16 elements) <- element-wise sum over all ranks; stream-ordered.
 int comm_sum_fr(zk_ctx* ctx, zk_comm* c, Fr* vals, int n_vals) {
   if (!c || c->world == 1) return ZK_OK;
+  if (c->peer_ok && ctx->peer_exchange && n_vals <= kPeerVals) {
+    c->xseq++;
+    unsigned int* pub_error = ctx->rs.sink.pub_flag ? ctx->rs.sink.pub_flag + 1 : nullptr;
+    // polls pause 32 ns: the limit is a few seconds, far beyond the skew between ranks of a healthy run
+    k_exchange_sum<<<1, 256, 0, ctx->stream>>>(vals, n_vals, c->rank, c->world, c->peers, c->xseq, 40u << 20, vals,
+                                               ctx->rs.sink, pub_error);
+    ctx->launches++;
+    return ZK_OK;
+  }
   int rc = g_nccl.all_gather(vals, c->gather_buf, (size_t)n_vals * sizeof(Fr), 1 /*ncclUint8*/, c->comm, ctx->stream);
   if (rc != 0) return fail(ZK_ERR_COMM, "ncclAllGather: %s", g_nccl.errstr ? g_nccl.errstr(rc) : "error");
   k_sum_ranks<<<1, 32, 0, ctx->stream>>>(c->gather_buf, c->world, n_vals, vals, ctx->rs.sink);
@@ -205,15 +381,19 @@ int zk_comm_init(zk_ctx* ctx, int rank, int world, const uint8_t unique_id[128],
     delete c;
     return fail(ZK_ERR_OOM, "comm_init: %s", cudaGetErrorString(e));
   }
+  if (world > 1) peer_setup(ctx, c);
   *out = c;
   return ZK_OK;
 }
+
+int zk_comm_peer_exchange(const zk_comm* c) { return c && c->peer_ok ? 1 : 0; }
 
 void zk_comm_free(zk_ctx* ctx, zk_comm* c) {
   if (!c) return;
   if (ctx) {
     CtxLock lk(ctx);
     cudaStreamSynchronize(ctx->stream);
+    peer_teardown(c);
     cudaFree(c->gather_buf);
     if (c->comm && g_nccl.destroy) g_nccl.destroy(c->comm);
   }

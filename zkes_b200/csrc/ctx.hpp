@@ -1,6 +1,7 @@
 // The library context and small host helpers shared by the C ABI translation units.
 #pragma once
 #include <atomic>
+#include <chrono>
 #include <cstdarg>
 #include <cstring>
 #include <mutex>
@@ -73,7 +74,12 @@ struct zk_ctx {
   size_t cmp_bytes = 0;
   uint64_t replicate_entries = zk::kReplicateEntries;  // sharded proves gather the tables at this many entries in all (0: never)
   bool sharded_finished = false; // set by the dense round loop of a sharded prove when it gathered the tables and ran to the end
+  bool peer_exchange = true;     // sharded proves exchange round messages through peer memory when the ranks could map it
   bool device_tail = true;       // run the last dense rounds in the single-block kernel (zk_set_option turns it off)
+  // host clock (microseconds since the first entry) at which each host-stepped round of the most recent
+  // proves had its challenge: where the time of a prove goes, round by round (zk_round_times)
+  std::vector<double> round_times;
+  std::chrono::steady_clock::time_point round_t0;
   MsmStatsPod last_msm;          // shape of the most recent MSM (window width, windows, entries)
   std::mutex mu;
   std::atomic<uint64_t> launches{0};
@@ -114,6 +120,8 @@ struct zk_transcript {
 
 namespace zk {
 typedef int (*fs_round_fn_t)(void* user, const uint64_t* msgs, uint32_t n_msgs, uint64_t challenge_out[4]);
+bool comm_peer_args(const zk_ctx* ctx, const zk_comm* c, PeerExchange* out);
+void comm_peer_advance(zk_comm* c, unsigned int n);
 int fs_round(zk_ctx* ctx, zk_comm* comm, int n_msgs, uint32_t round, fs_round_fn_t fs, void* fs_user, zk_transcript* tr,
              uint64_t* round_msgs, uint64_t* challenges, Fr* challenge);
 int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr** cur, Fr** ping, Fr** pong,

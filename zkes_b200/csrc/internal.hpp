@@ -71,11 +71,35 @@ int launch_tail(int num_poly, const Fr* const* src, uint32_t size, bool fold_fir
                 Fr* out_msgs, Fr* out_chal, Fr* out_final, StrobeState* out_st, cudaStream_t stream,
                 const Fr* r_dev = nullptr, const StrobeState* st_dev = nullptr);
 
+// Exchange of round messages between the ranks of a sharded prove through peer memory (comm.cu).
+// Every rank owns one ExchangeBox in its own HBM and holds a peer mapping of every other rank's.
+// An exchange with sequence number x uses slot set x & 1: a rank stores its values into slot
+// [its rank] of every rank's box, fences, stores x into the matching flag of every box, then polls
+// the flags of its own box until all ranks' x has landed and adds the values in rank order.  Ranks
+// only write remotely and read locally; a rank is at most one exchange ahead of the slowest.
+constexpr int kPeerRanks = 16;   // ranks a box has slots for (one NVSwitch domain)
+constexpr int kPeerVals = 16;    // values per exchange (a round message has at most 5)
+struct ExchangeBox {
+  Fr slots[2][kPeerRanks][kPeerVals];
+  unsigned int flags[2][kPeerRanks];
+};
+struct PeerTable {
+  ExchangeBox* box[kPeerRanks];
+};
+struct PeerExchange {
+  PeerTable peers;
+  int rank, world;
+  unsigned int xseq_base;   // exchanges made before this launch (the same on every rank)
+  unsigned int spin_limit;  // polls (32 ns apart) before a wait gives up
+};
+
 // resident.cu
 struct ResidentShared;
+// px != nullptr: the tables are this rank's chunks of a sharded instance; every round's message is the
+// sum over the ranks, exchanged through the peer boxes by the block that completes the local sums.
 int launch_resident(int num_poly, const Fr* const* src, Fr* const* ping, Fr* const* pong, uint64_t size, uint32_t rounds,
                     const StrobeState& st, Fr* partials, int max_blocks, int sm_count, ResidentShared* sh, Fr* out_msgs,
-                    Fr* out_chal, cudaStream_t stream);
+                    Fr* out_chal, cudaStream_t stream, const PeerExchange* px = nullptr);
 
 // sparse.cu
 void launch_sparse_msg(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,

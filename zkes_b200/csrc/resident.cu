@@ -8,6 +8,7 @@
 // hand-over.  The launch is cooperative so that all blocks are resident together; every wait is
 // bounded and reports through ResidentShared::error instead of spinning on.
 // Rounds: linear_prover.rs:59-72; message :82-140; fold :151-178.
+#include <cstring>
 #include "internal.hpp"
 #include "round_pass.cuh"
 #include "strobe_dev.cuh"
@@ -32,6 +33,7 @@ struct ResidentParams {
   Fr* out_msgs;         // rounds * (L + 1)
   Fr* out_chal;         // rounds
   Fr pow2[8];           // 2^(32 j + 64) mod r as plain integers: rows of a multiplier table
+  PeerExchange px;      // px.world > 1: sharded instance, messages are summed over the ranks
 };
 
 template <int L>
@@ -41,7 +43,7 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
   __shared__ Fr red[kWarps][L + 1];
   __shared__ Fr msg[L + 1];
   __shared__ __align__(16) uint8_t stream[WarpStrobe::round_stream_bytes<L>() + 15];
-  __shared__ int flag, ok_flag;
+  __shared__ int flag, ok_flag, px_ok;
   __shared__ __align__(16) uint64_t keccak_scratch[64];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int NV = L + 1;
@@ -119,6 +121,51 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
         msg[threadIdx.x] = w;
       }
       __syncthreads();
+      if (p.px.world > 1) {
+        // Sharded instance: msg holds this rank's share.  Store it into every rank's box, publish the
+        // exchange number, wait (bounded) for the other ranks' shares in this rank's own box and add
+        // them in rank order, so every rank absorbs the same message and derives the same challenge.
+        const unsigned int xseq = p.px.xseq_base + round + 1;
+        const int par = xseq & 1u, t = threadIdx.x;
+        if (t == 0) px_ok = 1;
+        for (int k = t; k < p.px.world * NV; k += kThreads) {
+          const int r = k / NV, c = k - r * NV;
+          st_fr_sys(&p.px.peers.box[r]->slots[par][p.px.rank][c], msg[c]);
+        }
+        __threadfence_system();
+        __syncthreads();
+        ExchangeBox* mine = p.px.peers.box[p.px.rank];
+        if (t < p.px.world) {
+          *reinterpret_cast<volatile unsigned int*>(&p.px.peers.box[t]->flags[par][p.px.rank]) = xseq;
+          const volatile unsigned int* f = reinterpret_cast<const volatile unsigned int*>(&mine->flags[par][t]);
+          unsigned int polls = 0;
+          while (*f != xseq) {
+            if (++polls > p.px.spin_limit) {
+              px_ok = 0;
+              break;
+            }
+            __nanosleep(32);
+          }
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (!px_ok) {  // a rank is missing: stop every block of this launch through the error word
+          if (t == 0) atomicExch(&p.sh->error, 2u);
+          return;
+        }
+        if (t < NV) {
+          Fr sum = Fr::zero();
+          for (int r = 0; r < p.px.world; r++) {
+            const volatile uint32_t* q = reinterpret_cast<const volatile uint32_t*>(&mine->slots[par][r][t]);
+            Fr v;
+#pragma unroll
+            for (int i = 0; i < 8; i++) v.v[i] = q[i];
+            sum = add(sum, v);
+          }
+          msg[t] = sum;
+        }
+        __syncthreads();
+      }
       if (warp == 0) {
         WarpStrobe ws;
         ws.scratch = keccak_scratch;
@@ -192,8 +239,14 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
 template <int L>
 int launch_resident_t(const Fr* const* src, Fr* const* ping, Fr* const* pong, uint64_t size, uint32_t rounds,
                       const StrobeState& st, Fr* partials, int max_blocks, int sm_count, ResidentShared* sh, Fr* out_msgs,
-                      Fr* out_chal, cudaStream_t stream) {
+                      Fr* out_chal, cudaStream_t stream, const PeerExchange* px) {
   ResidentParams<L> p;
+  if (px) {
+    p.px = *px;
+  } else {
+    memset(&p.px, 0, sizeof p.px);
+    p.px.world = 1;
+  }
   for (int i = 0; i < L; i++) {
     p.src[i] = src[i];
     p.ping[i] = ping[i];
@@ -241,12 +294,12 @@ int launch_resident_t(const Fr* const* src, Fr* const* ping, Fr* const* pong, ui
 // launch was not possible and nothing ran.
 int launch_resident(int num_poly, const Fr* const* src, Fr* const* ping, Fr* const* pong, uint64_t size, uint32_t rounds,
                     const StrobeState& st, Fr* partials, int max_blocks, int sm_count, ResidentShared* sh, Fr* out_msgs,
-                    Fr* out_chal, cudaStream_t stream) {
+                    Fr* out_chal, cudaStream_t stream, const PeerExchange* px) {
   switch (num_poly) {
-    case 1: return launch_resident_t<1>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream);
-    case 2: return launch_resident_t<2>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream);
-    case 3: return launch_resident_t<3>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream);
-    case 4: return launch_resident_t<4>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream);
+    case 1: return launch_resident_t<1>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream, px);
+    case 2: return launch_resident_t<2>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream, px);
+    case 3: return launch_resident_t<3>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream, px);
+    case 4: return launch_resident_t<4>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream, px);
     default: return -1;
   }
 }

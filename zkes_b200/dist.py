@@ -76,6 +76,12 @@ class Comm:
         check(lib.zk_comm_init(ctx.handle, self.rank, self.world, uid, ctypes.byref(h)), "zk_comm_init")
         self.handle = h
 
+    @property
+    def peer_exchange(self) -> bool:
+        """True when the ranks mapped each other's exchange boxes (round messages then cross NVLink by
+        peer stores inside one kernel per round instead of an NCCL all-gather)."""
+        return bool(lib.zk_comm_peer_exchange(self.handle))
+
     def close(self):
         if self.handle:
             lib.zk_comm_free(self.ctx.handle, self.handle)
