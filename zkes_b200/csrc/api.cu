@@ -246,7 +246,7 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
     ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->tail_out, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     if (resident) ZK_CUDA(cudaMemcpyAsync(h_flags, sh, 16, cudaMemcpyDeviceToHost, ctx->stream));
     ZK_CUDA(cudaStreamSynchronize(ctx->stream));
-    if (resident && h_flags[2] == 2) return fail(ZK_ERR_TIMEOUT, "resident round kernel: another rank's partial sums did not arrive");
+    if (resident && h_flags[2] >= 2) return fail(ZK_ERR_TIMEOUT, "sharded rounds: another rank's partial sums or table chunk did not arrive");
     if (resident && h_flags[2] != 0) return fail(ZK_ERR_TIMEOUT, "resident round kernel: a wait for a challenge ran out");
     const Fr* h_msgs = reinterpret_cast<const Fr*>(ctx->host_small);
     const Fr* h_chal = h_msgs + (size_t)left * (L + 1);
@@ -292,9 +292,7 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
       Fr* d_chal = d_msgs + (size_t)left * (L + 1);
       StrobeState* d_st = reinterpret_cast<StrobeState*>(d_chal + left);
       ResidentShared* sh = reinterpret_cast<ResidentShared*>(ctx->resident_sh);
-      Fr* rep = nullptr;
-      int rc = ctx->reserve_aux((size_t)L * kTailMax * sizeof(Fr) + 256, (void**)&rep);
-      if (rc) return rc;
+      int rc = ZK_OK;
       ctx->prof_begin(ZK_PROF_ROUND, 64.0 * L * (double)(size / 2) + 192.0 * L * (double)(size / 2));
       const int lrc = launch_resident(L, cur, ping, pong, size, R, st, ctx->rs.sink.partials, ctx->rs.max_blocks,
                                       ctx->sm_count, sh, d_msgs, d_chal, ctx->stream, &px);
@@ -304,13 +302,11 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
         comm_peer_advance(comm, R);
         Fr** last = ((R - 1) & 1) ? ping : pong;
         const uint64_t m = size >> (R - 1);
+        // the ranks store their chunks into each other's boxes (one launch; a wait that runs out lands
+        // in the resident kernel's error word, which the read-back below checks)
         const Fr* gathered[kMaxPolys];
-        for (int i = 0; i < L; i++) {
-          Fr* whole = rep + (size_t)i * kTailMax;
-          rc = comm_gather_bytes(ctx, comm, last[i], m * sizeof(Fr), whole);
-          if (rc) return rc;
-          gathered[i] = whole;
-        }
+        rc = comm_peer_gather(ctx, comm, L, last, (uint32_t)m, &sh->error, gathered);
+        if (rc) return rc;
         if (launch_tail(L, gathered, kTailMax, true, *challenge, st, d_msgs + (size_t)R * (L + 1), d_chal + R, ctx->final_out,
                         d_st, ctx->stream, &sh->challenge, &sh->st))
           return fail(ZK_ERR_CUDA, "tail kernel launch failed");

@@ -69,61 +69,60 @@ __global__ void k_sum_ranks(const Fr* __restrict__ gathered, int world, int n_va
   }
 }
 
-// ---- exchange of the round messages through peer memory
-//
-// Every rank owns one ExchangeBox in its own HBM and holds a peer mapping of every other rank's
-// box.  A round's exchange is one single-block kernel per rank: it stores this rank's partial sums
-// into slot [rank] of every rank's box (ordinary stores over NVLink), fences, stores the exchange's
-// sequence number into the matching flag of every box, then polls the flags of its *own* box until
-// all ranks' values of this exchange have landed, adds them in rank order (the same order on every
-// rank, so the sums are bit-identical) and publishes the complete message to the polling host.
-// Ranks only ever write remotely and read locally.  Two sets of slots alternate: a rank can be at
-// most one exchange ahead of the slowest, because finishing exchange k needs everybody's flag k.
-// The wait is bounded; when it runs out the kernel reports through the error word and returns.
-__global__ void __launch_bounds__(256) k_exchange_sum(const Fr* vals, int n_vals, int rank, int world, const PeerTable peers,
-                                                      unsigned int xseq, unsigned int spin_limit, Fr* out,
-                                                      const MsgSink sink, unsigned int* pub_error) {
-  __shared__ int ok;
-  const int par = xseq & 1u, t = threadIdx.x;
-  if (t == 0) ok = 1;
-  if (t < world * n_vals) {
-    const int r = t / n_vals, c = t - r * n_vals;
-    st_fr_sys(&peers.box[r]->slots[par][rank][c], vals[c]);
-  }
-  __threadfence_system();
+// ---- exchange of the round messages through peer memory (the protocol: internal.hpp, ExchangeBox)
+// One single-block kernel per rank and exchange, for the rounds that the host steps: stores this
+// rank's partial sums into every rank's box, waits (bounded) for the others' in its own box, adds
+// them in rank order and publishes the complete message to the polling host.  When the wait runs
+// out the kernel reports through the error word beside the host's sequence word and returns.
+__global__ void __launch_bounds__(256) k_exchange_sum(const Fr* vals, int n_vals, const PeerExchange px, unsigned int xseq,
+                                                      Fr* out, const MsgSink sink, unsigned int* pub_error) {
+  __shared__ uint32_t stage[kPeerRanks * kPeerVals * 8];
+  __shared__ Fr v[kPeerVals];
+  __shared__ int ok_shared;
+  const int t = threadIdx.x;
+  if (t < n_vals) v[t] = vals[t];
   __syncthreads();
-  if (t < world) *reinterpret_cast<volatile unsigned int*>(&peers.box[t]->flags[par][rank]) = xseq;
-  ExchangeBox* mine = peers.box[rank];
-  if (t < world) {
-    const volatile unsigned int* f = reinterpret_cast<const volatile unsigned int*>(&mine->flags[par][t]);
-    unsigned int polls = 0;
-    while (*f != xseq) {
-      if (++polls > spin_limit) {
-        ok = 0;
-        break;
-      }
-      __nanosleep(32);
-    }
-  }
-  __threadfence_system();
-  __syncthreads();
+  const bool ok = peer_exchange_sum(px, xseq, v, n_vals, stage, &ok_shared, t, blockDim.x);
   if (t < n_vals && ok) {
-    Fr sum = Fr::zero();
-    for (int r = 0; r < world; r++) {
-      const volatile uint32_t* q = reinterpret_cast<const volatile uint32_t*>(&mine->slots[par][r][t]);
-      Fr v;
-#pragma unroll
-      for (int i = 0; i < 8; i++) v.v[i] = q[i];
-      sum = add(sum, v);
-    }
-    out[t] = sum;
-    if (sink.pub_flag) st_fr_sys(sink.pub_msg + t, sum);
+    out[t] = v[t];
+    if (sink.pub_flag) st_fr_sys(sink.pub_msg + t, v[t]);
   }
   if (sink.pub_flag) {
     if (t == 0) *reinterpret_cast<volatile unsigned int*>(pub_error) = ok ? 0u : 1u;
     __threadfence_system();
     __syncthreads();
     if (t == 0) *reinterpret_cast<volatile unsigned int*>(sink.pub_flag) = sink.seq;
+  }
+}
+
+// Block r stores this rank's chunks into rank r's box, fences, raises its flag there, then waits for
+// rank r's flag in this rank's own box: when the kernel ends, every chunk has arrived here.
+__global__ void __launch_bounds__(256) k_peer_gather(const PeerExchange px, unsigned int gseq, int n_tables, uint32_t m,
+                                                     const Fr* t0, const Fr* t1, const Fr* t2, const Fr* t3,
+                                                     unsigned int* error_word) {
+  const int r = blockIdx.x;
+  ExchangeBox* theirs = px.peers.box[r];
+  const Fr* src[kMaxPolys] = {t0, t1, t2, t3};
+  const uint32_t chunks = m * 2;  // 16-byte pieces per table chunk
+  for (int i = 0; i < n_tables; i++) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src[i]);
+    uint4* d4 = reinterpret_cast<uint4*>(&theirs->gather[i][(size_t)px.rank * m]);
+    for (uint32_t k = threadIdx.x; k < chunks; k += blockDim.x) d4[k] = s4[k];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *reinterpret_cast<volatile unsigned int*>(&theirs->gather_flag[px.rank]) = gseq;
+    const volatile unsigned int* f = reinterpret_cast<const volatile unsigned int*>(&px.peers.box[px.rank]->gather_flag[r]);
+    unsigned int polls = 0;
+    while (*f != gseq) {
+      if (++polls > px.spin_limit) {
+        atomicExch(error_word, 3u);
+        break;
+      }
+      __nanosleep(64);
+    }
+    __threadfence_system();
   }
 }
 
@@ -165,6 +164,7 @@ struct zk_comm {
   ExchangeBox* box = nullptr;  // this rank's box
   PeerTable peers;             // every rank's box as this rank addresses it
   unsigned int xseq = 0;       // exchanges so far: the same on every rank
+  unsigned int gseq = 0;       // table hand-overs so far
 };
 
 // Maps every rank's exchange box into this process.  Leaves c->peer_ok false (and the NCCL path
@@ -267,8 +267,24 @@ bool comm_peer_args(const zk_ctx* ctx, const zk_comm* c, PeerExchange* out) {
   out->rank = c->rank;
   out->world = c->world;
   out->xseq_base = c->xseq;
-  out->spin_limit = 40u << 20;
+  out->spin_limit = 40u << 20;  // polls pause 32 ns: seconds, far beyond the skew between the ranks of a healthy run
   return true;
+}
+// Every rank's m-entry chunk of each of the n_tables tables, gathered in rank order into this rank's
+// box by the ranks' own stores; tables_out[i] is the complete table i (kGatherEntries = world * m
+// entries at most).  error_word (device) is set to 3 when a wait ran out.
+int comm_peer_gather(zk_ctx* ctx, zk_comm* c, int n_tables, const Fr* const* chunks, uint32_t m, unsigned int* error_word,
+                     const Fr** tables_out) {
+  PeerExchange px;
+  if (!comm_peer_args(ctx, c, &px)) return fail(ZK_ERR_COMM, "peer gather without a peer mapping");
+  if (n_tables > kMaxPolys || (uint64_t)m * c->world > kGatherEntries) return fail(ZK_ERR_ARG, "peer gather: too large");
+  c->gseq++;
+  const Fr* t[kMaxPolys] = {nullptr, nullptr, nullptr, nullptr};
+  for (int i = 0; i < n_tables; i++) t[i] = chunks[i];
+  k_peer_gather<<<c->world, 256, 0, ctx->stream>>>(px, c->gseq, n_tables, m, t[0], t[1], t[2], t[3], error_word);
+  ctx->launches++;
+  for (int i = 0; i < n_tables; i++) tables_out[i] = c->box->gather[i];
+  return ZK_OK;
 }
 // Accounts for `n` exchanges a kernel made on its own.
 void comm_peer_advance(zk_comm* c, unsigned int n) { c->xseq += n; }
@@ -278,11 +294,11 @@ int comm_rank(const zk_comm* c) { return c ? c->rank : 0; }
 int comm_sum_fr(zk_ctx* ctx, zk_comm* c, Fr* vals, int n_vals) {
   if (!c || c->world == 1) return ZK_OK;
   if (c->peer_ok && ctx->peer_exchange && n_vals <= kPeerVals) {
+    PeerExchange px;
+    comm_peer_args(ctx, c, &px);
     c->xseq++;
     unsigned int* pub_error = ctx->rs.sink.pub_flag ? ctx->rs.sink.pub_flag + 1 : nullptr;
-    // polls pause 32 ns: the limit is a few seconds, far beyond the skew between ranks of a healthy run
-    k_exchange_sum<<<1, 256, 0, ctx->stream>>>(vals, n_vals, c->rank, c->world, c->peers, c->xseq, 40u << 20, vals,
-                                               ctx->rs.sink, pub_error);
+    k_exchange_sum<<<1, 256, 0, ctx->stream>>>(vals, n_vals, px, c->xseq, vals, ctx->rs.sink, pub_error);
     ctx->launches++;
     return ZK_OK;
   }

@@ -122,6 +122,8 @@ namespace zk {
 typedef int (*fs_round_fn_t)(void* user, const uint64_t* msgs, uint32_t n_msgs, uint64_t challenge_out[4]);
 bool comm_peer_args(const zk_ctx* ctx, const zk_comm* c, PeerExchange* out);
 void comm_peer_advance(zk_comm* c, unsigned int n);
+int comm_peer_gather(zk_ctx* ctx, zk_comm* c, int n_tables, const Fr* const* chunks, uint32_t m, unsigned int* error_word,
+                     const Fr** tables_out);
 int fs_round(zk_ctx* ctx, zk_comm* comm, int n_msgs, uint32_t round, fs_round_fn_t fs, void* fs_user, zk_transcript* tr,
              uint64_t* round_msgs, uint64_t* challenges, Fr* challenge);
 int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr** cur, Fr** ping, Fr** pong,

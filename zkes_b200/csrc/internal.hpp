@@ -73,15 +73,22 @@ int launch_tail(int num_poly, const Fr* const* src, uint32_t size, bool fold_fir
 
 // Exchange of round messages between the ranks of a sharded prove through peer memory (comm.cu).
 // Every rank owns one ExchangeBox in its own HBM and holds a peer mapping of every other rank's.
-// An exchange with sequence number x uses slot set x & 1: a rank stores its values into slot
-// [its rank] of every rank's box, fences, stores x into the matching flag of every box, then polls
-// the flags of its own box until all ranks' x has landed and adds the values in rank order.  Ranks
-// only write remotely and read locally; a rank is at most one exchange ahead of the slowest.
+// A value crosses as eight 8-byte words {limb, exchange number}: an aligned 8-byte store arrives
+// whole, so a word that shows the expected number carries its limb, and neither fences nor a
+// separate flag are needed (one NVLink store latency per exchange).  An exchange with number x uses
+// slot set x & 1: a rank stores its values into slot [its rank] of every rank's box, then polls its
+// own box until every rank's words show x and adds the values in rank order.  Ranks only write
+// remotely and read locally; a rank is at most one exchange ahead of the slowest, so two slot sets
+// are enough.
 constexpr int kPeerRanks = 16;   // ranks a box has slots for (one NVSwitch domain)
 constexpr int kPeerVals = 16;    // values per exchange (a round message has at most 5)
+constexpr uint32_t kGatherEntries = 1024;  // entries per gathered table (the single-block tail kernel's size)
 struct ExchangeBox {
-  Fr slots[2][kPeerRanks][kPeerVals];
-  unsigned int flags[2][kPeerRanks];
+  uint2 words[2][kPeerRanks][kPeerVals][8];
+  // hand-over of a sharded prove to the single-block tail: every rank's chunk of each table, stored
+  // here by the ranks themselves (plain stores, a system-wide fence, then the flag)
+  Fr gather[kMaxPolys][kGatherEntries];
+  unsigned int gather_flag[kPeerRanks];
 };
 struct PeerTable {
   ExchangeBox* box[kPeerRanks];
@@ -92,6 +99,59 @@ struct PeerExchange {
   unsigned int xseq_base;   // exchanges made before this launch (the same on every rank)
   unsigned int spin_limit;  // polls (32 ns apart) before a wait gives up
 };
+
+// comm.cu: every rank stores its m-entry chunk of each of the L tables at position rank * m of gather[i]
+// in every rank's box and waits (bounded) for the other ranks' chunks; *error_word is set when a wait
+// ran out.  On success *tables_out[i] points at this rank's complete gather[i].
+#ifdef __CUDACC__
+// One exchange by a whole block of nthreads threads (all must call): vals[0 .. n_vals) in shared or
+// global memory is replaced by the sum over the ranks.  stage: world * n_vals * 8 words of shared
+// memory.  Returns false (to every thread) when a wait ran out.
+__device__ __forceinline__ bool peer_exchange_sum(const PeerExchange& px, unsigned int xseq, Fr* vals, int n_vals,
+                                                  uint32_t* stage, int* ok_shared, int tid, int nthreads) {
+  const int par = xseq & 1u;
+  const int words = px.world * n_vals * 8;
+  if (tid == 0) *ok_shared = 1;
+  __syncthreads();
+  for (int k = tid; k < words; k += nthreads) {
+    const int r = k / (n_vals * 8), rem = k - r * (n_vals * 8), c = rem >> 3, limb = rem & 7;
+    uint2* dst = &px.peers.box[r]->words[par][px.rank][c][limb];
+    const uint32_t v = vals[c].v[limb];
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(v), "r"(xseq) : "memory");
+  }
+  const ExchangeBox* mine = px.peers.box[px.rank];
+  for (int k = tid; k < words; k += nthreads) {
+    const int r = k / (n_vals * 8), rem = k - r * (n_vals * 8), c = rem >> 3, limb = rem & 7;
+    const uint2* src = &mine->words[par][r][c][limb];
+    uint32_t v, q;
+    unsigned int polls = 0;
+    for (;;) {
+      asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(q) : "l"(src) : "memory");
+      if (q == xseq) break;
+      if (++polls > px.spin_limit || *reinterpret_cast<volatile int*>(ok_shared) == 0) {
+        *reinterpret_cast<volatile int*>(ok_shared) = 0;
+        break;
+      }
+      __nanosleep(32);
+    }
+    stage[k] = v;
+  }
+  __syncthreads();
+  const bool ok = *ok_shared != 0;
+  if (ok && tid < n_vals) {
+    Fr sum = Fr::zero();
+    for (int r = 0; r < px.world; r++) {
+      Fr v;
+#pragma unroll
+      for (int i = 0; i < 8; i++) v.v[i] = stage[(r * n_vals + tid) * 8 + i];
+      sum = add(sum, v);
+    }
+    vals[tid] = sum;
+  }
+  __syncthreads();
+  return ok;
+}
+#endif
 
 // resident.cu
 struct ResidentShared;

@@ -44,6 +44,7 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
   __shared__ Fr msg[L + 1];
   __shared__ __align__(16) uint8_t stream[WarpStrobe::round_stream_bytes<L>() + 15];
   __shared__ int flag, ok_flag, px_ok;
+  __shared__ uint32_t px_stage[kPeerRanks * (L + 1) * 8];
   __shared__ __align__(16) uint64_t keccak_scratch[64];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int NV = L + 1;
@@ -122,49 +123,14 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
       }
       __syncthreads();
       if (p.px.world > 1) {
-        // Sharded instance: msg holds this rank's share.  Store it into every rank's box, publish the
-        // exchange number, wait (bounded) for the other ranks' shares in this rank's own box and add
-        // them in rank order, so every rank absorbs the same message and derives the same challenge.
+        // Sharded instance: msg holds this rank's share.  Store it into every rank's box, wait (bounded)
+        // for the other ranks' shares in this rank's own box and add them in rank order, so every rank
+        // absorbs the same message and derives the same challenge.
         const unsigned int xseq = p.px.xseq_base + round + 1;
-        const int par = xseq & 1u, t = threadIdx.x;
-        if (t == 0) px_ok = 1;
-        for (int k = t; k < p.px.world * NV; k += kThreads) {
-          const int r = k / NV, c = k - r * NV;
-          st_fr_sys(&p.px.peers.box[r]->slots[par][p.px.rank][c], msg[c]);
-        }
-        __threadfence_system();
-        __syncthreads();
-        ExchangeBox* mine = p.px.peers.box[p.px.rank];
-        if (t < p.px.world) {
-          *reinterpret_cast<volatile unsigned int*>(&p.px.peers.box[t]->flags[par][p.px.rank]) = xseq;
-          const volatile unsigned int* f = reinterpret_cast<const volatile unsigned int*>(&mine->flags[par][t]);
-          unsigned int polls = 0;
-          while (*f != xseq) {
-            if (++polls > p.px.spin_limit) {
-              px_ok = 0;
-              break;
-            }
-            __nanosleep(32);
-          }
-        }
-        __threadfence_system();
-        __syncthreads();
-        if (!px_ok) {  // a rank is missing: stop every block of this launch through the error word
-          if (t == 0) atomicExch(&p.sh->error, 2u);
+        if (!peer_exchange_sum(p.px, xseq, msg, NV, px_stage, &px_ok, threadIdx.x, kThreads)) {
+          if (threadIdx.x == 0) atomicExch(&p.sh->error, 2u);  // a rank is missing: stops every block of this launch
           return;
         }
-        if (t < NV) {
-          Fr sum = Fr::zero();
-          for (int r = 0; r < p.px.world; r++) {
-            const volatile uint32_t* q = reinterpret_cast<const volatile uint32_t*>(&mine->slots[par][r][t]);
-            Fr v;
-#pragma unroll
-            for (int i = 0; i < 8; i++) v.v[i] = q[i];
-            sum = add(sum, v);
-          }
-          msg[t] = sum;
-        }
-        __syncthreads();
       }
       if (warp == 0) {
         WarpStrobe ws;
