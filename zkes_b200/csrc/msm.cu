@@ -324,10 +324,7 @@ __global__ void __launch_bounds__(256) k_msm_fixup_few(const uint32_t* __restric
     return;
   }
   Xyzz acc = ld_xyzz(tails + c0);
-  for (uint32_t c = c0 + 1; c <= c1; c++) {
-    const Xyzz h = ld_xyzz(heads + c);
-    add_to(&acc, &h);
-  }
+  for (uint32_t c = c0 + 1; c <= c1; c++) acc = add(acc, ld_xyzz(heads + c));  // one call site: inlined
   st_xyzz(bucket_sums + b, acc);
 }
 
@@ -640,7 +637,7 @@ int msm_run_rows(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const
   // buckets per thread: the running sums cost 2 additions per bucket, the thread's offset multiple and
   // the block tree are per-thread overhead, so threads take up to 32 buckets while enough threads remain
   uint32_t per_thread = 4;
-  while (per_thread < 32 && (uint64_t)rows * k_windows * (half / (per_thread * 2)) >= 200000) per_thread *= 2;
+  while (per_thread < 32 && (uint64_t)rows * k_windows * (half / (per_thread * 2)) >= 100000) per_thread *= 2;
   uint32_t threads = half / per_thread;
   if (threads < 32) threads = 32;
   if (threads > 256) threads = 256;
