@@ -74,6 +74,22 @@ def test_batched_msm(ctx, points, rows, n, kind):
     assert got == [o.g1_msm(bases, r) for r in mat]
 
 
+@pytest.mark.parametrize("bits", [8, 16])
+def test_batched_msm_many_rows(ctx, points, bits):
+    """Thousands of short rows over shared bases (the shape of a commitment's d_x rows): the bucket
+    sums of a row are then reduced by eight lanes, four rows to a warp.  Sampled rows against the oracle."""
+    rnd = random.Random(bits)
+    n = 256
+    bases = [points[i % len(points)] if i < len(points) else o.g1_mul(o.G1_GEN, 1000 + i) for i in range(n)]
+    rows = 1100
+    mat = [[small(rnd, bits) for _ in range(n)] for _ in range(rows)]
+    mat[7] = [0] * n
+    mat[8] = [o.fr_from_int(-(1 << (bits - 1)))] * n  # the largest magnitude everywhere
+    got = curve.msm_batched(ctx, curve.affine_to_array(bases), mat)
+    for r in (0, 7, 8, 9, 511, 1024, rows - 1):
+        assert got[r] == o.g1_msm(bases, mat[r]), r
+
+
 def test_sparse_msm(ctx, points):
     rnd = random.Random(5)
     idx = [rnd.randrange(len(points)) for _ in range(50)]  # repeats allowed

@@ -267,7 +267,7 @@ bool comm_peer_args(const zk_ctx* ctx, const zk_comm* c, PeerExchange* out) {
   out->rank = c->rank;
   out->world = c->world;
   out->xseq_base = c->xseq;
-  out->spin_limit = 40u << 20;  // polls pause 32 ns: seconds, far beyond the skew between the ranks of a healthy run
+  out->spin_limit = 2u << 20;  // a poll is a load from this GPU's memory plus a 32 ns pause, about a microsecond: seconds in all, far beyond the skew between the ranks of a healthy run
   return true;
 }
 // Every rank's m-entry chunk of each of the n_tables tables, gathered in rank order into this rank's

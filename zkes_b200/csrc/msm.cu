@@ -418,6 +418,60 @@ __global__ void __launch_bounds__(256) k_msm_bucket_reduce(const Xyzz* __restric
   if (threadIdx.x == 0) st_xyzz(window_sums + blockIdx.x, acc);
 }
 
+// Many short rows (the d_x / d_y rows of a commitment: thousands of (row, window) items of at most
+// 256 buckets): a block per item leaves most of its additions to idle lanes.  Here eight lanes share
+// an item and four items a warp.  Lane l takes `per` consecutive buckets: running sums give its local
+// weighted sum A_l = sum_j (j - lo + 1) B_j and its plain sum R_l.  The item's result is
+// sum_l A_l + per * sum_{l >= 1} S_l with S_l = sum_{u >= l} R_u (a suffix scan over the eight lanes), so
+// every lane doubles its own S_l log2(per) times, adds A_l, and one three-level tree finishes.
+constexpr int kRowLanes = 8;
+__global__ void __launch_bounds__(128) k_msm_bucket_reduce_rows(const Xyzz* __restrict__ bucket_sums, uint32_t half,
+                                                               uint32_t n_items, Xyzz* window_sums) {
+  __shared__ Xyzz sh[128];
+  const uint32_t t = threadIdx.x, l = t & (kRowLanes - 1);
+  const uint32_t item = blockIdx.x * (128 / kRowLanes) + t / kRowLanes;
+  const bool live = item < n_items;
+  const uint32_t per = half / kRowLanes;  // a power of two, at least 1
+  const Xyzz* B = bucket_sums + (size_t)(live ? item : 0) * half;
+  Xyzz running = Xyzz::inf(), acc = Xyzz::inf();
+  if (live) {
+    const uint32_t lo = l * per;
+    for (uint32_t j = lo + per; j-- > lo;) {
+      const Xyzz bj = ld_xyzz(B + j);
+      add_to(&running, &bj);
+      add_to(&acc, &running);
+    }
+  }
+  // inclusive suffix scan of the running sums over the item's lanes
+  sh[t] = running;
+  __syncwarp();
+#pragma unroll
+  for (uint32_t off = 1; off < kRowLanes; off <<= 1) {
+    Xyzz other = Xyzz::inf();
+    if (l + off < kRowLanes) other = sh[t + off];
+    __syncwarp();
+    add_to(&running, &other);
+    sh[t] = running;
+    __syncwarp();
+  }
+  // lane l >= 1 contributes per * S_l
+  if (l == 0) running = Xyzz::inf();
+  for (uint32_t k = per; k > 1; k >>= 1) dbl_in_place(&running);
+  add_to(&acc, &running);
+  sh[t] = acc;
+  __syncwarp();
+#pragma unroll
+  for (uint32_t off = kRowLanes / 2; off > 0; off >>= 1) {
+    Xyzz other = Xyzz::inf();
+    if (l < off) other = sh[t + off];
+    __syncwarp();
+    add_to(&acc, &other);
+    sh[t] = acc;
+    __syncwarp();
+  }
+  if (live && l == 0) st_xyzz(window_sums + item, acc);
+}
+
 __global__ void k_msm_combine(const Xyzz* __restrict__ window_sums, uint32_t rows, int w, int k_windows, Jacobian* out) {
   const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= rows) return;
@@ -641,7 +695,11 @@ int msm_run_rows(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const
   uint32_t threads = half / per_thread;
   if (threads < 32) threads = 32;
   if (threads > 256) threads = 256;
-  k_msm_bucket_reduce<<<rows * k_windows, threads, threads * sizeof(Xyzz), s>>>(bucket_sums, half, window_sums);
+  const uint32_t n_items = rows * (uint32_t)k_windows;
+  if (n_items >= 1024 && half >= kRowLanes && half <= 256)
+    k_msm_bucket_reduce_rows<<<(n_items + 15) / 16, 128, 0, s>>>(bucket_sums, half, n_items, window_sums);
+  else
+    k_msm_bucket_reduce<<<n_items, threads, threads * sizeof(Xyzz), s>>>(bucket_sums, half, window_sums);
   k_msm_combine<<<(rows + 63) / 64, 64, 0, s>>>(window_sums, rows, w, k_windows, out_dev);
   ctx->launches += 2;
   ZK_CUDA(cudaGetLastError());
