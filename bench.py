@@ -211,6 +211,8 @@ def gpu_arm(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local_rank)
     if world > 1:
+        # NCCL's own version / debug lines belong on stderr: stdout carries the one JSON line
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = Context(local_rank)
     if args.device_tail is not None:
@@ -342,6 +344,11 @@ def gpu_arm(args):
                "ms_per_step": e2e_ms, "steps": e2e_steps}
         del h_dense, h_vals, h_idx
     clocks = sampler.stop() if rank == 0 else None
+    args.msm_sharded = None
+    if comm is not None and not args.no_msm:
+        del dense, vals, idx
+        torch.cuda.empty_cache()
+        args.msm_sharded = msm_leg_sharded(ctx, comm, rank, world, timed)
     if comm is not None:
         barrier()
         comm.close()
@@ -405,6 +412,53 @@ def msm_leg(ctx, n=24, steps=5):
                                          "32-bit multiply-add rate of this GPU (zk_microbench kind 0)"}}
 
 
+def msm_leg_sharded(ctx, comm, rank, world, timed):
+    """The MSM half of the metric on N GPUs, weak scaling: KZH2 commit of 2^(24 + log2 N) int8 evaluations,
+    every rank holding the 2^24 evaluations (and SRS points) of its x-rows.  C is a partial MSM per rank plus
+    one exchange of the partial points; the d_x rows are local and gathered.  points/s = 2 * 2^n / t."""
+    import numpy as np
+    import torch
+
+    from zkes_b200 import dist as zd
+    from zkes_b200._lib import ZK_MEM_DEVICE, check, lib
+    from zkes_b200.field import from_mont_array
+
+    lg = world.bit_length() - 1
+    n = 24 + lg
+    x_log, y_log = n // 2, n - n // 2
+
+    def uniform(stream, count):
+        t = torch.empty((count, 4), dtype=torch.int64, device="cuda")
+        torch.cuda.synchronize()
+        check(lib.zk_gen_uniform_fr(ctx.handle, 2, stream, 0, count, t.data_ptr()), "zk_gen_uniform_fr")
+        return from_mont_array(t.cpu().numpy().view(np.uint64))
+
+    tau_x, tau_y, alpha = uniform(1, 1 << x_log), uniform(2, 1 << y_log), uniform(3, 1)[0]
+    g = (1368015179489954701390400359078579693043519447331113978918064868415326638035,
+         9918110051302171585080402603319702774565515993150576347155970296011118125764)
+    srs = zd.sharded_kzh_setup(ctx, comm, 2, n, g, tau_x, tau_y, alpha=alpha)
+    local = (1 << n) // world
+    f = torch.empty((local, 4), dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    check(lib.zk_gen_small_fr(ctx.handle, 2, 7, rank * local, local, 8, f.data_ptr()), "zk_gen_small_fr")
+    c = np.zeros((1, 8), dtype=np.uint64)
+    dx = np.zeros((1 << x_log, 12), dtype=np.uint64)
+    vp = ctypes.c_void_p
+
+    def step():
+        check(lib.zk_kzh_commit_sharded(ctx.handle, comm.handle, srs.handle, vp(f.data_ptr()), ZK_MEM_DEVICE,
+                                        vp(c.ctypes.data), vp(dx.ctypes.data)), "zk_kzh_commit_sharded")
+
+    steps = 5
+    ms = timed(step, steps, 2) / steps
+    srs.close()
+    pairs = 2.0 * (1 << n)
+    return {"metric": "kzh2_commit_msm_points_per_s", "value": pairs / (ms * 1e-3), "unit": "points/s", "ms_per_commit": ms,
+            "n_gpus": world, "scaling": "weak",
+            "config": f"KZH2 commit, 2^{n} int8 evaluations, 2^{x_log} x 2^{y_log} split, seed 2, x-rows sharded over "
+                      f"{world} GPUs (2^24 evaluations and SRS points per GPU)"}
+
+
 def measured_peak_gbs():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -458,6 +512,8 @@ def main():
     msm = None
     if world == 1 and not args.no_msm:
         msm = msm_leg(ctx)
+    elif world > 1:
+        msm = args.msm_sharded
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
