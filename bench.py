@@ -211,8 +211,6 @@ def gpu_arm(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local_rank)
     if world > 1:
-        # NCCL's own version / debug lines belong on stderr: stdout carries the one JSON line
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = Context(local_rank)
     if args.device_tail is not None:
@@ -477,11 +475,20 @@ def main():
     if args.impl == "reference":
         reference_arm(args)
         return
+    # stdout carries the one JSON line and nothing else: whatever libraries write to file descriptor 1 while
+    # the bench runs (NCCL prints a version banner there) is sent to stderr, and the line goes to the real one
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj):
+        sys.stdout.flush()
+        os.write(real_stdout, (json.dumps(obj) + "\n").encode())
     if args.msm_only:
         from zkes_b200 import Context
 
         ctx = Context(0)
-        print(json.dumps(msm_leg(ctx, args.msm_log, max(1, args.steps))))
+        emit(msm_leg(ctx, args.msm_log, max(1, args.steps)))
         return
     ctx, rank, world, ms_per_step, value, launches, prof, e2e, clocks = gpu_arm(args)
     if rank != 0:
@@ -521,7 +528,7 @@ def main():
         "config": workload_config(args.num_var, args.nnz_log, world, getattr(args, "exchange", "nccl")),
         "gpu_launches": launches, "clocks": clocks, "e2e": e2e, "roofline": roofline, "cpu_baseline": cpu, "msm": msm,
     }
-    print(json.dumps(out))
+    emit(out)
 
 
 if __name__ == "__main__":
