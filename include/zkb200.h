@@ -213,6 +213,20 @@ int zk_fix_from_right(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem eva
 /* evaluate_multilinear_extension / DenseMLPoly::evaluate_at_point, src/util/poly.rs:622-652, 788-791:
  * out (4 x u64, host) = sum_i evals[i] * eq(i, point) for a table of 2^n elements and n coordinates. */
 int zk_mle_eval(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem, const uint64_t* point, uint64_t* out);
+/* Range-proof preprocessing of Dag::prove_range, src/dag/mod.rs:1314-1337, one call per auxiliary selection
+ * polynomial.  point: the k coordinates of the node's claim; (input_idx[e], table_idx[e]), e < n_sel: the pairs of
+ * SelectionPolynomial::selection (util/poly.rs:1017-1022), in idx_mem; the table has 2^table_log entries.
+ *   part[t] = sum over the pairs with table_idx = t of eq(point)[input_idx]      (:1324-1329)
+ *   middle_claim_out (4 x u64, host) = sum_t part[t] * t                          (:1330)
+ *   acc[t] += beta_gamma * part[t]    (:1332-1336 and the fold over the aux polynomials, :1339)
+ * acc (2^table_log elements in acc_mem) is updated in place: start from zeros and call once per polynomial.
+ * An index >= 2^k or >= 2^table_log is ZK_ERR_ARG (the reference panics on the slice index). */
+int zk_range_aux_accumulate(zk_ctx* ctx, uint32_t k, const uint64_t* point, uint64_t n_sel, const uint64_t* input_idx,
+                            const uint64_t* table_idx, zk_mem idx_mem, const uint64_t* beta_gamma, uint32_t table_log,
+                            uint64_t* acc, zk_mem acc_mem, uint64_t* middle_claim_out);
+/* range_dense(n).add_by_scalar(alpha), src/util/poly.rs:1359-1366 and 915-927 (dag/mod.rs:1340): out[i] = i + alpha
+ * for i < 2^n (n <= 32: the reference's entries are u32). */
+int zk_range_table(zk_ctx* ctx, uint32_t n, const uint64_t* alpha, uint64_t* out, zk_mem out_mem);
 /* permute_evals_by_ranges, src/basicblock/einsum.rs:142-198: reorders the variables of a table of 2^n elements
  * of elem_bytes (32: field elements; 16: the i128 witness integers).  ranges holds n_ranges (start, end) pairs
  * of old variable indices; listed one after the other they are the new variable order, lowest first.  Ranges

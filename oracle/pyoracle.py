@@ -247,6 +247,23 @@ def fix_variables_from_right(evals, fixed):
     return out
 
 
+def range_aux_accumulate(point, selection, beta_gamma, table_log, acc):
+    """src/dag/mod.rs:1314-1337 for one auxiliary polynomial: part[table_idx] += lagrange_basis[input_idx] over the
+    selection pairs (:1324-1329); middle claim sum_idx part[idx] * idx (:1330); the touched entries times beta_gamma
+    (:1332-1334; the others are zero), added to the running sum of the aux polynomials (:1339).  -> (middle, acc)."""
+    basis = evaluate_lagrange_basis(point)
+    part = [0] * (1 << table_log)
+    for input_idx, table_idx in selection:
+        part[table_idx] = (part[table_idx] + basis[input_idx]) % R_MOD
+    middle = sum(v * i for i, v in enumerate(part)) % R_MOD
+    return middle, [(a + beta_gamma * v) % R_MOD for a, v in zip(acc, part)]
+
+
+def range_table(n, alpha):
+    """range_dense(n).add_by_scalar(alpha): src/util/poly.rs:1359-1366, 915-927."""
+    return [(i + alpha) % R_MOD for i in range(1 << n)]
+
+
 def permute_evals_by_ranges(evals, n, ranges):
     """src/basicblock/einsum.rs:142-198: the ranges, one after the other, list the old variables in their new
     order; bit old_var of the old index moves to its new position."""

@@ -56,6 +56,9 @@ SIGNATURES = {
     "zk_kzh_open_sharded": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_uint32, c_void_p, c_void_p,
                                     c_void_p, c_void_p]),
     "zk_mle_eval": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_void_p, c_void_p]),
+    "zk_range_aux_accumulate": (c_int, [c_void_p, c_uint32, c_void_p, c_uint64, c_void_p, c_void_p, c_int, c_void_p, c_uint32,
+                                        c_void_p, c_int, c_void_p]),
+    "zk_range_table": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_int]),
     "zk_permute_by_ranges": (c_int, [c_void_p, c_uint32, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_int]),
     "zk_fix_variables_int": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_int]),
     "zk_eq_table": (c_int, [c_void_p, c_uint32, c_void_p, c_void_p, c_int]),

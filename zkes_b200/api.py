@@ -204,6 +204,29 @@ def fix_variables_zkgpt(ctx: Context, num_vars: int, t_idx, r, q_bits: int = 0) 
     return DenseMLPoly(num_vars - k, mont=out)
 
 
+def range_aux_accumulate(ctx: Context, point, selection, beta_gamma: int, table_log: int, acc: "DenseMLPoly"):
+    """src/dag/mod.rs:1314-1337 for one auxiliary selection polynomial: scatter-adds the Lagrange weights of
+    `point` at the pairs' input indices into their table indices, returns the middle claim sum_t part[t] * t
+    and adds beta_gamma * part to acc (a DenseMLPoly of table_log variables, updated in place)."""
+    k = len(point)
+    assert acc.n == table_log
+    pt = to_mont_array(point) if k else np.zeros((1, 4), dtype=np.uint64)
+    ii = np.ascontiguousarray(np.array([p[0] for p in selection] or [0], dtype=np.uint64))
+    tt = np.ascontiguousarray(np.array([p[1] for p in selection] or [0], dtype=np.uint64))
+    bg = to_mont_array([beta_gamma])
+    mid = np.zeros((1, 4), dtype=np.uint64)
+    check(lib.zk_range_aux_accumulate(ctx.handle, k, _ptr(pt), len(selection), _ptr(ii), _ptr(tt), ZK_MEM_HOST, _ptr(bg),
+                                      table_log, _ptr(acc.mont), ZK_MEM_HOST, _ptr(mid)), "zk_range_aux_accumulate")
+    return from_mont_array(mid)[0]
+
+
+def range_table(ctx: Context, n: int, alpha: int) -> "DenseMLPoly":
+    """range_dense(n).add_by_scalar(alpha) (src/util/poly.rs:1359-1366, 915-927)."""
+    out = np.zeros((1 << n, 4), dtype=np.uint64)
+    check(lib.zk_range_table(ctx.handle, n, _ptr(to_mont_array([alpha])), _ptr(out), ZK_MEM_HOST), "zk_range_table")
+    return DenseMLPoly(n, mont=out)
+
+
 class SumcheckProof:
     """src/crypto/sumcheck/prover.rs:9-14."""
 
