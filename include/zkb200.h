@@ -171,6 +171,12 @@ void zk_comm_free(zk_ctx* ctx, zk_comm* comm);
  * access) at zk_comm_init, so that ZK_OPT_PEER_EXCHANGE applies; 0 when the ranks stay on NCCL.  No counterpart
  * in the reference (single process). */
 int zk_comm_peer_exchange(const zk_comm* comm);
+/* Self-test of the bounded wait of the peer exchange on one GPU: runs the exchange kernel as rank 0 of two
+ * with both boxes mapped to one scratch box, so that rank 1's share never arrives; the wait gives up after
+ * `polls` polls (about a microsecond each, at most 2^22) and the call returns ZK_ERR_TIMEOUT, which is the
+ * expected outcome; the context stays usable.  ZK_OK would mean the wait was satisfied by nothing.  No
+ * counterpart in the reference. */
+int zk_comm_wait_selftest(zk_ctx* ctx, uint32_t polls);
 /* Sharded provers: the hypercube is cut on its top log2(world) variables, rank p holding entries
  * [p 2^num_var / world, (p+1) 2^num_var / world) of every table (for the sparse table: the
  * entries of that range, with indices relative to its start).  Each local round ends with an

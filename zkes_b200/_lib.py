@@ -97,6 +97,7 @@ SIGNATURES = {
     "zk_comm_init": (c_int, [c_void_p, c_int, c_int, c_void_p, POINTER(c_void_p)]),
     "zk_comm_free": (None, [c_void_p, c_void_p]),
     "zk_comm_peer_exchange": (c_int, [c_void_p]),
+    "zk_comm_wait_selftest": (c_int, [c_void_p, c_uint32]),
     "zk_round_times": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p]),
     "zk_sumcheck_linear_prove_sharded": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, POINTER(c_void_p), c_int,
                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -404,6 +404,40 @@ int zk_comm_init(zk_ctx* ctx, int rank, int world, const uint8_t unique_id[128],
 
 int zk_comm_peer_exchange(const zk_comm* c) { return c && c->peer_ok ? 1 : 0; }
 
+int zk_comm_wait_selftest(zk_ctx* ctx, uint32_t polls) {
+  if (!ctx || polls == 0 || polls > (1u << 22)) return fail(ZK_ERR_ARG, "comm_wait_selftest: polls must be in 1 .. 2^22");
+  CtxLock lk(ctx);
+  cudaStream_t s = ctx->stream;
+  ExchangeBox* box = nullptr;
+  cudaError_t e = cudaMalloc(&box, sizeof(ExchangeBox));
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(ZK_ERR_OOM, "comm_wait_selftest: %s", cudaGetErrorString(e));
+  }
+  ZK_CUDA(cudaMemsetAsync(box, 0, sizeof(ExchangeBox), s));
+  // two ranks on paper, one in fact: both boxes are this one, so rank 0's own words arrive and rank 1's never do
+  PeerExchange px;
+  for (int r = 0; r < kPeerRanks; r++) px.peers.box[r] = r < 2 ? box : nullptr;
+  px.rank = 0;
+  px.world = 2;
+  px.xseq_base = 0;
+  px.spin_limit = polls;
+  RoundScratch sc = ctx->next_msg_scratch(false);
+  volatile unsigned int* flag =
+      reinterpret_cast<volatile unsigned int*>(reinterpret_cast<char*>(ctx->mailbox) + 16 * sizeof(Fr));
+  k_exchange_sum<<<1, 256, 0, s>>>(ctx->rs.sink.msg, 3, px, 1u, ctx->rs.sink.msg, sc.sink, sc.sink.pub_flag + 1);
+  ctx->launches++;
+  cudaError_t le = cudaGetLastError();
+  cudaError_t se = cudaStreamSynchronize(s);
+  cudaFree(box);
+  if (le != cudaSuccess || se != cudaSuccess) return fail(ZK_ERR_CUDA, "comm_wait_selftest: %s", cudaGetErrorString(le != cudaSuccess ? le : se));
+  const bool published = flag[0] == sc.sink.seq, timed_out = flag[1] != 0;
+  flag[1] = 0;  // the error word belongs to the next exchange again
+  if (!published) return fail(ZK_ERR_CUDA, "comm_wait_selftest: the kernel did not publish");
+  if (timed_out) return fail(ZK_ERR_TIMEOUT, "comm_wait_selftest: the wait for rank 1 ran out after %u polls (expected)", polls);
+  return ZK_OK;
+}
+
 void zk_comm_free(zk_ctx* ctx, zk_comm* c) {
   if (!c) return;
   if (ctx) {
