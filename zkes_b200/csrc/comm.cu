@@ -267,7 +267,10 @@ bool comm_peer_args(const zk_ctx* ctx, const zk_comm* c, PeerExchange* out) {
   out->rank = c->rank;
   out->world = c->world;
   out->xseq_base = c->xseq;
-  out->spin_limit = 2u << 20;  // a poll is a load from this GPU's memory plus a 32 ns pause, about a microsecond: seconds in all, far beyond the skew between the ranks of a healthy run
+  // a poll is a load from this GPU's memory plus a 32 ns pause, about a microsecond: some tens of seconds in all.
+  // The ranks of a prove are separate host processes and may reach a call seconds apart (one still copying its
+  // inputs); the bound is there to end a wait for a rank that is gone, not to police that skew
+  out->spin_limit = 16u << 20;
   return true;
 }
 // Every rank's m-entry chunk of each of the n_tables tables, gathered in rank order into this rank's
