@@ -220,7 +220,9 @@ int launch_resident_t(const Fr* const* src, Fr* const* ping, Fr* const* pong, ui
   }
   p.size = size;
   p.rounds = rounds;
-  p.spin_limit = 8u << 20;  // with the 64 ns pause between polls: seconds
+  // with the 64 ns pause between polls: seconds; sharded, the blocks also sit out the wait of the block
+  // that exchanges with the other ranks, which tolerates ranks that start seconds apart
+  p.spin_limit = px ? (48u << 20) : (8u << 20);
   p.st = st;
   p.partials = partials;
   p.sh = sh;
