@@ -368,8 +368,11 @@ int zk_sparse_kzh3_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const 
  * without waiting for it.  It uses the calling thread's current device, takes no zk_ctx, and
  * calls no cudaMalloc / cudaFree or any other allocating routine: the intermediate tables
  * live in a 1.5 MiB array that is part of the library image on every GPU that loads it.
- * The first call on a device looks up that array's device address; make that first call
- * outside any stream capture.  All calls on a device share the array (it keeps the previous
+ * The first call on a device looks up that array's device address, and with CUDA's lazy module
+ * loading it may also be the moment the driver places the library's code and this array in device
+ * memory: make that first call outside any stream capture and before the host hands the rest of
+ * HBM to its own pool (a warm-up call on a tiny table is enough).  Later calls on that device
+ * leave the free device memory untouched.  All calls on a device share the array (it keeps the previous
  * call's intermediates; nothing in it has to start at zero, every element read was written
  * earlier in the same call), so two calls whose work overlaps on the GPU race: keep them on
  * one stream or order them yourself. */
@@ -396,10 +399,9 @@ int zk_gen_gauss_fr(zk_ctx* ctx, uint64_t seed, uint64_t stream, uint64_t start,
 
 /* ---- measurement ---------------------------------------------------------------------- */
 /* Throughput probe for the integer roofline (no counterpart in the reference).  kind 0: 32-bit
- * multiply-add, 1: 32x32+64 wide multiply-add, 2 / 3: Montgomery product in Fr / Fq, 4 / 5: wide
- * multiply-adds inside carry chains (without / with carry-out), 6: separate lo and hi multiply-adds,
- * 7: 32-bit adds in carry chains, 8: fp64 fused multiply-add, 9: product with a launch-constant multiplier in Fr.  Runs the
- * probe twice and reports the second run: elapsed milliseconds and operations executed. */
+ * multiply-add, 2 / 3: Montgomery product in Fr / Fq, 4: 32x32+64 multiply-adds inside carry chains (the
+ * row primitive of the Montgomery product).  Runs the probe twice and reports the second run: elapsed
+ * milliseconds and operations executed. */
 int zk_microbench(zk_ctx* ctx, int kind, int blocks, int threads, int iters, float* ms_out, double* ops_out);
 
 #ifdef __cplusplus

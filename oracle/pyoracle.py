@@ -16,10 +16,10 @@ Parity status: the reference's own tests hold no golden vector for this path
 (they are property tests with a thread-seeded SRS).  What is pinned here:
 Keccak-f against hashlib's SHA3/SHAKE, the hand-derivable fold / eq / claimed-sum
 cases of the reference's tests, the sumcheck verifier accepting every proof, and
-the trapdoor identities of the KZH commitments.  The Merlin known-answer
-("test protocol" / "some label" / "some data") is reproduced from the published
-merlin test as recalled; everything beyond that is "parity unpinned" against the
-un-buildable arkworks/merlin crates.
+the trapdoor identities of the KZH commitments.  The transcript reproduces the
+known answer that the merlin crate pins in its own unit test `equivalence_simple`
+("test protocol" / "some label" / "some data"); everything beyond that is
+"parity unpinned" against the un-buildable arkworks/merlin crates.
 """
 from __future__ import annotations
 

@@ -47,8 +47,8 @@ def mle_at(ctx, n, f_ptr, point):
     return from_mont_array(out)[0]
 
 
-def test_kzh2_config3_shape(ctx):
-    """BASELINE config 3: 2^24 int8 evaluations on a 2^12 x 2^12 split."""
+def test_kzh2_int8_2p24(ctx):
+    """2^24 int8 evaluations (quantised weights) on a 2^12 x 2^12 split, seed 2."""
     import torch
     n, xl, yl = 24, 12, 12
     tx, ty = host_ints(dev_uniform(ctx, 2, 1, 1 << xl)), host_ints(dev_uniform(ctx, 2, 2, 1 << yl))
@@ -85,11 +85,12 @@ def test_kzh2_config3_shape(ctx):
     srs.close()
 
 
-def test_kzh3_config4_shape_reduced(ctx):
-    """BASELINE config 4's mix at n = 22 (8, 7, 7): alternating x-slabs of int16 fixed-point activations
-    and full-width values."""
+def run_kzh3_mix(ctx, n):
+    """KZH3 commit + open of 2^n evaluations in alternating x-slabs of int16 fixed-point activations
+    (N(0,1) * 2^8 rounded) and full-width values, checked by the trapdoor identities and the
+    identities of kzh3_verify (kzh3.rs:836-886)."""
     import torch
-    n, (xl, yl, zl) = 22, o.kzh3_degrees(22)
+    xl, yl, zl = o.kzh3_degrees(n)
     tx = host_ints(dev_uniform(ctx, 3, 1, 1 << xl))
     ty = host_ints(dev_uniform(ctx, 3, 2, 1 << yl))
     tz = host_ints(dev_uniform(ctx, 3, 3, 1 << zl))
@@ -98,11 +99,8 @@ def test_kzh3_config4_shape_reduced(ctx):
     torch.cuda.synchronize()
     check(lib.zk_gen_uniform_fr(ctx.handle, 3, 7, 0, 1 << n, f.data_ptr()), "gen")
     slab = 1 << (yl + zl)
-    act = torch.empty((slab, 4), dtype=torch.int64, device="cuda")
     for x in range(0, 1 << xl, 2):  # even slabs: N(0,1) * 2^8 rounded
-        torch.cuda.synchronize()
-        check(lib.zk_gen_gauss_fr(ctx.handle, 3, 8, x * slab, slab, 8, act.data_ptr()), "gen")
-        f[x * slab:(x + 1) * slab] = act
+        check(lib.zk_gen_gauss_fr(ctx.handle, 3, 8, x * slab, slab, 8, f[x * slab:(x + 1) * slab].data_ptr()), "gen")
     torch.cuda.synchronize()
     small = host_ints(f[:64])
     assert all(v < (1 << 15) or M - v < (1 << 15) for v in small) and len(set(small)) > 8
@@ -112,7 +110,7 @@ def test_kzh3_config4_shape_reduced(ctx):
     tyz = [ty[i >> zl] * tz[i & ((1 << zl) - 1)] % M for i in range(1 << (yl + zl))]
     assert com.c == o.g1_mul(G, sum(a * b for a, b in zip(gyz, tyz)) % M)
     d_x = com.d_x
-    for i in (0, 1, 255):  # an activation slab, a full-width slab, the last slab
+    for i in (0, 1, (1 << xl) - 1):  # an activation slab, a full-width slab, the last slab
         row = host_ints(f[i * slab:(i + 1) * slab])
         assert d_x[i] == o.g1_mul(G, sum(a * b for a, b in zip(row, tyz)) % M)
     rnd = random.Random(4)
@@ -122,8 +120,22 @@ def test_kzh3_config4_shape_reduced(ctx):
     assert o.evaluate_multilinear_extension(f_star, r_z) == mle_at(ctx, n, f.data_ptr(), pt)
     f_prime = contract_high(ctx, n, f.data_ptr(), xl, o.evaluate_lagrange_basis(r_x))
     assert c_y == o.g1_mul(G, sum(a * b for a, b in zip(f_prime, tyz)) % M)  # c_y = MSM(h_yz, f_prime) = sum eq d_x
-    for i in (0, 77, 127):
+    for i in (0, 77, (1 << yl) - 1):
         row = f_prime[i << zl:(i + 1) << zl]
         assert d_y[i] == o.g1_mul(G, sum(a * b for a, b in zip(row, tz)) % M)
     assert o.g1_mul(G, sum(a * b for a, b in zip(f_star, tz)) % M) == o.g1_msm(d_y, o.evaluate_lagrange_basis(r_y))
     srs.close()
+    del f
+    torch.cuda.empty_cache()
+
+
+def test_kzh3_mix_reduced(ctx):
+    """The int16 / full-width mix at n = 22 (8, 7, 7)."""
+    run_kzh3_mix(ctx, 22)
+
+
+def test_kzh3_mix_full_size(ctx):
+    """n = 28 on the 2^10 x 2^9 x 2^9 split: 8 GiB of evaluations against a 16 GiB h_xyz; the commitment's
+    MSM makes about 2.3 * 10^9 digit entries, the size at which 32-bit entry counts and offsets are closest
+    to their limit."""
+    run_kzh3_mix(ctx, 28)

@@ -6,7 +6,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("kind", [0, 1, 2, 3, 4, 5, 6, 7, 8, 9])
+@pytest.mark.parametrize("kind", [0, 2, 3, 4])
 def test_microbench_runs(ctx, kind):
     from zkes_b200._lib import check, lib
 

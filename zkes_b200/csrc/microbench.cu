@@ -1,5 +1,6 @@
 // Dependency-light throughput probes used as roofline denominators for the integer-bound
-// kernels: 32-bit multiply-add, 32x32+64 wide multiply-add, and the Montgomery product itself.
+// kernels: the 32-bit multiply-add rate (the nominal integer peak), wide multiply-adds inside carry
+// chains (the form big-integer arithmetic needs), and the Montgomery product itself.
 #include "../../include/zkb200.h"
 #include "ctx.hpp"
 
@@ -21,26 +22,8 @@ __global__ void k_imad(uint32_t* out, uint32_t b, uint32_t c, int iters) {
   out[blockIdx.x * blockDim.x + threadIdx.x] = s;
 }
 
-__global__ void k_imad_wide(uint32_t* out, uint32_t b, int iters) {
-  unsigned long long a[8];
-  uint32_t x[8];
-#pragma unroll
-  for (int k = 0; k < 8; k++) {
-    a[k] = threadIdx.x + k;
-    x[k] = threadIdx.x * 2654435761u + k;
-  }
-  for (int i = 0; i < iters; i++) {
-#pragma unroll
-    for (int k = 0; k < 8; k++) asm volatile("mad.wide.u32 %0, %1, %2, %0;" : "+l"(a[k]) : "r"(x[k]), "r"(b));
-  }
-  unsigned long long s = 0;
-#pragma unroll
-  for (int k = 0; k < 8; k++) s ^= a[k];
-  out[blockIdx.x * blockDim.x + threadIdx.x] = (uint32_t)s ^ (uint32_t)(s >> 32);
-}
-
 // Four independent madwide4 chains per thread (the Montgomery product's row primitive).
-__global__ void k_chain(uint32_t* out, uint32_t b, int iters, int with_carry) {
+__global__ void k_chain(uint32_t* out, uint32_t b, int iters) {
   uint32_t acc[4][8];
 #pragma unroll
   for (int c = 0; c < 4; c++)
@@ -50,10 +33,7 @@ __global__ void k_chain(uint32_t* out, uint32_t b, int iters, int with_carry) {
   for (int i = 0; i < iters; i++) {
 #pragma unroll
     for (int c = 0; c < 4; c++) {
-      if (with_carry)
-        cs += madwide4_c(acc[c], x0, x1, x2, x3, b);
-      else
-        madwide4(acc[c], x0, x1, x2, x3, b);
+      madwide4(acc[c], x0, x1, x2, x3, b);
     }
   }
   uint32_t s = cs;
@@ -61,64 +41,6 @@ __global__ void k_chain(uint32_t* out, uint32_t b, int iters, int with_carry) {
   for (int c = 0; c < 4; c++)
 #pragma unroll
     for (int k = 0; k < 8; k++) s ^= acc[c][k];
-  out[blockIdx.x * blockDim.x + threadIdx.x] = s;
-}
-
-// Unchained pairs: lo and hi halves of a product added into separate accumulators (no carries).
-__global__ void k_lohi(uint32_t* out, uint32_t b, int iters) {
-  uint32_t lo[8], hi[8], x[8];
-#pragma unroll
-  for (int k = 0; k < 8; k++) {
-    lo[k] = threadIdx.x + k;
-    hi[k] = threadIdx.x * 3 + k;
-    x[k] = threadIdx.x * 2654435761u + k;
-  }
-  for (int i = 0; i < iters; i++) {
-#pragma unroll
-    for (int k = 0; k < 8; k++) {
-      asm volatile("mad.lo.u32 %0, %1, %2, %0;" : "+r"(lo[k]) : "r"(x[k]), "r"(b));
-      asm volatile("mad.hi.u32 %0, %1, %2, %0;" : "+r"(hi[k]) : "r"(x[k]), "r"(b));
-    }
-  }
-  uint32_t s = 0;
-#pragma unroll
-  for (int k = 0; k < 8; k++) s ^= lo[k] ^ hi[k];
-  out[blockIdx.x * blockDim.x + threadIdx.x] = s;
-}
-
-// 8-limb add chains (add.cc / addc.cc), four independent per thread.
-__global__ void k_addchain(uint32_t* out, int iters) {
-  uint32_t a[4][8], b[8];
-#pragma unroll
-  for (int k = 0; k < 8; k++) b[k] = threadIdx.x * 11u + k;
-#pragma unroll
-  for (int c = 0; c < 4; c++)
-#pragma unroll
-    for (int k = 0; k < 8; k++) a[c][k] = threadIdx.x + c + k;
-  uint32_t cs = 0;
-  for (int i = 0; i < iters; i++) {
-#pragma unroll
-    for (int c = 0; c < 4; c++) cs += add8(a[c], a[c], b);
-  }
-  uint32_t s = cs;
-#pragma unroll
-  for (int c = 0; c < 4; c++)
-#pragma unroll
-    for (int k = 0; k < 8; k++) s ^= a[c][k];
-  out[blockIdx.x * blockDim.x + threadIdx.x] = s;
-}
-
-__global__ void k_dfma(double* out, double b, double c, int iters) {
-  double a[8];
-#pragma unroll
-  for (int k = 0; k < 8; k++) a[k] = threadIdx.x + k;
-  for (int i = 0; i < iters; i++) {
-#pragma unroll
-    for (int k = 0; k < 8; k++) asm volatile("fma.rn.f64 %0, %0, %1, %2;" : "+d"(a[k]) : "d"(b), "d"(c));
-  }
-  double s = 0;
-#pragma unroll
-  for (int k = 0; k < 8; k++) s += a[k];
   out[blockIdx.x * blockDim.x + threadIdx.x] = s;
 }
 
@@ -131,18 +53,6 @@ __global__ void k_modmul(Fp<P>* out, int iters) {
   for (int i = 0; i < iters; i++) {
     x = mul(x, y);
     z = mul(z, y);  // two independent chains per thread
-  }
-  out[blockIdx.x * blockDim.x + threadIdx.x] = add(x, z);
-}
-
-template <class P>
-__global__ void k_modmul_fixed(Fp<P>* out, const FixedMul<P> t, int iters) {
-  Fp<P> x = Fp<P>::one(), z = Fp<P>::r3();
-  x.v[0] ^= threadIdx.x;
-  z.v[1] ^= blockIdx.x;
-  for (int i = 0; i < iters; i++) {
-    x = mul_fixed(t, x);
-    z = mul_fixed(t, z);
   }
   out[blockIdx.x * blockDim.x + threadIdx.x] = add(x, z);
 }
@@ -164,15 +74,9 @@ extern "C" int zk_microbench(zk_ctx* ctx, int kind, int blocks, int threads, int
     ZK_CUDA(cudaEventRecord(e0, ctx->stream));
     switch (kind) {
       case 0: k_imad<<<blocks, threads, 0, ctx->stream>>>((uint32_t*)buf, 0x9e3779b9u, 12345u, iters); break;
-      case 1: k_imad_wide<<<blocks, threads, 0, ctx->stream>>>((uint32_t*)buf, 0x9e3779b9u, iters); break;
       case 2: k_modmul<FrParams><<<blocks, threads, 0, ctx->stream>>>((Fr*)buf, iters); break;
       case 3: k_modmul<FqParams><<<blocks, threads, 0, ctx->stream>>>((Fq*)buf, iters); break;
-      case 9: k_modmul_fixed<FrParams><<<blocks, threads, 0, ctx->stream>>>((Fr*)buf, make_fixed_mul(Fr::r2()), iters); break;
-      case 4: k_chain<<<blocks, threads, 0, ctx->stream>>>((uint32_t*)buf, 0x9e3779b9u, iters, 0); break;
-      case 5: k_chain<<<blocks, threads, 0, ctx->stream>>>((uint32_t*)buf, 0x9e3779b9u, iters, 1); break;
-      case 6: k_lohi<<<blocks, threads, 0, ctx->stream>>>((uint32_t*)buf, 0x9e3779b9u, iters); break;
-      case 7: k_addchain<<<blocks, threads, 0, ctx->stream>>>((uint32_t*)buf, iters); break;
-      case 8: k_dfma<<<blocks, threads, 0, ctx->stream>>>((double*)buf, 1.0000001, 0.5, iters); break;
+      case 4: k_chain<<<blocks, threads, 0, ctx->stream>>>((uint32_t*)buf, 0x9e3779b9u, iters); break;
       default: return fail(ZK_ERR_ARG, "zk_microbench: unknown kind %d", kind);
     }
     ctx->launches++;
@@ -183,12 +87,10 @@ extern "C" int zk_microbench(zk_ctx* ctx, int kind, int blocks, int threads, int
   ZK_CUDA(cudaEventElapsedTime(ms_out, e0, e1));
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
-  // operations per thread: multiply-adds (0, 1, 8), Montgomery products (2, 3), wide
-  // multiply-adds inside carry chains (4, 5), lo+hi pairs (6), 32-bit adds in chains (7)
+  // operations per thread: multiply-adds (0), Montgomery products (2, 3), wide multiply-adds inside carry chains (4)
   double per_thread = 8.0 * iters;
-  if (kind == 2 || kind == 3 || kind == 9) per_thread = 2.0 * iters;
-  if (kind == 4 || kind == 5) per_thread = 16.0 * iters;
-  if (kind == 7) per_thread = 32.0 * iters;
+  if (kind == 2 || kind == 3) per_thread = 2.0 * iters;
+  if (kind == 4) per_thread = 16.0 * iters;
   *ops_out = per_thread * blocks * (double)threads;
   return ZK_OK;
 }
