@@ -66,8 +66,13 @@ uint64_t zk_launch_count(const zk_ctx* ctx);
  * ZK_OPT_PEER_EXCHANGE (default 1): sharded proves exchange the per-round partial sums through peer memory
  * (one kernel per round that stores into every rank's box over NVLink and waits, bounded, for the others'
  * shares) when zk_comm_init could map the ranks' boxes; 0 uses the NCCL all-gather (identical outputs).  Set it
- * to the same value on every rank. */
-typedef enum zk_option { ZK_OPT_DEVICE_TAIL = 1, ZK_OPT_REPLICATE_LOG = 2, ZK_OPT_PEER_EXCHANGE = 3 } zk_option;
+ * to the same value on every rank.
+ * ZK_OPT_EXCHANGE_WAIT_MS (default 16000): roughly how long a kernel of a sharded prove waits for another
+ * rank's words before it gives up and the call returns ZK_ERR_TIMEOUT (the ranks are separate processes and
+ * may reach a call seconds apart; a service with tight deadlines, or a test, sets it lower). */
+typedef enum zk_option {
+  ZK_OPT_DEVICE_TAIL = 1, ZK_OPT_REPLICATE_LOG = 2, ZK_OPT_PEER_EXCHANGE = 3, ZK_OPT_EXCHANGE_WAIT_MS = 4
+} zk_option;
 int zk_set_option(zk_ctx* ctx, int option, int value);
 /* Diagnostics: the host clock, in microseconds from the first entry, at which each round that the host steps
  * (a caller's transcript, the entry-form rounds of the sparse provers, sharded rounds) had its challenge, for
@@ -161,10 +166,29 @@ int zk_sumcheck_general_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, 
                               void* fs_user, zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges,
                               uint64_t* final_tables, uint64_t* final_eval);
 
+/* SumcheckVerifier::verify, src/crypto/sumcheck/verifier.rs:27-69 (the header num_var, num_poly is absorbed
+ * by the caller as ::new does, :14-17): checks every round's s(0) + s(1) against the running sum, absorbs the
+ * evaluations, draws the challenge and interpolates (evaluate_univariate_polynomial, src/util/poly.rs:446-563).
+ * Host arithmetic only, no device is touched.  round_msgs: n_rounds x msgs_per_round elements.  *accepted = 1
+ * with the last running sum in final_sum_out (the caller compares it with the product of the tables' values at
+ * the challenges) and the challenges in challenges_out (either may be NULL); *accepted = 0 where the reference
+ * returns (None, vec![]): a wrong round count, a wrong number of evaluations, or a round that does not continue
+ * the running sum (its index in *failed_round, optional). */
+int zk_sumcheck_verify(zk_transcript* tr, uint32_t num_var, uint32_t num_poly, const uint64_t* round_msgs,
+                       uint32_t n_rounds, uint32_t msgs_per_round, const uint64_t* claimed_sum,
+                       uint64_t* challenges_out, uint64_t* final_sum_out, int* accepted, uint32_t* failed_round);
+
 /* ---- multi-GPU (one process per GPU; no counterpart in the reference, which is single-process) --- */
 /* A communicator over `world` ranks (a power of two, at most 64), bound to NCCL at run time.
  * Rank 0 calls zk_comm_unique_id and the host distributes the 128 bytes to the other ranks. */
 int zk_comm_unique_id(uint8_t out[128]);
+/* Error contract of the sharded calls below (every entry point that takes a zk_comm): they are collective,
+ * every rank makes the same calls in the same order.  When one of them returns non-zero on a rank, the
+ * communicator is retired on that rank: the ranks may have parted mid-exchange (one returned early, the
+ * others ran into a bounded wait and returned ZK_ERR_TIMEOUT), so every later sharded call on it returns
+ * ZK_ERR_COMM at once, without launching anything, until the host calls zk_comm_free and zk_comm_init
+ * again on all ranks.  A prove therefore either succeeds on every rank or fails on every rank, and a stale
+ * share of an aborted round is never taken for a fresh one. */
 int zk_comm_init(zk_ctx* ctx, int rank, int world, const uint8_t unique_id[128], zk_comm** out);
 void zk_comm_free(zk_ctx* ctx, zk_comm* comm);
 /* 1 when every rank of the communicator mapped every other rank's exchange box (CUDA IPC over NVLink peer

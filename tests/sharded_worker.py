@@ -3,7 +3,14 @@
   mode "gloo": CPU emulation of the sharded protocol with the oracle's arithmetic and the
                product's sharding helpers, exchanged over gloo; checks equality with the
                single-process oracle proof.
-  mode "nccl": the CUDA library's sharded provers on one GPU per rank against the oracle."""
+  mode "nccl": the CUDA library's sharded provers on one GPU per rank against the oracle.
+  mode "gloo-faults": failures injected on the host among CPU ranks (a rank that never posts its share, a
+               share damaged on the way, a rank that rejects its arguments): every rank must come back with
+               an error status instead of waiting on, the communicator must stay retired until it is made
+               anew, and a fresh one must prove correctly.
+  mode "nccl-faults": the same contract through the CUDA library on 2+ GPUs: one rank rejects its arguments
+               before launching anything, the other's bounded device-side wait runs out (ZK_ERR_TIMEOUT), both
+               then see ZK_ERR_COMM until the communicator is made anew."""
 import os
 import random
 import sys
@@ -92,10 +99,197 @@ def emulate_sharded_linear(tables, rank, world, label, replicate_entries=0):
     return msgs, chals, [t[0] for t in tail], final
 
 
+class ExchangeError(Exception):
+    def __init__(self, status):
+        super().__init__(status)
+        self.status = status
+
+
+class HostBox:
+    """CPU stand-in for the ranks' exchange boxes with the rules of the library's communicator: a share is
+    posted under its exchange number, a wait for the others' shares is bounded, and the first failure
+    retires the box on the rank that saw it (every later exchange fails at once)."""
+
+    def __init__(self, store, name, rank, world, wait_s=1.5):
+        self.store, self.name, self.rank, self.world, self.wait_s = store, name, rank, world, wait_s
+        self.xseq = 0
+        self.poisoned = False
+
+    def exchange_sum(self, vals, skip_post=False, damage=False):
+        import datetime
+        import pickle
+        if self.poisoned:
+            raise ExchangeError("COMM")
+        self.xseq += 1
+        mine = [(v + 1) % o.R_MOD for v in vals] if damage else list(vals)
+        if not skip_post:
+            self.store.set(f"{self.name}/x{self.xseq}/{self.rank}", pickle.dumps(mine))
+        total = [0] * len(vals)
+        for r in range(self.world):
+            key = f"{self.name}/x{self.xseq}/{r}"
+            try:
+                self.store.wait([key], datetime.timedelta(seconds=self.wait_s))
+            except Exception:
+                self.poisoned = True
+                raise ExchangeError("TIMEOUT")
+            share = vals if r == self.rank and not skip_post and not damage else pickle.loads(self.store.get(key))
+            total = [(a + b) % o.R_MOD for a, b in zip(total, share)]
+        return total
+
+
+def boxed_sharded_linear(box, tables, rank, world, label, fault=None):
+    """The sharded protocol over a HostBox.  fault = (kind, rank, round): "skip" (the rank never posts that
+    round's share), "damage" (its share arrives changed), "args" (it rejects its arguments before round 0).
+    Returns ("OK", proof parts) or raises ExchangeError with the status the library would return."""
+    from zkes_b200 import SumcheckVerifier, Transcript
+    if box.poisoned:
+        raise ExchangeError("COMM")
+    n = len(tables[0]).bit_length() - 1
+    L = len(tables)
+    try:
+        if fault and fault[0] == "args" and fault[1] == rank:
+            raise ExchangeError("ARG")
+        local = [zd.shard_dense(t, rank, world) for t in tables]
+        tr = o.Transcript(label)
+        tr.append_u64(b"num_var", n)
+        tr.append_u64(b"num_poly", L)
+        helper = o.LinearSumcheckProver.__new__(o.LinearSumcheckProver)
+        helper.num_poly = L
+        msgs, chals = [], []
+        n_local = n - zd.log2_exact(world)
+        for rnd_i in range(n_local):
+            helper.a_arrays = local
+            part = helper._round_message()
+            hit = fault and fault[1] == rank and fault[2] == rnd_i
+            msg = box.exchange_sum(part, skip_post=bool(hit and fault[0] == "skip"), damage=bool(hit and fault[0] == "damage"))
+            for m in msg:
+                tr.append_scalar(b"round_message", m)
+            ch = tr.challenge_scalar(b"challenge")
+            msgs.append(msg)
+            chals.append(ch)
+            local = [o.fix_variables(t, [ch]) for t in local]
+        finals = [box.exchange_sum([t[0] if r == rank else 0 for r in range(world) for t in local])]
+        per_rank = [finals[0][r * L:(r + 1) * L] for r in range(world)]
+        tail = zd.tail_tables(per_rank)
+        for _ in range(n - n_local):
+            helper.a_arrays = tail
+            msg = helper._round_message()
+            for m in msg:
+                tr.append_scalar(b"round_message", m)
+            ch = tr.challenge_scalar(b"challenge")
+            msgs.append(msg)
+            chals.append(ch)
+            tail = [o.fix_variables(t, [ch]) for t in tail]
+        final = 1
+        for t in tail:
+            final = final * t[0] % o.R_MOD
+        # the library's self-check of a sharded prove: every summed message continues the round before it
+        vt = Transcript(label)
+        res, _ = SumcheckVerifier(n, L, vt).verify(vt, msgs, (msgs[0][0] + msgs[0][1]) % o.R_MOD)
+        if res is None or res != final:
+            raise ExchangeError("COMM")
+        return msgs, chals, final
+    except ExchangeError:
+        box.poisoned = True
+        raise
+
+
+def gloo_faults(rank, world):
+    store = dist.distributed_c10d._get_default_store()
+    n = 6
+    idx, vals, dense, f = problem(n, 20, 9)
+    t = o.Transcript(b"faults")
+    p = o.LinearSumcheckProver(n, 2, t)
+    want = p.prove([dense, f], t)
+
+    def run(box, fault=None):
+        try:
+            got = boxed_sharded_linear(box, [dense, f], rank, world, b"faults", fault)
+            assert got[0] == want.round_messages and got[1] == p.challenges and got[2] == want.final_eval
+            return "OK"
+        except ExchangeError as e:
+            return e.status
+
+    victim = world - 1
+    for case, fault in enumerate([("skip", victim, 2), ("damage", victim, 1), ("args", victim, 0)]):
+        box = HostBox(store, f"case{case}", rank, world)
+        assert run(box) == "OK"                      # a healthy prove first
+        st = run(box, fault)
+        statuses = [None] * world
+        dist.all_gather_object(statuses, st)
+        assert all(s != "OK" for s in statuses), (fault, statuses)   # nobody returns a proof, nobody hangs
+        if fault[0] == "args":
+            assert statuses[victim] == "ARG" and all(s == "TIMEOUT" for r, s in enumerate(statuses) if r != victim)
+        if fault[0] == "damage":
+            assert all(s == "COMM" for s in statuses), statuses        # the round chain breaks on every rank alike
+        assert run(box) == "COMM"                    # retired: fails at once, on every rank
+        dist.barrier()
+        fresh = HostBox(store, f"case{case}-fresh", rank, world)
+        assert run(fresh) == "OK"
+
+
+def nccl_faults(rank, world, local_rank):
+    import ctypes
+    import numpy as np
+    from zkes_b200 import Context, DenseMLPoly, Transcript
+    from zkes_b200._lib import (ZK_ERR_ARG, ZK_ERR_COMM, ZK_ERR_TIMEOUT, ZK_MEM_HOST, ZK_OPT_EXCHANGE_WAIT_MS, ZkError, lib)
+    ctx = Context(local_rank)
+    ctx.set_option(ZK_OPT_EXCHANGE_WAIT_MS, 400)
+    comm = zd.Comm(ctx)
+    assert comm.peer_exchange, "the ranks could not map each other's boxes: the bounded wait is the peer path's"
+    n = 13  # all local rounds in the resident kernel, exchanged through the boxes (no NCCL collective on the path)
+    idx, vals, dense, f = problem(n, 50, 5)
+    ot = o.Transcript(b"faults")
+    op = o.LinearSumcheckProver(n, 2, ot)
+    want = op.prove([dense, f], ot)
+    local = [DenseMLPoly.from_evaluations(zd.shard_dense(tb, rank, world)) for tb in (dense, f)]
+
+    def prove(c):
+        t = Transcript(b"faults")
+        t.append_u64(b"num_var", n)
+        t.append_u64(b"num_poly", 2)
+        return zd.sharded_linear_prove(ctx, c, n, local, t)
+
+    msgs, chals, _, fin = prove(comm)
+    assert msgs == want.round_messages and fin == want.final_eval
+    dist.barrier()
+    # the last rank rejects its arguments (no table pointers) and launches nothing; the others wait, bounded
+    if rank == world - 1:
+        rc = lib.zk_sumcheck_linear_prove_sharded(ctx.handle, comm.handle, n, 0, None, ZK_MEM_HOST, None, None, None, None,
+                                                  None, None, None)
+        assert rc == ZK_ERR_ARG, rc
+    else:
+        try:
+            prove(comm)
+            raise AssertionError("a prove with a rank missing returned a proof")
+        except ZkError as e:
+            assert e.code == ZK_ERR_TIMEOUT, e
+    try:  # retired on every rank: nothing is launched, the status comes back at once
+        prove(comm)
+        raise AssertionError("a retired communicator proved")
+    except ZkError as e:
+        assert e.code == ZK_ERR_COMM, e
+    dist.barrier()
+    comm.close()
+    comm = zd.Comm(ctx)
+    msgs, chals, _, fin = prove(comm)  # a communicator made anew works, and the context was never lost
+    assert msgs == want.round_messages and chals == op.challenges and fin == want.final_eval
+    comm.close()
+    ctx.close()
+
+
 def main():
     mode = sys.argv[1]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    if mode == "gloo":
+    if mode == "gloo-faults":
+        dist.init_process_group("gloo")
+        gloo_faults(rank, world)
+    elif mode == "nccl-faults":
+        local_rank = int(os.environ.get("LOCAL_RANK", rank))
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        nccl_faults(rank, world, local_rank)
+    elif mode == "gloo":
         dist.init_process_group("gloo")
         for n, nnz, seed in [(5, 7, 1), (7, 30, 2)]:
             idx, vals, dense, f = problem(n, nnz, seed)

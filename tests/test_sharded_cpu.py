@@ -31,3 +31,16 @@ def test_gloo_sharded_protocol(world):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert "sharded worker ok" in r.stdout
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_gloo_injected_failures(world):
+    """A rank that never posts its share, a share damaged on the way, a rank that rejects its arguments: every
+    rank returns an error status (nobody waits on, nobody returns a proof), the communicator stays retired,
+    a fresh one proves correctly."""
+    port = 29700 + world + (os.getpid() % 1000)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "sharded_worker.py"), "gloo-faults"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    assert "sharded worker ok" in r.stdout

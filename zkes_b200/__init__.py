@@ -7,7 +7,8 @@ import importlib
 
 _API = ("Context", "DenseMLPoly", "LinearSumcheckProver", "SumcheckProof", "Transcript",
         "SparseDenseSumcheckProver", "evaluate_lagrange_basis", "fix_variables_from_right", "permute_evals_by_ranges", "fix_variables_zkgpt",
-        "SparseBoolSumcheckProver", "GeneralLinearSumcheckProver", "range_aux_accumulate", "range_table")
+        "SparseBoolSumcheckProver", "GeneralLinearSumcheckProver", "range_aux_accumulate", "range_table",
+        "SumcheckVerifier")
 
 
 def __getattr__(name):

@@ -13,6 +13,7 @@ ZK_MEM_HOST, ZK_MEM_DEVICE = 0, 1
 ZK_OPT_DEVICE_TAIL = 1
 ZK_OPT_REPLICATE_LOG = 2
 ZK_OPT_PEER_EXCHANGE = 3
+ZK_OPT_EXCHANGE_WAIT_MS = 4
 ZK_OK, ZK_ERR_ARG, ZK_ERR_OOM, ZK_ERR_CUDA, ZK_ERR_TIMEOUT, ZK_ERR_FS_CALLBACK, ZK_ERR_COMM = 0, -1, -2, -3, -4, -5, -6
 
 FS_ROUND_FN = ctypes.CFUNCTYPE(c_int, c_void_p, POINTER(c_uint64), c_uint32, POINTER(c_uint64))
@@ -48,6 +49,8 @@ SIGNATURES = {
     "zk_sumcheck_sparse_dense_prove": (c_int, [c_void_p, c_uint32, c_uint64, c_void_p, c_void_p, c_void_p, c_int,
                                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                c_void_p]),
+    "zk_sumcheck_verify": (c_int, [c_void_p, c_uint32, c_uint32, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p,
+                                   c_void_p, POINTER(c_int), POINTER(c_uint32)]),
     "zk_fix_from_right": (c_int, [c_void_p, c_uint32, c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_int]),
     "zk_kzh_verify_g1": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_void_p]),

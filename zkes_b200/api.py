@@ -235,6 +235,33 @@ class SumcheckProof:
         self.round_messages = round_messages
 
 
+class SumcheckVerifier:
+    """src/crypto/sumcheck/verifier.rs:7-70 (host arithmetic inside the library, no device needed)."""
+
+    def __init__(self, num_var: int, num_poly: int, transcript: Transcript):
+        transcript.append_u64(b"num_var", num_var)
+        transcript.append_u64(b"num_poly", num_poly)
+        self.num_var = num_var
+        self.num_poly = num_poly
+
+    def verify(self, transcript: Transcript, round_messages, claimed_sum):
+        """(final running sum or None, challenges), as the reference returns them."""
+        per = len(round_messages[0]) if round_messages else self.num_poly + 1
+        if any(len(m) != per for m in round_messages):
+            return None, []
+        flat = to_mont_array([v for m in round_messages for v in m] or [0])
+        claim = to_mont_array([claimed_sum])
+        chal = np.zeros((max(len(round_messages), 1), 4), dtype=np.uint64)
+        fin = np.zeros((1, 4), dtype=np.uint64)
+        ok, failed = ctypes.c_int(0), ctypes.c_uint32(0)
+        check(lib.zk_sumcheck_verify(transcript.handle, self.num_var, self.num_poly, _ptr(flat), len(round_messages), per,
+                                     _ptr(claim), _ptr(chal), _ptr(fin), ctypes.byref(ok), ctypes.byref(failed)),
+              "zk_sumcheck_verify")
+        if not ok.value:
+            return None, []
+        return from_mont_array(fin)[0], from_mont_array(chal[: len(round_messages)])
+
+
 class LinearSumcheckProver:
     """src/crypto/sumcheck/linear_prover.rs:13-191 on the GPU."""
 

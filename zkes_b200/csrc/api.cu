@@ -53,8 +53,13 @@ int fs_round(zk_ctx* ctx, zk_comm* comm, int n_msgs, uint32_t round, zk_fs_round
       }
     }
   }
-  if (comm && *reinterpret_cast<volatile unsigned int*>(reinterpret_cast<char*>(ctx->mailbox) + 16 * sizeof(Fr) + 4) != 0)
-    return fail(ZK_ERR_TIMEOUT, "round %u: the other ranks' partial sums did not arrive", round);  // the exchange kernel's wait ran out
+  if (comm) {  // the peer-exchange kernel's wait ran out: it said so in the word beside the sequence word
+    volatile unsigned int* err = reinterpret_cast<volatile unsigned int*>(reinterpret_cast<char*>(ctx->mailbox) + 16 * sizeof(Fr) + 4);
+    if (*err != 0) {
+      *err = 0;  // only that kernel writes the word: leave it clear for rounds that take the NCCL path
+      return fail(ZK_ERR_TIMEOUT, "round %u: the other ranks' partial sums did not arrive", round);
+    }
+  }
   const Fr* msg = reinterpret_cast<const Fr*>(ctx->mailbox);
   uint64_t* out_msg = round_msgs + (uint64_t)round * n_msgs * 4;
   for (int c = 0; c < n_msgs; c++) fr_store(out_msg + 4 * c, msg[c]);
@@ -113,6 +118,10 @@ int zk_set_option(zk_ctx* ctx, int option, int value) {
   switch (option) {
     case ZK_OPT_DEVICE_TAIL: ctx->device_tail = value != 0; return ZK_OK;
     case ZK_OPT_PEER_EXCHANGE: ctx->peer_exchange = value != 0; return ZK_OK;
+    case ZK_OPT_EXCHANGE_WAIT_MS:
+      if (value < 1 || value > 600000) return fail(ZK_ERR_ARG, "zk_set_option: exchange wait out of range (1 .. 600000 ms)");
+      ctx->exchange_wait_ms = (uint32_t)value;
+      return ZK_OK;
     case ZK_OPT_REPLICATE_LOG:
       if (value < 0 || value > 30) return fail(ZK_ERR_ARG, "zk_set_option: replicate threshold out of range");
       ctx->replicate_entries = value == 0 ? 0 : 1ull << value;
@@ -432,6 +441,40 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
   return ZK_OK;
 }
 
+// Self-check of a sharded prove on the host, a few microseconds: every summed message must continue the
+// round before it, s_m(0) + s_m(1) = s_{m-1}(r_{m-1}) (the identity SumcheckVerifier checks, verifier.rs:
+// 7-70).  A share that was damaged on its way between the ranks breaks it on every rank alike, so all
+// ranks report ZK_ERR_COMM instead of returning a proof no verifier accepts.  n_msgs = degree + 1 values
+// per round at the points 0..degree; Lagrange form with the denominators cleared:
+//   degree! * s(r) = sum_i (-1)^(degree-i) C(degree, i) s(i) prod_{j != i} (r - j).
+int check_round_chain(const uint64_t* round_msgs, const uint64_t* challenges, uint32_t rounds, int n_msgs) {
+  const int d = n_msgs - 1;
+  if (d < 1 || d > 8) return ZK_OK;
+  uint32_t fact = 1, binom[9];
+  for (int i = 1; i <= d; i++) fact *= i;
+  binom[0] = 1;
+  for (int i = 1; i <= d; i++) binom[i] = binom[i - 1] * (d - i + 1) / i;
+  const Fr fact_m = from_u32<FrParams>(fact);
+  for (uint32_t m = 1; m < rounds; m++) {
+    const uint64_t* prev = round_msgs + (uint64_t)(m - 1) * n_msgs * 4;
+    const uint64_t* cur = round_msgs + (uint64_t)m * n_msgs * 4;
+    const Fr r = fr_load(challenges + 4 * (uint64_t)(m - 1));
+    Fr diff[9];
+    for (int j = 0; j <= d; j++) diff[j] = sub(r, from_u32<FrParams>((uint32_t)j));
+    Fr rhs = Fr::zero();
+    for (int i = 0; i <= d; i++) {
+      Fr term = mul(fr_load(prev + 4 * i), from_u32<FrParams>(binom[i]));
+      for (int j = 0; j <= d; j++)
+        if (j != i) term = mul(term, diff[j]);
+      rhs = ((d - i) & 1) ? sub(rhs, term) : add(rhs, term);
+    }
+    const Fr lhs = mul(fact_m, add(fr_load(cur), fr_load(cur + 4)));
+    if (lhs != rhs)
+      return fail(ZK_ERR_COMM, "round %u: the summed message does not continue round %u (a rank's share was damaged in the exchange)", m, m - 1);
+  }
+  return ZK_OK;
+}
+
 // After the local rounds of a sharded prove: ctx->final_out[0..L) holds this rank's fully bound
 // value of each table.  Gathers them into L tables of `world` entries, runs the remaining
 // log2(world) rounds identically on every rank and leaves the final values in ctx->final_out.
@@ -533,6 +576,7 @@ int linear_prove_impl(zk_ctx* ctx, zk_comm* comm, uint32_t num_var, uint32_t num
   if (final_table0)
     for (int i = 0; i < L; i++) fr_store(final_table0 + 4 * i, fin[i]);
   fr_store(final_eval, fin[L]);
+  if (world > 1) return check_round_chain(round_msgs, challenges, num_var, L + 1);
   return ZK_OK;
 }
 
@@ -553,8 +597,10 @@ int zk_sumcheck_linear_prove_sharded(zk_ctx* ctx, zk_comm* comm, uint32_t num_va
                                      void* fs_user, zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges,
                                      uint64_t* final_table0, uint64_t* final_eval) {
   if (!comm) return fail(ZK_ERR_ARG, "linear_prove_sharded: NULL communicator");
-  return linear_prove_impl(ctx, comm, num_var, num_poly, local_tables, tables_mem, fs, fs_user, tr, round_msgs, challenges,
-                           final_table0, final_eval);
+  return sharded_call(comm, "linear_prove_sharded", [&] {
+    return linear_prove_impl(ctx, comm, num_var, num_poly, local_tables, tables_mem, fs, fs_user, tr, round_msgs, challenges,
+                             final_table0, final_eval);
+  });
 }
 
 // ---------------------------------------------------------------------------- folds

@@ -363,7 +363,7 @@ int zk_kzh3_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uint
 // kzh2_open / kzh3_open over a table sharded by x-rows (the layout of zk_kzh_commit_sharded): every
 // rank contracts its slab with its slice of eq(r_x), the partial tables are summed over the ranks,
 // and the small remainder of the opening (d_y, f_star, c_y) is computed on every rank alike.
-int zk_kzh_open_sharded(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs* srs, const uint64_t* local_evals, zk_mem evals_mem,
+static int kzh_open_sharded_impl(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs* srs, const uint64_t* local_evals, zk_mem evals_mem,
                         const uint64_t* point, uint32_t point_len, const uint64_t* d_x_jac, uint64_t* d_y_jac_out,
                         uint64_t* c_y_affine_out, uint64_t* f_star_out) {
   if (!ctx || !comm || !srs || !local_evals || !f_star_out || (point_len && !point))
@@ -410,6 +410,13 @@ int zk_kzh_open_sharded(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs* srs, const
     return ZK_OK;
   }
   return kzh3_open_tail(ctx, srs, f_prime, pt, d_x_jac, tail_mem, d_y_jac_out, c_y_affine_out, f_star_out);
+}
+
+int zk_kzh_open_sharded(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs* srs, const uint64_t* local_evals, zk_mem evals_mem,
+                        const uint64_t* point, uint32_t point_len, const uint64_t* d_x_jac, uint64_t* d_y_jac_out,
+                        uint64_t* c_y_affine_out, uint64_t* f_star_out) {
+  if (!comm) return fail(ZK_ERR_ARG, "kzh_open_sharded: NULL communicator");
+  return sharded_call(comm, "kzh_open_sharded", [&] { return kzh_open_sharded_impl(ctx, comm, srs, local_evals, evals_mem, point, point_len, d_x_jac, d_y_jac_out, c_y_affine_out, f_star_out); });
 }
 
 // The G1 and field checks of kzh2_verify (kzh2.rs:763-789: steps 2 and 3) and kzh3_verify

@@ -21,7 +21,7 @@ inline size_t al(size_t x) { return (x + 255) & ~(size_t)255; }
 
 extern "C" {
 
-int zk_msm_g1_sharded(zk_ctx* ctx, zk_comm* comm, const uint64_t* local_bases, zk_mem bases_mem,
+static int msm_g1_sharded_impl(zk_ctx* ctx, zk_comm* comm, const uint64_t* local_bases, zk_mem bases_mem,
                       const uint64_t* local_scalars, zk_mem scalars_mem, uint64_t n_local, uint64_t* out_jac) {
   if (!ctx || !comm || !out_jac) return fail(ZK_ERR_ARG, "msm_g1_sharded: NULL argument");
   if (n_local && (!local_bases || !local_scalars)) return fail(ZK_ERR_ARG, "msm_g1_sharded: NULL input");
@@ -57,9 +57,15 @@ int zk_msm_g1_sharded(zk_ctx* ctx, zk_comm* comm, const uint64_t* local_bases, z
   return ZK_OK;
 }
 
+int zk_msm_g1_sharded(zk_ctx* ctx, zk_comm* comm, const uint64_t* local_bases, zk_mem bases_mem,
+                      const uint64_t* local_scalars, zk_mem scalars_mem, uint64_t n_local, uint64_t* out_jac) {
+  if (!comm) return fail(ZK_ERR_ARG, "msm_g1_sharded: NULL communicator");
+  return sharded_call(comm, "msm_g1_sharded", [&] { return msm_g1_sharded_impl(ctx, comm, local_bases, bases_mem, local_scalars, scalars_mem, n_local, out_jac); });
+}
+
 // Commit with an SRS made by zk_kzh_srs_setup_sharded: local_evals is this rank's slab of the
 // polynomial (2^n / world elements = its x-rows).  Every rank receives c and the full d_x.
-int zk_kzh_commit_sharded(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs* srs, const uint64_t* local_evals,
+static int kzh_commit_sharded_impl(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs* srs, const uint64_t* local_evals,
                           zk_mem evals_mem, uint64_t* c_affine_out, uint64_t* d_x_jac_out) {
   if (!ctx || !comm || !srs || !local_evals || !c_affine_out || !d_x_jac_out)
     return fail(ZK_ERR_ARG, "kzh_commit_sharded: NULL argument");
@@ -102,10 +108,16 @@ int zk_kzh_commit_sharded(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs* srs, con
   return ZK_OK;
 }
 
+int zk_kzh_commit_sharded(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs* srs, const uint64_t* local_evals,
+                          zk_mem evals_mem, uint64_t* c_affine_out, uint64_t* d_x_jac_out) {
+  if (!comm) return fail(ZK_ERR_ARG, "kzh_commit_sharded: NULL communicator");
+  return sharded_call(comm, "kzh_commit_sharded", [&] { return kzh_commit_sharded_impl(ctx, comm, srs, local_evals, evals_mem, c_affine_out, d_x_jac_out); });
+}
+
 // fix_variables_from_right over a table sharded on its top variables: local_evals holds the
 // rank's 2^n / world entries; point binds the k highest variables (k >= log2 world).  Every rank
 // receives the full 2^(n-k) result.
-int zk_fix_from_right_sharded(zk_ctx* ctx, zk_comm* comm, uint32_t n, const uint64_t* local_evals, zk_mem evals_mem,
+static int fix_from_right_sharded_impl(zk_ctx* ctx, zk_comm* comm, uint32_t n, const uint64_t* local_evals, zk_mem evals_mem,
                               uint32_t k, const uint64_t* point, uint64_t* out) {
   if (!ctx || !comm || !local_evals || !out || (k && !point)) return fail(ZK_ERR_ARG, "fix_from_right_sharded: NULL argument");
   const int world = comm_world(comm), rank = comm_rank(comm);
@@ -143,6 +155,12 @@ int zk_fix_from_right_sharded(zk_ctx* ctx, zk_comm* comm, uint32_t n, const uint
   ZK_CUDA(cudaMemcpyAsync(out, d_out, lo_n * sizeof(Fr), cudaMemcpyDeviceToHost, s));
   ZK_CUDA(cudaStreamSynchronize(s));
   return ZK_OK;
+}
+
+int zk_fix_from_right_sharded(zk_ctx* ctx, zk_comm* comm, uint32_t n, const uint64_t* local_evals, zk_mem evals_mem,
+                              uint32_t k, const uint64_t* point, uint64_t* out) {
+  if (!comm) return fail(ZK_ERR_ARG, "fix_from_right_sharded: NULL communicator");
+  return sharded_call(comm, "fix_from_right_sharded", [&] { return fix_from_right_sharded_impl(ctx, comm, n, local_evals, evals_mem, k, point, out); });
 }
 
 }  // extern "C"

@@ -206,6 +206,7 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
     fr_store(final_table0 + 4, fin[1]);
   }
   fr_store(final_eval, fin[2]);
+  if (comm) return check_round_chain(round_msgs, challenges, total_var, 3);
   return ZK_OK;
 }
 
@@ -225,6 +226,8 @@ extern "C" int zk_sumcheck_sparse_dense_prove_sharded(zk_ctx* ctx, zk_comm* comm
                                                       uint64_t* challenges, uint64_t* final_table0,
                                                       uint64_t* final_eval) {
   if (!comm) return fail(ZK_ERR_ARG, "sparse_dense_prove_sharded: NULL communicator");
-  return sparse_dense_impl(ctx, comm, num_var, local_nnz, local_idx, local_vals, local_dense, mem, fs, fs_user, tr,
-                           round_msgs, challenges, final_table0, final_eval);
+  return sharded_call(comm, "sparse_dense_prove_sharded", [&] {
+    return sparse_dense_impl(ctx, comm, num_var, local_nnz, local_idx, local_vals, local_dense, mem, fs, fs_user, tr,
+                             round_msgs, challenges, final_table0, final_eval);
+  });
 }

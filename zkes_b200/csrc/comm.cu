@@ -165,6 +165,7 @@ struct zk_comm {
   PeerTable peers;             // every rank's box as this rank addresses it
   unsigned int xseq = 0;       // exchanges so far: the same on every rank
   unsigned int gseq = 0;       // table hand-overs so far
+  bool poisoned = false;       // a sharded call failed: the ranks' counters may differ, nothing more runs on it
 };
 
 // Maps every rank's exchange box into this process.  Leaves c->peer_ok false (and the NCCL path
@@ -187,14 +188,13 @@ static void peer_setup(zk_ctx* ctx, zk_comm* c) {
       mine_ok = 0;
     }
   }
-  // all-gather (handle, ok) through NCCL: 128 bytes per rank
+  // all-gather (handle, ok) through NCCL: 128 bytes per rank.  The staging is the communicator's own gather
+  // buffer (512 bytes per rank, allocated before this function runs): a rank never skips a collective because
+  // of a local failure, it takes part and carries the failure in its ok byte, so that all ranks agree.
   constexpr size_t kRec = 128;
   static_assert(sizeof(cudaIpcMemHandle_t) < kRec, "record too small");
-  unsigned char* d_rec = nullptr;
-  if (cudaMalloc(&d_rec, kRec * (c->world + 1)) != cudaSuccess) {
-    cudaGetLastError();
-    return;  // cannot even exchange the outcome; every rank that fails here stays on NCCL, the others time out loudly
-  }
+  static_assert(kRec * 2 <= 16 * sizeof(Fr), "the gather buffer holds a record per rank and this rank's own");
+  unsigned char* d_rec = reinterpret_cast<unsigned char*>(c->gather_buf);
   std::vector<unsigned char> rec(kRec * (c->world + 1), 0);
   memcpy(rec.data(), &handle, sizeof handle);
   rec[kRec - 1] = mine_ok;
@@ -202,12 +202,8 @@ static void peer_setup(zk_ctx* ctx, zk_comm* c) {
               g_nccl.all_gather(d_rec, d_rec + kRec, kRec, 1, c->comm, s) == 0 &&
               cudaMemcpyAsync(rec.data() + kRec, d_rec + kRec, kRec * c->world, cudaMemcpyDeviceToHost, s) == cudaSuccess &&
               cudaStreamSynchronize(s) == cudaSuccess;
-  cudaFree(d_rec);
-  if (!good) {
-    cudaGetLastError();
-    return;
-  }
-  bool all_ok = true;
+  if (!good) cudaGetLastError();
+  bool all_ok = good;
   for (int r = 0; r < c->world; r++) all_ok = all_ok && rec[kRec * (r + 1) + kRec - 1] == 1;
   unsigned char open_ok = all_ok ? 1 : 0;
   if (all_ok) {
@@ -228,24 +224,18 @@ static void peer_setup(zk_ctx* ctx, zk_comm* c) {
     }
   }
   // second agreement: every rank opened every box
-  unsigned char* d_ok = nullptr;
-  if (cudaMalloc(&d_ok, 256 * (c->world + 1)) != cudaSuccess) {
-    cudaGetLastError();
-    return;
-  }
-  std::vector<unsigned char> oks(256 * (c->world + 1), 0);
+  std::vector<unsigned char> oks(kRec * (c->world + 1), 0);
   oks[0] = open_ok;
-  good = cudaMemcpyAsync(d_ok, oks.data(), 256, cudaMemcpyHostToDevice, s) == cudaSuccess &&
-         g_nccl.all_gather(d_ok, d_ok + 256, 256, 1, c->comm, s) == 0 &&
-         cudaMemcpyAsync(oks.data() + 256, d_ok + 256, 256 * c->world, cudaMemcpyDeviceToHost, s) == cudaSuccess &&
+  good = cudaMemcpyAsync(d_rec, oks.data(), kRec, cudaMemcpyHostToDevice, s) == cudaSuccess &&
+         g_nccl.all_gather(d_rec, d_rec + kRec, kRec, 1, c->comm, s) == 0 &&
+         cudaMemcpyAsync(oks.data() + kRec, d_rec + kRec, kRec * c->world, cudaMemcpyDeviceToHost, s) == cudaSuccess &&
          cudaStreamSynchronize(s) == cudaSuccess;
-  cudaFree(d_ok);
   if (!good) {
     cudaGetLastError();
     return;
   }
   bool every = true;
-  for (int r = 0; r < c->world; r++) every = every && oks[256 * (r + 1)] == 1;
+  for (int r = 0; r < c->world; r++) every = every && oks[kRec * (r + 1)] == 1;
   c->peer_ok = every;
 }
 
@@ -258,6 +248,10 @@ static void peer_teardown(zk_comm* c) {
 
 namespace zk {
 int comm_world(const zk_comm* c) { return c ? c->world : 1; }
+bool comm_poisoned(const zk_comm* c) { return c && c->poisoned; }
+void comm_poison(zk_comm* c) {
+  if (c) c->poisoned = true;
+}
 
 // Arguments for kernels that exchange through the peer boxes themselves; false when the ranks have
 // no peer mapping (or the option is off) and the caller has to stay on the host-stepped exchange.
@@ -267,10 +261,10 @@ bool comm_peer_args(const zk_ctx* ctx, const zk_comm* c, PeerExchange* out) {
   out->rank = c->rank;
   out->world = c->world;
   out->xseq_base = c->xseq;
-  // a poll is a load from this GPU's memory plus a 32 ns pause, about a microsecond: some tens of seconds in all.
+  // a poll is a load from this GPU's memory plus a 32 ns pause, about a microsecond: 16 s and more by default.
   // The ranks of a prove are separate host processes and may reach a call seconds apart (one still copying its
   // inputs); the bound is there to end a wait for a rank that is gone, not to police that skew
-  out->spin_limit = 16u << 20;
+  out->spin_limit = ctx->exchange_wait_ms * 1024u;
   return true;
 }
 // Every rank's m-entry chunk of each of the n_tables tables, gathered in rank order into this rank's

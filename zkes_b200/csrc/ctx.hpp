@@ -75,6 +75,7 @@ struct zk_ctx {
   uint64_t replicate_entries = zk::kReplicateEntries;  // sharded proves gather the tables at this many entries in all (0: never)
   bool sharded_finished = false; // set by the dense round loop of a sharded prove when it gathered the tables and ran to the end
   bool peer_exchange = true;     // sharded proves exchange round messages through peer memory when the ranks could map it
+  uint32_t exchange_wait_ms = 16000;  // bound of a device-side wait for another rank's words (ZK_OPT_EXCHANGE_WAIT_MS)
   bool device_tail = true;       // run the last dense rounds in the single-block kernel (zk_set_option turns it off)
   // host clock (microseconds since the first entry) at which each host-stepped round of the most recent
   // proves had its challenge: where the time of a prove goes, round by round (zk_round_times)
@@ -129,6 +130,7 @@ int fs_round(zk_ctx* ctx, zk_comm* comm, int n_msgs, uint32_t round, fs_round_fn
 int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr** cur, Fr** ping, Fr** pong,
                   uint32_t round_offset, fs_round_fn_t fs, void* fs_user, zk_transcript* tr, uint64_t* round_msgs,
                   uint64_t* challenges, Fr* challenge, bool* finals_done);
+int check_round_chain(const uint64_t* round_msgs, const uint64_t* challenges, uint32_t rounds, int n_msgs);
 int sharded_tail(zk_ctx* ctx, zk_comm* comm, int L, uint32_t n_local, fs_round_fn_t fs, void* fs_user,
                  zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges, Fr* challenge);
 // comm.cu
@@ -137,6 +139,20 @@ int comm_rank(const zk_comm* c);
 int comm_sum_fr(zk_ctx* ctx, zk_comm* c, Fr* vals, int n_vals);
 int comm_gather_fr(zk_ctx* ctx, zk_comm* c, const Fr* vals, int n_vals, Fr* out);
 int comm_gather_bytes(zk_ctx* ctx, zk_comm* c, const void* send, size_t bytes, void* recv);
+// A communicator is retired by the first sharded call that fails on it: the ranks' exchange counters may have
+// parted (one rank returned early, the others ran on into a wait), and words of the aborted exchange are
+// still in the boxes.  Every later sharded call returns ZK_ERR_COMM at once, on every rank that saw a
+// failure, until the host frees the communicator and makes a new one on all ranks.
+bool comm_poisoned(const zk_comm* c);
+void comm_poison(zk_comm* c);
+template <class F>
+int sharded_call(zk_comm* comm, const char* name, F&& body) {
+  if (comm_poisoned(comm))
+    return fail(-6 /*ZK_ERR_COMM*/, "%s: an earlier sharded call failed on this communicator; free it and call zk_comm_init again on every rank", name);
+  const int rc = body();
+  if (rc != 0) comm_poison(comm);
+  return rc;
+}
 
 // Serialises calls on a context and makes its device current for the calling thread.
 struct CtxLock {

@@ -185,8 +185,12 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
       uint32_t polls = 0;
       int ok = 1;
       while (*seq < round + 1) {
-        if (*err != 0 || ++polls > p.spin_limit) {
-          atomicExch(&p.sh->error, 1u);
+        if (*err != 0) {  // another block gave up and said why: leave its code in place
+          ok = 0;
+          break;
+        }
+        if (++polls > p.spin_limit) {
+          atomicCAS(&p.sh->error, 0u, 1u);
           ok = 0;
           break;
         }
@@ -222,7 +226,7 @@ int launch_resident_t(const Fr* const* src, Fr* const* ping, Fr* const* pong, ui
   p.rounds = rounds;
   // with the 64 ns pause between polls: seconds; sharded, the blocks also sit out the wait of the block
   // that exchanges with the other ranks, which tolerates ranks that start seconds apart
-  p.spin_limit = px ? (48u << 20) : (8u << 20);
+  p.spin_limit = px ? 3u * px->spin_limit : (8u << 20);
   p.st = st;
   p.partials = partials;
   p.sh = sh;

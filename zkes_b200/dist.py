@@ -68,10 +68,11 @@ class Comm:
         uid = (ctypes.c_uint8 * 128)()
         if self.rank == 0:
             check(lib.zk_comm_unique_id(uid), "zk_comm_unique_id")
-        dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
-        t = torch.tensor(list(uid), dtype=torch.uint8, device=dev)
-        dist.broadcast(t, src=0)
-        uid = (ctypes.c_uint8 * 128)(*t.cpu().tolist())
+        if self.world > 1:
+            dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
+            t = torch.tensor(list(uid), dtype=torch.uint8, device=dev)
+            dist.broadcast(t, src=0)
+            uid = (ctypes.c_uint8 * 128)(*t.cpu().tolist())
         h = c_void_p()
         check(lib.zk_comm_init(ctx.handle, self.rank, self.world, uid, ctypes.byref(h)), "zk_comm_init")
         self.handle = h
