@@ -4,6 +4,7 @@
 #include <cstdint>
 #include <string>
 #include "poly.h"
+#include "gen.h"
 
 namespace orc {
 int g_threads = 1;
@@ -96,6 +97,14 @@ void orc_fix_from_right(uint32_t n, const uint64_t* evals, uint32_t k, const uin
 void orc_mle_eval(uint32_t n, const uint64_t* evals, const uint64_t* point, uint64_t* out) {
   Fr v = mle_eval(load_table(evals, size_t(1) << n), load_table(point, n));
   memcpy(out, v.l, 32);
+}
+
+// Seeded input streams (gen.h), elements in Montgomery form.
+void orc_gen_uniform_fr(uint64_t seed, uint64_t stream, uint64_t start, uint64_t count, uint64_t* out) {
+  gen_uniform(seed, stream, start, count, out);
+}
+void orc_gen_small_fr(uint64_t seed, uint64_t stream, uint64_t start, uint64_t count, int bits, uint64_t* out) {
+  gen_small(seed, stream, start, count, bits, out);
 }
 
 }  // extern "C"

@@ -137,3 +137,68 @@ def mle_eval(evals, point):
     em, pm = mont(evals), mont(point)
     lib.orc_mle_eval(c_uint32(len(point)), _p(em), _p(pm), _p(out))
     return unmont(out)[0]
+
+
+# ---- G1 (g1.h): points cross as (n, 8) uint64 arrays {x, y} in Montgomery form mod q, zeros for infinity
+Q_MOD = 0x30644E72E131A029B85045B68181585D97816A916871CA8D3C208C16D87CFD47
+
+
+def affine_array(points) -> np.ndarray:
+    """list of (x, y) tuples / None -> wire array."""
+    flat = []
+    for p in points:
+        flat += [0, 0] if p is None else [p[0], p[1]]
+    return mont(flat, Q_MOD).reshape(-1, 8) if points else np.zeros((0, 8), dtype=np.uint64)
+
+
+def affine_tuples(arr):
+    v = unmont(np.asarray(arr, dtype=np.uint64).reshape(-1, 4), Q_MOD)
+    return [None if (v[2 * i] == 0 and v[2 * i + 1] == 0) else (v[2 * i], v[2 * i + 1]) for i in range(len(v) // 2)]
+
+
+def g1_normalize(jac: np.ndarray):
+    n = jac.reshape(-1, 12).shape[0]
+    out = np.zeros((max(n, 1), 8), dtype=np.uint64)
+    lib.orc_g1_normalize(c_uint64(n), _p(np.ascontiguousarray(jac)), _p(out))
+    return affine_tuples(out[:n])
+
+
+def g1_msm_mont(bases_arr: np.ndarray, scalars_mont: np.ndarray):
+    """Bucket-method MSM over wire-form inputs on the configured threads -> affine tuple (None: infinity)."""
+    n = int(bases_arr.reshape(-1, 8).shape[0])
+    out = np.zeros((1, 12), dtype=np.uint64)
+    lib.orc_g1_msm(c_uint64(n), _p(np.ascontiguousarray(bases_arr)), _p(np.ascontiguousarray(scalars_mont)), _p(out))
+    return g1_normalize(out)[0]
+
+
+def g1_msm(points, scalars):
+    return g1_msm_mont(affine_array(points), mont(scalars))
+
+
+def g1_msm_rows_mont(bases_arr: np.ndarray, scalars_mont: np.ndarray, n_rows: int):
+    n = int(bases_arr.reshape(-1, 8).shape[0])
+    out = np.zeros((max(n_rows, 1), 12), dtype=np.uint64)
+    lib.orc_g1_msm_rows(c_uint64(n), c_uint64(n_rows), _p(np.ascontiguousarray(bases_arr)),
+                        _p(np.ascontiguousarray(scalars_mont)), _p(out))
+    return g1_normalize(out[:n_rows])
+
+
+def g1_mul(point, k: int):
+    out = np.zeros((1, 12), dtype=np.uint64)
+    kc = np.array([(k >> (64 * i)) & _M64 for i in range(4)], dtype=np.uint64)
+    b = affine_array([point])
+    lib.orc_g1_mul(_p(b), _p(kc), _p(out))
+    return g1_normalize(out)[0]
+
+
+def gen_uniform_fr_mont(seed: int, stream: int, start: int, count: int) -> np.ndarray:
+    """Element i = ChaCha20 block start+i of (seed, stream) as a 512-bit integer mod r, wire form (count, 4)."""
+    out = np.empty((max(count, 1), 4), dtype=np.uint64)
+    lib.orc_gen_uniform_fr(c_uint64(seed), c_uint64(stream), c_uint64(start), c_uint64(count), _p(out))
+    return out[:count]
+
+
+def gen_small_fr_mont(seed: int, stream: int, start: int, count: int, bits: int) -> np.ndarray:
+    out = np.empty((max(count, 1), 4), dtype=np.uint64)
+    lib.orc_gen_small_fr(c_uint64(seed), c_uint64(stream), c_uint64(start), c_uint64(count), c_int(bits), _p(out))
+    return out[:count]

@@ -135,3 +135,38 @@ def test_normalize(ctx, points):
             rows += [p[0] * z * z % Q_MOD, p[1] * z * z * z % Q_MOD, z]
     jac = to_mont_array(rows, Q_MOD).reshape(-1, 12)
     assert curve.normalize(ctx, jac) == points[:10] + [None]
+
+
+@pytest.mark.parametrize("n,kind", [(1 << 14, "full"), (1 << 15, "mixed"), (3000, "int8"), (1 << 13, "int16")])
+def test_msm_against_cpp_oracle_thousands_of_points(ctx, n, kind):
+    """Sizes the big-integer oracle cannot reach: the bases are an SRS vector generated on the device
+    (distinct multiples of g, read back), the expected point comes from the C++ bucket-method MSM."""
+    import ctypes
+
+    import coracle
+    from zkes_b200 import kzh
+    from zkes_b200._lib import ZK_MEM_HOST, check, lib
+    from zkes_b200.field import to_mont_array
+
+    coracle.set_threads(8)
+    rnd = random.Random(n + len(kind))
+    log = (n - 1).bit_length()
+    xl = log // 2
+    tx = [rnd.randrange(1, o.R_MOD) for _ in range(1 << xl)]
+    ty = [rnd.randrange(1, o.R_MOD) for _ in range(1 << (log - xl))]
+    srs = kzh.KZHSRS.setup(ctx, 2, log, o.g1_mul(o.G1_GEN, 31337), tx, ty, alpha=5)
+    bases = np.zeros((n, 8), dtype=np.uint64)
+    check(lib.zk_kzh_srs_read(ctx.handle, srs.handle, 0, 0, n, ctypes.c_void_p(bases.ctypes.data)), "zk_kzh_srs_read")
+    srs.close()
+    if kind == "full":
+        sc = [rnd.randrange(o.R_MOD) for _ in range(n)]
+    elif kind == "mixed":
+        sc = [small(rnd, 16) if (i >> 6) % 2 else rnd.randrange(o.R_MOD) for i in range(n)]
+    else:
+        sc = [small(rnd, 8 if kind == "int8" else 16) for _ in range(n)]
+    sm = to_mont_array(sc)
+    out = np.zeros((1, 12), dtype=np.uint64)
+    vp = ctypes.c_void_p
+    check(lib.zk_msm_g1(ctx.handle, vp(bases.ctypes.data), ZK_MEM_HOST, vp(sm.ctypes.data), ZK_MEM_HOST, n,
+                        vp(out.ctypes.data), ZK_MEM_HOST), "zk_msm_g1")
+    assert curve.jacobian_to_affine_py(out)[0] == coracle.g1_msm_mont(bases, sm)

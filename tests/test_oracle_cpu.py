@@ -174,3 +174,26 @@ def test_g1_compressed_encoding_round_trip():
         p = o.g1_mul(g, rnd.randrange(1, o.R_MOD))
         assert o.g1_deserialize_compressed(o.g1_serialize_compressed(p)) == p
     assert o.g1_deserialize_compressed(o.g1_serialize_compressed(None)) is None
+
+
+def test_cpp_g1_against_bigint_oracle():
+    """oracle/g1.h (Jacobian formulas, bucket-method MSM on threads) against the big-integer restatement."""
+    rnd = random.Random(5)
+    pts = [o.g1_mul(o.G1_GEN, rnd.randrange(1, o.R_MOD)) for _ in range(70)]
+    pts[7] = None
+    sc = [rnd.randrange(o.R_MOD) if i % 3 else o.fr_from_int(rnd.randrange(-128, 128)) for i in range(70)]
+    sc[11] = 0
+    assert c.g1_mul(o.G1_GEN, 12345) == o.g1_mul(o.G1_GEN, 12345)
+    for n in (0, 1, 2, 31, 32, 70):
+        assert c.g1_msm(pts[:n], sc[:n]) == o.g1_msm(pts[:n], sc[:n]), n
+    c.set_threads(4)
+    big = [pts[i % 70] for i in range(4500)]  # above the threshold at which the points are split over threads
+    bs = [rnd.randrange(o.R_MOD) for _ in range(4500)]
+    folded = [sum(bs[i] for i in range(j, 4500, 70)) % o.R_MOD for j in range(70)]
+    assert c.g1_msm(big, bs) == o.g1_msm(pts, folded)
+    rows = c.g1_msm_rows_mont(c.affine_array(pts[:16]), c.mont(sc[:64]), 4)
+    assert rows == [o.g1_msm(pts[:16], sc[16 * r:16 * r + 16]) for r in range(4)]
+    p = pts[0]
+    assert c.g1_msm([p, p], [1, 1]) == o.g1_mul(p, 2)  # the doubling branch of the mixed addition
+    assert c.g1_msm([p, o.g1_neg(p)], [5, 5]) is None
+    c.set_threads(1)
