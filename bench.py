@@ -1,21 +1,31 @@
 #!/usr/bin/env python
-"""Benchmark of the proving hot path on B200: sparse x dense product sumcheck over BN254 Fr.
+"""Benchmark of the proving hot path on B200.
 
-Workload (one "step" = one whole prove, transcript included): num_var = 26, dense table of 2^26
-uniform Fr elements, sparse table of 2^20 int8 values at distinct uniform indices, seed 1.
-Metric: Fr-evals/s = (2^26 + 2^20) / seconds per prove.
+Headline workload (one "step" = one whole prove, transcript included): the sparse x dense product
+sumcheck over BN254 Fr with num_var = 26: a dense table of 2^26 uniform elements, a sparse table of
+2^20 int8 values at distinct uniform positions, seed 1.  Metric: Fr-evals/s = (2^26 + 2^20) / seconds
+per prove.  Beside it, in the same JSON line, every other configuration that runs on this hardware:
+
+  linear_n20   dense prover, two tables of 2^20 uniform elements (seed 0)
+  msm          KZH2 commit of 2^24 int8 evaluations on a 2^12 x 2^12 split (seed 2), MSM points/s
+  kzh2_open    the opening of that commitment (fix_variables_from_right over 512 MiB)
+  kzh3         KZH3 commit + open of 2^28 evaluations, half int16 activations, half full width (seed 3)
+  strong       a num_var = 28 sparse x dense instance cut over the N GPUs of the run (fixed total work)
+  gpt2_trace   the hot-path calls of a GPT-2-small proof (shapes only, synthetic values), in seconds
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Prints one JSON line.  `value` is measured with the inputs resident in HBM; `e2e` goes through
-the C ABI with pinned host buffers (host->device copies inside the timed region).  The
-reference arm times the CPU restatement of the reference's prover (oracle/) on the host cores,
-because the reference is a Rust crate and no Rust toolchain exists on the box.
+Prints one JSON line.  `value` is measured with the inputs resident in HBM; `e2e` goes through the
+C ABI with pinned host buffers (host->device copies inside the timed region).  Every proof that was
+timed is verified afterwards (`verified`).  The reference arm times the CPU restatement of the
+reference's prover (oracle/) on the host cores on the same inputs, because the reference is a Rust
+crate and no Rust toolchain exists on the box.
 """
 from __future__ import annotations
 
 import argparse
 import ctypes
+import hashlib
 import json
 import os
 import subprocess
@@ -29,10 +39,15 @@ sys.path.insert(0, ROOT)
 NUM_VAR = 26
 NNZ_LOG = 20
 SEED = 1
-CPU_SAMPLE_VAR = 22      # bounded sample the CPU arm runs per step: same density, 2^22 domain
-CPU_SAMPLE_NNZ_LOG = 16
+STRONG_VAR = 28          # strong-scaling instance: fixed total size, cut over the GPUs of the run
+STRONG_NNZ_LOG = 22
 METRIC = "sumcheck_fr_evals_per_s"
 UNIT = "Fr-evals/s"
+R_MOD = 0x30644E72E131A029B85045B68181585D2833E84879B9709143E1F593F0000001
+# g = 2 * (1, 2) on y^2 = x^3 + 3, affine
+G2X = 1368015179489954701390400359078579693043519447331113978918064868415326638035
+G2Y = 9918110051302171585080402603319702774565515993150576347155970296011118125764
+vp = ctypes.c_void_p
 
 
 def parse_args():
@@ -48,9 +63,16 @@ def parse_args():
     ap.add_argument("--device-tail", type=int, default=None, help="override the library's ZK_OPT_DEVICE_TAIL default (0/1)")
     ap.add_argument("--peer-exchange", type=int, default=None, help="override ZK_OPT_PEER_EXCHANGE (0: NCCL all-gather per round)")
     ap.add_argument("--trace", action="store_true", help="print rank 0's per-round host times of one prove to stderr")
-    ap.add_argument("--no-msm", action="store_true", help="skip the KZH2 commit (MSM points/s) leg")
-    ap.add_argument("--msm-only", action="store_true", help="run the KZH2 commit leg alone and print its JSON (profiling captures)")
+    ap.add_argument("--no-msm", action="store_true", help="skip the KZH2 legs (commit MSM points/s, open)")
+    ap.add_argument("--no-kzh3", action="store_true", help="skip the KZH3 2^28 leg")
+    ap.add_argument("--no-linear", action="store_true", help="skip the dense num_var = 20 leg")
+    ap.add_argument("--no-strong", action="store_true", help="skip the num_var = 28 strong-scaling leg")
+    ap.add_argument("--no-gpt2", action="store_true", help="skip the GPT-2-small trace replay")
+    ap.add_argument("--only", default=None, choices=["msm", "kzh3", "linear", "strong", "gpt2"],
+                    help="run one extra leg alone and print its JSON (profiling captures)")
     ap.add_argument("--msm-log", type=int, default=24, help="log2 of the committed table (smaller sizes are for profiling captures only)")
+    ap.add_argument("--kzh3-log", type=int, default=28)
+    ap.add_argument("--linear-log", type=int, default=20)
     return ap.parse_args()
 
 
@@ -59,6 +81,9 @@ def workload_config(num_var: int, nnz_log: int, gpus: int, exchange: str = "nccl
     return {"workload": f"sparse-dense product sumcheck, BN254 Fr, num_var={num_var}, dense 2^{num_var} uniform, "
                         f"sparse 2^{nnz_log} int8 non-zeros, seed {SEED}" +
                         (f" per GPU (one instance of num_var={num_var + lg} sharded on its top {lg} variables)" if lg else ""),
+            "inputs": "ChaCha20 streams keyed by (seed, stream): dense = stream 0, element i = block i mod r; sparse values = "
+                      "stream 2 + 4 rank, int8; sparse positions = stream 3 + 4 rank, distinct 32-bit words masked to the "
+                      "rank's domain, sorted (zkes_b200/synth.py)",
             "parallelism": (f"hypercube sharded over {gpus} GPUs, partial round messages exchanged per round "
                             + ("by peer stores over NVLink inside one kernel" if exchange == "peer memory"
                                else "by an NCCL all-gather")
@@ -120,341 +145,11 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-# ----------------------------------------------------------------------------- CPU arm (oracle)
 def host_threads() -> int:
     try:
         return len(os.sched_getaffinity(0))
     except AttributeError:
         return os.cpu_count() or 1
-
-
-def cpu_sample_inputs(ctx, num_var: int, nnz_log: int):
-    """Inputs of the bounded CPU sample, generated by the same device-side generator."""
-    import numpy as np
-    import torch
-    from zkes_b200._lib import check, lib
-
-    dense = torch.empty((1 << num_var, 4), dtype=torch.int64, device="cuda")
-    vals = torch.empty((1 << nnz_log, 4), dtype=torch.int64, device="cuda")
-    torch.cuda.synchronize()
-    check(lib.zk_gen_uniform_fr(ctx.handle, SEED, 0, 0, 1 << num_var, dense.data_ptr()), "gen")
-    check(lib.zk_gen_small_fr(ctx.handle, SEED, 2, 0, 1 << nnz_log, 8, vals.data_ptr()), "gen")
-    g = torch.Generator(device="cuda")
-    g.manual_seed(SEED)
-    idx = torch.randperm(1 << num_var, generator=g, device="cuda")[: 1 << nnz_log].sort().values
-    return (idx.cpu().numpy().astype(np.uint64), vals.cpu().numpy().view(np.uint64), dense.cpu().numpy().view(np.uint64))
-
-
-def run_cpu_oracle(inputs, num_var: int, steps: int, warmup: int):
-    """Times the CPU restatement of the reference prover on all host threads."""
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import coracle
-
-    threads = host_threads()
-    coracle.set_threads(threads)
-    idx, vals, dense = inputs
-    times = []
-    for i in range(warmup + steps):
-        t0 = time.perf_counter()
-        coracle.sparse_dense_prove_mont(b"sumcheck_bench", num_var, idx, vals, dense)
-        if i >= warmup:
-            times.append(time.perf_counter() - t0)
-    return sum(times) / len(times), threads
-
-
-def synth_inputs_numpy(num_var: int, nnz_log: int):
-    """CPU-only input synthesis for the reference arm when no GPU generator is wanted."""
-    import numpy as np
-
-    rng = np.random.default_rng(SEED)
-    dense = rng.integers(0, 1 << 61, size=(1 << num_var, 4), dtype=np.uint64)  # top limb < 2^61: value < r
-    vals = np.zeros((1 << nnz_log, 4), dtype=np.uint64)
-    vals[:, 0] = rng.integers(1, 128, size=1 << nnz_log, dtype=np.uint64)
-    idx = np.sort(rng.choice(1 << num_var, size=1 << nnz_log, replace=False)).astype(np.uint64)
-    return idx, vals, dense
-
-
-def reference_arm(args):
-    """`--impl reference`: the reference's CPU algorithm (restated in oracle/, kind "port") on a
-    bounded sample of the workload per step.  Rank 0 only."""
-    if int(os.environ.get("RANK", "0")) != 0:
-        return
-    evals = (1 << CPU_SAMPLE_VAR) + (1 << CPU_SAMPLE_NNZ_LOG)
-    inputs = synth_inputs_numpy(CPU_SAMPLE_VAR, CPU_SAMPLE_NNZ_LOG)
-    sec, threads = run_cpu_oracle(inputs, CPU_SAMPLE_VAR, args.steps, min(args.warmup, 1))
-    value = evals / sec
-    sample = (f"per step: one prove on num_var={CPU_SAMPLE_VAR}, nnz=2^{CPU_SAMPLE_NNZ_LOG} (same 1/64 density); "
-              "throughput in Fr-evals/s is size-normalised")
-    print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "u256 (BN254 Fr, Montgomery)", "data": "synthetic",
-        "config": workload_config(NUM_VAR, NNZ_LOG, args.gpus),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
-        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }))
-
-
-# ----------------------------------------------------------------------------- GPU arm
-def gpu_arm(args):
-    import numpy as np
-    import torch
-    import torch.distributed as dist
-
-    from zkes_b200 import Context
-    from zkes_b200._lib import ZK_MEM_DEVICE, ZK_MEM_HOST, check, lib
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    ctx = Context(local_rank)
-    if args.device_tail is not None:
-        from zkes_b200._lib import ZK_OPT_DEVICE_TAIL
-        ctx.set_option(ZK_OPT_DEVICE_TAIL, args.device_tail)
-    n, k = args.num_var, args.nnz_log
-    comm = None
-    if world > 1:
-        from zkes_b200.dist import Comm, log2_exact
-        comm = Comm(ctx, rank, world)
-        if args.peer_exchange is not None:
-            from zkes_b200._lib import ZK_OPT_PEER_EXCHANGE
-            ctx.set_option(ZK_OPT_PEER_EXCHANGE, args.peer_exchange)
-        args.exchange = "peer memory" if comm.peer_exchange and args.peer_exchange != 0 else "nccl"
-    total_var = n + (world.bit_length() - 1)  # weak scaling: every rank owns a 2^n chunk of a 2^total_var table
-
-    # ---- inputs, resident in HBM (weak scaling: every rank owns a 2^n chunk of one sharded instance)
-    dense = torch.empty((1 << n, 4), dtype=torch.int64, device="cuda")
-    vals = torch.empty((1 << k, 4), dtype=torch.int64, device="cuda")
-    torch.cuda.synchronize()
-    check(lib.zk_gen_uniform_fr(ctx.handle, SEED, rank, 0, 1 << n, dense.data_ptr()), "zk_gen_uniform_fr")
-    check(lib.zk_gen_small_fr(ctx.handle, SEED, 1000 + rank, 0, 1 << k, 8, vals.data_ptr()), "zk_gen_small_fr")
-    g = torch.Generator(device="cuda")
-    g.manual_seed(SEED + rank)
-    idx = torch.randperm(1 << n, generator=g, device="cuda")[: 1 << k].sort().values.contiguous()
-    torch.cuda.synchronize()
-
-    msgs = np.zeros((total_var, 3, 4), dtype=np.uint64)
-    chal = np.zeros((total_var, 4), dtype=np.uint64)
-    fin_t = np.zeros((2, 4), dtype=np.uint64)
-    fin = np.zeros((1, 4), dtype=np.uint64)
-    vp = ctypes.c_void_p
-
-    def prove(idx_p, val_p, dense_p, mem):
-        tr = lib.zk_transcript_new(b"sumcheck_bench", 14)
-        lib.zk_transcript_append_u64(tr, b"num_var", 7, total_var)
-        lib.zk_transcript_append_u64(tr, b"num_poly", 8, 2)
-        if comm is None:
-            rc = lib.zk_sumcheck_sparse_dense_prove(ctx.handle, n, 1 << k, vp(idx_p), vp(val_p), vp(dense_p), mem, None,
-                                                    None, tr, vp(msgs.ctypes.data), vp(chal.ctypes.data),
-                                                    vp(fin_t.ctypes.data), vp(fin.ctypes.data))
-        else:
-            rc = lib.zk_sumcheck_sparse_dense_prove_sharded(ctx.handle, comm.handle, total_var, 1 << k, vp(idx_p),
-                                                            vp(val_p), vp(dense_p), mem, None, None, tr,
-                                                            vp(msgs.ctypes.data), vp(chal.ctypes.data),
-                                                            vp(fin_t.ctypes.data), vp(fin.ctypes.data))
-        lib.zk_transcript_free(tr)
-        check(rc, "zk_sumcheck_sparse_dense_prove")
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        ctx.sync()
-
-    stream = torch.cuda.ExternalStream(lib.zk_stream(ctx.handle))
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-
-    def timed(fn, steps, warmup):
-        for _ in range(warmup):
-            fn()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(steps):
-            fn()
-        e1.record(stream)
-        e1.synchronize()
-        barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
-
-    # ---- device-resident run (the `value`): the library's per-kernel event timing is off here
-    def dev_step():
-        prove(idx.data_ptr(), vals.data_ptr(), dense.data_ptr(), ZK_MEM_DEVICE)
-
-    for _ in range(args.warmup):
-        dev_step()
-    if args.trace:
-        buf = (ctypes.c_double * 4096)()
-        cnt = ctypes.c_uint32()
-        lib.zk_round_times(ctx.handle, buf, 4096, ctypes.byref(cnt))  # clears the warm-up's record
-        barrier()
-        t0 = time.perf_counter()
-        dev_step()
-        t1 = time.perf_counter()
-        lib.zk_round_times(ctx.handle, buf, 4096, ctypes.byref(cnt))
-        if rank == 0:
-            ts = [buf[i] for i in range(cnt.value)]
-            sys.stderr.write("trace: prove %.1f us; host-stepped rounds at (us): %s\n" % (
-                (t1 - t0) * 1e6, " ".join("%.0f" % t for t in ts)))
-            sys.stderr.write("trace: per-round gaps (us): %s\n" % " ".join("%.0f" % (b - a) for a, b in zip(ts, ts[1:])))
-    l0 = ctx.launch_count
-    total_ms = timed(dev_step, args.steps, 0)
-    launches = ctx.launch_count - l0
-    # ---- the same K steps again with CUDA events around every kernel of the path (roofline figures)
-    check(lib.zk_profile_enable(ctx.handle, 1), "zk_profile_enable")
-    profiled_ms = timed(dev_step, args.steps, 0)
-    prof = {"_profiled_ms_per_step": profiled_ms / args.steps}
-    for kind, name in enumerate(["round", "fold", "sparse_msg", "sparse_fold"]):
-        nl, ms, by = ctypes.c_uint64(), ctypes.c_double(), ctypes.c_double()
-        check(lib.zk_profile_get(ctx.handle, kind, ctypes.byref(nl), ctypes.byref(ms), ctypes.byref(by)), "zk_profile_get")
-        prof[name] = {"launches": nl.value, "ms": ms.value, "bytes": by.value}
-    check(lib.zk_profile_enable(ctx.handle, 0), "zk_profile_enable")
-    ms_per_step = total_ms / args.steps
-    evals = ((1 << n) + (1 << k)) * world
-    value = evals / (ms_per_step * 1e-3)
-
-    # ---- end to end through the C ABI with pinned host buffers
-    e2e = None
-    if not args.no_e2e:
-        h_dense = torch.empty(dense.shape, dtype=dense.dtype, pin_memory=True).copy_(dense)
-        h_vals = torch.empty(vals.shape, dtype=vals.dtype, pin_memory=True).copy_(vals)
-        h_idx = torch.empty(idx.shape, dtype=idx.dtype, pin_memory=True).copy_(idx)
-        torch.cuda.synchronize()
-
-        def host_step():
-            prove(h_idx.data_ptr(), h_vals.data_ptr(), h_dense.data_ptr(), ZK_MEM_HOST)
-
-        e2e_steps = max(1, min(args.steps, 5))
-        e2e_ms = timed(host_step, e2e_steps, 1) / e2e_steps
-        h2d = h_dense.numel() * 8 + h_vals.numel() * 8 + h_idx.numel() * 8
-        d2h = (total_var * 3 + 3) * 32 + 4
-        e2e = {"value": evals / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": e2e_ms, "steps": e2e_steps}
-        del h_dense, h_vals, h_idx
-    clocks = sampler.stop() if rank == 0 else None
-    args.msm_sharded = None
-    if comm is not None and not args.no_msm:
-        del dense, vals, idx
-        torch.cuda.empty_cache()
-        args.msm_sharded = msm_leg_sharded(ctx, comm, rank, world, timed)
-    if comm is not None:
-        barrier()
-        comm.close()
-        dist.destroy_process_group()
-    return ctx, rank, world, ms_per_step, value, launches, prof, e2e, clocks
-
-
-def msm_leg(ctx, n=24, steps=5):
-    """Second half of the metric: KZH2 commit of 2^24 int8 evaluations on a 2^12 x 2^12 split
-    (BASELINE.json config 3), points/s = 2 * 2^24 / t, with the integer-pipe fraction."""
-    import numpy as np
-    import torch
-
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    from zkes_b200 import DenseMLPoly, curve, kzh
-    from zkes_b200._lib import check, lib
-    from zkes_b200.field import from_mont_array
-
-    x_log, y_log = n // 2, n - n // 2
-
-    def uniform(stream, count):
-        t = torch.empty((count, 4), dtype=torch.int64, device="cuda")
-        torch.cuda.synchronize()
-        check(lib.zk_gen_uniform_fr(ctx.handle, 2, stream, 0, count, t.data_ptr()), "zk_gen_uniform_fr")
-        return from_mont_array(t.cpu().numpy().view(np.uint64))
-
-    tau_x, tau_y, alpha = uniform(1, 1 << x_log), uniform(2, 1 << y_log), uniform(3, 1)[0]
-    # g = 2 * (1, 2) on y^2 = x^3 + 3, in affine form
-    g = (1368015179489954701390400359078579693043519447331113978918064868415326638035,
-         9918110051302171585080402603319702774565515993150576347155970296011118125764)
-    t0 = time.perf_counter()
-    srs = kzh.KZHSRS.setup(ctx, 2, n, g, tau_x, tau_y, alpha=alpha)
-    setup_s = time.perf_counter() - t0
-    f = torch.empty((1 << n, 4), dtype=torch.int64, device="cuda")
-    torch.cuda.synchronize()
-    check(lib.zk_gen_small_fr(ctx.handle, 2, 7, 0, 1 << n, 8, f.data_ptr()), "zk_gen_small_fr")
-    poly = DenseMLPoly(n, device_ptr=f.data_ptr())
-    stream = torch.cuda.ExternalStream(lib.zk_stream(ctx.handle))
-    kzh.commit(ctx, srs, poly)  # warm-up (allocates scratch)
-    kzh.commit(ctx, srs, poly)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(steps):
-        kzh.commit(ctx, srs, poly)
-    e1.record(stream)
-    e1.synchronize()
-    ms = e0.elapsed_time(e1) / steps
-    stats = curve.last_stats(ctx)
-    ms_imad, ops = ctypes.c_float(), ctypes.c_double()
-    check(lib.zk_microbench(ctx.handle, 0, 148 * 8, 256, 4000, ctypes.byref(ms_imad), ctypes.byref(ops)), "zk_microbench")
-    imad_peak = ops.value / (ms_imad.value * 1e-3)
-    pairs = 2.0 * (1 << n)
-    mac32 = pairs * (255.0 / 256.0) * 1360.0  # one mixed addition (10 products of 136) per non-zero digit
-    srs.close()
-    return {"metric": "kzh2_commit_msm_points_per_s", "value": pairs / (ms * 1e-3), "unit": "points/s", "ms_per_commit": ms,
-            "config": f"KZH2 commit, 2^{n} int8 evaluations, 2^{x_log} x 2^{y_log} split, seed 2 (C over 2^{n} points + 2^{x_log} rows of 2^{y_log})",
-            "srs_setup_s": setup_s, "window_bits_last_msm": stats["window_bits"],
-            "integer_roofline": {"bound": "imad", "achieved_mac32_per_s": mac32 / (ms * 1e-3), "peak_mac32_per_s": imad_peak,
-                                 "frac": mac32 / (ms * 1e-3) / imad_peak,
-                                 "note": "algorithmic 32x32+64 multiply-adds (1360 per mixed addition) over the measured "
-                                         "32-bit multiply-add rate of this GPU (zk_microbench kind 0)"}}
-
-
-def msm_leg_sharded(ctx, comm, rank, world, timed):
-    """The MSM half of the metric on N GPUs, weak scaling: KZH2 commit of 2^(24 + log2 N) int8 evaluations,
-    every rank holding the 2^24 evaluations (and SRS points) of its x-rows.  C is a partial MSM per rank plus
-    one exchange of the partial points; the d_x rows are local and gathered.  points/s = 2 * 2^n / t."""
-    import numpy as np
-    import torch
-
-    from zkes_b200 import dist as zd
-    from zkes_b200._lib import ZK_MEM_DEVICE, check, lib
-    from zkes_b200.field import from_mont_array
-
-    lg = world.bit_length() - 1
-    n = 24 + lg
-    x_log, y_log = n // 2, n - n // 2
-
-    def uniform(stream, count):
-        t = torch.empty((count, 4), dtype=torch.int64, device="cuda")
-        torch.cuda.synchronize()
-        check(lib.zk_gen_uniform_fr(ctx.handle, 2, stream, 0, count, t.data_ptr()), "zk_gen_uniform_fr")
-        return from_mont_array(t.cpu().numpy().view(np.uint64))
-
-    tau_x, tau_y, alpha = uniform(1, 1 << x_log), uniform(2, 1 << y_log), uniform(3, 1)[0]
-    g = (1368015179489954701390400359078579693043519447331113978918064868415326638035,
-         9918110051302171585080402603319702774565515993150576347155970296011118125764)
-    srs = zd.sharded_kzh_setup(ctx, comm, 2, n, g, tau_x, tau_y, alpha=alpha)
-    local = (1 << n) // world
-    f = torch.empty((local, 4), dtype=torch.int64, device="cuda")
-    torch.cuda.synchronize()
-    check(lib.zk_gen_small_fr(ctx.handle, 2, 7, rank * local, local, 8, f.data_ptr()), "zk_gen_small_fr")
-    c = np.zeros((1, 8), dtype=np.uint64)
-    dx = np.zeros((1 << x_log, 12), dtype=np.uint64)
-    vp = ctypes.c_void_p
-
-    def step():
-        check(lib.zk_kzh_commit_sharded(ctx.handle, comm.handle, srs.handle, vp(f.data_ptr()), ZK_MEM_DEVICE,
-                                        vp(c.ctypes.data), vp(dx.ctypes.data)), "zk_kzh_commit_sharded")
-
-    steps = 5
-    ms = timed(step, steps, 2) / steps
-    srs.close()
-    pairs = 2.0 * (1 << n)
-    return {"metric": "kzh2_commit_msm_points_per_s", "value": pairs / (ms * 1e-3), "unit": "points/s", "ms_per_commit": ms,
-            "n_gpus": world, "scaling": "weak",
-            "config": f"KZH2 commit, 2^{n} int8 evaluations, 2^{x_log} x 2^{y_log} split, seed 2, x-rows sharded over "
-                      f"{world} GPUs (2^24 evaluations and SRS points per GPU)"}
 
 
 def measured_peak_gbs():
@@ -463,6 +158,791 @@ def measured_peak_gbs():
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json, burst copy)"
     except (OSError, KeyError, ValueError):
         return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+# ----------------------------------------------------------------------------- CPU arm (oracle)
+def load_oracle():
+    """The CPU restatement of the reference (test infrastructure): only the CPU-baseline legs and the reference arm
+    of this file call it, never the measured GPU path."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import coracle
+
+    coracle.set_threads(host_threads())
+    return coracle
+
+
+def cpu_sparse_dense(coracle, num_var, idx, vals, dense, steps, warmup):
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        coracle.sparse_dense_prove_mont(b"sumcheck_bench", num_var, idx, vals, dense)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    return sum(times) / len(times)
+
+
+def reference_arm(args):
+    """`--impl reference`: the reference's CPU algorithm (restated in oracle/, kind "port") on the workload the GPU
+    arm runs at one GPU, on the same bytes: the host-side generators of the oracle produce the streams that the
+    device generators produce.  The CPU prover is the dense LinearSumcheckProver on [a.to_dense(), b], which is how
+    the output of the sparse x dense prover is defined.  Rank 0 only; the other ranks exit without work."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import numpy as np
+
+    from zkes_b200 import synth
+
+    coracle = load_oracle()
+    n, k = args.num_var, args.nnz_log
+    dense = coracle.gen_uniform_fr_mont(SEED, 0, 0, 1 << n)
+    vals = coracle.gen_small_fr_mont(SEED, 2, 0, 1 << k, 8)
+    idx = synth.sparse_indices(SEED, n, 1 << k)
+    warm = min(args.warmup, 1)
+    steps = args.steps
+    t0 = time.perf_counter()
+    coracle.sparse_dense_prove_mont(b"sumcheck_bench", n, idx, vals, dense)
+    first = time.perf_counter() - t0  # the warm-up step (first touch of the tables) when warm == 1, else step 1
+    capped = None
+    if first * steps > 240.0:  # keep the whole run within a few minutes
+        steps = max(1, int(240.0 / first))
+        capped = f"steps capped at {steps} (one prove takes {first:.1f} s on this host)"
+    if warm:
+        sec = cpu_sparse_dense(coracle, n, idx, vals, dense, steps, 0)
+    elif steps > 1:
+        sec = (first + cpu_sparse_dense(coracle, n, idx, vals, dense, steps - 1, 0) * (steps - 1)) / steps
+    else:
+        sec = first
+    evals = (1 << n) + (1 << k)
+    value = evals / sec
+    sample = (f"per step: one whole prove of the workload (num_var={n}, 2^{k} non-zeros, the same input bytes as the GPU arm), "
+              f"{sec:.2f} s each; CPU restatement of the reference prover, not arkworks" + (f"; {capped}" if capped else ""))
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warm, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u256 (BN254 Fr, Montgomery)", "data": "synthetic",
+        "config": workload_config(n, k, 1),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": host_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ----------------------------------------------------------------------------- GPU helpers
+class Env:
+    """What every leg needs: the library context, the ranks, a timer over the context's stream."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+
+        from zkes_b200 import Context
+        from zkes_b200._lib import lib
+
+        self.args = args
+        self.torch, self.dist, self.lib = torch, dist, lib
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if self.world != args.gpus:
+            raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={self.world}: launch with torch.distributed.run")
+        torch.cuda.set_device(self.local_rank)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+        self.ctx = Context(self.local_rank)
+        self.comm = None
+        self.exchange = "nccl"
+        if self.world > 1:
+            from zkes_b200._lib import ZK_OPT_PEER_EXCHANGE
+            from zkes_b200.dist import Comm
+            self.comm = Comm(self.ctx, self.rank, self.world)
+            if args.peer_exchange is not None:
+                self.ctx.set_option(ZK_OPT_PEER_EXCHANGE, args.peer_exchange)
+            self.exchange = "peer memory" if self.comm.peer_exchange and args.peer_exchange != 0 else "nccl"
+        if args.device_tail is not None:
+            from zkes_b200._lib import ZK_OPT_DEVICE_TAIL
+            self.ctx.set_option(ZK_OPT_DEVICE_TAIL, args.device_tail)
+        self.stream = torch.cuda.ExternalStream(lib.zk_stream(self.ctx.handle))
+        self.logw = self.world.bit_length() - 1
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+        self.ctx.sync()
+
+    def timed(self, fn, steps, warmup):
+        """Milliseconds for `steps` calls of fn on the context's stream (CUDA events), max over the ranks."""
+        torch = self.torch
+        for _ in range(warmup):
+            fn()
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(self.stream)
+        for _ in range(steps):
+            fn()
+        e1.record(self.stream)
+        e1.synchronize()
+        self.barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if self.world > 1:
+            self.dist.all_reduce(ms, op=self.dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    def tensor(self, count):
+        t = self.torch.empty((count, 4), dtype=self.torch.int64, device="cuda")
+        self.torch.cuda.synchronize()
+        return t
+
+    def uniform(self, seed, stream, start, count):
+        from zkes_b200._lib import check
+        t = self.tensor(count)
+        check(self.lib.zk_gen_uniform_fr(self.ctx.handle, seed, stream, start, count, t.data_ptr()), "zk_gen_uniform_fr")
+        return t
+
+    def small(self, seed, stream, start, count, bits=8):
+        from zkes_b200._lib import check
+        t = self.tensor(count)
+        check(self.lib.zk_gen_small_fr(self.ctx.handle, seed, stream, start, count, bits, t.data_ptr()), "zk_gen_small_fr")
+        return t
+
+    def host_ints(self, t):
+        import numpy as np
+        from zkes_b200.field import from_mont_array
+        return from_mont_array(t.cpu().numpy().view(np.uint64))
+
+    def free(self):
+        self.torch.cuda.synchronize()
+        self.torch.cuda.empty_cache()
+
+    def imad_peaks(self):
+        """The integer roofline's denominators, measured on this GPU: the 32-bit multiply-add rate, the rate of wide
+        multiply-adds inside carry chains (what big-integer arithmetic issues), and Fq Montgomery products."""
+        from zkes_b200._lib import check
+        out = {}
+        for name, kind in (("imad32_per_s", 0), ("chained_wide_mad_per_s", 4), ("fq_products_per_s", 3)):
+            ms, ops = ctypes.c_float(), ctypes.c_double()
+            check(self.lib.zk_microbench(self.ctx.handle, kind, 148 * 8, 256, 4000, ctypes.byref(ms), ctypes.byref(ops)),
+                  "zk_microbench")
+            out[name] = ops.value / (ms.value * 1e-3)
+        return out
+
+
+class SparseDenseInstance:
+    """One sparse x dense instance of `total_var` variables cut over the ranks (each owns 2^(total_var - log2 N)
+    consecutive entries of the dense table and the sparse entries that fall there)."""
+
+    def __init__(self, env: Env, total_var: int, nnz_log_per_rank: int, world: int = None, rank: int = None):
+        import numpy as np
+
+        from zkes_b200 import synth
+
+        self.env = env
+        self.world = env.world if world is None else world
+        self.rank = env.rank if rank is None else rank
+        self.logw = self.world.bit_length() - 1
+        self.total_var = total_var
+        self.n = total_var - self.logw
+        self.k = nnz_log_per_rank
+        size = 1 << self.n
+        self.dense = env.uniform(SEED, 0, self.rank * size, size)
+        self.vals = env.small(SEED, 2 + 4 * self.rank, 0, 1 << self.k)
+        self.idx_host = synth.sparse_indices(SEED, self.n, 1 << self.k, stream=synth.SPARSE_INDEX_STREAM + 4 * self.rank)
+        self.idx = env.torch.from_numpy(self.idx_host.view(np.int64)).cuda()
+        env.torch.cuda.synchronize()
+        self.msgs = np.zeros((total_var, 3, 4), dtype=np.uint64)
+        self.chal = np.zeros((total_var, 4), dtype=np.uint64)
+        self.fin_t = np.zeros((2, 4), dtype=np.uint64)
+        self.fin = np.zeros((1, 4), dtype=np.uint64)
+
+    def evals(self):
+        return ((1 << self.n) + (1 << self.k)) * self.world
+
+    def prove(self, idx_p=None, val_p=None, dense_p=None, mem=None):
+        from zkes_b200._lib import ZK_MEM_DEVICE, check
+        lib, env = self.env.lib, self.env
+        idx_p = self.idx.data_ptr() if idx_p is None else idx_p
+        val_p = self.vals.data_ptr() if val_p is None else val_p
+        dense_p = self.dense.data_ptr() if dense_p is None else dense_p
+        mem = ZK_MEM_DEVICE if mem is None else mem
+        tr = lib.zk_transcript_new(b"sumcheck_bench", 14)
+        lib.zk_transcript_append_u64(tr, b"num_var", 7, self.total_var)
+        lib.zk_transcript_append_u64(tr, b"num_poly", 8, 2)
+        out = (vp(self.msgs.ctypes.data), vp(self.chal.ctypes.data), vp(self.fin_t.ctypes.data), vp(self.fin.ctypes.data))
+        if self.world == 1:
+            rc = lib.zk_sumcheck_sparse_dense_prove(env.ctx.handle, self.n, 1 << self.k, vp(idx_p), vp(val_p), vp(dense_p),
+                                                    mem, None, None, tr, *out)
+        else:
+            rc = lib.zk_sumcheck_sparse_dense_prove_sharded(env.ctx.handle, env.comm.handle, self.total_var, 1 << self.k,
+                                                            vp(idx_p), vp(val_p), vp(dense_p), mem, None, None, tr, *out)
+        lib.zk_transcript_free(tr)
+        check(rc, "zk_sumcheck_sparse_dense_prove")
+
+    def verify(self):
+        """Checks the proof the last prove() left: (1) the restated SumcheckVerifier accepts it (verifier.rs:27-69)
+        with the claimed sum s_0(0) + s_0(1) and re-derives the same challenges; (2) its final value is a(r) b(r)
+        with both factors evaluated independently of the prover (zk_mle_eval: eq table + dot product over the
+        original tables, combined over the ranks' chunks with the weights of the top variables); (3) all ranks
+        hold identical outputs."""
+        import numpy as np
+
+        from zkes_b200._lib import ZK_MEM_DEVICE, check
+        from zkes_b200.field import from_mont_array, to_mont_array
+        env, lib, torch = self.env, self.env.lib, self.env.torch
+        n_all = self.total_var
+        msgs = from_mont_array(self.msgs.reshape(-1, 4))
+        chal = from_mont_array(self.chal)
+        fin_t, fin = from_mont_array(self.fin_t), from_mont_array(self.fin)[0]
+        ok = True
+        tr = lib.zk_transcript_new(b"sumcheck_bench", 14)
+        lib.zk_transcript_append_u64(tr, b"num_var", 7, n_all)
+        lib.zk_transcript_append_u64(tr, b"num_poly", 8, 2)
+        claim = to_mont_array([(msgs[0] + msgs[1]) % R_MOD])
+        ch2 = np.zeros((n_all, 4), dtype=np.uint64)
+        last = np.zeros((1, 4), dtype=np.uint64)
+        acc, failed = ctypes.c_int(0), ctypes.c_uint32(0)
+        check(lib.zk_sumcheck_verify(tr, n_all, 2, vp(self.msgs.ctypes.data), n_all, 3, vp(claim.ctypes.data),
+                                     vp(ch2.ctypes.data), vp(last.ctypes.data), ctypes.byref(acc), ctypes.byref(failed)),
+              "zk_sumcheck_verify")
+        lib.zk_transcript_free(tr)
+        ok = ok and acc.value == 1 and from_mont_array(ch2) == chal and from_mont_array(last)[0] == fin
+        # independent evaluation of both tables at the challenge point
+        low = to_mont_array(chal[:self.n]) if self.n else np.zeros((1, 4), dtype=np.uint64)
+        a_dense = torch.zeros((1 << self.n, 4), dtype=torch.int64, device="cuda")
+        a_dense[self.idx] = self.vals
+        torch.cuda.synchronize()
+        part = []
+        for t in (a_dense, self.dense):
+            out = np.zeros((1, 4), dtype=np.uint64)
+            check(lib.zk_mle_eval(env.ctx.handle, self.n, vp(t.data_ptr()), ZK_MEM_DEVICE, vp(low.ctypes.data),
+                                  vp(out.ctypes.data)), "zk_mle_eval")
+            part.append(from_mont_array(out)[0])
+        del a_dense
+        if self.world > 1 and self.world == env.world:
+            gathered = [None] * self.world
+            env.dist.all_gather_object(gathered, part)
+        else:
+            gathered = [part]
+        top = chal[self.n:]
+        a_r = b_r = 0
+        for r, (pa, pb) in enumerate(gathered):
+            w = 1
+            for j, rj in enumerate(top):
+                w = w * (rj if (r >> j) & 1 else (1 - rj)) % R_MOD
+            a_r = (a_r + w * pa) % R_MOD
+            b_r = (b_r + w * pb) % R_MOD
+        ok = ok and fin_t == [a_r, b_r] and fin == a_r * b_r % R_MOD
+        if self.world > 1 and self.world == env.world:
+            digest = hashlib.sha256(self.msgs.tobytes() + self.chal.tobytes() + self.fin_t.tobytes() + self.fin.tobytes()).hexdigest()
+            all_d = [None] * self.world
+            env.dist.all_gather_object(all_d, (digest, bool(ok)))
+            ok = all(d == all_d[0][0] and o for d, o in all_d)
+        return bool(ok)
+
+    def release(self):
+        del self.dense, self.vals, self.idx
+        self.env.free()
+
+
+# ----------------------------------------------------------------------------- headline leg
+def headline(env: Env):
+    """Weak scaling: every rank owns a 2^num_var chunk of one instance of num_var + log2 N variables."""
+    import torch
+
+    from zkes_b200._lib import ZK_MEM_HOST, check
+    args, lib, ctx = env.args, env.lib, env.ctx
+    n, k = args.num_var, args.nnz_log
+    inst = SparseDenseInstance(env, n + env.logw, k)
+    sampler = ClockSampler(env.local_rank)
+    if env.rank == 0:
+        sampler.start()
+    for _ in range(args.warmup):
+        inst.prove()
+    if args.trace:
+        buf = (ctypes.c_double * 4096)()
+        cnt = ctypes.c_uint32()
+        lib.zk_round_times(ctx.handle, buf, 4096, ctypes.byref(cnt))  # clears the warm-up's record
+        env.barrier()
+        t0 = time.perf_counter()
+        inst.prove()
+        t1 = time.perf_counter()
+        lib.zk_round_times(ctx.handle, buf, 4096, ctypes.byref(cnt))
+        if env.rank == 0:
+            ts = [buf[i] for i in range(cnt.value)]
+            sys.stderr.write("trace: prove %.1f us; host-stepped rounds at (us): %s\n" % (
+                (t1 - t0) * 1e6, " ".join("%.0f" % t for t in ts)))
+            sys.stderr.write("trace: per-round gaps (us): %s\n" % " ".join("%.0f" % (b - a) for a, b in zip(ts, ts[1:])))
+    l0 = ctx.launch_count
+    total_ms = env.timed(inst.prove, args.steps, 0)
+    launches = ctx.launch_count - l0
+    verified = inst.verify()
+    # the same K steps again with CUDA events around every kernel of the path (roofline figures)
+    check(lib.zk_profile_enable(ctx.handle, 1), "zk_profile_enable")
+    profiled_ms = env.timed(inst.prove, args.steps, 0)
+    prof = {"_profiled_ms_per_step": profiled_ms / args.steps}
+    for kind, name in enumerate(["round", "fold", "sparse_msg", "sparse_fold"]):
+        nl, ms, by = ctypes.c_uint64(), ctypes.c_double(), ctypes.c_double()
+        check(lib.zk_profile_get(ctx.handle, kind, ctypes.byref(nl), ctypes.byref(ms), ctypes.byref(by)), "zk_profile_get")
+        prof[name] = {"launches": nl.value, "ms": ms.value, "bytes": by.value}
+    check(lib.zk_profile_enable(ctx.handle, 0), "zk_profile_enable")
+    ms_per_step = total_ms / args.steps
+    evals = inst.evals()
+    value = evals / (ms_per_step * 1e-3)
+
+    e2e = None
+    if not args.no_e2e:
+        h_dense = torch.empty(inst.dense.shape, dtype=inst.dense.dtype, pin_memory=True).copy_(inst.dense)
+        h_vals = torch.empty(inst.vals.shape, dtype=inst.vals.dtype, pin_memory=True).copy_(inst.vals)
+        h_idx = torch.empty(inst.idx.shape, dtype=inst.idx.dtype, pin_memory=True).copy_(inst.idx)
+        torch.cuda.synchronize()
+
+        def host_step():
+            inst.prove(h_idx.data_ptr(), h_vals.data_ptr(), h_dense.data_ptr(), ZK_MEM_HOST)
+
+        e2e_steps = max(1, min(args.steps, 5))
+        e2e_ms = env.timed(host_step, e2e_steps, 1) / e2e_steps
+        h2d = h_dense.numel() * 8 + h_vals.numel() * 8 + h_idx.numel() * 8
+        d2h = ((n + env.logw) * 3 + 3) * 32 + 4
+        e2e = {"value": evals / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": e2e_ms, "steps": e2e_steps,
+               "note": "the host->device copy of the 2 GiB table is the step: PCIe rate, nothing of the prove can start "
+                       "before the table is resident"}
+        verified = verified and inst.verify()
+        del h_dense, h_vals, h_idx
+    clocks = sampler.stop() if env.rank == 0 else None
+
+    cpu = None
+    if env.world == 1 and env.rank == 0 and not args.no_cpu_baseline:
+        import numpy as np
+        coracle = load_oracle()
+        dense_h = inst.dense.cpu().numpy().view(np.uint64)
+        vals_h = inst.vals.cpu().numpy().view(np.uint64)
+        sec = cpu_sparse_dense(coracle, n, inst.idx_host, vals_h, dense_h, 2, 0)
+        cpu = {"value": ((1 << n) + (1 << k)) / sec, "unit": UNIT, "cores": host_threads(), "kind": "port",
+               "sample": f"2 whole proves of this workload on the same input bytes, {sec:.2f} s each; CPU restatement of "
+                         "the reference prover (dense prover on the densified table), not arkworks"}
+        del dense_h, vals_h
+    inst.release()
+    return {"ms_per_step": ms_per_step, "value": value, "launches": launches, "prof": prof, "e2e": e2e, "clocks": clocks,
+            "cpu": cpu, "verified": verified}
+
+
+# ----------------------------------------------------------------------------- dense prover, num_var = 20
+def linear_leg(env: Env, n=20, ell=2, steps=20):
+    """Dense LinearSumcheckProver on two tables of 2^20 uniform elements, seed 0 (the reference's
+    benches/sumcheck_prover.rs shape): Fr-evals/s = ell * 2^n / t, and the HBM fraction over the algorithmic bytes
+    32 ell (2^n + 1.5 (2^(n+1) - 2))."""
+    import numpy as np
+
+    from zkes_b200._lib import ZK_MEM_DEVICE, check
+    from zkes_b200.field import from_mont_array, to_mont_array
+    lib, ctx = env.lib, env.ctx
+    tables = [env.uniform(0, i, 0, 1 << n) for i in range(ell)]
+    ptrs = (vp * ell)(*[vp(t.data_ptr()) for t in tables])
+    msgs = np.zeros((n, ell + 1, 4), dtype=np.uint64)
+    chal = np.zeros((n, 4), dtype=np.uint64)
+    fin_t = np.zeros((ell, 4), dtype=np.uint64)
+    fin = np.zeros((1, 4), dtype=np.uint64)
+
+    def new_tr():
+        tr = lib.zk_transcript_new(b"sumcheck_bench", 14)
+        lib.zk_transcript_append_u64(tr, b"num_var", 7, n)
+        lib.zk_transcript_append_u64(tr, b"num_poly", 8, ell)
+        return tr
+
+    def step():
+        tr = new_tr()
+        rc = lib.zk_sumcheck_linear_prove(ctx.handle, n, ell, ptrs, ZK_MEM_DEVICE, None, None, tr, vp(msgs.ctypes.data),
+                                          vp(chal.ctypes.data), vp(fin_t.ctypes.data), vp(fin.ctypes.data))
+        lib.zk_transcript_free(tr)
+        check(rc, "zk_sumcheck_linear_prove")
+
+    ms = env.timed(step, steps, 3) / steps
+    # verify: chain accepted, final value = product of the tables' independent evaluations at the challenges
+    m = from_mont_array(msgs.reshape(-1, 4))
+    claim = to_mont_array([(m[0] + m[1]) % R_MOD])
+    acc, last = ctypes.c_int(0), np.zeros((1, 4), dtype=np.uint64)
+    tr = new_tr()
+    check(lib.zk_sumcheck_verify(tr, n, ell, vp(msgs.ctypes.data), n, ell + 1, vp(claim.ctypes.data), None,
+                                 vp(last.ctypes.data), ctypes.byref(acc), None), "zk_sumcheck_verify")
+    lib.zk_transcript_free(tr)
+    prod = 1
+    vals = []
+    for t in tables:
+        out = np.zeros((1, 4), dtype=np.uint64)
+        check(lib.zk_mle_eval(ctx.handle, n, vp(t.data_ptr()), ZK_MEM_DEVICE, vp(chal.ctypes.data), vp(out.ctypes.data)), "zk_mle_eval")
+        vals.append(from_mont_array(out)[0])
+        prod = prod * vals[-1] % R_MOD
+    f = from_mont_array(fin)[0]
+    verified = acc.value == 1 and from_mont_array(last)[0] == f and f == prod and from_mont_array(fin_t) == vals
+    peak, src = measured_peak_gbs()
+    algo_bytes = 32.0 * ell * ((1 << n) + 1.5 * ((1 << (n + 1)) - 2))
+    cpu = None
+    if env.rank == 0 and not env.args.no_cpu_baseline:
+        coracle = load_oracle()
+        host_tabs = [t.cpu().numpy().view(np.uint64) for t in tables]
+        t0 = time.perf_counter()
+        reps = 3
+        for _ in range(reps):
+            coracle.linear_prove_mont(b"sumcheck_bench", n, host_tabs)
+        sec = (time.perf_counter() - t0) / reps
+        cpu = {"value": ell * (1 << n) / sec, "unit": UNIT, "cores": host_threads(), "kind": "port",
+               "sample": f"{reps} whole proves of this workload on the same input bytes, {sec * 1e3:.0f} ms each"}
+    del tables
+    env.free()
+    return {"metric": METRIC, "value": ell * (1 << n) / (ms * 1e-3), "unit": UNIT, "ms_per_prove": ms,
+            "config": f"dense LinearSumcheckProver, num_var={n}, {ell} tables of 2^{n} uniform elements, seed 0, tables resident",
+            "verified": bool(verified), "us_per_round": ms * 1e3 / n,
+            "roofline": {"bound": "hbm", "achieved": algo_bytes / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": algo_bytes / (ms * 1e-3) / 1e9 / peak, "peak_source": src, "algorithmic_bytes": algo_bytes,
+                         "note": f"{n} dependent rounds: at full HBM rate the data would take "
+                                 f"{algo_bytes / (peak * 1e9) * 1e6:.0f} us, so the per-round latency sets the time"},
+            "cpu_baseline": cpu}
+
+
+# ----------------------------------------------------------------------------- KZH legs
+def trapdoors(env, seed, sizes):
+    return [env.host_ints(env.uniform(seed, 1 + i, 0, s)) for i, s in enumerate(sizes)]
+
+
+def msm_point(env, scalar):
+    """scalar * g through the library (a one-point MSM), normalised to affine integers."""
+    import numpy as np
+
+    from zkes_b200 import curve
+    return curve.msm(env.ctx, curve.affine_to_array([(G2X, G2Y)]), [scalar])
+
+
+def contract_high(env, n, f_ptr, k, weights):
+    """out[lo] = sum_hi weights[hi] f[hi * 2^(n-k) + lo] on the device (the column-sum kernel with caller weights)."""
+    import numpy as np
+
+    from zkes_b200._lib import ZK_MEM_DEVICE, ZK_MEM_HOST, check
+    from zkes_b200.field import from_mont_array, to_mont_array
+    w = to_mont_array(weights)
+    out = np.zeros((1 << (n - k), 4), dtype=np.uint64)
+    check(env.lib.zk_weighted_fold_from_right(env.ctx.handle, n, vp(f_ptr), ZK_MEM_DEVICE, k, vp(w.ctypes.data), ZK_MEM_HOST,
+                                              vp(out.ctypes.data), ZK_MEM_HOST), "zk_weighted_fold_from_right")
+    return from_mont_array(out)
+
+
+def msm_work(env, reset=True):
+    calls, entries, buckets = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
+    env.lib.zk_msm_work(env.ctx.handle, ctypes.byref(calls), ctypes.byref(entries), ctypes.byref(buckets), 1 if reset else 0)
+    return calls.value, entries.value, buckets.value
+
+
+def integer_roofline(entries, buckets, ms, peaks):
+    """Algorithmic multiply-adds of an MSM: one mixed addition (10 products of 136 multiply-adds) per non-zero digit
+    and two full additions (14 products each) per bucket in the reduction."""
+    mac32 = entries * 1360.0 + buckets * 2 * 14 * 136.0
+    per_s = mac32 / (ms * 1e-3)
+    return {"bound": "imad", "achieved_mac32_per_s": per_s, "peak_mac32_per_s": peaks["imad32_per_s"],
+            "frac": per_s / peaks["imad32_per_s"],
+            "frac_of_chained_ceiling": per_s / peaks["chained_wide_mad_per_s"],
+            "digit_entries": entries, "buckets": buckets,
+            "note": "algorithmic 32x32+64 multiply-adds (1360 per bucket addition, 3808 per reduced bucket) over the measured "
+                    "32-bit multiply-add rate of this GPU; the second fraction is over the measured rate of wide multiply-adds "
+                    "inside carry chains, the form a 256-bit product issues"}
+
+
+def cpu_msm_baseline(env, srs, f_dev, n_c, rows, row_len, label):
+    """The C++ restatement of the bucket-method MSM on the host threads, on a bounded sample of the commitment: the C
+    part over the first n_c points and `rows` rows of d_x, on the same bases and scalars."""
+    import numpy as np
+
+    from zkes_b200._lib import check
+    coracle = load_oracle()
+    bases = np.zeros((n_c, 8), dtype=np.uint64)
+    check(env.lib.zk_kzh_srs_read(env.ctx.handle, srs.handle, 0, 0, n_c, vp(bases.ctypes.data)), "zk_kzh_srs_read")
+    mid = np.zeros((row_len, 8), dtype=np.uint64)
+    check(env.lib.zk_kzh_srs_read(env.ctx.handle, srs.handle, 1, 0, row_len, vp(mid.ctypes.data)), "zk_kzh_srs_read")
+    sc = f_dev[:max(n_c, rows * row_len)].cpu().numpy().view(np.uint64)
+    t0 = time.perf_counter()
+    coracle.g1_msm_mont(bases, sc[:n_c])
+    t_c = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    coracle.g1_msm_rows_mont(mid, sc[:rows * row_len], rows)
+    t_r = time.perf_counter() - t0
+    pairs = n_c + rows * row_len
+    return {"value": pairs / (t_c + t_r), "unit": "points/s", "cores": host_threads(), "kind": "port",
+            "sample": f"{label}: C over the first 2^{n_c.bit_length() - 1} points ({t_c:.2f} s) and {rows} rows of d_x "
+                      f"({t_r:.2f} s) of the same commitment; points/s is size-normalised (linear extrapolation); C++ "
+                      "restatement of the bucket method (negative weights are full-width scalars, as for arkworks), not arkworks"}
+
+
+def kzh2_leg(env: Env, n=24, steps=5):
+    """KZH2 commit (MSM points/s = 2 * 2^n / t) and open (fix_variables_from_right, GB/s) of 2^n int8 evaluations on
+    a 2^(n/2) x 2^(n - n/2) split, seed 2."""
+    import numpy as np
+
+    from zkes_b200 import DenseMLPoly, curve, kzh
+    from zkes_b200._lib import ZK_MEM_DEVICE, check
+    from zkes_b200.field import to_mont_array
+    x_log, y_log = n // 2, n - n // 2
+    tau_x, tau_y, (alpha,) = trapdoors(env, 2, [1 << x_log, 1 << y_log, 1])
+    t0 = time.perf_counter()
+    srs = kzh.KZHSRS.setup(env.ctx, 2, n, (G2X, G2Y), tau_x, tau_y, alpha=alpha)
+    setup_s = time.perf_counter() - t0
+    f = env.small(2, 7, 0, 1 << n)
+    poly = DenseMLPoly(n, device_ptr=f.data_ptr())
+    box = {}
+
+    def commit():
+        box["com"] = kzh.commit(env.ctx, srs, poly)
+
+    commit()
+    msm_work(env)
+    commit()
+    _, entries, buckets = msm_work(env)
+    ms = env.timed(commit, steps, 1) / steps
+    stats = curve.last_stats(env.ctx)
+    peaks = env.imad_peaks()
+    # trapdoor identity: C = (sum_x tau_x[x] sum_y tau_y[y] f[x, y]) g
+    gy = contract_high(env, n, f.data_ptr(), x_log, tau_x)
+    s = sum(a * b for a, b in zip(gy, tau_y)) % R_MOD
+    verified = box["com"].c == msm_point(env, s)
+    d_x = curve.jacobian_to_affine_py(box["com"].d_x_jac[:2])
+    for i in range(2):
+        row = env.host_ints(f[i << y_log:(i + 1) << y_log])
+        verified = verified and d_x[i] == msm_point(env, alpha * sum(a * b for a, b in zip(row, tau_y)) % R_MOD)
+    # open: f_star = fix_variables_from_right(poly, r_x)
+    pt_ints = env.host_ints(env.uniform(2, 9, 0, n))
+    pt = to_mont_array(pt_ints)
+    f_star = np.zeros((1 << y_log, 4), dtype=np.uint64)
+
+    def open_():
+        check(env.lib.zk_kzh2_open(env.ctx.handle, srs.handle, n, vp(f.data_ptr()), ZK_MEM_DEVICE, vp(pt.ctypes.data), n,
+                                   vp(f_star.ctypes.data)), "zk_kzh2_open")
+
+    open_ms = env.timed(open_, steps, 2) / steps
+    # f_star(r_y) must equal f(point), the latter by the independent LSB-fold path
+    from zkes_b200.field import from_mont_array
+    fs_poly = DenseMLPoly(y_log, mont=f_star)
+    whole = np.zeros((1, 4), dtype=np.uint64)
+    check(env.lib.zk_fold_lsb(env.ctx.handle, n, vp(f.data_ptr()), ZK_MEM_DEVICE, n, vp(pt.ctypes.data), vp(whole.ctypes.data), 0), "zk_fold_lsb")
+    open_ok = fs_poly.evaluate_at_point(env.ctx, pt_ints[:y_log]) == from_mont_array(whole)[0]
+    peak, src = measured_peak_gbs()
+    open_bytes = 32.0 * ((1 << n) + (1 << y_log))
+    cpu = None
+    if env.rank == 0 and not env.args.no_cpu_baseline:
+        cpu = cpu_msm_baseline(env, srs, f, min(1 << n, 1 << 21), min(1 << x_log, 128), 1 << y_log, "KZH2 commit")
+    srs.close()
+    del f
+    env.free()
+    pairs = 2.0 * (1 << n)
+    msm = {"metric": "kzh2_commit_msm_points_per_s", "value": pairs / (ms * 1e-3), "unit": "points/s", "ms_per_commit": ms,
+           "config": f"KZH2 commit, 2^{n} int8 evaluations, 2^{x_log} x 2^{y_log} split, seed 2 (C over 2^{n} points + 2^{x_log} rows of 2^{y_log})",
+           "srs_setup_s": setup_s, "window_bits_last_msm": stats["window_bits"], "verified": bool(verified),
+           "integer_roofline": integer_roofline(entries, buckets, ms, peaks), "cpu_baseline": cpu}
+    opn = {"metric": "kzh2_open_gb_per_s", "value": open_bytes / (open_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_open": open_ms,
+           "config": f"KZH2 open of the same polynomial: fix_variables_from_right binds the top {x_log} variables (2^{n} -> 2^{y_log}), "
+                     "table resident, eq table and result copy included",
+           "verified": bool(open_ok),
+           "roofline": {"bound": "hbm", "achieved": open_bytes / (open_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                        "frac": open_bytes / (open_ms * 1e-3) / 1e9 / peak, "peak_source": src, "algorithmic_bytes": open_bytes}}
+    return msm, opn
+
+
+def kzh3_mix(env, n, x_log, slab, count, start):
+    """Evaluations [start, start + count) of the KZH3 workload: x-slabs alternate between int16 fixed-point activations
+    round(N(0,1) 2^8) (even slabs) and full-width uniform elements (odd slabs), seed 3."""
+    from zkes_b200._lib import check
+    f = env.uniform(3, 7, start, count)
+    for x in range(start // slab, (start + count) // slab):
+        if x % 2 == 0:
+            lo = x * slab - start
+            check(env.lib.zk_gen_gauss_fr(env.ctx.handle, 3, 8, x * slab, slab, 8, f[lo:lo + slab].data_ptr()), "zk_gen_gauss_fr")
+    env.torch.cuda.synchronize()
+    return f
+
+
+def kzh3_leg(env: Env, n=28):
+    """KZH3 commit + open of 2^n evaluations on the (x, y, z) split of kzh3.rs:429-437.  At N > 1 the same instance
+    is cut by x-rows over the ranks (fixed total work: strong scaling)."""
+    import numpy as np
+
+    from zkes_b200 import DenseMLPoly, curve, kzh
+    from zkes_b200 import dist as zd
+    from zkes_b200._lib import ZK_MEM_DEVICE, check
+    from zkes_b200.field import to_mont_array
+    rem, third = n % 3, n // 3
+    x_log, y_log, z_log = (third + 1 if rem >= 1 else third), (third + 1 if rem == 2 else third), third
+    slab = 1 << (y_log + z_log)
+    tau_x, tau_y, tau_z = trapdoors(env, 3, [1 << x_log, 1 << y_log, 1 << z_log])
+    world, rank = env.world, env.rank
+    local = (1 << n) // world
+    t0 = time.perf_counter()
+    if world == 1:
+        srs = kzh.KZHSRS.setup(env.ctx, 3, n, (G2X, G2Y), tau_x, tau_y, tau_z=tau_z)
+    else:
+        srs = zd.sharded_kzh_setup(env.ctx, env.comm, 3, n, (G2X, G2Y), tau_x, tau_y, tau_z=tau_z)
+    env.ctx.sync()
+    setup_s = time.perf_counter() - t0
+    f = kzh3_mix(env, n, x_log, slab, local, rank * local)
+    c = np.zeros((1, 8), dtype=np.uint64)
+    dx = np.zeros((1 << x_log, 12), dtype=np.uint64)
+    lib = env.lib
+
+    def commit():
+        if world == 1:
+            check(lib.zk_kzh_commit(env.ctx.handle, srs.handle, n, vp(f.data_ptr()), ZK_MEM_DEVICE, vp(c.ctypes.data), vp(dx.ctypes.data)), "zk_kzh_commit")
+        else:
+            check(lib.zk_kzh_commit_sharded(env.ctx.handle, env.comm.handle, srs.handle, vp(f.data_ptr()), ZK_MEM_DEVICE,
+                                            vp(c.ctypes.data), vp(dx.ctypes.data)), "zk_kzh_commit_sharded")
+
+    commit()
+    msm_work(env)
+    commit_steps = 2
+    commit_ms = env.timed(commit, commit_steps, 0) / commit_steps
+    _, entries, buckets = msm_work(env)
+    entries //= commit_steps
+    buckets //= commit_steps
+    if world > 1:
+        tot = env.torch.tensor([entries, buckets], dtype=env.torch.int64, device="cuda")
+        env.dist.all_reduce(tot)
+        entries, buckets = int(tot[0].item()), int(tot[1].item())
+    pt_ints = env.host_ints(env.uniform(3, 9, 0, n))
+    pt = to_mont_array(pt_ints)
+    dy = np.zeros((1 << y_log, 12), dtype=np.uint64)
+    cy = np.zeros((1, 8), dtype=np.uint64)
+    fs = np.zeros((1 << z_log, 4), dtype=np.uint64)
+
+    def open_():
+        if world == 1:
+            check(lib.zk_kzh3_open(env.ctx.handle, srs.handle, n, vp(f.data_ptr()), ZK_MEM_DEVICE, vp(pt.ctypes.data), n,
+                                   vp(dx.ctypes.data), vp(dy.ctypes.data), vp(cy.ctypes.data), vp(fs.ctypes.data)), "zk_kzh3_open")
+        else:
+            check(lib.zk_kzh_open_sharded(env.ctx.handle, env.comm.handle, srs.handle, vp(f.data_ptr()), ZK_MEM_DEVICE,
+                                          vp(pt.ctypes.data), n, vp(dx.ctypes.data), vp(dy.ctypes.data), vp(cy.ctypes.data),
+                                          vp(fs.ctypes.data)), "zk_kzh_open_sharded")
+
+    msm_work(env)
+    open_steps = 3
+    open_ms = env.timed(open_, open_steps, 1) / open_steps
+    # ---- verification by identities (no CPU MSM is feasible at this size)
+    verified = None
+    if world == 1:
+        from zkes_b200.field import from_mont_array
+        gyz = contract_high(env, n, f.data_ptr(), x_log, tau_x)
+        tyz = [tau_y[i >> z_log] * tau_z[i & ((1 << z_log) - 1)] % R_MOD for i in range(slab)]
+        c_aff = curve.affine_from_array(c)[0]
+        verified = c_aff == msm_point(env, sum(a * b for a, b in zip(gyz, tyz)) % R_MOD)
+        d_x = curve.jacobian_to_affine_py(dx[:2])
+        for i in range(2):  # an activation slab and a full-width slab
+            row = env.host_ints(f[i * slab:(i + 1) * slab])
+            verified = verified and d_x[i] == msm_point(env, sum(a * b for a, b in zip(row, tyz)) % R_MOD)
+        # opening: f_star(r_z) = f(point) (independent LSB-fold path); MSM(h_z, f_star) = sum_i eq(r_y)[i] d_y[i] and
+        # c_y = sum_i eq(r_x)[i] d_x[i] through the library's own verifier checks
+        whole = np.zeros((1, 4), dtype=np.uint64)
+        check(lib.zk_fold_lsb(env.ctx.handle, n, vp(f.data_ptr()), ZK_MEM_DEVICE, n, vp(pt.ctypes.data), vp(whole.ctypes.data), 0), "zk_fold_lsb")
+        ok, failed = ctypes.c_int(0), ctypes.c_int(0)
+        check(lib.zk_kzh_verify_g1(env.ctx.handle, srs.handle, vp(pt.ctypes.data), n, vp(whole.ctypes.data), vp(dx.ctypes.data),
+                                   vp(dy.ctypes.data), vp(cy.ctypes.data), vp(fs.ctypes.data), ctypes.byref(ok), ctypes.byref(failed)),
+              "zk_kzh_verify_g1")
+        verified = bool(verified and ok.value == 1)
+    else:
+        digest = hashlib.sha256(c.tobytes() + dx.tobytes() + dy.tobytes() + cy.tobytes() + fs.tobytes()).hexdigest()
+        all_d = [None] * world
+        env.dist.all_gather_object(all_d, digest)
+        verified = all(d == all_d[0] for d in all_d)
+    peaks = env.imad_peaks()
+    cpu = None
+    if world == 1 and env.rank == 0 and not env.args.no_cpu_baseline:
+        cpu = cpu_msm_baseline(env, srs, f, min(1 << n, 1 << 19), 2, slab, "KZH3 commit")
+    srs.close()
+    del f
+    env.free()
+    pairs = 2.0 * (1 << n)
+    return {"metric": "kzh3_commit_msm_points_per_s", "value": pairs / (commit_ms * 1e-3), "unit": "points/s",
+            "ms_per_commit": commit_ms, "ms_per_open": open_ms, "srs_setup_s": setup_s, "n_gpus": world,
+            "scaling": "strong" if world > 1 else None,
+            "config": f"KZH3 commit + open, 2^{n} evaluations on a 2^{x_log} x 2^{y_log} x 2^{z_log} split, x-slabs alternating int16 "
+                      "activations round(N(0,1) 2^8) and full-width uniform elements, seed 3" +
+                      (f", x-rows cut over {world} GPUs" if world > 1 else ""),
+            "verified": verified, "integer_roofline": integer_roofline(entries, buckets, commit_ms * world, peaks),
+            "cpu_baseline": cpu}
+
+
+def msm_leg_sharded(env: Env):
+    """The MSM half of the metric on N GPUs, weak scaling: KZH2 commit of 2^(24 + log2 N) int8 evaluations,
+    every rank holding the 2^24 evaluations (and SRS points) of its x-rows.  C is a partial MSM per rank plus
+    one exchange of the partial points; the d_x rows are local and gathered.  points/s = 2 * 2^n / t."""
+    import numpy as np
+
+    from zkes_b200 import dist as zd
+    from zkes_b200._lib import ZK_MEM_DEVICE, check
+    world, rank = env.world, env.rank
+    n = 24 + env.logw
+    x_log, y_log = n // 2, n - n // 2
+    tau_x, tau_y, (alpha,) = trapdoors(env, 2, [1 << x_log, 1 << y_log, 1])
+    srs = zd.sharded_kzh_setup(env.ctx, env.comm, 2, n, (G2X, G2Y), tau_x, tau_y, alpha=alpha)
+    local = (1 << n) // world
+    f = env.small(2, 7, rank * local, local)
+    c = np.zeros((1, 8), dtype=np.uint64)
+    dx = np.zeros((1 << x_log, 12), dtype=np.uint64)
+
+    def step():
+        check(env.lib.zk_kzh_commit_sharded(env.ctx.handle, env.comm.handle, srs.handle, vp(f.data_ptr()), ZK_MEM_DEVICE,
+                                            vp(c.ctypes.data), vp(dx.ctypes.data)), "zk_kzh_commit_sharded")
+
+    steps = 5
+    ms = env.timed(step, steps, 2) / steps
+    digest = hashlib.sha256(c.tobytes() + dx.tobytes()).hexdigest()
+    all_d = [None] * world
+    env.dist.all_gather_object(all_d, digest)
+    srs.close()
+    del f
+    env.free()
+    pairs = 2.0 * (1 << n)
+    return {"metric": "kzh2_commit_msm_points_per_s", "value": pairs / (ms * 1e-3), "unit": "points/s", "ms_per_commit": ms,
+            "n_gpus": world, "scaling": "weak", "verified": all(d == all_d[0] for d in all_d),
+            "config": f"KZH2 commit, 2^{n} int8 evaluations, 2^{x_log} x 2^{y_log} split, seed 2, x-rows sharded over "
+                      f"{world} GPUs (2^24 evaluations and SRS points per GPU)"}
+
+
+# ----------------------------------------------------------------------------- strong scaling
+def strong_leg(env: Env, steps=5):
+    """One sparse x dense instance of num_var = 28 (2^28 dense elements = 8 GiB, 2^22 int8 non-zeros) cut over the N
+    GPUs of the run: total work fixed.  At N > 1 rank 0 also proves the whole instance alone on its GPU, so that the
+    speed-up is measured inside one run on one box."""
+    world = env.world
+    inst = SparseDenseInstance(env, STRONG_VAR, STRONG_NNZ_LOG - env.logw)
+    ms = env.timed(inst.prove, steps, 2) / steps
+    ok = inst.verify()
+    evals = inst.evals()
+    inst.release()
+    out = {"metric": METRIC, "unit": UNIT, "value": evals / (ms * 1e-3), "ms_per_prove": ms, "n_gpus": world, "scaling": "strong",
+           "verified": ok,
+           "config": f"sparse-dense product sumcheck, num_var={STRONG_VAR}, 2^{STRONG_NNZ_LOG} int8 non-zeros in all, seed {SEED}, "
+                     f"cut on the top {env.logw} variables over {world} GPU(s)"}
+    if world > 1:
+        one_ms = None
+        if env.rank == 0:
+            solo = SparseDenseInstance(env, STRONG_VAR, STRONG_NNZ_LOG, world=1, rank=0)
+            torch = env.torch
+            for _ in range(2):
+                solo.prove()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(env.stream)
+            for _ in range(steps):
+                solo.prove()
+            e1.record(env.stream)
+            e1.synchronize()
+            one_ms = e0.elapsed_time(e1) / steps
+            out["one_gpu_verified"] = solo.verify()
+            solo.release()
+        env.barrier()
+        if env.rank == 0:
+            out["one_gpu_ms_per_prove"] = one_ms
+            out["speedup_over_one_gpu"] = one_ms / ms
+            out["note"] = ("the one-GPU instance draws its sparse positions from one stream over the whole domain, the sharded "
+                           "one from a stream per rank: same sizes and densities, different positions")
+    return out
+
+
+def gpt2_leg(env: Env):
+    from zkes_b200 import gpt2_trace
+    return gpt2_trace.run(env.ctx, comm=env.comm, rank=env.rank, world=env.world, seq_len=128, seed=4)
 
 
 # DRAM bytes per launch of the dominant kernel from an ncu capture, relative to its algorithmic
@@ -484,15 +964,45 @@ def main():
     def emit(obj):
         sys.stdout.flush()
         os.write(real_stdout, (json.dumps(obj) + "\n").encode())
-    if args.msm_only:
-        from zkes_b200 import Context
 
-        ctx = Context(0)
-        emit(msm_leg(ctx, args.msm_log, max(1, args.steps)))
+    env = Env(args)
+    if args.only:
+        if args.only == "msm":
+            msm, opn = kzh2_leg(env, args.msm_log, max(1, args.steps))
+            out = {"msm": msm, "kzh2_open": opn}
+        elif args.only == "kzh3":
+            out = kzh3_leg(env, args.kzh3_log)
+        elif args.only == "linear":
+            out = linear_leg(env, args.linear_log, 2, max(1, args.steps))
+        elif args.only == "strong":
+            out = strong_leg(env, max(1, args.steps))
+        else:
+            out = gpt2_leg(env)
+        if env.rank == 0:
+            emit(out)
         return
-    ctx, rank, world, ms_per_step, value, launches, prof, e2e, clocks = gpu_arm(args)
-    if rank != 0:
+    head = headline(env)
+    extra = {}
+    if env.world == 1:
+        if not args.no_linear:
+            extra["linear_n20"] = linear_leg(env, args.linear_log)
+        if not args.no_msm:
+            extra["msm"], extra["kzh2_open"] = kzh2_leg(env, args.msm_log)
+    elif not args.no_msm:
+        extra["msm"] = msm_leg_sharded(env)
+    if not args.no_kzh3:
+        extra["kzh3"] = kzh3_leg(env, args.kzh3_log)
+    if not args.no_strong:
+        extra["strong"] = strong_leg(env)
+    if not args.no_gpt2:
+        extra["gpt2_trace"] = gpt2_leg(env)
+    if env.comm is not None:
+        env.barrier()
+        env.comm.close()
+        env.dist.destroy_process_group()
+    if env.rank != 0:
         return
+    prof = head["prof"]
     peak, peak_src = measured_peak_gbs()
     profiled_ms_per_step = prof.pop("_profiled_ms_per_step")
     top = max(prof, key=lambda k: prof[k]["ms"])
@@ -508,26 +1018,16 @@ def main():
                 "traffic": per_launch_bytes * ratio if ratio else None,
                 "profiled_ms_per_step": profiled_ms_per_step,
                 "share_of_step": {k: v["ms"] / (profiled_ms_per_step * args.steps) for k, v in prof.items()}}
-    cpu = None
-    if not args.no_cpu_baseline:
-        inputs = cpu_sample_inputs(ctx, CPU_SAMPLE_VAR, CPU_SAMPLE_NNZ_LOG)
-        sec, threads = run_cpu_oracle(inputs, CPU_SAMPLE_VAR, 2, 1)
-        cpu = {"value": ((1 << CPU_SAMPLE_VAR) + (1 << CPU_SAMPLE_NNZ_LOG)) / sec, "unit": UNIT, "cores": threads,
-               "kind": "port",
-               "sample": f"one prove on num_var={CPU_SAMPLE_VAR}, nnz=2^{CPU_SAMPLE_NNZ_LOG} (same density), mean of 2 "
-                         f"runs, {sec:.2f} s each; CPU restatement of the reference prover, not arkworks"}
-    msm = None
-    if world == 1 and not args.no_msm:
-        msm = msm_leg(ctx)
-    elif world > 1:
-        msm = args.msm_sharded
+    verified = bool(head["verified"]) and all(v.get("verified", True) is not False for v in extra.values() if isinstance(v, dict))
     out = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": METRIC, "value": head["value"], "unit": UNIT, "n_gpus": env.world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u256 (BN254 Fr, Montgomery, 8x32-bit limbs)", "data": "synthetic",
-        "config": workload_config(args.num_var, args.nnz_log, world, getattr(args, "exchange", "nccl")),
-        "gpu_launches": launches, "clocks": clocks, "e2e": e2e, "roofline": roofline, "cpu_baseline": cpu, "msm": msm,
+        "config": workload_config(args.num_var, args.nnz_log, env.world, env.exchange),
+        "gpu_launches": head["launches"], "clocks": head["clocks"], "e2e": head["e2e"], "roofline": roofline,
+        "cpu_baseline": head["cpu"], "verified": verified, "verified_headline": bool(head["verified"]),
     }
+    out.update(extra)
     emit(out)
 
 

@@ -309,6 +309,10 @@ int zk_g1_decompress(zk_ctx* ctx, const uint8_t* in, zk_mem in_mem, uint64_t n, 
 /* Shape the last MSM on this context chose (window width, windows, largest scalar magnitude in
  * bits, digit entries, buckets): used to report algorithmic work. */
 int zk_msm_last_stats(zk_ctx* ctx, int* window_bits, int* windows, int* max_bits, uint64_t* entries, uint64_t* buckets);
+/* Work of all the MSMs this context ran since the last reset (a KZH commit runs two, an opening several): the
+ * number of MSM pipelines, their non-zero signed digits (each is one mixed addition into a bucket) and the
+ * buckets they reduced.  reset != 0 clears the counters after reading.  No counterpart in the reference. */
+int zk_msm_work(zk_ctx* ctx, uint64_t* calls, uint64_t* entries, uint64_t* buckets, int reset);
 
 /* ---- KZH2 / KZH3 polynomial commitments, G1 side ------------------------------------------ */
 /* Device-resident structured reference string.  dims = 2: KZH2SRS {h_xy, h_y} (kzh2.rs:27-35),

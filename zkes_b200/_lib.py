@@ -72,6 +72,7 @@ SIGNATURES = {
     "zk_g1_normalize": (c_int, [c_void_p, c_void_p, c_int, c_uint64, c_void_p, c_int]),
     "zk_msm_last_stats": (c_int, [c_void_p, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_uint64),
                                   POINTER(c_uint64)]),
+    "zk_msm_work": (c_int, [c_void_p, POINTER(c_uint64), POINTER(c_uint64), POINTER(c_uint64), c_int]),
     "zk_kzh_srs_setup": (c_int, [c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  POINTER(c_void_p)]),
     "zk_kzh_srs_upload": (c_int, [c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p)]),

@@ -9,6 +9,9 @@ using namespace zk;
 
 namespace zk {
 int eq_table_device(zk_ctx* ctx, const uint64_t* point_host, uint32_t k, Fr* point_dev, Fr* table);
+size_t keyset_scratch_bytes(uint32_t n_terms, uint32_t num_var);
+int keyset_order(zk_ctx* ctx, const uint64_t* positions_dev, const uint64_t* term_begin_dev, uint32_t n_terms, uint64_t total,
+                 uint32_t num_var, void* scratch, uint32_t* keys_out, uint32_t bad_host[2]);
 }
 
 namespace {
@@ -28,22 +31,14 @@ int zk_sumcheck_sparse_bool_prove(zk_ctx* ctx, uint32_t num_var, uint32_t n_term
   uint32_t term_bits = 0;
   while ((1ull << term_bits) < n_terms) term_bits++;
   if (num_var + term_bits > 32) return fail(ZK_ERR_ARG, "sparse_bool_prove: num_var %u with %u terms exceeds the 32-bit key space", num_var, n_terms);
-  // entries: sort every term's positions (linear_prover.rs:497-506), key = term * 2^num_var + position
-  std::vector<uint32_t> keys;
-  uint64_t off = 0;
-  for (uint32_t j = 0; j < n_terms; j++) {
-    if (n_positions[j] && !positions) return fail(ZK_ERR_ARG, "sparse_bool_prove: NULL positions");
-    std::vector<uint64_t> pos(positions + off, positions + off + n_positions[j]);
-    off += n_positions[j];
-    std::sort(pos.begin(), pos.end());
-    for (size_t i = 0; i < pos.size(); i++) {
-      if (pos[i] >> num_var) return fail(ZK_ERR_ARG, "sparse_bool_prove: position out of range in term %u", j);
-      if (i && pos[i] == pos[i - 1]) return fail(ZK_ERR_ARG, "sparse_bool_prove: duplicate position in term %u", j);
-      keys.push_back((uint32_t)(((uint64_t)j << num_var) | pos[i]));
-    }
-  }
-  const uint32_t K = (uint32_t)keys.size();
-  if (keys.size() >> 31) return fail(ZK_ERR_ARG, "sparse_bool_prove: too many entries");
+  // entries: every term's positions in increasing order (linear_prover.rs:497-506), key = term * 2^num_var + position;
+  // the ordering runs on the device (keyset.cu)
+  std::vector<uint64_t> term_begin(n_terms + 1, 0);
+  for (uint32_t j = 0; j < n_terms; j++) term_begin[j + 1] = term_begin[j] + n_positions[j];
+  const uint64_t total = term_begin[n_terms];
+  if (total && !positions) return fail(ZK_ERR_ARG, "sparse_bool_prove: NULL positions");
+  if (total >> 31) return fail(ZK_ERR_ARG, "sparse_bool_prove: too many entries");
+  const uint32_t K = (uint32_t)total;
 
   CtxLock lk(ctx);
   cudaStream_t s = ctx->stream;
@@ -64,7 +59,21 @@ int zk_sumcheck_sparse_bool_prove(zk_ctx* ctx, uint32_t num_var, uint32_t n_term
   Fr* d_w = (Fr*)take((n_terms + 1) * sizeof(Fr));
   uint32_t* counts = (uint32_t*)take(256);
 
-  if (K) ZK_CUDA(cudaMemcpyAsync(e_key[0], keys.data(), (size_t)K * 4, cudaMemcpyHostToDevice, s));
+  if (K) {
+    char* ks = nullptr;
+    const size_t pos_bytes = al((size_t)K * 8), tb_bytes = al((size_t)(n_terms + 1) * 8);
+    rc = ctx->reserve_aux(pos_bytes + tb_bytes + keyset_scratch_bytes(n_terms, num_var), (void**)&ks);
+    if (rc) return rc;
+    uint64_t* d_pos = reinterpret_cast<uint64_t*>(ks);
+    uint64_t* d_tb = reinterpret_cast<uint64_t*>(ks + pos_bytes);
+    ZK_CUDA(cudaMemcpyAsync(d_pos, positions, (size_t)K * 8, cudaMemcpyHostToDevice, s));
+    ZK_CUDA(cudaMemcpyAsync(d_tb, term_begin.data(), (size_t)(n_terms + 1) * 8, cudaMemcpyHostToDevice, s));
+    uint32_t bad[2] = {0, 0};
+    rc = keyset_order(ctx, d_pos, d_tb, n_terms, K, num_var, ks + pos_bytes + tb_bytes, e_key[0], bad);
+    if (rc) return rc;
+    if (bad[0]) return fail(ZK_ERR_ARG, "sparse_bool_prove: position out of range in term %u", bad[0] - 1);
+    if (bad[1]) return fail(ZK_ERR_ARG, "sparse_bool_prove: duplicate position in term %u", bad[1] - 1);
+  }
   if (n_terms) ZK_CUDA(cudaMemcpyAsync(d_w, weights, (size_t)n_terms * sizeof(Fr), cudaMemcpyHostToDevice, s));
   ZK_CUDA(cudaMemsetAsync(counts, 0, 256, s));
   ZK_CUDA(cudaMemcpyAsync(counts, &K, 4, cudaMemcpyHostToDevice, s));

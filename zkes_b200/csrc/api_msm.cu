@@ -143,6 +143,16 @@ int zk_g1_normalize(zk_ctx* ctx, const uint64_t* jac, zk_mem jac_mem, uint64_t n
   return ZK_OK;
 }
 
+int zk_msm_work(zk_ctx* ctx, uint64_t* calls, uint64_t* entries, uint64_t* buckets, int reset) {
+  if (!ctx) return fail(ZK_ERR_ARG, "msm_work: NULL context");
+  CtxLock lk(ctx);
+  if (calls) *calls = ctx->msm_calls;
+  if (entries) *entries = ctx->msm_entries_sum;
+  if (buckets) *buckets = ctx->msm_bucket_sum;
+  if (reset) ctx->msm_calls = ctx->msm_entries_sum = ctx->msm_bucket_sum = 0;
+  return ZK_OK;
+}
+
 int zk_msm_last_stats(zk_ctx* ctx, int* window_bits, int* windows, int* max_bits, uint64_t* entries, uint64_t* buckets) {
   if (!ctx) return fail(ZK_ERR_ARG, "msm_last_stats: NULL context");
   CtxLock lk(ctx);

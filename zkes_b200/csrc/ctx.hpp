@@ -82,6 +82,9 @@ struct zk_ctx {
   std::vector<double> round_times;
   std::chrono::steady_clock::time_point round_t0;
   MsmStatsPod last_msm;          // shape of the most recent MSM (window width, windows, entries)
+  uint64_t msm_entries_sum = 0;  // digit entries (= bucket additions) of every MSM since the last zk_msm_work reset
+  uint64_t msm_bucket_sum = 0;   // buckets reduced by those MSMs
+  uint64_t msm_calls = 0;
   std::mutex mu;
   std::atomic<uint64_t> launches{0};
 

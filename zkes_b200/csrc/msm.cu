@@ -703,6 +703,9 @@ int msm_run_rows(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const
   k_msm_combine<<<(rows + 63) / 64, 64, 0, s>>>(window_sums, rows, w, k_windows, out_dev);
   ctx->launches += 2;
   ZK_CUDA(cudaGetLastError());
+  ctx->msm_entries_sum += n_entries;
+  ctx->msm_bucket_sum += n_buckets;
+  ctx->msm_calls++;
   if (stats) {
     stats->window_bits = w;
     stats->windows = k_windows;
