@@ -73,6 +73,7 @@ def parse_args():
     ap.add_argument("--msm-log", type=int, default=24, help="log2 of the committed table (smaller sizes are for profiling captures only)")
     ap.add_argument("--kzh3-log", type=int, default=28)
     ap.add_argument("--linear-log", type=int, default=20)
+    ap.add_argument("--gpt2-layers", type=int, default=12, help="fewer layers are for profiling captures only")
     return ap.parse_args()
 
 
@@ -88,7 +89,7 @@ def workload_config(num_var: int, nnz_log: int, gpus: int, exchange: str = "nccl
                             + ("by peer stores over NVLink inside one kernel" if exchange == "peer memory"
                                else "by an NCCL all-gather")
                             if gpus > 1 else "1 GPU"),
-            "l2": "inputs (2 GiB dense table) larger than the 126 MB L2"}
+            "l2": f"inputs ({(32 << num_var) / 2**30:g} GiB dense table) larger than the 126 MB L2"}
 
 
 class ClockSampler:
@@ -942,7 +943,7 @@ def strong_leg(env: Env, steps=5):
 
 def gpt2_leg(env: Env):
     from zkes_b200 import gpt2_trace
-    return gpt2_trace.run(env.ctx, comm=env.comm, rank=env.rank, world=env.world, seq_len=128, seed=4)
+    return gpt2_trace.run(env.ctx, comm=env.comm, rank=env.rank, world=env.world, seq_len=128, seed=4, layers=env.args.gpt2_layers)
 
 
 # DRAM bytes per launch of the dominant kernel from an ncu capture, relative to its algorithmic

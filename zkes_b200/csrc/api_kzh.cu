@@ -151,6 +151,87 @@ int kzh3_open_tail(zk_ctx* ctx, const zk_kzh_srs* srs, const Fr* f_prime, const 
   return ZK_OK;
 }
 
+// ---- opening of a sparse polynomial: the contraction over x runs over the non-zero entries only
+// (sparse_kzh2.rs:99-116, sparse_kzh3.rs:140-170):  out[lo] = sum over entries (idx = hi * 2^low_bits + lo, v)
+// of eq(r_x)[hi] * v.  Entries that share `lo` meet in no particular order; a field element has no atomic add,
+// but a sum of Montgomery representations is linear, so every 32-bit limb of a term goes into its own 64-bit
+// counter with one native atomic, and a second pass carries and reduces the eight counters of an output.
+__global__ void __launch_bounds__(256) k_sparse_contract(const uint64_t* __restrict__ idx, const Fr* __restrict__ vals,
+                                                         uint64_t nnz, uint32_t low_bits, uint64_t limit,
+                                                         const Fr* __restrict__ eq, unsigned long long* limbs, unsigned int* bad) {
+  for (uint64_t e = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; e < nnz; e += (uint64_t)gridDim.x * blockDim.x) {
+    const uint64_t i = idx[e];
+    if (i >= limit) {
+      atomicExch(bad, 1u);
+      continue;
+    }
+    Fr w = eq[i >> low_bits];
+    if (vals) w = mul(w, vals[e]);
+    unsigned long long* L = limbs + (i & ((1ull << low_bits) - 1)) * 8;
+#pragma unroll
+    for (int k = 0; k < 8; k++) atomicAdd(L + k, (unsigned long long)w.v[k]);
+  }
+}
+
+__global__ void __launch_bounds__(256) k_limbs_to_fr(const unsigned long long* __restrict__ limbs, uint64_t n, Fr* out) {
+  for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (uint64_t)gridDim.x * blockDim.x) {
+    Wide x;
+#pragma unroll
+    for (int k = 0; k < 16; k++) x.v[k] = 0;
+    unsigned long long carry = 0;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const unsigned long long v = limbs[t * 8 + j];
+      const unsigned long long s = (v & 0xffffffffull) + (carry & 0xffffffffull);
+      x.v[j] = (uint32_t)s;
+      carry = (v >> 32) + (carry >> 32) + (s >> 32);
+    }
+    x.v[8] = (uint32_t)carry;
+    x.v[9] = (uint32_t)(carry >> 32);
+    out[t] = to_mont(redc<FrParams>(x));  // X mod r: redc gives X / R, the product by R^2 restores the factor
+  }
+}
+
+// f_prime (device, 2^(n - x_log) elements) of a sparse polynomial.  mem: sparse_contract_bytes() of device memory.
+size_t sparse_contract_bytes(const zk_kzh_srs* srs, uint64_t nnz, bool with_vals) {
+  const uint64_t nx = 1ull << srs->x_log, lo_n = 1ull << (srs->n - srs->x_log);
+  return al(nnz * 8 + 8) + (with_vals ? al(nnz * sizeof(Fr) + 32) : 0) + al((nx + srs->x_log + 16) * sizeof(Fr)) + al(lo_n * 64) + 512;
+}
+
+int sparse_contract_x(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const uint64_t* indices, const uint64_t* vals,
+                      const uint64_t* r_x, char* mem, Fr* f_prime) {
+  cudaStream_t st = ctx->stream;
+  const uint32_t xl = srs->x_log, low_bits = srs->n - xl;
+  const uint64_t nx = 1ull << xl, lo_n = 1ull << low_bits;
+  size_t off = 0;
+  auto take = [&](size_t bytes) { char* p = mem + off; off += al(bytes); return p; };
+  uint64_t* d_idx = (uint64_t*)take(nnz * 8 + 8);
+  Fr* d_val = vals ? (Fr*)take(nnz * sizeof(Fr) + 32) : nullptr;
+  Fr* eq = (Fr*)take((nx + xl + 16) * sizeof(Fr));
+  unsigned long long* limbs = (unsigned long long*)take(lo_n * 64);
+  unsigned int* bad = ctx->rs.sink.counter + 16;
+  if (nnz) {
+    ZK_CUDA(cudaMemcpyAsync(d_idx, indices, nnz * 8, cudaMemcpyHostToDevice, st));
+    if (vals) ZK_CUDA(cudaMemcpyAsync(d_val, vals, nnz * sizeof(Fr), cudaMemcpyHostToDevice, st));
+  }
+  int rc = eq_table_device(ctx, r_x, xl, eq + nx, eq);
+  if (rc) return rc;
+  ZK_CUDA(cudaMemsetAsync(limbs, 0, lo_n * 64, st));
+  ZK_CUDA(cudaMemsetAsync(bad, 0, 4, st));
+  if (nnz) {
+    uint64_t blocks = (nnz + 255) / 256;
+    if (blocks > (uint64_t)ctx->sm_count * 8) blocks = ctx->sm_count * 8;
+    k_sparse_contract<<<(unsigned)blocks, 256, 0, st>>>(d_idx, d_val, nnz, low_bits, 1ull << srs->n, eq, limbs, bad);
+    ctx->launches++;
+  }
+  uint64_t blocks = (lo_n + 255) / 256;
+  if (blocks > (uint64_t)ctx->sm_count * 8) blocks = ctx->sm_count * 8;
+  k_limbs_to_fr<<<(unsigned)blocks, 256, 0, st>>>(limbs, lo_n, f_prime);
+  ctx->launches++;
+  ZK_CUDA(cudaGetLastError());
+  return ZK_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -278,16 +359,17 @@ int zk_kzh_commit(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uin
   rc = msm_run(ctx, srs->h[0], nullptr, f, size, 1, d_jac + rows, &ctx->last_msm, &prep);
   ctx->prof_end();
   if (rc) return rc;
-  rc = normalize_device(ctx, d_jac + rows, 1, d_c);
-  if (rc) return rc;
   // d_x[i] = sum_j f[i * 2^(n - x_log) + j] h_mid[j]   (kzh2.rs:653-660, kzh3.rs:680-687)
   ctx->prof_begin(ZK_PROF_MSM, 0.0, 8);
   rc = msm_run(ctx, srs->h[1], nullptr, f, srs->count[1], (uint32_t)rows, d_jac, nullptr, &prep);
   ctx->prof_end();
   if (rc) return rc;
-  ZK_CUDA(cudaMemcpyAsync(c_affine_out, d_c, sizeof(Affine), cudaMemcpyDeviceToHost, st));
+  Jacobian* h_c = reinterpret_cast<Jacobian*>(reinterpret_cast<char*>(ctx->host_small) + 4096);
+  ZK_CUDA(cudaMemcpyAsync(h_c, d_jac + rows, sizeof(Jacobian), cudaMemcpyDeviceToHost, st));
   ZK_CUDA(cudaMemcpyAsync(d_x_jac_out, d_jac, rows * sizeof(Jacobian), cudaMemcpyDeviceToHost, st));
   ZK_CUDA(cudaStreamSynchronize(st));
+  const Affine c_aff = jacobian_to_affine_host(*h_c);  // the commitment's affine form (into_affine)
+  memcpy(c_affine_out, &c_aff, sizeof(Affine));
   return ZK_OK;
 }
 
@@ -506,6 +588,62 @@ int zk_kzh_verify_g1(zk_ctx* ctx, const zk_kzh_srs* srs, const uint64_t* point, 
   *ok = bad == 0;
   if (failed_check) *failed_check = bad;
   return ZK_OK;
+}
+
+// sparse_kzh2_open (sparse_kzh2.rs:84-127): same point convention as the dense open (split_input, :97-98).
+int zk_sparse_kzh2_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const uint64_t* indices, const uint64_t* vals,
+                        const uint64_t* point, uint32_t point_len, uint64_t* f_star_out) {
+  if (!ctx || !srs || !f_star_out || (nnz && !indices) || (point_len && !point)) return fail(ZK_ERR_ARG, "sparse_kzh2_open: NULL argument");
+  if (srs->dims != 2) return fail(ZK_ERR_ARG, "sparse_kzh2_open: the SRS is not a KZH2 SRS");
+  if (srs->world != 1) return fail(ZK_ERR_ARG, "sparse_kzh2_open: needs an unsharded SRS");
+  CtxLock lk(ctx);
+  cudaStream_t st = ctx->stream;
+  const uint64_t ny = 1ull << srs->y_log;
+  std::vector<uint64_t> pt;
+  pad_point(point, point_len, srs->n, pt);
+  char* base = nullptr;
+  int rc = ctx->reserve_work(sparse_contract_bytes(srs, nnz, vals != nullptr) + al(ny * sizeof(Fr)) + 1024, (void**)&base);
+  if (rc) return rc;
+  Fr* f_star = reinterpret_cast<Fr*>(base);
+  rc = sparse_contract_x(ctx, srs, nnz, indices, vals, pt.data() + (size_t)srs->y_log * 4, base + al(ny * sizeof(Fr)), f_star);
+  if (rc) return rc;
+  unsigned int* bad = ctx->rs.sink.counter + 16;
+  ZK_CUDA(cudaMemcpyAsync(f_star_out, f_star, ny * sizeof(Fr), cudaMemcpyDeviceToHost, st));
+  ZK_CUDA(cudaMemcpyAsync(ctx->host_small, bad, 4, cudaMemcpyDeviceToHost, st));
+  ZK_CUDA(cudaStreamSynchronize(st));
+  if (*reinterpret_cast<const unsigned int*>(ctx->host_small)) return fail(ZK_ERR_ARG, "sparse_kzh2_open: an index is outside the SRS domain");
+  return ZK_OK;
+}
+
+// sparse_kzh3_open (sparse_kzh3.rs:112-232); a short point is padded with trailing zeros here (:124-131), unlike
+// the dense open.
+int zk_sparse_kzh3_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const uint64_t* indices, const uint64_t* vals,
+                        const uint64_t* point, uint32_t point_len, const uint64_t* d_x_jac, uint64_t* d_y_jac_out,
+                        uint64_t* c_y_affine_out, uint64_t* f_star_out) {
+  if (!ctx || !srs || (nnz && !indices) || (point_len && !point) || !d_x_jac || !d_y_jac_out || !c_y_affine_out || !f_star_out)
+    return fail(ZK_ERR_ARG, "sparse_kzh3_open: NULL argument");
+  if (srs->dims != 3) return fail(ZK_ERR_ARG, "sparse_kzh3_open: the SRS is not a KZH3 SRS");
+  if (srs->world != 1) return fail(ZK_ERR_ARG, "sparse_kzh3_open: needs an unsharded SRS");
+  std::vector<uint64_t> pt((size_t)srs->n * 4, 0);
+  const uint32_t take_n = point_len < srs->n ? point_len : srs->n;
+  if (take_n) memcpy(pt.data(), point, (size_t)take_n * 32);
+  CtxLock lk(ctx);
+  cudaStream_t st = ctx->stream;
+  const uint64_t nyz = 1ull << (srs->y_log + srs->z_log);
+  char* base = nullptr;
+  int rc = ctx->reserve_work(sparse_contract_bytes(srs, nnz, vals != nullptr) + al(nyz * sizeof(Fr)) + kzh3_tail_bytes(ctx, srs) + 1024,
+                             (void**)&base);
+  if (rc) return rc;
+  Fr* f_prime = reinterpret_cast<Fr*>(base);
+  char* tail_mem = base + al(nyz * sizeof(Fr));
+  char* contract_mem = tail_mem + kzh3_tail_bytes(ctx, srs);
+  rc = sparse_contract_x(ctx, srs, nnz, indices, vals, pt.data() + (size_t)(srs->y_log + srs->z_log) * 4, contract_mem, f_prime);
+  if (rc) return rc;
+  unsigned int* bad = ctx->rs.sink.counter + 16;
+  ZK_CUDA(cudaMemcpyAsync(ctx->host_small, bad, 4, cudaMemcpyDeviceToHost, st));
+  ZK_CUDA(cudaStreamSynchronize(st));
+  if (*reinterpret_cast<const unsigned int*>(ctx->host_small)) return fail(ZK_ERR_ARG, "sparse_kzh3_open: an index is outside the SRS domain");
+  return kzh3_open_tail(ctx, srs, f_prime, pt, d_x_jac, tail_mem, d_y_jac_out, c_y_affine_out, f_star_out);
 }
 
 }  // extern "C"

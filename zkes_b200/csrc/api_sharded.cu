@@ -91,8 +91,6 @@ static int kzh_commit_sharded_impl(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs*
   if (rc) return rc;
   rc = comm_sum_points_n(ctx, comm, d_jac + rows, 1);
   if (rc) return rc;
-  rc = normalize_device(ctx, d_jac + rows, 1, d_c);
-  if (rc) return rc;
   // this rank's rows of d_x, written at their place in the full vector, then all-gathered in place
   Jacobian* mine = d_jac + rows_local * srs->rank;
   rc = msm_run(ctx, srs->h[1], nullptr, f, srs->count[1], (uint32_t)rows_local, mine, nullptr, &prep);
@@ -102,9 +100,12 @@ static int kzh_commit_sharded_impl(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs*
   if (rc) return rc;
   rc = comm_gather_bytes(ctx, comm, mine, rows_local * sizeof(Jacobian), tmp);
   if (rc) return rc;
-  ZK_CUDA(cudaMemcpyAsync(c_affine_out, d_c, sizeof(Affine), cudaMemcpyDeviceToHost, st));
+  Jacobian* h_c = reinterpret_cast<Jacobian*>(reinterpret_cast<char*>(ctx->host_small) + 4096);
+  ZK_CUDA(cudaMemcpyAsync(h_c, d_jac + rows, sizeof(Jacobian), cudaMemcpyDeviceToHost, st));
   ZK_CUDA(cudaMemcpyAsync(d_x_jac_out, tmp, rows * sizeof(Jacobian), cudaMemcpyDeviceToHost, st));
   ZK_CUDA(cudaStreamSynchronize(st));
+  const Affine c_aff = jacobian_to_affine_host(*h_c);  // the commitment's affine form (into_affine)
+  memcpy(c_affine_out, &c_aff, sizeof(Affine));
   return ZK_OK;
 }
 

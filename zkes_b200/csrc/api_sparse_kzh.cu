@@ -1,8 +1,7 @@
 // C ABI: KZH commit / open of sparse polynomials (non-zero entries given as (index, value) pairs):
 // sparse_kzh2_commit / open (src/crypto/polycommit/sparse_kzh2.rs:14-127) and sparse_kzh3_commit / open
 // (sparse_kzh3.rs:32-232).  Commit is two gather-MSMs (sparse_msm, polycommit/mod.rs:10-31): one over
-// the full vector, one with every entry routed to the row of its x index.  Open scatters the entries
-// into a dense table on the device and runs the dense open (the sums are the same field elements).
+// the full vector, one with every entry routed to the row of its x index.  The opens are in api_kzh.cu.
 #include "../../include/zkb200.h"
 #include "kzh.hpp"
 
@@ -29,45 +28,13 @@ __global__ void k_split_index(const uint64_t* __restrict__ idx, uint32_t n, uint
   }
 }
 
-__global__ void k_scatter64(const uint64_t* __restrict__ idx, const Fr* __restrict__ val, uint32_t n, Fr* dense) {
-  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) dense[idx[i]] = val[i];
-}
-
-// Dense device copy of a sparse polynomial (entries must have distinct indices below 2^n).
-int densify(zk_ctx* ctx, uint32_t n, uint64_t nnz, const uint64_t* indices, const uint64_t* vals, Fr** out) {
-  CtxLock lk(ctx);
-  cudaStream_t s = ctx->stream;
-  Fr* dense = nullptr;
-  cudaError_t e = cudaMalloc(&dense, (sizeof(Fr) << n) + 256);
-  if (e != cudaSuccess) {
-    cudaGetLastError();
-    return fail(ZK_ERR_OOM, "sparse_kzh open: dense table of 2^%u elements: %s", n, cudaGetErrorString(e));
-  }
-  char* base = nullptr;
-  int rc = ctx->reserve_work(al(nnz * 8) + al(nnz * sizeof(Fr)) + 1024, (void**)&base);
-  if (rc) { cudaFree(dense); return rc; }
-  uint64_t* d_idx = (uint64_t*)base;
-  Fr* d_val = (Fr*)(base + al(nnz * 8));
-  ZK_CUDA(cudaMemsetAsync(dense, 0, sizeof(Fr) << n, s));
-  if (nnz) {
-    ZK_CUDA(cudaMemcpyAsync(d_idx, indices, nnz * 8, cudaMemcpyHostToDevice, s));
-    ZK_CUDA(cudaMemcpyAsync(d_val, vals, nnz * sizeof(Fr), cudaMemcpyHostToDevice, s));
-    k_scatter64<<<ctx->sm_count * 4, 256, 0, s>>>(d_idx, d_val, (uint32_t)nnz, dense);
-    ctx->launches++;
-  }
-  ZK_CUDA(cudaGetLastError());
-  ZK_CUDA(cudaStreamSynchronize(s));
-  *out = dense;
-  return ZK_OK;
-}
-
 }  // namespace
 
 extern "C" {
 
 int zk_sparse_kzh_commit(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const uint64_t* indices, const uint64_t* vals,
                          uint64_t* c_affine_out, uint64_t* d_x_jac_out) {
-  if (!ctx || !srs || !c_affine_out || !d_x_jac_out || (nnz && (!indices || !vals)))
+  if (!ctx || !srs || !c_affine_out || !d_x_jac_out || (nnz && !indices))
     return fail(ZK_ERR_ARG, "sparse_kzh_commit: NULL argument");
   if (srs->world != 1) return fail(ZK_ERR_ARG, "sparse_kzh_commit: needs an unsharded SRS");
   if (nnz >> 31) return fail(ZK_ERR_ARG, "sparse_kzh_commit: too many entries");
@@ -91,7 +58,12 @@ int zk_sparse_kzh_commit(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const
   uint32_t* bad = ctx->rs.sink.counter + 16;
   if (nnz) {
     ZK_CUDA(cudaMemcpyAsync(d_idx, indices, nnz * 8, cudaMemcpyHostToDevice, st));
-    ZK_CUDA(cudaMemcpyAsync(d_val, vals, nnz * sizeof(Fr), cudaMemcpyHostToDevice, st));
+    if (vals) {
+      ZK_CUDA(cudaMemcpyAsync(d_val, vals, nnz * sizeof(Fr), cudaMemcpyHostToDevice, st));
+    } else {  // a selection polynomial: every listed entry is one
+      launch_fill_ones(d_val, (uint32_t)nnz, ctx->sm_count, st);
+      ctx->launches++;
+    }
     ZK_CUDA(cudaMemsetAsync(bad, 0, 4, st));
     k_split_index<<<ctx->sm_count * 4, 256, 0, st>>>(d_idx, (uint32_t)nnz, low_bits, 1ull << srs->n, d_full, d_low, d_row, bad);
     ctx->launches++;
@@ -104,44 +76,16 @@ int zk_sparse_kzh_commit(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const
   // C = sparse_msm(h_full, indices, scalars)   (sparse_kzh2.rs:27-38, sparse_kzh3.rs:45-56)
   rc = msm_run(ctx, srs->h[0], d_full, d_val, nnz, 1, d_jac + rows, &ctx->last_msm);
   if (rc) return rc;
-  rc = normalize_device(ctx, d_jac + rows, 1, d_c);
-  if (rc) return rc;
   // d_x[x] = sparse_msm(h_mid, low indices of the entries with that x, their values)   (sparse_kzh2.rs:42-80)
   rc = msm_run_rows(ctx, srs->h[1], d_low, d_row, d_val, nnz, (uint32_t)rows, d_jac, nullptr);
   if (rc) return rc;
-  ZK_CUDA(cudaMemcpyAsync(c_affine_out, d_c, sizeof(Affine), cudaMemcpyDeviceToHost, st));
+  Jacobian* h_c = reinterpret_cast<Jacobian*>(reinterpret_cast<char*>(ctx->host_small) + 4096);
+  ZK_CUDA(cudaMemcpyAsync(h_c, d_jac + rows, sizeof(Jacobian), cudaMemcpyDeviceToHost, st));
   ZK_CUDA(cudaMemcpyAsync(d_x_jac_out, d_jac, rows * sizeof(Jacobian), cudaMemcpyDeviceToHost, st));
   ZK_CUDA(cudaStreamSynchronize(st));
+  const Affine c_aff = jacobian_to_affine_host(*h_c);  // the commitment's affine form (into_affine)
+  memcpy(c_affine_out, &c_aff, sizeof(Affine));
   return ZK_OK;
-}
-
-int zk_sparse_kzh2_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const uint64_t* indices, const uint64_t* vals,
-                        const uint64_t* point, uint32_t point_len, uint64_t* f_star_out) {
-  if (!ctx || !srs || (nnz && (!indices || !vals))) return fail(ZK_ERR_ARG, "sparse_kzh2_open: NULL argument");
-  Fr* dense = nullptr;
-  int rc = densify(ctx, srs->n, nnz, indices, vals, &dense);
-  if (rc) return rc;
-  // same point convention as the dense open (split_input, sparse_kzh2.rs:97-98)
-  rc = zk_kzh2_open(ctx, srs, srs->n, reinterpret_cast<const uint64_t*>(dense), ZK_MEM_DEVICE, point, point_len, f_star_out);
-  cudaFree(dense);
-  return rc;
-}
-
-int zk_sparse_kzh3_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const uint64_t* indices, const uint64_t* vals,
-                        const uint64_t* point, uint32_t point_len, const uint64_t* d_x_jac, uint64_t* d_y_jac_out,
-                        uint64_t* c_y_affine_out, uint64_t* f_star_out) {
-  if (!ctx || !srs || (nnz && (!indices || !vals)) || (point_len && !point)) return fail(ZK_ERR_ARG, "sparse_kzh3_open: NULL argument");
-  // a short point is padded with trailing zeros here (sparse_kzh3.rs:124-131), unlike the dense open
-  std::vector<uint64_t> pt((size_t)srs->n * 4, 0);
-  const uint32_t take = point_len < srs->n ? point_len : srs->n;
-  if (take) memcpy(pt.data(), point, (size_t)take * 32);
-  Fr* dense = nullptr;
-  int rc = densify(ctx, srs->n, nnz, indices, vals, &dense);
-  if (rc) return rc;
-  rc = zk_kzh3_open(ctx, srs, srs->n, reinterpret_cast<const uint64_t*>(dense), ZK_MEM_DEVICE, pt.data(), srs->n, d_x_jac,
-                    d_y_jac_out, c_y_affine_out, f_star_out);
-  cudaFree(dense);
-  return rc;
 }
 
 }  // extern "C"

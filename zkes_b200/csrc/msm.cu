@@ -307,6 +307,7 @@ __global__ void __launch_bounds__(128) k_msm_accumulate(const Affine* __restrict
 }
 
 constexpr uint32_t kFewPieces = 8;
+constexpr uint32_t kFixupPartials = 4096;  // partial sums of the grouped fix-up (buckets x groups)
 
 // One thread per bucket: buckets cut into at most kFewPieces pieces are summed in place; longer
 // ones are left to the warp-per-bucket kernel below (found through the `many` list).
@@ -381,6 +382,58 @@ __global__ void __launch_bounds__(128) k_msm_fixup_block(const uint32_t* __restr
       sh[threadIdx.x] = acc;
     }
     __syncthreads();
+  }
+  if (threadIdx.x == 0) st_xyzz(bucket_sums + b, acc);
+}
+
+// Very long buckets (a narrow window over millions of points, or the single bucket of an all-ones MSM): the
+// pieces of a bucket are shared by `groups` blocks, each leaving a partial sum, and a second small launch adds
+// the partial sums of every bucket.
+__global__ void __launch_bounds__(128) k_msm_fixup_groups(const uint32_t* __restrict__ offsets, uint32_t seg, uint32_t groups,
+                                                          const Xyzz* heads, const Xyzz* tails, Xyzz* partial) {
+  __shared__ Xyzz sh[128];
+  const uint32_t b = blockIdx.x, g = blockIdx.y;
+  const uint32_t s = offsets[b], e = offsets[b + 1];
+  Xyzz acc = Xyzz::inf();
+  if (e > s) {
+    const uint32_t c0 = s / seg, c1 = (e - 1) / seg;
+    if (c0 != c1)
+      for (uint32_t c = c0 + g + groups * threadIdx.x; c <= c1; c += groups * blockDim.x) {
+        const Xyzz h = ld_xyzz(c == c0 ? tails + c : heads + c);
+        add_to(&acc, &h);
+      }
+  }
+  sh[threadIdx.x] = acc;
+  __syncthreads();
+  for (uint32_t off = blockDim.x >> 1; off > 0; off >>= 1) {
+    if (threadIdx.x < off) {
+      add_to(&acc, &sh[threadIdx.x + off]);
+      sh[threadIdx.x] = acc;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) st_xyzz(partial + (size_t)b * groups + g, acc);
+}
+
+__global__ void __launch_bounds__(32) k_msm_fixup_groups_final(const uint32_t* __restrict__ offsets, uint32_t seg, uint32_t groups,
+                                                               const Xyzz* partial, Xyzz* bucket_sums) {
+  __shared__ Xyzz sh[32];
+  const uint32_t b = blockIdx.x;
+  const uint32_t s = offsets[b], e = offsets[b + 1];
+  if (e <= s || s / seg == (e - 1) / seg) return;  // the accumulation wrote this bucket directly
+  Xyzz acc = Xyzz::inf();
+  for (uint32_t g = threadIdx.x; g < groups; g += 32) {
+    const Xyzz h = ld_xyzz(partial + (size_t)b * groups + g);
+    add_to(&acc, &h);
+  }
+  sh[threadIdx.x] = acc;
+  __syncwarp();
+  for (int off = 16; off > 0; off >>= 1) {
+    if (threadIdx.x < (unsigned)off) {
+      add_to(&acc, &sh[threadIdx.x + off]);
+      sh[threadIdx.x] = acc;
+    }
+    __syncwarp();
   }
   if (threadIdx.x == 0) st_xyzz(bucket_sums + b, acc);
 }
@@ -606,7 +659,7 @@ int msm_run_rows(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const
   // entries and chunk slots are sized after the count pass; reserve the worst case now
   uint64_t chunk_guess = max_entries / 32 + 1;
   if (chunk_guess > (1u << 20)) chunk_guess = 1u << 20;
-  need += align256(max_entries * 4) + 2 * align256((chunk_guess + 1) * sizeof(Xyzz));
+  need += align256(max_entries * 4) + 2 * align256((chunk_guess + 1) * sizeof(Xyzz)) + align256((size_t)kFixupPartials * sizeof(Xyzz));
   int rc = ctx->reserve_aux(need, (void**)&base);
   if (rc) return rc;
   size_t off = 0;
@@ -619,6 +672,7 @@ int msm_run_rows(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const
   uint32_t* entries = (uint32_t*)take(max_entries * 4);
   Xyzz* heads = (Xyzz*)take((chunk_guess + 1) * sizeof(Xyzz));
   Xyzz* tails = (Xyzz*)take((chunk_guess + 1) * sizeof(Xyzz));
+  Xyzz* fix_part = (Xyzz*)take((size_t)kFixupPartials * sizeof(Xyzz));
 
   // ---- pass 2: count, scan, scatter
   ZK_CUDA(cudaMemsetAsync(offsets, 0, (n_buckets + 2) * 4ull, s));
@@ -675,7 +729,15 @@ int msm_run_rows(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const
     n_chunks = (n_entries + seg - 1) / seg;
     k_msm_accumulate<<<(n_chunks + 127) / 128, 128, 0, s>>>(bases, gather, entries, offsets, n_buckets, n_entries, seg,
                                                            n_chunks, bucket_sums, heads, tails);
-    if (n_buckets <= 8192) {
+    // pieces per bucket on average; from a few hundred on, one block per bucket is a long serial chain
+    const uint32_t avg_pieces = n_chunks / n_buckets;
+    uint32_t groups = (avg_pieces + 255) / 256;
+    if (n_buckets <= kFixupPartials && groups > kFixupPartials / n_buckets) groups = kFixupPartials / n_buckets;
+    if (n_buckets <= 8192 && n_buckets <= kFixupPartials && groups >= 2) {
+      k_msm_fixup_groups<<<dim3(n_buckets, groups), 128, 0, s>>>(offsets, seg, groups, heads, tails, fix_part);
+      k_msm_fixup_groups_final<<<n_buckets, 32, 0, s>>>(offsets, seg, groups, fix_part, bucket_sums);
+      ctx->launches++;
+    } else if (n_buckets <= 8192) {
       k_msm_fixup_block<<<n_buckets, 128, 0, s>>>(offsets, seg, bucket_sums, heads, tails);
     } else {
       // cursor[] is free again after the scatter: reuse it as the list of long buckets

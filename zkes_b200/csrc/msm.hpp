@@ -33,4 +33,19 @@ int msm_run(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const Fr* 
 int msm_run_rows(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const uint32_t* row_ids, const Fr* scalars,
                  uint64_t n, uint32_t rows, Jacobian* out_dev, MsmStats* stats, MsmPrep* prep = nullptr);
 
+// CurveGroup::into_affine of one point on the host: a single inversion is a chain of some 380 dependent field
+// products, about 150 us for one GPU thread and a few tens of microseconds for a CPU core.
+inline Affine jacobian_to_affine_host(const Jacobian& j) {
+  Affine a;
+  if (j.z.is_zero()) {
+    a.x = Fq::zero();
+    a.y = Fq::zero();
+  } else {
+    const Fq zi = inverse(j.z), zi2 = sqr(zi);
+    a.x = mul(j.x, zi2);
+    a.y = mul(j.y, mul(zi2, zi));
+  }
+  return a;
+}
+
 }  // namespace zk

@@ -79,12 +79,30 @@ __global__ void __launch_bounds__(256) k_from_right(const Fr* __restrict__ f, co
   st_fr_plain(partial + (uint64_t)blockIdx.y * lo_n + lo, redc<FrParams>(acc));
 }
 
+// out[lo] = sum_k partial[k * lo_n + lo].  A block takes 32 columns; its eight warps share the splits (warp g
+// sums splits g, g + 8, ...: a warp reads 1 KiB of one split at a time, and the loads of a thread do not wait
+// for one another), then the eight partial sums of a column are added through shared memory.
 __global__ void __launch_bounds__(256) k_sum_splits(const Fr* __restrict__ partial, uint64_t lo_n, uint32_t splits, Fr* out) {
-  const uint64_t lo = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (lo >= lo_n) return;
-  Fr s = ld_fr_plain(partial + lo);
-  for (uint32_t k = 1; k < splits; k++) s = add(s, ld_fr_plain(partial + (uint64_t)k * lo_n + lo));
-  st_fr_plain(out + lo, s);
+  __shared__ Fr sh[8][32];
+  const int col = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const uint64_t lo = (uint64_t)blockIdx.x * 32 + col;
+  Fr s = Fr::zero();
+  if (lo < lo_n) {
+    uint32_t k = g;
+    for (; k + 24 < splits; k += 32) {  // four loads in flight
+      const Fr a = ld_fr_plain(partial + (uint64_t)k * lo_n + lo), b = ld_fr_plain(partial + (uint64_t)(k + 8) * lo_n + lo);
+      const Fr c = ld_fr_plain(partial + (uint64_t)(k + 16) * lo_n + lo), d = ld_fr_plain(partial + (uint64_t)(k + 24) * lo_n + lo);
+      s = add(add(s, add(a, b)), add(c, d));
+    }
+    for (; k < splits; k += 8) s = add(s, ld_fr_plain(partial + (uint64_t)k * lo_n + lo));
+  }
+  sh[g][col] = s;
+  __syncthreads();
+  if (g == 0 && lo < lo_n) {
+#pragma unroll
+    for (int w = 1; w < 8; w++) s = add(s, sh[w][col]);
+    st_fr_plain(out + lo, s);
+  }
 }
 
 // sum_i a[i] * b[i] with lazily reduced products (evaluate_multilinear_extension's final sum, poly.rs:635-647).
@@ -155,7 +173,7 @@ int launch_from_right(const Fr* f, const Fr* eq, uint64_t lo_n, uint64_t hi_n, F
     return 1;
   }
   k_from_right<<<grid, 256, 0, s>>>(f, eq, lo_n, hi_n, per, partial);
-  k_sum_splits<<<(unsigned)((lo_n + 255) / 256), 256, 0, s>>>(partial, lo_n, splits, out);
+  k_sum_splits<<<(unsigned)((lo_n + 31) / 32), 256, 0, s>>>(partial, lo_n, splits, out);
   return 2;
 }
 

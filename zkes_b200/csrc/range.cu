@@ -45,6 +45,42 @@ __global__ void __launch_bounds__(256) k_range_scatter(const uint64_t* __restric
   }
 }
 
+// The same for a small table (at most kSmallTable entries: lookup blocks of a few bits): with so few counters
+// every global atomic would meet thousands of others on its address, so a block first adds into its own copy
+// of the counters in shared memory and then flushes each non-zero counter with one global atomic.
+constexpr uint32_t kSmallTable = 512;
+__global__ void __launch_bounds__(256) k_range_scatter_small(const uint64_t* __restrict__ input_idx,
+                                                             const uint64_t* __restrict__ table_idx, uint64_t n_sel,
+                                                             const Fr* __restrict__ eq, uint64_t n_inputs, uint32_t n_table,
+                                                             unsigned long long* limbs, unsigned int* bad) {
+  extern __shared__ unsigned long long sh_limbs[];
+  for (uint32_t k = threadIdx.x; k < n_table * 8; k += blockDim.x) sh_limbs[k] = 0;
+  __syncthreads();
+  for (uint64_t e = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n_sel; e += (uint64_t)gridDim.x * blockDim.x) {
+    const uint64_t i = input_idx[e], t = table_idx[e];
+    if (i >= n_inputs || t >= n_table) {
+      atomicExch(bad, 1u);
+      continue;
+    }
+    const uint4 lo = __ldg(reinterpret_cast<const uint4*>(eq + i));
+    const uint4 hi = __ldg(reinterpret_cast<const uint4*>(eq + i) + 1);
+    unsigned long long* L = sh_limbs + t * 8;
+    atomicAdd(L + 0, (unsigned long long)lo.x);
+    atomicAdd(L + 1, (unsigned long long)lo.y);
+    atomicAdd(L + 2, (unsigned long long)lo.z);
+    atomicAdd(L + 3, (unsigned long long)lo.w);
+    atomicAdd(L + 4, (unsigned long long)hi.x);
+    atomicAdd(L + 5, (unsigned long long)hi.y);
+    atomicAdd(L + 6, (unsigned long long)hi.z);
+    atomicAdd(L + 7, (unsigned long long)hi.w);
+  }
+  __syncthreads();
+  for (uint32_t k = threadIdx.x; k < n_table * 8; k += blockDim.x) {
+    const unsigned long long v = sh_limbs[k];
+    if (v) atomicAdd(limbs + k, v);
+  }
+}
+
 // part[t] from its limb counters; acc[t] += beta_gamma * part[t]; sink.msg[0] = sum_t part[t] * t.
 __global__ void __launch_bounds__(256) k_range_finish(const unsigned long long* __restrict__ limbs, uint64_t n_table,
                                                       const FixedMul<FrParams> bg, Fr* acc, const MsgSink sink) {
@@ -135,7 +171,12 @@ int zk_range_aux_accumulate(zk_ctx* ctx, uint32_t k, const uint64_t* point, uint
   if (n_sel) {
     uint64_t blocks = (n_sel + 255) / 256;
     if (blocks > (uint64_t)ctx->sm_count * 8) blocks = ctx->sm_count * 8;
-    k_range_scatter<<<(unsigned)blocks, 256, 0, s>>>(d_in, d_tab, n_sel, eq, n_inputs, n_table, limbs, bad);
+    if (n_table <= kSmallTable) {
+      if (blocks > (uint64_t)ctx->sm_count * 4) blocks = ctx->sm_count * 4;
+      k_range_scatter_small<<<(unsigned)blocks, 256, n_table * 64, s>>>(d_in, d_tab, n_sel, eq, n_inputs, (uint32_t)n_table, limbs, bad);
+    } else {
+      k_range_scatter<<<(unsigned)blocks, 256, 0, s>>>(d_in, d_tab, n_sel, eq, n_inputs, n_table, limbs, bad);
+    }
     ctx->launches++;
   }
   RoundScratch sc = ctx->rs;

@@ -174,7 +174,6 @@ def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12)
     for n in sorted(set(lookups)):
         digits = rnd.integers(0, 1 << TABLE_BLOCK_LOG, size=1 << n, dtype=np.uint64)
         aux_pos[n] = np.ascontiguousarray((digits << np.uint64(n)) | np.arange(1 << n, dtype=np.uint64))
-    ones = {n: to_mont_array([1]).repeat(1 << n, axis=0) for n in aux_pos}
 
     def barrier():
         if world > 1:
@@ -206,7 +205,7 @@ def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12)
             if mine(item):
                 m = n + TABLE_BLOCK_LOG
                 dx = np.zeros((1 << srs[m].x_log, 12), dtype=np.uint64)
-                check(lib.zk_sparse_kzh_commit(h, srs[m].handle, 1 << n, vp(aux_pos[n].ctypes.data), vp(ones[n].ctypes.data),
+                check(lib.zk_sparse_kzh_commit(h, srs[m].handle, 1 << n, vp(aux_pos[n].ctypes.data), None,
                                                vp(c_out.ctypes.data), vp(dx.ctypes.data)), "zk_sparse_kzh_commit")
                 commitments[("s", m)] = dx
                 n_sparse_commits += 1
@@ -337,13 +336,13 @@ def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12)
             if mine(item):
                 if dims == 2:
                     out = np.zeros((1 << s.y_log, 4), dtype=np.uint64)
-                    check(lib.zk_sparse_kzh2_open(h, s.handle, 1 << n, vp(aux_pos[n].ctypes.data), vp(ones[n].ctypes.data),
+                    check(lib.zk_sparse_kzh2_open(h, s.handle, 1 << n, vp(aux_pos[n].ctypes.data), None,
                                                   vp(point.ctypes.data), m, vp(out.ctypes.data)), "zk_sparse_kzh2_open")
                 else:
                     dy = np.zeros((1 << s.y_log, 12), dtype=np.uint64)
                     cy = np.zeros((1, 8), dtype=np.uint64)
                     fs = np.zeros((1 << s.z_log, 4), dtype=np.uint64)
-                    check(lib.zk_sparse_kzh3_open(h, s.handle, 1 << n, vp(aux_pos[n].ctypes.data), vp(ones[n].ctypes.data),
+                    check(lib.zk_sparse_kzh3_open(h, s.handle, 1 << n, vp(aux_pos[n].ctypes.data), None,
                                                   vp(point.ctypes.data), m, vp(commitments[("s", m)].ctypes.data), vp(dy.ctypes.data),
                                                   vp(cy.ctypes.data), vp(fs.ctypes.data)), "zk_sparse_kzh3_open")
                 n_sparse_open += 1
