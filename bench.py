@@ -841,7 +841,14 @@ def kzh3_leg(env: Env, n=28):
               "zk_kzh_verify_g1")
         verified = bool(verified and ok.value == 1)
     else:
-        digest = hashlib.sha256(c.tobytes() + dx.tobytes() + dy.tobytes() + cy.tobytes() + fs.tobytes()).hexdigest()
+        # the ranks must hold the same opening; Jacobian coordinates of one point differ with the order of the
+        # additions, so the points are compared in affine form
+        def affine_bytes(jac):
+            out = np.zeros((jac.shape[0], 8), dtype=np.uint64)
+            check(lib.zk_g1_normalize(env.ctx.handle, vp(jac.ctypes.data), 0, jac.shape[0], vp(out.ctypes.data), 0), "zk_g1_normalize")
+            return out.tobytes()
+
+        digest = hashlib.sha256(c.tobytes() + affine_bytes(dx) + affine_bytes(dy) + cy.tobytes() + fs.tobytes()).hexdigest()
         all_d = [None] * world
         env.dist.all_gather_object(all_d, digest)
         verified = all(d == all_d[0] for d in all_d)

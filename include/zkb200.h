@@ -18,7 +18,10 @@
  *    the panic / Err(String) the trait in question documents.
  *  - `mem` arguments say where a caller buffer lives: ZK_MEM_HOST or ZK_MEM_DEVICE (a CUDA
  *    device pointer on the context's GPU).  Inputs are never modified.
- *  - A zk_ctx may be shared by host threads; calls on one context are serialised.
+ *  - A zk_ctx may be shared by host threads, as the reference opens its commitments from many rayon workers at
+ *    once (src/dag/mod.rs:893-936): up to ZK_OPT_LANES calls run concurrently, each on a stream and scratch of
+ *    its own; SRS handles and caller buffers are shared and only read.  Sharded calls (a zk_comm) and the calls
+ *    that read the context's statistics take the first lane and are serialised among themselves.
  */
 #ifndef ZKB200_H
 #define ZKB200_H
@@ -69,9 +72,12 @@ uint64_t zk_launch_count(const zk_ctx* ctx);
  * to the same value on every rank.
  * ZK_OPT_EXCHANGE_WAIT_MS (default 16000): roughly how long a kernel of a sharded prove waits for another
  * rank's words before it gives up and the call returns ZK_ERR_TIMEOUT (the ranks are separate processes and
- * may reach a call seconds apart; a service with tight deadlines, or a test, sets it lower). */
+ * may reach a call seconds apart; a service with tight deadlines, or a test, sets it lower).
+ * ZK_OPT_LANES (default 4): how many calls on this context may run at the same time.  Each concurrent call gets a
+ * lane of its own (a stream and grow-only scratch, created when a second, third ... thread first arrives and kept
+ * until zk_free); further callers wait for a free lane.  A single-threaded host only ever uses the first lane. */
 typedef enum zk_option {
-  ZK_OPT_DEVICE_TAIL = 1, ZK_OPT_REPLICATE_LOG = 2, ZK_OPT_PEER_EXCHANGE = 3, ZK_OPT_EXCHANGE_WAIT_MS = 4
+  ZK_OPT_DEVICE_TAIL = 1, ZK_OPT_REPLICATE_LOG = 2, ZK_OPT_PEER_EXCHANGE = 3, ZK_OPT_EXCHANGE_WAIT_MS = 4, ZK_OPT_LANES = 5
 } zk_option;
 int zk_set_option(zk_ctx* ctx, int option, int value);
 /* Diagnostics: the host clock, in microseconds from the first entry, at which each round that the host steps

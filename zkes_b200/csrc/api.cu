@@ -110,29 +110,39 @@ void zk_free(zk_ctx* ctx) {
   delete ctx;
 }
 
-uint64_t zk_launch_count(const zk_ctx* ctx) { return ctx ? ctx->launches.load() : 0; }
+uint64_t zk_launch_count(const zk_ctx* ctx) { return ctx ? ctx->total_launches() : 0; }
 
 int zk_set_option(zk_ctx* ctx, int option, int value) {
   if (!ctx) return fail(ZK_ERR_ARG, "zk_set_option: NULL context");
-  CtxLock lk(ctx);
-  switch (option) {
-    case ZK_OPT_DEVICE_TAIL: ctx->device_tail = value != 0; return ZK_OK;
-    case ZK_OPT_PEER_EXCHANGE: ctx->peer_exchange = value != 0; return ZK_OK;
-    case ZK_OPT_EXCHANGE_WAIT_MS:
-      if (value < 1 || value > 600000) return fail(ZK_ERR_ARG, "zk_set_option: exchange wait out of range (1 .. 600000 ms)");
-      ctx->exchange_wait_ms = (uint32_t)value;
-      return ZK_OK;
-    case ZK_OPT_REPLICATE_LOG:
-      if (value < 0 || value > 30) return fail(ZK_ERR_ARG, "zk_set_option: replicate threshold out of range");
-      ctx->replicate_entries = value == 0 ? 0 : 1ull << value;
-      return ZK_OK;
-    default: return fail(ZK_ERR_ARG, "zk_set_option: unknown option %d", option);
+  CtxLock lk(ctx, true);
+  std::vector<zk_ctx*> all = ctx->lanes;  // an option holds for every lane of the context
+  all.push_back(ctx);
+  for (zk_ctx* c : all) {
+    switch (option) {
+      case ZK_OPT_DEVICE_TAIL: c->device_tail = value != 0; break;
+      case ZK_OPT_PEER_EXCHANGE: c->peer_exchange = value != 0; break;
+      case ZK_OPT_EXCHANGE_WAIT_MS:
+        if (value < 1 || value > 600000) return fail(ZK_ERR_ARG, "zk_set_option: exchange wait out of range (1 .. 600000 ms)");
+        c->exchange_wait_ms = (uint32_t)value;
+        break;
+      case ZK_OPT_REPLICATE_LOG:
+        if (value < 0 || value > 30) return fail(ZK_ERR_ARG, "zk_set_option: replicate threshold out of range");
+        c->replicate_entries = value == 0 ? 0 : 1ull << value;
+        break;
+      case ZK_OPT_LANES:
+        if (value < 1 || value > 64) return fail(ZK_ERR_ARG, "zk_set_option: 1 to 64 lanes");
+        if (c == ctx) ctx->max_lanes = value;
+        break;
+      default: return fail(ZK_ERR_ARG, "zk_set_option: unknown option %d", option);
+    }
   }
+  return ZK_OK;
 }
 
 int zk_round_times(zk_ctx* ctx, double* out_us, uint32_t cap, uint32_t* n) {
   if (!ctx || !n) return fail(ZK_ERR_ARG, "zk_round_times: NULL argument");
-  CtxLock lk(ctx);
+  CtxLock lk(ctx, true);
+  ctx = lk.lane;
   *n = (uint32_t)ctx->round_times.size();
   for (uint32_t i = 0; i < *n && i < cap && out_us; i++) out_us[i] = ctx->round_times[i];
   ctx->round_times.clear();
@@ -143,7 +153,8 @@ void* zk_stream(zk_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
 
 int zk_profile_enable(zk_ctx* ctx, int on) {
   if (!ctx) return fail(ZK_ERR_ARG, "zk_profile_enable: NULL context");
-  CtxLock lk(ctx);
+  CtxLock lk(ctx, true);
+  ctx = lk.lane;
   ZK_CUDA(cudaStreamSynchronize(ctx->stream));
   int rc = ctx->prof_collect();
   if (rc) return rc;
@@ -160,7 +171,8 @@ int zk_profile_enable(zk_ctx* ctx, int on) {
 
 int zk_profile_get(zk_ctx* ctx, int kind, uint64_t* launches, double* ms, double* bytes) {
   if (!ctx || kind < 0 || kind >= zk_ctx::kProfKinds) return fail(ZK_ERR_ARG, "zk_profile_get: bad argument");
-  CtxLock lk(ctx);
+  CtxLock lk(ctx, true);
+  ctx = lk.lane;
   ZK_CUDA(cudaStreamSynchronize(ctx->stream));
   int rc = ctx->prof_collect();
   if (rc) return rc;
@@ -173,6 +185,7 @@ int zk_profile_get(zk_ctx* ctx, int kind, uint64_t* launches, double* ms, double
 int zk_device_alloc(zk_ctx* ctx, size_t bytes, void** out) {
   if (!ctx || !out) return fail(ZK_ERR_ARG, "zk_device_alloc: NULL argument");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaError_t e = cudaMalloc(out, bytes ? bytes : 1);
   if (e != cudaSuccess) {
     cudaGetLastError();
@@ -184,6 +197,7 @@ int zk_device_alloc(zk_ctx* ctx, size_t bytes, void** out) {
 int zk_device_free(zk_ctx* ctx, void* ptr) {
   if (!ctx) return fail(ZK_ERR_ARG, "zk_device_free: NULL context");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   ZK_CUDA(cudaFree(ptr));
   return ZK_OK;
 }
@@ -191,6 +205,7 @@ int zk_device_free(zk_ctx* ctx, void* ptr) {
 int zk_device_copy(zk_ctx* ctx, void* dst, zk_mem dst_mem, const void* src, zk_mem src_mem, size_t bytes) {
   if (!ctx || (bytes && (!dst || !src))) return fail(ZK_ERR_ARG, "zk_device_copy: NULL argument");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   ZK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, ctx->stream));
   ZK_CUDA(cudaStreamSynchronize(ctx->stream));
   (void)dst_mem;
@@ -200,8 +215,10 @@ int zk_device_copy(zk_ctx* ctx, void* dst, zk_mem dst_mem, const void* src, zk_m
 
 int zk_device_sync(zk_ctx* ctx) {
   if (!ctx) return fail(ZK_ERR_ARG, "zk_device_sync: NULL context");
-  CtxLock lk(ctx);
+  CtxLock lk(ctx, true);
+  ctx = lk.lane;
   ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+  for (zk_ctx* l : ctx->lanes) ZK_CUDA(cudaStreamSynchronize(l->stream));
   return ZK_OK;
 }
 
@@ -531,7 +548,8 @@ int linear_prove_impl(zk_ctx* ctx, zk_comm* comm, uint32_t num_var, uint32_t num
   if (num_var < logw) return fail(ZK_ERR_ARG, "linear_prove: %u variables cannot be sharded over %d ranks", num_var, world);
   if (world > 64) return fail(ZK_ERR_ARG, "linear_prove: at most 64 ranks");
 
-  CtxLock lk(ctx);
+  CtxLock lk(ctx, world > 1);  // a sharded prove runs on the lane its communicator was made on
+  ctx = lk.lane;
   const uint32_t n_local = num_var - logw;
   const uint64_t size = 1ull << n_local;
   const int L = (int)num_poly;
@@ -610,6 +628,7 @@ int zk_fold_lsb(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem
   if (k > n) return fail(ZK_ERR_ARG, "invalid size of partial point");
   if (n > 40) return fail(ZK_ERR_ARG, "fold_lsb: n %u too large", n);
   CtxLock lk(ctx);
+  ctx = lk.lane;
   const uint64_t size = 1ull << n;
   const uint64_t in_elems = evals_mem == ZK_MEM_HOST ? size : 0;
   Fr* base = nullptr;

@@ -38,6 +38,7 @@ int zk_permute_by_ranges(zk_ctx* ctx, uint32_t n, uint32_t elem_bytes, const voi
   }
   if (covered != n) return fail(ZK_ERR_ARG, "ranges must cover all variables exactly once");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   const uint64_t bytes = (1ull << n) * elem_bytes;
   const size_t in_b = evals_mem == ZK_MEM_HOST ? align_up(bytes, 256) : 0, out_b = out_mem == ZK_MEM_HOST ? align_up(bytes, 256) : 0;
@@ -65,6 +66,7 @@ int zk_fix_variables_int(zk_ctx* ctx, uint32_t num_vars, const void* t, zk_mem t
   if (k > num_vars) return fail(ZK_ERR_ARG, "fix_variables_int: %u challenges for %u variables", k, num_vars);
   if (num_vars > 34) return fail(ZK_ERR_ARG, "fix_variables_int: num_vars %u too large", num_vars);
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   const uint64_t n_rows = 1ull << k, m_cols = 1ull << (num_vars - k);
   const uint64_t in_bytes = (1ull << num_vars) * 16;

@@ -41,6 +41,7 @@ int zk_sumcheck_sparse_bool_prove(zk_ctx* ctx, uint32_t num_var, uint32_t n_term
   const uint32_t K = (uint32_t)total;
 
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   const uint64_t size = 1ull << num_var;
   char* base = nullptr;
@@ -130,6 +131,7 @@ int zk_sumcheck_general_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, 
     if (!tables[i]) return fail(ZK_ERR_ARG, "Polynomial %u has incorrect size", i);
 
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   const uint64_t size = 1ull << num_var;
   const uint64_t all = (uint64_t)nt + 1;  // tables + eq

@@ -255,6 +255,7 @@ int zk_kzh_srs_setup_sharded(zk_ctx* ctx, int rank, int world, int dims, uint32_
   int rc = alloc_srs(ctx, dims, n, rank, world, &s);
   if (rc) return rc;
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t st = ctx->stream;
   const uint64_t nx = 1ull << s->x_log, ny = 1ull << s->y_log, nz = dims == 3 ? 1ull << s->z_log : 0;
   char* base = nullptr;
@@ -300,6 +301,7 @@ int zk_kzh_srs_upload(zk_ctx* ctx, int dims, uint32_t n, const uint64_t* h_full,
   int rc = alloc_srs(ctx, dims, n, 0, 1, &s);
   if (rc) return rc;
   CtxLock lk(ctx);
+  ctx = lk.lane;
   const uint64_t* src[3] = {h_full, h_mid, h_low};
   for (int k = 0; k < 3; k++)
     if (s->count[k]) ZK_CUDA(cudaMemcpyAsync(s->h[k], src[k], s->count[k] * sizeof(Affine), cudaMemcpyDefault, ctx->stream));
@@ -313,6 +315,7 @@ void zk_kzh_srs_free(zk_ctx* ctx, zk_kzh_srs* srs) {
   if (!srs) return;
   if (ctx) {
     CtxLock lk(ctx);
+  ctx = lk.lane;
     cudaStreamSynchronize(ctx->stream);
     for (int k = 0; k < 3; k++) cudaFree(srs->h[k]);
   }
@@ -331,6 +334,7 @@ int zk_kzh_srs_read(zk_ctx* ctx, const zk_kzh_srs* srs, int which, uint64_t offs
   if (!ctx || !srs || !out || which < 0 || which > 2) return fail(ZK_ERR_ARG, "kzh_srs_read: bad argument");
   if (offset + count > srs->count[which]) return fail(ZK_ERR_ARG, "kzh_srs_read: range past the end");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   ZK_CUDA(cudaMemcpyAsync(out, srs->h[which] + offset, count * sizeof(Affine), cudaMemcpyDeviceToHost, ctx->stream));
   ZK_CUDA(cudaStreamSynchronize(ctx->stream));
   return ZK_OK;
@@ -341,6 +345,7 @@ int zk_kzh_commit(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uin
   if (!ctx || !srs || !evals || !c_affine_out || !d_x_jac_out) return fail(ZK_ERR_ARG, "kzh_commit: NULL argument");
   if (poly_n > srs->n) return fail(ZK_ERR_ARG, "Cannot extend to fewer variables");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t st = ctx->stream;
   const uint32_t n = srs->n;
   const uint64_t size = 1ull << n, rows = 1ull << srs->x_log;
@@ -379,6 +384,7 @@ int zk_kzh2_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uint
   if (srs->dims != 2) return fail(ZK_ERR_ARG, "kzh2_open: the SRS is not a KZH2 SRS");
   if (poly_n > srs->n) return fail(ZK_ERR_ARG, "Cannot extend to fewer variables");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t st = ctx->stream;
   const uint32_t n = srs->n;
   const uint64_t size = 1ull << n, ny = 1ull << srs->y_log;
@@ -414,6 +420,7 @@ int zk_kzh3_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint32_t poly_n, const uint
   if (srs->dims != 3) return fail(ZK_ERR_ARG, "kzh3_open: the SRS is not a KZH3 SRS");
   if (poly_n > srs->n) return fail(ZK_ERR_ARG, "Cannot extend to fewer variables");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t st = ctx->stream;
   const uint32_t n = srs->n, xl = srs->x_log;
   const uint64_t size = 1ull << n, nyz = 1ull << (srs->y_log + srs->z_log);
@@ -454,7 +461,8 @@ static int kzh_open_sharded_impl(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs* s
   if (k3 && (!d_x_jac || !d_y_jac_out || !c_y_affine_out)) return fail(ZK_ERR_ARG, "kzh_open_sharded: a KZH3 opening needs d_x, d_y and c_y");
   const int world = comm_world(comm), rank = comm_rank(comm);
   if (world != srs->world || rank != srs->rank) return fail(ZK_ERR_ARG, "kzh_open_sharded: the SRS was set up for rank %d of %d", srs->rank, srs->world);
-  CtxLock lk(ctx);
+  CtxLock lk(ctx, true);
+  ctx = lk.lane;
   cudaStream_t st = ctx->stream;
   const uint32_t n = srs->n, xl = srs->x_log;
   const uint64_t lo_n = 1ull << (n - xl), hi_n = 1ull << xl, hi_local = hi_n / world, slab = hi_local * lo_n;
@@ -511,6 +519,7 @@ int zk_kzh_verify_g1(zk_ctx* ctx, const zk_kzh_srs* srs, const uint64_t* point, 
   if (srs->dims == 3 && (!d_y_jac || !c_y_affine)) return fail(ZK_ERR_ARG, "kzh_verify_g1: a KZH3 opening carries d_y and c_y");
   if (srs->world != 1) return fail(ZK_ERR_ARG, "kzh_verify_g1: needs a whole (unsharded) SRS");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t st = ctx->stream;
   const bool k3 = srs->dims == 3;
   const uint32_t n = srs->n, xl = srs->x_log, yl = srs->y_log, zl = srs->z_log;
@@ -597,6 +606,7 @@ int zk_sparse_kzh2_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const 
   if (srs->dims != 2) return fail(ZK_ERR_ARG, "sparse_kzh2_open: the SRS is not a KZH2 SRS");
   if (srs->world != 1) return fail(ZK_ERR_ARG, "sparse_kzh2_open: needs an unsharded SRS");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t st = ctx->stream;
   const uint64_t ny = 1ull << srs->y_log;
   std::vector<uint64_t> pt;
@@ -628,6 +638,7 @@ int zk_sparse_kzh3_open(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const 
   const uint32_t take_n = point_len < srs->n ? point_len : srs->n;
   if (take_n) memcpy(pt.data(), point, (size_t)take_n * 32);
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t st = ctx->stream;
   const uint64_t nyz = 1ull << (srs->y_log + srs->z_log);
   char* base = nullptr;

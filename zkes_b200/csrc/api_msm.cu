@@ -48,6 +48,7 @@ int msm_entry(zk_ctx* ctx, const uint64_t* bases, zk_mem bases_mem, uint64_t n_b
   if (rows == 0) return ZK_OK;
   if (rows >= (1ull << 31) || n >= (1ull << 31)) return fail(ZK_ERR_ARG, "%s: dimensions too large", who);
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   size_t need = 4096 + rows * sizeof(Jacobian) + 256;
   if (bases_mem == ZK_MEM_HOST) need += n_bases * sizeof(Affine) + 256;
@@ -122,6 +123,7 @@ int zk_g1_normalize(zk_ctx* ctx, const uint64_t* jac, zk_mem jac_mem, uint64_t n
   if (!ctx || (n && (!jac || !affine_out))) return fail(ZK_ERR_ARG, "g1_normalize: NULL argument");
   if (n == 0) return ZK_OK;
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   char* base = nullptr;
   int rc = ctx->reserve_work(n * (sizeof(Jacobian) + sizeof(Affine)) + 1024, (void**)&base);
@@ -145,17 +147,26 @@ int zk_g1_normalize(zk_ctx* ctx, const uint64_t* jac, zk_mem jac_mem, uint64_t n
 
 int zk_msm_work(zk_ctx* ctx, uint64_t* calls, uint64_t* entries, uint64_t* buckets, int reset) {
   if (!ctx) return fail(ZK_ERR_ARG, "msm_work: NULL context");
-  CtxLock lk(ctx);
-  if (calls) *calls = ctx->msm_calls;
-  if (entries) *entries = ctx->msm_entries_sum;
-  if (buckets) *buckets = ctx->msm_bucket_sum;
+  CtxLock lk(ctx, true);
+  ctx = lk.lane;
+  uint64_t c = ctx->msm_calls, e = ctx->msm_entries_sum, b = ctx->msm_bucket_sum;
+  for (zk_ctx* l : ctx->lanes) {  // lanes at rest: a caller reads this between its calls
+    c += l->msm_calls;
+    e += l->msm_entries_sum;
+    b += l->msm_bucket_sum;
+    if (reset) l->msm_calls = l->msm_entries_sum = l->msm_bucket_sum = 0;
+  }
+  if (calls) *calls = c;
+  if (entries) *entries = e;
+  if (buckets) *buckets = b;
   if (reset) ctx->msm_calls = ctx->msm_entries_sum = ctx->msm_bucket_sum = 0;
   return ZK_OK;
 }
 
 int zk_msm_last_stats(zk_ctx* ctx, int* window_bits, int* windows, int* max_bits, uint64_t* entries, uint64_t* buckets) {
   if (!ctx) return fail(ZK_ERR_ARG, "msm_last_stats: NULL context");
-  CtxLock lk(ctx);
+  CtxLock lk(ctx, true);
+  ctx = lk.lane;
   if (window_bits) *window_bits = ctx->last_msm.window_bits;
   if (windows) *windows = ctx->last_msm.windows;
   if (max_bits) *max_bits = ctx->last_msm.max_bits;

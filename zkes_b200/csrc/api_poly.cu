@@ -43,6 +43,7 @@ int zk_eq_table(zk_ctx* ctx, uint32_t k, const uint64_t* point, uint64_t* out, z
   if (!ctx || !out || (k && !point)) return fail(ZK_ERR_ARG, "eq_table: NULL argument");
   if (k > 34) return fail(ZK_ERR_ARG, "eq_table: k %u too large", k);
   CtxLock lk(ctx);
+  ctx = lk.lane;
   const uint64_t size = 1ull << k;
   Fr* base = nullptr;
   int rc = ctx->reserve_work((k + 8 + (out_mem == ZK_MEM_HOST ? size : 0)) * sizeof(Fr), (void**)&base);
@@ -61,6 +62,7 @@ int zk_weighted_fold_from_right(zk_ctx* ctx, uint32_t n, const uint64_t* evals, 
   if (!ctx || !evals || !out || !weights) return fail(ZK_ERR_ARG, "weighted_fold_from_right: NULL argument");
   if (k > n || n > 34) return fail(ZK_ERR_ARG, "weighted_fold_from_right: bad dimensions");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   const uint64_t size = 1ull << n, lo_n = 1ull << (n - k), hi_n = 1ull << k;
   const size_t in_elems = evals_mem == ZK_MEM_HOST ? size : 0;
@@ -92,6 +94,7 @@ int zk_mle_eval(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem evals_mem
   if (!ctx || !evals || !out || (n && !point)) return fail(ZK_ERR_ARG, "mle_eval: NULL argument");
   if (n > 34) return fail(ZK_ERR_ARG, "mle_eval: n %u too large", n);
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   const uint64_t size = 1ull << n;
   const size_t in_elems = evals_mem == ZK_MEM_HOST ? size : 0;
@@ -123,6 +126,7 @@ int zk_fix_from_right(zk_ctx* ctx, uint32_t n, const uint64_t* evals, zk_mem eva
   if (k > n) return fail(ZK_ERR_ARG, "invalid size of partial point");
   if (n > 34) return fail(ZK_ERR_ARG, "fix_from_right: n %u too large", n);
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   const uint64_t size = 1ull << n, lo_n = 1ull << (n - k);
   const size_t in_elems = evals_mem == ZK_MEM_HOST ? size : 0;

@@ -25,7 +25,8 @@ static int msm_g1_sharded_impl(zk_ctx* ctx, zk_comm* comm, const uint64_t* local
                       const uint64_t* local_scalars, zk_mem scalars_mem, uint64_t n_local, uint64_t* out_jac) {
   if (!ctx || !comm || !out_jac) return fail(ZK_ERR_ARG, "msm_g1_sharded: NULL argument");
   if (n_local && (!local_bases || !local_scalars)) return fail(ZK_ERR_ARG, "msm_g1_sharded: NULL input");
-  CtxLock lk(ctx);
+  CtxLock lk(ctx, true);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   char* base = nullptr;
   size_t need = 4096 + al(sizeof(Jacobian));
@@ -71,7 +72,8 @@ static int kzh_commit_sharded_impl(zk_ctx* ctx, zk_comm* comm, const zk_kzh_srs*
     return fail(ZK_ERR_ARG, "kzh_commit_sharded: NULL argument");
   if (comm_world(comm) != srs->world || comm_rank(comm) != srs->rank)
     return fail(ZK_ERR_ARG, "kzh_commit_sharded: the SRS was set up for rank %d of %d", srs->rank, srs->world);
-  CtxLock lk(ctx);
+  CtxLock lk(ctx, true);
+  ctx = lk.lane;
   cudaStream_t st = ctx->stream;
   const uint64_t slab = srs->count[0], rows = 1ull << srs->x_log, rows_local = rows / srs->world;
   char* base = nullptr;
@@ -125,7 +127,8 @@ static int fix_from_right_sharded_impl(zk_ctx* ctx, zk_comm* comm, uint32_t n, c
   uint32_t logw = 0;
   while ((1 << logw) < world) logw++;
   if (k > n || k < logw) return fail(ZK_ERR_ARG, "fix_from_right_sharded: k = %u must cover the %u sharded variables", k, logw);
-  CtxLock lk(ctx);
+  CtxLock lk(ctx, true);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   const uint64_t lo_n = 1ull << (n - k), hi_n = 1ull << k, hi_local = hi_n / world, slab = hi_local * lo_n;
   const uint32_t splits = from_right_splits(lo_n, hi_local, ctx->sm_count);

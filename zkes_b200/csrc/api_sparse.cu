@@ -39,7 +39,8 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
   if (!fs && !tr) return fail(ZK_ERR_ARG, "sparse_dense_prove: neither a callback nor a transcript was given");
   if (!final_eval || (total_var && (!round_msgs || !challenges))) return fail(ZK_ERR_ARG, "sparse_dense_prove: NULL output");
 
-  CtxLock lk(ctx);
+  CtxLock lk(ctx, comm != nullptr);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   const uint32_t K = (uint32_t)nnz;
   // Sharded: every rank must leave the entry form at the same round (the dense rounds exchange

@@ -39,6 +39,7 @@ int zk_sparse_kzh_commit(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const
   if (srs->world != 1) return fail(ZK_ERR_ARG, "sparse_kzh_commit: needs an unsharded SRS");
   if (nnz >> 31) return fail(ZK_ERR_ARG, "sparse_kzh_commit: too many entries");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t st = ctx->stream;
   const uint64_t rows = 1ull << srs->x_log;
   const uint32_t low_bits = srs->n - srs->x_log;

@@ -103,6 +103,7 @@ int zk_g1_compress(zk_ctx* ctx, const uint64_t* affine, zk_mem affine_mem, uint6
   if (!ctx || (n && (!affine || !out))) return fail(ZK_ERR_ARG, "g1_compress: NULL argument");
   if (n == 0) return ZK_OK;
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   char* base = nullptr;
   const size_t in_b = affine_mem == ZK_MEM_HOST ? n * sizeof(Affine) : 0, out_b = out_mem == ZK_MEM_HOST ? n * 32 : 0;
@@ -128,6 +129,7 @@ int zk_g1_decompress(zk_ctx* ctx, const uint8_t* in, zk_mem in_mem, uint64_t n, 
   if (!ctx || (n && (!in || !affine_out))) return fail(ZK_ERR_ARG, "g1_decompress: NULL argument");
   if (n == 0) return ZK_OK;
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   char* base = nullptr;
   const size_t in_b = in_mem == ZK_MEM_HOST ? n * 32 : 0, out_b = out_mem == ZK_MEM_HOST ? n * sizeof(Affine) : 0;

@@ -377,7 +377,8 @@ int zk_comm_init(zk_ctx* ctx, int rank, int world, const uint8_t unique_id[128],
   if (world & (world - 1)) return fail(ZK_ERR_ARG, "comm_init: the number of ranks must be a power of two");
   int rc = load_nccl();
   if (rc) return rc;
-  CtxLock lk(ctx);
+  CtxLock lk(ctx, true);
+  ctx = lk.lane;
   zk_comm* c = new zk_comm();
   c->rank = rank;
   c->world = world;
@@ -403,7 +404,8 @@ int zk_comm_peer_exchange(const zk_comm* c) { return c && c->peer_ok ? 1 : 0; }
 
 int zk_comm_wait_selftest(zk_ctx* ctx, uint32_t polls) {
   if (!ctx || polls == 0 || polls > (1u << 22)) return fail(ZK_ERR_ARG, "comm_wait_selftest: polls must be in 1 .. 2^22");
-  CtxLock lk(ctx);
+  CtxLock lk(ctx, true);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   ExchangeBox* box = nullptr;
   cudaError_t e = cudaMalloc(&box, sizeof(ExchangeBox));
@@ -438,7 +440,8 @@ int zk_comm_wait_selftest(zk_ctx* ctx, uint32_t polls) {
 void zk_comm_free(zk_ctx* ctx, zk_comm* c) {
   if (!c) return;
   if (ctx) {
-    CtxLock lk(ctx);
+    CtxLock lk(ctx, true);
+  ctx = lk.lane;
     cudaStreamSynchronize(ctx->stream);
     peer_teardown(c);
     cudaFree(c->gather_buf);

@@ -33,7 +33,61 @@ int zk_ctx::setup() {
   return 0;
 }
 
+zk_ctx* zk_ctx::acquire_lane(bool primary_only) {
+  std::unique_lock<std::mutex> lk(pool_mu);
+  for (;;) {
+    if (!busy) {
+      busy = true;
+      return this;
+    }
+    if (!primary_only) {
+      for (zk_ctx* l : lanes)
+        if (!l->busy) {
+          l->busy = true;
+          return l;
+        }
+      if ((int)lanes.size() + 1 < max_lanes) {
+        zk_ctx* l = new zk_ctx();
+        l->device = device;
+        l->primary = this;
+        l->replicate_entries = replicate_entries;
+        l->peer_exchange = peer_exchange;
+        l->device_tail = device_tail;
+        l->exchange_wait_ms = exchange_wait_ms;
+        if (l->setup() == 0) {
+          l->busy = true;
+          lanes.push_back(l);
+          return l;
+        }
+        l->teardown();  // no memory for another lane: wait for a free one instead
+        delete l;
+        max_lanes = (int)lanes.size() + 1;
+      }
+    }
+    pool_cv.wait(lk);
+  }
+}
+
+void zk_ctx::release_lane(zk_ctx* lane) {
+  {
+    std::lock_guard<std::mutex> lk(pool_mu);
+    lane->busy = false;
+  }
+  pool_cv.notify_all();
+}
+
+uint64_t zk_ctx::total_launches() const {
+  uint64_t n = launches.load();
+  for (const zk_ctx* l : lanes) n += l->launches.load();
+  return n;
+}
+
 void zk_ctx::teardown() {
+  for (zk_ctx* l : lanes) {
+    l->teardown();
+    delete l;
+  }
+  lanes.clear();
   cudaSetDevice(device);
   if (stream) cudaStreamSynchronize(stream);
   if (side_stream) cudaStreamSynchronize(side_stream);

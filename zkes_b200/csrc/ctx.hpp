@@ -2,6 +2,7 @@
 #pragma once
 #include <atomic>
 #include <chrono>
+#include <condition_variable>
 #include <cstdarg>
 #include <cstring>
 #include <mutex>
@@ -85,8 +86,20 @@ struct zk_ctx {
   uint64_t msm_entries_sum = 0;  // digit entries (= bucket additions) of every MSM since the last zk_msm_work reset
   uint64_t msm_bucket_sum = 0;   // buckets reduced by those MSMs
   uint64_t msm_calls = 0;
-  std::mutex mu;
   std::atomic<uint64_t> launches{0};
+  // Lanes.  The handle a caller holds is the primary lane; calls that arrive while it is busy (the reference opens
+  // its commitments from many rayon workers at once, dag/mod.rs:893-905) run on further lanes, each a context of
+  // its own (stream, scratch, mailbox) on the same device, created when first needed and kept.  Device objects
+  // the caller passes in (SRS handles, device buffers) are shared and only read.
+  zk_ctx* primary = nullptr;        // on an extra lane: the handle it belongs to
+  std::vector<zk_ctx*> lanes;       // on the primary: the extra lanes
+  int max_lanes = 4;                // lanes in all, the primary included (ZK_OPT_LANES)
+  bool busy = false;                // guarded by the primary's pool_mu
+  std::mutex pool_mu;
+  std::condition_variable pool_cv;
+  zk_ctx* acquire_lane(bool primary_only);
+  void release_lane(zk_ctx* lane);
+  uint64_t total_launches() const;
 
   // Optional per-kernel-kind timing with CUDA events on the context's stream.
   static constexpr int kProfKinds = 8;
@@ -157,9 +170,18 @@ int sharded_call(zk_comm* comm, const char* name, F&& body) {
   return rc;
 }
 
-// Serialises calls on a context and makes its device current for the calling thread.
+// Gives the calling thread a lane of the context for the duration of a call and makes its device current.  Entry
+// points go on with `ctx = lk.lane`.  primary_only: the call needs the primary lane itself (sharded calls, whose
+// communicator is tied to it, and calls that read or set state kept there); it waits until that lane is free.
 struct CtxLock {
-  std::unique_lock<std::mutex> lk;
-  explicit CtxLock(zk_ctx* c) : lk(c->mu) { cudaSetDevice(c->device); }
+  zk_ctx* owner;
+  zk_ctx* lane;
+  explicit CtxLock(zk_ctx* c, bool primary_only = false) : owner(c->primary ? c->primary : c) {
+    lane = owner->acquire_lane(primary_only);
+    cudaSetDevice(lane->device);
+  }
+  ~CtxLock() { owner->release_lane(lane); }
+  CtxLock(const CtxLock&) = delete;
+  CtxLock& operator=(const CtxLock&) = delete;
 };
 }  // namespace zk

