@@ -28,6 +28,18 @@ def test_library_exports_every_declared_symbol():
         assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
 
 
+def test_rust_declarations_cover_the_header():
+    """INTEGRATION.md shows the Rust `extern "C"` block a maintainer adds: it must name exactly the functions the
+    header declares, each once."""
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    blocks = re.findall(r"```rust(.*?)```", text, flags=re.S)
+    ext = [b for b in blocks if 'extern "C" {' in b]
+    assert len(ext) == 1
+    names = re.findall(r"pub fn (zk_[a-z0-9_]+)\(", ext[0])
+    assert sorted(names) == declared_symbols()
+    assert len(names) == len(set(names))
+
+
 def test_transcript_matches_oracle():
     from zkes_b200 import Transcript
     rnd = random.Random(3)

@@ -60,3 +60,46 @@ def test_commitment_transcript_bytes(ctx):
     c2 = kzh.commit(ctx, srs2, DenseMLPoly.from_evaluations(f[:4]))
     assert c3.to_transcript_bytes(ctx) == o.g1_serialize_compressed(c3.c)
     assert c2.to_transcript_bytes(ctx) == b""
+
+
+def test_srs_file_and_opening_round_trip(ctx, tmp_path):
+    """`{n}.srs` written from a device SRS and read back gives the same G1 vectors (and hands the G2 part through);
+    a KZH3 opening survives its bincode form, and its point bytes are the compressed encoding the oracle gives."""
+    import random
+
+    import pyoracle as o
+    from zkes_b200 import DenseMLPoly, curve, kzh, wire
+
+    rnd = random.Random(8)
+    n = 7
+    xl, yl, zl = o.kzh3_degrees(n)
+    tx, ty, tz = ([rnd.randrange(1, o.R_MOD) for _ in range(1 << lg)] for lg in (xl, yl, zl))
+    srs = kzh.KZHSRS.setup(ctx, 3, n, o.g1_mul(o.G1_GEN, 5), tx, ty, tau_z=tz)
+    g2 = {k: bytes(rnd.randrange(256) for _ in range(64 * c)) for k, c in (("v_x", 1 << xl), ("v_y", 1 << yl), ("v_z", 1 << zl), ("v", 1))}
+    path = tmp_path / wire.srs_file_name(n)
+    kzh.store_kzh3_srs(ctx, srs, path, g2["v_x"], g2["v_y"], g2["v_z"], g2["v"])
+    loaded, g2_back = kzh.load_kzh3_srs(ctx, path, n)
+    assert g2_back == g2
+    for which, count in ((0, 1 << n), (1, 1 << (yl + zl)), (2, 1 << zl)):
+        assert loaded.read(which, 0, count) == srs.read(which, 0, count)
+    with open(path, "rb") as f:
+        raw = wire.read_kzh3_srs(f)
+    osrs = o.KZH3SRS(n, 5, tx, ty, tz)
+    assert raw["h_z"] == b"".join(o.g1_serialize_compressed(p) for p in osrs.h_z)
+    with pytest.raises(ValueError):
+        kzh.load_kzh3_srs(ctx, path, n + 1)
+    # an opening through bincode and back
+    poly = DenseMLPoly.from_evaluations([rnd.randrange(o.R_MOD) for _ in range(1 << n)])
+    com = kzh.commit(ctx, loaded, poly)
+    pt = [rnd.randrange(o.R_MOD) for _ in range(n)]
+    d_x, d_y, c_y, f_star = kzh.kzh3_open(ctx, loaded, pt, com, poly)
+    dy_jac = curve.affine_to_array(d_y)
+    jac = lambda pts: kzh._jac_array(pts)  # noqa: E731
+    data = kzh.kzh3_opening_to_bincode(ctx, com.d_x_jac, jac(d_y), c_y, f_star)
+    bx, by, bc, fn, fe = wire.kzh3_opening_from_bincode(data)
+    assert curve.deserialize_compressed(ctx, bx) == d_x and curve.deserialize_compressed(ctx, by) == d_y
+    assert curve.deserialize_compressed(ctx, bc) == [c_y] and (fn, fe) == (zl, f_star)
+    assert bc == o.g1_serialize_compressed(c_y)
+    del dy_jac
+    srs.close()
+    loaded.close()

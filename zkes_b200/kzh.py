@@ -180,3 +180,58 @@ def sparse_kzh3_open(ctx, srs: KZHSRS, point, com: KZHCommitment, evaluations: d
     check(lib.zk_sparse_kzh3_open(ctx.handle, srs.handle, len(evaluations), _p(idx), _p(vals), _p(pt), len(point),
                                   _p(com.d_x_jac), _p(dy), _p(cy), _p(fs)), "zk_sparse_kzh3_open")
     return com.d_x, curve.jacobian_to_affine_py(dy), curve.affine_from_array(cy)[0], from_mont_array(fs)
+
+
+# ---- file formats (zkes_b200/wire.py): `{n}.srs` and bincode openings, with the points coded on the device
+def store_kzh3_srs(ctx, srs: KZHSRS, path, v_x: bytes = b"", v_y: bytes = b"", v_z: bytes = b"", v: bytes = bytes(64)):
+    """store_kzh3_srs (src/crypto/srs_storage.rs:15-35): the G1 vectors of the device-resident SRS in compressed form;
+    the G2 vectors (64-byte compressed points, kept by the caller: the verifier side is not on the device) pass through."""
+    from . import wire
+    assert srs.dims == 3
+    blobs = []
+    for which, count in ((0, 1 << srs.n), (1, 1 << (srs.y_log + srs.z_log)), (2, 1 << srs.z_log)):
+        pts = np.zeros((count, 8), dtype=np.uint64)
+        check(lib.zk_kzh_srs_read(ctx.handle, srs.handle, which, 0, count, _p(pts)), "zk_kzh_srs_read")
+        out = np.zeros(count * 32, dtype=np.uint8)
+        check(lib.zk_g1_compress(ctx.handle, _p(pts), ZK_MEM_HOST, count, _p(out), ZK_MEM_HOST), "zk_g1_compress")
+        blobs.append(out.tobytes())
+    with open(path, "wb") as f:
+        wire.write_kzh3_srs(f, (1 << srs.x_log, 1 << srs.y_log, 1 << srs.z_log), blobs[0], blobs[1], blobs[2], v_x, v_y, v_z, v)
+
+
+def load_kzh3_srs(ctx, path, n: int):
+    """load_kzh3_srs (srs_storage.rs:39-58) -> (device SRS, {"v_x", "v_y", "v_z", "v"}: the G2 part as stored)."""
+    from . import wire
+    with open(path, "rb") as f:
+        d = wire.read_kzh3_srs(f)
+    arrays = []
+    for name in ("h_xyz", "h_yz", "h_z"):
+        count = len(d[name]) // 32
+        src = np.frombuffer(d[name], dtype=np.uint8).copy()
+        pts = np.zeros((count, 8), dtype=np.uint64)
+        check(lib.zk_g1_decompress(ctx.handle, _p(src), ZK_MEM_HOST, count, _p(pts), ZK_MEM_HOST), "zk_g1_decompress")
+        arrays.append(pts)
+    h = c_void_p()
+    check(lib.zk_kzh_srs_upload(ctx.handle, 3, n, _p(arrays[0]), _p(arrays[1]), _p(arrays[2]), ZK_MEM_HOST, ctypes.byref(h)),
+          "zk_kzh_srs_upload")
+    srs = KZHSRS(ctx, 3, n, h)
+    if d["degrees"] != (1 << srs.x_log, 1 << srs.y_log, 1 << srs.z_log):
+        srs.close()
+        raise ValueError(f"the file holds degrees {d['degrees']}, not those of {n} variables")
+    return srs, {k: d[k] for k in ("v_x", "v_y", "v_z", "v")}
+
+
+def kzh3_opening_to_bincode(ctx, d_x_jac: np.ndarray, d_y_jac: np.ndarray, c_y, f_star) -> bytes:
+    """The bincode form of KZH3Opening (kzh3.rs:104-117, util/serialization.rs:91-98): projective points are written
+    in compressed affine form, as ark-serialize does for a Projective."""
+    from . import wire
+    blobs = []
+    for jac in (d_x_jac, d_y_jac):
+        n = jac.shape[0]
+        aff = np.zeros((n, 8), dtype=np.uint64)
+        check(lib.zk_g1_normalize(ctx.handle, _p(jac), ZK_MEM_HOST, n, _p(aff), ZK_MEM_HOST), "zk_g1_normalize")
+        out = np.zeros(n * 32, dtype=np.uint8)
+        check(lib.zk_g1_compress(ctx.handle, _p(aff), ZK_MEM_HOST, n, _p(out), ZK_MEM_HOST), "zk_g1_compress")
+        blobs.append(out.tobytes())
+    return wire.kzh3_opening_to_bincode(blobs[0], blobs[1], curve.serialize_compressed(ctx, [c_y]),
+                                        len(f_star).bit_length() - 1, f_star)
