@@ -110,7 +110,9 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
   bool pending = false;  // the dense table still has to be folded by pend_r (done together with the next fold)
   Fr pend_r = Fr::zero();
   auto other_buf = [&](const Fr* cur) { return cur == b_buf[0] ? b_buf[1] : b_buf[0]; };
-  int e = 0;             // which entry buffers are current
+  const int e = 0;       // the entries are updated in place
+  bool e_pending = false;  // the entries still have to be bound on e_r (the next message kernel does it)
+  Fr e_r = Fr::zero();
   uint32_t k_upper = K;  // bound on the live entry count
   Fr challenge = Fr::zero();
   uint64_t S = size;
@@ -125,8 +127,13 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
         b_cur = nb;
         pending = false;
       }
+      if (e_pending) {  // the entries still carry the last challenge
+        launch_sparse_bind(e_idx[e], e_val[e], counts + e, k_upper, e_r, ctx->sm_count, s);
+        ctx->launches++;
+        e_pending = false;
+      }
       ZK_CUDA(cudaMemsetAsync(a_dense, 0, S * sizeof(Fr), s));
-      launch_scatter(e_idx[e], e_val[e], counts + e, k_upper, a_dense, ctx->sm_count, s);
+      launch_scatter_runs(e_idx[e], e_val[e], counts + e, k_upper, a_dense, ctx->sm_count, s);
       ctx->launches++;
       const Fr* d_cur[2] = {a_dense, b_cur};
       bool done = false;
@@ -142,8 +149,8 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
     }
     const RoundScratch sc = ctx->next_msg_scratch(comm != nullptr);
     // per live entry: index + value read, one 64-byte pair of b gathered
-    ctx->prof_begin(ZK_PROF_SPARSE_MSG, 104.0 * k_upper);
-    launch_sparse_msg(e_idx[e], e_val[e], counts + e, k_upper, b_cur, pending ? &pend_r : nullptr, sc, s);
+    ctx->prof_begin(ZK_PROF_SPARSE_MSG, (e_pending ? 144.0 : 104.0) * k_upper);
+    launch_sparse_msg(e_idx[e], e_val[e], counts + e, k_upper, b_cur, pending ? &pend_r : nullptr, e_pending ? &e_r : nullptr, sc, s);
     ctx->prof_end();
     ctx->launches++;
     rc = fs_round(ctx, comm, 3, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
@@ -182,13 +189,14 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
       b_cur = nb;
     }
     if (beside) ZK_CUDA(cudaEventRecord(ctx->ev_join, fs_stream));
-    ctx->prof_begin(ZK_PROF_SPARSE_FOLD, 80.0 * k_upper, 3);
-    ctx->launches += launch_sparse_fold(e_idx[e], e_val[e], counts + e, k_upper, challenge, block_counts, e_idx[e ^ 1],
-                                        e_val[e ^ 1], counts + (e ^ 1), s);
-    ctx->prof_end();
+    // the entries are bound on this challenge by the next message kernel (or at the hand-over), in place
+    e_pending = true;
+    e_r = challenge;
     if (beside) ZK_CUDA(cudaStreamWaitEvent(s, ctx->ev_join, 0));
-    e ^= 1;
-    if ((uint64_t)k_upper > S / 2) k_upper = (uint32_t)(S / 2);
+  }
+  if (!finished && e_pending) {  // the entry form ran to the end (no entries anywhere): bind the last challenge
+    launch_sparse_bind(e_idx[e], e_val[e], counts + e, k_upper, e_r, ctx->sm_count, s);
+    ctx->launches++;
   }
   if (!finished) {  // no entries, or no variables: the entry form ran to the end
     launch_sd_final(e_idx[e], e_val[e], counts + e, b_cur, ctx->final_out, s);

@@ -162,8 +162,12 @@ int launch_resident(int num_poly, const Fr* const* src, Fr* const* ping, Fr* con
                     Fr* out_chal, cudaStream_t stream, const PeerExchange* px = nullptr);
 
 // sparse.cu
-void launch_sparse_msg(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
-                       const Fr* pending, const RoundScratch& sc, cudaStream_t s);
+void launch_sparse_msg(uint32_t* idx, Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
+                       const Fr* pending, const Fr* bind, const RoundScratch& sc, cudaStream_t s);
+void launch_sparse_bind(uint32_t* idx, Fr* val, const uint32_t* count, uint32_t upper, const Fr& r, int sm_count,
+                        cudaStream_t s);
+void launch_scatter_runs(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, Fr* dense,
+                         int sm_count, cudaStream_t s);
 int launch_sparse_fold(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr& r,
                        uint32_t* block_counts, uint32_t* idx_out, Fr* val_out, uint32_t* count_out, cudaStream_t s);
 void launch_scatter(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, Fr* dense,

@@ -34,11 +34,24 @@ __device__ __forceinline__ bool is_leader(const uint32_t* idx, uint32_t i, uint3
 
 // With DEFERRED the dense table has not been folded by the previous challenge yet: the two
 // values an entry pair needs are folded on the fly from four consecutive entries.
-template <bool DEFERRED>
-__global__ void __launch_bounds__(kSpThreads) k_sparse_msg(const uint32_t* __restrict__ idx, const Fr* __restrict__ val,
+//
+// The message is additive over the entries: with (b0, b1) the dense pair at an entry's pair position,
+//   s(0) = sum over even entries v b0,   s(1) = sum over odd entries v b1,
+//   s(2) = sum_y (2 v1 - v0)(2 b1 - b0) = sum over even entries v (b0 - 2 b1) + sum over odd entries v (4 b1 - 2 b0),
+// so an entry never looks at its neighbour and costs two products whatever its parity: v times the dense value
+// on its own side (added to s(0) or s(1) by a mask, so that the warp does not branch on the parity) and v times
+// e = b0 - 2 b1 or -2 e.
+//
+// The fold of the entries is additive in the same way: binding r on a table sends an even entry (pos, v) to
+// (pos / 2, (1 - r) v) and an odd one to (pos / 2, r v).  Two entries that land on one position are simply both
+// kept (the list stays sorted, and every sum above is linear in v), so the entries are never merged or
+// compacted while the prover is in entry form; with FOLD the kernel binds the previous round's challenge on
+// its entries first and writes them back in place, which makes one launch per round.
+template <bool DEFERRED, bool FOLD>
+__global__ void __launch_bounds__(kSpThreads) k_sparse_msg(uint32_t* __restrict__ idx, Fr* __restrict__ val,
                                                            const uint32_t* __restrict__ count,
                                                            const Fr* __restrict__ dense, const FixedMul<FrParams> pend,
-                                                           const MsgSink sink) {
+                                                           const FixedMul<FrParams> bind, const MsgSink sink) {
   const uint32_t n = *count;
   Wide acc[3];
 #pragma unroll
@@ -47,23 +60,16 @@ __global__ void __launch_bounds__(kSpThreads) k_sparse_msg(const uint32_t* __res
     for (int k = 0; k < 16; k++) acc[c].v[k] = 0;
   int pending = 0;
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-    // everything that depends on i alone is loaded at once (the partner's value speculatively), so that
-    // only the gather of the dense pair waits for an earlier load
-    const uint32_t pos = idx[i];
-    const uint32_t prev = i ? idx[i - 1] : 0u;
-    const bool has_next = i + 1 < n;
-    const uint32_t next = has_next ? idx[i + 1] : 0u;
-    const Fr va = ld_fr(val + i);
-    const Fr vb = has_next ? ld_fr(val + i + 1) : Fr::zero();
-    const bool even = (pos & 1u) == 0;
-    if (!(even || i == 0 || prev != pos - 1)) continue;  // the odd partner of the entry before it
-    Fr v0 = Fr::zero(), v1 = Fr::zero();
-    if (even) {
-      v0 = va;
-      if (has_next && next == pos + 1) v1 = vb;
-    } else {
-      v1 = va;
+    uint32_t pos = idx[i];
+    Fr v = ld_fr(val + i);
+    if (FOLD) {
+      const Fr t = mul_fixed(bind, v);  // r v
+      v = (pos & 1u) ? t : sub(v, t);
+      pos >>= 1;
+      idx[i] = pos;
+      st_fr(val + i, v);
     }
+    const bool odd = (pos & 1u) != 0;
     Fr b0, b1;
     if (DEFERRED) {
       const Fr* q = dense + 4 * (uint64_t)(pos >> 1);
@@ -74,13 +80,26 @@ __global__ void __launch_bounds__(kSpThreads) k_sparse_msg(const uint32_t* __res
       b0 = ld_fr(dense + (pos & ~1u));
       b1 = ld_fr(dense + (pos | 1u));
     }
+    const Fr e = sub(b0, dbl(b1));
+    const Fr e_odd = neg(dbl(e));
+    Fr side, two;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+      side.v[k] = odd ? b1.v[k] : b0.v[k];
+      two.v[k] = odd ? e_odd.v[k] : e.v[k];
+    }
     Wide w;
-    mul_wide(w, v0.v, b0.v);
-    wide_add(acc[0], w);
-    mul_wide(w, v1.v, b1.v);
-    wide_add(acc[1], w);
-    const Fr v2 = add(v1, sub(v1, v0)), b2 = add(b1, sub(b1, b0));
-    mul_wide(w, v2.v, b2.v);
+    mul_wide(w, v.v, side.v);
+    const uint32_t m1 = odd ? 0xffffffffu : 0u, m0 = ~m1;
+    Wide w0, w1;
+#pragma unroll
+    for (int k = 0; k < 16; k++) {
+      w0.v[k] = w.v[k] & m0;
+      w1.v[k] = w.v[k] & m1;
+    }
+    wide_add(acc[0], w0);
+    wide_add(acc[1], w1);
+    mul_wide(w, v.v, two.v);
     wide_add(acc[2], w);
     if (++pending == kLazyProducts) {
 #pragma unroll
@@ -185,6 +204,33 @@ __global__ void k_scatter(const uint32_t* __restrict__ idx, const Fr* __restrict
     st_fr(dense + idx[i], ld_fr(val + i));
 }
 
+// Entries bound by r in place (the step k_sparse_msg<., true> does on the fly), for the hand-over to the dense form.
+__global__ void k_sparse_bind(uint32_t* __restrict__ idx, Fr* __restrict__ val, const uint32_t* __restrict__ count,
+                              const FixedMul<FrParams> bind) {
+  const uint32_t n = *count;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const uint32_t pos = idx[i];
+    const Fr v = ld_fr(val + i);
+    const Fr t = mul_fixed(bind, v);
+    idx[i] = pos >> 1;
+    st_fr(val + i, (pos & 1u) ? t : sub(v, t));
+  }
+}
+
+// Dense table from a sorted entry list that may hold several entries per position: the first entry of a run adds
+// up its run (a run is at most 2^rounds long and short in practice) and writes the position.
+__global__ void k_scatter_runs(const uint32_t* __restrict__ idx, const Fr* __restrict__ val,
+                               const uint32_t* __restrict__ count, Fr* dense) {
+  const uint32_t n = *count;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const uint32_t pos = idx[i];
+    if (i && idx[i - 1] == pos) continue;
+    Fr s = ld_fr(val + i);
+    for (uint32_t j = i + 1; j < n && idx[j] == pos; j++) s = add(s, ld_fr(val + j));
+    st_fr(dense + pos, s);
+  }
+}
+
 // 1 when idx[0..n) is strictly increasing and below `limit`, else 0.
 __global__ void k_check_sorted(const uint32_t* __restrict__ idx, uint32_t n, uint64_t limit, uint32_t* bad) {
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
@@ -227,15 +273,32 @@ inline int blocks_for(uint64_t n, int threads, int cap) {
 
 }  // namespace
 
-// pending: the challenge the dense table still has to be folded by, or nullptr.
-void launch_sparse_msg(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
-                       const Fr* pending, const RoundScratch& sc, cudaStream_t s) {
+// pending: the challenge the dense table still has to be folded by, or nullptr.  bind: the challenge the entries
+// still have to be bound on (done first, in place), or nullptr.
+void launch_sparse_msg(uint32_t* idx, Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
+                       const Fr* pending, const Fr* bind, const RoundScratch& sc, cudaStream_t s) {
   const int cap = sc.sm_count * 4 < sc.max_blocks ? sc.sm_count * 4 : sc.max_blocks;
   const int grid = blocks_for(upper, kSpThreads, cap);
-  if (pending)
-    k_sparse_msg<true><<<grid, kSpThreads, 0, s>>>(idx, val, count, dense, make_fixed_mul(*pending), sc.sink);
+  const FixedMul<FrParams> pt = pending ? make_fixed_mul(*pending) : FixedMul<FrParams>();
+  const FixedMul<FrParams> bt = bind ? make_fixed_mul(*bind) : FixedMul<FrParams>();
+  if (pending && bind)
+    k_sparse_msg<true, true><<<grid, kSpThreads, 0, s>>>(idx, val, count, dense, pt, bt, sc.sink);
+  else if (pending)
+    k_sparse_msg<true, false><<<grid, kSpThreads, 0, s>>>(idx, val, count, dense, pt, bt, sc.sink);
+  else if (bind)
+    k_sparse_msg<false, true><<<grid, kSpThreads, 0, s>>>(idx, val, count, dense, pt, bt, sc.sink);
   else
-    k_sparse_msg<false><<<grid, kSpThreads, 0, s>>>(idx, val, count, dense, FixedMul<FrParams>(), sc.sink);
+    k_sparse_msg<false, false><<<grid, kSpThreads, 0, s>>>(idx, val, count, dense, pt, bt, sc.sink);
+}
+
+void launch_sparse_bind(uint32_t* idx, Fr* val, const uint32_t* count, uint32_t upper, const Fr& r, int sm_count,
+                        cudaStream_t s) {
+  k_sparse_bind<<<blocks_for(upper, 256, sm_count * 8), 256, 0, s>>>(idx, val, count, make_fixed_mul(r));
+}
+
+void launch_scatter_runs(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, Fr* dense,
+                         int sm_count, cudaStream_t s) {
+  k_scatter_runs<<<blocks_for(upper, 256, sm_count * 8), 256, 0, s>>>(idx, val, count, dense);
 }
 
 int launch_sparse_fold(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, const Fr& r,
