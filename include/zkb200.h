@@ -75,9 +75,13 @@ uint64_t zk_launch_count(const zk_ctx* ctx);
  * may reach a call seconds apart; a service with tight deadlines, or a test, sets it lower).
  * ZK_OPT_LANES (default 4): how many calls on this context may run at the same time.  Each concurrent call gets a
  * lane of its own (a stream and grow-only scratch, created when a second, third ... thread first arrives and kept
- * until zk_free); further callers wait for a free lane.  A single-threaded host only ever uses the first lane. */
+ * until zk_free); further callers wait for a free lane.  A single-threaded host only ever uses the first lane.
+ * ZK_OPT_AHEAD_LOG (default 17): once the tables of an unsharded dense prove with the built-in transcript are down
+ * to 2^value entries, the multi-round kernel tabulates each message as a polynomial in the challenge before it while
+ * that challenge is still being hashed (identical outputs; at most three tables); 0 keeps every round in step. */
 typedef enum zk_option {
-  ZK_OPT_DEVICE_TAIL = 1, ZK_OPT_REPLICATE_LOG = 2, ZK_OPT_PEER_EXCHANGE = 3, ZK_OPT_EXCHANGE_WAIT_MS = 4, ZK_OPT_LANES = 5
+  ZK_OPT_DEVICE_TAIL = 1, ZK_OPT_REPLICATE_LOG = 2, ZK_OPT_PEER_EXCHANGE = 3, ZK_OPT_EXCHANGE_WAIT_MS = 4, ZK_OPT_LANES = 5,
+  ZK_OPT_AHEAD_LOG = 6
 } zk_option;
 int zk_set_option(zk_ctx* ctx, int option, int value);
 /* Diagnostics: the host clock, in microseconds from the first entry, at which each round that the host steps

@@ -15,6 +15,7 @@ ZK_OPT_REPLICATE_LOG = 2
 ZK_OPT_PEER_EXCHANGE = 3
 ZK_OPT_EXCHANGE_WAIT_MS = 4
 ZK_OPT_LANES = 5
+ZK_OPT_AHEAD_LOG = 6
 ZK_OK, ZK_ERR_ARG, ZK_ERR_OOM, ZK_ERR_CUDA, ZK_ERR_TIMEOUT, ZK_ERR_FS_CALLBACK, ZK_ERR_COMM = 0, -1, -2, -3, -4, -5, -6
 
 FS_ROUND_FN = ctypes.CFUNCTYPE(c_int, c_void_p, POINTER(c_uint64), c_uint32, POINTER(c_uint64))

@@ -110,6 +110,13 @@ void zk_free(zk_ctx* ctx) {
   delete ctx;
 }
 
+#ifdef ZK_RESIDENT_TRACE
+int zk_debug_resident_trace(zk_ctx* ctx, unsigned long long* out, int n) {
+  cudaStreamSynchronize(ctx->stream);
+  return (int)cudaMemcpy(out, reinterpret_cast<char*>(ctx->resident_sh) + 4096, 8 * (size_t)n, cudaMemcpyDeviceToHost);
+}
+#endif
+
 uint64_t zk_launch_count(const zk_ctx* ctx) { return ctx ? ctx->total_launches() : 0; }
 
 int zk_set_option(zk_ctx* ctx, int option, int value) {
@@ -128,6 +135,10 @@ int zk_set_option(zk_ctx* ctx, int option, int value) {
       case ZK_OPT_REPLICATE_LOG:
         if (value < 0 || value > 30) return fail(ZK_ERR_ARG, "zk_set_option: replicate threshold out of range");
         c->replicate_entries = value == 0 ? 0 : 1ull << value;
+        break;
+      case ZK_OPT_AHEAD_LOG:
+        if (value < 0 || value > 24) return fail(ZK_ERR_ARG, "zk_set_option: run-ahead threshold out of range (0 .. 24)");
+        c->ahead_log = (uint32_t)value;
         break;
       case ZK_OPT_LANES:
         if (value < 1 || value > 64) return fail(ZK_ERR_ARG, "zk_set_option: 1 to 64 lanes");
@@ -265,7 +276,8 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
   uint32_t resident_rounds = 0;  // rounds the resident kernel has produced (their results are still on the device)
   // Reads back what the device-resident rounds left in ctx->tail_out: `left` messages and challenges
   // (rounds round_offset + first ...), the transcript state and the resident kernel's error word.
-  auto collect_device_rounds = [&](uint32_t first, uint32_t left, bool resident) -> int {
+  // Rounds from `canonical_from` on (counted like `first`) come back as canonical integers.
+  auto collect_device_rounds = [&](uint32_t first, uint32_t left, bool resident, uint32_t canonical_from = 0xffffffffu) -> int {
     ResidentShared* sh = reinterpret_cast<ResidentShared*>(ctx->resident_sh);
     const size_t bytes = ((size_t)left * (L + 2)) * sizeof(Fr) + sizeof(StrobeState);
     unsigned int* h_flags = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(ctx->host_small) + 8192 - 16);
@@ -274,10 +286,14 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
     ZK_CUDA(cudaStreamSynchronize(ctx->stream));
     if (resident && h_flags[2] >= 2) return fail(ZK_ERR_TIMEOUT, "sharded rounds: another rank's partial sums or table chunk did not arrive");
     if (resident && h_flags[2] != 0) return fail(ZK_ERR_TIMEOUT, "resident round kernel: a wait for a challenge ran out");
-    const Fr* h_msgs = reinterpret_cast<const Fr*>(ctx->host_small);
-    const Fr* h_chal = h_msgs + (size_t)left * (L + 1);
+    Fr* h_msgs = reinterpret_cast<Fr*>(ctx->host_small);
+    Fr* h_chal = h_msgs + (size_t)left * (L + 1);
     const StrobeState* h_st = reinterpret_cast<const StrobeState*>(h_chal + left);
     for (uint32_t k = 0; k < left; k++) {
+      if (first + k >= canonical_from) {
+        for (int c = 0; c <= L; c++) h_msgs[(size_t)k * (L + 1) + c] = to_mont(h_msgs[(size_t)k * (L + 1) + c]);
+        h_chal[k] = to_mont(h_chal[k]);
+      }
       for (int c = 0; c <= L; c++)
         fr_store(round_msgs + ((uint64_t)(round_offset + first + k) * (L + 1) + c) * 4, h_msgs[(size_t)k * (L + 1) + c]);
       fr_store(challenges + 4 * (uint64_t)(round_offset + first + k), h_chal[k]);
@@ -359,6 +375,25 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
       StrobeState* d_st = reinterpret_cast<StrobeState*>(d_chal + left);
       ResidentShared* sh = reinterpret_cast<ResidentShared*>(ctx->resident_sh);
       bool resident = false;
+      if (round == 0 && rounds >= 2 && L <= 3 && ctx->ahead_log >= 2 &&
+          (size_t)left * (L + 2) * sizeof(Fr) + sizeof(StrobeState) <= 8192 - 16) {
+        // All rounds in one cooperative launch: in step while the tables are large, prepared ahead of their
+        // challenges once they are small, final values included.
+        uint32_t ahead_from = 0;
+        const ResidentToEnd te = {ctx->ahead_log, ctx->final_out, d_st, &ahead_from};
+        ctx->prof_begin(ZK_PROF_ROUND, 64.0 * L * (double)(cur_size / 2) + 192.0 * L * (double)(cur_size / 2));
+        const int lrc = launch_resident(L, cur, ping, pong, cur_size, rounds, st, ctx->rs.sink.partials, ctx->rs.max_blocks,
+                                        ctx->sm_count, sh, d_msgs, d_chal, ctx->stream, nullptr, &te);
+        ctx->prof_end();
+        if (lrc == 0) {
+          ctx->launches++;
+          int rc = collect_device_rounds(0, left, true, ahead_from);
+          if (rc) return rc;
+          *finals_done = true;
+          return ZK_OK;
+        }
+        // no cooperative launch on this device: the kernels below
+      }
       if (cur_size > kTailMax) {
         // rounds whose tables (before the fold) are above kTailMax entries: log2(size) - 10 folds + the first
         uint32_t lg = 0;

@@ -25,8 +25,8 @@ int zk_ctx::setup() {
   rs.sink.seq = 0;
   ZK_CUDA(cudaMalloc(&final_out, sizeof(Fr) * 16));
   ZK_CUDA(cudaMalloc(&tail_out, 8192));
-  ZK_CUDA(cudaMalloc(&resident_sh, 1024));
-  ZK_CUDA(cudaMemsetAsync(resident_sh, 0, 1024, stream));
+  ZK_CUDA(cudaMalloc(&resident_sh, 8192));
+  ZK_CUDA(cudaMemsetAsync(resident_sh, 0, 8192, stream));
   ZK_CUDA(cudaMalloc(&tail_buf, sizeof(Fr) * 64 * kMaxPolys * 4));
   ZK_CUDA(cudaHostAlloc(&host_small, 8192, cudaHostAllocDefault));
   ZK_CUDA(cudaStreamSynchronize(stream));
@@ -54,6 +54,7 @@ zk_ctx* zk_ctx::acquire_lane(bool primary_only) {
         l->peer_exchange = peer_exchange;
         l->device_tail = device_tail;
         l->exchange_wait_ms = exchange_wait_ms;
+        l->ahead_log = ahead_log;
         if (l->setup() == 0) {
           l->busy = true;
           lanes.push_back(l);

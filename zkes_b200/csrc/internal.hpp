@@ -155,11 +155,17 @@ __device__ __forceinline__ bool peer_exchange_sum(const PeerExchange& px, unsign
 
 // resident.cu
 struct ResidentShared;
+struct ResidentToEnd {    // launch_resident runs to the end of the protocol
+  uint32_t ahead_log;     // tables of at most 2^ahead_log entries: rounds prepared ahead of their challenge
+  Fr* out_final;          // L table values at the challenge point, then their product
+  StrobeState* out_st;    // transcript state after the last challenge
+  uint32_t* ahead_from;   // host: first round whose message and challenge come back as canonical integers
+};
 // px != nullptr: the tables are this rank's chunks of a sharded instance; every round's message is the
 // sum over the ranks, exchanged through the peer boxes by the block that completes the local sums.
 int launch_resident(int num_poly, const Fr* const* src, Fr* const* ping, Fr* const* pong, uint64_t size, uint32_t rounds,
                     const StrobeState& st, Fr* partials, int max_blocks, int sm_count, ResidentShared* sh, Fr* out_msgs,
-                    Fr* out_chal, cudaStream_t stream, const PeerExchange* px = nullptr);
+                    Fr* out_chal, cudaStream_t stream, const PeerExchange* px = nullptr, const ResidentToEnd* to_end = nullptr);
 
 // sparse.cu
 void launch_sparse_msg(uint32_t* idx, Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,

@@ -1,13 +1,22 @@
 // Several rounds of the dense prover in one cooperative launch.
 //
-// With the built-in transcript nothing of a round has to leave the device: every block folds and
-// sums its share of the tables, the last block to arrive adds the partial messages, runs the
-// Fiat-Shamir step (one warp, transcript.rs:27-42 over STROBE / Keccak-f), and publishes the
-// challenge's multiplier table; the other blocks wait for it and start the next round.  That
-// replaces a launch, a read-back and a host transcript step per round by one device-side
-// hand-over.  The launch is cooperative so that all blocks are resident together; every wait is
-// bounded and reports through ResidentShared::error instead of spinning on.
-// Rounds: linear_prover.rs:59-72; message :82-140; fold :151-178.
+// With the built-in transcript nothing of a round has to leave the device.  The launch is cooperative so that
+// all blocks are resident together; every wait is bounded and reports through ResidentShared::error instead of
+// spinning on.  Rounds: linear_prover.rs:59-72; message :82-140; fold :151-178; final :181-190.
+//
+// Large tables, rounds "in step": every block folds and sums its share of the tables, the last block to arrive
+// adds the partial messages, runs the Fiat-Shamir step (one warp, transcript.rs:27-42 over STROBE / Keccak-f) and
+// publishes the challenge's multiplier table; the other blocks wait for it and start the next round.
+//
+// Small tables, rounds "ahead" (ahead_rounds below): a round is then all latency - a dependent field product
+// takes about 0.5 us, the transcript step 5 us, a hand-over between blocks 0.5 us - and in step these add up.
+// Block 0 does nothing but the transcript chain, and the other blocks prepare message t + 1 while r_t is still
+// being hashed: folding by r_t is linear in r_t, so message t + 1 is a polynomial of degree L in r_t,
+//     s_{t+1}(c) = G(c, r_t),   G(c, rho) = sum_y prod_i bilinear(T_i[4y .. 4y+3]; rho, c),
+// the round polynomial of two variables at once.  The workers tabulate G on {0..L}^2 right after the fold that
+// produced the tables; block 0 interpolates the message when r_t is out (one product deep) and goes straight on to
+// hash it.  Every value is an exact field element, so the messages are the reference's, bit for bit.  This mode
+// runs to the end of the protocol, final values included.
 #include <cstring>
 #include "internal.hpp"
 #include "round_pass.cuh"
@@ -18,6 +27,7 @@ namespace {
 
 constexpr int kThreads = kRoundThreads;
 constexpr int kWarps = kRoundWarps;
+static_assert(sizeof(ResidentShared) <= 8192, "the context allocates 8192 bytes for the hand-over area");
 
 template <int L>
 struct ResidentParams {
@@ -25,16 +35,399 @@ struct ResidentParams {
   Fr* ping[L];
   Fr* pong[L];
   uint64_t size;        // entries per table on entry (a power of two, at least 4)
-  uint32_t rounds;      // messages to produce; the last challenge is left unbound
+  uint32_t rounds;      // messages to produce
   uint32_t spin_limit;  // polls before a wait gives up
+  uint32_t ahead_from;  // first round whose message is prepared ahead of its challenge; >= rounds: none, and the
+                        // last challenge is left unbound.  Otherwise 1 <= ahead_from < rounds, rounds = log2(size),
+                        // and the launch also binds the last challenge and writes the final values.
   StrobeState st;       // transcript state on entry
   Fr* partials;         // gridDim.x * (L + 1)
-  ResidentShared* sh;   // zeroed arrive / seq / error on entry
-  Fr* out_msgs;         // rounds * (L + 1)
-  Fr* out_chal;         // rounds
+  ResidentShared* sh;   // zeroed on entry
+  Fr* out_msgs;         // rounds * (L + 1): Montgomery form for rounds in step, canonical integers for rounds ahead
+  Fr* out_chal;         // rounds: Montgomery form for rounds in step, canonical integers for rounds ahead
+  Fr* out_final;        // rounds ahead: the L table values at the challenge point, then their product
+  StrobeState* out_st;  // rounds ahead: transcript state after the last challenge
   Fr pow2[8];           // 2^(32 j + 64) mod r as plain integers: rows of a multiplier table
+  Fr kconst[L + 1];     // R^(L+1) / prod_{k != j} (j - k) as integers: scales the grid sums for the interpolation
   PeerExchange px;      // px.world > 1: sharded instance, messages are summed over the ranks
 };
+
+#ifdef ZK_RESIDENT_TRACE
+__device__ __forceinline__ void trace_stamp(ResidentShared* sh, int slot) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(sh) + 4096)[slot] = t;
+}
+#define ZK_TRACE(sh, slot) trace_stamp(sh, slot)
+#else
+#define ZK_TRACE(sh, slot)
+#endif
+
+// Field products outside the streaming passes are called, not inlined: a product is about 3.5 KB of code, the
+// rounds of small tables run each piece of code once per round, and what bounds them then is fetching
+// instructions, not executing them.  One shared copy stays in the instruction cache.
+__device__ __noinline__ Fr mul_call(Fr a, Fr b) { return mul(a, b); }
+__device__ __forceinline__ Fr to_mont_call(const Fr& a) { return mul_call(Fr::r2(), a); }
+__device__ __forceinline__ Fr from_mont_call(const Fr& a) {
+  Fr o = Fr::zero();
+  o.v[0] = 1;
+  return mul_call(a, o);
+}
+
+// Bounded wait for a counter to reach `want`; false when it gave up (or another block did).  Called by all the
+// lanes of a warp together, which then poll in lockstep (one transaction per poll): with a single lane in the
+// loop the warp stayed split after the wait and ran what followed - the transcript step - several times slower.
+__device__ __forceinline__ bool wait_counter(const unsigned int* counter, unsigned int want, unsigned int* error, uint32_t limit) {
+  const volatile unsigned int* c = reinterpret_cast<const volatile unsigned int*>(counter);
+  const volatile unsigned int* err = reinterpret_cast<const volatile unsigned int*>(error);
+  uint32_t polls = 0;
+  bool ok = true;
+  while (true) {
+    // lane 0's reading decides for the warp, so that the lanes leave the loop together
+    const unsigned int v = __shfl_sync(0xffffffffu, *c, 0), e = __shfl_sync(0xffffffffu, *err, 0);
+    if (v >= want) break;
+    if (e != 0) {  // another block gave up and said why: leave its code in place
+      ok = false;
+      break;
+    }
+    if (++polls > limit) {
+      if ((threadIdx.x & 31) == 0) atomicCAS(error, 0u, 1u);
+      ok = false;
+      break;
+    }
+    const long long until = clock64() + 96;  // a pause between polls
+    while (clock64() < until) {
+    }
+  }
+  __threadfence();
+  return ok;
+}
+
+__device__ __forceinline__ Fr shfl_xor_fr(const Fr& x, int mask) {
+  Fr r;
+#pragma unroll
+  for (int i = 0; i < 8; i++) r.v[i] = __shfl_xor_sync(0xffffffffu, x.v[i], mask);
+  return r;
+}
+
+// a + k (b - a) for k in 0 .. 3 (additions only).
+__device__ __forceinline__ Fr lin_small(const Fr& a, const Fr& b, int k) {
+  if (k == 0) return a;
+  const Fr d = sub(b, a);
+  Fr r = b;
+  for (int i = 1; i < k; i++) r = add(r, d);
+  return r;
+}
+
+// x mod r for any 256-bit x (x < 6 r).
+__device__ __forceinline__ Fr reduce_256(const Fr& x) {
+  Fr r = x;
+#pragma unroll
+  for (int sh = 2; sh >= 0; sh--) {  // 4 r, 2 r, r
+    uint32_t m[8], d[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+      m[i] = (FrParams::mod(i) << sh) | (sh && i ? FrParams::mod(i - 1) >> (32 - sh) : 0u);
+    const uint32_t borrow = sub8(d, r.v, m);
+#pragma unroll
+    for (int i = 0; i < 8; i++) r.v[i] = borrow ? r.v[i] : d[i];
+  }
+  return r;
+}
+
+// How a warp of a worker block splits a unit of the rounds ahead.  A unit is QW quads of the folded tables
+// (four consecutive entries each).  Lane = ql * LQ + e * LT + ts: quad ql of the unit, entry e of the quad, table
+// slot ts.  Fold: lanes with ts < L bind the challenge on their entry (one product).  Grid: the (L + 1)^2 points
+// of a quad are dealt to its LQ lanes, point pt = w + k * LQ to lane w = e * LT + ts (L - 1 products each).
+template <int L>
+struct AheadSplit {
+  static constexpr int NV = L + 1, NG = NV * NV;
+  static constexpr int LT = L == 1 ? 1 : (L == 2 ? 2 : 4);
+  static constexpr int LQ = 4 * LT;
+  static constexpr int QW = 32 / LQ;
+  static constexpr int PL = (NG + LQ - 1) / LQ;
+};
+
+// The rounds from p.ahead_from to the end.  On entry every block has left the in-step round ahead_from - 1: the
+// tables `cur` (cur_size entries) are the ones message ahead_from - 1 is over, complete and visible, and the
+// challenge of that round is in sh->challenge (Montgomery form) with the transcript state in sh->st.
+template <int L>
+__device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const Fr* (&cur)[L], uint64_t cur_size, uint8_t* stream,
+                                             uint64_t* keccak_scratch, int* ok_flag, int* flag) {
+  using S = AheadSplit<L>;
+  constexpr int NV = S::NV, NG = S::NG, LT = S::LT, LQ = S::LQ, QW = S::QW, PL = S::PL;
+  __shared__ Fr xch[kWarps][32];
+  __shared__ Fr red[kWarps][NG];
+  __shared__ unsigned long long limbs[NG][8];
+  __shared__ Fr lag[NG];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t t0 = p.ahead_from;
+  ResidentShared* sh = p.sh;
+
+  if (blockIdx.x == 0) {
+    // ------------------------------------------------------------------ the transcript chain (one warp)
+    if (warp != 0) return;
+    WarpStrobe ws;
+    ws.scratch = keccak_scratch;
+    ws.a = lane < 25 ? __ldcg(reinterpret_cast<const unsigned long long*>(&sh->st.lanes[lane])) : 0;
+    ws.pos = __ldcg(&sh->st.pos);
+    ws.pos_begin = __ldcg(&sh->st.pos_begin);
+    if (lane == 0) ZK_TRACE(sh, 1);
+    Fr r = from_mont_call(ld_cg_fr(&sh->challenge));  // canonical
+    const int j = lane % NV;
+    for (uint32_t t = t0; t < p.rounds; t++) {
+      // lambda'_j = prod_{k != j} (r - k) / R^(L-1); the grid sums arrive scaled by R^L / prod_{k != j} (j - k)
+      Fr lam;
+      {
+        bool first = true;
+#pragma unroll
+        for (int k = 0; k < NV; k++) {
+          if (k == j) continue;
+          Fr kk = Fr::zero();
+          kk.v[0] = (uint32_t)k;
+          const Fr term = sub(r, kk);
+          lam = first ? term : mul_call(lam, term);
+          first = false;
+        }
+      }
+      int ok = 1;
+      if (lane == 0 && t - t0 < 8) ZK_TRACE(sh, 16 + 4 * (t - t0));
+      ok = wait_counter(&sh->gseq, t + 1, &sh->error, p.spin_limit) ? 1 : 0;
+      if (!ok) return;
+      if (lane == 0 && t - t0 < 8) ZK_TRACE(sh, 17 + 4 * (t - t0));
+      if (lane < NG) lag[lane] = mul_call(lam, ld_cg_fr(&sh->gsum[t & 1][lane]));  // lane = c * NV + j
+      __syncwarp();
+      if (lane < NV) {  // s_t(c), canonical
+        Fr s = lag[lane * NV];
+#pragma unroll
+        for (int k = 1; k < NV; k++) s = add(s, lag[lane * NV + k]);
+        p.out_msgs[(size_t)t * NV + lane] = s;
+        uint8_t* dst = WarpStrobe::round_stream_data(stream, lane);
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+#pragma unroll
+          for (int k = 0; k < 4; k++) dst[4 * i + k] = (uint8_t)(s.v[i] >> (8 * k));
+      }
+      __syncwarp();
+      if (lane == 0 && t - t0 < 8) ZK_TRACE(sh, 18 + 4 * (t - t0));
+      Fr raw;
+      ws.fs_round<L>(stream, lane, raw.v);
+      r = reduce_256(raw);
+      if (lane == 0 && t - t0 < 8) ZK_TRACE(sh, 19 + 4 * (t - t0));
+      if (lane == 0) {
+        p.out_chal[t] = r;
+        sh->rplain[t & 1] = r;
+      }
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) *reinterpret_cast<volatile unsigned int*>(&sh->seq) = t + 1;
+    }
+    if (lane < 25) p.out_st->lanes[lane] = ws.a;
+    if (lane == 0) {
+      p.out_st->pos = ws.pos;
+      p.out_st->pos_begin = ws.pos_begin;
+      p.out_st->cur_flags = 1u | 2u | 4u;
+      p.out_st->pad = 0;
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- workers
+  const uint32_t nbw = gridDim.x - 1;                      // worker blocks
+  const uint64_t wid = (blockIdx.x - 1) + (uint64_t)nbw * warp;  // consecutive units go to different SMs first
+  const uint64_t wtotal = (uint64_t)nbw * kWarps;
+  const int ql = lane / LQ, w = lane % LQ, e = w / LT, ts = w % LT;
+  unsigned int tickets = 0;  // arrivals expected so far at sh->garrive (the same in every block that is still here)
+  Fr r_mont = Fr::zero();
+  // pass `it` = t0 - 1: the grid of message t0 over the tables as they are.  Pass it >= t0: bind r_{it-1}, which
+  // gives the tables of message `it`, then the grid of message it + 1 over them (none after the last message).
+  for (uint32_t it = t0 - 1; it < p.rounds; it++) {
+    const bool do_fold = it >= t0, do_grid = it + 1 < p.rounds;
+    const uint64_t e_out = do_fold ? cur_size >> 1 : cur_size;  // entries of the tables this pass leaves
+    const uint64_t n_q = e_out >> 2;
+    const uint64_t n_units = n_q ? (n_q + QW - 1) / QW : 1;
+    if (blockIdx.x - 1 >= n_units) return;  // no unit in this pass, and none in any later one
+    const unsigned int active = (unsigned int)(n_units < nbw ? n_units : nbw);
+    const int tr_base = 64 + 8 * (int)(it - (t0 - 1));
+    const bool tr_on = blockIdx.x == 1 && threadIdx.x == 0 && it - (t0 - 1) < 8;
+    if (tr_on) ZK_TRACE(sh, tr_base + 0);
+    Fr* dst[L];
+#pragma unroll
+    for (int i = 0; i < L; i++) dst[i] = (it & 1) ? p.ping[i] : p.pong[i];
+    const Fr* my_src = cur[0];  // the table of this lane's slot
+    Fr* my_dst = dst[0];
+#pragma unroll
+    for (int i = 1; i < L; i++) {
+      if (ts == i) {
+        my_src = cur[i];
+        my_dst = dst[i];
+      }
+    }
+    if (it >= t0) {  // the pass before is complete in every block: its tables, and its tickets
+      if (warp == 0) {
+        const bool ok = wait_counter(&sh->gseq, it + 1, &sh->error, p.spin_limit);
+        if (lane == 0) *ok_flag = ok ? 1 : 0;
+      }
+      __syncthreads();
+      if (!*ok_flag) return;
+    }
+    if (tr_on) ZK_TRACE(sh, tr_base + 1);
+    // the first unit's entries do not depend on the challenge: fetch them before waiting for it
+    uint64_t u = wid;
+    Fr a0 = Fr::zero(), a1 = Fr::zero();
+    auto fetch = [&](uint64_t unit) {
+      const uint64_t i = 4 * (unit * QW + ql) + e;
+      if (ts < L && i < e_out) {
+        if (do_fold) {
+          a0 = ld_cg_fr(my_src + 2 * i);
+          a1 = ld_cg_fr(my_src + 2 * i + 1);
+        } else {
+          a0 = ld_cg_fr(my_src + i);
+        }
+      }
+    };
+    if (u < n_units) fetch(u);
+    if (it > t0) {
+      __syncthreads();  // ok_flag is free again
+      if (warp == 0) {
+        const bool ok = wait_counter(&sh->seq, it, &sh->error, p.spin_limit);
+        if (lane == 0) *ok_flag = ok ? 1 : 0;
+      }
+      __syncthreads();
+      if (!*ok_flag) return;
+      r_mont = to_mont_call(ld_cg_fr(&sh->rplain[(it - 1) & 1]));
+    } else if (it == t0) {
+      r_mont = ld_cg_fr(&sh->challenge);
+    }
+    if (tr_on) ZK_TRACE(sh, tr_base + 2);
+    Fr acc[PL];
+#pragma unroll
+    for (int k = 0; k < PL; k++) acc[k] = Fr::zero();
+    for (; u < n_units; u += wtotal) {
+      if (u != wid) fetch(u);
+      const uint64_t q = u * QW + ql, i = 4 * q + e;
+      const bool ent_ok = ts < L && i < e_out;
+      Fr v = a0;
+      if (do_fold) {
+        v = add(a0, mul_call(r_mont, sub(a1, a0)));
+        if (ent_ok) my_dst[i] = v;
+      }
+      xch[warp][lane] = ent_ok ? v : Fr::zero();
+      __syncwarp();
+      if (do_grid && q < n_q) {
+        const Fr* quad = &xch[warp][ql * LQ];  // entry e', table t' at [e' * LT + t']
+#pragma unroll
+        for (int k = 0; k < PL; k++) {
+          const int pt = w + k * LQ;
+          if (pt < NG) {
+            const int c = pt / NV, rho = pt % NV;
+            Fr prod;
+#pragma unroll
+            for (int t = 0; t < L; t++) {
+              const Fr e0 = lin_small(quad[0 * LT + t], quad[1 * LT + t], rho);
+              const Fr e1 = lin_small(quad[2 * LT + t], quad[3 * LT + t], rho);
+              const Fr x = lin_small(e0, e1, c);
+              prod = t == 0 ? x : mul_call(prod, x);
+            }
+            acc[k] = add(acc[k], prod);
+          }
+        }
+      }
+      __syncwarp();
+    }
+    if (tr_on) ZK_TRACE(sh, tr_base + 3);
+    if (do_grid) {
+      // lanes of equal role over the quads of the warp, then the warps of the block as plain 64-bit limb sums,
+      // then the blocks by atomic additions of those limbs: no modular arithmetic until the very end
+#pragma unroll
+      for (int k = 0; k < PL; k++) {
+#pragma unroll
+        for (int off = LQ; off < 32; off <<= 1) acc[k] = add(acc[k], shfl_xor_fr(acc[k], off));
+        const int pt = w + k * LQ;
+        if (ql == 0 && pt < NG) red[warp][pt] = acc[k];
+      }
+      __syncthreads();
+      const int par = (it + 1) & 1;
+      if (threadIdx.x < NG * 8) {
+        const int pt = threadIdx.x >> 3, limb = threadIdx.x & 7;
+        unsigned long long s = 0;
+#pragma unroll
+        for (int ww = 0; ww < kWarps; ww++)
+          if ((blockIdx.x - 1) + (uint64_t)nbw * ww < n_units) s += red[ww][pt].v[limb];
+        atomicAdd(&sh->gacc[par][pt][limb], s);
+      }
+      __threadfence();  // this block's folded entries and its share of the grid, before the ticket
+      __syncthreads();
+      if (tr_on) ZK_TRACE(sh, tr_base + 4);
+      tickets += active;
+      if (threadIdx.x == 0) *flag = atomicAdd(&sh->garrive, 1u) == tickets - 1;
+      __syncthreads();
+      if (tr_on) ZK_TRACE(sh, tr_base + 5);
+      if (*flag) {
+        __threadfence();
+        if (threadIdx.x < NG * 8) {
+          const int pt = threadIdx.x >> 3, limb = threadIdx.x & 7;
+          limbs[pt][limb] = __ldcg(&sh->gacc[par][pt][limb]);
+          sh->gacc[par][pt][limb] = 0;  // for the pass after the next
+        }
+        __syncthreads();
+        if (threadIdx.x < NG) {
+          Wide x;
+#pragma unroll
+          for (int k = 0; k < 16; k++) x.v[k] = 0;
+          unsigned long long carry = 0;
+#pragma unroll
+          for (int k = 0; k < 8; k++) {
+            const unsigned long long v = limbs[threadIdx.x][k];
+            const unsigned long long s = (v & 0xffffffffull) + (carry & 0xffffffffull);
+            x.v[k] = (uint32_t)s;
+            carry = (v >> 32) + (carry >> 32) + (s >> 32);
+          }
+          x.v[8] = (uint32_t)carry;
+          x.v[9] = (uint32_t)(carry >> 32);
+          // the sum of Montgomery forms is G R as an integer: / R, then the constant of this point's column
+          Fr kc = p.kconst[0];
+#pragma unroll
+          for (int k = 1; k < NV; k++)
+            if ((int)(threadIdx.x % NV) == k) kc = p.kconst[k];
+          sh->gsum[par][threadIdx.x] = mul_call(redc<FrParams>(x), kc);
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(&sh->gseq) = it + 2;
+        if (tr_on) ZK_TRACE(sh, tr_base + 6);
+      }
+    } else {
+      __syncthreads();
+    }
+    if (do_fold) {
+#pragma unroll
+      for (int i = 0; i < L; i++) cur[i] = dst[i];
+      cur_size >>= 1;
+    }
+  }
+  // The last pass left two entries per table, folded by unit 0 = this block's warp 0 (block 1 only gets here with
+  // a unit; the others have left), still in its exchange buffer.  Bind the last challenge.
+  if (blockIdx.x != 1 || warp != 0) return;
+  int ok = 1;
+  ok = wait_counter(&sh->seq, p.rounds, &sh->error, p.spin_limit) ? 1 : 0;
+  if (!ok) return;
+  r_mont = to_mont_call(ld_cg_fr(&sh->rplain[(p.rounds - 1) & 1]));
+  if (lane < L) {
+    const Fr b0 = xch[0][0 * LT + lane], b1 = xch[0][1 * LT + lane];
+    const Fr f = add(b0, mul_call(r_mont, sub(b1, b0)));
+    p.out_final[lane] = f;
+    lag[lane] = f;
+  }
+  __syncwarp();
+  if (lane == 0) {
+    Fr prod = lag[0];
+#pragma unroll
+    for (int t = 1; t < L; t++) prod = mul_call(prod, lag[t]);
+    p.out_final[L] = prod;
+    ZK_TRACE(sh, 2);
+  }
+}
 
 template <int L>
 __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const ResidentParams<L> p) {
@@ -49,12 +442,14 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int NV = L + 1;
   if (threadIdx.x == 0) WarpStrobe::init_round_stream<L>(stream);
+  if (blockIdx.x == 0 && threadIdx.x == 0) ZK_TRACE(p.sh, 0);
 
   const Fr* cur[L];
 #pragma unroll
   for (int i = 0; i < L; i++) cur[i] = p.src[i];
   uint64_t cur_size = p.size;
-  const uint64_t warp_global = (uint64_t)blockIdx.x * kWarps + warp, warp_stride = (uint64_t)gridDim.x * kWarps;
+  // consecutive tiles go to different blocks first, so that a small table spreads over the SMs
+  const uint64_t warp_global = blockIdx.x + (uint64_t)gridDim.x * warp, warp_stride = (uint64_t)gridDim.x * kWarps;
 
   for (uint32_t round = 0; round < p.rounds; round++) {
     Fr s[NV];
@@ -72,7 +467,7 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
     // block total -> global; the last block to arrive owns the rest of the round.  Only blocks that
     // had tiles this round hold a non-zero share: the others skip the store and are not read.
     const uint64_t tiles = ((cur_size >> 1) + 31) >> 5;  // cur_size: entries of the table the message is over
-    const unsigned int active = (unsigned int)((tiles + kWarps - 1) / kWarps < gridDim.x ? (tiles + kWarps - 1) / kWarps : gridDim.x);
+    const unsigned int active = (unsigned int)(tiles < gridDim.x ? tiles : gridDim.x);
     if (blockIdx.x < active) {
 #pragma unroll
       for (int c = 0; c < NV; c++) {
@@ -82,7 +477,8 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
       __syncthreads();
       if (threadIdx.x < NV) {
         Fr t = red[0][threadIdx.x];
-        for (int w = 1; w < kWarps; w++) t = add(t, red[w][threadIdx.x]);
+        for (int w = 1; w < kWarps; w++)
+          if (blockIdx.x + (uint64_t)gridDim.x * w < tiles) t = add(t, red[w][threadIdx.x]);
         p.partials[(size_t)blockIdx.x * NV + threadIdx.x] = t;
       }
       __threadfence();  // this block's folded entries and its share, before the ticket
@@ -147,7 +543,7 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
         if (lane <= L) {
           const Fr t = msg[lane];
           p.out_msgs[(size_t)round * NV + lane] = t;
-          const Fr canon = from_mont(t);
+          const Fr canon = from_mont_call(t);
           uint8_t* dst = WarpStrobe::round_stream_data(stream, lane);
 #pragma unroll
           for (int i = 0; i < 8; i++)
@@ -158,8 +554,8 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
         Fr raw;
         ws.fs_round<L>(stream, lane, raw.v);
         if (lane < 8) {  // eight lanes build the eight rows of the challenge's multiplier table
-          const Fr ch = to_mont(raw);
-          const Fr row = mul(ch, p.pow2[lane]);
+          const Fr ch = to_mont_call(raw);
+          const Fr row = mul_call(ch, p.pow2[lane]);
 #pragma unroll
           for (int k = 0; k < 8; k++) p.sh->table.c[lane][k] = row.v[k];
           if (lane == 0) {
@@ -179,28 +575,17 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
     }
     if (round + 1 == p.rounds) break;  // the last challenge is consumed by whoever runs next
     // wait for this round's challenge
-    if (threadIdx.x == 0) {
-      const volatile unsigned int* seq = reinterpret_cast<const volatile unsigned int*>(&p.sh->seq);
-      const volatile unsigned int* err = reinterpret_cast<const volatile unsigned int*>(&p.sh->error);
-      uint32_t polls = 0;
-      int ok = 1;
-      while (*seq < round + 1) {
-        if (*err != 0) {  // another block gave up and said why: leave its code in place
-          ok = 0;
-          break;
-        }
-        if (++polls > p.spin_limit) {
-          atomicCAS(&p.sh->error, 0u, 1u);
-          ok = 0;
-          break;
-        }
-        __nanosleep(64);
-      }
-      __threadfence();
-      ok_flag = ok;
+    if (warp == 0) {
+      const bool ok = wait_counter(&p.sh->seq, round + 1, &p.sh->error, p.spin_limit);
+      if (lane == 0) ok_flag = ok ? 1 : 0;
     }
     __syncthreads();
     if (!ok_flag) return;
+    if (round + 1 == p.ahead_from) {  // the tables are small from here on
+      __syncthreads();
+      if constexpr (L <= 3) ahead_rounds<L>(p, cur, cur_size, stream, keccak_scratch, &ok_flag, &flag);
+      return;
+    }
     if (threadIdx.x < 64) (&r_tab.c[0][0])[threadIdx.x] = __ldcg(&p.sh->table.c[0][0] + threadIdx.x);
     __syncthreads();
   }
@@ -209,7 +594,7 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
 template <int L>
 int launch_resident_t(const Fr* const* src, Fr* const* ping, Fr* const* pong, uint64_t size, uint32_t rounds,
                       const StrobeState& st, Fr* partials, int max_blocks, int sm_count, ResidentShared* sh, Fr* out_msgs,
-                      Fr* out_chal, cudaStream_t stream, const PeerExchange* px) {
+                      Fr* out_chal, cudaStream_t stream, const PeerExchange* px, const ResidentToEnd* to_end) {
   ResidentParams<L> p;
   if (px) {
     p.px = *px;
@@ -243,13 +628,51 @@ int launch_resident_t(const Fr* const* src, Fr* const* ping, Fr* const* pong, ui
   }
   int occ = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_resident<L>, kThreads, 0) != cudaSuccess || occ < 1) return -2;
-  uint64_t grid = ((size >> 1) + 31) / 32;  // tiles of the first round
-  grid = (grid + kWarps - 1) / kWarps;
+  uint64_t grid = ((size >> 1) + 31) / 32;  // tiles of the first round, a warp each
   const uint64_t cap = (uint64_t)sm_count * occ < (uint64_t)max_blocks ? (uint64_t)sm_count * occ : (uint64_t)max_blocks;
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
+  p.ahead_from = rounds;
+  p.out_final = nullptr;
+  p.out_st = nullptr;
+  if (to_end) {
+    // Rounds run ahead once the tables a grid pass reads have at most 2^ahead_log entries: message t is tabulated
+    // over the tables of message t - 1 (size >> (t - 1) entries), at (L + 1)^2 products per four entries.  Needs
+    // a block for the transcript beside at least one worker, a grid of at most kResidentGrid points, one GPU,
+    // and all the rounds of the tables in this launch.
+    if (px || L > 3 || cap < 2 || rounds < 2 || size != (1ull << rounds) || to_end->ahead_log < 2) return -5;
+    uint32_t t = 1;
+    while (t + 1 < rounds && (size >> (t - 1)) > (1ull << to_end->ahead_log)) t++;
+    p.ahead_from = t;
+    // a block per unit of the first pass ahead (and the transcript block), so that the units spread over the SMs
+    const uint64_t quads = (size >> (t - 1)) >> 2;
+    const uint64_t units = quads ? (quads + AheadSplit<L < 4 ? L : 1>::QW - 1) / AheadSplit<L < 4 ? L : 1>::QW : 1;
+    if (grid < units + 1) grid = units + 1 < cap ? units + 1 : cap;
+    p.out_final = to_end->out_final;
+    p.out_st = to_end->out_st;
+    // host field inversions are slow (hundreds of products each): once per process and L
+    struct Consts {
+      Fr k[L + 1];
+      Consts() {
+        for (int j = 0; j <= L; j++) {
+          Fr den = Fr::one();
+          for (int i = 0; i <= L; i++) {
+            if (i == j) continue;
+            const Fr d = j > i ? from_u32<FrParams>((uint32_t)(j - i)) : neg(from_u32<FrParams>((uint32_t)(i - j)));
+            den = mul(den, d);
+          }
+          Fr c = inverse(den);                          // R / den
+          for (int i = 0; i < L; i++) c = to_mont(c);   // R^(L+1) / den
+          k[j] = c;
+        }
+      }
+    };
+    static const Consts consts;
+    for (int j = 0; j <= L; j++) p.kconst[j] = consts.k[j];
+    *to_end->ahead_from = t;
+  }
   void* args[] = {&p};
-  if (cudaMemsetAsync(sh, 0, 16, stream) != cudaSuccess) return -3;
+  if (cudaMemsetAsync(sh, 0, sizeof(ResidentShared), stream) != cudaSuccess) return -3;
   if (cudaLaunchCooperativeKernel((const void*)k_resident<L>, dim3((unsigned)grid), dim3(kThreads), args, 0, stream) !=
       cudaSuccess) {
     cudaGetLastError();
@@ -263,15 +686,18 @@ int launch_resident_t(const Fr* const* src, Fr* const* ping, Fr* const* pong, ui
 // Runs `rounds` rounds on tables of `size` entries.  Afterwards the tables that the last fold
 // wrote are ((rounds - 1) & 1 ? ping : pong) for rounds >= 2 (src for rounds == 1), the last
 // challenge is in sh->challenge and the transcript state in sh->st.  Non-zero: the cooperative
-// launch was not possible and nothing ran.
+// launch was not possible and nothing ran.  With to_end (unsharded, at most three tables, rounds = log2(size) >= 2)
+// the launch runs to the end of the protocol instead: the rounds from *to_end->ahead_from on are prepared ahead of
+// their challenges, their messages and challenges come back as canonical integers (not Montgomery form), and the
+// final values and the transcript state are written to to_end->out_final / out_st.
 int launch_resident(int num_poly, const Fr* const* src, Fr* const* ping, Fr* const* pong, uint64_t size, uint32_t rounds,
                     const StrobeState& st, Fr* partials, int max_blocks, int sm_count, ResidentShared* sh, Fr* out_msgs,
-                    Fr* out_chal, cudaStream_t stream, const PeerExchange* px) {
+                    Fr* out_chal, cudaStream_t stream, const PeerExchange* px, const ResidentToEnd* to_end) {
   switch (num_poly) {
-    case 1: return launch_resident_t<1>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream, px);
-    case 2: return launch_resident_t<2>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream, px);
-    case 3: return launch_resident_t<3>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream, px);
-    case 4: return launch_resident_t<4>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream, px);
+    case 1: return launch_resident_t<1>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream, px, to_end);
+    case 2: return launch_resident_t<2>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream, px, to_end);
+    case 3: return launch_resident_t<3>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream, px, to_end);
+    case 4: return launch_resident_t<4>(src, ping, pong, size, rounds, st, partials, max_blocks, sm_count, sh, out_msgs, out_chal, stream, px, to_end);
     default: return -1;
   }
 }

@@ -47,21 +47,53 @@ __device__ __forceinline__ bool is_leader(const uint32_t* idx, uint32_t i, uint3
 // kept (the list stays sorted, and every sum above is linear in v), so the entries are never merged or
 // compacted while the prover is in entry form; with FOLD the kernel binds the previous round's challenge on
 // its entries first and writes them back in place, which makes one launch per round.
+//
+// The gather of the dense values depends on the entry's position, and a thread has few entries: without care
+// the kernel waits on that chain.  Every thread therefore runs a two-stage pipeline of asynchronous copies into
+// its own shared-memory slots (no registers held): while entry k is computed, the dense values and the value of
+// entry k + 1 are in flight and the position of entry k + 2 is being loaded.
 template <bool DEFERRED, bool FOLD>
-__global__ void __launch_bounds__(kSpThreads) k_sparse_msg(uint32_t* __restrict__ idx, Fr* __restrict__ val,
-                                                           const uint32_t* __restrict__ count,
-                                                           const Fr* __restrict__ dense, const FixedMul<FrParams> pend,
-                                                           const FixedMul<FrParams> bind, const MsgSink sink) {
+__global__ void __launch_bounds__(kSpThreads, 2) k_sparse_msg(uint32_t* __restrict__ idx, Fr* __restrict__ val,
+                                                              const uint32_t* __restrict__ count,
+                                                              const Fr* __restrict__ dense, const FixedMul<FrParams> pend,
+                                                              const FixedMul<FrParams> bind, const MsgSink sink) {
+  constexpr int DCH = DEFERRED ? 8 : 4;  // 16-byte chunks of dense values per entry
+  constexpr int CH = DCH + 2;            // plus the entry's value
+  extern __shared__ uint4 sp_stage[];    // [2 slots][CH chunks][kSpThreads]: a thread's chunks are kSpThreads apart
   const uint32_t n = *count;
+  const uint32_t stride = gridDim.x * blockDim.x;
+  const int tid = threadIdx.x;
+  auto issue = [&](int slot, uint32_t e, uint32_t stored_pos) {
+    const uint32_t pos = FOLD ? stored_pos >> 1 : stored_pos;
+    const uint4* src = reinterpret_cast<const uint4*>(dense + (DEFERRED ? 4 * (uint64_t)(pos >> 1) : (uint64_t)(pos & ~1u)));
+    const uint4* vsrc = reinterpret_cast<const uint4*>(val + e);
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(sp_stage + ((size_t)(slot * CH + c) * kSpThreads + tid));
+      const uint4* g = c < DCH ? src + c : vsrc + (c - DCH);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(g) : "memory");
+    }
+  };
+  auto staged = [&](int slot, int c) { return sp_stage[(size_t)(slot * CH + c) * kSpThreads + tid]; };
   Wide acc[3];
 #pragma unroll
   for (int c = 0; c < 3; c++)
 #pragma unroll
     for (int k = 0; k < 16; k++) acc[c].v[k] = 0;
   int pending = 0;
-  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-    uint32_t pos = idx[i];
-    Fr v = ld_fr(val + i);
+  uint32_t i = blockIdx.x * blockDim.x + tid, inext = i + stride;
+  uint32_t st_cur = i < n ? idx[i] : 0u, st_next = inext < n ? idx[inext] : 0u;
+  if (i < n) issue(0, i, st_cur);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  int slot = 0;
+  while (i < n) {
+    if (inext < n) issue(slot ^ 1, inext, st_next);
+    asm volatile("cp.async.commit_group;" ::: "memory");  // one group per iteration, empty or not
+    const uint32_t inn = inext < n ? inext + stride : inext;  // (no wrap: inext >= n stays put)
+    const uint32_t st_nn = inn < n ? idx[inn] : 0u;
+    asm volatile("cp.async.wait_group 1;" ::: "memory");    // the copies of entry i have landed
+    uint32_t pos = st_cur;
+    Fr v = fr_from_chunks(staged(slot, DCH), staged(slot, DCH + 1));
     if (FOLD) {
       const Fr t = mul_fixed(bind, v);  // r v
       v = (pos & 1u) ? t : sub(v, t);
@@ -72,13 +104,13 @@ __global__ void __launch_bounds__(kSpThreads) k_sparse_msg(uint32_t* __restrict_
     const bool odd = (pos & 1u) != 0;
     Fr b0, b1;
     if (DEFERRED) {
-      const Fr* q = dense + 4 * (uint64_t)(pos >> 1);
-      const Fr t0 = ld_fr(q), t1 = ld_fr(q + 1), t2 = ld_fr(q + 2), t3 = ld_fr(q + 3);
+      const Fr t0 = fr_from_chunks(staged(slot, 0), staged(slot, 1)), t1 = fr_from_chunks(staged(slot, 2), staged(slot, 3));
+      const Fr t2 = fr_from_chunks(staged(slot, 4), staged(slot, 5)), t3 = fr_from_chunks(staged(slot, 6), staged(slot, 7));
       b0 = add(t0, mul_fixed(pend, sub(t1, t0)));
       b1 = add(t2, mul_fixed(pend, sub(t3, t2)));
     } else {
-      b0 = ld_fr(dense + (pos & ~1u));
-      b1 = ld_fr(dense + (pos | 1u));
+      b0 = fr_from_chunks(staged(slot, 0), staged(slot, 1));
+      b1 = fr_from_chunks(staged(slot, 2), staged(slot, 3));
     }
     const Fr e = sub(b0, dbl(b1));
     const Fr e_odd = neg(dbl(e));
@@ -106,7 +138,13 @@ __global__ void __launch_bounds__(kSpThreads) k_sparse_msg(uint32_t* __restrict_
       for (int c = 0; c < 3; c++) wide_trim<FrParams>(acc[c]);
       pending = 0;
     }
+    i = inext;
+    inext = inn;
+    st_cur = st_next;
+    st_next = st_nn;
+    slot ^= 1;
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   Fr s[3];
 #pragma unroll
   for (int c = 0; c < 3; c++) {
@@ -275,20 +313,33 @@ inline int blocks_for(uint64_t n, int threads, int cap) {
 
 // pending: the challenge the dense table still has to be folded by, or nullptr.  bind: the challenge the entries
 // still have to be bound on (done first, in place), or nullptr.
+template <bool D, bool F>
+static void launch_sparse_msg_t(uint32_t* idx, Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
+                                const FixedMul<FrParams>& pt, const FixedMul<FrParams>& bt, const RoundScratch& sc,
+                                cudaStream_t s) {
+  constexpr size_t smem = (size_t)2 * ((D ? 8 : 4) + 2) * kSpThreads * sizeof(uint4);
+  cudaFuncSetAttribute(k_sparse_msg<D, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  int occ = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_sparse_msg<D, F>, kSpThreads, smem) != cudaSuccess || occ < 1) occ = 1;
+  // one wave of resident blocks: every thread walks its entries through the copy pipeline
+  int cap = sc.sm_count * occ;
+  if (cap > sc.max_blocks) cap = sc.max_blocks;
+  const int grid = blocks_for(upper, kSpThreads, cap);
+  k_sparse_msg<D, F><<<grid, kSpThreads, smem, s>>>(idx, val, count, dense, pt, bt, sc.sink);
+}
+
 void launch_sparse_msg(uint32_t* idx, Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
                        const Fr* pending, const Fr* bind, const RoundScratch& sc, cudaStream_t s) {
-  const int cap = sc.sm_count * 4 < sc.max_blocks ? sc.sm_count * 4 : sc.max_blocks;
-  const int grid = blocks_for(upper, kSpThreads, cap);
   const FixedMul<FrParams> pt = pending ? make_fixed_mul(*pending) : FixedMul<FrParams>();
   const FixedMul<FrParams> bt = bind ? make_fixed_mul(*bind) : FixedMul<FrParams>();
   if (pending && bind)
-    k_sparse_msg<true, true><<<grid, kSpThreads, 0, s>>>(idx, val, count, dense, pt, bt, sc.sink);
+    launch_sparse_msg_t<true, true>(idx, val, count, upper, dense, pt, bt, sc, s);
   else if (pending)
-    k_sparse_msg<true, false><<<grid, kSpThreads, 0, s>>>(idx, val, count, dense, pt, bt, sc.sink);
+    launch_sparse_msg_t<true, false>(idx, val, count, upper, dense, pt, bt, sc, s);
   else if (bind)
-    k_sparse_msg<false, true><<<grid, kSpThreads, 0, s>>>(idx, val, count, dense, pt, bt, sc.sink);
+    launch_sparse_msg_t<false, true>(idx, val, count, upper, dense, pt, bt, sc, s);
   else
-    k_sparse_msg<false, false><<<grid, kSpThreads, 0, s>>>(idx, val, count, dense, pt, bt, sc.sink);
+    launch_sparse_msg_t<false, false>(idx, val, count, upper, dense, pt, bt, sc, s);
 }
 
 void launch_sparse_bind(uint32_t* idx, Fr* val, const uint32_t* count, uint32_t upper, const Fr& r, int sm_count,

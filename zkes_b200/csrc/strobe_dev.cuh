@@ -14,14 +14,20 @@ struct StrobeState {
 
 // Hand-over area of the resident multi-round kernel (device global memory).
 struct ResidentShared {
-  unsigned int arrive;       // block tickets, counted up over all rounds
+  unsigned int arrive;       // block tickets of the message sums, counted up over all rounds
   unsigned int seq;          // rounds whose challenge has been published
   unsigned int error;        // non-zero: a bounded wait ran out
-  unsigned int pad;
-  FixedMul<FrParams> table;  // multiplier table of the latest challenge
-  Fr challenge;              // the latest challenge (Montgomery form)
-  StrobeState st;            // transcript state after the latest challenge
+  unsigned int garrive;      // block tickets of the grid sums (rounds whose message is prepared ahead)
+  unsigned int gseq;         // grid of message `gseq - 1` is complete in gsum[(gseq - 1) & 1]
+  unsigned int pad[3];
+  FixedMul<FrParams> table;  // multiplier table of the latest challenge (rounds in step)
+  Fr challenge;              // the latest challenge of a round in step (Montgomery form)
+  StrobeState st;            // transcript state after the latest challenge of a round in step
+  Fr rplain[2];              // rounds ahead: the challenge of round t as a canonical integer in rplain[t & 1]
+  Fr gsum[2][16];            // message t tabulated as a polynomial in the challenge before it, scaled, in gsum[t & 1]
+  unsigned long long gacc[2][16][8];  // the same grid while the blocks add their shares: 64-bit sums of 32-bit limbs
 };
+constexpr int kResidentGrid = 16;  // grid points of a message: (L + 1)^2 for L <= 3
 
 ZK_HD uint64_t rotl64_c(uint64_t x, int n) { return n ? (x << n) | (x >> (64 - n)) : x; }
 
@@ -163,7 +169,9 @@ static __device__ __noinline__ uint2 keccak_f1600_warp(uint2 a, int lane, uint64
   const uint64_t* row = B + 6 * y;
   const int x1 = (x + 1) % 5, x2 = (x + 2) % 5;
   uint32_t lo = a.x, hi = a.y;
-#pragma unroll
+  // Not unrolled: the transcript step runs once per sumcheck round, often on an SM that has not run it before,
+  // and fetching 24 copies of the round body costs more than the loop saves.
+#pragma unroll 1
   for (int round = 0; round < 24; round++) {
     const uint64_t rc = kKeccakRcDev[round];  // uniform load; selected, not branched on, so the warp stays converged
     if (lane < 25) *reinterpret_cast<uint2*>(a_slot) = make_uint2(lo, hi);
@@ -245,7 +253,7 @@ struct WarpStrobe {
   __device__ __forceinline__ void fs_round(uint8_t* stream, int lane, uint32_t* raw) {
     constexpr int kPieces = 2 * (L + 1) + 2;
     uint32_t off = 0, seg_off = 0, seg_pos = pos;
-#pragma unroll
+#pragma unroll 1
     for (int j = 0; j < kPieces; j++) {
       const uint32_t len = j == kPieces - 1 ? 0u : (j == kPieces - 2 ? 13u : ((j & 1) ? 32u : 17u));
       if (lane == 0) stream[off] = (uint8_t)pos_begin;  // the operation's first framing byte
