@@ -76,9 +76,10 @@ uint64_t zk_launch_count(const zk_ctx* ctx);
  * ZK_OPT_LANES (default 4): how many calls on this context may run at the same time.  Each concurrent call gets a
  * lane of its own (a stream and grow-only scratch, created when a second, third ... thread first arrives and kept
  * until zk_free); further callers wait for a free lane.  A single-threaded host only ever uses the first lane.
- * ZK_OPT_AHEAD_LOG (default 17): once the tables of an unsharded dense prove with the built-in transcript are down
- * to 2^value entries, the multi-round kernel tabulates each message as a polynomial in the challenge before it while
- * that challenge is still being hashed (identical outputs; at most three tables); 0 keeps every round in step. */
+ * ZK_OPT_AHEAD_LOG (default 15): an unsharded dense prove with the built-in transcript and at most three tables runs
+ * in one launch; once its tables are down to 2^value entries (four times that for a single table), each message is
+ * tabulated as a polynomial in the challenge before it while that challenge is still being hashed (identical
+ * outputs).  0 keeps every round in step and hands the last rounds to the single-block kernel. */
 typedef enum zk_option {
   ZK_OPT_DEVICE_TAIL = 1, ZK_OPT_REPLICATE_LOG = 2, ZK_OPT_PEER_EXCHANGE = 3, ZK_OPT_EXCHANGE_WAIT_MS = 4, ZK_OPT_LANES = 5,
   ZK_OPT_AHEAD_LOG = 6

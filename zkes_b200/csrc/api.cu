@@ -113,7 +113,7 @@ void zk_free(zk_ctx* ctx) {
 #ifdef ZK_RESIDENT_TRACE
 int zk_debug_resident_trace(zk_ctx* ctx, unsigned long long* out, int n) {
   cudaStreamSynchronize(ctx->stream);
-  return (int)cudaMemcpy(out, reinterpret_cast<char*>(ctx->resident_sh) + 4096, 8 * (size_t)n, cudaMemcpyDeviceToHost);
+  return (int)cudaMemcpy(out, reinterpret_cast<char*>(ctx->resident_sh) + 6144, 8 * (size_t)n, cudaMemcpyDeviceToHost);
 }
 #endif
 

@@ -77,7 +77,7 @@ struct zk_ctx {
   bool sharded_finished = false; // set by the dense round loop of a sharded prove when it gathered the tables and ran to the end
   bool peer_exchange = true;     // sharded proves exchange round messages through peer memory when the ranks could map it
   uint32_t exchange_wait_ms = 16000;  // bound of a device-side wait for another rank's words (ZK_OPT_EXCHANGE_WAIT_MS)
-  uint32_t ahead_log = 17;       // dense tables of at most 2^ahead_log entries: rounds prepared ahead of their challenge (ZK_OPT_AHEAD_LOG)
+  uint32_t ahead_log = 15;       // dense tables of at most 2^ahead_log entries: rounds prepared ahead of their challenge (ZK_OPT_AHEAD_LOG)
   bool device_tail = true;       // run the last dense rounds in the single-block kernel (zk_set_option turns it off)
   // host clock (microseconds since the first entry) at which each host-stepped round of the most recent
   // proves had its challenge: where the time of a prove goes, round by round (zk_round_times)

@@ -27,7 +27,7 @@ namespace {
 
 constexpr int kThreads = kRoundThreads;
 constexpr int kWarps = kRoundWarps;
-static_assert(sizeof(ResidentShared) <= 8192, "the context allocates 8192 bytes for the hand-over area");
+static_assert(sizeof(ResidentShared) <= 6144, "the context allocates 8192 bytes for the hand-over area");
 
 template <int L>
 struct ResidentParams {
@@ -56,7 +56,7 @@ struct ResidentParams {
 __device__ __forceinline__ void trace_stamp(ResidentShared* sh, int slot) {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(sh) + 4096)[slot] = t;
+  reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(sh) + 6144)[slot] = t;
 }
 #define ZK_TRACE(sh, slot) trace_stamp(sh, slot)
 #else
@@ -95,9 +95,7 @@ __device__ __forceinline__ bool wait_counter(const unsigned int* counter, unsign
       ok = false;
       break;
     }
-    const long long until = clock64() + 96;  // a pause between polls
-    while (clock64() < until) {
-    }
+    __nanosleep(40);  // a pause that leaves the issue slots to the block this SM may share with
   }
   __threadfence();
   return ok;
@@ -110,9 +108,45 @@ __device__ __forceinline__ Fr shfl_xor_fr(const Fr& x, int mask) {
   return r;
 }
 
+// Chunk `part` (0..2) of a tagged element.
+__device__ __forceinline__ void st_tagged_part(TaggedFr* dst, const Fr& x, uint32_t tag, int part) {
+  const uint32_t a = x.v[3 * part], b = x.v[3 * part + 1], c = part < 2 ? x.v[3 * part + 2] : 0u;
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(&dst->w[part][0]), "r"(a), "r"(b), "r"(c), "r"(tag) : "memory");
+}
+__device__ __forceinline__ void st_tagged(TaggedFr* dst, const Fr& x, uint32_t tag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(&dst->w[0][0]), "r"(x.v[0]), "r"(x.v[1]), "r"(x.v[2]), "r"(tag) : "memory");
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(&dst->w[1][0]), "r"(x.v[3]), "r"(x.v[4]), "r"(x.v[5]), "r"(tag) : "memory");
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(&dst->w[2][0]), "r"(x.v[6]), "r"(x.v[7]), "r"(0u), "r"(tag) : "memory");
+}
+// One reading of a tagged element: true when all three chunks carry `tag` (then `out` is the element).
+__device__ __forceinline__ bool ld_tagged(const TaggedFr* src, uint32_t tag, Fr& out) {
+  uint32_t t0, t1, t2, z;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(out.v[0]), "=r"(out.v[1]), "=r"(out.v[2]), "=r"(t0) : "l"(&src->w[0][0]) : "memory");
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(out.v[3]), "=r"(out.v[4]), "=r"(out.v[5]), "=r"(t1) : "l"(&src->w[1][0]) : "memory");
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(out.v[6]), "=r"(out.v[7]), "=r"(z), "=r"(t2) : "l"(&src->w[2][0]) : "memory");
+  return t0 == tag && t1 == tag && t2 == tag;
+}
+// Bounded wait of a whole warp for tagged elements: lanes with `mine` poll their own element, the others go along;
+// the lanes leave the loop together.  false when it gave up (or another block did).
+__device__ __forceinline__ bool wait_tagged(const TaggedFr* src, bool mine, uint32_t tag, Fr& out, unsigned int* error, uint32_t limit) {
+  const volatile unsigned int* err = reinterpret_cast<const volatile unsigned int*>(error);
+  uint32_t polls = 0;
+  while (true) {
+    const bool have = !mine || ld_tagged(src, tag, out);
+    if (__all_sync(0xffffffffu, have)) return true;
+    if (__shfl_sync(0xffffffffu, *err, 0) != 0) return false;  // another block gave up and said why
+    if (++polls > limit) {
+      if ((threadIdx.x & 31) == 0) atomicCAS(error, 0u, 1u);
+      return false;
+    }
+    __nanosleep(40);  // a pause that leaves the issue slots to the block this SM may share with
+  }
+}
+
 // a + k (b - a) for k in 0 .. 3 (additions only).
 __device__ __forceinline__ Fr lin_small(const Fr& a, const Fr& b, int k) {
   if (k == 0) return a;
+  if (k == 1) return b;
   const Fr d = sub(b, a);
   Fr r = b;
   for (int i = 1; i < k; i++) r = add(r, d);
@@ -138,11 +172,13 @@ __device__ __forceinline__ Fr reduce_256(const Fr& x) {
 // How a warp of a worker block splits a unit of the rounds ahead.  A unit is QW quads of the folded tables
 // (four consecutive entries each).  Lane = ql * LQ + e * LT + ts: quad ql of the unit, entry e of the quad, table
 // slot ts.  Fold: lanes with ts < L bind the challenge on their entry (one product).  Grid: the (L + 1)^2 points
-// of a quad are dealt to its LQ lanes, point pt = w + k * LQ to lane w = e * LT + ts (L - 1 products each).
+// of a quad are dealt to its LQ lanes, point pt = w + k * LQ to lane w = e * LT + ts (L - 1 products each).  Two
+// tables get four slots as well: sixteen lanes then take the nine points one each, which is a product less on the
+// way from the challenge to the next message than eight lanes with two points on one of them.
 template <int L>
 struct AheadSplit {
   static constexpr int NV = L + 1, NG = NV * NV;
-  static constexpr int LT = L == 1 ? 1 : (L == 2 ? 2 : 4);
+  static constexpr int LT = L == 1 ? 1 : 4;
   static constexpr int LQ = 4 * LT;
   static constexpr int QW = 32 / LQ;
   static constexpr int PL = (NG + LQ - 1) / LQ;
@@ -160,6 +196,7 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
   __shared__ Fr red[kWarps][NG];
   __shared__ unsigned long long limbs[NG][8];
   __shared__ Fr lag[NG];
+  __shared__ Fr r_sm;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t t0 = p.ahead_from;
   ResidentShared* sh = p.sh;
@@ -177,25 +214,20 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
     const int j = lane % NV;
     for (uint32_t t = t0; t < p.rounds; t++) {
       // lambda'_j = prod_{k != j} (r - k) / R^(L-1); the grid sums arrive scaled by R^L / prod_{k != j} (j - k)
+      // (the L nodes other than j, in the same order of operations in every lane: one product sequence per warp)
       Fr lam;
-      {
-        bool first = true;
 #pragma unroll
-        for (int k = 0; k < NV; k++) {
-          if (k == j) continue;
-          Fr kk = Fr::zero();
-          kk.v[0] = (uint32_t)k;
-          const Fr term = sub(r, kk);
-          lam = first ? term : mul_call(lam, term);
-          first = false;
-        }
+      for (int m = 0; m < L; m++) {
+        Fr kk = Fr::zero();
+        kk.v[0] = (uint32_t)(m < j ? m : m + 1);
+        const Fr term = sub(r, kk);
+        lam = m == 0 ? term : mul_call(lam, term);
       }
-      int ok = 1;
       if (lane == 0 && t - t0 < 8) ZK_TRACE(sh, 16 + 4 * (t - t0));
-      ok = wait_counter(&sh->gseq, t + 1, &sh->error, p.spin_limit) ? 1 : 0;
-      if (!ok) return;
+      Fr g = Fr::zero();
+      if (!wait_tagged(&sh->gsum[t & 1][lane < NG ? lane : 0], lane < NG, t + 1, g, &sh->error, p.spin_limit)) return;
       if (lane == 0 && t - t0 < 8) ZK_TRACE(sh, 17 + 4 * (t - t0));
-      if (lane < NG) lag[lane] = mul_call(lam, ld_cg_fr(&sh->gsum[t & 1][lane]));  // lane = c * NV + j
+      if (lane < NG) lag[lane] = mul_call(lam, g);  // lane = c * NV + j
       __syncwarp();
       if (lane < NV) {  // s_t(c), canonical
         Fr s = lag[lane * NV];
@@ -214,13 +246,8 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
       ws.fs_round<L>(stream, lane, raw.v);
       r = reduce_256(raw);
       if (lane == 0 && t - t0 < 8) ZK_TRACE(sh, 19 + 4 * (t - t0));
-      if (lane == 0) {
-        p.out_chal[t] = r;
-        sh->rplain[t & 1] = r;
-      }
-      __threadfence();
-      __syncwarp();
-      if (lane == 0) *reinterpret_cast<volatile unsigned int*>(&sh->seq) = t + 1;
+      if (lane < 3) st_tagged_part(&sh->rplain[t & 1], r, t + 1, lane);  // the hand-over to the workers
+      if (lane == 0) p.out_chal[t] = r;
     }
     if (lane < 25) p.out_st->lanes[lane] = ws.a;
     if (lane == 0) {
@@ -290,12 +317,16 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
     if (it > t0) {
       __syncthreads();  // ok_flag is free again
       if (warp == 0) {
-        const bool ok = wait_counter(&sh->seq, it, &sh->error, p.spin_limit);
-        if (lane == 0) *ok_flag = ok ? 1 : 0;
+        Fr rp = Fr::zero();
+        const bool ok = wait_tagged(&sh->rplain[(it - 1) & 1], true, it, rp, &sh->error, p.spin_limit);
+        if (lane == 0) {
+          *ok_flag = ok ? 1 : 0;
+          r_sm = rp;
+        }
       }
       __syncthreads();
       if (!*ok_flag) return;
-      r_mont = to_mont_call(ld_cg_fr(&sh->rplain[(it - 1) & 1]));
+      r_mont = to_mont_call(r_sm);
     } else if (it == t0) {
       r_mont = ld_cg_fr(&sh->challenge);
     }
@@ -367,8 +398,7 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
         __threadfence();
         if (threadIdx.x < NG * 8) {
           const int pt = threadIdx.x >> 3, limb = threadIdx.x & 7;
-          limbs[pt][limb] = __ldcg(&sh->gacc[par][pt][limb]);
-          sh->gacc[par][pt][limb] = 0;  // for the pass after the next
+          limbs[pt][limb] = atomicExch(&sh->gacc[par][pt][limb], 0ull);  // read, and cleared for the pass after the next
         }
         __syncthreads();
         if (threadIdx.x < NG) {
@@ -390,10 +420,9 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
 #pragma unroll
           for (int k = 1; k < NV; k++)
             if ((int)(threadIdx.x % NV) == k) kc = p.kconst[k];
-          sh->gsum[par][threadIdx.x] = mul_call(redc<FrParams>(x), kc);
+          st_tagged(&sh->gsum[par][threadIdx.x], mul_call(redc<FrParams>(x), kc), it + 2);  // to the transcript block
         }
-        __threadfence();
-        __syncthreads();
+        // to the workers: the fence after the ticket orders every block's entries before this store
         if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(&sh->gseq) = it + 2;
         if (tr_on) ZK_TRACE(sh, tr_base + 6);
       }
@@ -409,10 +438,9 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
   // The last pass left two entries per table, folded by unit 0 = this block's warp 0 (block 1 only gets here with
   // a unit; the others have left), still in its exchange buffer.  Bind the last challenge.
   if (blockIdx.x != 1 || warp != 0) return;
-  int ok = 1;
-  ok = wait_counter(&sh->seq, p.rounds, &sh->error, p.spin_limit) ? 1 : 0;
-  if (!ok) return;
-  r_mont = to_mont_call(ld_cg_fr(&sh->rplain[(p.rounds - 1) & 1]));
+  Fr rp = Fr::zero();
+  if (!wait_tagged(&sh->rplain[(p.rounds - 1) & 1], true, p.rounds, rp, &sh->error, p.spin_limit)) return;
+  r_mont = to_mont_call(rp);
   if (lane < L) {
     const Fr b0 = xch[0][0 * LT + lane], b1 = xch[0][1 * LT + lane];
     const Fr f = add(b0, mul_call(r_mont, sub(b1, b0)));
@@ -431,7 +459,8 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
 
 template <int L>
 __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const ResidentParams<L> p) {
-  __shared__ uint4 stage[kWarps][WarpTile<8>::kChunks];
+  extern __shared__ uint4 resident_stage[];  // per warp: 2 stages x L tables of WarpTile<8>::kChunks slots
+  uint4* const my_stage = resident_stage + (size_t)(threadIdx.x >> 5) * (2 * L * WarpTile<8>::kChunks);
   __shared__ FixedMul<FrParams> r_tab;
   __shared__ Fr red[kWarps][L + 1];
   __shared__ Fr msg[L + 1];
@@ -444,6 +473,11 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
   if (threadIdx.x == 0) WarpStrobe::init_round_stream<L>(stream);
   if (blockIdx.x == 0 && threadIdx.x == 0) ZK_TRACE(p.sh, 0);
 
+  WarpStrobe ws;  // the transcript: block 0, warp 0
+  ws.scratch = keccak_scratch;
+  ws.a = lane < 25 ? p.st.lanes[lane] : 0;
+  ws.pos = p.st.pos;
+  ws.pos_begin = p.st.pos_begin;
   const Fr* cur[L];
 #pragma unroll
   for (int i = 0; i < L; i++) cur[i] = p.src[i];
@@ -452,18 +486,22 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
   const uint64_t warp_global = blockIdx.x + (uint64_t)gridDim.x * warp, warp_stride = (uint64_t)gridDim.x * kWarps;
 
   for (uint32_t round = 0; round < p.rounds; round++) {
+    const int ib = 128 + 8 * (int)round;
+    const bool itr = blockIdx.x == 0 && threadIdx.x == 0 && round < 12;
+    if (itr) ZK_TRACE(p.sh, ib + 0);
     Fr s[NV];
     if (round == 0) {
-      round_pass<L, false, false>(cur, cur, r_tab, cur_size >> 1, warp_global, warp_stride, stage[warp], lane, s);
+      round_pass_async<L, false>(cur, cur, r_tab, cur_size >> 1, warp_global, warp_stride, my_stage, lane, s);
     } else {
       Fr* dst[L];
 #pragma unroll
       for (int i = 0; i < L; i++) dst[i] = (round & 1) ? p.ping[i] : p.pong[i];
-      round_pass<L, true, true>(cur, dst, r_tab, cur_size >> 2, warp_global, warp_stride, stage[warp], lane, s);
+      round_pass_async<L, true>(cur, dst, r_tab, cur_size >> 2, warp_global, warp_stride, my_stage, lane, s);
 #pragma unroll
       for (int i = 0; i < L; i++) cur[i] = dst[i];
       cur_size >>= 1;
     }
+    if (itr) ZK_TRACE(p.sh, ib + 1);
     // block total -> global; the last block to arrive owns the rest of the round.  Only blocks that
     // had tiles this round hold a non-zero share: the others skip the store and are not read.
     const uint64_t tiles = ((cur_size >> 1) + 31) >> 5;  // cur_size: entries of the table the message is over
@@ -484,12 +522,28 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
       __threadfence();  // this block's folded entries and its share, before the ticket
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      const unsigned int ticket = atomicAdd(&p.sh->arrive, 1u);
-      flag = ticket == (round + 1) * gridDim.x - 1;
+    // Block 0 owns the rest of every round: it waits until all blocks have arrived.  (The last block to arrive
+    // could go on at once, but it is a different block, on a different SM, every round, and the code of the sum
+    // and of the transcript step is then fetched anew: that cost more than this hand-over.)
+    if (threadIdx.x == 0) atomicAdd(&p.sh->arrive, 1u);
+    if (blockIdx.x == 0) {
+      if (warp == 0) {
+        const bool ok = wait_counter(&p.sh->arrive, (round + 1) * gridDim.x, &p.sh->error, p.spin_limit);
+        if (lane == 0) ok_flag = ok ? 1 : 0;
+      }
+      __syncthreads();
+      if (!ok_flag) return;
     }
-    __syncthreads();
-    if (flag) {
+    if (itr) ZK_TRACE(p.sh, ib + 2);
+    if (blockIdx.x == 0) {
+      if (threadIdx.x == 0 && round < 12) ZK_TRACE(p.sh, ib + 3);
+#ifdef ZK_RESIDENT_TRACE
+      if (threadIdx.x == 0 && round < 12) {
+        unsigned int smid;
+        asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+        reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.sh) + 6144)[232 + round] = ((unsigned long long)blockIdx.x << 32) | smid;
+      }
+#endif
       __threadfence();
       // NV * active values over the block: all of a thread's loads are issued before its additions
       Fr t[NV];
@@ -528,18 +582,8 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
           return;
         }
       }
+      if (threadIdx.x == 0 && round < 12) ZK_TRACE(p.sh, ib + 4);
       if (warp == 0) {
-        WarpStrobe ws;
-        ws.scratch = keccak_scratch;
-        if (round == 0) {
-          ws.a = lane < 25 ? p.st.lanes[lane] : 0;
-          ws.pos = p.st.pos;
-          ws.pos_begin = p.st.pos_begin;
-        } else {
-          ws.a = lane < 25 ? __ldcg(reinterpret_cast<const unsigned long long*>(&p.sh->st.lanes[lane])) : 0;
-          ws.pos = __ldcg(&p.sh->st.pos);
-          ws.pos_begin = __ldcg(&p.sh->st.pos_begin);
-        }
         if (lane <= L) {
           const Fr t = msg[lane];
           p.out_msgs[(size_t)round * NV + lane] = t;
@@ -553,6 +597,7 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
         __syncwarp();
         Fr raw;
         ws.fs_round<L>(stream, lane, raw.v);
+        if (lane == 0 && round < 12) ZK_TRACE(p.sh, ib + 5);
         if (lane < 8) {  // eight lanes build the eight rows of the challenge's multiplier table
           const Fr ch = to_mont_call(raw);
           const Fr row = mul_call(ch, p.pow2[lane]);
@@ -567,10 +612,11 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
             p.sh->st.pad = 0;
           }
         }
-        if (lane < 25) p.sh->st.lanes[lane] = ws.a;
+        if (lane < 25 && (round + 1 == p.rounds || round + 1 == p.ahead_from)) p.sh->st.lanes[lane] = ws.a;  // for whoever goes on
         __threadfence();
         __syncwarp();
         if (lane == 0) *reinterpret_cast<volatile unsigned int*>(&p.sh->seq) = round + 1;
+        if (lane == 0 && round < 12) ZK_TRACE(p.sh, ib + 6);
       }
     }
     if (round + 1 == p.rounds) break;  // the last challenge is consumed by whoever runs next
@@ -581,6 +627,7 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
     }
     __syncthreads();
     if (!ok_flag) return;
+    if (itr) ZK_TRACE(p.sh, ib + 7);
     if (round + 1 == p.ahead_from) {  // the tables are small from here on
       __syncthreads();
       if constexpr (L <= 3) ahead_rounds<L>(p, cur, cur_size, stream, keccak_scratch, &ok_flag, &flag);
@@ -626,8 +673,11 @@ int launch_resident_t(const Fr* const* src, Fr* const* ping, Fr* const* pong, ui
     p.pow2[j] = cur;
     cur = mul(cur, step);
   }
+  // the opt-in for more than 48 KB of dynamic shared memory is per device, and a process may hold contexts on several
+  constexpr size_t kStageBytes = (size_t)kWarps * 2 * L * WarpTile<8>::kChunks * sizeof(uint4);
+  if (cudaFuncSetAttribute(k_resident<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStageBytes) != cudaSuccess) return -2;
   int occ = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_resident<L>, kThreads, 0) != cudaSuccess || occ < 1) return -2;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_resident<L>, kThreads, kStageBytes) != cudaSuccess || occ < 1) return -2;
   uint64_t grid = ((size >> 1) + 31) / 32;  // tiles of the first round, a warp each
   const uint64_t cap = (uint64_t)sm_count * occ < (uint64_t)max_blocks ? (uint64_t)sm_count * occ : (uint64_t)max_blocks;
   if (grid > cap) grid = cap;
@@ -641,8 +691,10 @@ int launch_resident_t(const Fr* const* src, Fr* const* ping, Fr* const* pong, ui
     // a block for the transcript beside at least one worker, a grid of at most kResidentGrid points, one GPU,
     // and all the rounds of the tables in this launch.
     if (px || L > 3 || cap < 2 || rounds < 2 || size != (1ull << rounds) || to_end->ahead_log < 2) return -5;
+    // (a single table has no products in its grid, only additions: it can run ahead four times earlier)
+    const uint32_t lg = to_end->ahead_log + (L == 1 ? 2 : 0);
     uint32_t t = 1;
-    while (t + 1 < rounds && (size >> (t - 1)) > (1ull << to_end->ahead_log)) t++;
+    while (t + 1 < rounds && (size >> (t - 1)) > (1ull << lg)) t++;
     p.ahead_from = t;
     // a block per unit of the first pass ahead (and the transcript block), so that the units spread over the SMs
     const uint64_t quads = (size >> (t - 1)) >> 2;
@@ -673,7 +725,7 @@ int launch_resident_t(const Fr* const* src, Fr* const* ping, Fr* const* pong, ui
   }
   void* args[] = {&p};
   if (cudaMemsetAsync(sh, 0, sizeof(ResidentShared), stream) != cudaSuccess) return -3;
-  if (cudaLaunchCooperativeKernel((const void*)k_resident<L>, dim3((unsigned)grid), dim3(kThreads), args, 0, stream) !=
+  if (cudaLaunchCooperativeKernel((const void*)k_resident<L>, dim3((unsigned)grid), dim3(kThreads), args, kStageBytes, stream) !=
       cudaSuccess) {
     cudaGetLastError();
     return -4;

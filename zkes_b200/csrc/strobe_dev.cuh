@@ -12,6 +12,14 @@ struct StrobeState {
   uint32_t pos, pos_begin, cur_flags, pad;
 };
 
+// A field element handed from one block to another without a fence or a separate flag: three 16-byte chunks, each
+// written and read as one transaction and each carrying the tag of the hand-over in its last word.  The reader polls
+// the chunks until all three show the tag it expects.
+struct alignas(16) TaggedFr {
+  uint32_t w[3][4];  // {v0, v1, v2, tag}, {v3, v4, v5, tag}, {v6, v7, 0, tag}
+  uint32_t pad[4];
+};
+
 // Hand-over area of the resident multi-round kernel (device global memory).
 struct ResidentShared {
   unsigned int arrive;       // block tickets of the message sums, counted up over all rounds
@@ -23,8 +31,8 @@ struct ResidentShared {
   FixedMul<FrParams> table;  // multiplier table of the latest challenge (rounds in step)
   Fr challenge;              // the latest challenge of a round in step (Montgomery form)
   StrobeState st;            // transcript state after the latest challenge of a round in step
-  Fr rplain[2];              // rounds ahead: the challenge of round t as a canonical integer in rplain[t & 1]
-  Fr gsum[2][16];            // message t tabulated as a polynomial in the challenge before it, scaled, in gsum[t & 1]
+  TaggedFr rplain[2];        // rounds ahead: the challenge of round t as a canonical integer in rplain[t & 1], tag t + 1
+  TaggedFr gsum[2][16];      // message t tabulated as a polynomial in the challenge before it, scaled, in gsum[t & 1], tag t + 1
   unsigned long long gacc[2][16][8];  // the same grid while the blocks add their shares: 64-bit sums of 32-bit limbs
 };
 constexpr int kResidentGrid = 16;  // grid points of a message: (L + 1)^2 for L <= 3
@@ -169,9 +177,7 @@ static __device__ __noinline__ uint2 keccak_f1600_warp(uint2 a, int lane, uint64
   const uint64_t* row = B + 6 * y;
   const int x1 = (x + 1) % 5, x2 = (x + 2) % 5;
   uint32_t lo = a.x, hi = a.y;
-  // Not unrolled: the transcript step runs once per sumcheck round, often on an SM that has not run it before,
-  // and fetching 24 copies of the round body costs more than the loop saves.
-#pragma unroll 1
+#pragma unroll
   for (int round = 0; round < 24; round++) {
     const uint64_t rc = kKeccakRcDev[round];  // uniform load; selected, not branched on, so the warp stays converged
     if (lane < 25) *reinterpret_cast<uint2*>(a_slot) = make_uint2(lo, hi);
