@@ -174,13 +174,13 @@ def test_fix_variables_random(ctx, n, k):
 @pytest.mark.parametrize("ell", [1, 2, 3, 4])
 @pytest.mark.parametrize("n", [0, 1, 4, 9, 10, 11, 13])
 def test_device_tail_option(ctx, n, ell):
-    """ZK_OPT_DEVICE_TAIL (on by default) runs the last rounds (tables of at most 1024 entries) in one
-    resident block with the transcript on the device; switched off, every round goes through the per-round
-    kernels with the transcript on the host.  Every output and the transcript state must be the same."""
+    """ZK_OPT_DEVICE_TAIL (on by default) keeps the rounds on the device with the transcript in a warp; switched
+    off, every round goes through the per-round kernels with the transcript on the host.  Every output and the
+    transcript state must be the same."""
     from zkes_b200._lib import ZK_OPT_DEVICE_TAIL
     rnd = random.Random(5000 + 10 * n + ell)
     tables = [[rnd.randrange(o.R_MOD) for _ in range(1 << n)] for _ in range(ell)]
-    run_both(ctx, tables)  # default: device-resident rounds (multi-block above 1024 entries, then one block)
+    run_both(ctx, tables)  # default: device-resident rounds
     ctx.set_option(ZK_OPT_DEVICE_TAIL, 0)
     try:
         run_both(ctx, tables)
@@ -190,8 +190,8 @@ def test_device_tail_option(ctx, n, ell):
 
 @pytest.mark.parametrize("n,ell", [(12, 1), (14, 3), (15, 2), (16, 2), (12, 4)])
 def test_resident_rounds(ctx, n, ell):
-    """Tables above 1024 entries: the cooperative multi-block kernel runs the first rounds with the transcript
-    on the device and hands the last 1024 entries to the single-block kernel without a host step between."""
+    """Tables above 1024 entries: the cooperative multi-block kernel runs all rounds with the transcript on the
+    device, the later ones prepared ahead of their challenges."""
     rnd = random.Random(9100 + 10 * n + ell)
     edge = [0, 1, o.R_MOD - 1]
     tables = [[rnd.choice(edge) if rnd.random() < 0.05 else rnd.randrange(o.R_MOD) for _ in range(1 << n)]
@@ -210,3 +210,36 @@ def test_device_transcript_block_boundaries(ctx, label_len, ell):
     rnd = random.Random(7000 + 10 * label_len + ell)
     tables = [[rnd.randrange(o.R_MOD) for _ in range(1 << 4)] for _ in range(ell)]
     run_both(ctx, tables, label=bytes(rnd.randrange(256) for _ in range(label_len)))
+
+
+@pytest.mark.parametrize("ell", [1, 2, 3])
+@pytest.mark.parametrize("n", [2, 3, 4, 6, 9, 12, 14])
+def test_run_ahead_thresholds(ctx, n, ell):
+    """ZK_OPT_AHEAD_LOG moves the round from which the multi-round kernel prepares messages ahead of their
+    challenges (0: never, and the single-block kernel finishes; 2: only the very last rounds; large: from the
+    second round on).  Messages, challenges, final values and the transcript state must not depend on it."""
+    from zkes_b200._lib import ZK_OPT_AHEAD_LOG
+    rnd = random.Random(7300 + 10 * n + ell)
+    edge = [0, 1, o.R_MOD - 1]
+    tables = [[rnd.choice(edge) if rnd.random() < 0.1 else rnd.randrange(o.R_MOD) for _ in range(1 << n)]
+              for _ in range(ell)]
+    try:
+        for log in (0, 2, 5, 10, 24):
+            ctx.set_option(ZK_OPT_AHEAD_LOG, log)
+            run_both(ctx, tables, label=b"ahead-%d" % log)
+    finally:
+        ctx.set_option(ZK_OPT_AHEAD_LOG, 15)
+
+
+def test_run_ahead_large_tables(ctx):
+    """Two tables of 2^16 entries with the run-ahead threshold above the table size: every round but the first is
+    prepared ahead, with many units per warp and every worker block busy."""
+    from zkes_b200._lib import ZK_OPT_AHEAD_LOG
+    n = 16
+    rnd = random.Random(99)
+    tables = [[rnd.randrange(o.R_MOD) for _ in range(1 << n)] for _ in range(2)]
+    try:
+        ctx.set_option(ZK_OPT_AHEAD_LOG, 20)
+        run_both(ctx, tables, label=b"ahead-large")
+    finally:
+        ctx.set_option(ZK_OPT_AHEAD_LOG, 15)

@@ -110,13 +110,6 @@ void zk_free(zk_ctx* ctx) {
   delete ctx;
 }
 
-#ifdef ZK_RESIDENT_TRACE
-int zk_debug_resident_trace(zk_ctx* ctx, unsigned long long* out, int n) {
-  cudaStreamSynchronize(ctx->stream);
-  return (int)cudaMemcpy(out, reinterpret_cast<char*>(ctx->resident_sh) + 6144, 8 * (size_t)n, cudaMemcpyDeviceToHost);
-}
-#endif
-
 uint64_t zk_launch_count(const zk_ctx* ctx) { return ctx ? ctx->total_launches() : 0; }
 
 int zk_set_option(zk_ctx* ctx, int option, int value) {
@@ -276,8 +269,8 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
   uint32_t resident_rounds = 0;  // rounds the resident kernel has produced (their results are still on the device)
   // Reads back what the device-resident rounds left in ctx->tail_out: `left` messages and challenges
   // (rounds round_offset + first ...), the transcript state and the resident kernel's error word.
-  // Rounds from `canonical_from` on (counted like `first`) come back as canonical integers.
-  auto collect_device_rounds = [&](uint32_t first, uint32_t left, bool resident, uint32_t canonical_from = 0xffffffffu) -> int {
+  // The first `canonical` of them are the multi-round kernel's, which writes canonical integers, not Montgomery form.
+  auto collect_device_rounds = [&](uint32_t first, uint32_t left, bool resident, uint32_t canonical) -> int {
     ResidentShared* sh = reinterpret_cast<ResidentShared*>(ctx->resident_sh);
     const size_t bytes = ((size_t)left * (L + 2)) * sizeof(Fr) + sizeof(StrobeState);
     unsigned int* h_flags = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(ctx->host_small) + 8192 - 16);
@@ -290,7 +283,7 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
     Fr* h_chal = h_msgs + (size_t)left * (L + 1);
     const StrobeState* h_st = reinterpret_cast<const StrobeState*>(h_chal + left);
     for (uint32_t k = 0; k < left; k++) {
-      if (first + k >= canonical_from) {
+      if (k < canonical) {
         for (int c = 0; c <= L; c++) h_msgs[(size_t)k * (L + 1) + c] = to_mont(h_msgs[(size_t)k * (L + 1) + c]);
         h_chal[k] = to_mont(h_chal[k]);
       }
@@ -354,7 +347,7 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
           return fail(ZK_ERR_CUDA, "tail kernel launch failed");
         ctx->launches++;
         ZK_CUDA(cudaGetLastError());
-        rc = collect_device_rounds(0, left, true);
+        rc = collect_device_rounds(0, left, true, R);
         if (rc) return rc;
         ctx->sharded_finished = true;
         *finals_done = true;
@@ -387,7 +380,7 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
         ctx->prof_end();
         if (lrc == 0) {
           ctx->launches++;
-          int rc = collect_device_rounds(0, left, true, ahead_from);
+          int rc = collect_device_rounds(0, left, true, left);
           if (rc) return rc;
           *finals_done = true;
           return ZK_OK;
@@ -421,7 +414,7 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
           return fail(ZK_ERR_CUDA, "tail kernel launch failed");
         ctx->launches++;
         ZK_CUDA(cudaGetLastError());
-        int rc = collect_device_rounds(round, left, resident);
+        int rc = collect_device_rounds(round, left, resident, resident ? resident_rounds : 0);
         if (rc) return rc;
         *finals_done = true;
         return ZK_OK;

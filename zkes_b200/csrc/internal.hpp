@@ -159,7 +159,7 @@ struct ResidentToEnd {    // launch_resident runs to the end of the protocol
   uint32_t ahead_log;     // tables of at most 2^ahead_log entries: rounds prepared ahead of their challenge
   Fr* out_final;          // L table values at the challenge point, then their product
   StrobeState* out_st;    // transcript state after the last challenge
-  uint32_t* ahead_from;   // host: first round whose message and challenge come back as canonical integers
+  uint32_t* ahead_from;   // host: first round that was prepared ahead of its challenge (for diagnostics)
 };
 // px != nullptr: the tables are this rank's chunks of a sharded instance; every round's message is the
 // sum over the ranks, exchanged through the peer boxes by the block that completes the local sums.

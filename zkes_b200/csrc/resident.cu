@@ -4,9 +4,13 @@
 // all blocks are resident together; every wait is bounded and reports through ResidentShared::error instead of
 // spinning on.  Rounds: linear_prover.rs:59-72; message :82-140; fold :151-178; final :181-190.
 //
-// Large tables, rounds "in step": every block folds and sums its share of the tables, the last block to arrive
-// adds the partial messages, runs the Fiat-Shamir step (one warp, transcript.rs:27-42 over STROBE / Keccak-f) and
-// publishes the challenge's multiplier table; the other blocks wait for it and start the next round.
+// Large tables, rounds "in step": every block folds and sums its share of the tables and adds it to the round's
+// accumulators (atomic additions of 64-bit limb sums, no modular arithmetic); block 0 waits until all have arrived,
+// reduces the sums, runs the Fiat-Shamir step (one warp, transcript.rs:27-42 over STROBE / Keccak-f; the state
+// stays in that warp's registers for the whole launch) and hands the challenge out as a tagged element; every block
+// builds the challenge's multiplier table from it (one product) and starts the next round.  Waits are polled by a
+// whole warp in lockstep: a warp that leaves a single-lane polling loop stays split and runs the code after it
+// several times slower.
 //
 // Small tables, rounds "ahead" (ahead_rounds below): a round is then all latency - a dependent field product
 // takes about 0.5 us, the transcript step 5 us, a hand-over between blocks 0.5 us - and in step these add up.
@@ -27,7 +31,7 @@ namespace {
 
 constexpr int kThreads = kRoundThreads;
 constexpr int kWarps = kRoundWarps;
-static_assert(sizeof(ResidentShared) <= 6144, "the context allocates 8192 bytes for the hand-over area");
+static_assert(sizeof(ResidentShared) <= 8192, "the context allocates 8192 bytes for the hand-over area");
 
 template <int L>
 struct ResidentParams {
@@ -43,36 +47,21 @@ struct ResidentParams {
   StrobeState st;       // transcript state on entry
   Fr* partials;         // gridDim.x * (L + 1)
   ResidentShared* sh;   // zeroed on entry
-  Fr* out_msgs;         // rounds * (L + 1): Montgomery form for rounds in step, canonical integers for rounds ahead
-  Fr* out_chal;         // rounds: Montgomery form for rounds in step, canonical integers for rounds ahead
+  Fr* out_msgs;         // rounds * (L + 1), canonical integers (not Montgomery form)
+  Fr* out_chal;         // rounds, canonical integers
   Fr* out_final;        // rounds ahead: the L table values at the challenge point, then their product
   StrobeState* out_st;  // rounds ahead: transcript state after the last challenge
-  Fr pow2[8];           // 2^(32 j + 64) mod r as plain integers: rows of a multiplier table
+  Fr pow2[8];           // 2^(32 j + 64) mod r in Montgomery form: times a canonical challenge, the rows of its multiplier table
   Fr kconst[L + 1];     // R^(L+1) / prod_{k != j} (j - k) as integers: scales the grid sums for the interpolation
   PeerExchange px;      // px.world > 1: sharded instance, messages are summed over the ranks
 };
 
-#ifdef ZK_RESIDENT_TRACE
-__device__ __forceinline__ void trace_stamp(ResidentShared* sh, int slot) {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(sh) + 6144)[slot] = t;
-}
-#define ZK_TRACE(sh, slot) trace_stamp(sh, slot)
-#else
-#define ZK_TRACE(sh, slot)
-#endif
 
 // Field products outside the streaming passes are called, not inlined: a product is about 3.5 KB of code, the
 // rounds of small tables run each piece of code once per round, and what bounds them then is fetching
 // instructions, not executing them.  One shared copy stays in the instruction cache.
 __device__ __noinline__ Fr mul_call(Fr a, Fr b) { return mul(a, b); }
 __device__ __forceinline__ Fr to_mont_call(const Fr& a) { return mul_call(Fr::r2(), a); }
-__device__ __forceinline__ Fr from_mont_call(const Fr& a) {
-  Fr o = Fr::zero();
-  o.v[0] = 1;
-  return mul_call(a, o);
-}
 
 // Bounded wait for a counter to reach `want`; false when it gave up (or another block did).  Called by all the
 // lanes of a warp together, which then poll in lockstep (one transaction per poll): with a single lane in the
@@ -121,6 +110,7 @@ __device__ __forceinline__ void st_tagged(TaggedFr* dst, const Fr& x, uint32_t t
 // One reading of a tagged element: true when all three chunks carry `tag` (then `out` is the element).
 __device__ __forceinline__ bool ld_tagged(const TaggedFr* src, uint32_t tag, Fr& out) {
   uint32_t t0, t1, t2, z;
+  (void)z;
   asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(out.v[0]), "=r"(out.v[1]), "=r"(out.v[2]), "=r"(t0) : "l"(&src->w[0][0]) : "memory");
   asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(out.v[3]), "=r"(out.v[4]), "=r"(out.v[5]), "=r"(t1) : "l"(&src->w[1][0]) : "memory");
   asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(out.v[6]), "=r"(out.v[7]), "=r"(z), "=r"(t2) : "l"(&src->w[2][0]) : "memory");
@@ -184,12 +174,13 @@ struct AheadSplit {
   static constexpr int PL = (NG + LQ - 1) / LQ;
 };
 
-// The rounds from p.ahead_from to the end.  On entry every block has left the in-step round ahead_from - 1: the
-// tables `cur` (cur_size entries) are the ones message ahead_from - 1 is over, complete and visible, and the
-// challenge of that round is in sh->challenge (Montgomery form) with the transcript state in sh->st.
+// The rounds from p.ahead_from to the end.  Entered by every block right after its part of the in-step round
+// ahead_from - 1 (block 0: after that round's transcript step, with the state in `ws`): the tables `cur` (cur_size
+// entries) are the ones message ahead_from - 1 is over, complete once every block has arrived at that round's
+// ticket, and the challenge of that round arrives as rplain[(ahead_from - 1) & 1].
 template <int L>
-__device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const Fr* (&cur)[L], uint64_t cur_size, uint8_t* stream,
-                                             uint64_t* keccak_scratch, int* ok_flag, int* flag) {
+__device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, WarpStrobe& ws, const Fr* (&cur)[L], uint64_t cur_size,
+                                             uint8_t* stream, int* ok_flag, int* flag) {
   using S = AheadSplit<L>;
   constexpr int NV = S::NV, NG = S::NG, LT = S::LT, LQ = S::LQ, QW = S::QW, PL = S::PL;
   __shared__ Fr xch[kWarps][32];
@@ -204,13 +195,8 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
   if (blockIdx.x == 0) {
     // ------------------------------------------------------------------ the transcript chain (one warp)
     if (warp != 0) return;
-    WarpStrobe ws;
-    ws.scratch = keccak_scratch;
-    ws.a = lane < 25 ? __ldcg(reinterpret_cast<const unsigned long long*>(&sh->st.lanes[lane])) : 0;
-    ws.pos = __ldcg(&sh->st.pos);
-    ws.pos_begin = __ldcg(&sh->st.pos_begin);
-    if (lane == 0) ZK_TRACE(sh, 1);
-    Fr r = from_mont_call(ld_cg_fr(&sh->challenge));  // canonical
+    Fr r = Fr::zero();  // the challenge of the round before, canonical; the transcript state is in this warp's registers
+    if (!wait_tagged(&sh->rplain[(t0 - 1) & 1], true, t0, r, &sh->error, p.spin_limit)) return;
     const int j = lane % NV;
     for (uint32_t t = t0; t < p.rounds; t++) {
       // lambda'_j = prod_{k != j} (r - k) / R^(L-1); the grid sums arrive scaled by R^L / prod_{k != j} (j - k)
@@ -223,10 +209,8 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
         const Fr term = sub(r, kk);
         lam = m == 0 ? term : mul_call(lam, term);
       }
-      if (lane == 0 && t - t0 < 8) ZK_TRACE(sh, 16 + 4 * (t - t0));
       Fr g = Fr::zero();
       if (!wait_tagged(&sh->gsum[t & 1][lane < NG ? lane : 0], lane < NG, t + 1, g, &sh->error, p.spin_limit)) return;
-      if (lane == 0 && t - t0 < 8) ZK_TRACE(sh, 17 + 4 * (t - t0));
       if (lane < NG) lag[lane] = mul_call(lam, g);  // lane = c * NV + j
       __syncwarp();
       if (lane < NV) {  // s_t(c), canonical
@@ -241,11 +225,9 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
           for (int k = 0; k < 4; k++) dst[4 * i + k] = (uint8_t)(s.v[i] >> (8 * k));
       }
       __syncwarp();
-      if (lane == 0 && t - t0 < 8) ZK_TRACE(sh, 18 + 4 * (t - t0));
       Fr raw;
       ws.fs_round<L>(stream, lane, raw.v);
       r = reduce_256(raw);
-      if (lane == 0 && t - t0 < 8) ZK_TRACE(sh, 19 + 4 * (t - t0));
       if (lane < 3) st_tagged_part(&sh->rplain[t & 1], r, t + 1, lane);  // the hand-over to the workers
       if (lane == 0) p.out_chal[t] = r;
     }
@@ -275,9 +257,6 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
     const uint64_t n_units = n_q ? (n_q + QW - 1) / QW : 1;
     if (blockIdx.x - 1 >= n_units) return;  // no unit in this pass, and none in any later one
     const unsigned int active = (unsigned int)(n_units < nbw ? n_units : nbw);
-    const int tr_base = 64 + 8 * (int)(it - (t0 - 1));
-    const bool tr_on = blockIdx.x == 1 && threadIdx.x == 0 && it - (t0 - 1) < 8;
-    if (tr_on) ZK_TRACE(sh, tr_base + 0);
     Fr* dst[L];
 #pragma unroll
     for (int i = 0; i < L; i++) dst[i] = (it & 1) ? p.ping[i] : p.pong[i];
@@ -290,15 +269,16 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
         my_dst = dst[i];
       }
     }
-    if (it >= t0) {  // the pass before is complete in every block: its tables, and its tickets
+    {  // what this pass reads is complete in every block: the tables of the last round in step (every block has
+       // arrived there), or those of the pass before, whose tickets are then all in as well
       if (warp == 0) {
-        const bool ok = wait_counter(&sh->gseq, it + 1, &sh->error, p.spin_limit);
+        const bool ok = it >= t0 ? wait_counter(&sh->gseq, it + 1, &sh->error, p.spin_limit)
+                                 : wait_counter(&sh->arrive, t0 * gridDim.x, &sh->error, p.spin_limit);
         if (lane == 0) *ok_flag = ok ? 1 : 0;
       }
       __syncthreads();
       if (!*ok_flag) return;
     }
-    if (tr_on) ZK_TRACE(sh, tr_base + 1);
     // the first unit's entries do not depend on the challenge: fetch them before waiting for it
     uint64_t u = wid;
     Fr a0 = Fr::zero(), a1 = Fr::zero();
@@ -314,7 +294,7 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
       }
     };
     if (u < n_units) fetch(u);
-    if (it > t0) {
+    if (it >= t0) {
       __syncthreads();  // ok_flag is free again
       if (warp == 0) {
         Fr rp = Fr::zero();
@@ -327,10 +307,7 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
       __syncthreads();
       if (!*ok_flag) return;
       r_mont = to_mont_call(r_sm);
-    } else if (it == t0) {
-      r_mont = ld_cg_fr(&sh->challenge);
     }
-    if (tr_on) ZK_TRACE(sh, tr_base + 2);
     Fr acc[PL];
 #pragma unroll
     for (int k = 0; k < PL; k++) acc[k] = Fr::zero();
@@ -366,7 +343,6 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
       }
       __syncwarp();
     }
-    if (tr_on) ZK_TRACE(sh, tr_base + 3);
     if (do_grid) {
       // lanes of equal role over the quads of the warp, then the warps of the block as plain 64-bit limb sums,
       // then the blocks by atomic additions of those limbs: no modular arithmetic until the very end
@@ -389,11 +365,9 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
       }
       __threadfence();  // this block's folded entries and its share of the grid, before the ticket
       __syncthreads();
-      if (tr_on) ZK_TRACE(sh, tr_base + 4);
       tickets += active;
       if (threadIdx.x == 0) *flag = atomicAdd(&sh->garrive, 1u) == tickets - 1;
       __syncthreads();
-      if (tr_on) ZK_TRACE(sh, tr_base + 5);
       if (*flag) {
         __threadfence();
         if (threadIdx.x < NG * 8) {
@@ -424,7 +398,6 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
         }
         // to the workers: the fence after the ticket orders every block's entries before this store
         if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(&sh->gseq) = it + 2;
-        if (tr_on) ZK_TRACE(sh, tr_base + 6);
       }
     } else {
       __syncthreads();
@@ -453,7 +426,6 @@ __device__ __forceinline__ void ahead_rounds(const ResidentParams<L>& p, const F
 #pragma unroll
     for (int t = 1; t < L; t++) prod = mul_call(prod, lag[t]);
     p.out_final[L] = prod;
-    ZK_TRACE(sh, 2);
   }
 }
 
@@ -465,13 +437,13 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
   __shared__ Fr red[kWarps][L + 1];
   __shared__ Fr msg[L + 1];
   __shared__ __align__(16) uint8_t stream[WarpStrobe::round_stream_bytes<L>() + 15];
+  __shared__ unsigned long long macc_sm[L + 1][8];
   __shared__ int flag, ok_flag, px_ok;
   __shared__ uint32_t px_stage[kPeerRanks * (L + 1) * 8];
   __shared__ __align__(16) uint64_t keccak_scratch[64];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int NV = L + 1;
   if (threadIdx.x == 0) WarpStrobe::init_round_stream<L>(stream);
-  if (blockIdx.x == 0 && threadIdx.x == 0) ZK_TRACE(p.sh, 0);
 
   WarpStrobe ws;  // the transcript: block 0, warp 0
   ws.scratch = keccak_scratch;
@@ -486,9 +458,6 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
   const uint64_t warp_global = blockIdx.x + (uint64_t)gridDim.x * warp, warp_stride = (uint64_t)gridDim.x * kWarps;
 
   for (uint32_t round = 0; round < p.rounds; round++) {
-    const int ib = 128 + 8 * (int)round;
-    const bool itr = blockIdx.x == 0 && threadIdx.x == 0 && round < 12;
-    if (itr) ZK_TRACE(p.sh, ib + 0);
     Fr s[NV];
     if (round == 0) {
       round_pass_async<L, false>(cur, cur, r_tab, cur_size >> 1, warp_global, warp_stride, my_stage, lane, s);
@@ -501,30 +470,31 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
       for (int i = 0; i < L; i++) cur[i] = dst[i];
       cur_size >>= 1;
     }
-    if (itr) ZK_TRACE(p.sh, ib + 1);
-    // block total -> global; the last block to arrive owns the rest of the round.  Only blocks that
-    // had tiles this round hold a non-zero share: the others skip the store and are not read.
+    // Block total -> global: the warps' sums are added as plain 64-bit sums of their 32-bit limbs, and the blocks add
+    // those to the round's accumulators by atomics, so nobody has to read a partial sum per block afterwards.
     const uint64_t tiles = ((cur_size >> 1) + 31) >> 5;  // cur_size: entries of the table the message is over
-    const unsigned int active = (unsigned int)(tiles < gridDim.x ? tiles : gridDim.x);
-    if (blockIdx.x < active) {
+    const int mpar = round & 1;
+    if (blockIdx.x < tiles) {  // the others had no tile this round
 #pragma unroll
       for (int c = 0; c < NV; c++) {
         const Fr t = warp_sum(s[c]);
         if (lane == 0) red[warp][c] = t;
       }
       __syncthreads();
-      if (threadIdx.x < NV) {
-        Fr t = red[0][threadIdx.x];
-        for (int w = 1; w < kWarps; w++)
-          if (blockIdx.x + (uint64_t)gridDim.x * w < tiles) t = add(t, red[w][threadIdx.x]);
-        p.partials[(size_t)blockIdx.x * NV + threadIdx.x] = t;
+      if (threadIdx.x < NV * 8) {
+        const int c = threadIdx.x >> 3, limb = threadIdx.x & 7;
+        unsigned long long v = 0;
+#pragma unroll
+        for (int w = 0; w < kWarps; w++)
+          if (blockIdx.x + (uint64_t)gridDim.x * w < tiles) v += red[w][c].v[limb];
+        atomicAdd(&p.sh->macc[mpar][c][limb], v);
       }
       __threadfence();  // this block's folded entries and its share, before the ticket
     }
     __syncthreads();
     // Block 0 owns the rest of every round: it waits until all blocks have arrived.  (The last block to arrive
-    // could go on at once, but it is a different block, on a different SM, every round, and the code of the sum
-    // and of the transcript step is then fetched anew: that cost more than this hand-over.)
+    // could go on at once, but it is a different block, on a different SM, every round, and the code of the
+    // transcript step is then fetched anew: that cost more than this hand-over.)
     if (threadIdx.x == 0) atomicAdd(&p.sh->arrive, 1u);
     if (blockIdx.x == 0) {
       if (warp == 0) {
@@ -534,42 +504,27 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
       __syncthreads();
       if (!ok_flag) return;
     }
-    if (itr) ZK_TRACE(p.sh, ib + 2);
     if (blockIdx.x == 0) {
-      if (threadIdx.x == 0 && round < 12) ZK_TRACE(p.sh, ib + 3);
-#ifdef ZK_RESIDENT_TRACE
-      if (threadIdx.x == 0 && round < 12) {
-        unsigned int smid;
-        asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
-        reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.sh) + 6144)[232 + round] = ((unsigned long long)blockIdx.x << 32) | smid;
-      }
-#endif
-      __threadfence();
-      // NV * active values over the block: all of a thread's loads are issued before its additions
-      Fr t[NV];
-#pragma unroll
-      for (int c = 0; c < NV; c++) t[c] = Fr::zero();
-      for (unsigned int b0 = 0; b0 < active; b0 += 2 * kThreads) {
-        const unsigned int b1 = b0 + threadIdx.x, b2 = b1 + kThreads;
-        Fr u[NV], v[NV];
-#pragma unroll
-        for (int c = 0; c < NV; c++) {
-          u[c] = b1 < active ? ld_cg_fr(p.partials + (size_t)b1 * NV + c) : Fr::zero();
-          v[c] = b2 < active ? ld_cg_fr(p.partials + (size_t)b2 * NV + c) : Fr::zero();
-        }
-#pragma unroll
-        for (int c = 0; c < NV; c++) t[c] = add(t[c], add(u[c], v[c]));
-      }
-#pragma unroll
-      for (int c = 0; c < NV; c++) {
-        const Fr w = warp_sum(t[c]);
-        if (lane == 0) red[warp][c] = w;
+      if (threadIdx.x < NV * 8) {  // read, and cleared for the round after the next
+        const int c = threadIdx.x >> 3, limb = threadIdx.x & 7;
+        macc_sm[c][limb] = atomicExch(&p.sh->macc[mpar][c][limb], 0ull);
       }
       __syncthreads();
       if (threadIdx.x < NV) {
-        Fr w = red[0][threadIdx.x];
-        for (int k = 1; k < kWarps; k++) w = add(w, red[k][threadIdx.x]);
-        msg[threadIdx.x] = w;
+        Wide x;
+#pragma unroll
+        for (int k = 0; k < 16; k++) x.v[k] = 0;
+        unsigned long long carry = 0;
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+          const unsigned long long v = macc_sm[threadIdx.x][k];
+          const unsigned long long lo = (v & 0xffffffffull) + (carry & 0xffffffffull);
+          x.v[k] = (uint32_t)lo;
+          carry = (v >> 32) + (carry >> 32) + (lo >> 32);
+        }
+        x.v[8] = (uint32_t)carry;
+        x.v[9] = (uint32_t)(carry >> 32);
+        msg[threadIdx.x] = redc<FrParams>(x);  // the sum of Montgomery forms, / R: the message as canonical integers
       }
       __syncthreads();
       if (p.px.world > 1) {
@@ -582,12 +537,10 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
           return;
         }
       }
-      if (threadIdx.x == 0 && round < 12) ZK_TRACE(p.sh, ib + 4);
       if (warp == 0) {
         if (lane <= L) {
-          const Fr t = msg[lane];
-          p.out_msgs[(size_t)round * NV + lane] = t;
-          const Fr canon = from_mont_call(t);
+          const Fr canon = msg[lane];
+          p.out_msgs[(size_t)round * NV + lane] = canon;
           uint8_t* dst = WarpStrobe::round_stream_data(stream, lane);
 #pragma unroll
           for (int i = 0; i < 8; i++)
@@ -597,44 +550,39 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
         __syncwarp();
         Fr raw;
         ws.fs_round<L>(stream, lane, raw.v);
-        if (lane == 0 && round < 12) ZK_TRACE(p.sh, ib + 5);
-        if (lane < 8) {  // eight lanes build the eight rows of the challenge's multiplier table
-          const Fr ch = to_mont_call(raw);
-          const Fr row = mul_call(ch, p.pow2[lane]);
-#pragma unroll
-          for (int k = 0; k < 8; k++) p.sh->table.c[lane][k] = row.v[k];
+        const Fr r = reduce_256(raw);
+        if (lane < 3) st_tagged_part(&p.sh->rplain[round & 1], r, round + 1, lane);  // the hand-over to every block
+        if (lane == 0) p.out_chal[round] = r;
+        if (round + 1 == p.rounds) {  // for the kernel that goes on: challenge in Montgomery form, transcript state
+          if (lane < 25) p.sh->st.lanes[lane] = ws.a;
           if (lane == 0) {
-            p.out_chal[round] = ch;
-            p.sh->challenge = ch;
+            p.sh->challenge = to_mont_call(r);
             p.sh->st.pos = ws.pos;
             p.sh->st.pos_begin = ws.pos_begin;
             p.sh->st.cur_flags = 1u | 2u | 4u;
             p.sh->st.pad = 0;
           }
         }
-        if (lane < 25 && (round + 1 == p.rounds || round + 1 == p.ahead_from)) p.sh->st.lanes[lane] = ws.a;  // for whoever goes on
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) *reinterpret_cast<volatile unsigned int*>(&p.sh->seq) = round + 1;
-        if (lane == 0 && round < 12) ZK_TRACE(p.sh, ib + 6);
       }
     }
     if (round + 1 == p.rounds) break;  // the last challenge is consumed by whoever runs next
-    // wait for this round's challenge
+    // wait for this round's challenge; every block builds the multiplier table from it by itself (one product)
+    if (round + 1 == p.ahead_from) {  // the tables are small from here on
+      if constexpr (L <= 3) ahead_rounds<L>(p, ws, cur, cur_size, stream, &ok_flag, &flag);
+      return;
+    }
     if (warp == 0) {
-      const bool ok = wait_counter(&p.sh->seq, round + 1, &p.sh->error, p.spin_limit);
+      Fr r = Fr::zero();
+      const bool ok = wait_tagged(&p.sh->rplain[round & 1], true, round + 1, r, &p.sh->error, p.spin_limit);
       if (lane == 0) ok_flag = ok ? 1 : 0;
+      if (ok && lane < 8) {  // row j = r 2^(32 j + 64) mod r as plain integers
+        const Fr row = mul_call(r, p.pow2[lane]);
+#pragma unroll
+        for (int k = 0; k < 8; k++) r_tab.c[lane][k] = row.v[k];
+      }
     }
     __syncthreads();
     if (!ok_flag) return;
-    if (itr) ZK_TRACE(p.sh, ib + 7);
-    if (round + 1 == p.ahead_from) {  // the tables are small from here on
-      __syncthreads();
-      if constexpr (L <= 3) ahead_rounds<L>(p, cur, cur_size, stream, keccak_scratch, &ok_flag, &flag);
-      return;
-    }
-    if (threadIdx.x < 64) (&r_tab.c[0][0])[threadIdx.x] = __ldcg(&p.sh->table.c[0][0] + threadIdx.x);
-    __syncthreads();
   }
 }
 
@@ -670,7 +618,7 @@ int launch_resident_t(const Fr* const* src, Fr* const* ping, Fr* const* pong, ui
   step.v[1] = 1;
   step = to_mont(step);  // (2^32) R: a Montgomery product with it multiplies a plain integer by 2^32
   for (int j = 0; j < 8; j++) {
-    p.pow2[j] = cur;
+    p.pow2[j] = to_mont(cur);  // times a canonical challenge (Montgomery product): r 2^(32 j + 64) as a plain integer
     cur = mul(cur, step);
   }
   // the opt-in for more than 48 KB of dynamic shared memory is per device, and a process may hold contexts on several
@@ -740,8 +688,8 @@ int launch_resident_t(const Fr* const* src, Fr* const* ping, Fr* const* pong, ui
 // challenge is in sh->challenge and the transcript state in sh->st.  Non-zero: the cooperative
 // launch was not possible and nothing ran.  With to_end (unsharded, at most three tables, rounds = log2(size) >= 2)
 // the launch runs to the end of the protocol instead: the rounds from *to_end->ahead_from on are prepared ahead of
-// their challenges, their messages and challenges come back as canonical integers (not Montgomery form), and the
-// final values and the transcript state are written to to_end->out_final / out_st.
+// their challenges, and the final values and the transcript state are written to to_end->out_final / out_st.
+// Either way out_msgs and out_chal receive canonical integers, not Montgomery form.
 int launch_resident(int num_poly, const Fr* const* src, Fr* const* ping, Fr* const* pong, uint64_t size, uint32_t rounds,
                     const StrobeState& st, Fr* partials, int max_blocks, int sm_count, ResidentShared* sh, Fr* out_msgs,
                     Fr* out_chal, cudaStream_t stream, const PeerExchange* px, const ResidentToEnd* to_end) {

@@ -22,16 +22,16 @@ struct alignas(16) TaggedFr {
 
 // Hand-over area of the resident multi-round kernel (device global memory).
 struct ResidentShared {
-  unsigned int arrive;       // block tickets of the message sums, counted up over all rounds
-  unsigned int seq;          // rounds whose challenge has been published
+  unsigned int arrive;       // blocks that have added their share of a message, counted up over all rounds in step
+  unsigned int seq;          // (unused)
   unsigned int error;        // non-zero: a bounded wait ran out
   unsigned int garrive;      // block tickets of the grid sums (rounds whose message is prepared ahead)
   unsigned int gseq;         // grid of message `gseq - 1` is complete in gsum[(gseq - 1) & 1]
   unsigned int pad[3];
-  FixedMul<FrParams> table;  // multiplier table of the latest challenge (rounds in step)
-  Fr challenge;              // the latest challenge of a round in step (Montgomery form)
-  StrobeState st;            // transcript state after the latest challenge of a round in step
-  TaggedFr rplain[2];        // rounds ahead: the challenge of round t as a canonical integer in rplain[t & 1], tag t + 1
+  Fr challenge;              // the last challenge of a launch that stops before the end (Montgomery form)
+  StrobeState st;            // transcript state after that challenge
+  TaggedFr rplain[2];        // the challenge of round t as a canonical integer in rplain[t & 1], tag t + 1
+  unsigned long long macc[2][5][8];  // rounds in step: message t while the blocks add their shares, in macc[t & 1]
   TaggedFr gsum[2][16];      // message t tabulated as a polynomial in the challenge before it, scaled, in gsum[t & 1], tag t + 1
   unsigned long long gacc[2][16][8];  // the same grid while the blocks add their shares: 64-bit sums of 32-bit limbs
 };
