@@ -318,10 +318,17 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
       (uint32_t)px.world <= kTailMax / 2) {
     uint32_t logw = 0;
     while ((1 << logw) < px.world) logw++;
-    const uint32_t R = rounds - 9 + logw;       // leaves kTailMax / world entries per table, last challenge unbound
-    const uint32_t left = rounds + logw;         // messages until the end of the protocol
+    // The hand-over: when the ranks together hold `gathered_entries` entries per table (last challenge unbound) they
+    // store their chunks into each other's boxes and every rank finishes on the whole tables by itself, without
+    // further exchanges.  With the multi-block kernel for that (at most three tables) the hand-over is at 2^14
+    // entries and the rest runs ahead of its challenges; otherwise at 1024 entries into the single-block kernel.
+    const bool own_rest = L <= 3 && ctx->ahead_log >= 2 && rounds + logw >= 15;
+    const uint32_t gathered_log = own_rest ? 14 : 10;
+    const uint64_t gathered_entries = 1ull << gathered_log;
+    const uint32_t R = rounds + 1 + logw - gathered_log;  // messages of the sharded launch
+    const uint32_t left = rounds + logw;                   // messages until the end of the protocol
     const size_t bytes = ((size_t)left * (L + 2)) * sizeof(Fr) + sizeof(StrobeState);
-    if (R <= rounds && bytes <= 8192 - 16) {
+    if (R >= 1 && R <= rounds && bytes <= 8192 - 16) {
       const StrobeState st = strobe_now();
       Fr* d_msgs = reinterpret_cast<Fr*>(ctx->tail_out);
       Fr* d_chal = d_msgs + (size_t)left * (L + 1);
@@ -335,19 +342,36 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
       if (lrc == 0) {
         ctx->launches++;
         comm_peer_advance(comm, R);
-        Fr** last = ((R - 1) & 1) ? ping : pong;
+        const Fr* const* last = R == 1 ? cur : (((R - 1) & 1) ? ping : pong);
         const uint64_t m = size >> (R - 1);
         // the ranks store their chunks into each other's boxes (one launch; a wait that runs out lands
         // in the resident kernel's error word, which the read-back below checks)
         const Fr* gathered[kMaxPolys];
         rc = comm_peer_gather(ctx, comm, L, last, (uint32_t)m, &sh->error, gathered);
         if (rc) return rc;
-        if (launch_tail(L, gathered, kTailMax, true, *challenge, st, d_msgs + (size_t)R * (L + 1), d_chal + R, ctx->final_out,
-                        d_st, ctx->stream, &sh->challenge, &sh->st))
+        if (own_rest) {
+          Fr* scratch = nullptr;
+          rc = ctx->reserve_aux((size_t)L * (gathered_entries / 2 + gathered_entries / 4 + 2) * sizeof(Fr), (void**)&scratch);
+          if (rc) return rc;
+          Fr *tping[kMaxPolys], *tpong[kMaxPolys];
+          for (int i = 0; i < L; i++) {
+            tping[i] = scratch + (size_t)i * (gathered_entries / 2);
+            tpong[i] = scratch + (size_t)L * (gathered_entries / 2) + (size_t)i * (gathered_entries / 4);
+          }
+          uint32_t ahead_from = 0;
+          // message k of the rest is message R + k of the protocol: the kernel writes it at index k + 1
+          const ResidentToEnd te = {ctx->ahead_log, ctx->final_out, d_st, &ahead_from, true};
+          if (launch_resident(L, gathered, tping, tpong, gathered_entries, gathered_log, st, ctx->rs.sink.partials,
+                              ctx->rs.max_blocks, ctx->sm_count, sh, d_msgs + (size_t)(R - 1) * (L + 1), d_chal + (R - 1),
+                              ctx->stream, nullptr, &te))
+            return fail(ZK_ERR_CUDA, "sharded rounds: the launch that finishes on the gathered tables failed");
+        } else if (launch_tail(L, gathered, kTailMax, true, *challenge, st, d_msgs + (size_t)R * (L + 1), d_chal + R, ctx->final_out,
+                               d_st, ctx->stream, &sh->challenge, &sh->st)) {
           return fail(ZK_ERR_CUDA, "tail kernel launch failed");
+        }
         ctx->launches++;
         ZK_CUDA(cudaGetLastError());
-        rc = collect_device_rounds(0, left, true, R);
+        rc = collect_device_rounds(0, left, true, own_rest ? left : R);
         if (rc) return rc;
         ctx->sharded_finished = true;
         *finals_done = true;
@@ -373,7 +397,7 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
         // All rounds in one cooperative launch: in step while the tables are large, prepared ahead of their
         // challenges once they are small, final values included.
         uint32_t ahead_from = 0;
-        const ResidentToEnd te = {ctx->ahead_log, ctx->final_out, d_st, &ahead_from};
+        const ResidentToEnd te = {ctx->ahead_log, ctx->final_out, d_st, &ahead_from, false};
         ctx->prof_begin(ZK_PROF_ROUND, 64.0 * L * (double)(cur_size / 2) + 192.0 * L * (double)(cur_size / 2));
         const int lrc = launch_resident(L, cur, ping, pong, cur_size, rounds, st, ctx->rs.sink.partials, ctx->rs.max_blocks,
                                         ctx->sm_count, sh, d_msgs, d_chal, ctx->stream, nullptr, &te);

@@ -82,7 +82,7 @@ int launch_tail(int num_poly, const Fr* const* src, uint32_t size, bool fold_fir
 // are enough.
 constexpr int kPeerRanks = 16;   // ranks a box has slots for (one NVSwitch domain)
 constexpr int kPeerVals = 16;    // values per exchange (a round message has at most 5)
-constexpr uint32_t kGatherEntries = 1024;  // entries per gathered table (the single-block tail kernel's size)
+constexpr uint32_t kGatherEntries = 1u << 14;  // entries per gathered table: the hand-over of a sharded prove to the rounds every rank runs on its own
 struct ExchangeBox {
   uint2 words[2][kPeerRanks][kPeerVals][8];
   // hand-over of a sharded prove to the single-block tail: every rank's chunk of each table, stored
@@ -160,6 +160,9 @@ struct ResidentToEnd {    // launch_resident runs to the end of the protocol
   Fr* out_final;          // L table values at the challenge point, then their product
   StrobeState* out_st;    // transcript state after the last challenge
   uint32_t* ahead_from;   // host: first round that was prepared ahead of its challenge (for diagnostics)
+  bool pending;           // the tables still have to be bound on sh->challenge, left with the transcript state in sh->st by
+                          // the launch before (which stopped early): log2(size) - 1 messages remain, all prepared ahead;
+                          // message k of them goes to out_msgs[(k + 1) * (L + 1)], its challenge to out_chal[k + 1]
 };
 // px != nullptr: the tables are this rank's chunks of a sharded instance; every round's message is the
 // sum over the ranks, exchanged through the peer boxes by the block that completes the local sums.

@@ -41,6 +41,8 @@ struct ResidentParams {
   uint64_t size;        // entries per table on entry (a power of two, at least 4)
   uint32_t rounds;      // messages to produce
   uint32_t spin_limit;  // polls before a wait gives up
+  uint32_t pending;     // non-zero: no round in step; the tables are entered with sh->challenge still to be bound (as if
+                        // round 0 had been done elsewhere), ahead_from = 1, and sh->st holds the transcript state
   uint32_t ahead_from;  // first round whose message is prepared ahead of its challenge; >= rounds: none, and the
                         // last challenge is left unbound.  Otherwise 1 <= ahead_from < rounds, rounds = log2(size),
                         // and the launch also binds the last challenge and writes the final values.
@@ -457,6 +459,22 @@ __global__ void __launch_bounds__(kThreads, (L <= 1 ? 3 : 2)) k_resident(const R
   // consecutive tiles go to different blocks first, so that a small table spreads over the SMs
   const uint64_t warp_global = blockIdx.x + (uint64_t)gridDim.x * warp, warp_stride = (uint64_t)gridDim.x * kWarps;
 
+  if (p.pending) {
+    if constexpr (L <= 3) {
+      if (threadIdx.x == 0) atomicAdd(&p.sh->arrive, 1u);  // stands for the ticket of the round that was done elsewhere
+      if (blockIdx.x == 0 && warp == 0) {
+        ws.a = lane < 25 ? p.sh->st.lanes[lane] : 0;
+        ws.pos = p.sh->st.pos;
+        ws.pos_begin = p.sh->st.pos_begin;
+        Fr one_plain = Fr::zero();
+        one_plain.v[0] = 1;
+        const Fr rc = mul_call(p.sh->challenge, one_plain);  // out of Montgomery form
+        if (lane < 3) st_tagged_part(&p.sh->rplain[0], rc, 1, lane);
+      }
+      ahead_rounds<L>(p, ws, cur, cur_size, stream, &ok_flag, &flag);
+    }
+    return;
+  }
   for (uint32_t round = 0; round < p.rounds; round++) {
     Fr s[NV];
     if (round == 0) {
@@ -631,6 +649,7 @@ int launch_resident_t(const Fr* const* src, Fr* const* ping, Fr* const* pong, ui
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
   p.ahead_from = rounds;
+  p.pending = 0;
   p.out_final = nullptr;
   p.out_st = nullptr;
   if (to_end) {
@@ -642,8 +661,9 @@ int launch_resident_t(const Fr* const* src, Fr* const* ping, Fr* const* pong, ui
     // (a single table has no products in its grid, only additions: it can run ahead four times earlier)
     const uint32_t lg = to_end->ahead_log + (L == 1 ? 2 : 0);
     uint32_t t = 1;
-    while (t + 1 < rounds && (size >> (t - 1)) > (1ull << lg)) t++;
+    while (!to_end->pending && t + 1 < rounds && (size >> (t - 1)) > (1ull << lg)) t++;
     p.ahead_from = t;
+    p.pending = to_end->pending ? 1u : 0u;
     // a block per unit of the first pass ahead (and the transcript block), so that the units spread over the SMs
     const uint64_t quads = (size >> (t - 1)) >> 2;
     const uint64_t units = quads ? (quads + AheadSplit<L < 4 ? L : 1>::QW - 1) / AheadSplit<L < 4 ? L : 1>::QW : 1;
@@ -672,7 +692,14 @@ int launch_resident_t(const Fr* const* src, Fr* const* ping, Fr* const* pong, ui
     *to_end->ahead_from = t;
   }
   void* args[] = {&p};
-  if (cudaMemsetAsync(sh, 0, sizeof(ResidentShared), stream) != cudaSuccess) return -3;
+  // counters, tags and accumulators start from zero; a pending launch keeps the error word of the launch before
+  // (its waits then give up at once) beside the challenge and the state that launch left
+  if (p.pending) {
+    if (cudaMemsetAsync(sh, 0, offsetof(ResidentShared, error), stream) != cudaSuccess) return -3;
+    if (cudaMemsetAsync(&sh->garrive, 0, offsetof(ResidentShared, challenge) - offsetof(ResidentShared, garrive), stream) != cudaSuccess) return -3;
+  } else if (cudaMemsetAsync(sh, 0, offsetof(ResidentShared, challenge), stream) != cudaSuccess) {
+    return -3;
+  }
   if (cudaLaunchCooperativeKernel((const void*)k_resident<L>, dim3((unsigned)grid), dim3(kThreads), args, kStageBytes, stream) !=
       cudaSuccess) {
     cudaGetLastError();

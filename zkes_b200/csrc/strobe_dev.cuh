@@ -28,12 +28,14 @@ struct ResidentShared {
   unsigned int garrive;      // block tickets of the grid sums (rounds whose message is prepared ahead)
   unsigned int gseq;         // grid of message `gseq - 1` is complete in gsum[(gseq - 1) & 1]
   unsigned int pad[3];
-  Fr challenge;              // the last challenge of a launch that stops before the end (Montgomery form)
-  StrobeState st;            // transcript state after that challenge
   TaggedFr rplain[2];        // the challenge of round t as a canonical integer in rplain[t & 1], tag t + 1
-  unsigned long long macc[2][5][8];  // rounds in step: message t while the blocks add their shares, in macc[t & 1]
   TaggedFr gsum[2][16];      // message t tabulated as a polynomial in the challenge before it, scaled, in gsum[t & 1], tag t + 1
   unsigned long long gacc[2][16][8];  // the same grid while the blocks add their shares: 64-bit sums of 32-bit limbs
+  unsigned long long macc[2][5][8];   // rounds in step: message t while the blocks add their shares, in macc[t & 1]
+  // What a launch that stops before the end of the protocol leaves for the kernel that goes on; not cleared by
+  // the next launch, which may be that kernel.
+  Fr challenge;              // the last challenge (Montgomery form), still to be bound on the tables
+  StrobeState st;            // transcript state after that challenge
 };
 constexpr int kResidentGrid = 16;  // grid points of a message: (L + 1)^2 for L <= 3
 
