@@ -18,16 +18,26 @@ __device__ __forceinline__ Fr g_ld(const Fr* p) {
   return fr_from_chunks(lo, hi);
 }
 
-// T(c), c = 0..3, over the live entries (compute_round_message, :529-591).
-__global__ void __launch_bounds__(kGThreads) k_sbool_msg(const uint32_t* __restrict__ keys, const Fr* __restrict__ val,
+// T(c), c = 0..3, over the live entries (compute_round_message, :529-591): sum_j w_j sum_y aux(aux - 1) eq at the
+// point c.  The entries are ordered by (term, position), so a warp that walks a contiguous span of them stays
+// inside one term for thousands of entries: the weight is taken out of the inner sum (two products per point
+// instead of three) and multiplied in when a lane's term changes.
+__global__ void __launch_bounds__(kGThreads, 2) k_sbool_msg(const uint32_t* __restrict__ keys, const Fr* __restrict__ val,
                                                          const uint32_t* __restrict__ count, const Fr* __restrict__ eq,
                                                          const Fr* __restrict__ weights, uint32_t vars_left,
                                                          const MsgSink sink) {
   const uint32_t n = *count;
   const uint32_t mask = (vars_left >= 32) ? 0xffffffffu : ((1u << vars_left) - 1u);
   const Fr one = Fr::one();
-  Fr s[4] = {Fr::zero(), Fr::zero(), Fr::zero(), Fr::zero()};
-  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+  Fr s[4] = {Fr::zero(), Fr::zero(), Fr::zero(), Fr::zero()};      // weighted, all terms
+  Fr inner[4] = {Fr::zero(), Fr::zero(), Fr::zero(), Fr::zero()};  // the term this lane is in, without its weight
+  uint32_t cur_term = 0xffffffffu;
+  const uint32_t lane = threadIdx.x & 31;
+  const uint64_t warp = (uint64_t)blockIdx.x * (kGThreads / 32) + (threadIdx.x >> 5);
+  const uint64_t warps = (uint64_t)gridDim.x * (kGThreads / 32);
+  const uint64_t span = (((uint64_t)n + warps - 1) / warps + 31) & ~31ull;  // entries per warp, a multiple of the warp width
+  const uint64_t begin = warp * span, end = begin + span < n ? begin + span : n;
+  for (uint64_t i = begin + lane; i < end; i += 32) {
     const uint32_t key = keys[i];
     const bool lead = (key & 1u) == 0 || i == 0 || keys[i - 1] != key - 1;
     if (!lead) continue;
@@ -39,18 +49,33 @@ __global__ void __launch_bounds__(kGThreads) k_sbool_msg(const uint32_t* __restr
       v1 = g_ld(val + i);
     }
     const uint32_t pos = key & mask;
-    const Fr w = g_ld(weights + (vars_left >= 32 ? 0 : (key >> vars_left)));
+    const uint32_t term = vars_left >= 32 ? 0 : (key >> vars_left);
+    if (term != cur_term) {
+      if (cur_term != 0xffffffffu) {
+        const Fr w = g_ld(weights + cur_term);
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          s[c] = add(s[c], mul(w, inner[c]));
+          inner[c] = Fr::zero();
+        }
+      }
+      cur_term = term;
+    }
     const Fr e0 = g_ld(eq + (pos & ~1u)), e1 = g_ld(eq + (pos | 1u));
     const Fr dv = sub(v1, v0), de = sub(e1, e0);
     Fr aux = v0, e = e0;
 #pragma unroll
     for (int c = 0; c < 4; c++) {
-      // w * aux * (aux - 1) * eq at evaluation point c
-      const Fr t = mul(mul(w, aux), mul(sub(aux, one), e));
-      s[c] = add(s[c], t);
+      // aux * (aux - 1) * eq at evaluation point c
+      inner[c] = add(inner[c], mul(mul(aux, sub(aux, one)), e));
       aux = add(aux, dv);
       e = add(e, de);
     }
+  }
+  if (cur_term != 0xffffffffu) {
+    const Fr w = g_ld(weights + cur_term);
+#pragma unroll
+    for (int c = 0; c < 4; c++) s[c] = add(s[c], mul(w, inner[c]));
   }
   grid_sum<4, kGThreads / 32>(s, sink);
 }
