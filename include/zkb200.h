@@ -88,8 +88,9 @@ int zk_set_option(zk_ctx* ctx, int option, int value);
 /* Diagnostics: the host clock, in microseconds from the first entry, at which each round that the host steps
  * (a caller's transcript, the entry-form rounds of the sparse provers, sharded rounds) had its challenge, for
  * the proves since the last call (at most 4096 entries are kept).  Writes up to cap entries, sets *n to the
- * number recorded and clears the record.  Rounds that run inside the resident kernels leave no entry.  No
- * counterpart in the reference. */
+ * number recorded and clears the record.  Rounds that run inside the resident kernels leave no entry.  The
+ * sparse x dense prover also marks its entry, the return of its dense rounds and its exit.  No counterpart in the
+ * reference. */
 int zk_round_times(zk_ctx* ctx, double* out_us, uint32_t cap, uint32_t* n);
 /* The CUDA stream (cudaStream_t) every kernel of this context is launched on, so a host can
  * bracket calls with its own events. */

@@ -25,40 +25,67 @@ int fail(int code, const char* fmt, ...) {
 }  // namespace zk
 
 namespace zk {
+// The kernel that completes a message publishes it to the host-mapped mailbox and then writes this launch's
+// sequence number: poll for it instead of synchronising the stream.  `exchanged`: the message went through the
+// ranks' exchange, whose kernel reports a wait that ran out in the word beside the sequence word.
+int wait_mailbox(zk_ctx* ctx, bool exchanged, uint32_t round) {
+  volatile unsigned int* flag =
+      reinterpret_cast<volatile unsigned int*>(reinterpret_cast<char*>(ctx->mailbox) + 16 * sizeof(Fr));
+  const unsigned int want = ctx->rs.sink.seq;
+  const auto t0 = std::chrono::steady_clock::now();
+  uint64_t spins = 0;
+  while (*flag != want) {
+    if ((++spins & 0x3fff) == 0) {
+      cudaError_t e = cudaStreamQuery(ctx->stream);
+      if (e != cudaSuccess && e != cudaErrorNotReady) return fail(ZK_ERR_CUDA, "round kernel failed: %s", cudaGetErrorString(e));
+      const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+      if (e == cudaSuccess && *flag != want && waited > 1.0)
+        return fail(ZK_ERR_TIMEOUT, "round %u: the stream drained without publishing the message", round);
+      if (waited > 60.0) return fail(ZK_ERR_TIMEOUT, "round %u: no message after 60 s", round);
+    }
+  }
+  if (exchanged) {
+    volatile unsigned int* err = reinterpret_cast<volatile unsigned int*>(reinterpret_cast<char*>(ctx->mailbox) + 16 * sizeof(Fr) + 4);
+    if (*err != 0) {
+      *err = 0;  // only the peer-exchange kernel writes the word: leave it clear for rounds that take the NCCL path
+      return fail(ZK_ERR_TIMEOUT, "round %u: the other ranks' partial sums did not arrive", round);
+    }
+  }
+  return ZK_OK;
+}
+
+// Every rank's 32-bit count in one exchange (the same machinery as a round message: peer stores or an NCCL
+// all-gather, published to the polling host): rank r puts its count into a 64-bit slot of its own in one of up
+// to four values, so that the sum over the ranks is the list of counts.  out: world counts.
+int exchange_counts(zk_ctx* ctx, zk_comm* comm, uint32_t mine, uint32_t* out) {
+  const int world = comm_world(comm), rank = comm_rank(comm);
+  if (world > 16) return fail(ZK_ERR_ARG, "exchange_counts: more than 16 ranks");
+  Fr* enc = reinterpret_cast<Fr*>(ctx->host_small);
+  for (int i = 0; i < 4; i++) enc[i] = Fr::zero();
+  enc[rank / 4].v[2 * (rank % 4)] = mine;
+  (void)ctx->next_msg_scratch(true);  // a sequence number for this exchange
+  ZK_CUDA(cudaMemcpyAsync(ctx->rs.sink.msg, enc, 4 * sizeof(Fr), cudaMemcpyHostToDevice, ctx->stream));
+  int rc = comm_sum_fr(ctx, comm, ctx->rs.sink.msg, 4);
+  if (rc) return rc;
+  rc = wait_mailbox(ctx, true, 0);
+  if (rc) return rc;
+  const Fr* sum = reinterpret_cast<const Fr*>(ctx->mailbox);
+  for (int r = 0; r < world; r++) out[r] = sum[r / 4].v[2 * (r % 4)];
+  return ZK_OK;
+}
+
 // Reads the round message the last kernel left in rs.msg, records it, runs the Fiat-Shamir
 // step (callback or built-in transcript) and records the challenge.
 int fs_round(zk_ctx* ctx, zk_comm* comm, int n_msgs, uint32_t round, zk_fs_round_fn fs, void* fs_user, zk_transcript* tr,
-             uint64_t* round_msgs, uint64_t* challenges, Fr* challenge) {
+             uint64_t* round_msgs, uint64_t* challenges, Fr* challenge, bool exchanged_by_kernel) {
   ZK_CUDA(cudaGetLastError());
-  if (comm) {  // every rank holds a partial message: sum them so all ranks absorb the same scalars
+  if (comm && !exchanged_by_kernel) {  // every rank holds a partial message: sum them so all ranks absorb the same scalars
     int rc = comm_sum_fr(ctx, comm, ctx->rs.sink.msg, n_msgs);
     if (rc) return rc;
   }
-  // The kernel that completes the message publishes it to the host-mapped mailbox and then
-  // writes this launch's sequence number; poll for it instead of synchronising the stream.
   {
-    volatile unsigned int* flag =
-        reinterpret_cast<volatile unsigned int*>(reinterpret_cast<char*>(ctx->mailbox) + 16 * sizeof(Fr));
-    const unsigned int want = ctx->rs.sink.seq;
-    const auto t0 = std::chrono::steady_clock::now();
-    uint64_t spins = 0;
-    while (*flag != want) {
-      if ((++spins & 0x3fff) == 0) {
-        cudaError_t e = cudaStreamQuery(ctx->stream);
-        if (e != cudaSuccess && e != cudaErrorNotReady) return fail(ZK_ERR_CUDA, "round kernel failed: %s", cudaGetErrorString(e));
-        const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
-        if (e == cudaSuccess && *flag != want && waited > 1.0)
-          return fail(ZK_ERR_TIMEOUT, "round %u: the stream drained without publishing the message", round);
-        if (waited > 60.0) return fail(ZK_ERR_TIMEOUT, "round %u: no message after 60 s", round);
-      }
-    }
-  }
-  if (comm) {  // the peer-exchange kernel's wait ran out: it said so in the word beside the sequence word
-    volatile unsigned int* err = reinterpret_cast<volatile unsigned int*>(reinterpret_cast<char*>(ctx->mailbox) + 16 * sizeof(Fr) + 4);
-    if (*err != 0) {
-      *err = 0;  // only that kernel writes the word: leave it clear for rounds that take the NCCL path
-      return fail(ZK_ERR_TIMEOUT, "round %u: the other ranks' partial sums did not arrive", round);
-    }
+    const int rc = wait_mailbox(ctx, comm != nullptr, round);
+    if (rc) return rc;
   }
   const Fr* msg = reinterpret_cast<const Fr*>(ctx->mailbox);
   uint64_t* out_msg = round_msgs + (uint64_t)round * n_msgs * 4;
@@ -73,11 +100,7 @@ int fs_round(zk_ctx* ctx, zk_comm* comm, int n_msgs, uint32_t round, zk_fs_round
     *challenge = transcript_challenge_scalar(tr->m, (const uint8_t*)"challenge", 9);
   }
   fr_store(challenges + 4 * (uint64_t)round, *challenge);
-  if (ctx->round_times.size() < 4096) {
-    const auto now = std::chrono::steady_clock::now();
-    if (ctx->round_times.empty()) ctx->round_t0 = now;
-    ctx->round_times.push_back(std::chrono::duration<double, std::micro>(now - ctx->round_t0).count());
-  }
+  ctx->time_mark();
   return ZK_OK;
 }
 }  // namespace zk

@@ -45,15 +45,12 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
   const uint32_t K = (uint32_t)nnz;
   // Sharded: every rank must leave the entry form at the same round (the dense rounds exchange
   // differently, and may gather the tables), so the rule below uses the largest entry count of any rank.
+  ctx->time_mark();  // call entry
   uint32_t K_rule = K;
   if (comm) {
-    uint32_t* d_k = reinterpret_cast<uint32_t*>(ctx->tail_buf);
-    ZK_CUDA(cudaMemcpyAsync(d_k, &K, 4, cudaMemcpyHostToDevice, s));
-    int grc = comm_gather_bytes(ctx, comm, d_k, 4, d_k + 64);
+    uint32_t all[16];
+    const int grc = exchange_counts(ctx, comm, K, all);
     if (grc) return grc;
-    ZK_CUDA(cudaMemcpyAsync(ctx->host_small, d_k + 64, 4 * (size_t)world, cudaMemcpyDeviceToHost, s));
-    ZK_CUDA(cudaStreamSynchronize(s));
-    const uint32_t* all = reinterpret_cast<const uint32_t*>(ctx->host_small);
     for (int r = 0; r < world; r++)
       if (all[r] > K_rule) K_rule = all[r];
   }
@@ -140,6 +137,7 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
       rc = linear_rounds(ctx, comm, 2, num_var - round, d_cur, d_ping, d_pong, round, fs, fs_user, tr, round_msgs,
                          challenges, &challenge, &done);
       if (rc) return rc;
+      ctx->time_mark();  // the dense rounds are back
       if (!done) {
         launch_final(2, true, d_cur, challenge, ctx->final_out, s);
         ctx->launches++;
@@ -147,13 +145,18 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
       finished = true;
       break;
     }
-    const RoundScratch sc = ctx->next_msg_scratch(comm != nullptr);
+    // Sharded over peer memory: the message kernel's last block exchanges the message itself (no launch between)
+    PeerExchange px;
+    const bool fused = comm && world <= kPeerRanks && ctx->rs.sink.pub_flag && comm_peer_args(ctx, comm, &px);
+    const RoundScratch sc = ctx->next_msg_scratch(comm != nullptr && !fused);
     // per live entry: index + value read, one 64-byte pair of b gathered
     ctx->prof_begin(ZK_PROF_SPARSE_MSG, (e_pending ? 144.0 : 104.0) * k_upper);
-    launch_sparse_msg(e_idx[e], e_val[e], counts + e, k_upper, b_cur, pending ? &pend_r : nullptr, e_pending ? &e_r : nullptr, sc, s);
+    launch_sparse_msg(e_idx[e], e_val[e], counts + e, k_upper, b_cur, pending ? &pend_r : nullptr, e_pending ? &e_r : nullptr, sc, s,
+                      fused ? &px : nullptr, fused ? px.xseq_base + 1 : 0);
     ctx->prof_end();
     ctx->launches++;
-    rc = fs_round(ctx, comm, 3, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
+    if (fused) comm_peer_advance(comm, 1);
+    rc = fs_round(ctx, comm, 3, round, fs, fs_user, tr, round_msgs, challenges, &challenge, fused);
     if (rc != ZK_OK) return rc;
     // Fold of the dense table.  When the next round is still in entry form its message can fold
     // the few values it needs on the fly, so this fold waits and is done together with the next
@@ -215,6 +218,7 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
     fr_store(final_table0 + 4, fin[1]);
   }
   fr_store(final_eval, fin[2]);
+  ctx->time_mark();  // call exit
   if (comm) return check_round_chain(round_msgs, challenges, total_var, 3);
   return ZK_OK;
 }

@@ -83,6 +83,12 @@ struct zk_ctx {
   // proves had its challenge: where the time of a prove goes, round by round (zk_round_times)
   std::vector<double> round_times;
   std::chrono::steady_clock::time_point round_t0;
+  void time_mark() {  // one more entry of round_times: now
+    if (round_times.size() >= 4096) return;
+    const auto now = std::chrono::steady_clock::now();
+    if (round_times.empty()) round_t0 = now;
+    round_times.push_back(std::chrono::duration<double, std::micro>(now - round_t0).count());
+  }
   MsmStatsPod last_msm;          // shape of the most recent MSM (window width, windows, entries)
   uint64_t msm_entries_sum = 0;  // digit entries (= bucket additions) of every MSM since the last zk_msm_work reset
   uint64_t msm_bucket_sum = 0;   // buckets reduced by those MSMs
@@ -143,7 +149,8 @@ void comm_peer_advance(zk_comm* c, unsigned int n);
 int comm_peer_gather(zk_ctx* ctx, zk_comm* c, int n_tables, const Fr* const* chunks, uint32_t m, unsigned int* error_word,
                      const Fr** tables_out);
 int fs_round(zk_ctx* ctx, zk_comm* comm, int n_msgs, uint32_t round, fs_round_fn_t fs, void* fs_user, zk_transcript* tr,
-             uint64_t* round_msgs, uint64_t* challenges, Fr* challenge);
+             uint64_t* round_msgs, uint64_t* challenges, Fr* challenge,
+             bool exchanged_by_kernel = false);
 int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr** cur, Fr** ping, Fr** pong,
                   uint32_t round_offset, fs_round_fn_t fs, void* fs_user, zk_transcript* tr, uint64_t* round_msgs,
                   uint64_t* challenges, Fr* challenge, bool* finals_done);
@@ -152,6 +159,7 @@ int sharded_tail(zk_ctx* ctx, zk_comm* comm, int L, uint32_t n_local, fs_round_f
                  zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges, Fr* challenge);
 // comm.cu
 int comm_world(const zk_comm* c);
+int exchange_counts(zk_ctx* ctx, zk_comm* comm, uint32_t mine, uint32_t* out);  // api.cu: every rank's count, through the message exchange
 int comm_rank(const zk_comm* c);
 int comm_sum_fr(zk_ctx* ctx, zk_comm* c, Fr* vals, int n_vals);
 int comm_gather_fr(zk_ctx* ctx, zk_comm* c, const Fr* vals, int n_vals, Fr* out);

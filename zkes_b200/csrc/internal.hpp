@@ -171,8 +171,11 @@ int launch_resident(int num_poly, const Fr* const* src, Fr* const* ping, Fr* con
                     Fr* out_chal, cudaStream_t stream, const PeerExchange* px = nullptr, const ResidentToEnd* to_end = nullptr);
 
 // sparse.cu
+// exchange != nullptr (one rank of a sharded instance, sc.sink publishes to the host): the kernel's last block
+// exchanges the message with the other ranks' kernels as exchange number xseq and publishes the sum.
 void launch_sparse_msg(uint32_t* idx, Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
-                       const Fr* pending, const Fr* bind, const RoundScratch& sc, cudaStream_t s);
+                       const Fr* pending, const Fr* bind, const RoundScratch& sc, cudaStream_t s,
+                       const PeerExchange* exchange = nullptr, unsigned int xseq = 0);
 void launch_sparse_bind(uint32_t* idx, Fr* val, const uint32_t* count, uint32_t upper, const Fr& r, int sm_count,
                         cudaStream_t s);
 void launch_scatter_runs(const uint32_t* idx, const Fr* val, const uint32_t* count, uint32_t upper, Fr* dense,

@@ -95,4 +95,64 @@ __device__ __forceinline__ void grid_sum(Fr (&s)[NV], const MsgSink& sink) {
   }
 }
 
+// grid_sum for one rank of a sharded instance: the last block to arrive also exchanges the totals with the other
+// ranks' kernels through the peer boxes (every rank's kernel does the same at its end), adds the shares in rank
+// order and publishes the complete message, with the outcome of the wait in the word beside the sequence word:
+// the exchange needs no launch of its own.  sink.pub_flag must be set.
+template <int NV, int kWarps>
+__device__ __forceinline__ void grid_sum_exchange(Fr (&s)[NV], const MsgSink& sink, const PeerExchange& px, unsigned int xseq) {
+  Fr* partials = sink.partials;
+  unsigned int* counter = sink.counter;
+  __shared__ Fr sh[kWarps][NV];
+  __shared__ Fr tot[NV];
+  __shared__ uint32_t stage[kPeerRanks * NV * 8];
+  __shared__ int ok_shared;
+  __shared__ bool is_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int c = 0; c < NV; c++) {
+    Fr t = warp_sum(s[c]);
+    if (lane == 0) sh[warp][c] = t;
+  }
+  __syncthreads();
+  if (threadIdx.x < NV) {
+    Fr t = sh[0][threadIdx.x];
+    for (int w = 1; w < kWarps; w++) t = add(t, sh[w][threadIdx.x]);
+    partials[(size_t)blockIdx.x * NV + threadIdx.x] = t;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int ticket = atomicAdd(counter, 1u);
+    is_last = (ticket == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+#pragma unroll
+  for (int c = 0; c < NV; c++) {
+    Fr t = Fr::zero();
+    for (unsigned int b = threadIdx.x; b < gridDim.x; b += blockDim.x) t = add(t, ld_cg_fr(partials + (size_t)b * NV + c));
+    t = warp_sum(t);
+    if (lane == 0) sh[warp][c] = t;
+  }
+  __syncthreads();
+  if (threadIdx.x < NV) {
+    Fr t = sh[0][threadIdx.x];
+    for (int w = 1; w < kWarps; w++) t = add(t, sh[w][threadIdx.x]);
+    tot[threadIdx.x] = t;
+  }
+  if (threadIdx.x == 0) *counter = 0;
+  __syncthreads();
+  const bool ok = peer_exchange_sum(px, xseq, tot, NV, stage, &ok_shared, threadIdx.x, blockDim.x);
+  if (threadIdx.x < NV && ok) {
+    sink.msg[threadIdx.x] = tot[threadIdx.x];
+    st_fr_sys(sink.pub_msg + threadIdx.x, tot[threadIdx.x]);
+  }
+  if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(sink.pub_flag + 1) = ok ? 0u : 1u;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(sink.pub_flag) = sink.seq;
+}
+
 }  // namespace zk

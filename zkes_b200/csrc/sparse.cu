@@ -7,6 +7,7 @@
 // scattered into a dense table and the dense round kernel takes over.  The outputs equal those
 // of the dense prover on [a.to_dense(), b] (linear_prover.rs:43-191): zero entries of `a`
 // contribute nothing to any message.
+#include <cstring>
 #include "internal.hpp"
 #include "reduce.cuh"
 
@@ -56,7 +57,8 @@ template <bool DEFERRED, bool FOLD>
 __global__ void __launch_bounds__(kSpThreads, 2) k_sparse_msg(uint32_t* __restrict__ idx, Fr* __restrict__ val,
                                                               const uint32_t* __restrict__ count,
                                                               const Fr* __restrict__ dense, const FixedMul<FrParams> pend,
-                                                              const FixedMul<FrParams> bind, const MsgSink sink) {
+                                                              const FixedMul<FrParams> bind, const MsgSink sink,
+                                                              const PeerExchange px, const unsigned int xseq) {
   constexpr int DCH = DEFERRED ? 8 : 4;  // 16-byte chunks of dense values per entry
   constexpr int CH = DCH + 2;            // plus the entry's value
   extern __shared__ uint4 sp_stage[];    // [2 slots][CH chunks][kSpThreads]: a thread's chunks are kSpThreads apart
@@ -151,7 +153,10 @@ __global__ void __launch_bounds__(kSpThreads, 2) k_sparse_msg(uint32_t* __restri
     wide_trim<FrParams>(acc[c]);
     s[c] = redc<FrParams>(acc[c]);
   }
-  grid_sum<3, kSpThreads / 32>(s, sink);
+  if (xseq)  // one rank of a sharded instance: the last block exchanges the message with the other ranks' kernels
+    grid_sum_exchange<3, kSpThreads / 32>(s, sink, px, xseq);
+  else
+    grid_sum<3, kSpThreads / 32>(s, sink);
 }
 
 // Pass 1 of the entry fold: leaders per block.
@@ -316,7 +321,7 @@ inline int blocks_for(uint64_t n, int threads, int cap) {
 template <bool D, bool F>
 static void launch_sparse_msg_t(uint32_t* idx, Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
                                 const FixedMul<FrParams>& pt, const FixedMul<FrParams>& bt, const RoundScratch& sc,
-                                cudaStream_t s) {
+                                cudaStream_t s, const PeerExchange& px, unsigned int xseq) {
   constexpr size_t smem = (size_t)2 * ((D ? 8 : 4) + 2) * kSpThreads * sizeof(uint4);
   cudaFuncSetAttribute(k_sparse_msg<D, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   int occ = 0;
@@ -325,21 +330,29 @@ static void launch_sparse_msg_t(uint32_t* idx, Fr* val, const uint32_t* count, u
   int cap = sc.sm_count * occ;
   if (cap > sc.max_blocks) cap = sc.max_blocks;
   const int grid = blocks_for(upper, kSpThreads, cap);
-  k_sparse_msg<D, F><<<grid, kSpThreads, smem, s>>>(idx, val, count, dense, pt, bt, sc.sink);
+  k_sparse_msg<D, F><<<grid, kSpThreads, smem, s>>>(idx, val, count, dense, pt, bt, sc.sink, px, xseq);
 }
 
 void launch_sparse_msg(uint32_t* idx, Fr* val, const uint32_t* count, uint32_t upper, const Fr* dense,
-                       const Fr* pending, const Fr* bind, const RoundScratch& sc, cudaStream_t s) {
+                       const Fr* pending, const Fr* bind, const RoundScratch& sc, cudaStream_t s, const PeerExchange* exchange,
+                       unsigned int xseq) {
+  PeerExchange px;
+  if (exchange) {
+    px = *exchange;
+  } else {
+    memset(&px, 0, sizeof px);
+    xseq = 0;
+  }
   const FixedMul<FrParams> pt = pending ? make_fixed_mul(*pending) : FixedMul<FrParams>();
   const FixedMul<FrParams> bt = bind ? make_fixed_mul(*bind) : FixedMul<FrParams>();
   if (pending && bind)
-    launch_sparse_msg_t<true, true>(idx, val, count, upper, dense, pt, bt, sc, s);
+    launch_sparse_msg_t<true, true>(idx, val, count, upper, dense, pt, bt, sc, s, px, xseq);
   else if (pending)
-    launch_sparse_msg_t<true, false>(idx, val, count, upper, dense, pt, bt, sc, s);
+    launch_sparse_msg_t<true, false>(idx, val, count, upper, dense, pt, bt, sc, s, px, xseq);
   else if (bind)
-    launch_sparse_msg_t<false, true>(idx, val, count, upper, dense, pt, bt, sc, s);
+    launch_sparse_msg_t<false, true>(idx, val, count, upper, dense, pt, bt, sc, s, px, xseq);
   else
-    launch_sparse_msg_t<false, false>(idx, val, count, upper, dense, pt, bt, sc, s);
+    launch_sparse_msg_t<false, false>(idx, val, count, upper, dense, pt, bt, sc, s, px, xseq);
 }
 
 void launch_sparse_bind(uint32_t* idx, Fr* val, const uint32_t* count, uint32_t upper, const Fr& r, int sm_count,
