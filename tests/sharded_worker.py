@@ -359,6 +359,36 @@ def main():
                   ot = o.Transcript(b"sharded")
                   op, opr = o.sparse_dense_prove(n, idx, vals, dense, ot)
                   assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
+        # ---- large enough for the sharded launch to hand over at 2^14 gathered entries to the launch that runs the rest
+        # of the rounds ahead of their challenges on every rank (defaults: peer exchange, replication at 2^18)
+        ctx.set_option(ZK_OPT_PEER_EXCHANGE, 1)
+        ctx.set_option(ZK_OPT_REPLICATE_LOG, 18)
+        n = 15 + zd.log2_exact(world) - 1
+        idx, vals, dense, f = problem(n, 4000, 9)
+        a = [0] * (1 << n)
+        for i, v in zip(idx, vals):
+            a[i] = v
+        for tables in ([a, dense], [dense, f, a]):
+            t = Transcript(b"sharded")
+            t.append_u64(b"num_var", n)
+            t.append_u64(b"num_poly", len(tables))
+            local = [DenseMLPoly.from_evaluations(zd.shard_dense(tb, rank, world)) for tb in tables]
+            msgs, chals, fin_t, fin = zd.sharded_linear_prove(ctx, comm, n, local, t)
+            ot = o.Transcript(b"sharded")
+            op = o.LinearSumcheckProver(n, len(tables), ot)
+            opr = op.prove(tables, ot)
+            assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
+            assert fin_t == [x[0] for x in op.a_arrays]
+            assert t.challenge_scalar(b"after") == ot.challenge_scalar(b"after")
+        t = Transcript(b"sharded")
+        t.append_u64(b"num_var", n)
+        t.append_u64(b"num_poly", 2)
+        li, lv = zd.shard_sparse(idx, vals, rank, world, n)
+        ld = DenseMLPoly.from_evaluations(zd.shard_dense(dense, rank, world))
+        msgs, chals, fin_t, fin = zd.sharded_sparse_dense_prove(ctx, comm, n, li, lv, ld, t)
+        ot = o.Transcript(b"sharded")
+        op, opr = o.sparse_dense_prove(n, idx, vals, dense, ot)
+        assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
         # ---- MSM by point range, KZH commit by x-rows, fix_from_right over the top variables
         from zkes_b200 import curve
         rnd = random.Random(77)
