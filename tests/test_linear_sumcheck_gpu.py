@@ -243,3 +243,11 @@ def test_run_ahead_large_tables(ctx):
         run_both(ctx, tables, label=b"ahead-large")
     finally:
         ctx.set_option(ZK_OPT_AHEAD_LOG, 15)
+
+
+def test_run_ahead_option_range(ctx):
+    from zkes_b200._lib import ZK_OPT_AHEAD_LOG
+    for bad in (-1, 25):
+        with pytest.raises(Exception):
+            ctx.set_option(ZK_OPT_AHEAD_LOG, bad)
+    ctx.set_option(ZK_OPT_AHEAD_LOG, 15)
