@@ -136,6 +136,56 @@ def test_sparse_kzh_commit_open(ctx, dims, n, nnz, ones):
             assert (dy, cy, fs) == (ody, ocy, ofs)
 
 
+@pytest.mark.parametrize("dims,n,nnz", [(2, 6, 20), (2, 8, 200), (3, 7, 40), (3, 9, 300), (2, 6, 1), (2, 6, 64)])
+def test_selection_polynomial_commit(ctx, dims, n, nnz):
+    """A selection polynomial passes no values (every listed entry is one): its commitment is computed as plain
+    sums of SRS points over runs of the ordered index list, whatever order the caller lists them in; with explicit
+    ones, or with an index listed twice, it goes through the general MSM.  All must give the oracle's commitment."""
+    import ctypes
+    import numpy as np
+    from zkes_b200 import curve
+    from zkes_b200._lib import check, lib
+    from zkes_b200.field import to_mont_array
+    rnd = random.Random(77 * dims + n)
+    if dims == 2:
+        xl, yl = o.kzh2_degrees(n)
+        gk, tx, ty, rest = trapdoors(7, 1 << xl, 1 << yl)
+        osrs = o.KZH2SRS(n, gk, tx, ty, rest[0])
+        srs = kzh.KZHSRS.upload(ctx, 2, n, osrs.h_xy, osrs.h_y)
+    else:
+        xl, yl, zl = o.kzh3_degrees(n)
+        gk, tx, ty, tz = trapdoors(8, 1 << xl, 1 << yl, 1 << zl)
+        osrs = o.KZH3SRS(n, gk, tx, ty, tz[:1 << zl])
+        srs = kzh.KZHSRS.upload(ctx, 3, n, osrs.h_xyz, osrs.h_yz, osrs.h_z)
+    positions = sorted(rnd.sample(range(1 << n), nnz))
+    ev = {i: 1 for i in positions}
+    oc, odx = (o.sparse_kzh2_commit if dims == 2 else o.sparse_kzh3_commit)(osrs, ev)
+
+    def commit(order, with_values):
+        idx = np.array(order, dtype=np.uint64)
+        vals = to_mont_array([1] * len(order)) if with_values else None
+        c = np.zeros((1, 8), dtype=np.uint64)
+        dx = np.zeros((1 << srs.x_log, 12), dtype=np.uint64)
+        vp = ctypes.c_void_p
+        check(lib.zk_sparse_kzh_commit(ctx.handle, srs.handle, len(order), vp(idx.ctypes.data),
+                                       vp(vals.ctypes.data) if vals is not None else None, vp(c.ctypes.data), vp(dx.ctypes.data)),
+              "zk_sparse_kzh_commit")
+        return kzh.KZHCommitment(srs, curve.affine_from_array(c)[0], dx)
+
+    shuffled = positions[:]
+    rnd.shuffle(shuffled)
+    for order, with_values in ((positions, False), (shuffled, False), (positions, True)):
+        com = commit(order, with_values)
+        assert com.c == oc and com.d_x == odx
+    if nnz > 1:  # an index listed twice counts twice, as in the reference's loop over the entries
+        twice = shuffled + [shuffled[0]]
+        ev2 = dict(ev)
+        ev2[shuffled[0]] = 2
+        oc2, odx2 = (o.sparse_kzh2_commit if dims == 2 else o.sparse_kzh3_commit)(osrs, ev2)
+        com = commit(twice, False)
+        assert com.c == oc2 and com.d_x == odx2
+
+
 @pytest.mark.parametrize("n", [2, 4, 5])
 def test_kzh2_verify_g1(ctx, n):
     """The G1 / field steps of kzh2_verify (kzh2.rs:763-789) on the device: an honest opening passes,

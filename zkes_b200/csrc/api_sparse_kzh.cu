@@ -11,6 +11,10 @@ using namespace zk;
 
 namespace zk {
 int normalize_device(zk_ctx* ctx, const Jacobian* in, uint64_t n, Affine* out);
+// keyset.cu: distinct keys in increasing order through a bitmap of the domain
+size_t keyset_scratch_bytes(uint32_t n_terms, uint32_t num_var);
+int keyset_order(zk_ctx* ctx, const uint64_t* positions_dev, const uint64_t* term_begin_dev, uint32_t n_terms, uint64_t total,
+                 uint32_t num_var, void* scratch, uint32_t* keys_out, uint32_t bad_host[2]);
 }
 
 namespace {
@@ -44,8 +48,10 @@ int zk_sparse_kzh_commit(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const
   const uint64_t rows = 1ull << srs->x_log;
   const uint32_t low_bits = srs->n - srs->x_log;
   char* base = nullptr;
+  const bool selection = !vals && nnz && srs->n <= 30;  // every listed entry is one
   int rc = ctx->reserve_work(al(nnz * 8) + al(nnz * sizeof(Fr)) + 3 * al(nnz * 4 + 4) + al((rows + 1) * sizeof(Jacobian)) +
-                             al(sizeof(Affine)) + 1024, (void**)&base);
+                             al(sizeof(Affine)) + al(rows * sizeof(Xyzz)) + 256 +
+                             (selection ? al(keyset_scratch_bytes(1, srs->n)) : 0) + 1024, (void**)&base);
   if (rc) return rc;
   size_t off = 0;
   auto take = [&](size_t bytes) { char* p = base + off; off += al(bytes); return p; };
@@ -56,7 +62,36 @@ int zk_sparse_kzh_commit(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const
   uint32_t* d_row = (uint32_t*)take(nnz * 4 + 4);
   Jacobian* d_jac = (Jacobian*)take((rows + 1) * sizeof(Jacobian));
   Affine* d_c = (Affine*)take(sizeof(Affine));
+  void* d_sel = take(rows * sizeof(Xyzz));
+  uint64_t* d_begin = (uint64_t*)take(16);
   uint32_t* bad = ctx->rs.sink.counter + 16;
+  if (selection) {
+    // A selection polynomial: both commitments are plain sums of SRS points.  The indices are put in order through
+    // a bitmap of the domain (they are distinct: a duplicate sends the call to the general path below, which adds
+    // the point twice as the reference's loop would); a row of d_x is then a contiguous run of the list, and the
+    // digit, sort and bucket passes of the general MSM are not needed.
+    void* ks = take(keyset_scratch_bytes(1, srs->n));
+    uint64_t* h_begin = reinterpret_cast<uint64_t*>(reinterpret_cast<char*>(ctx->host_small) + 2048);
+    h_begin[0] = 0;
+    h_begin[1] = nnz;
+    ZK_CUDA(cudaMemcpyAsync(d_idx, indices, nnz * 8, cudaMemcpyHostToDevice, st));
+    ZK_CUDA(cudaMemcpyAsync(d_begin, h_begin, 16, cudaMemcpyHostToDevice, st));
+    uint32_t bad_keys[2] = {0, 0};
+    rc = keyset_order(ctx, d_idx, d_begin, 1, nnz, srs->n, ks, d_full, bad_keys);
+    if (rc) return rc;
+    if (bad_keys[0]) return fail(ZK_ERR_ARG, "sparse_kzh_commit: an index is outside the SRS domain");
+    if (!bad_keys[1]) {
+      rc = msm_select_sums(ctx, srs->h[0], srs->h[1], d_full, (uint32_t)nnz, low_bits, (uint32_t)rows, d_jac, d_sel);
+      if (rc) return rc;
+      Jacobian* h_c = reinterpret_cast<Jacobian*>(reinterpret_cast<char*>(ctx->host_small) + 4096);
+      ZK_CUDA(cudaMemcpyAsync(h_c, d_jac + rows, sizeof(Jacobian), cudaMemcpyDeviceToHost, st));
+      ZK_CUDA(cudaMemcpyAsync(d_x_jac_out, d_jac, rows * sizeof(Jacobian), cudaMemcpyDeviceToHost, st));
+      ZK_CUDA(cudaStreamSynchronize(st));
+      const Affine c_aff = jacobian_to_affine_host(*h_c);
+      memcpy(c_affine_out, &c_aff, sizeof(Affine));
+      return ZK_OK;
+    }
+  }
   if (nnz) {
     ZK_CUDA(cudaMemcpyAsync(d_idx, indices, nnz * 8, cudaMemcpyHostToDevice, st));
     if (vals) {

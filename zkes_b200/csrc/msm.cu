@@ -551,6 +551,96 @@ __global__ void k_set_infinity(Jacobian* out, uint32_t rows) {
   if (row < rows) out[row] = to_jacobian(Xyzz::inf());
 }
 
+// ---- Sums of selected SRS points: the commitment of a selection polynomial (every listed entry is one).
+// sparse_kzh2_commit / sparse_kzh3_commit (sparse_kzh2.rs:27-80, sparse_kzh3.rs:45-110) with all values one are
+// C = sum_i h_full[idx_i] and d_x[r] = sum_{i in row r} h_mid[idx_i mod 2^low_bits], row r = idx >> low_bits.  With the
+// indices in non-decreasing order a row is a contiguous run of the list, so the digit, sort and bucket passes of
+// the general MSM are not needed: sixteen lanes take a row, each sums its share with mixed additions, a tree over
+// the sixteen (through shared memory) finishes the row, and the same walk adds the row's share of C.
+constexpr int kSelLanes = 16;
+
+__device__ __forceinline__ uint32_t sel_lower_bound(const uint32_t* __restrict__ idx, uint32_t n, uint64_t key) {
+  uint32_t lo = 0, hi = n;  // first position with idx >= key
+  while (lo < hi) {
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    if (idx[mid] < key) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(128) k_select_sums(const Affine* __restrict__ full, const Affine* __restrict__ mid,
+                                                     const uint32_t* __restrict__ idx, uint32_t n, uint32_t low_bits,
+                                                     uint32_t rows, Jacobian* d_x, Xyzz* c_partial) {
+  const uint32_t group = (blockIdx.x * blockDim.x + threadIdx.x) / kSelLanes, gl = threadIdx.x % kSelLanes;
+  uint32_t lo = 0, hi = 0;
+  if (group < rows) {
+    lo = sel_lower_bound(idx, n, (uint64_t)group << low_bits);
+    hi = sel_lower_bound(idx, n, ((uint64_t)group + 1) << low_bits);
+  }
+  const uint32_t mask = low_bits >= 32 ? 0xffffffffu : (1u << low_bits) - 1u;
+  Xyzz acc_c = Xyzz::inf(), acc_r = Xyzz::inf();
+  for (uint32_t i = lo + gl; i < hi; i += kSelLanes) {
+    const uint32_t v = idx[i];
+    acc_c = add_mixed_calls(acc_c, ld_affine(full + v));
+    acc_r = add_mixed_calls(acc_r, ld_affine(mid + (v & mask)));
+  }
+  // the sixteen shares of a row: a tree through shared memory (lanes of a row are in one warp)
+  __shared__ Xyzz sh_c[128], sh_r[128];
+  sh_c[threadIdx.x] = acc_c;
+  sh_r[threadIdx.x] = acc_r;
+  __syncwarp();
+#pragma unroll 1
+  for (int off = kSelLanes / 2; off > 0; off >>= 1) {
+    if ((int)gl < off) {
+      add_to(&acc_c, &sh_c[threadIdx.x + off]);
+      add_to(&acc_r, &sh_r[threadIdx.x + off]);
+    }
+    __syncwarp();
+    if ((int)gl < off) {
+      sh_c[threadIdx.x] = acc_c;
+      sh_r[threadIdx.x] = acc_r;
+    }
+    __syncwarp();
+  }
+  if (group < rows && gl == 0) d_x[group] = to_jacobian(acc_r);
+  // the block's eight rows' shares of C: one more tree, by the first eight lanes of the block
+  __syncthreads();  // sh_c[16 k] holds row k's share
+  if (threadIdx.x < 8) {
+    Xyzz v = sh_c[kSelLanes * threadIdx.x];
+    __syncwarp(0xffu);
+#pragma unroll 1
+    for (int off = 4; off > 0; off >>= 1) {
+      sh_c[threadIdx.x] = v;
+      __syncwarp(0xffu);
+      if ((int)threadIdx.x < off) add_to(&v, &sh_c[threadIdx.x + off]);
+      __syncwarp(0xffu);
+    }
+    if (threadIdx.x == 0) st_xyzz(c_partial + blockIdx.x, v);
+  }
+}
+
+// C = the sum of the blocks' shares (one block).
+__global__ void __launch_bounds__(256) k_select_total(const Xyzz* __restrict__ c_partial, uint32_t rows, Jacobian* c_out) {
+  __shared__ Xyzz sh[256];
+  Xyzz acc = Xyzz::inf();
+  for (uint32_t r = threadIdx.x; r < rows; r += blockDim.x) {
+    const Xyzz v = ld_xyzz(c_partial + r);
+    add_to(&acc, &v);
+  }
+  sh[threadIdx.x] = acc;
+  __syncthreads();
+#pragma unroll 1
+  for (int off = 128; off > 0; off >>= 1) {
+    if ((int)threadIdx.x < off) {
+      const Xyzz v = sh[threadIdx.x + off];
+      add_to(&acc, &v);
+      sh[threadIdx.x] = acc;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *c_out = to_jacobian(acc);
+}
+
 }  // namespace
 
 // Window width for n points per row whose scalars have at most max_bits magnitude bits.
@@ -775,6 +865,24 @@ int msm_run_rows(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const
     stats->buckets = n_buckets;
     stats->max_bits = (int)max_bits;
   }
+  return 0;
+}
+
+// C (out_dev[rows]) and d_x (out_dev[0 .. rows)) of a selection polynomial over n indices in non-decreasing order
+// (device, 32-bit), below rows << low_bits.  scratch: rows Xyzz elements of device memory.
+int msm_select_sums(zk_ctx* ctx, const Affine* full, const Affine* mid, const uint32_t* idx_dev, uint32_t n, uint32_t low_bits,
+                    uint32_t rows, Jacobian* out_dev, void* scratch) {
+  cudaStream_t s = ctx->stream;
+  Xyzz* partial = reinterpret_cast<Xyzz*>(scratch);
+  const uint32_t threads = rows * kSelLanes;
+  const uint32_t blocks = (threads + 127) / 128;
+  k_select_sums<<<blocks, 128, 0, s>>>(full, mid, idx_dev, n, low_bits, rows, out_dev, partial);
+  k_select_total<<<1, 256, 0, s>>>(partial, blocks, out_dev + rows);
+  ctx->launches += 2;
+  ctx->msm_calls += 2;
+  ctx->msm_entries_sum += 2ull * n;
+  ctx->msm_bucket_sum += rows + 1;
+  ZK_CUDA(cudaGetLastError());
   return 0;
 }
 

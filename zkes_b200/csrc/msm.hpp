@@ -33,6 +33,10 @@ int msm_run(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const Fr* 
 int msm_run_rows(zk_ctx* ctx, const Affine* bases, const uint32_t* gather, const uint32_t* row_ids, const Fr* scalars,
                  uint64_t n, uint32_t rows, Jacobian* out_dev, MsmStats* stats, MsmPrep* prep = nullptr);
 
+// Commitment of a selection polynomial (all listed entries one) without the digit / sort / bucket passes: msm.cu.
+int msm_select_sums(zk_ctx* ctx, const Affine* full, const Affine* mid, const uint32_t* idx_dev, uint32_t n, uint32_t low_bits,
+                    uint32_t rows, Jacobian* out_dev, void* scratch);
+
 // CurveGroup::into_affine of one point on the host: a single inversion is a chain of some 380 dependent field
 // products, about 150 us for one GPU thread and a few tens of microseconds for a CPU core.
 inline Affine jacobian_to_affine_host(const Jacobian& j) {
