@@ -286,6 +286,7 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
                   uint64_t* challenges, Fr* challenge, bool* finals_done) {
   const uint64_t size = 1ull << rounds;
   *finals_done = false;
+  ctx->final_on_host = false;
   if (comm) ctx->sharded_finished = false;
   uint64_t cur_size = size;  // entries of the tables cur[] points at
   const bool tail_ok = ctx->device_tail && !fs && tr && !comm;
@@ -299,7 +300,11 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
     unsigned int* h_flags = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(ctx->host_small) + 8192 - 16);
     ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->tail_out, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     if (resident) ZK_CUDA(cudaMemcpyAsync(h_flags, sh, 16, cudaMemcpyDeviceToHost, ctx->stream));
+    // the final values come back in the same synchronisation (the kernels before this point have written them)
+    ZK_CUDA(cudaMemcpyAsync(reinterpret_cast<char*>(ctx->host_small) + kFinalHostOffset, ctx->final_out,
+                            (kMaxPolys + 1) * sizeof(Fr), cudaMemcpyDeviceToHost, ctx->stream));
     ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+    ctx->final_on_host = true;
     if (resident && h_flags[2] >= 2) return fail(ZK_ERR_TIMEOUT, "sharded rounds: another rank's partial sums or table chunk did not arrive");
     if (resident && h_flags[2] != 0) return fail(ZK_ERR_TIMEOUT, "resident round kernel: a wait for a challenge ran out");
     Fr* h_msgs = reinterpret_cast<Fr*>(ctx->host_small);
@@ -663,9 +668,12 @@ int linear_prove_impl(zk_ctx* ctx, zk_comm* comm, uint32_t num_var, uint32_t num
     if (rc) return rc;
   }
   ZK_CUDA(cudaGetLastError());
-  ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->final_out, (L + 1) * sizeof(Fr), cudaMemcpyDeviceToHost, ctx->stream));
-  ZK_CUDA(cudaStreamSynchronize(ctx->stream));
-  const Fr* fin = reinterpret_cast<const Fr*>(ctx->host_small);
+  const Fr* fin = reinterpret_cast<const Fr*>(reinterpret_cast<char*>(ctx->host_small) + kFinalHostOffset);
+  if (!(done && ctx->final_on_host && (world == 1 || ctx->sharded_finished))) {  // not read back with the rounds
+    fin = reinterpret_cast<const Fr*>(ctx->host_small);
+    ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->final_out, (L + 1) * sizeof(Fr), cudaMemcpyDeviceToHost, ctx->stream));
+    ZK_CUDA(cudaStreamSynchronize(ctx->stream));
+  }
   if (final_table0)
     for (int i = 0; i < L; i++) fr_store(final_table0 + 4 * i, fin[i]);
   fr_store(final_eval, fin[L]);

@@ -92,17 +92,25 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
   // entries: narrow the indices, copy the values, check order
   ZK_CUDA(cudaMemsetAsync(counts, 0, 64 * 4, s));
   ZK_CUDA(cudaMemcpyAsync(counts, &K, 4, cudaMemcpyHostToDevice, s));
+  // The order and range of the indices are checked on the device; the host reads the flag when it next hears from
+  // the stream (the first round's message), not before: out-of-range indices are clamped, so the kernels in
+  // between stay inside their tables whatever the caller passed.
+  uint32_t* h_bad = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(ctx->host_small) + 3072);
+  bool bad_checked = K == 0;
   if (K) {
-    launch_narrow_idx(idx64, K, e_idx[0], counts + 2, ctx->sm_count, s);
+    launch_narrow_idx(idx64, K, e_idx[0], counts + 2, ctx->sm_count, s, size);
     launch_check_sorted(e_idx[0], K, size, counts + 2, ctx->sm_count, s);
     ctx->launches += 2;
     ZK_CUDA(cudaMemcpyAsync(e_val[0], val_in, K * sizeof(Fr), cudaMemcpyDefault, s));
-    uint32_t bad = 0;
-    ZK_CUDA(cudaMemcpyAsync(ctx->host_small, counts + 2, 4, cudaMemcpyDeviceToHost, s));
-    ZK_CUDA(cudaStreamSynchronize(s));
-    memcpy(&bad, ctx->host_small, 4);
-    if (bad) return fail(ZK_ERR_ARG, "sparse_dense_prove: indices must be strictly increasing and below 2^num_var");
+    ZK_CUDA(cudaMemcpyAsync(h_bad, counts + 2, 4, cudaMemcpyDeviceToHost, s));
   }
+  auto check_bad = [&](bool synchronise) -> int {  // after the stream has passed the copy above
+    if (bad_checked) return ZK_OK;
+    if (synchronise) ZK_CUDA(cudaStreamSynchronize(s));
+    bad_checked = true;
+    if (*h_bad) return fail(ZK_ERR_ARG, "sparse_dense_prove: indices must be strictly increasing and below 2^num_var");
+    return ZK_OK;
+  };
 
   bool pending = false;  // the dense table still has to be folded by pend_r (done together with the next fold)
   Fr pend_r = Fr::zero();
@@ -114,9 +122,12 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
   Fr challenge = Fr::zero();
   uint64_t S = size;
   bool finished = false;  // the dense phase ran to the end (final values are in ctx->final_out)
+  bool dense_done = false;  // ... inside the device-resident rounds, which read the final values back with the rounds
   for (uint32_t round = 0; round < num_var; round++, S >>= 1) {
     if (K_rule && S <= dense_cap) {
       // hand over to the dense prover: scatter the entries into a table and run the remaining rounds
+      rc = check_bad(true);  // (no entry-form round ran: the flag has not been looked at yet)
+      if (rc != ZK_OK) return rc;
       if (pending) {  // not reached with the pairing rule below; kept so the hand-over never sees a stale table
         Fr* nb = other_buf(b_cur);
         launch_fold(b_cur, nb, pend_r, S, ctx->rs.max_blocks, s);
@@ -137,6 +148,7 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
       rc = linear_rounds(ctx, comm, 2, num_var - round, d_cur, d_ping, d_pong, round, fs, fs_user, tr, round_msgs,
                          challenges, &challenge, &done);
       if (rc) return rc;
+      dense_done = done;
       ctx->time_mark();  // the dense rounds are back
       if (!done) {
         launch_final(2, true, d_cur, challenge, ctx->final_out, s);
@@ -157,6 +169,8 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
     ctx->launches++;
     if (fused) comm_peer_advance(comm, 1);
     rc = fs_round(ctx, comm, 3, round, fs, fs_user, tr, round_msgs, challenges, &challenge, fused);
+    if (rc != ZK_OK) return rc;
+    rc = check_bad(false);  // the message kernel ran after the copy of the flag
     if (rc != ZK_OK) return rc;
     // Fold of the dense table.  When the next round is still in entry form its message can fold
     // the few values it needs on the fly, so this fold waits and is done together with the next
@@ -197,6 +211,8 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
     e_r = challenge;
     if (beside) ZK_CUDA(cudaStreamWaitEvent(s, ctx->ev_join, 0));
   }
+  rc = check_bad(true);
+  if (rc != ZK_OK) return rc;
   if (!finished && e_pending) {  // the entry form ran to the end (no entries anywhere): bind the last challenge
     launch_sparse_bind(e_idx[e], e_val[e], counts + e, k_upper, e_r, ctx->sm_count, s);
     ctx->launches++;
@@ -210,9 +226,12 @@ static int sparse_dense_impl(zk_ctx* ctx, zk_comm* comm, uint32_t total_var, uin
     if (rc) return rc;
   }
   ZK_CUDA(cudaGetLastError());
-  ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->final_out, 3 * sizeof(Fr), cudaMemcpyDeviceToHost, s));
-  ZK_CUDA(cudaStreamSynchronize(s));
-  const Fr* fin = reinterpret_cast<const Fr*>(ctx->host_small);
+  const Fr* fin = reinterpret_cast<const Fr*>(reinterpret_cast<char*>(ctx->host_small) + kFinalHostOffset);
+  if (!(dense_done && ctx->final_on_host && (!comm || ctx->sharded_finished))) {  // not read back with the dense rounds
+    fin = reinterpret_cast<const Fr*>(ctx->host_small);
+    ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->final_out, 3 * sizeof(Fr), cudaMemcpyDeviceToHost, s));
+    ZK_CUDA(cudaStreamSynchronize(s));
+  }
   if (final_table0) {
     fr_store(final_table0, fin[0]);
     fr_store(final_table0 + 4, fin[1]);

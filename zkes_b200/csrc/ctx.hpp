@@ -54,6 +54,8 @@ struct MsmStatsPod {
 
 struct zk_comm;
 
+constexpr size_t kFinalHostOffset = 7168;  // zk_ctx::host_small: where the final values land when they are read back with the rounds
+
 struct zk_ctx {
   int device = 0;
   int sm_count = 0;
@@ -74,6 +76,7 @@ struct zk_ctx {
   void* cmp = nullptr;           // third grow-only scratch (compact small scalars of the MSM)
   size_t cmp_bytes = 0;
   uint64_t replicate_entries = zk::kReplicateEntries;  // sharded proves gather the tables at this many entries in all (0: never)
+  bool final_on_host = false;    // the dense round loop read final_out back together with its rounds (host_small + kFinalHostOffset)
   bool sharded_finished = false; // set by the dense round loop of a sharded prove when it gathered the tables and ran to the end
   bool peer_exchange = true;     // sharded proves exchange round messages through peer memory when the ranks could map it
   uint32_t exchange_wait_ms = 16000;  // bound of a device-side wait for another rank's words (ZK_OPT_EXCHANGE_WAIT_MS)

@@ -186,7 +186,8 @@ void launch_scatter(const uint32_t* idx, const Fr* val, const uint32_t* count, u
                     int sm_count, cudaStream_t s);
 void launch_check_sorted(const uint32_t* idx, uint32_t n, uint64_t limit, uint32_t* bad, int sm_count, cudaStream_t s);
 void launch_check_bound(const uint32_t* idx, uint32_t n, uint64_t limit, uint32_t* bad, int sm_count, cudaStream_t s);
-void launch_narrow_idx(const uint64_t* in, uint32_t n, uint32_t* out, uint32_t* bad, int sm_count, cudaStream_t s);
+void launch_narrow_idx(const uint64_t* in, uint32_t n, uint32_t* out, uint32_t* bad, int sm_count, cudaStream_t s,
+                       uint64_t clamp_below = 0);
 void launch_sd_final(const uint32_t* idx, const Fr* val, const uint32_t* count, const Fr* dense, Fr* out,
                      cudaStream_t s);
 

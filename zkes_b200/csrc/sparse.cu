@@ -288,10 +288,16 @@ __global__ void k_check_bound(const uint32_t* __restrict__ idx, uint32_t n, uint
 }
 
 // Narrow caller indices (u64) to the 32-bit form the kernels use; flags values >= 2^32.
-__global__ void k_narrow_idx(const uint64_t* __restrict__ in, uint32_t n, uint32_t* out, uint32_t* bad) {
+// With clamp_below > 0 a value at or above it is flagged and stored as clamp_below - 1, so that the kernels after
+// this one stay inside their tables whatever the caller passed (the host looks at the flag later).
+__global__ void k_narrow_idx(const uint64_t* __restrict__ in, uint32_t n, uint32_t* out, uint32_t* bad, uint64_t clamp_below) {
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-    const uint64_t v = in[i];
+    uint64_t v = in[i];
     if (v >> 32) *bad = 1;
+    if (clamp_below && v >= clamp_below) {
+      *bad = 1;
+      v = clamp_below - 1;
+    }
     out[i] = (uint32_t)v;
   }
 }
@@ -387,8 +393,9 @@ void launch_check_bound(const uint32_t* idx, uint32_t n, uint64_t limit, uint32_
   k_check_bound<<<blocks_for(n, 256, sm_count * 8), 256, 0, s>>>(idx, n, limit, bad);
 }
 
-void launch_narrow_idx(const uint64_t* in, uint32_t n, uint32_t* out, uint32_t* bad, int sm_count, cudaStream_t s) {
-  k_narrow_idx<<<blocks_for(n, 256, sm_count * 8), 256, 0, s>>>(in, n, out, bad);
+void launch_narrow_idx(const uint64_t* in, uint32_t n, uint32_t* out, uint32_t* bad, int sm_count, cudaStream_t s,
+                       uint64_t clamp_below) {
+  k_narrow_idx<<<blocks_for(n, 256, sm_count * 8), 256, 0, s>>>(in, n, out, bad, clamp_below);
 }
 
 void launch_sd_final(const uint32_t* idx, const Fr* val, const uint32_t* count, const Fr* dense, Fr* out,
