@@ -389,9 +389,10 @@ int zk_kzh_verify_g1(zk_ctx* ctx, const zk_kzh_srs* srs, const uint64_t* point, 
                      int* ok, int* failed_check);
 
 /* sparse_kzh2_commit (src/crypto/polycommit/sparse_kzh2.rs:14-82) / sparse_kzh3_commit (sparse_kzh3.rs:32-110):
- * the polynomial is given by nnz (index, value) pairs with distinct indices below 2^n (host arrays).  vals may be
- * NULL: every listed entry is then one (a selection polynomial, as the auxiliary polynomials of the lookups are);
- * the same holds for the two opens below. */
+ * the polynomial is given by nnz (index, value) pairs with distinct indices below 2^n (host arrays, in any order).
+ * vals may be NULL: every listed entry is then one (a selection polynomial, as the auxiliary polynomials of the
+ * lookups are), and the commitment is computed as plain sums of SRS points instead of a multi-scalar product; the
+ * same holds for the two opens below. */
 int zk_sparse_kzh_commit(zk_ctx* ctx, const zk_kzh_srs* srs, uint64_t nnz, const uint64_t* indices, const uint64_t* vals,
                          uint64_t* c_affine_out, uint64_t* d_x_jac_out);
 /* sparse_kzh2_open (sparse_kzh2.rs:84-127): f_star_out receives 2^y_log elements. */
