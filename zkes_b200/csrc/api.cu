@@ -335,12 +335,12 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
     st.pad = 0;
     return st;
   };
-  // Sharded prove with the built-in transcript and peer-mapped exchange boxes: all local rounds in one
-  // cooperative launch per rank.  The block that completes a round's local sums exchanges them with the
-  // other ranks' kernels through the boxes (stores over NVLink, bounded wait) and runs the transcript
-  // step, so no round returns to the host.  The launch stops when the ranks together hold kTailMax
-  // entries per table; the chunks are gathered (rank order is table order) and every rank finishes in
-  // the single-block kernel, which also covers the rounds of the ranks' own variables.
+  // Sharded prove with the built-in transcript and peer-mapped exchange boxes: the local rounds in one
+  // cooperative launch per rank.  Block 0 exchanges a round's local sums with the other ranks' kernels through
+  // the boxes (stores over NVLink, bounded wait) and runs the transcript step, so no round returns to the host.
+  // The launch stops when the ranks together hold few entries per table; the chunks are gathered (rank order is
+  // table order) and every rank finishes on the whole tables by itself, which also covers the rounds of the
+  // ranks' own variables.
   PeerExchange px;
   if (comm && ctx->device_tail && !fs && tr && rounds >= 11 && comm_peer_args(ctx, comm, &px) &&
       (uint32_t)px.world <= kTailMax / 2) {
@@ -410,9 +410,9 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
   }
   for (uint32_t round = 0; round < rounds; round++) {
     if (tail_ok && (cur_size <= kTailMax || round == 0)) {
-      // Device-resident rounds.  Tables above kTailMax entries go through the cooperative multi-block
-      // kernel until kTailMax entries are left, then (or at once, for small tables) one block finishes
-      // in shared memory; messages, challenges and the transcript state come back in a single copy.
+      // Device-resident rounds: the cooperative multi-block kernel runs the whole protocol (at most three tables);
+      // otherwise it runs until kTailMax entries are left and one block finishes in shared memory (at once, for
+      // small tables).  Messages, challenges and the transcript state come back in a single copy.
       const StrobeState st = strobe_now();
       const uint32_t left = rounds - round;
       Fr* d_msgs = reinterpret_cast<Fr*>(ctx->tail_out);
