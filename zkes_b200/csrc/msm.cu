@@ -555,9 +555,9 @@ __global__ void k_set_infinity(Jacobian* out, uint32_t rows) {
 // sparse_kzh2_commit / sparse_kzh3_commit (sparse_kzh2.rs:27-80, sparse_kzh3.rs:45-110) with all values one are
 // C = sum_i h_full[idx_i] and d_x[r] = sum_{i in row r} h_mid[idx_i mod 2^low_bits], row r = idx >> low_bits.  With the
 // indices in non-decreasing order a row is a contiguous run of the list, so the digit, sort and bucket passes of
-// the general MSM are not needed: sixteen lanes take a row, each sums its share with mixed additions, a tree over
-// the sixteen (through shared memory) finishes the row, and the same walk adds the row's share of C.
-constexpr int kSelLanes = 16;
+// the general MSM are not needed: sixteen lanes take a row, each lane sums its share with mixed additions, a tree over
+// the lanes (through shared memory) finishes the row, and the same walk adds the row's share of C.
+constexpr int kSelLanes = 16;  // lanes per row (a full warp per row measured no faster: the calls are bound by their host steps)
 
 __device__ __forceinline__ uint32_t sel_lower_bound(const uint32_t* __restrict__ idx, uint32_t n, uint64_t key) {
   uint32_t lo = 0, hi = n;  // first position with idx >= key
@@ -584,7 +584,7 @@ __global__ void __launch_bounds__(128) k_select_sums(const Affine* __restrict__ 
     acc_c = add_mixed_calls(acc_c, ld_affine(full + v));
     acc_r = add_mixed_calls(acc_r, ld_affine(mid + (v & mask)));
   }
-  // the sixteen shares of a row: a tree through shared memory (lanes of a row are in one warp)
+  // the lanes' shares of a row: a tree through shared memory (the lanes of a row are in one warp)
   __shared__ Xyzz sh_c[128], sh_r[128];
   sh_c[threadIdx.x] = acc_c;
   sh_r[threadIdx.x] = acc_r;
@@ -603,17 +603,19 @@ __global__ void __launch_bounds__(128) k_select_sums(const Affine* __restrict__ 
     __syncwarp();
   }
   if (group < rows && gl == 0) d_x[group] = to_jacobian(acc_r);
-  // the block's eight rows' shares of C: one more tree, by the first eight lanes of the block
-  __syncthreads();  // sh_c[16 k] holds row k's share
-  if (threadIdx.x < 8) {
+  // the shares of C of the block's rows: one more tree, by the first lanes of the block
+  constexpr int kRowsPerBlock = 128 / kSelLanes;
+  constexpr unsigned kRowMask = (1u << kRowsPerBlock) - 1u;
+  __syncthreads();  // sh_c[kSelLanes k] holds row k's share
+  if (threadIdx.x < kRowsPerBlock) {
     Xyzz v = sh_c[kSelLanes * threadIdx.x];
-    __syncwarp(0xffu);
+    __syncwarp(kRowMask);
 #pragma unroll 1
-    for (int off = 4; off > 0; off >>= 1) {
+    for (int off = kRowsPerBlock / 2; off > 0; off >>= 1) {
       sh_c[threadIdx.x] = v;
-      __syncwarp(0xffu);
+      __syncwarp(kRowMask);
       if ((int)threadIdx.x < off) add_to(&v, &sh_c[threadIdx.x + off]);
-      __syncwarp(0xffu);
+      __syncwarp(kRowMask);
     }
     if (threadIdx.x == 0) st_xyzz(c_partial + blockIdx.x, v);
   }
