@@ -301,10 +301,12 @@ int linear_rounds(zk_ctx* ctx, zk_comm* comm, int L, uint32_t rounds, const Fr**
     ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->tail_out, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     if (resident) ZK_CUDA(cudaMemcpyAsync(h_flags, sh, 16, cudaMemcpyDeviceToHost, ctx->stream));
     // the final values come back in the same synchronisation (the kernels before this point have written them)
-    ZK_CUDA(cudaMemcpyAsync(reinterpret_cast<char*>(ctx->host_small) + kFinalHostOffset, ctx->final_out,
-                            (kMaxPolys + 1) * sizeof(Fr), cudaMemcpyDeviceToHost, ctx->stream));
+    const bool with_final = bytes <= kFinalHostOffset;  // (always, for tables that fit a GPU)
+    if (with_final)
+      ZK_CUDA(cudaMemcpyAsync(reinterpret_cast<char*>(ctx->host_small) + kFinalHostOffset, ctx->final_out,
+                              (kMaxPolys + 1) * sizeof(Fr), cudaMemcpyDeviceToHost, ctx->stream));
     ZK_CUDA(cudaStreamSynchronize(ctx->stream));
-    ctx->final_on_host = true;
+    ctx->final_on_host = with_final;
     if (resident && h_flags[2] >= 2) return fail(ZK_ERR_TIMEOUT, "sharded rounds: another rank's partial sums or table chunk did not arrive");
     if (resident && h_flags[2] != 0) return fail(ZK_ERR_TIMEOUT, "resident round kernel: a wait for a challenge ran out");
     Fr* h_msgs = reinterpret_cast<Fr*>(ctx->host_small);
