@@ -169,11 +169,16 @@ def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12)
     ctx.sync()
     setup_s = time.perf_counter() - t0
 
-    # ---- auxiliary selection polynomials: K = 2^n ones, position = table digit << n | element index
-    aux_pos = {}
+    # ---- auxiliary selection polynomials: K = 2^n ones, position = table digit << n | element index.  The lists live
+    # in pinned host memory, like the boolean sumchecks' below: each is committed once and opened twice, and a prover
+    # that hands the same list to the library three times would register it once
+    aux_pos, aux_pinned = {}, {}
     for n in sorted(set(lookups)):
         digits = rnd.integers(0, 1 << TABLE_BLOCK_LOG, size=1 << n, dtype=np.uint64)
-        aux_pos[n] = np.ascontiguousarray((digits << np.uint64(n)) | np.arange(1 << n, dtype=np.uint64))
+        t = torch.empty((1 << n,), dtype=torch.int64, pin_memory=True)
+        aux_pinned[n] = t  # keeps the pinned allocation alive
+        aux_pos[n] = t.numpy().view(np.uint64)
+        aux_pos[n][:] = (digits << np.uint64(n)) | np.arange(1 << n, dtype=np.uint64)
 
     # the position lists of the boolean sumchecks (one list per term, concatenated), in pinned host memory
     bool_terms = {}
