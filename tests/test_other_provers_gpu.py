@@ -30,7 +30,8 @@ def test_sparse_bool_golden(ctx):
 
 
 @pytest.mark.parametrize("n,terms,k", [(0, 1, 1), (1, 1, 1), (1, 2, 2), (3, 1, 8), (6, 3, 10), (9, 5, 100), (12, 4, 2000),
-                                       (13, 5, 512), (10, 0, 0), (8, 2, 0)])
+                                       (13, 5, 512), (10, 0, 0), (8, 2, 0),
+                                       (14, 64, 8192), (15, 40, 3000)])  # pairs by the hundred per warp; and mostly lone entries
 def test_sparse_bool_random(ctx, n, terms, k):
     rnd = random.Random(n * 31 + terms * 7 + k)
     w = [rnd.randrange(M) for _ in range(terms)]

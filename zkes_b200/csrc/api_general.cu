@@ -45,7 +45,7 @@ int zk_sumcheck_sparse_bool_prove(zk_ctx* ctx, uint32_t num_var, uint32_t n_term
   cudaStream_t s = ctx->stream;
   const uint64_t size = 1ull << num_var;
   char* base = nullptr;
-  size_t need = al((size + size / 2 + 8) * sizeof(Fr)) + al((num_var + 8) * sizeof(Fr)) + 2 * (al((K + 1) * 4ull) + al((K + 1) * sizeof(Fr))) +
+  size_t need = al((size + size / 2 + 8) * sizeof(Fr)) + al((size / 2 * 3 + 8) * sizeof(Fr)) + al((num_var + 8) * sizeof(Fr)) + 2 * (al((K + 1) * 4ull) + al((K + 1) * sizeof(Fr))) +
                 al((K / 256 + 2) * 4ull) + al((n_terms + 1) * sizeof(Fr)) + 4096;
   int rc = ctx->reserve_work(need, (void**)&base);
   if (rc) return rc;
@@ -53,6 +53,7 @@ int zk_sumcheck_sparse_bool_prove(zk_ctx* ctx, uint32_t num_var, uint32_t n_term
   auto take = [&](size_t bytes) { char* p = base + o; o += al(bytes); return p; };
   Fr* eq0 = (Fr*)take((size + 1) * sizeof(Fr));
   Fr* eq1 = (Fr*)take((size / 2 + 1) * sizeof(Fr));
+  Fr* eq_rec = (Fr*)take((size / 2 * 3 + 8) * sizeof(Fr));  // per-position records of the rounds after the first
   Fr* pt_dev = (Fr*)take((num_var + 8) * sizeof(Fr));
   uint32_t* e_key[2] = {(uint32_t*)take((K + 1) * 4ull), (uint32_t*)take((K + 1) * 4ull)};
   Fr* e_val[2] = {(Fr*)take((K + 1) * sizeof(Fr)), (Fr*)take((K + 1) * sizeof(Fr))};
@@ -94,7 +95,13 @@ int zk_sumcheck_sparse_bool_prove(zk_ctx* ctx, uint32_t num_var, uint32_t n_term
   for (uint32_t round = 0; round < num_var; round++) {
     const uint32_t vars_left = num_var - round;
     const uint64_t S = 1ull << vars_left;
-    launch_sbool_msg(e_key[e], e_val[e], counts + e, k_upper, eq_cur, d_w, vars_left, ctx->next_msg_scratch(false), s);
+    // every value is one in the first round (the fill above); later rounds read the eq factors from records
+    if (round) {
+      launch_eq_records(eq_cur, S / 2, eq_rec, ctx->sm_count, s);
+      ctx->launches++;
+    }
+    launch_sbool_msg(e_key[e], e_val[e], counts + e, k_upper, round ? eq_rec : eq_cur, d_w, vars_left, round == 0,
+                     ctx->next_msg_scratch(false), s);
     ctx->launches++;
     rc = fs_round(ctx, nullptr, 4, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
     if (rc) return rc;

@@ -19,64 +19,177 @@ __device__ __forceinline__ Fr g_ld(const Fr* p) {
 }
 
 // T(c), c = 0..3, over the live entries (compute_round_message, :529-591): sum_j w_j sum_y aux(aux - 1) eq at the
-// point c.  The entries are ordered by (term, position), so a warp that walks a contiguous span of them stays
-// inside one term for thousands of entries: the weight is taken out of the inner sum (two products per point
-// instead of three) and multiplied in when a lane's term changes.
+// point c, where aux(c) = v0 (1 - c) + v1 c for the pair (v0, v1) of an even / odd position.
+//
+// Entry by entry instead of pair by pair: (a + b)^2 - (a + b) = (a^2 - a) + (b^2 - b) + 2 a b, so a pair is its two
+// entries taken alone plus the cross term 2 v0 v1 c (1 - c).  An entry alone (value v on side b, nothing on the
+// other side) gives, with q = v^2:
+//   c = b: q - v         c = 1 - b: 0         c = 2: b ? 4q - 2v : q + v         c = 3: b ? 9q - 3v : 4q + 2v
+// times eq(c): one square and three products per entry whatever its parity (no branch), against eight for a pair
+// formed first.  The cross term (-4 v0 v1 eq(2) and -12 v0 v1 eq(3)) exists only where both sides are present,
+// one entry in sixteen for the selection polynomials of the lookups; those entries are queued per warp and worked
+// off thirty-two at a time, so that the rare case does not cost every warp its products.
+//
+// The eq factors come from a per-position record built once per round (k_eq_records; the table is far smaller than
+// the entry list, which repeats every position once per term): an even position holds {eq(0), eq(2), 2 eq(3)}, an
+// odd one {eq(1), 2 eq(2), 3 eq(3)}, so the entry's own factors are q - v, then q + v or 2q - v, then 2q + v or
+// 3q - v: sums of at most four field elements, formed without reduction (they stay below 2^256, which the second
+// operand of mul() may be).
+//
+// The entries are ordered by (term, position), so a warp that walks a contiguous span of them stays inside one term
+// for thousands of entries: the weight is taken out of the inner sum and multiplied in when a lane's term changes.
+//
+// ONES: the first round, where every value is one (the selection polynomials are 0/1): an entry alone gives
+// 2 eq(2) and 6 eq(3), a pair nothing; no value is read and nothing is multiplied but the weights.
+constexpr int kPairQueue = 64;  // per warp: a batch of 32 plus what one more sweep can add
+
+__global__ void __launch_bounds__(256) k_eq_records(const Fr* __restrict__ eq, uint64_t pairs, Fr* __restrict__ rec) {
+  for (uint64_t j = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; j < pairs; j += (uint64_t)gridDim.x * blockDim.x) {
+    const Fr e0 = g_ld(eq + 2 * j), e1 = g_ld(eq + 2 * j + 1);
+    const Fr de = sub(e1, e0);
+    const Fr e2 = add(e1, de), e3 = add(add(e1, de), de);
+    Fr* out = rec + 6 * j;
+    out[0] = e0;
+    out[1] = e2;
+    out[2] = add(e3, e3);
+    out[3] = e1;
+    out[4] = add(e2, e2);
+    out[5] = add(add(e3, e3), e3);
+  }
+}
+
+template <bool ONES>
 __global__ void __launch_bounds__(kGThreads, 2) k_sbool_msg(const uint32_t* __restrict__ keys, const Fr* __restrict__ val,
-                                                         const uint32_t* __restrict__ count, const Fr* __restrict__ eq,
-                                                         const Fr* __restrict__ weights, uint32_t vars_left,
-                                                         const MsgSink sink) {
+                                                            const uint32_t* __restrict__ count, const Fr* __restrict__ eq,
+                                                            const Fr* __restrict__ weights, uint32_t vars_left,
+                                                            const MsgSink sink) {
+  __shared__ uint32_t queue[ONES ? 1 : kGThreads / 32][ONES ? 1 : kPairQueue];
   const uint32_t n = *count;
   const uint32_t mask = (vars_left >= 32) ? 0xffffffffu : ((1u << vars_left) - 1u);
-  const Fr one = Fr::one();
-  Fr s[4] = {Fr::zero(), Fr::zero(), Fr::zero(), Fr::zero()};      // weighted, all terms
+  // the weighted sums over all terms are touched once per term: they live in shared memory, which leaves the
+  // registers to the four running sums and the products (no spills at two blocks per SM)
+  __shared__ Fr s_sm[4][kGThreads];
+  auto s_add = [&](int c, const Fr& x, bool negate) {
+    const Fr cur = s_sm[c][threadIdx.x];
+    s_sm[c][threadIdx.x] = negate ? sub(cur, x) : add(cur, x);
+  };
+#pragma unroll
+  for (int c = 0; c < 4; c++) s_sm[c][threadIdx.x] = Fr::zero();
   Fr inner[4] = {Fr::zero(), Fr::zero(), Fr::zero(), Fr::zero()};  // the term this lane is in, without its weight
   uint32_t cur_term = 0xffffffffu;
-  const uint32_t lane = threadIdx.x & 31;
-  const uint64_t warp = (uint64_t)blockIdx.x * (kGThreads / 32) + (threadIdx.x >> 5);
+  const uint32_t lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const uint64_t warp = (uint64_t)blockIdx.x * (kGThreads / 32) + wib;
   const uint64_t warps = (uint64_t)gridDim.x * (kGThreads / 32);
   const uint64_t span = (((uint64_t)n + warps - 1) / warps + 31) & ~31ull;  // entries per warp, a multiple of the warp width
   const uint64_t begin = warp * span, end = begin + span < n ? begin + span : n;
-  for (uint64_t i = begin + lane; i < end; i += 32) {
-    const uint32_t key = keys[i];
-    const bool lead = (key & 1u) == 0 || i == 0 || keys[i - 1] != key - 1;
-    if (!lead) continue;
-    Fr v0 = Fr::zero(), v1 = Fr::zero();
-    if ((key & 1u) == 0) {
-      v0 = g_ld(val + i);
-      if (i + 1 < n && keys[i + 1] == key + 1) v1 = g_ld(val + i + 1);
+  uint32_t queued = 0;  // the same in every lane of the warp
+  auto flush = [&](uint32_t term) {
+    const Fr w = g_ld(weights + term);
+    if constexpr (ONES) {
+      const Fr t2 = add(inner[2], inner[2]), t3 = add(inner[3], inner[3]);
+      s_add(2, mul(w, t2), false);
+      s_add(3, mul(w, add(add(t3, t3), t3)), false);
+      inner[2] = inner[3] = Fr::zero();
     } else {
-      v1 = g_ld(val + i);
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        s_add(c, mul(w, inner[c]), false);
+        inner[c] = Fr::zero();
+      }
     }
+  };
+  // the cross terms of 32 queued pairs (or of what is left, at the end); the even position's record holds
+  // eq(2) and 2 eq(3)
+  auto work_off = [&](uint32_t cnt) {
+    if (lane < cnt) {
+      const uint32_t i = queue[ONES ? 0 : wib][ONES ? 0 : lane];
+      const uint32_t key = keys[i];
+      const Fr* rec = eq + 3 * (uint64_t)(key & mask);
+      const Fr w = g_ld(weights + (vars_left >= 32 ? 0 : (key >> vars_left)));
+      const Fr wx = mul(w, mul(g_ld(val + i), g_ld(val + i + 1)));
+      const Fr a = mul(wx, g_ld(rec + 1)), b = mul(wx, g_ld(rec + 2));
+      const Fr a2 = add(a, a), b2 = add(b, b);
+      s_add(2, add(a2, a2), true);           // 4 v0 v1 eq(2)
+      s_add(3, add(add(b2, b2), b2), true);  // 12 v0 v1 eq(3)
+    }
+  };
+  for (uint64_t base = begin; base < end; base += 32) {
+    const uint64_t i = base + lane;
+    const bool valid = i < end;
+    const uint32_t key = valid ? keys[i] : 0u;
+    const bool odd = key & 1u;
     const uint32_t pos = key & mask;
     const uint32_t term = vars_left >= 32 ? 0 : (key >> vars_left);
-    if (term != cur_term) {
-      if (cur_term != 0xffffffffu) {
-        const Fr w = g_ld(weights + cur_term);
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-          s[c] = add(s[c], mul(w, inner[c]));
-          inner[c] = Fr::zero();
-        }
-      }
+    if (valid && term != cur_term) {
+      if (cur_term != 0xffffffffu) flush(cur_term);
       cur_term = term;
     }
-    const Fr e0 = g_ld(eq + (pos & ~1u)), e1 = g_ld(eq + (pos | 1u));
-    const Fr dv = sub(v1, v0), de = sub(e1, e0);
-    Fr aux = v0, e = e0;
+    if constexpr (ONES) {
+      // alone unless the neighbour of the same pair is the next (previous) entry
+      const bool lone = valid && (odd ? !(i > 0 && keys[i - 1] == key - 1) : !(i + 1 < n && keys[i + 1] == key + 1));
+      if (lone) {
+        const Fr e0 = g_ld(eq + (pos & ~1u)), e1 = g_ld(eq + (pos | 1u));
+        const Fr de = sub(e1, e0);
+        const Fr e2 = add(e1, de);
+        inner[2] = add(inner[2], e2);
+        inner[3] = add(inner[3], add(e2, de));
+      }
+    } else {
+      if (valid) {
+        const Fr v = g_ld(val + i);
+        const Fr* rec = eq + 3 * (uint64_t)pos;
+        const Fr q = mul(v, v);
+        uint32_t pm[8];
 #pragma unroll
-    for (int c = 0; c < 4; c++) {
-      // aux * (aux - 1) * eq at evaluation point c
-      inner[c] = add(inner[c], mul(mul(aux, sub(aux, one)), e));
-      aux = add(aux, dv);
-      e = add(e, de);
+        for (int k = 0; k < 8; k++) pm[k] = FrParams::mod(k);
+        Fr f0, f2, f3, sv, q2, q3, t2, t3;
+        sub_lazy(f0.v, q, v);                 // q - v (+ p)
+        (void)sub8(sv.v, pm, v.v);            // p - v
+        (void)add8(q2.v, q.v, q.v);           // 2q
+        (void)add8(q3.v, q2.v, q.v);          // 3q
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+          sv.v[k] = odd ? sv.v[k] : v.v[k];   // +v on the even side, -v on the odd one
+          t2.v[k] = odd ? q2.v[k] : q.v[k];
+          t3.v[k] = odd ? q3.v[k] : q2.v[k];
+        }
+        (void)add8(f2.v, t2.v, sv.v);         // q + v | 2q - v  (< 3p)
+        (void)add8(f3.v, t3.v, sv.v);         // 2q + v | 3q - v  (< 4p < 2^256)
+        const Fr same = mul(g_ld(rec), f0);
+        Fr acc;
+#pragma unroll
+        for (int k = 0; k < 8; k++) acc.v[k] = odd ? inner[1].v[k] : inner[0].v[k];
+        acc = add(acc, same);
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+          inner[0].v[k] = odd ? inner[0].v[k] : acc.v[k];
+          inner[1].v[k] = odd ? acc.v[k] : inner[1].v[k];
+        }
+        inner[2] = add(inner[2], mul(g_ld(rec + 1), f2));
+        inner[3] = add(inner[3], mul(g_ld(rec + 2), f3));
+      }
+      // an even entry whose odd neighbour is present: queue the pair's cross term
+      const bool pair = valid && !odd && i + 1 < n && keys[i + 1] == key + 1;
+      const uint32_t m = __ballot_sync(0xffffffffu, pair);
+      if (pair) queue[wib][queued + __popc(m & ((1u << lane) - 1u))] = (uint32_t)i;
+      queued += __popc(m);
+      __syncwarp();
+      if (queued >= 32) {
+        work_off(32);
+        __syncwarp();
+        if (lane + 32 < queued) queue[wib][lane] = queue[wib][lane + 32];  // at most 16 are left over
+        queued -= 32;
+        __syncwarp();
+      }
     }
   }
-  if (cur_term != 0xffffffffu) {
-    const Fr w = g_ld(weights + cur_term);
-#pragma unroll
-    for (int c = 0; c < 4; c++) s[c] = add(s[c], mul(w, inner[c]));
+  if constexpr (!ONES) {
+    if (queued) work_off(queued);
   }
+  if (cur_term != 0xffffffffu) flush(cur_term);
+  Fr s[4];
+#pragma unroll
+  for (int c = 0; c < 4; c++) s[c] = s_sm[c][threadIdx.x];
   grid_sum<4, kGThreads / 32>(s, sink);
 }
 
@@ -180,8 +293,16 @@ inline int g_blocks(uint64_t n, const RoundScratch& sc) {
 }  // namespace
 
 void launch_sbool_msg(const uint32_t* keys, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* eq,
-                      const Fr* weights, uint32_t vars_left, const RoundScratch& sc, cudaStream_t s) {
-  k_sbool_msg<<<g_blocks(upper, sc), kGThreads, 0, s>>>(keys, val, count, eq, weights, vars_left, sc.sink);
+                      const Fr* weights, uint32_t vars_left, bool ones, const RoundScratch& sc, cudaStream_t s) {
+  if (ones)
+    k_sbool_msg<true><<<g_blocks(upper, sc), kGThreads, 0, s>>>(keys, val, count, eq, weights, vars_left, sc.sink);
+  else
+    k_sbool_msg<false><<<g_blocks(upper, sc), kGThreads, 0, s>>>(keys, val, count, eq, weights, vars_left, sc.sink);
+}
+void launch_eq_records(const Fr* eq, uint64_t pairs, Fr* rec, int sm_count, cudaStream_t s) {
+  const uint64_t want = (pairs + 255) / 256;
+  const int blocks = (int)(want < (uint64_t)sm_count * 8 ? (want ? want : 1) : (uint64_t)sm_count * 8);
+  k_eq_records<<<blocks, 256, 0, s>>>(eq, pairs, rec);
 }
 void launch_sbool_final(const uint32_t* keys, const Fr* val, const uint32_t* count, const Fr* eq, const Fr* weights,
                         uint32_t n_terms, Fr* out, cudaStream_t s) {

@@ -51,8 +51,12 @@ int launch_int_fold(const void* t, const Fr* eq, uint64_t n_rows, uint64_t m_col
                     cudaStream_t s);
 
 // general.cu
+// eq: the plain table when `ones` (first round, every value one), else the per-position records of launch_eq_records
 void launch_sbool_msg(const uint32_t* keys, const Fr* val, const uint32_t* count, uint32_t upper, const Fr* eq,
-                      const Fr* weights, uint32_t vars_left, const RoundScratch& sc, cudaStream_t s);
+                      const Fr* weights, uint32_t vars_left, bool ones, const RoundScratch& sc, cudaStream_t s);
+// rec[3 p .. 3 p + 2] for every position p of the 2 * pairs entries of eq: {eq(0), eq(2), 2 eq(3)} (p even) or
+// {eq(1), 2 eq(2), 3 eq(3)} (p odd) of p's pair
+void launch_eq_records(const Fr* eq, uint64_t pairs, Fr* rec, int sm_count, cudaStream_t s);
 void launch_sbool_final(const uint32_t* keys, const Fr* val, const uint32_t* count, const Fr* eq, const Fr* weights,
                         uint32_t n_terms, Fr* out, cudaStream_t s);
 void launch_fill_ones(Fr* out, uint32_t n, int sm_count, cudaStream_t s);
