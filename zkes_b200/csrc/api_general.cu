@@ -111,6 +111,9 @@ int zk_sumcheck_sparse_bool_prove(zk_ctx* ctx, uint32_t num_var, uint32_t n_term
     ctx->launches += 1 + launch_sparse_fold(e_key[e], e_val[e], counts + e, k_upper, challenge, block_counts, e_key[e ^ 1],
                                             e_val[e ^ 1], counts + (e ^ 1), s);
     e ^= 1;
+    // a term keeps at most one entry per remaining position: the bound the next round's grids are sized by
+    const uint64_t cap = (uint64_t)n_terms * (S / 2);
+    if (cap < k_upper) k_upper = (uint32_t)cap;
   }
   launch_sbool_final(e_key[e], e_val[e], counts + e, eq_cur, d_w, n_terms, ctx->final_out, s);
   ctx->launches++;

@@ -170,16 +170,25 @@ __global__ void __launch_bounds__(kSpThreads) k_sparse_count(const uint32_t* __r
   if (threadIdx.x == 0) block_counts[blockIdx.x] = (uint32_t)c;
 }
 
-// Pass 2: exclusive scan of the block counts by one block; total goes to count_out.
+// Pass 2: exclusive scan of the block counts by one block; total goes to count_out.  Eight counts per thread and
+// sweep (a serial prefix inside the thread, then the usual two-level scan of the thread totals), so that the half
+// million counts of a 2^27-entry list take sixty sweeps.
+constexpr int kScanPerThread = 8;
 __global__ void __launch_bounds__(1024) k_scan_blocks(uint32_t* block_counts, uint32_t n_blocks, uint32_t* count_out) {
   __shared__ uint32_t warp_tot[32];
   __shared__ uint32_t carry;
   if (threadIdx.x == 0) carry = 0;
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (uint32_t base = 0; base < n_blocks; base += 1024) {
-    const uint32_t i = base + threadIdx.x;
-    const uint32_t v = i < n_blocks ? block_counts[i] : 0;
+  for (uint32_t base = 0; base < n_blocks; base += 1024 * kScanPerThread) {
+    const uint32_t i0 = base + threadIdx.x * kScanPerThread;
+    uint32_t c[kScanPerThread];
+    uint32_t v = 0;
+#pragma unroll
+    for (int k = 0; k < kScanPerThread; k++) {
+      c[k] = i0 + k < n_blocks ? block_counts[i0 + k] : 0;
+      v += c[k];
+    }
     uint32_t x = v;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
@@ -198,10 +207,15 @@ __global__ void __launch_bounds__(1024) k_scan_blocks(uint32_t* block_counts, ui
       warp_tot[lane] = t;  // inclusive over warps
     }
     __syncthreads();
-    const uint32_t before = carry + (warp ? warp_tot[warp - 1] : 0) + x - v;
-    if (i < n_blocks) block_counts[i] = before;
+    uint32_t before = carry + (warp ? warp_tot[warp - 1] : 0) + x - v;
+    const uint32_t sweep_total = warp_tot[31];
+#pragma unroll
+    for (int k = 0; k < kScanPerThread; k++) {
+      if (i0 + k < n_blocks) block_counts[i0 + k] = before;
+      before += c[k];
+    }
     __syncthreads();
-    if (threadIdx.x == 1023) carry = before + v;
+    if (threadIdx.x == 0) carry += sweep_total;
     __syncthreads();
   }
   if (threadIdx.x == 0) *count_out = carry;
