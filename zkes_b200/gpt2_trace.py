@@ -214,6 +214,7 @@ def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12)
                                 vp(dx.ctypes.data)), "zk_kzh_commit")
         commitments[("d", n)] = dx
         n_dense_commits += 1
+    dense_commit_s = time.perf_counter() - t0  # each call returns its result on the host, so the split needs no sync
     item = len(dense)
     for n in lookups:
         for _ in range(TABLE_BLOCKS):
@@ -339,6 +340,7 @@ def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12)
                                    vp(commitments[("d", n)].ctypes.data), vp(dy.ctypes.data), vp(cy.ctypes.data), vp(fs.ctypes.data)),
                   "zk_kzh3_open")
         n_dense_open += 1
+    dense_open_s = time.perf_counter() - t0
     item = len(dense)
     for n in lookups:
         m = n + TABLE_BLOCK_LOG
@@ -377,9 +379,11 @@ def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12)
                 "not a run of the reference's gpt2 bin",
         "config": f"12 layers, d_model 768 (padded 1024), d_ff 3072 (4096), 12 heads (16), sequence length {seq_len}, "
                   f"KZH{dims}, lookups in 5 blocks of 4 table bits; seed {seed}",
-        "commit_s": commit_s, "prove_s": prove_s,
+        "commit_s": commit_s, "commit_breakdown_s": {"dense": dense_commit_s, "selection": commit_s - dense_commit_s},
+        "prove_s": prove_s,
         "prove_breakdown_s": {"node_proofs": nodes_s, "range_preprocessing_and_table_sumcheck": range_s,
                               "sparse_bool_sumchecks": bool_s, "openings": open_s},
+        "openings_breakdown_s": {"dense": dense_open_s, "selection": open_s - dense_open_s},
         "srs_setup_s": setup_s,
         "calls": {"dense_commits": len(dense), "sparse_commits": TABLE_BLOCKS * len(lookups), "node_calls": counts,
                   "range_accumulates": TABLE_BLOCKS * len(lookups), "sparse_bool_proves": len(bool_terms),
