@@ -75,6 +75,8 @@ def parse_args():
     ap.add_argument("--kzh3-log", type=int, default=28)
     ap.add_argument("--linear-log", type=int, default=20)
     ap.add_argument("--gpt2-layers", type=int, default=12, help="fewer layers are for profiling captures only")
+    ap.add_argument("--gpt2-open-threads", type=int, default=4,
+                    help="host threads that open the trace's commitments (the reference opens from a rayon loop); 1 = one by one")
     return ap.parse_args()
 
 
@@ -961,7 +963,8 @@ def gpt2_leg(env: Env):
     # The replay is about a thousand host-driven calls of a few hundred microseconds each, so another tenant's load
     # on the host cores shows up as whole phases taking several times longer in one run and not in the next: two
     # timed runs, the faster one reported, both listed.
-    runs = [gpt2_trace.run(env.ctx, comm=env.comm, rank=env.rank, world=env.world, seq_len=128, seed=4, layers=env.args.gpt2_layers)
+    runs = [gpt2_trace.run(env.ctx, comm=env.comm, rank=env.rank, world=env.world, seq_len=128, seed=4, layers=env.args.gpt2_layers,
+                           open_threads=env.args.gpt2_open_threads)
             for _ in range(2)]
     out = min(runs, key=lambda r: r["prove_s"] + r["commit_s"])
     out["warmup"] = "one layer replayed once, untimed"

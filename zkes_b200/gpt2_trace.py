@@ -31,6 +31,8 @@ openings to threads; the sumchecks share one transcript and run on every rank al
 """
 from __future__ import annotations
 
+from concurrent.futures import ThreadPoolExecutor
+
 import ctypes
 import time
 from ctypes import c_void_p as vp
@@ -137,7 +139,7 @@ class _Buffers:
         return self.out[n]
 
 
-def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12):
+def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12, open_threads=4):
     """Runs the trace and returns the JSON-ready report (seconds per phase, call counts)."""
     import torch
 
@@ -323,10 +325,11 @@ def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12)
     # ---- openings (dag/mod.rs:876-936): one per dense commitment, two per auxiliary polynomial
     barrier()
     t0 = time.perf_counter()
+    # The reference opens its commitments from a rayon loop (dag/mod.rs:893-936): the replay hands them to a few
+    # host threads, each call on a lane of the context (ctypes releases the interpreter lock for the call).
     n_dense_open = n_sparse_open = 0
-    for i, n in enumerate(dense):
-        if not mine(i):
-            continue
+
+    def open_dense(n):
         if dims == 2:
             out = np.zeros((1 << srs[n].y_log, 4), dtype=np.uint64)
             check(lib.zk_kzh2_open(h, srs[n].handle, n, vp(buf.fr(n, 8).data_ptr()), ZK_MEM_DEVICE, vp(point.ctypes.data), n,
@@ -339,27 +342,46 @@ def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12)
             check(lib.zk_kzh3_open(h, s.handle, n, vp(buf.fr(n, 8).data_ptr()), ZK_MEM_DEVICE, vp(point.ctypes.data), n,
                                    vp(commitments[("d", n)].ctypes.data), vp(dy.ctypes.data), vp(cy.ctypes.data), vp(fs.ctypes.data)),
                   "zk_kzh3_open")
-        n_dense_open += 1
-    dense_open_s = time.perf_counter() - t0
-    item = len(dense)
-    for n in lookups:
+
+    def open_selection(n):
         m = n + TABLE_BLOCK_LOG
         s = srs[m]
+        if dims == 2:
+            out = np.zeros((1 << s.y_log, 4), dtype=np.uint64)
+            check(lib.zk_sparse_kzh2_open(h, s.handle, 1 << n, vp(aux_pos[n].ctypes.data), None,
+                                          vp(point.ctypes.data), m, vp(out.ctypes.data)), "zk_sparse_kzh2_open")
+        else:
+            dy = np.zeros((1 << s.y_log, 12), dtype=np.uint64)
+            cy = np.zeros((1, 8), dtype=np.uint64)
+            fs = np.zeros((1 << s.z_log, 4), dtype=np.uint64)
+            check(lib.zk_sparse_kzh3_open(h, s.handle, 1 << n, vp(aux_pos[n].ctypes.data), None,
+                                          vp(point.ctypes.data), m, vp(commitments[("s", m)].ctypes.data), vp(dy.ctypes.data),
+                                          vp(cy.ctypes.data), vp(fs.ctypes.data)), "zk_sparse_kzh3_open")
+
+    def run_all(fn, items):
+        if open_threads <= 1 or len(items) < 2:
+            for n in items:
+                fn(n)
+        else:
+            for _ in pool.map(fn, items):  # re-raises a worker's exception
+                pass
+
+    pool = ThreadPoolExecutor(max_workers=open_threads) if open_threads > 1 else None
+    dense_items = [n for i, n in enumerate(dense) if mine(i)]
+    n_dense_open = len(dense_items)
+    run_all(open_dense, dense_items)
+    dense_open_s = time.perf_counter() - t0
+    sel_items = []
+    item = len(dense)
+    for n in lookups:
         for _ in range(2 * TABLE_BLOCKS):
             if mine(item):
-                if dims == 2:
-                    out = np.zeros((1 << s.y_log, 4), dtype=np.uint64)
-                    check(lib.zk_sparse_kzh2_open(h, s.handle, 1 << n, vp(aux_pos[n].ctypes.data), None,
-                                                  vp(point.ctypes.data), m, vp(out.ctypes.data)), "zk_sparse_kzh2_open")
-                else:
-                    dy = np.zeros((1 << s.y_log, 12), dtype=np.uint64)
-                    cy = np.zeros((1, 8), dtype=np.uint64)
-                    fs = np.zeros((1 << s.z_log, 4), dtype=np.uint64)
-                    check(lib.zk_sparse_kzh3_open(h, s.handle, 1 << n, vp(aux_pos[n].ctypes.data), None,
-                                                  vp(point.ctypes.data), m, vp(commitments[("s", m)].ctypes.data), vp(dy.ctypes.data),
-                                                  vp(cy.ctypes.data), vp(fs.ctypes.data)), "zk_sparse_kzh3_open")
-                n_sparse_open += 1
+                sel_items.append(n)
             item += 1
+    n_sparse_open = len(sel_items)
+    run_all(open_selection, sel_items)
+    if pool is not None:
+        pool.shutdown()
     barrier()
     open_s = time.perf_counter() - t0
     lib.zk_transcript_free(tr)
@@ -384,6 +406,7 @@ def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12)
         "prove_breakdown_s": {"node_proofs": nodes_s, "range_preprocessing_and_table_sumcheck": range_s,
                               "sparse_bool_sumchecks": bool_s, "openings": open_s},
         "openings_breakdown_s": {"dense": dense_open_s, "selection": open_s - dense_open_s},
+        "opening_threads": open_threads,
         "srs_setup_s": setup_s,
         "calls": {"dense_commits": len(dense), "sparse_commits": TABLE_BLOCKS * len(lookups), "node_calls": counts,
                   "range_accumulates": TABLE_BLOCKS * len(lookups), "sparse_bool_proves": len(bool_terms),
