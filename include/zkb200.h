@@ -230,6 +230,15 @@ int zk_sumcheck_sparse_dense_prove_sharded(zk_ctx* ctx, zk_comm* comm, uint32_t 
                                            const uint64_t* local_dense, zk_mem mem, zk_fs_round_fn fs, void* fs_user,
                                            zk_transcript* tr, uint64_t* round_msgs, uint64_t* challenges,
                                            uint64_t* final_table0, uint64_t* final_eval);
+/* The boolean-check prover sharded by terms (the reference's prover is one loop over the terms,
+ * linear_prover.rs:529-591: no counterpart of the split itself): every rank passes its own share of the terms
+ * (weights, positions, n_positions as in zk_sumcheck_sparse_bool_prove; a rank may hold none), the same num_var and
+ * eq_point, and an equal-state transcript.  The ranks' partial round messages and partial final values are summed
+ * across the ranks; all ranks return the outputs of the unsharded call over all the terms. */
+int zk_sumcheck_sparse_bool_prove_sharded(zk_ctx* ctx, zk_comm* comm, uint32_t num_var, uint32_t n_local_terms,
+                                          const uint64_t* weights, const uint64_t* positions, const uint64_t* n_positions,
+                                          const uint64_t* eq_point, zk_fs_round_fn fs, void* fs_user, zk_transcript* tr,
+                                          uint64_t* round_msgs, uint64_t* challenges, uint64_t* final_eval);
 
 /* MSM sharded by point range: every rank passes its own bases and scalars (n_local pairs), the
  * partial G1 sums are all-gathered and added; all ranks receive the same Jacobian point. */

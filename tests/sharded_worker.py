@@ -389,6 +389,25 @@ def main():
         ot = o.Transcript(b"sharded")
         op, opr = o.sparse_dense_prove(n, idx, vals, dense, ot)
         assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
+        # ---- the boolean-check prover with its terms dealt to the ranks (a rank may hold none), through peer memory
+        # and through NCCL
+        for peer in (1, 0):
+            ctx.set_option(ZK_OPT_PEER_EXCHANGE, peer)
+            for bn, terms, k in [(4, 1, 5), (6, 3, 10), (9, 5, 100), (12, 2 * world + 1, 700), (0, 2, 1)]:
+                rnd = random.Random(bn * 31 + terms)
+                w = [rnd.randrange(o.R_MOD) for _ in range(terms)]
+                pos = [rnd.sample(range(1 << bn), min(k, 1 << bn)) for _ in range(terms)]
+                pt = [rnd.randrange(o.R_MOD) for _ in range(bn)]
+                t = Transcript(b"range")
+                t.append_u64(b"num_var", bn)
+                t.append_u64(b"num_poly", 3)
+                msgs, chals, fin = zd.sharded_sparse_bool_prove(ctx, comm, bn, w[rank::world], pos[rank::world], pt, t)
+                ot = o.Transcript(b"range")
+                op = o.SparseBoolSumcheckProver(bn, ot)
+                opr = op.prove(w, pos, pt, ot)
+                assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
+                assert t.challenge_scalar(b"after") == ot.challenge_scalar(b"after")
+        ctx.set_option(ZK_OPT_PEER_EXCHANGE, 1)
         # ---- MSM by point range, KZH commit by x-rows, fix_from_right over the top variables
         from zkes_b200 import curve
         rnd = random.Random(77)

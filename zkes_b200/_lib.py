@@ -97,6 +97,8 @@ SIGNATURES = {
     "zk_gen_small_fr": (c_int, [c_void_p, c_uint64, c_uint64, c_uint64, c_uint64, c_int, c_void_p]),
     "zk_sumcheck_sparse_bool_prove": (c_int, [c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p,
                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "zk_sumcheck_sparse_bool_prove_sharded": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p,
+                                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "zk_sumcheck_general_prove": (c_int, [c_void_p, c_uint32, c_uint32, c_uint32, c_void_p, POINTER(c_void_p), c_void_p,
                                           c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "zk_comm_unique_id": (c_int, [c_void_p]),

@@ -12,18 +12,22 @@ int eq_table_device(zk_ctx* ctx, const uint64_t* point_host, uint32_t k, Fr* poi
 size_t keyset_scratch_bytes(uint32_t n_terms, uint32_t num_var);
 int keyset_order(zk_ctx* ctx, const uint64_t* positions_dev, const uint64_t* term_begin_dev, uint32_t n_terms, uint64_t total,
                  uint32_t num_var, void* scratch, uint32_t* keys_out, uint32_t bad_host[2]);
+int comm_sum_fr_vec(zk_ctx* ctx, zk_comm* c, Fr* vals, uint64_t n);
 }
 
 namespace {
 inline size_t al(size_t x) { return (x + 255) & ~(size_t)255; }
 }
 
-extern "C" {
+namespace {
 
-int zk_sumcheck_sparse_bool_prove(zk_ctx* ctx, uint32_t num_var, uint32_t n_terms, const uint64_t* weights,
-                                  const uint64_t* positions, const uint64_t* n_positions, const uint64_t* eq_point,
-                                  zk_fs_round_fn fs, void* fs_user, zk_transcript* tr, uint64_t* round_msgs,
-                                  uint64_t* challenges, uint64_t* final_eval) {
+// The boolean-check prover; with a communicator the terms given are this rank's share of them (the sum over
+// terms is the only thing the ranks have in common: the partial messages and the partial final value are summed
+// across the ranks, everything else is local).
+int sbool_prove(zk_ctx* ctx, zk_comm* comm, uint32_t num_var, uint32_t n_terms, const uint64_t* weights,
+                const uint64_t* positions, const uint64_t* n_positions, const uint64_t* eq_point,
+                zk_fs_round_fn fs, void* fs_user, zk_transcript* tr, uint64_t* round_msgs,
+                uint64_t* challenges, uint64_t* final_eval) {
   if (!ctx || !final_eval) return fail(ZK_ERR_ARG, "sparse_bool_prove: NULL argument");
   if (n_terms && (!weights || !n_positions)) return fail(ZK_ERR_ARG, "sparse_bool_prove: NULL input");
   if (num_var && (!eq_point || !round_msgs || !challenges)) return fail(ZK_ERR_ARG, "sparse_bool_prove: NULL argument");
@@ -40,7 +44,7 @@ int zk_sumcheck_sparse_bool_prove(zk_ctx* ctx, uint32_t num_var, uint32_t n_term
   if (total >> 31) return fail(ZK_ERR_ARG, "sparse_bool_prove: too many entries");
   const uint32_t K = (uint32_t)total;
 
-  CtxLock lk(ctx);
+  CtxLock lk(ctx, comm != nullptr);  // a sharded call takes the first lane
   ctx = lk.lane;
   cudaStream_t s = ctx->stream;
   const uint64_t size = 1ull << num_var;
@@ -101,9 +105,9 @@ int zk_sumcheck_sparse_bool_prove(zk_ctx* ctx, uint32_t num_var, uint32_t n_term
       ctx->launches++;
     }
     launch_sbool_msg(e_key[e], e_val[e], counts + e, k_upper, round ? eq_rec : eq_cur, d_w, vars_left, round == 0,
-                     ctx->next_msg_scratch(false), s);
+                     ctx->next_msg_scratch(comm != nullptr), s);
     ctx->launches++;
-    rc = fs_round(ctx, nullptr, 4, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
+    rc = fs_round(ctx, comm, 4, round, fs, fs_user, tr, round_msgs, challenges, &challenge);
     if (rc) return rc;
     Fr* eq_next = (round & 1) ? eq0 : eq1;  // eq0 holds 2^n, eq1 2^(n-1); later rounds fit either
     launch_fold(eq_cur, eq_next, challenge, S / 2, ctx->rs.max_blocks, s);
@@ -118,10 +122,33 @@ int zk_sumcheck_sparse_bool_prove(zk_ctx* ctx, uint32_t num_var, uint32_t n_term
   launch_sbool_final(e_key[e], e_val[e], counts + e, eq_cur, d_w, n_terms, ctx->final_out, s);
   ctx->launches++;
   ZK_CUDA(cudaGetLastError());
+  rc = comm_sum_fr_vec(ctx, comm, ctx->final_out, 1);  // the final value is a sum over terms too
+  if (rc) return rc;
   ZK_CUDA(cudaMemcpyAsync(ctx->host_small, ctx->final_out, sizeof(Fr), cudaMemcpyDeviceToHost, s));
   ZK_CUDA(cudaStreamSynchronize(s));
   fr_store(final_eval, *reinterpret_cast<const Fr*>(ctx->host_small));
   return ZK_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int zk_sumcheck_sparse_bool_prove(zk_ctx* ctx, uint32_t num_var, uint32_t n_terms, const uint64_t* weights,
+                                  const uint64_t* positions, const uint64_t* n_positions, const uint64_t* eq_point,
+                                  zk_fs_round_fn fs, void* fs_user, zk_transcript* tr, uint64_t* round_msgs,
+                                  uint64_t* challenges, uint64_t* final_eval) {
+  return sbool_prove(ctx, nullptr, num_var, n_terms, weights, positions, n_positions, eq_point, fs, fs_user, tr, round_msgs,
+                     challenges, final_eval);
+}
+
+int zk_sumcheck_sparse_bool_prove_sharded(zk_ctx* ctx, zk_comm* comm, uint32_t num_var, uint32_t n_local_terms,
+                                          const uint64_t* weights, const uint64_t* positions, const uint64_t* n_positions,
+                                          const uint64_t* eq_point, zk_fs_round_fn fs, void* fs_user, zk_transcript* tr,
+                                          uint64_t* round_msgs, uint64_t* challenges, uint64_t* final_eval) {
+  if (!comm) return fail(ZK_ERR_ARG, "sparse_bool_prove_sharded: NULL communicator");
+  return sbool_prove(ctx, comm, num_var, n_local_terms, weights, positions, n_positions, eq_point, fs, fs_user, tr, round_msgs,
+                     challenges, final_eval);
 }
 
 int zk_sumcheck_general_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, uint32_t n_terms, const uint64_t* scalars,

@@ -126,6 +126,23 @@ def sharded_sparse_dense_prove(ctx, comm: Comm, num_var: int, local_idx, local_v
             from_mont_array(fin)[0])
 
 
+def sharded_sparse_bool_prove(ctx, comm: Comm, num_var: int, local_weights, local_positions, eq_challenge, transcript):
+    """SparseBoolSumcheckProver::prove (linear_prover.rs:486-656) with the terms dealt to the ranks: this rank's
+    weights and position lists in, the proof over all the terms out (the same on every rank)."""
+    n = num_var
+    w = to_mont_array(local_weights) if len(local_weights) else np.zeros((1, 4), dtype=np.uint64)
+    flat = np.array([p for pos in local_positions for p in pos] or [0], dtype=np.uint64)
+    cnt = np.array([len(p) for p in local_positions] or [0], dtype=np.uint64)
+    pt = to_mont_array(eq_challenge) if n else np.zeros((1, 4), dtype=np.uint64)
+    msgs = np.zeros((max(n, 1), 4, 4), dtype=np.uint64)
+    chal = np.zeros((max(n, 1), 4), dtype=np.uint64)
+    fin = np.zeros((1, 4), dtype=np.uint64)
+    check(lib.zk_sumcheck_sparse_bool_prove_sharded(ctx.handle, comm.handle, n, len(local_weights), _p(w), _p(flat), _p(cnt),
+                                                    _p(pt), None, None, transcript.handle, _p(msgs), _p(chal), _p(fin)),
+          "zk_sumcheck_sparse_bool_prove_sharded")
+    return [from_mont_array(msgs[r]) for r in range(n)], from_mont_array(chal[:n]), from_mont_array(fin)[0]
+
+
 def sharded_msm(ctx, comm: Comm, local_bases_arr: np.ndarray, local_scalars):
     """sum over all ranks of MSM(local bases, local scalars) -> affine tuple, the same on every rank."""
     from . import curve

@@ -27,7 +27,8 @@ Simplifications, stated so that the number is read as a trace and not as the bin
 polynomial two (its boolean claim and its lookup claim); the commitment scheme is a parameter (KZH2 as the
 benchmark configuration names it; the bin itself uses KZH3).  At N > 1 GPUs the independent items (commits
 and openings) are dealt round-robin to the ranks with no exchange, as the reference's rayon loop deals the
-openings to threads; the sumchecks share one transcript and run on every rank alike.
+openings to threads; the terms of each boolean-check sumcheck are dealt to the ranks in blocks (the partial
+round messages are summed across the ranks); the other sumchecks share one transcript and run on every rank alike.
 """
 from __future__ import annotations
 
@@ -316,9 +317,19 @@ def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12,
         bchal = np.zeros((m, 4), dtype=np.uint64)
         lib.zk_transcript_append_u64(tr, b"num_var", 7, m)
         lib.zk_transcript_append_u64(tr, b"num_poly", 8, 3)
-        check(lib.zk_sumcheck_sparse_bool_prove(h, m, terms, vp(weights.ctypes.data), vp(positions.data_ptr()), vp(n_pos.ctypes.data),
-                                                vp(point.ctypes.data), None, None, tr, vp(bmsgs.ctypes.data), vp(bchal.ctypes.data),
-                                                vp(fin.ctypes.data)), "zk_sumcheck_sparse_bool_prove")
+        if world > 1 and comm is not None:
+            # the terms are dealt to the ranks in contiguous blocks; the partial messages are summed across the ranks
+            per = (terms + world - 1) // world
+            lo, hi = min(terms, rank * per), min(terms, (rank + 1) * per)
+            check(lib.zk_sumcheck_sparse_bool_prove_sharded(
+                h, comm.handle, m, hi - lo, vp(weights[lo:].ctypes.data), vp(positions.data_ptr() + (lo << n) * 8),
+                vp(n_pos.ctypes.data), vp(point.ctypes.data), None, None, tr, vp(bmsgs.ctypes.data), vp(bchal.ctypes.data),
+                vp(fin.ctypes.data)), "zk_sumcheck_sparse_bool_prove_sharded")
+        else:
+            check(lib.zk_sumcheck_sparse_bool_prove(h, m, terms, vp(weights.ctypes.data), vp(positions.data_ptr()),
+                                                    vp(n_pos.ctypes.data), vp(point.ctypes.data), None, None, tr,
+                                                    vp(bmsgs.ctypes.data), vp(bchal.ctypes.data), vp(fin.ctypes.data)),
+                  "zk_sumcheck_sparse_bool_prove")
     ctx.sync()
     bool_s = time.perf_counter() - t0
 
@@ -415,5 +426,6 @@ def run(ctx, comm=None, rank=0, world=1, seq_len=128, seed=4, dims=2, layers=12,
                   "this_rank": {"dense_commits": n_dense_commits, "sparse_commits": n_sparse_commits,
                                 "dense_openings": n_dense_open, "sparse_openings": n_sparse_open}},
         "parallelism": "1 GPU" if world == 1 else f"commits and openings dealt round-robin to {world} GPUs (no exchange); "
-                                                  "sumchecks and lookup preprocessing on every rank (one shared transcript)",
+                                                  "the terms of the boolean-check sumchecks dealt to the ranks (partial messages summed); "
+                                                  "node proofs and lookup preprocessing on every rank (one shared transcript)",
     }
