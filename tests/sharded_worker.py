@@ -99,6 +99,48 @@ def emulate_sharded_linear(tables, rank, world, label, replicate_entries=0):
     return msgs, chals, [t[0] for t in tail], final
 
 
+def emulate_sharded_sbool(weights, positions, eq_challenge, rank, world, label):
+    """The boolean-check prover with its terms dealt to the ranks (rank r holds terms r, r + world, ...), in big
+    integers: partial round messages over the local terms, all-gather, sum, replicated transcript, local folds;
+    the final value is summed the same way (linear_prover.rs:529-656 run on a share of the terms)."""
+    n = len(eq_challenge)
+    tr = o.Transcript(label)
+    tr.append_u64(b"num_var", n)
+    tr.append_u64(b"num_poly", 3)
+    terms = [(w, sorted((p, 1) for p in pos)) for w, pos in zip(weights[rank::world], positions[rank::world])]
+    eq = o.evaluate_lagrange_basis(eq_challenge)
+
+    def summed(vals):
+        parts = [None] * world
+        dist.all_gather_object(parts, vals)
+        return [sum(p[c] for p in parts) % o.R_MOD for c in range(len(vals))]
+
+    msgs, chals = [], []
+    for _ in range(n):
+        t = [0, 0, 0, 0]
+        for w, entries in terms:
+            for rest, v0, v1 in o._pair_walk(entries):
+                e0, e1 = eq[2 * rest], eq[2 * rest + 1]
+                for c in range(4):
+                    aux = v0 + c * (v1 - v0)
+                    t[c] += w * aux * (aux - 1) * (e0 + c * (e1 - e0))
+        msg = summed([x % o.R_MOD for x in t])
+        for m in msg:
+            tr.append_scalar(b"round_message", m)
+        ch = tr.challenge_scalar(b"challenge")
+        msgs.append(msg)
+        chals.append(ch)
+        eq = o.fix_variables(eq, [ch])
+        terms = [(w, [(rest, (v0 + ch * (v1 - v0)) % o.R_MOD) for rest, v0, v1 in o._pair_walk(entries)
+                      if (v0 + ch * (v1 - v0)) % o.R_MOD]) for w, entries in terms]
+    inner = 0
+    for w, entries in terms:
+        v = entries[0][1] if entries and entries[0][0] == 0 else 0
+        inner += w * v * (v - 1)
+    fin = summed([(eq[0] if eq else 0) * inner % o.R_MOD])[0]
+    return msgs, chals, fin, tr
+
+
 class ExchangeError(Exception):
     def __init__(self, status):
         super().__init__(status)
@@ -314,6 +356,18 @@ def main():
                 rep = emulate_sharded_linear([a, dense, f], rank, world, b"sharded", replicate_entries=entries)
                 assert rep[0] == pr.round_messages and rep[1] == p.challenges and rep[3] == pr.final_eval
                 assert rep[2] == [x[0] for x in p.a_arrays]
+        # the boolean-check prover with its terms dealt to the ranks (with fewer terms than ranks, some hold none)
+        for bn, terms, k in [(3, 1, 4), (5, 3, 9), (7, 2 * world + 1, 40)]:
+            rnd = random.Random(bn * 31 + terms)
+            w = [rnd.randrange(o.R_MOD) for _ in range(terms)]
+            pos = [rnd.sample(range(1 << bn), k) for _ in range(terms)]
+            pt = [rnd.randrange(o.R_MOD) for _ in range(bn)]
+            msgs, chals, fin, tr = emulate_sharded_sbool(w, pos, pt, rank, world, b"range")
+            ot = o.Transcript(b"range")
+            op = o.SparseBoolSumcheckProver(bn, ot)
+            opr = op.prove(w, pos, pt, ot)
+            assert msgs == opr.round_messages and chals == op.challenges and fin == opr.final_eval
+            assert tr.challenge_scalar(b"after") == ot.challenge_scalar(b"after")
     else:
         local_rank = int(os.environ.get("LOCAL_RANK", rank))
         torch.cuda.set_device(local_rank)
