@@ -147,8 +147,11 @@ int zk_sumcheck_sparse_bool_prove_sharded(zk_ctx* ctx, zk_comm* comm, uint32_t n
                                           const uint64_t* eq_point, zk_fs_round_fn fs, void* fs_user, zk_transcript* tr,
                                           uint64_t* round_msgs, uint64_t* challenges, uint64_t* final_eval) {
   if (!comm) return fail(ZK_ERR_ARG, "sparse_bool_prove_sharded: NULL communicator");
-  return sbool_prove(ctx, comm, num_var, n_local_terms, weights, positions, n_positions, eq_point, fs, fs_user, tr, round_msgs,
-                     challenges, final_eval);
+  // collective: after a failure on this rank the communicator is retired here, and the other ranks' bounded waits end
+  return sharded_call(comm, "sparse_bool_prove_sharded", [&] {
+    return sbool_prove(ctx, comm, num_var, n_local_terms, weights, positions, n_positions, eq_point, fs, fs_user, tr,
+                       round_msgs, challenges, final_eval);
+  });
 }
 
 int zk_sumcheck_general_prove(zk_ctx* ctx, uint32_t num_var, uint32_t num_poly, uint32_t n_terms, const uint64_t* scalars,
