@@ -52,6 +52,39 @@ def test_sparse_bool_random(ctx, n, terms, k):
     assert res == pr.final_eval
 
 
+def test_sparse_bool_lookup_scale_verifies(ctx):
+    """At the size of one of the trace's boolean checks (48 selection terms of 2^17 ones over 2^21 positions, 6.3
+    million entries: every warp's span is thousands of entries long and crosses terms, the pair queue fills many
+    times) the oracle's prover would take minutes; instead the proof must pass the verifier with claimed sum 0
+    (dag/mod.rs:1343-1351) and its final value must be eq(point, r) sum_j w_j s_j(r) (s_j(r) - 1) with the s_j(r)
+    summed independently from the eq table of the challenges."""
+    import numpy as np
+    n_low, digit_log, terms = 17, 4, 48
+    n = n_low + digit_log
+    rnd = random.Random(2024)
+    rng = np.random.default_rng(11)
+    w = [rnd.randrange(M) for _ in range(terms)]
+    pt = [rnd.randrange(M) for _ in range(n)]
+    base = np.arange(1 << n_low, dtype=np.uint64)
+    pos = [((rng.integers(0, 1 << digit_log, size=1 << n_low, dtype=np.uint64) << np.uint64(n_low)) | base).tolist()
+           for _ in range(terms)]
+    t = Transcript(b"range")
+    p = SparseBoolSumcheckProver(n, t)
+    pr = p.prove(ctx, w, pos, pt, t)
+    vt = o.Transcript(b"range")
+    res, chals = o.SumcheckVerifier(n, 3, vt).verify(vt, pr.round_messages, 0)
+    assert res is not None and res == pr.final_eval and chals == p.challenges
+    eq_r = o.evaluate_lagrange_basis(chals)
+    inner = 0
+    for wj, pj in zip(w, pos):
+        v = sum(eq_r[x] for x in pj) % M
+        inner += wj * v * (v - 1)
+    eq_val = 1
+    for a, b in zip(pt, chals):
+        eq_val = eq_val * ((a * b + (1 - a) * (1 - b)) % M) % M
+    assert pr.final_eval == eq_val * inner % M
+
+
 def test_sparse_bool_rejects_duplicates(ctx):
     t = Transcript(b"range")
     p = SparseBoolSumcheckProver(3, t)
