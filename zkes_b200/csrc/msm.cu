@@ -557,7 +557,7 @@ __global__ void k_set_infinity(Jacobian* out, uint32_t rows) {
 // indices in non-decreasing order a row is a contiguous run of the list, so the digit, sort and bucket passes of
 // the general MSM are not needed: sixteen lanes take a row, each lane sums its share with mixed additions, a tree over
 // the lanes (through shared memory) finishes the row, and the same walk adds the row's share of C.
-constexpr int kSelLanes = 16;  // lanes per row (a full warp per row measured no faster: the calls are bound by their host steps)
+constexpr int kSelLanes = 16;  // lanes per row (a full warp per row measured 20-35 % slower: twice the tree additions)
 
 __device__ __forceinline__ uint32_t sel_lower_bound(const uint32_t* __restrict__ idx, uint32_t n, uint64_t key) {
   uint32_t lo = 0, hi = n;  // first position with idx >= key
@@ -584,27 +584,29 @@ __global__ void __launch_bounds__(128) k_select_sums(const Affine* __restrict__ 
     acc_c = add_mixed_calls(acc_c, ld_affine(full + v));
     acc_r = add_mixed_calls(acc_r, ld_affine(mid + (v & mask)));
   }
-  // the lanes' shares of a row: a tree through shared memory (the lanes of a row are in one warp)
-  __shared__ Xyzz sh_c[128], sh_r[128];
-  sh_c[threadIdx.x] = acc_c;
-  sh_r[threadIdx.x] = acc_r;
-  __syncwarp();
+  // The lanes' shares of a row: a tree through shared memory.  The time of this kernel follows the number of
+  // warp-wide additions it issues, so the additions of a level are packed into as few warps as they fill: the row
+  // sums' pairs take the first threads of the block, C's pairs the next, and whole warps sit a level out
+  // (128, 64, 32 and 16 additions for the four levels, against two additions by every warp at every level).
+  __shared__ Xyzz sh[2 * 128];  // [0, 128): shares of the rows' sums; [128, 256): shares of C
+  sh[threadIdx.x] = acc_r;
+  sh[128 + threadIdx.x] = acc_c;
+  __syncthreads();
+  constexpr int kRowsPerBlock = 128 / kSelLanes;
 #pragma unroll 1
   for (int off = kSelLanes / 2; off > 0; off >>= 1) {
-    if ((int)gl < off) {
-      add_to(&acc_c, &sh_c[threadIdx.x + off]);
-      add_to(&acc_r, &sh_r[threadIdx.x + off]);
+    const int per_kind = kRowsPerBlock * off;  // additions of this level for one of the two sums
+    if ((int)threadIdx.x < 2 * per_kind) {
+      const int kind = (int)threadIdx.x / per_kind, t = (int)threadIdx.x % per_kind;
+      Xyzz* at = sh + kind * 128 + (t / off) * kSelLanes + (t % off);
+      add_to(at, at + off);
     }
-    __syncwarp();
-    if ((int)gl < off) {
-      sh_c[threadIdx.x] = acc_c;
-      sh_r[threadIdx.x] = acc_r;
-    }
-    __syncwarp();
+    __syncthreads();
   }
+  acc_r = sh[threadIdx.x];
+  Xyzz* sh_c = sh + 128;
   if (group < rows && gl == 0) d_x[group] = to_jacobian(acc_r);
   // the shares of C of the block's rows: one more tree, by the first lanes of the block
-  constexpr int kRowsPerBlock = 128 / kSelLanes;
   constexpr unsigned kRowMask = (1u << kRowsPerBlock) - 1u;
   __syncthreads();  // sh_c[kSelLanes k] holds row k's share
   if (threadIdx.x < kRowsPerBlock) {
