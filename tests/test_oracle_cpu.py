@@ -197,3 +197,42 @@ def test_cpp_g1_against_bigint_oracle():
     assert c.g1_msm([p, p], [1, 1]) == o.g1_mul(p, 2)  # the doubling branch of the mixed addition
     assert c.g1_msm([p, o.g1_neg(p)], [5, 5]) is None
     c.set_threads(1)
+
+
+def test_boolean_check_entrywise_identity():
+    """The algebra the CUDA message kernel of the boolean-check prover relies on (zkes_b200/csrc/general.cu), checked
+    in big integers against the pairwise form of linear_prover.rs:529-591: a pair (v0, v1) contributes, at c = 0..3,
+    aux (aux - 1) eq with aux = v0 + c (v1 - v0); taken entry by entry that is, per entry of value v on side b with
+    q = v^2 and the per-position record {eq(b), eq(2) * (1 + b), eq(3) * (2 + b)}:
+      T(b) += (q - v) rec0;  T(2) += (b ? 2q - v : q + v) rec1;  T(3) += (b ? 3q - v : 2q + v) rec2,
+    plus, where both sides are present, T(2) -= 4 v0 v1 eq(2) and T(3) -= 6 v0 v1 (2 eq(3)).  With every value one
+    (the first round) a lone entry gives 2 eq(2), 6 eq(3) and a pair nothing."""
+    M = o.R_MOD
+    rnd = random.Random(5)
+    for case in range(200):
+        v0 = rnd.randrange(M) if case % 3 != 1 else 0
+        v1 = rnd.randrange(M) if case % 3 != 2 else 0
+        if case >= 150:  # first-round shape: present entries are one
+            v0, v1 = (1 if v0 else 0), (1 if v1 else 0)
+        e0, e1 = rnd.randrange(M), rnd.randrange(M)
+        e = [e0, e1, (2 * e1 - e0) % M, (3 * e1 - 2 * e0) % M]
+        pair = []
+        for cc in range(4):
+            aux = (v0 + cc * (v1 - v0)) % M
+            pair.append(aux * (aux - 1) * e[cc] % M)
+        t = [0, 0, 0, 0]
+        for b, v in ((0, v0), (1, v1)):
+            if v == 0:
+                continue
+            q = v * v % M
+            rec = [e[b], e[2] * (1 + b) % M, e[3] * (2 + b) % M]
+            t[b] += (q - v) * rec[0]
+            t[2] += ((2 * q - v) if b else (q + v)) * rec[1]
+            t[3] += ((3 * q - v) if b else (2 * q + v)) * rec[2]
+        if v0 and v1:
+            t[2] -= 4 * v0 * v1 * e[2]
+            t[3] -= 6 * v0 * v1 * (2 * e[3])
+        assert [x % M for x in t] == pair
+        if case >= 150:
+            lone = (v0 == 1) != (v1 == 1)
+            assert pair == ([0, 0, 2 * e[2] % M, 6 * e[3] % M] if lone else [0, 0, 0, 0])
